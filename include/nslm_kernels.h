@@ -1,0 +1,148 @@
+/* nslm_kernels.h - C ABI of the B200 (sm_100a) seed-decode kernels.
+ *
+ * The kc_* / kq4_* entry points below have the names, argument order and meaning of NanoSeedLM's CUDA kernel
+ * interface (engine/kernels_cuda.h, engine/kernels_qwen4.h), so the reference's C host code (engine/qwen4_cuda.c,
+ * engine/mova_cuda.c, tests/kernel_backend_cuda.c, harness/nslm-mova-kbench.c) links against this library for the
+ * seed mat-vec / grouped GEMM / grouping / combine / expert-cache part of a forward without source changes.  Each
+ * declaration cites the reference declaration it replaces.  The nsl_* entry points are additions (raw-f32 outputs for
+ * parity tests, the bit-exact decode, status words, the expert-parallel layer).
+ *
+ * Conventions (engine/kernels_cuda.h:1-7; engine/qwen4_cuda.c:1219-1234): the first argument is the stream; calls
+ * are asynchronous launches that return void and allocate nothing; the caller owns every buffer; errors surface at the
+ * caller's cudaStreamSynchronize + cudaGetLastError.  Activations are f32 arrays of bf16-rounded values; xs / ys are
+ * row strides in floats.  Only the SEED4P4 weight format (MF_SEED4P4) is implemented: a call with another format
+ * launches nothing and records an error that nsl_last_error() returns. */
+#pragma once
+#include <stddef.h>
+#include <stdint.h>
+
+#include <cuda_runtime_api.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Weight formats: numeric values of engine/kernels_moe.metal:15. */
+enum { MF_BF16 = 0, MF_SEED4 = 1, MF_Q8 = 2, MF_Q4 = 3, MF_SEED4P4 = 4, MF_SEED6P8 = 5, MF_TCQ = 8 };
+
+#define MV_MAXT 8                 /* engine/kernels_moe.metal:16  dense mat-vec: tokens per call */
+#define MMT_BM 64                 /* engine/kernels_cuda.h:115    GEMM tile constants callers size buffers with */
+#define MMT_BN 128                /* engine/kernels_cuda.h:116    pairs per tile-table entry */
+#define MMT_BK 32                 /* engine/kernels_cuda.h:118 */
+#define BUCKET_MAX_EXPERTS 1024   /* engine/kernels_cuda.h:104 */
+#define CACHE_MAX_PER_LAYER 1024  /* engine/kernels_cuda.h:52 */
+#define CACHE_TICK_BASE 0x40000000u /* engine/kernels_cuda.h:48 */
+enum { CACHE_PROTECT_PREV = 2 };  /* engine/kernels_cuda.h:51 */
+
+/* One slice's streams (engine/kernels_cuda.h:19-24).  SEED4P4: p[0] seeds u16 [R][K/8], p[1] coefficient words u16
+ * [R][K/8], p[3] exponent codes, two per byte, block g = r*(K/8)+b in nibble g&1 of byte g>>1; eb the slice's
+ * exponent bias.  Streams may live in device memory or in mapped pinned host memory. */
+typedef struct {
+    const void* p[4];
+    int32_t eb;
+    int32_t gs;
+    int32_t pad[2];
+} WSlice;
+
+/* Grouped GEMM: one expert's run of pairs in perm[] (engine/kernels_moe.metal:130). */
+typedef struct { int32_t slice, start, count, pad; } MmTile;
+
+/* The expert cache (engine/kernels_cuda.h:32-47): field order is the ABI. */
+typedef struct {
+    int32_t* unit_slot;
+    int32_t* slot_unit;
+    uint32_t* slot_last;
+    uint32_t* tick;
+    uint32_t* stats;
+    int32_t* jobs;
+    int32_t* njobs;
+    uint8_t* vram;
+    const uint8_t* host;
+    uint64_t unit_bytes;
+    int32_t slots, per_layer, ntens;
+    WSlice* tab;
+    uint32_t off[3][4];
+    uint64_t hits, misses;
+} CachePool;
+
+/* ---- mat-vec (decode and multi-token verify, T <= MV_MAXT) ---------------------------------------------------------- */
+/* engine/kernels_cuda.h:79  y[t][r] = bf16(W[r] . x[t]); add = 1: y = bf16(y + bf16(acc)).  G: the 65536-entry
+ * lfsr_stream32 table in device memory.  A token's result does not depend on T. */
+void kc_mv(cudaStream_t s, int fmt, WSlice w, int K, int R, const float* x, int xs, float* y, int ys, int T, int add,
+           const uint32_t* G);
+/* engine/kernels_cuda.h:82  pair p uses slice sel[p], input row p / xdiv, output row p. */
+void kc_mv_sel(cudaStream_t s, int fmt, const WSlice* ws, int K, int R, const float* x, int xs, float* y, int ys,
+               const int32_t* sel, int P, int xdiv, const uint32_t* G);
+/* engine/kernels_cuda.h:85  a[p][r] = bf16(silu_bf(bf16(gate . x)) * bf16(up . x)). */
+void kc_mv_gu(cudaStream_t s, int fmt, const WSlice* wg, const WSlice* wu, int K, int R, const float* x, int xs, float* a,
+              int ys, const int32_t* sel, int P, int xdiv, const uint32_t* G);
+
+/* ---- prompt GEMM (tcgen05 tensor-core path) ------------------------------------------------------------------------- */
+/* engine/kernels_cuda.h:96  1: seed weights exact in f32 (three bf16 terms); 0 (default): rounded to bf16. */
+void kc_seed_gemm_f32(int on);
+/* engine/kernels_cuda.h:97 */
+void kc_mm(cudaStream_t s, int fmt, WSlice w, int K, int R, const float* x, int xs, float* y, int ys, int T, int add,
+           const uint32_t* G);
+/* engine/kernels_cuda.h:99 */
+void kc_mm_grouped(cudaStream_t s, int fmt, const WSlice* ws, int K, int R, const float* x, int xs, float* y, int ys,
+                   int xdiv, const int32_t* perm, const MmTile* tiles, int ntiles, const uint32_t* G);
+/* engine/kernels_cuda.h:105  count selections over n experts -> perm, tiles, ntiles (2n+3 ints, [0] = tile count). */
+void kc_bucket(cudaStream_t s, const int32_t* inds, int count, int n, int32_t* perm, MmTile* tiles, int32_t* ntiles);
+/* engine/kernels_cuda.h:106  the tile count read on the device; the grid is max_tiles. */
+void kc_mm_grouped_dev(cudaStream_t s, int fmt, const WSlice* ws, int K, int R, const float* x, int xs, float* y, int ys,
+                       int xdiv, const int32_t* perm, const MmTile* tiles, const int32_t* ntiles, int max_tiles,
+                       const uint32_t* G);
+/* engine/kernels_cuda.h:110-114  activations packed to bf16 once, then reused by the GEMMs. */
+void kc_pack_input_bf16(cudaStream_t s, const float* x, uint16_t* y, size_t n);
+void kc_mm_packed(cudaStream_t s, int fmt, WSlice w, int K, int R, const uint16_t* x, int xs, float* y, int ys, int T, int add,
+                  const uint32_t* G);
+void kc_mm_grouped_packed(cudaStream_t s, int fmt, const WSlice* ws, int K, int R, const uint16_t* x, int xs, float* y, int ys,
+                          int xdiv, const int32_t* perm, const MmTile* tiles, const int32_t* nt, int max_tiles,
+                          const uint32_t* G);
+
+/* ---- elementwise and combine ------------------------------------------------------------------------------------- */
+/* engine/kernels_cuda.h:124  a = bf16(silu_bf(g) * u). */
+void kc_swiglu(cudaStream_t s, const float* g, const float* u, float* a, int n);
+/* engine/kernels_cuda.h:125  x = bf16(x + bf16(bf16(sum_j bf16(D_j bf16(w_j))) + shared)). */
+void kc_moe_combine(cudaStream_t s, const float* D, const float* w, const float* shared, float* x, int d, int k, int T);
+
+/* ---- router and combine of the qwen4 engine ------------------------------------------------------------------------ */
+/* engine/kernels_qwen4.h:53-54  softmax over all experts, top-k, ties to the higher index, weights renormalised.
+ * cfg points at the reference's Qwen4Cfg (nslm/qwen4_cfg.h:9-22); only its n_exp and top_k fields (ints 21 and 22)
+ * are read.  n_exp <= 1024, top_k <= 32. */
+void kq4_route(cudaStream_t s, const void* cfg, const float* logits, int32_t* ind, float* wt, int T);
+void kq4_route_ld(cudaStream_t s, const void* cfg, const float* logits, int ld, int32_t* ind, float* wt, int T);
+/* engine/kernels_qwen4.h:71  out[t] = sum_j wt[t][j] D[t*k+j] + sigmoid(sg[t*sgld]) sh[t], plain f32. */
+void kq4_moe_combine(cudaStream_t s, int d, int k, const float* D, const float* wt, const float* sh, const float* sg,
+                     int sgld, float* out, int T);
+
+/* ---- expert cache -------------------------------------------------------------------------------------------------- */
+/* engine/kernels_cuda.h:53  LRU admit of the units selected by inds[count] of sparse layer sl. */
+void kc_cache_admit(cudaStream_t s, const CachePool* p, int sl, const int32_t* inds, int count, int flags);
+/* engine/kernels_cuda.h:55  the queued units, host arena -> VRAM slots; blocks = the copy's grid. */
+void kc_cache_copy(cudaStream_t s, const CachePool* p, int blocks);
+
+/* ---- additions (no counterpart in the reference's header) ---------------------------------------------------------- */
+/* The router with its two sizes passed directly. */
+void nsl_route(cudaStream_t s, int n_exp, int top_k, const float* logits, int ld, int32_t* ind, float* wt, int T);
+/* Mat-vec with the f32 accumulator stored unrounded (the CPU seed path's result convention,
+ * nslm/lib_cpu_seed4.c:73,100), dense (sel == NULL: ws is a HOST pointer to the one slice, P = T tokens, xdiv = 1) or gathered (ws a device table). */
+void nsl_mv_raw(cudaStream_t s, const WSlice* ws, int K, int R, const float* x, int xs, float* y, int ys,
+                const int32_t* sel, int P, int xdiv, const uint32_t* G);
+/* Rows [0,R) of one slice decoded to the exact f32 weights (nslm/lib_rows.c:49-76) or their bf16 rounding
+ * (nslm/lib_search4.c:22-31): bit-exact.  out is [R][K]. */
+void nsl_decode_f32(cudaStream_t s, WSlice w, int K, int R, float* out, const uint32_t* G);
+void nsl_decode_bf16(cudaStream_t s, WSlice w, int K, int R, uint16_t* out, const uint32_t* G);
+/* Fills a 65536-entry host array with the stream table the G arguments expect (lfsr_stream32 of every seed,
+ * nslm/lfsr.h:53-59). */
+void nsl_stream_table(uint32_t* host_table);
+/* Message of the first host-side argument error since the last call (format not SEED4P4, bad shape), or "". */
+const char* nsl_last_error(void);
+/* Number of kernels this library has launched since it was loaded (bench bookkeeping). */
+uint64_t nsl_launch_count(void);
+/* Multiprocessor count the persistent grids are sized for (queried once per device). */
+int nsl_sm_count(void);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,346 @@
+// The small kernels either side of the seed mat-vec on the MoE path: router top-k, SwiGLU, the two combines, grouping
+// of (token, expert) pairs by expert, activation packing, and the expert cache's admit and copy.
+// Reference behaviour they reproduce: engine/kernels_qwen4.cu:385-422 (router), :506-515 (combine);
+// engine/kernels_moe.cu:775-788 (SwiGLU, MoVA combine), :527-573 (grouping), :2023-2112 (cache), :2196-2201 (pack).
+#include <math.h>
+
+#include "common.cuh"
+#include "seed_block.cuh"
+
+namespace nsl {
+
+constexpr uint32_t FULL = 0xFFFFFFFFu;
+
+// ---- router ------------------------------------------------------------------------------------------------------------
+// One warp per row.  Lane l holds experts l, l+32, ..; k rounds of a warp arg-max where equal logits go to the higher
+// expert id; weights exp(l - max) renormalised over the k picked.
+constexpr int ROUTE_PER_LANE = 32;   // experts <= 1024
+__global__ void __launch_bounds__(128) route_kernel(int E, int k, const float* __restrict__ logits, int ld,
+                                                    int32_t* __restrict__ ind, float* __restrict__ wt, int T) {
+    const int lane = threadIdx.x & 31, t = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (t >= T) return;
+    const float* l = logits + (size_t) t * ld;
+    float v[ROUTE_PER_LANE];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < ROUTE_PER_LANE; ++j) {
+        const int e = lane + 32 * j;
+        v[j] = e < E ? l[e] : -INFINITY;
+        mx = fmaxf(mx, v[j]);
+    }
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(FULL, mx, o));
+    float top = 0.0f, mine = 0.0f;   // lane r keeps round r's unnormalised weight
+    for (int r = 0; r < k; ++r) {
+        float bv = -INFINITY;
+        int bi = -1;
+#pragma unroll
+        for (int j = 0; j < ROUTE_PER_LANE; ++j) {
+            const int e = lane + 32 * j;
+            if (e < E && (v[j] > bv || (v[j] == bv && e > bi))) { bv = v[j]; bi = e; }
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(FULL, bv, o);
+            const int oi = __shfl_xor_sync(FULL, bi, o);
+            if (ov > bv || (ov == bv && oi > bi)) { bv = ov; bi = oi; }
+        }
+#pragma unroll
+        for (int j = 0; j < ROUTE_PER_LANE; ++j)
+            if (lane + 32 * j == bi) v[j] = -INFINITY;
+        const float w = expf(bv - mx);
+        top += w;
+        if (lane == r) mine = w;
+        if (lane == 0) ind[(size_t) t * k + r] = bi;
+    }
+    if (lane < k) wt[(size_t) t * k + lane] = mine / top;
+}
+
+// ---- elementwise --------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float silu_bf16(float g) {
+    const float s = bf16_round(1.0f / (1.0f + expf(-g)));
+    return bf16_round(g * s);
+}
+__global__ void swiglu_kernel(const float* __restrict__ g, const float* __restrict__ u, float* __restrict__ a, int n) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
+        a[i] = bf16_round(silu_bf16(g[i]) * u[i]);
+}
+
+// out[t][i] = sigmoid(sg[t*sgld]) sh[t][i] + sum_j wt[t][j] D[t*k+j][i], plain f32, j ascending; sh == NULL: no shared
+// expert term.
+__global__ void q4_combine_kernel(int d, int k, const float* __restrict__ D, const float* __restrict__ wt,
+                                  const float* __restrict__ sh, const float* __restrict__ sg, int sgld, float* __restrict__ out) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
+    if (i >= d) return;
+    float a = 0.0f;
+    if (sh) a = (1.0f / (1.0f + expf(-sg[(size_t) t * sgld]))) * sh[(size_t) t * d + i];
+    for (int j = 0; j < k; ++j) a += wt[t * k + j] * D[((size_t) t * k + j) * d + i];
+    out[(size_t) t * d + i] = a;
+}
+
+// x = bf16(x + bf16(bf16(sum_j bf16(D_j bf16(w_j))) + shared))
+__global__ void moe_combine_kernel(const float* __restrict__ D, const float* __restrict__ w, const float* __restrict__ shared,
+                                   float* __restrict__ x, int d, int k) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
+    if (c >= d) return;
+    float s = 0.0f;
+    for (int j = 0; j < k; ++j) s += bf16_round(__fmul_rn(D[((size_t) t * k + j) * d + c], bf16_round(w[t * k + j])));
+    const size_t i = (size_t) t * d + c;
+    x[i] = bf16_round(x[i] + bf16_round(bf16_round(s) + shared[i]));
+}
+
+__global__ void pack_bf16_kernel(const float* __restrict__ x, uint16_t* __restrict__ y, size_t n) {
+    const size_t n8 = n / 8;
+    for (size_t i = (size_t) blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (size_t) gridDim.x * blockDim.x) {
+        const float4 a = ((const float4*) x)[2 * i], b = ((const float4*) x)[2 * i + 1];
+        uint4 o;
+        o.x = bf16_bits(a.x) | ((uint32_t) bf16_bits(a.y) << 16);
+        o.y = bf16_bits(a.z) | ((uint32_t) bf16_bits(a.w) << 16);
+        o.z = bf16_bits(b.x) | ((uint32_t) bf16_bits(b.y) << 16);
+        o.w = bf16_bits(b.z) | ((uint32_t) bf16_bits(b.w) << 16);
+        ((uint4*) y)[i] = o;
+    }
+    if (blockIdx.x == 0 && threadIdx.x < (n & 7)) y[n8 * 8 + threadIdx.x] = bf16_bits(x[n8 * 8 + threadIdx.x]);
+}
+
+// ---- grouping ---------------------------------------------------------------------------------------------------------
+// work (2n+3 ints): [0] tile count, [1..n+1] pair offset of each expert, [n+2..2n+2] tile offset of each expert.
+// One block: histogram by shared-memory atomics, then an inclusive scan of pairs and tiles over the experts.
+__global__ void __launch_bounds__(1024) bucket_count_kernel(const int32_t* __restrict__ inds, int count, int n,
+                                                            int32_t* __restrict__ work) {
+    __shared__ int cnt[BUCKET_MAX_EXPERTS];
+    __shared__ int psum[BUCKET_MAX_EXPERTS], tsum[BUCKET_MAX_EXPERTS];
+    const int tid = threadIdx.x;
+    cnt[tid] = 0;
+    __syncthreads();
+    for (int i = tid; i < count; i += 1024) {
+        const int e = inds[i];
+        if (e >= 0 && e < n) atomicAdd(&cnt[e], 1);
+    }
+    __syncthreads();
+    const int c = tid < n ? cnt[tid] : 0;
+    psum[tid] = c;
+    tsum[tid] = (c + MMT_BN - 1) / MMT_BN;
+    __syncthreads();
+    for (int o = 1; o < 1024; o <<= 1) {   // Hillis-Steele inclusive scan
+        const int pv = tid >= o ? psum[tid - o] : 0, tv = tid >= o ? tsum[tid - o] : 0;
+        __syncthreads();
+        psum[tid] += pv;
+        tsum[tid] += tv;
+        __syncthreads();
+    }
+    if (tid < n) {
+        work[1 + tid] = psum[tid] - c;
+        work[2 + n + tid] = tsum[tid] - (c + MMT_BN - 1) / MMT_BN;
+    }
+    if (tid == n - 1 || (n == 0 && tid == 0)) {
+        work[1 + n] = n ? psum[tid] : 0;
+        work[2 + 2 * n] = n ? tsum[tid] : 0;
+        work[0] = n ? tsum[tid] : 0;
+    }
+}
+// One block per expert.  Each warp owns a contiguous range of the pair list: it counts its matches, the block scans the
+// 32 counts, then each warp writes its matches in order (a ballot prefix), so perm is ascending within the expert.
+__global__ void __launch_bounds__(1024) bucket_place_kernel(const int32_t* __restrict__ inds, int count,
+                                                            const int32_t* __restrict__ work, int32_t* __restrict__ perm,
+                                                            MmTile* __restrict__ tiles) {
+    __shared__ int wcount[32];
+    const int e = blockIdx.x, n = gridDim.x, tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    const int begin = work[1 + e], total = work[2 + e] - begin;
+    if (total > 0) {
+        const int per = ((count + 31) / 32 + 31) & ~31;   // pairs per warp, a multiple of 32
+        const int lo = w * per, hi = lo + per < count ? lo + per : count;
+        int mine = 0;
+        for (int i = lo + lane; i - lane < hi; i += 32) {
+            const bool f = i < hi && inds[i] == e;
+            mine += __popc(__ballot_sync(FULL, f));
+        }
+        if (lane == 0) wcount[w] = mine;
+        __syncthreads();
+        int at = begin;
+        for (int q = 0; q < w; ++q) at += wcount[q];
+        for (int i = lo + lane; i - lane < hi; i += 32) {
+            const bool f = i < hi && inds[i] == e;
+            const uint32_t m = __ballot_sync(FULL, f);
+            if (f) perm[at + __popc(m & ((1u << lane) - 1u))] = i;
+            at += __popc(m);
+        }
+        const int t0 = work[2 + n + e];
+        for (int t = tid; t * MMT_BN < total; t += 1024) {
+            MmTile tl = {e, begin + t * MMT_BN, total - t * MMT_BN < MMT_BN ? total - t * MMT_BN : MMT_BN, 0};
+            tiles[t0 + t] = tl;
+        }
+    }
+}
+
+// ---- expert cache -----------------------------------------------------------------------------------------------------
+// Admit (one block): mark the units this call needs; hits get the new tick; misses, in expert order, each take the least
+// recently used slot (ties: lowest slot) that this call has not touched and, with CACHE_PROTECT_PREV, that the previous
+// admit did not touch; the unit's slice tables are pointed at the slot and a (unit, slot) copy job is queued.  When no
+// slot may be replaced the remaining misses are left out (njobs = admitted count).
+__global__ void __launch_bounds__(CACHE_MAX_PER_LAYER) cache_admit_kernel(CachePool p, int sl, const int32_t* __restrict__ inds,
+                                                                         int count, int flags) {
+    __shared__ int need[CACHE_MAX_PER_LAYER];
+    __shared__ int misses[CACHE_MAX_PER_LAYER];
+    __shared__ int wmiss[32], wneed[32];
+    __shared__ unsigned long long best;
+    __shared__ int nmiss;
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    const uint32_t prev = (flags & CACHE_PROTECT_PREV) ? p.tick[0] : 0xFFFFFFFFu;
+    const uint32_t now = p.tick[0] + 1;
+    need[tid] = 0;
+    __syncthreads();
+    for (int i = tid; i < count; i += CACHE_MAX_PER_LAYER) {
+        const int e = inds[i];
+        if (e >= 0 && e < p.per_layer) need[e] = 1;
+    }
+    __syncthreads();
+    const bool is_need = tid < p.per_layer && need[tid];
+    const int slot0 = is_need ? p.unit_slot[(size_t) sl * p.per_layer + tid] : -1;
+    const bool is_miss = is_need && slot0 < 0;
+    if (is_need && slot0 >= 0) p.slot_last[slot0] = now;
+    const uint32_t mb = __ballot_sync(FULL, is_miss), nb = __ballot_sync(FULL, is_need);
+    if (lane == 0) { wmiss[w] = __popc(mb); wneed[w] = __popc(nb); }
+    __syncthreads();
+    if (is_miss) {
+        int at = __popc(mb & ((1u << lane) - 1u));
+        for (int q = 0; q < w; ++q) at += wmiss[q];
+        misses[at] = tid;
+    }
+    if (tid == 0) {
+        int nm = 0, nn = 0;
+        for (int q = 0; q < 32; ++q) { nm += wmiss[q]; nn += wneed[q]; }
+        nmiss = nm;
+        p.tick[0] = now;
+        p.stats[0] += (uint32_t) (nn - nm);
+        p.stats[1] += (uint32_t) nm;
+        *p.njobs = nm;
+        best = ~0ull;
+    }
+    __syncthreads();
+    const int nm = nmiss;
+    for (int m = 0; m < nm; ++m) {
+        unsigned long long key = ~0ull;   // (last use, slot): the minimum is the LRU slot, lowest index on ties
+        for (int s = tid; s < p.slots; s += CACHE_MAX_PER_LAYER) {
+            const uint32_t last = p.slot_last[s];
+            if (last == now || last == prev) continue;
+            const unsigned long long k2 = ((unsigned long long) last << 32) | (uint32_t) s;
+            key = k2 < key ? k2 : key;
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            const unsigned long long k2 = __shfl_xor_sync(FULL, key, o);
+            key = k2 < key ? k2 : key;
+        }
+        if (lane == 0 && key != ~0ull) atomicMin(&best, key);
+        __syncthreads();
+        const unsigned long long got = best;
+        __syncthreads();
+        if (got == ~0ull) {   // nothing may be replaced: stop admitting
+            if (tid == 0) *p.njobs = m;
+            break;
+        }
+        if (tid == 0) {
+            const int slot = (int) (got & 0xFFFFFFFFu), x = misses[m], u = sl * p.per_layer + x, old = p.slot_unit[slot];
+            if (old >= 0) p.unit_slot[old] = -1;
+            p.slot_unit[slot] = u;
+            p.unit_slot[u] = slot;
+            p.slot_last[slot] = now;
+            p.jobs[2 * m] = u;
+            p.jobs[2 * m + 1] = slot;
+            uint8_t* base = p.vram + (uint64_t) slot * p.unit_bytes;
+            for (int i = 0; i < p.ntens; ++i) {
+                WSlice* t = p.tab + ((size_t) sl * p.ntens + i) * p.per_layer + x;
+                for (int st = 0; st < 4; ++st)
+                    if (p.off[i][st] != 0xFFFFFFFFu) t->p[st] = base + p.off[i][st];
+            }
+            best = ~0ull;
+            __threadfence_block();
+        }
+        __syncthreads();
+    }
+}
+
+// Copy (grid = the caller's block count): every queued unit from the host arena (mapped pinned memory, read over PCIe by
+// the kernel) into its slot, 16 bytes per thread per step with four loads in flight per thread.
+__global__ void __launch_bounds__(512) cache_copy_kernel(CachePool p) {
+    const int nj = *p.njobs;
+    const uint64_t words = p.unit_bytes / 16, stride = (uint64_t) gridDim.x * blockDim.x;
+    for (int j = 0; j < nj; ++j) {
+        const uint4* src = (const uint4*) (p.host + (uint64_t) p.jobs[2 * j] * p.unit_bytes);
+        uint4* dst = (uint4*) (p.vram + (uint64_t) p.jobs[2 * j + 1] * p.unit_bytes);
+        uint64_t i = (uint64_t) blockIdx.x * blockDim.x + threadIdx.x;
+        for (; i + 3 * stride < words; i += 4 * stride) {
+            const uint4 a = src[i], b = src[i + stride], c = src[i + 2 * stride], d = src[i + 3 * stride];
+            dst[i] = a; dst[i + stride] = b; dst[i + 2 * stride] = c; dst[i + 3 * stride] = d;
+        }
+        for (; i < words; i += stride) dst[i] = src[i];
+    }
+}
+
+}   // namespace nsl
+
+using namespace nsl;
+
+extern "C" {
+
+void nsl_route(cudaStream_t s, int n_exp, int top_k, const float* logits, int ld, int32_t* ind, float* wt, int T) {
+    if (T <= 0) return;
+    if (n_exp < 1 || n_exp > 32 * ROUTE_PER_LANE || top_k < 1 || top_k > 32 || top_k > n_exp) {
+        set_error("router: %d experts (at most %d), top %d (at most 32)", n_exp, 32 * ROUTE_PER_LANE, top_k);
+        return;
+    }
+    route_kernel<<<(T + 3) / 4, 128, 0, s>>>(n_exp, top_k, logits, ld, ind, wt, T);
+    count_launch();
+}
+void kq4_route_ld(cudaStream_t s, const void* cfg, const float* logits, int ld, int32_t* ind, float* wt, int T) {
+    const int* c = (const int*) cfg;   // Qwen4Cfg: n_exp and top_k are its 22nd and 23rd ints
+    nsl_route(s, c[21], c[22], logits, ld, ind, wt, T);
+}
+void kq4_route(cudaStream_t s, const void* cfg, const float* logits, int32_t* ind, float* wt, int T) {
+    kq4_route_ld(s, cfg, logits, ((const int*) cfg)[21], ind, wt, T);
+}
+
+void kq4_moe_combine(cudaStream_t s, int d, int k, const float* D, const float* wt, const float* sh, const float* sg,
+                     int sgld, float* out, int T) {
+    if (T <= 0 || d <= 0) return;
+    q4_combine_kernel<<<dim3((unsigned) (d + 255) / 256, (unsigned) T), 256, 0, s>>>(d, k, D, wt, sh, sg, sgld, out);
+    count_launch();
+}
+
+void kc_swiglu(cudaStream_t s, const float* g, const float* u, float* a, int n) {
+    if (n <= 0) return;
+    const int blocks = (n + 255) / 256;
+    swiglu_kernel<<<blocks < sm_count() * 16 ? blocks : sm_count() * 16, 256, 0, s>>>(g, u, a, n);
+    count_launch();
+}
+
+void kc_moe_combine(cudaStream_t s, const float* D, const float* w, const float* shared, float* x, int d, int k, int T) {
+    if (T <= 0 || d <= 0) return;
+    moe_combine_kernel<<<dim3((unsigned) (d + 255) / 256, (unsigned) T), 256, 0, s>>>(D, w, shared, x, d, k);
+    count_launch();
+}
+
+void kc_pack_input_bf16(cudaStream_t s, const float* x, uint16_t* y, size_t n) {
+    if (!n) return;
+    const size_t blocks = (n / 8 + 255) / 256 + 1;
+    pack_bf16_kernel<<<(unsigned) (blocks < (size_t) sm_count() * 16 ? blocks : (size_t) sm_count() * 16), 256, 0, s>>>(x, y, n);
+    count_launch();
+}
+
+void kc_bucket(cudaStream_t s, const int32_t* inds, int count, int n, int32_t* perm, MmTile* tiles, int32_t* ntiles) {
+    if (n < 1 || n > BUCKET_MAX_EXPERTS) { set_error("kc_bucket: %d experts, at most %d", n, BUCKET_MAX_EXPERTS); return; }
+    bucket_count_kernel<<<1, 1024, 0, s>>>(inds, count, n, ntiles);
+    bucket_place_kernel<<<(unsigned) n, 1024, 0, s>>>(inds, count, ntiles, perm, tiles);
+    count_launch(2);
+}
+
+void kc_cache_admit(cudaStream_t s, const CachePool* p, int sl, const int32_t* inds, int count, int flags) {
+    if (p->per_layer > CACHE_MAX_PER_LAYER) { set_error("expert cache: %d experts per layer, at most %d", p->per_layer, CACHE_MAX_PER_LAYER); return; }
+    cache_admit_kernel<<<1, CACHE_MAX_PER_LAYER, 0, s>>>(*p, sl, inds, count, flags);
+    count_launch();
+}
+void kc_cache_copy(cudaStream_t s, const CachePool* p, int blocks) {
+    if (blocks < 1) blocks = 1;
+    cache_copy_kernel<<<(unsigned) blocks, 512, 0, s>>>(*p);
+    count_launch();
+}
+
+}   // extern "C"

@@ -1,0 +1,439 @@
+// Seed-decode mat-vec kernels for sm_100a: dense (kc_mv), gathered (kc_mv_sel), fused gate+up+SwiGLU (kc_mv_gu), the
+// raw-f32 variant and the bit-exact decode.  Replaces the SEED4P4 paths of the reference's k_mv / k_mv1 / k_mv_gu
+// (engine/kernels_moe.cu:130-159, 222-348, 2308-2328) and the weight reader used by its tests.
+//
+// Data movement.  A row of K weights is K/8 blocks; a "chunk" is 8 consecutive blocks = one 16-byte load of seeds, one
+// of coefficient words and one 4-byte load of exponent codes.  A lane owns one chunk position of the row (64 inputs),
+// so a warp reads a row's streams as contiguous 512 + 512 + 128 bytes, and the lane's 64 inputs (plus the per-block
+// centring constants) stay in registers while the warp walks over many rows: the only per-row traffic is the packed
+// streams.  Rows shorter than 32 chunks share a warp (K = 512: four rows per step, eight lanes each).
+//
+// Arithmetic per block: the dot form of seed_block.cuh (32 fused multiply-adds on 32 masked stream words, then the
+// four coefficients and the block's 2^code).  A token's sum is formed in the same order whatever the number of tokens
+// in the call (chunks ascending within a lane, blocks ascending within a chunk, then a butterfly over the row's
+// lanes), so a row of a multi-token call equals the single-token call bit for bit, as the reference requires
+// (tests/test_mova_kernels.c:173-183).
+#include <math.h>
+
+#include "common.cuh"
+#include "seed_block.cuh"
+
+namespace nsl {
+
+constexpr int MV_WARPS = 8;
+constexpr int MV_THREADS = 32 * MV_WARPS;
+enum { MODE_ROUND = 0, MODE_GU = 2 };   // the raw-f32 store is a run-time flag of MODE_ROUND
+
+struct MvParams {
+    const WSlice* ws;     // slice table on the device (gather), or NULL: w0
+    const WSlice* wu;     // gate+up: the up slices
+    WSlice w0;            // dense: the slice by value
+    const int32_t* sel;   // pair -> slice, or NULL (dense)
+    const float* x;
+    float* y;
+    const uint32_t* G;
+    int K, R, P, xdiv, xs, ys, add, raw;
+};
+
+__device__ __forceinline__ float silu_bf(float g) {   // each op rounded to bf16 (engine/kernels_moe.cu:28-31)
+    const float s = bf16_round(1.0f / (1.0f + expf(-g)));
+    return bf16_round(g * s);
+}
+
+struct Chunk { uint4 s, c; uint32_t cd; };
+
+__device__ __forceinline__ Chunk load_chunk(const WSlice& w, size_t chunk_index) {
+    Chunk k;
+    k.s = __ldg((const uint4*) w.p[0] + chunk_index);
+    k.c = __ldg((const uint4*) w.p[1] + chunk_index);
+    k.cd = __ldg((const uint32_t*) w.p[3] + chunk_index);
+    return k;
+}
+
+// One chunk (four block pairs) against one token's 64 inputs held in registers as pairs:
+// x2[bp][c] = {x[16 bp + c], x[16 bp + 8 + c]}, xm2[bp][p] likewise.  acc2 = {sum over even blocks, sum over odd blocks}.
+__device__ __forceinline__ u64 chunk_dot(const StreamTab& tab, const KConst& kc, const Chunk& k, const u64* x2, const u64* xm2,
+                                         u64 acc2) {
+    const uint32_t sw[4] = {k.s.x, k.s.y, k.s.z, k.s.w}, cw[4] = {k.c.x, k.c.y, k.c.z, k.c.w};
+#pragma unroll
+    for (int bp = 0; bp < 4; ++bp) {
+        u64 v[32], q[4];
+        pair_states(tab, sw[bp], kc, v);
+        pair_coefs(cw[bp], kc, q);
+        const u64 e2 = pack2(code_scale(k.cd, 2 * bp, kc), code_scale(k.cd, 2 * bp + 1, kc));
+        acc2 = fma2(pair_dot(v, q, x2 + 8 * bp, xm2 + 4 * bp), e2, acc2);
+    }
+    return acc2;
+}
+__device__ __forceinline__ float pair_total(u64 acc2) {
+    float lo, hi;
+    unpack2(acc2, lo, hi);
+    return lo + hi;
+}
+
+__device__ __forceinline__ float group_sum(float v, int lpr) {
+    for (int o = lpr >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+    return v;
+}
+
+template <int MODE>
+__device__ __forceinline__ void store_out(const MvParams& a, int pair, int r, float s, float su) {
+    float* yo = a.y + (size_t) pair * a.ys + r;
+    if (MODE == MODE_GU) *yo = bf16_round(silu_bf(bf16_round(s)) * bf16_round(su));
+    else if (a.raw) *yo = s;
+    else *yo = a.add ? bf16_round(*yo + bf16_round(s)) : bf16_round(s);   // engine/kernels_moe.cu:214
+}
+
+// ---- one token per pair, inputs in registers: rows of 1, 2, 4, .. 32 chunks (K = 64 .. 2048) -------------------------
+// Warps are dealt to pairs (P pairs share the grid's warps evenly); a warp loads its pair's inputs once and strides
+// over the pair's rows, prefetching the next row's streams while it expands the current one.
+template <int MODE>
+__global__ void __launch_bounds__(MV_THREADS, 1) mv_regx_kernel(MvParams a, KConst kc, int lpr_log2) {
+    __shared__ StreamTab tab;
+    load_stream_tab(tab, a.G, threadIdx.x, MV_THREADS);
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int lpr = 1 << lpr_log2, rpw = 32 >> lpr_log2;
+    const int jc = lane & (lpr - 1), ro = lane >> lpr_log2;
+    const int nw = gridDim.x * MV_WARPS, gw = blockIdx.x * MV_WARPS + warp;
+    const int wpp = nw / a.P > 0 ? nw / a.P : 1;
+    const long long nvw = (long long) a.P * wpp;
+    for (long long vw = gw; vw < nvw; vw += nw) {
+        const int pair = (int) (vw / wpp), wi = (int) (vw % wpp);
+        const int slice = a.sel ? a.sel[pair] : 0;
+        const WSlice wa = a.ws ? a.ws[slice] : a.w0;
+        WSlice wb = wa;
+        if (MODE == MODE_GU) wb = a.wu[slice];
+        u64 x2[32], xm2[16];
+        {
+            float x[64], xm[32];
+            const float4* xp = (const float4*) (a.x + (size_t) (pair / a.xdiv) * a.xs + (size_t) jc * 64);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float4 t = __ldg(xp + i);
+                x[4 * i] = t.x; x[4 * i + 1] = t.y; x[4 * i + 2] = t.z; x[4 * i + 3] = t.w;
+            }
+#pragma unroll
+            for (int b = 0; b < 8; ++b) block_offsets(x + 8 * b, xm + 4 * b);
+#pragma unroll
+            for (int bp = 0; bp < 4; ++bp) {
+#pragma unroll
+                for (int c = 0; c < 8; ++c) x2[8 * bp + c] = pack2(x[16 * bp + c], x[16 * bp + 8 + c]);
+#pragma unroll
+                for (int p = 0; p < 4; ++p) xm2[4 * bp + p] = pack2(xm[8 * bp + p], xm[8 * bp + 4 + p]);
+            }
+        }
+        const float sca = slice_scale(wa.eb), scb = slice_scale(wb.eb);
+        const int step = wpp * rpw;
+        int r = wi * rpw + ro;
+        Chunk ka, kb;
+        if (r < a.R) {
+            ka = load_chunk(wa, (size_t) r * lpr + jc);
+            if (MODE == MODE_GU) kb = load_chunk(wb, (size_t) r * lpr + jc);
+        }
+        for (int rbase = wi * rpw; rbase < a.R; rbase += step, r += step) {
+            const bool ok = r < a.R;
+            const int rn = r + step;
+            Chunk na, nb;
+            if (rn < a.R) {   // next row's streams in flight during this row's expansion
+                na = load_chunk(wa, (size_t) rn * lpr + jc);
+                if (MODE == MODE_GU) nb = load_chunk(wb, (size_t) rn * lpr + jc);
+            }
+            float s = 0.0f, su = 0.0f;
+            if (ok) {
+                s = pair_total(chunk_dot(tab, kc, ka, x2, xm2, 0ull));
+                if (MODE == MODE_GU) su = pair_total(chunk_dot(tab, kc, kb, x2, xm2, 0ull));
+            }
+            s = group_sum(s, lpr) * sca;
+            if (MODE == MODE_GU) su = group_sum(su, lpr) * scb;
+            if (ok && jc == 0) store_out<MODE>(a, pair, r, s, su);
+            ka = na;
+            if (MODE == MODE_GU) kb = nb;
+        }
+    }
+}
+
+// ---- inputs in shared memory: NT tokens share each expansion (dense verify rows), or rows longer than 32 chunks ------
+// Dense: the P = NT tokens are staged once per block and the rows are split over every warp of the grid.  Gather
+// (NT = 1): blocks are dealt to pairs and stage their pair's input row.
+// Shared layout, per token: xin2 [K/16 block pairs][8] float2 {x[16 bp + c], x[16 bp + 8 + c]}, then
+// xoff2 [K/16][4] float2 of the centring constants: the operands of pair_dot, loaded 16 bytes at a time.
+template <int MODE, int NT>
+__global__ void __launch_bounds__(MV_THREADS, 1) mv_smemx_kernel(MvParams a, KConst kc, int lpr_log2, int dense) {
+    extern __shared__ __align__(16) float smem_f[];
+    __shared__ StreamTab tab;
+    load_stream_tab(tab, a.G, threadIdx.x, MV_THREADS);
+    const int K = a.K, nbp = K / 16, ch = K / 64;
+    float* xin = smem_f;                           // [NT][K]
+    float* xoff = smem_f + (size_t) NT * K;        // [NT][K/2]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int lpr = 1 << lpr_log2, rpw = 32 >> lpr_log2;
+    const int jc = lane & (lpr - 1), ro = lane >> lpr_log2;
+    const int cpp = dense ? (int) gridDim.x : ((int) gridDim.x / a.P > 0 ? (int) gridDim.x / a.P : 1);
+    const long long nvc = dense ? (long long) gridDim.x : (long long) a.P * cpp;
+    for (long long vc = blockIdx.x; vc < nvc; vc += gridDim.x) {
+        const int pair = dense ? 0 : (int) (vc / cpp), ci = dense ? (int) blockIdx.x : (int) (vc % cpp);
+        const int slice = a.sel ? a.sel[pair] : 0;
+        const WSlice wa = a.ws ? a.ws[slice] : a.w0;
+        WSlice wb = wa;
+        if (MODE == MODE_GU) wb = a.wu[slice];
+        __syncthreads();   // the previous pair's inputs are no longer read
+        for (int i = threadIdx.x; i < NT * nbp; i += MV_THREADS) {
+            const int t = i / nbp, bp = i % nbp;
+            const float* xp = a.x + (size_t) (dense ? t : pair / a.xdiv) * a.xs + 16 * bp;
+            float x[16], xm[8];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float4 v4 = __ldg((const float4*) xp + j);
+                x[4 * j] = v4.x; x[4 * j + 1] = v4.y; x[4 * j + 2] = v4.z; x[4 * j + 3] = v4.w;
+            }
+            block_offsets(x, xm);
+            block_offsets(x + 8, xm + 4);
+            float2* xo = (float2*) (xin + (size_t) t * K) + 8 * bp;
+            float2* mo = (float2*) (xoff + (size_t) t * (K / 2)) + 4 * bp;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) xo[c] = make_float2(x[c], x[8 + c]);
+#pragma unroll
+            for (int p = 0; p < 4; ++p) mo[p] = make_float2(xm[p], xm[4 + p]);
+        }
+        __syncthreads();
+        const float sca = slice_scale(wa.eb), scb = slice_scale(wb.eb);
+        const int wi = ci * MV_WARPS + warp, step = cpp * MV_WARPS * rpw;
+        for (int rbase = wi * rpw; rbase < a.R; rbase += step) {
+            const int r = rbase + ro;
+            const bool ok = r < a.R;
+            u64 s2[NT], su2[NT];
+#pragma unroll
+            for (int t = 0; t < NT; ++t) s2[t] = su2[t] = 0ull;
+            if (ok) {
+                for (int j = jc; j < ch; j += lpr) {
+                    const Chunk ka = load_chunk(wa, (size_t) r * ch + j);
+                    Chunk kb = ka;
+                    if (MODE == MODE_GU) kb = load_chunk(wb, (size_t) r * ch + j);
+#pragma unroll
+                    for (int half = 0; half < (MODE == MODE_GU ? 2 : 1); ++half) {
+                        const Chunk& k = half ? kb : ka;
+                        const uint32_t sw[4] = {k.s.x, k.s.y, k.s.z, k.s.w}, cw[4] = {k.c.x, k.c.y, k.c.z, k.c.w};
+#pragma unroll
+                        for (int bp = 0; bp < 4; ++bp) {
+                            u64 v[32], q[4];
+                            pair_states(tab, sw[bp], kc, v);
+                            pair_coefs(cw[bp], kc, q);
+                            const u64 e2 = pack2(code_scale(k.cd, 2 * bp, kc), code_scale(k.cd, 2 * bp + 1, kc));
+                            const int gbp = j * 4 + bp;
+#pragma unroll
+                            for (int t = 0; t < NT; ++t) {
+                                u64 x2[8], xm2[4];
+                                const ulonglong2* xs2 = (const ulonglong2*) ((const float2*) (xin + (size_t) t * K) + 8 * gbp);
+                                const ulonglong2* ms2 = (const ulonglong2*) ((const float2*) (xoff + (size_t) t * (K / 2)) + 4 * gbp);
+#pragma unroll
+                                for (int c = 0; c < 4; ++c) { const ulonglong2 u = xs2[c]; x2[2 * c] = u.x; x2[2 * c + 1] = u.y; }
+#pragma unroll
+                                for (int p = 0; p < 2; ++p) { const ulonglong2 u = ms2[p]; xm2[2 * p] = u.x; xm2[2 * p + 1] = u.y; }
+                                const u64 d = pair_dot(v, q, x2, xm2);
+                                if (half) su2[t] = fma2(d, e2, su2[t]);
+                                else s2[t] = fma2(d, e2, s2[t]);
+                            }
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+                const float st = group_sum(pair_total(s2[t]), lpr) * sca;
+                float sut = 0.0f;
+                if (MODE == MODE_GU) sut = group_sum(pair_total(su2[t]), lpr) * scb;
+                if (ok && jc == 0) store_out<MODE>(a, dense ? t : pair, r, st, sut);
+            }
+        }
+    }
+}
+
+// ---- any K that is a multiple of 8, any alignment: one warp per (pair or dense, row), lanes over single blocks -------
+template <int MODE>
+__global__ void __launch_bounds__(MV_THREADS) mv_generic_kernel(MvParams a, KConst kc, int T) {
+    __shared__ StreamTab tab;
+    load_stream_tab(tab, a.G, threadIdx.x, MV_THREADS);
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nb = a.K / 8, dense = a.sel == NULL;
+    const long long ntask = (long long) (dense ? 1 : a.P) * a.R;
+    for (long long task = (long long) blockIdx.x * MV_WARPS + warp; task < ntask; task += (long long) gridDim.x * MV_WARPS) {
+        const int pair = (int) (task / a.R), r = (int) (task % a.R);
+        const int slice = a.sel ? a.sel[pair] : 0;
+        const WSlice wa = a.ws ? a.ws[slice] : a.w0;
+        WSlice wb = wa;
+        if (MODE == MODE_GU) wb = a.wu[slice];
+        float s[MV_MAXT], su[MV_MAXT];
+#pragma unroll
+        for (int t = 0; t < MV_MAXT; ++t) s[t] = su[t] = 0.0f;
+        for (int j = lane; j < nb; j += 32) {
+            const size_t gidx = (size_t) r * nb + j;
+#pragma unroll
+            for (int half = 0; half < (MODE == MODE_GU ? 2 : 1); ++half) {
+                const WSlice& w = half ? wb : wa;
+                const uint32_t seed = ((const uint16_t*) w.p[0])[gidx], cwi = ((const uint16_t*) w.p[1])[gidx];
+                const uint32_t code = (((const uint8_t*) w.p[3])[gidx >> 1] >> ((gidx & 1) * 4)) & 15u;
+                const uint32_t g = stream_bits(tab, seed);
+                const uint32_t aw = seed | (g << 16);
+                float v[32], q[4];
+                block_states(aw, g, kc, v);
+                block_coefs(cwi, kc, q);
+                const float e2 = __uint_as_float((code << 23) | 0x38000000u);
+#pragma unroll
+                for (int t = 0; t < MV_MAXT; ++t) {
+                    if (t >= T) break;
+                    const float* xp = a.x + (size_t) (dense ? t : pair / a.xdiv) * a.xs + (size_t) j * 8;
+                    float xr[8], xo[4];
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) xr[c] = __ldg(xp + c);
+                    block_offsets(xr, xo);
+                    const float d = states_dot(v, q, xr, xo);
+                    if (half) su[t] = fmaf(d, e2, su[t]);
+                    else s[t] = fmaf(d, e2, s[t]);
+                }
+            }
+        }
+        const float sca = slice_scale(wa.eb), scb = slice_scale(wb.eb);
+#pragma unroll
+        for (int t = 0; t < MV_MAXT; ++t) {
+            if (t >= T) break;
+            const float st = group_sum(s[t], 32) * sca;
+            float sut = 0.0f;
+            if (MODE == MODE_GU) sut = group_sum(su[t], 32) * scb;
+            if (lane == 0) store_out<MODE>(a, dense ? t : pair, r, st, sut);
+        }
+    }
+}
+
+// ---- bit-exact decode: one thread per block ---------------------------------------------------------------------------
+template <bool BF16>
+__global__ void __launch_bounds__(256) decode_kernel(WSlice w, KConst kc, int K, int R, void* out, const uint32_t* G) {
+    __shared__ StreamTab tab;
+    load_stream_tab(tab, G, threadIdx.x, 256);
+    __syncthreads();
+    const size_t nblk = (size_t) R * (K / 8);
+    for (size_t gidx = (size_t) blockIdx.x * 256 + threadIdx.x; gidx < nblk; gidx += (size_t) gridDim.x * 256) {
+        const uint32_t seed = ((const uint16_t*) w.p[0])[gidx], cw = ((const uint16_t*) w.p[1])[gidx];
+        const int code = (((const uint8_t*) w.p[3])[gidx >> 1] >> ((gidx & 1) * 4)) & 15;
+        const uint32_t g = stream_bits(tab, seed);
+        float wv[8];
+        block_weights(seed | (g << 16), g, cw, exact_scale16(w.eb + code), kc, wv);
+        if (BF16) {
+            uint4 o;
+            o.x = bf16_bits(wv[0]) | ((uint32_t) bf16_bits(wv[1]) << 16);
+            o.y = bf16_bits(wv[2]) | ((uint32_t) bf16_bits(wv[3]) << 16);
+            o.z = bf16_bits(wv[4]) | ((uint32_t) bf16_bits(wv[5]) << 16);
+            o.w = bf16_bits(wv[6]) | ((uint32_t) bf16_bits(wv[7]) << 16);
+            ((uint4*) out)[gidx] = o;
+        } else {
+            ((float4*) out)[2 * gidx] = make_float4(wv[0], wv[1], wv[2], wv[3]);
+            ((float4*) out)[2 * gidx + 1] = make_float4(wv[4], wv[5], wv[6], wv[7]);
+        }
+    }
+}
+
+// ---- launch selection ---------------------------------------------------------------------------------------------------
+static int log2_floor(int v) { int l = 0; while ((2 << l) <= v) ++l; return l; }
+
+template <int MODE, int NT>
+static void launch_smemx(cudaStream_t s, const MvParams& a, int lpr_log2, int dense, int grid, size_t smem) {
+    static bool attr_set[16];   // per device
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_set[dev & 15]) {
+        cudaFuncSetAttribute(mv_smemx_kernel<MODE, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin() - 4096);
+        attr_set[dev & 15] = true;
+    }
+    mv_smemx_kernel<MODE, NT><<<grid, MV_THREADS, smem, s>>>(a, kconst(), lpr_log2, dense);
+}
+
+template <int MODE>
+static void launch_mv(cudaStream_t s, const MvParams& a, int T) {
+    if (a.R <= 0 || a.P <= 0 || T <= 0) return;
+    if (a.K <= 0 || a.K % 8) { set_error("seed mat-vec: K = %d is not a multiple of 8", a.K); return; }
+    if (T > MV_MAXT) { set_error("seed mat-vec: %d tokens, at most %d", T, MV_MAXT); return; }
+    const int dense = a.sel == NULL, sms = sm_count();
+    const int ch = a.K / 64;
+    // The chunked kernels need whole chunks and 16-byte aligned rows of inputs; streams come 16-byte aligned from
+    // every allocator the callers use, and a row's chunks are contiguous, so only the inputs are checked here.
+    const bool chunked = a.K % 64 == 0 && aligned16(a.x) && a.xs % 4 == 0;
+    const bool pow2 = ch > 0 && (ch & (ch - 1)) == 0;
+    if (chunked && T == 1 && pow2 && ch <= 32) {
+        mv_regx_kernel<MODE><<<sms, MV_THREADS, 0, s>>>(a, kconst(), log2_floor(ch));
+        count_launch();
+        return;
+    }
+    const size_t smem = (size_t) (dense ? T : 1) * a.K * 6;   // inputs [K] and centring constants [K/2] per token
+    if (chunked && smem <= (size_t) max_smem_optin() - 4096) {
+        const int lpr_log2 = log2_floor(ch < 32 ? ch : 32);
+        if constexpr (MODE == MODE_GU) launch_smemx<MODE, 1>(s, a, lpr_log2, dense, sms, smem);
+        else switch (dense ? T : 1) {
+#define NSL_CASE(N) case N: launch_smemx<MODE, N>(s, a, lpr_log2, dense, sms, smem); break;
+            NSL_CASE(1) NSL_CASE(2) NSL_CASE(3) NSL_CASE(4) NSL_CASE(5) NSL_CASE(6) NSL_CASE(7) NSL_CASE(8)
+#undef NSL_CASE
+        }
+        count_launch();
+        return;
+    }
+    mv_generic_kernel<MODE><<<sms * 2, MV_THREADS, 0, s>>>(a, kconst(), dense ? T : 1);
+    count_launch();
+}
+
+static bool seed_fmt(int fmt, const char* who) {
+    if (fmt == MF_SEED4P4) return true;
+    set_error("%s: weight format %d is not served by this library (SEED4P4 = %d only)", who, fmt, (int) MF_SEED4P4);
+    return false;
+}
+
+}   // namespace nsl
+
+using namespace nsl;
+
+extern "C" {
+
+void kc_mv(cudaStream_t s, int fmt, WSlice w, int K, int R, const float* x, int xs, float* y, int ys, int T, int add,
+           const uint32_t* G) {
+    if (!seed_fmt(fmt, "kc_mv")) return;
+    MvParams a = {NULL, NULL, w, NULL, x, y, G, K, R, T, 1, xs, ys, add, 0};
+    launch_mv<MODE_ROUND>(s, a, T);
+}
+
+void kc_mv_sel(cudaStream_t s, int fmt, const WSlice* ws, int K, int R, const float* x, int xs, float* y, int ys,
+               const int32_t* sel, int P, int xdiv, const uint32_t* G) {
+    if (!seed_fmt(fmt, "kc_mv_sel")) return;
+    MvParams a = {ws, NULL, WSlice{}, sel, x, y, G, K, R, P, xdiv, xs, ys, 0, 0};
+    launch_mv<MODE_ROUND>(s, a, 1);
+}
+
+void kc_mv_gu(cudaStream_t s, int fmt, const WSlice* wg, const WSlice* wu, int K, int R, const float* x, int xs, float* out,
+              int ys, const int32_t* sel, int P, int xdiv, const uint32_t* G) {
+    if (!seed_fmt(fmt, "kc_mv_gu")) return;
+    MvParams a = {wg, wu, WSlice{}, sel, x, out, G, K, R, P, xdiv, xs, ys, 0, 0};
+    launch_mv<MODE_GU>(s, a, 1);
+}
+
+void nsl_mv_raw(cudaStream_t s, const WSlice* ws, int K, int R, const float* x, int xs, float* y, int ys,
+                const int32_t* sel, int P, int xdiv, const uint32_t* G) {
+    MvParams a = {sel ? ws : NULL, NULL, WSlice{}, sel, x, y, G, K, R, P, xdiv > 0 ? xdiv : 1, xs, ys, 0, 1};
+    if (!sel) a.w0 = *ws;   // dense: ws is a host pointer to the one slice
+    launch_mv<MODE_ROUND>(s, a, sel ? 1 : P);
+}
+
+void nsl_decode_f32(cudaStream_t s, WSlice w, int K, int R, float* out, const uint32_t* G) {
+    if (K <= 0 || K % 8 || R <= 0) { if (K % 8) set_error("nsl_decode_f32: K = %d is not a multiple of 8", K); return; }
+    const size_t nblk = (size_t) R * (K / 8);
+    const int grid = (int) ((nblk + 255) / 256 < (size_t) sm_count() * 8 ? (nblk + 255) / 256 : (size_t) sm_count() * 8);
+    decode_kernel<false><<<grid, 256, 0, s>>>(w, kconst(), K, R, out, G);
+    count_launch();
+}
+
+void nsl_decode_bf16(cudaStream_t s, WSlice w, int K, int R, uint16_t* out, const uint32_t* G) {
+    if (K <= 0 || K % 8 || R <= 0) { if (K % 8) set_error("nsl_decode_bf16: K = %d is not a multiple of 8", K); return; }
+    const size_t nblk = (size_t) R * (K / 8);
+    const int grid = (int) ((nblk + 255) / 256 < (size_t) sm_count() * 8 ? (nblk + 255) / 256 : (size_t) sm_count() * 8);
+    decode_kernel<true><<<grid, 256, 0, s>>>(w, kconst(), K, R, out, G);
+    count_launch();
+}
+
+}   // extern "C"

@@ -1,0 +1,93 @@
+"""ctypes view of libnslm_b200.so: the C ABI declared in include/nslm_kernels.h.
+
+There is no fallback: if the library is missing the import of the kernels fails with instructions to build it, and
+every call goes to the CUDA kernels.  torch is used only for device memory and streams."""
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libnslm_b200.so")
+
+MF_SEED4P4 = 4
+MV_MAXT = 8
+MMT_BN = 128
+MMT_BM = 64
+
+
+class WSlice(C.Structure):
+    _fields_ = [("p", C.c_void_p * 4), ("eb", C.c_int32), ("gs", C.c_int32), ("pad", C.c_int32 * 2)]
+
+
+class MmTile(C.Structure):
+    _fields_ = [("slice", C.c_int32), ("start", C.c_int32), ("count", C.c_int32), ("pad", C.c_int32)]
+
+
+class CachePool(C.Structure):
+    _fields_ = [("unit_slot", C.c_void_p), ("slot_unit", C.c_void_p), ("slot_last", C.c_void_p), ("tick", C.c_void_p),
+                ("stats", C.c_void_p), ("jobs", C.c_void_p), ("njobs", C.c_void_p), ("vram", C.c_void_p),
+                ("host", C.c_void_p), ("unit_bytes", C.c_uint64), ("slots", C.c_int32), ("per_layer", C.c_int32),
+                ("ntens", C.c_int32), ("tab", C.c_void_p), ("off", (C.c_uint32 * 4) * 3), ("hits", C.c_uint64),
+                ("misses", C.c_uint64)]
+
+
+assert C.sizeof(WSlice) == 48 and C.sizeof(MmTile) == 16
+
+_vp, _i, _sz = C.c_void_p, C.c_int, C.c_size_t
+
+# name -> (restype, argtypes): every symbol include/nslm_kernels.h declares
+PROTOTYPES = {
+    "kc_mv": (None, [_vp, _i, WSlice, _i, _i, _vp, _i, _vp, _i, _i, _i, _vp]),
+    "kc_mv_sel": (None, [_vp, _i, _vp, _i, _i, _vp, _i, _vp, _i, _vp, _i, _i, _vp]),
+    "kc_mv_gu": (None, [_vp, _i, _vp, _vp, _i, _i, _vp, _i, _vp, _i, _vp, _i, _i, _vp]),
+    "kc_seed_gemm_f32": (None, [_i]),
+    "kc_mm": (None, [_vp, _i, WSlice, _i, _i, _vp, _i, _vp, _i, _i, _i, _vp]),
+    "kc_mm_grouped": (None, [_vp, _i, _vp, _i, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _vp]),
+    "kc_bucket": (None, [_vp, _vp, _i, _i, _vp, _vp, _vp]),
+    "kc_mm_grouped_dev": (None, [_vp, _i, _vp, _i, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _vp]),
+    "kc_pack_input_bf16": (None, [_vp, _vp, _vp, _sz]),
+    "kc_mm_packed": (None, [_vp, _i, WSlice, _i, _i, _vp, _i, _vp, _i, _i, _i, _vp]),
+    "kc_mm_grouped_packed": (None, [_vp, _i, _vp, _i, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _vp]),
+    "kc_swiglu": (None, [_vp, _vp, _vp, _vp, _i]),
+    "kc_moe_combine": (None, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i]),
+    "kq4_route": (None, [_vp, _vp, _vp, _vp, _vp, _i]),
+    "kq4_route_ld": (None, [_vp, _vp, _vp, _i, _vp, _vp, _i]),
+    "kq4_moe_combine": (None, [_vp, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _i]),
+    "kc_cache_admit": (None, [_vp, C.POINTER(CachePool), _i, _vp, _i, _i]),
+    "kc_cache_copy": (None, [_vp, C.POINTER(CachePool), _i]),
+    "nsl_route": (None, [_vp, _i, _i, _vp, _i, _vp, _vp, _i]),
+    "nsl_mv_raw": (None, [_vp, _vp, _i, _i, _vp, _i, _vp, _i, _vp, _i, _i, _vp]),
+    "nsl_decode_f32": (None, [_vp, WSlice, _i, _i, _vp, _vp]),
+    "nsl_decode_bf16": (None, [_vp, WSlice, _i, _i, _vp, _vp]),
+    "nsl_stream_table": (None, [_vp]),
+    "nsl_last_error": (C.c_char_p, []),
+    "nsl_launch_count": (C.c_uint64, []),
+    "nsl_sm_count": (_i, []),
+}
+
+_lib = None
+
+
+def load():
+    """The library handle with every prototype set.  Raises when the library has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(f"{LIB_PATH} is missing: run `python -m nanoseedlm_b200.build` (there is no CPU path)")
+        lib = C.CDLL(LIB_PATH)
+        for name, (res, args) in PROTOTYPES.items():
+            fn = getattr(lib, name)   # AttributeError if the library does not export a declared symbol
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+def last_error():
+    return load().nsl_last_error().decode()
+
+
+def check():
+    """Raise if a call since the last check was refused for its arguments."""
+    msg = last_error()
+    if msg:
+        raise RuntimeError(msg)

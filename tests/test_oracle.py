@@ -1,0 +1,130 @@
+"""The CPU oracle against the reference's known answers and against fixtures produced by the reference's own code
+(tests/golden/make_golden.py).  No GPU."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+
+def test_period_and_first_states(oracle):
+    # reference: tests/test_lfsr.c:15-30
+    assert oracle.lib().orc_period() == 65535
+    assert list(oracle.states(1, 6)) == [0x8000, 0x4000, 0x2000, 0x1000, 0x8800, 0x4400]
+    assert oracle.states(0xACE1, 1)[0] != 0xACE1
+
+
+def test_fnv_golden_over_all_seeds(oracle):
+    # reference: tests/test_lfsr.c:41-56
+    assert oracle.lib().orc_fnv24_all_seeds() == 0x740E86E513D34463
+
+
+def test_stream_table_linear_and_windows(oracle):
+    # reference: tests/test_lfsr.c:87-93; window rule nslm/lib_rows.c:59,71
+    t = oracle.table32()
+    s = np.arange(65536)
+    assert np.array_equal(t[s], t[s & 0xFF] ^ t[s & 0xFF00])
+    for seed in (1, 0xACE1, 65535, 777):
+        st = oracle.states(seed, 32)
+        win = seed | (int(t[seed]) << 16)
+        assert all(((win >> k) & 0xFFFF) == st[k - 1] for k in range(1, 33))
+
+
+def test_states_match_reference_fixture(oracle, golden):
+    for i, seed in enumerate(golden["st_seeds"]):
+        assert np.array_equal(oracle.states(int(seed), 48), golden["states"][i])
+        assert int(oracle.table32()[int(seed)]) == int(golden["stream"][i])
+
+
+def test_block_decode_matches_reference_fixture(oracle, golden):
+    for i in range(len(golden["blk_seed"])):
+        got = oracle.decode_block_bf16(int(golden["blk_seed"][i]), int(golden["blk_coef"][i]), int(golden["blk_e"][i]))
+        assert np.array_equal(got, golden["blk_bf16"][i]), i
+
+
+def test_block_decode_against_double(oracle):
+    # reference: tests/test_search4.c:38-56
+    rng = np.random.default_rng(3)
+    r32 = np.float32(1.0) / np.float32(32767.0)
+    for it in range(500):
+        seed, coef, e = int(rng.integers(1, 65536)), int(rng.integers(0, 65536)), -20 + it % 9
+        st = oracle.states(seed, 32).astype(np.int64)
+        q = [oracle.lib().orc_q4(C.c_uint16(coef), p) for p in range(4)]
+        want = []
+        for c in range(8):
+            isum = sum((int(st[4 * c + p]) - 32768) * q[p] for p in range(4))
+            w = np.float32(isum) * (r32 * np.float32(2.0 ** e))
+            u = int(np.float32(w).view(np.uint32))
+            u = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFFFFFF
+            want.append(u >> 16)
+        assert list(oracle.decode_block_bf16(seed, coef, e)) == want
+
+
+def test_rows_match_reference_fixture_mid_byte_rows(oracle, golden):
+    rows, K, eb = (int(v) for v in golden["row_shape"])
+    m = oracle.Matrix(rows, K, 0, eb=eb)
+    m.seeds[:], m.coefs[:], m.codes[:] = golden["row_seeds"], golden["row_coefs"], golden["row_codes"]
+    w = oracle.decode_rows_f32(m)
+    assert np.array_equal(w.view(np.uint32), golden["row_f32"].view(np.uint32))
+    bf = oracle.decode_rows_bf16(m)
+    u = golden["row_f32"].view(np.uint32).astype(np.uint64)
+    assert np.array_equal(bf, ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16))
+
+
+def test_route_matches_reference_fixture(oracle, golden):
+    # reference: tests/test_qwen4_kernels.c:223-245 (the tie goes to the higher expert: 300 before 7)
+    ind, wt = oracle.route(golden["route_logits"], 10)
+    assert np.array_equal(ind, golden["route_ind"]) and ind[0, 0] == 300 and ind[0, 1] == 7
+    assert np.array_equal(wt, golden["route_wt"])
+
+
+def test_against_reference_library_when_built(oracle):
+    R = oracle.ref()
+    if R is None:
+        pytest.skip("oracle/_ref not built here (it needs the reference tree)")
+    rng = np.random.default_rng(11)
+    u16p = C.POINTER(C.c_uint16)
+    for _ in range(3000):
+        seed, coef, e = int(rng.integers(1, 65536)), int(rng.integers(0, 65536)), int(rng.integers(-30, 1))
+        o = np.zeros(8, np.uint16)
+        R.ref_decode_block(C.c_uint16(seed), C.c_uint16(coef), e, o.ctypes.data_as(u16p))
+        assert np.array_equal(o, oracle.decode_block_bf16(seed, coef, e))
+
+
+def test_bucket_grouping(oracle):
+    # reference: tests/test_qwen4_engine.c:34-61 (skewed selections, half on expert 0)
+    for n, rows, k in ((128, 512, 10), (64, 128, 8)):
+        P = rows * k
+        x = 12345
+        inds = np.zeros(P, np.int32)
+        for i in range(P):
+            x = (x * 1664525 + 1013904223) & 0xFFFFFFFF
+            inds[i] = ((x >> 8) % n) * ((x >> 4) & 1)
+        perm, tiles = oracle.bucket(inds, n)
+        at = 0
+        ti = 0
+        for e in range(n):
+            ids = np.nonzero(inds == e)[0]
+            assert np.array_equal(perm[at:at + len(ids)], ids)
+            for s in range(at, at + len(ids), 128):
+                assert tiles[ti] == (e, s, min(128, at + len(ids) - s))
+                ti += 1
+            at += len(ids)
+        assert ti == len(tiles)
+
+
+def test_rounding_points(oracle):
+    g = np.array([0.5, -1.25, 3.0, 0.0], np.float32)
+    u = np.array([2.0, 0.5, -1.0, 7.0], np.float32)
+    a = oracle.swiglu(g, u)
+    oracle.lib().orc_bfr.restype = C.c_float
+    oracle.lib().orc_bfr.argtypes = [C.c_float]
+    for i in range(4):
+        s = np.float32(oracle.lib().orc_silu_bf(C.c_float(float(g[i]))))
+        assert a[i] == np.float32(oracle.lib().orc_bfr(C.c_float(float(s * u[i]))))
+    assert a[3] == 0.0 and a[0] > 0
+    m = oracle.Matrix(24, 256, 5, eb=-19)
+    x = oracle.normal(1, 256, bf16=True)
+    y64, _ = oracle.matvec_f64(m, x)
+    y = oracle.mv(m, x)
+    assert np.all(np.abs(y[0] - y64[0]) <= np.abs(y64[0]) / 128 + 1e-30)   # one bf16 ulp
+    assert np.array_equal(y.view(np.uint32) & 0xFFFF, np.zeros_like(y.view(np.uint32)))
