@@ -1,0 +1,296 @@
+#!/usr/bin/env python
+"""Benchmark of the seed-decode MoE expert layer (BASELINE.json config 1) on B200.
+
+    python bench.py --gpus 1 --steps 200 --warmup 10              # this library (CUDA kernels behind the C ABI)
+    python bench.py --impl reference --steps 3 --warmup 1          # the CPU seed path on the host cores
+
+A step is one pass of the hot path over one batch: router top-8 over 128 experts, the routed experts' gate + up +
+SwiGLU and down projections regenerated from their seeds, and the weighted combine, for M tokens (default 8, the
+multi-token-prediction verify batch; --tokens 1 or 4 give the other rows of config 1).  Steps rotate over enough
+independent synthetic layers that every step's packed streams come from HBM, not L2.
+
+One JSON line is printed (rank 0).  value = tokens/s with inputs resident in HBM; e2e = the same through
+nsl_moe_forward_pinned with host buffers (H2D of the step's inputs from pinned memory, D2H of its output, every step);
+roofline = the dominant kernel (gate+up mat-vec) against the measured HBM copy peak; cpu_baseline = the CPU
+restatement of the reference's seed mat-vec timed on this host."""
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+D, FF, E, TOPK = 2048, 512, 128, 8
+BYTES_PER_MATRIX = D * FF // 8 * 4 + D * FF // 16        # 589,824: seeds + coefficient words + exponent codes
+WEIGHTS_PER_TOKEN = TOPK * 3 * D * FF                      # 25,165,824
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        return json.load(open(path)), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"], stdout=subprocess.PIPE, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            time.sleep(0.25)
+            self.proc.terminate()
+            self.t.join(timeout=2)
+
+    def summary(self):
+        sm = sorted(float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit())
+        mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 7 for n, v in zip(names, r[3:7]) if v.lower().startswith("active")})
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(sm)}
+
+
+def cpu_baseline(threads, seconds=12.0):
+    """The CPU seed mat-vec (oracle/cpu_seed4_port.c) on one config-1 decode token: 8 experts x (gate, up, down)."""
+    from oracle import binding as B
+    gate = B.Matrix(FF, D, 101)
+    down = B.Matrix(D, FF, 102)
+    xg, xd = B.normal(1, D), B.normal(2, FF)
+    t0 = time.perf_counter()
+    tg, _ = B.cpu_seed4_time(gate, xg, threads, 3)
+    td, _ = B.cpu_seed4_time(down, xd, threads, 3)
+    per = 4 * (tg + td) + 1e-9
+    reps = max(3, min(400, int((seconds - (time.perf_counter() - t0)) / per / 2)))
+    tg, _ = B.cpu_seed4_time(gate, xg, threads, reps)
+    td, _ = B.cpu_seed4_time(down, xd, threads, reps)
+    token_s = TOPK * (2 * tg + td)
+    return {"value": 1.0 / token_s, "unit": "tok/s", "cores": threads, "kind": "port",
+            "gweights_per_s": WEIGHTS_PER_TOKEN / token_s / 1e9,
+            "sample": f"one decode token of config 1 = 8 experts x (2 x 512x2048 + 2048x512) seed mat-vecs, best of {reps} "
+                      f"calls per shape on {threads} threads; the reference's own kernel needs Clang, this is its gcc restatement"}
+
+
+def run_reference(args):
+    threads = os.cpu_count() or 1
+    from oracle import binding as B
+    M = args.tokens
+    gate, down = B.Matrix(FF, D, 101), B.Matrix(D, FF, 102)
+    xg, xd = B.normal(1, D), B.normal(2, FF)
+
+    def step():   # M tokens x 8 experts x (gate, up, down): the reference runs one mat-vec pass per (row, expert) pair
+        for _ in range(M * TOPK):
+            B.cpu_seed4_matvec(gate, xg, threads=threads)
+            B.cpu_seed4_matvec(gate, xg, threads=threads)
+            B.cpu_seed4_matvec(down, xd, threads=threads)
+
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    value = M / dt
+    line = {"impl": "reference", "metric": "seed_decode_moe_gemv_tokens_per_s", "value": value, "unit": "tok/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(M),
+            "cpu_baseline": {"value": value, "unit": "tok/s", "cores": threads, "kind": "port",
+                             "sample": f"{args.steps} steps of {M} tokens x 8 experts x 3 seed mat-vecs on {threads} host threads "
+                                       "(gcc restatement of nslm/lib_cpu_seed4.c; the original needs Clang)"},
+            "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def workload_config(M, layers=None):
+    c = {"workload": f"BASELINE config 1: synthetic MoE expert layer at decode, hidden {D}, {E} seed-encoded (SEED4P4) "
+                     f"SwiGLU experts of intermediate {FF}, softmax top-{TOPK}, M={M} tokens, all experts resident",
+         "tokens": M, "experts": E, "top_k": TOPK, "hidden": D, "intermediate": FF}
+    if layers:
+        c["l2_policy"] = (f"steps rotate over {layers} independent layers ({layers * E * 3 * BYTES_PER_MATRIX / 1e9:.1f} GB of "
+                          "packed streams, far larger than the 126 MB L2), so each step's experts are read from HBM")
+    return c
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from nanoseedlm_b200 import lib as L, moe
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    lib = L.load()
+    M, K, W, NL = args.tokens, args.steps, max(args.warmup, 3), args.layers
+    gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
+    layers = [moe.DeviceLayer.random_on_device(D, FF, E, gen) for _ in range(NL)]
+    torch.cuda.synchronize()
+    m = moe.Moe(layers[0], TOPK, M)
+
+    # inputs: a pool of distinct batches (bf16-valued activations, N(0,1) logits), on the host and on the device
+    NB = 16
+    rng = np.random.default_rng(99 + rank)
+    hx = rng.standard_normal((NB, M, D)).astype(np.float32)
+    hx = (hx.view(np.uint32) + 0x7FFF + ((hx.view(np.uint32) >> 16) & 1) & 0xFFFF0000).view(np.float32)
+    hl = rng.standard_normal((NB, M, E)).astype(np.float32)
+    dx, dl = torch.from_numpy(hx).cuda(), torch.from_numpy(hl).cuda()
+    dout = torch.zeros(M, D, device="cuda")
+    distinct = [len(set(np.argsort(-hl[b], axis=1, kind="stable")[:, :TOPK].ravel().tolist())) for b in range(NB)]
+
+    stream = torch.cuda.Stream()
+    peaks, peak_kind = measured_peaks()
+
+    def enqueue(step, s):
+        m.set_layer(layers[step % NL])
+        m.forward_dev(dx[step % NB], dl[step % NB], dout, stream=s.cuda_stream)
+
+    # ---- value: inputs resident in HBM; the K steps are captured once as a CUDA graph and replayed ------------------
+    with torch.cuda.stream(stream):
+        for i in range(W):
+            enqueue(i, stream)
+        stream.synchronize()
+        # the steps are captured as a CUDA graph of `chunk` steps (the reference engine replays a graph per decode
+        # forward, engine/qwen4_cuda.c:1213-1231); K steps = K // chunk replays plus the remainder launched directly
+        chunk = min(K, 200)
+        launches0 = lib.nsl_launch_count()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for i in range(chunk):
+                enqueue(W + i, stream)
+        launches = (lib.nsl_launch_count() - launches0) // chunk * K
+        graph.replay()   # one untimed replay: graph upload
+        stream.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local) as clocks:
+            e0.record(stream)
+            for _ in range(K // chunk):
+                graph.replay()
+            for i in range(K % chunk):
+                enqueue(W + i, stream)
+            e1.record(stream)
+            e1.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / K
+    value = world * M / (ms_per_step * 1e-3)
+
+    # ---- roofline of the dominant kernel (gate+up mat-vec): CUDA events around each of its launches ------------------
+    G = m.G
+    A = torch.zeros(M * TOPK, FF, device="cuda")
+    ind = torch.zeros(M * TOPK, dtype=torch.int32, device="cuda")
+    wt = torch.zeros(M * TOPK, device="cuda")
+    gu_ms, gu_bytes = 0.0, 0.0
+    with torch.cuda.stream(stream):
+        evs = []
+        KR = min(K, 400)   # launches of the dominant kernel timed one by one
+        for i in range(KR):
+            lay, b = layers[(W + i) % NL], (W + i) % NB
+            lib.nsl_route(stream.cuda_stream, E, TOPK, dl[b].data_ptr(), E, ind.data_ptr(), wt.data_ptr(), M)
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record(stream)
+            lib.kc_mv_gu(stream.cuda_stream, L.MF_SEED4P4, lay.gate.table.data_ptr(), lay.up.table.data_ptr(), D, FF,
+                         dx[b].data_ptr(), D, A.data_ptr(), FF, ind.data_ptr(), M * TOPK, TOPK, G.data_ptr())
+            a1.record(stream)
+            evs.append((a0, a1, b))
+        stream.synchronize()
+        for a0, a1, b in evs:
+            gu_ms += a0.elapsed_time(a1)
+            gu_bytes += distinct[b] * 2 * BYTES_PER_MATRIX + M * D * 4 + M * TOPK * FF * 4
+    gu_us = gu_ms * 1e3 / KR
+    achieved = gu_bytes / KR / (gu_us * 1e-6) / 1e9
+
+    # ---- e2e: host buffers through the C host layer, H2D and D2H inside every step -----------------------------------
+    for i in range(W):
+        m.set_layer(layers[i % NL])
+        m.hx[:M], m.hlogits[:M] = hx[i % NB], hl[i % NB]
+        m.forward_pinned(M)
+    if world > 1:
+        dist.barrier()
+    KE = min(K, 2000)
+    t0 = time.perf_counter()
+    for i in range(KE):
+        m.set_layer(layers[(W + i) % NL])
+        m.hx[:M], m.hlogits[:M] = hx[(W + i) % NB], hl[(W + i) % NB]
+        m.forward_pinned(M)
+    e2e_s = (time.perf_counter() - t0) / KE
+    if world > 1:
+        t = torch.tensor([e2e_s], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    L.check()
+
+    if rank == 0:
+        line = {"metric": "seed_decode_moe_gemv_tokens_per_s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": K,
+                "warmup": W, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "f32", "data": "synthetic", "config": workload_config(M, NL),
+                "packed_gbs": world * sum(distinct[(W + i) % NB] for i in range(K)) / K * 3 * BYTES_PER_MATRIX / (ms_per_step * 1e-3) / 1e9,
+                "gpu_launches": int(launches), "clocks": clocks.summary(),
+                "e2e": {"value": world * M / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": M * D * 4 + M * E * 4,
+                        "d2h_bytes_per_step": M * D * 4, "ms_per_step": e2e_s * 1e3},
+                "roofline": {"bound": "hbm", "kernel": "mv_regx_kernel<gate+up>", "achieved": achieved, "peak": peaks["hbm_gbs"],
+                             "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_kind": peak_kind, "traffic": None,
+                             "us_per_launch": gu_us,
+                             "note": "the kernel is bound by integer/logic issue (LFSR expansion), not by HBM; see DESIGN.md"}}
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"] = cpu_baseline(os.cpu_count() or 1)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=4000)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tokens", type=int, default=8, choices=[1, 2, 3, 4, 5, 6, 7, 8])
+    ap.add_argument("--layers", type=int, default=20)
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        if int(os.environ.get("RANK", "0")) == 0:
+            run_reference(args)
+        return
+    run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -129,6 +129,9 @@ void nsl_route(cudaStream_t s, int n_exp, int top_k, const float* logits, int ld
  * nslm/lib_cpu_seed4.c:73,100), dense (sel == NULL: ws is a HOST pointer to the one slice, P = T tokens, xdiv = 1) or gathered (ws a device table). */
 void nsl_mv_raw(cudaStream_t s, const WSlice* ws, int K, int R, const float* x, int xs, float* y, int ys,
                 const int32_t* sel, int P, int xdiv, const uint32_t* G);
+/* kc_mv_gu without the bf16 rounding points: a = silu(gate . x) * (up . x) in f32. */
+void nsl_mv_gu_raw(cudaStream_t s, const WSlice* wg, const WSlice* wu, int K, int R, const float* x, int xs, float* a,
+                   int ys, const int32_t* sel, int P, int xdiv, const uint32_t* G);
 /* Rows [0,R) of one slice decoded to the exact f32 weights (nslm/lib_rows.c:49-76) or their bf16 rounding
  * (nslm/lib_search4.c:22-31): bit-exact.  out is [R][K]. */
 void nsl_decode_f32(cudaStream_t s, WSlice w, int K, int R, float* out, const uint32_t* G);

@@ -7,7 +7,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libnslm_b200.so")
-SOURCES = ["common.cu", "seed_mv.cu", "moe_misc.cu", "seed_gemm.cu"]
+SOURCES = ["common.cu", "seed_mv.cu", "moe_misc.cu", "seed_gemm.cu", "moe_host.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
               "-Xptxas", "-v"]
 
@@ -26,7 +26,7 @@ def _stale(target, deps):
 def build_library(force=False, verbose=False):
     """Compile every .cu under csrc/ to an object (in parallel) and link the shared library.  Returns its path."""
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
-    headers.append(os.path.join(HERE, "..", "include", "nslm_kernels.h"))
+    headers += [os.path.join(HERE, "..", "include", h) for h in ("nslm_kernels.h", "nslm_moe.h")]
     objdir = os.path.join(HERE, "build")
     os.makedirs(objdir, exist_ok=True)
     procs, objs = [], []
@@ -49,7 +49,8 @@ def build_library(force=False, verbose=False):
             sys.stderr.write(open(os.path.join(objdir, src.replace(".cu", ".o")) + ".log").read())
         raise RuntimeError("nvcc failed for " + ", ".join(failed))
     if force or procs or _stale(LIB, objs):
-        subprocess.run([_nvcc(), "-shared", "-o", LIB] + objs + ["-lcudart"], check=True)
+        subprocess.run([_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", LIB] + objs + ["-lcudart"],
+                       check=True)
     if verbose:
         print("built", LIB)
     return LIB

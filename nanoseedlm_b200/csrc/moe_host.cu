@@ -1,0 +1,149 @@
+// Host side of one MoE expert layer above the kernel ABI: the sequence the reference engine's moe() issues
+// (engine/qwen4_cuda.c:1023-1083) -- router top-k, routed experts' gate+up+SwiGLU and down projections over the
+// (token, expert) pairs, weighted combine -- for a layer whose experts are resident in device memory.  Rows <= MV_MAXT
+// take the mat-vec path (kc_mv_gu + kc_mv_sel), more rows the grouped prompt path (kc_bucket + kc_mm_grouped_dev x 3 +
+// kc_swiglu), as the reference decides at engine/qwen4_cuda.c:1058-1075.  Work buffers are allocated once at creation;
+// a forward allocates nothing and, in its device form, only enqueues launches (graph-capturable).
+#include <cstdlib>
+#include <cstring>
+
+#include "common.cuh"
+
+extern "C" {
+
+struct NslMoe {
+    int d, ff, n_exp, top_k, max_tokens;
+    const WSlice *wg, *wu, *wd;   // device tables [n_exp]
+    const uint32_t* G;            // device stream table
+    float *x, *logits, *wt, *A, *Dx, *Gb, *Ub, *out;
+    int32_t *ind, *perm, *ntiles;
+    MmTile* tiles;
+    float *hx, *hlogits, *hout;   // pinned staging for the host-buffer entry point
+    int32_t* hind;
+    cudaStream_t stream;
+    int grouped_min_tokens;       // rows from which the grouped prompt path is taken (MV_MAXT + 1)
+    int raw;                      // 1: no bf16 rounding points on the mat-vec path
+};
+
+static void* dalloc(size_t n) {
+    void* p = NULL;
+    if (cudaMalloc(&p, n ? n : 16) != cudaSuccess) return NULL;
+    return p;
+}
+
+NslMoe* nsl_moe_create(int d, int ff, int n_exp, int top_k, int max_tokens, const WSlice* wg, const WSlice* wu,
+                       const WSlice* wd, const uint32_t* G) {
+    if (d % 8 || ff % 8 || n_exp < 1 || n_exp > BUCKET_MAX_EXPERTS || top_k < 1 || top_k > 32 || max_tokens < 1) {
+        nsl::set_error("nsl_moe_create: unsupported shape d %d ff %d experts %d top_k %d tokens %d", d, ff, n_exp, top_k, max_tokens);
+        return NULL;
+    }
+    NslMoe* m = (NslMoe*) calloc(1, sizeof(NslMoe));
+    m->d = d; m->ff = ff; m->n_exp = n_exp; m->top_k = top_k; m->max_tokens = max_tokens;
+    m->wg = wg; m->wu = wu; m->wd = wd; m->G = G;
+    m->grouped_min_tokens = MV_MAXT + 1;
+    const size_t T = (size_t) max_tokens, P = T * top_k;
+    m->x = (float*) dalloc(T * d * 4);
+    m->logits = (float*) dalloc(T * n_exp * 4);
+    m->wt = (float*) dalloc(P * 4);
+    m->ind = (int32_t*) dalloc(P * 4);
+    m->A = (float*) dalloc(P * ff * 4);
+    m->Dx = (float*) dalloc(P * d * 4);
+    m->out = (float*) dalloc(T * d * 4);
+    const bool big = max_tokens > MV_MAXT;
+    m->Gb = big ? (float*) dalloc(P * ff * 4) : NULL;
+    m->Ub = big ? (float*) dalloc(P * ff * 4) : NULL;
+    m->perm = (int32_t*) dalloc(P * 4);
+    m->tiles = (MmTile*) dalloc((P / MMT_BN + n_exp + 1) * sizeof(MmTile));
+    m->ntiles = (int32_t*) dalloc((2 * (size_t) n_exp + 3) * 4);
+    cudaHostAlloc((void**) &m->hx, T * d * 4, cudaHostAllocDefault);
+    cudaHostAlloc((void**) &m->hlogits, T * n_exp * 4, cudaHostAllocDefault);
+    cudaHostAlloc((void**) &m->hout, T * d * 4, cudaHostAllocDefault);
+    cudaHostAlloc((void**) &m->hind, P * 4, cudaHostAllocDefault);
+    cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking);
+    if (!m->x || !m->logits || !m->wt || !m->ind || !m->A || !m->Dx || !m->out || !m->perm || !m->tiles || !m->ntiles ||
+        !m->hx || !m->hlogits || !m->hout || !m->hind || (big && (!m->Gb || !m->Ub))) {
+        nsl::set_error("nsl_moe_create: out of memory");
+        return NULL;
+    }
+    return m;
+}
+
+void nsl_moe_set_layer(NslMoe* m, const WSlice* wg, const WSlice* wu, const WSlice* wd) { m->wg = wg; m->wu = wu; m->wd = wd; }
+void nsl_moe_set_grouped_min_tokens(NslMoe* m, int t) { m->grouped_min_tokens = t; }
+void nsl_moe_set_rounding(NslMoe* m, int bf16_points) { m->raw = !bf16_points; }
+
+void nsl_moe_destroy(NslMoe* m) {
+    if (!m) return;
+    void* dv[] = {m->x, m->logits, m->wt, m->ind, m->A, m->Dx, m->out, m->Gb, m->Ub, m->perm, m->tiles, m->ntiles};
+    for (void* p : dv) if (p) cudaFree(p);
+    void* hv[] = {m->hx, m->hlogits, m->hout, m->hind};
+    for (void* p : hv) if (p) cudaFreeHost(p);
+    cudaStreamDestroy(m->stream);
+    free(m);
+}
+
+// Device form: x [T][d] and logits [T][n_exp] in device memory -> out [T][d]; ind_out / wt_out (device, optional) get
+// the routing.  Only launches are enqueued on s.
+int nsl_moe_forward_dev(NslMoe* m, cudaStream_t s, const float* x, const float* logits, int T, float* out) {
+    if (T < 1 || T > m->max_tokens) { nsl::set_error("nsl_moe_forward: %d rows, at most %d", T, m->max_tokens); return -1; }
+    const int k = m->top_k, P = T * k, d = m->d, ff = m->ff;
+    nsl_route(s, m->n_exp, k, logits, m->n_exp, m->ind, m->wt, T);
+    if (T >= m->grouped_min_tokens) {
+        const int mt = P / MMT_BN + m->n_exp;
+        kc_bucket(s, m->ind, P, m->n_exp, m->perm, m->tiles, m->ntiles);
+        kc_mm_grouped_dev(s, MF_SEED4P4, m->wg, d, ff, x, d, m->Gb, ff, k, m->perm, m->tiles, m->ntiles, mt, m->G);
+        kc_mm_grouped_dev(s, MF_SEED4P4, m->wu, d, ff, x, d, m->Ub, ff, k, m->perm, m->tiles, m->ntiles, mt, m->G);
+        kc_swiglu(s, m->Gb, m->Ub, m->A, P * ff);
+        kc_mm_grouped_dev(s, MF_SEED4P4, m->wd, ff, d, m->A, ff, m->Dx, d, 1, m->perm, m->tiles, m->ntiles, mt, m->G);
+    } else if (m->raw) {
+        nsl_mv_gu_raw(s, m->wg, m->wu, d, ff, x, d, m->A, ff, m->ind, P, k, m->G);
+        nsl_mv_raw(s, m->wd, ff, d, m->A, ff, m->Dx, d, m->ind, P, 1, m->G);
+    } else {
+        kc_mv_gu(s, MF_SEED4P4, m->wg, m->wu, d, ff, x, d, m->A, ff, m->ind, P, k, m->G);
+        kc_mv_sel(s, MF_SEED4P4, m->wd, ff, d, m->A, ff, m->Dx, d, m->ind, P, 1, m->G);
+    }
+    kq4_moe_combine(s, d, k, m->Dx, m->wt, NULL, NULL, 0, out, T);
+    return 0;
+}
+
+// Host form: x and logits in HOST memory, out to host memory.  Copies go through the layer's pinned staging buffers on
+// its own stream; returns after the result is on the host (-1 on an argument or CUDA error).
+int nsl_moe_forward_host(NslMoe* m, const float* x, const float* logits, int T, float* out, int32_t* ind_out) {
+    if (T < 1 || T > m->max_tokens) { nsl::set_error("nsl_moe_forward: %d rows, at most %d", T, m->max_tokens); return -1; }
+    const size_t xb = (size_t) T * m->d * 4, lb = (size_t) T * m->n_exp * 4;
+    memcpy(m->hx, x, xb);
+    memcpy(m->hlogits, logits, lb);
+    cudaMemcpyAsync(m->x, m->hx, xb, cudaMemcpyHostToDevice, m->stream);
+    cudaMemcpyAsync(m->logits, m->hlogits, lb, cudaMemcpyHostToDevice, m->stream);
+    if (nsl_moe_forward_dev(m, m->stream, m->x, m->logits, T, m->out)) return -1;
+    cudaMemcpyAsync(m->hout, m->out, xb, cudaMemcpyDeviceToHost, m->stream);
+    if (ind_out) cudaMemcpyAsync(m->hind, m->ind, (size_t) T * m->top_k * 4, cudaMemcpyDeviceToHost, m->stream);
+    if (cudaStreamSynchronize(m->stream) != cudaSuccess || cudaGetLastError() != cudaSuccess) {
+        nsl::set_error("nsl_moe_forward_host: CUDA error");
+        return -1;
+    }
+    memcpy(out, m->hout, xb);
+    if (ind_out) memcpy(ind_out, m->hind, (size_t) T * m->top_k * 4);
+    return 0;
+}
+
+// Pinned staging buffers, for callers that fill inputs in place and skip the two host copies.
+float* nsl_moe_host_x(NslMoe* m) { return m->hx; }
+float* nsl_moe_host_logits(NslMoe* m) { return m->hlogits; }
+float* nsl_moe_host_out(NslMoe* m) { return m->hout; }
+const int32_t* nsl_moe_dev_ind(NslMoe* m) { return m->ind; }
+const float* nsl_moe_dev_wt(NslMoe* m) { return m->wt; }
+cudaStream_t nsl_moe_stream(NslMoe* m) { return m->stream; }
+
+// The same with inputs already in the pinned buffers and the result left there: H2D, the layer, D2H, one sync.
+int nsl_moe_forward_pinned(NslMoe* m, int T) {
+    if (T < 1 || T > m->max_tokens) { nsl::set_error("nsl_moe_forward: %d rows, at most %d", T, m->max_tokens); return -1; }
+    const size_t xb = (size_t) T * m->d * 4, lb = (size_t) T * m->n_exp * 4;
+    cudaMemcpyAsync(m->x, m->hx, xb, cudaMemcpyHostToDevice, m->stream);
+    cudaMemcpyAsync(m->logits, m->hlogits, lb, cudaMemcpyHostToDevice, m->stream);
+    if (nsl_moe_forward_dev(m, m->stream, m->x, m->logits, T, m->out)) return -1;
+    cudaMemcpyAsync(m->hout, m->out, xb, cudaMemcpyDeviceToHost, m->stream);
+    return cudaStreamSynchronize(m->stream) == cudaSuccess ? 0 : -1;
+}
+
+}   // extern "C"

@@ -9,13 +9,14 @@
 // How the expansion is laid out here.  On this part the integer/logic pipe issues at half the FP32 rate (measured:
 // 63 LOP3/SHF/PRMT vs 119 FFMA lane-ops per clock per SM) and packed FP32 pairs (fma.rn.f32x2) halve the FP issue
 // count again, so a block costs what its integer operations cost.  They are kept to one shift per weight and one
-// logic operation per state:
+// AND per state:
 //   Y_c  = the window shifted so that stream bit 4c+1 sits at bit 4            (one shift per weight)
-//   v_cp = as_float((Y_c & (0xFFFF << (4+p))) | (130-p) << 23) = 2^(3-p) + state_(4c+p+1) / 2^16     (one LOP3, exact)
-// The offsets 8, 4, 2, 1 and the centring (-32768 = -0.5 in these units) fold into per-block constants.  The window
-// is held as two words, A = stream bits 0..31 (weights 0..3) and G = stream bits 16..47 (weights 4..7), so no shift
-// crosses a word.  The second constant of every two-constant logic operation comes from a register that the compiler
-// cannot see through (KConst, passed as a kernel argument): with two literals the assembler emits two instructions.
+//   v_cp = as_float(Y_c & (0xFFFF << (4+p))) = state_(4c+p+1) * 2^(p-145)      (one AND with a literal; a subnormal float)
+// FP32 subnormals are exact multiples of 2^-149 and this GPU's FMA takes them at full rate, so no exponent has to be
+// merged in (a second constant per logic operation costs a second instruction or a register move).  The mat-vec
+// kernels scale their inputs by 2^64 when they load them, so every product is a normal number; the powers of two and
+// the centring (-32768 per state) fold into per-block constants.  The window is held as two words, A = stream bits
+// 0..31 (weights 0..3) and G = stream bits 16..47 (weights 4..7), so no shift crosses a word.
 // Two adjacent blocks are expanded side by side and their state values packed as f32x2 pairs {block A, block B}, so
 // the 32 multiply-adds of each block issue as 32 packed operations per block pair.
 #pragma once
@@ -44,23 +45,30 @@ __device__ __forceinline__ uint32_t stream_bits(const StreamTab& t, uint32_t see
     return t.lo[seed & 0xFFu] ^ t.hi[(seed >> 8) & 0xFFu];
 }
 
-// Run-time constants of the expansion (see the header comment).  Filled by kconst() on the host.
+// Run-time constants of the coefficient and exponent-code conversions (kernel arguments, so that they stay register
+// or constant-bank operands).  Coefficient p becomes an exact float by placing nibble ^ 8 under an exponent chosen so
+// that the nibble's low bit has the wanted weight, then subtracting the offset:
+//   dot form   q'_p = q_p 2^(65-p):  exponent field 215 - 5p, offset 2^(88-5p) + 2^(68-p)
+//   exact form q"_p = q_p 2^(100-p): exponent field 250 - 5p, offset 2^(123-5p) + 2^(103-p)
 struct KConst {
-    uint32_t expo[4];   // (130 - p) << 23
-    uint32_t cxor[4];   // (150 - 4p) << 23 | 8 << 4p
-    uint32_t cor;       // 112 << 23
-    float coff[4];      // -(2^(23 - 4p) + 8)
+    uint32_t cxor[4];
+    float coff[4];
+    uint32_t cxor_x[4];
+    float coff_x[4];
+    uint32_t cor;       // 112 << 23: 2^(code - 15) from a code placed at bits 23..26
 };
 inline KConst kconst() {
     KConst k;
     for (int p = 0; p < 4; ++p) {
-        k.expo[p] = (uint32_t) (130 - p) << 23;
-        k.cxor[p] = ((uint32_t) (150 - 4 * p) << 23) | (8u << (4 * p));
-        k.coff[p] = -((float) (1u << (23 - 4 * p)) + 8.0f);
+        k.cxor[p] = ((uint32_t) (215 - 5 * p) << 23) | (8u << (4 * p));
+        k.coff[p] = -(ldexpf(1.0f, 88 - 5 * p) + ldexpf(1.0f, 68 - p));
+        k.cxor_x[p] = ((uint32_t) (250 - 5 * p) << 23) | (8u << (4 * p));
+        k.coff_x[p] = -(ldexpf(1.0f, 123 - 5 * p) + ldexpf(1.0f, 103 - p));
     }
     k.cor = 112u << 23;
     return k;
 }
+#define NSL_XSCALE 18446744073709551616.0f   // 2^64: the mat-vec kernels' input scaling
 
 __device__ __forceinline__ float bf16_round(float x) {   // round to nearest even, kept as f32 (nslm/lfsr.h:104-109)
     uint32_t u = __float_as_uint(x);
@@ -87,6 +95,23 @@ __device__ __forceinline__ uint32_t and_xor(uint32_t a, uint32_t c) {
     return d;
 }
 
+// The same on two words at once, the results packed as a 64-bit pair {lo, hi}: written as one unit so the assembler
+// places each result directly in its half of the pair (packing two separately produced values costs a move each).
+template <uint32_t MASK>
+__device__ __forceinline__ unsigned long long and_or_pair(uint32_t a0, uint32_t a1, uint32_t c) {
+    unsigned long long d;
+    asm("{\n\t.reg .b32 lo, hi;\n\tlop3.b32 lo, %1, %3, %4, 0xEA;\n\tlop3.b32 hi, %2, %3, %4, 0xEA;\n\tmov.b64 %0, {lo, hi};\n\t}"
+        : "=l"(d) : "r"(a0), "r"(a1), "n"(MASK), "r"(c));
+    return d;
+}
+template <uint32_t MASK>
+__device__ __forceinline__ unsigned long long and_xor_pair(uint32_t a0, uint32_t a1, uint32_t c) {
+    unsigned long long d;
+    asm("{\n\t.reg .b32 lo, hi;\n\tlop3.b32 lo, %1, %3, %4, 0x6A;\n\tlop3.b32 hi, %2, %3, %4, 0x6A;\n\tmov.b64 %0, {lo, hi};\n\t}"
+        : "=l"(d) : "r"(a0), "r"(a1), "n"(MASK), "r"(c));
+    return d;
+}
+
 // The shifted copy for weight c: stream bit 4c+1 at bit 4.  a = stream bits 0..31, g = bits 16..47.
 template <int C>
 __device__ __forceinline__ uint32_t weight_word(uint32_t a, uint32_t g) {
@@ -94,16 +119,16 @@ __device__ __forceinline__ uint32_t weight_word(uint32_t a, uint32_t g) {
     constexpr int cc = C & 3;
     return cc == 0 ? src * 8u : src >> (4 * cc - 3);   // the left shift as a multiply: it issues on the FMA pipe
 }
-// v_cp = 2^(3-p) + state / 2^16
+// v_cp = state_(4c+p+1) * 2^(p-145), a subnormal
 template <int P>
-__device__ __forceinline__ float state_value(uint32_t y, const KConst& k) {
-    return __uint_as_float(and_or<(0xFFFFu << (4 + P))>(y, k.expo[P]));
+__device__ __forceinline__ float state_value(uint32_t y) {
+    return __uint_as_float(y & (0xFFFFu << (4 + P)));
 }
-// Coefficient p as an exact float: nibble ^ 8 under a power of two chosen so the nibble's low bit weighs 1, before the
-// subtraction of coff[p].  cw holds the coefficient word in bits 0..15 (higher bits are ignored).
+// Coefficient p before the subtraction of its offset.  cw holds the coefficient word in bits 0..15 (higher bits are
+// ignored).
 template <int P>
-__device__ __forceinline__ float coef_raw(uint32_t cw, const KConst& k) {
-    return __uint_as_float(and_xor<(0xFu << (4 * P))>(cw, k.cxor[P]));
+__device__ __forceinline__ float coef_raw(uint32_t cw, uint32_t cx) {
+    return __uint_as_float(and_xor<(0xFu << (4 * P))>(cw, cx));
 }
 // 2^(code - 15) for block i (0..7) of a chunk whose eight codes are the nibbles of cd.
 __device__ __forceinline__ float code_scale(uint32_t cd, int i, const KConst& k) {   // i: a constant after unrolling
@@ -111,41 +136,51 @@ __device__ __forceinline__ float code_scale(uint32_t cd, int i, const KConst& k)
     const uint32_t f = sh >= 0 ? cd * (1u << (sh & 31)) : cd >> ((-sh) & 31);
     return __uint_as_float(and_or<0x07800000u>(f, k.cor));
 }
+// {2^(code - 15) of block 2 bp, of block 2 bp + 1} of the chunk.
+__device__ __forceinline__ unsigned long long code_scale_pair(uint32_t cd, int bp, const KConst& k) {
+    const int s0 = 23 - 8 * bp, s1 = 19 - 8 * bp;
+    const uint32_t f0 = s0 >= 0 ? cd * (1u << (s0 & 31)) : cd >> ((-s0) & 31);
+    const uint32_t f1 = s1 >= 0 ? cd * (1u << (s1 & 31)) : cd >> ((-s1) & 31);
+    return and_or_pair<0x07800000u>(f0, f1, k.cor);
+}
 // The factor that completes code_scale: R32 * 2^(eb + 31) (a power-of-two scaling of R32: exact).
 __device__ __forceinline__ float slice_scale(int eb) {
     return __uint_as_float(__float_as_uint(1.0f / 32767.0f) + ((uint32_t) (eb + 31) << 23));
 }
 
-// Input-side constants of one block: xm[p] = -(2^(3-p) + 0.5) * sum(x), which centres the states.
-__device__ __forceinline__ void block_offsets(const float* x, float* xm) {
-    const float s = ((x[0] + x[4]) + (x[1] + x[5])) + ((x[2] + x[6]) + (x[3] + x[7]));
-    xm[0] = -8.5f * s;
-    xm[1] = -4.5f * s;
-    xm[2] = -2.5f * s;
-    xm[3] = -1.5f * s;
+// Input-side constants of one block of SCALED inputs x' = 2^64 x: xm[p] = -32768 * 2^(p-145) * sum(x') =
+// -2^(p-130) sum(x'), which centres the states.  The sum is taken on the unscaled values' order of magnitude by the
+// caller passing the scaled inputs; 2^-66 etc. keep every factor a normal number.
+__device__ __forceinline__ void block_offsets(const float* xs, float* xm) {   // xs: the 8 scaled inputs
+    const float s = (((xs[0] + xs[4]) + (xs[1] + xs[5])) + ((xs[2] + xs[6]) + (xs[3] + xs[7]))) * 5.421010862427522e-20f;   // 2^-64
+    xm[0] = -1.3552527156068805e-20f * s;   // -2^-66
+    xm[1] = -2.710505431213761e-20f * s;    // -2^-65
+    xm[2] = -5.421010862427522e-20f * s;    // -2^-64
+    xm[3] = -1.0842021724855044e-19f * s;   // -2^-63
 }
 
 // ---- single block (the any-shape mat-vec, the decode, the GEMM tiles) -----------------------------------------------
 // The 32 state values: v[4c+p].
-__device__ __forceinline__ void block_states(uint32_t a, uint32_t g, const KConst& k, float* v) {
-#define NSL_V(C)                                         \
-    {                                                    \
-        const uint32_t y = weight_word<C>(a, g);         \
-        v[4 * C + 0] = state_value<0>(y, k);             \
-        v[4 * C + 1] = state_value<1>(y, k);             \
-        v[4 * C + 2] = state_value<2>(y, k);             \
-        v[4 * C + 3] = state_value<3>(y, k);             \
+__device__ __forceinline__ void block_states(uint32_t a, uint32_t g, float* v) {
+#define NSL_V(C)                                      \
+    {                                                 \
+        const uint32_t y = weight_word<C>(a, g);      \
+        v[4 * C + 0] = state_value<0>(y);             \
+        v[4 * C + 1] = state_value<1>(y);             \
+        v[4 * C + 2] = state_value<2>(y);             \
+        v[4 * C + 3] = state_value<3>(y);             \
     }
     NSL_V(0) NSL_V(1) NSL_V(2) NSL_V(3) NSL_V(4) NSL_V(5) NSL_V(6) NSL_V(7)
 #undef NSL_V
 }
-__device__ __forceinline__ void block_coefs(uint32_t cw, const KConst& k, float* q) {
-    q[0] = coef_raw<0>(cw, k) + k.coff[0];
-    q[1] = coef_raw<1>(cw, k) + k.coff[1];
-    q[2] = coef_raw<2>(cw, k) + k.coff[2];
-    q[3] = coef_raw<3>(cw, k) + k.coff[3];
+__device__ __forceinline__ void block_coefs(uint32_t cw, const KConst& k, float* q) {   // q'_p = q_p 2^(65-p)
+    q[0] = coef_raw<0>(cw, k.cxor[0]) + k.coff[0];
+    q[1] = coef_raw<1>(cw, k.cxor[1]) + k.coff[1];
+    q[2] = coef_raw<2>(cw, k.cxor[2]) + k.coff[2];
+    q[3] = coef_raw<3>(cw, k.cxor[3]) + k.coff[3];
 }
-// Dot form: sum_c x_c isum_c / 2^16.  d_p = xm_p + sum_c x_c v_cp (c ascending); result = ((q0 d0 + q1 d1) + q2 d2) + q3 d3
+// Dot form: sum_c x_c isum_c / 2^16 from scaled inputs.  d_p = xm_p + sum_c x'_c v_cp (c ascending);
+// result = ((q'0 d0 + q'1 d1) + q'2 d2) + q'3 d3
 __device__ __forceinline__ float states_dot(const float* v, const float* q, const float* x, const float* xm) {
     float d0 = xm[0], d1 = xm[1], d2 = xm[2], d3 = xm[3];
 #pragma unroll
@@ -157,24 +192,30 @@ __device__ __forceinline__ float states_dot(const float* v, const float* q, cons
     }
     return fmaf(q[3], d3, fmaf(q[2], d2, fmaf(q[1], d1, q[0] * d0)));
 }
-// Exact form: the eight weights bit for bit.  sum_p q_p v_cp stays below 2^8 in units of 2^-16, so every partial sum is
-// exact in f32; adding kq = -sum_p q_p (2^(3-p) + 0.5) leaves isum_c / 2^16 exactly, and one multiply by
-// sc16 = fl(R32 2^e) * 2^16 is the spec's single rounding.
-__device__ __forceinline__ void block_weights(uint32_t a, uint32_t g, uint32_t cw, float sc16, const KConst& k, float* w) {
+// Exact form: the eight weights bit for bit.  With q"_p = q_p 2^(100-p) every product q"_p v_cp is the integer
+// q_p state in units of 2^-45 and every partial sum is exact in f32; adding kq = -2^-30 sum_p q_p (the centring)
+// leaves isum_c 2^-45 exactly, and one multiply by sc45 = fl(R32 2^e) * 2^45 is the spec's single rounding.
+__device__ __forceinline__ void block_weights(uint32_t a, uint32_t g, uint32_t cw, float sc45, const KConst& k, float* w) {
     float v[32], q[4];
-    block_states(a, g, k, v);
-    block_coefs(cw, k, q);
-    const float kq = __fmaf_rn(q[3], -1.5f, __fmaf_rn(q[2], -2.5f, __fmaf_rn(q[1], -4.5f, __fmul_rn(q[0], -8.5f))));
+    block_states(a, g, v);
+    q[0] = coef_raw<0>(cw, k.cxor_x[0]) + k.coff_x[0];
+    q[1] = coef_raw<1>(cw, k.cxor_x[1]) + k.coff_x[1];
+    q[2] = coef_raw<2>(cw, k.cxor_x[2]) + k.coff_x[2];
+    q[3] = coef_raw<3>(cw, k.cxor_x[3]) + k.coff_x[3];
+    // -2^(p-130) q"_p = -2^-30 q_p; the four constants are subnormal or tiny but exact
+    const float kq = __fmaf_rn(q[3], -5.877471754111438e-39f,
+                               __fmaf_rn(q[2], -2.938735877055719e-39f,
+                                         __fmaf_rn(q[1], -1.4693679385278594e-39f, __fmul_rn(q[0], -7.346839692639297e-40f))));
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
         const float t = __fmaf_rn(q[3], v[4 * c + 3],
                                   __fmaf_rn(q[2], v[4 * c + 2], __fmaf_rn(q[1], v[4 * c + 1], __fmul_rn(q[0], v[4 * c]))));
-        w[c] = __fmul_rn(__fadd_rn(t, kq), sc16);
+        w[c] = __fmul_rn(__fadd_rn(t, kq), sc45);
     }
 }
-// fl(R32 2^e) * 2^16 from exponent bits.
-__device__ __forceinline__ float exact_scale16(int e) {
-    return __uint_as_float(__float_as_uint(1.0f / 32767.0f) + ((uint32_t) (e + 16) << 23));
+// fl(R32 2^e) * 2^45 from exponent bits.
+__device__ __forceinline__ float exact_scale45(int e) {
+    return __uint_as_float(__float_as_uint(1.0f / 32767.0f) + ((uint32_t) (e + 45) << 23));
 }
 
 // ---- two adjacent blocks as f32x2 pairs {even block, odd block} ----------------------------------------------------
@@ -201,17 +242,17 @@ __device__ __forceinline__ u64 add2(u64 a, u64 b) {
 }
 
 // The 32 state-value pairs of the blocks whose seeds are the two halves of sw: v[4c+p] = {even, odd}.
-__device__ __forceinline__ void pair_states(const StreamTab& tab, uint32_t sw, const KConst& k, u64* v) {
+__device__ __forceinline__ void pair_states(const StreamTab& tab, uint32_t sw, u64* v) {
     const uint32_t s0 = sw & 0xFFFFu, s1 = sw >> 16;
     const uint32_t g0 = stream_bits(tab, s0), g1 = stream_bits(tab, s1);
     const uint32_t a0 = g0 * 65536u + s0, a1 = g1 * 65536u + s1;
 #define NSL_V2(C)                                                                  \
     {                                                                              \
         const uint32_t y0 = weight_word<C>(a0, g0), y1 = weight_word<C>(a1, g1);   \
-        v[4 * C + 0] = pack2(state_value<0>(y0, k), state_value<0>(y1, k));        \
-        v[4 * C + 1] = pack2(state_value<1>(y0, k), state_value<1>(y1, k));        \
-        v[4 * C + 2] = pack2(state_value<2>(y0, k), state_value<2>(y1, k));        \
-        v[4 * C + 3] = pack2(state_value<3>(y0, k), state_value<3>(y1, k));        \
+        v[4 * C + 0] = pack2(state_value<0>(y0), state_value<0>(y1));              \
+        v[4 * C + 1] = pack2(state_value<1>(y0), state_value<1>(y1));              \
+        v[4 * C + 2] = pack2(state_value<2>(y0), state_value<2>(y1));              \
+        v[4 * C + 3] = pack2(state_value<3>(y0), state_value<3>(y1));              \
     }
     NSL_V2(0) NSL_V2(1) NSL_V2(2) NSL_V2(3) NSL_V2(4) NSL_V2(5) NSL_V2(6) NSL_V2(7)
 #undef NSL_V2
@@ -219,10 +260,10 @@ __device__ __forceinline__ void pair_states(const StreamTab& tab, uint32_t sw, c
 // The four coefficient pairs of the two words packed in cw.
 __device__ __forceinline__ void pair_coefs(uint32_t cw, const KConst& k, u64* q) {
     const uint32_t c1 = cw >> 16;
-    q[0] = add2(pack2(coef_raw<0>(cw, k), coef_raw<0>(c1, k)), pack2(k.coff[0], k.coff[0]));
-    q[1] = add2(pack2(coef_raw<1>(cw, k), coef_raw<1>(c1, k)), pack2(k.coff[1], k.coff[1]));
-    q[2] = add2(pack2(coef_raw<2>(cw, k), coef_raw<2>(c1, k)), pack2(k.coff[2], k.coff[2]));
-    q[3] = add2(pack2(coef_raw<3>(cw, k), coef_raw<3>(c1, k)), pack2(k.coff[3], k.coff[3]));
+    q[0] = add2(and_xor_pair<0x000Fu>(cw, c1, k.cxor[0]), pack2(k.coff[0], k.coff[0]));
+    q[1] = add2(and_xor_pair<0x00F0u>(cw, c1, k.cxor[1]), pack2(k.coff[1], k.coff[1]));
+    q[2] = add2(and_xor_pair<0x0F00u>(cw, c1, k.cxor[2]), pack2(k.coff[2], k.coff[2]));
+    q[3] = add2(and_xor_pair<0xF000u>(cw, c1, k.cxor[3]), pack2(k.coff[3], k.coff[3]));
 }
 // Both blocks' dot forms at once: x2[c] = {x of the even block, x of the odd block}, xm2[p] likewise.
 __device__ __forceinline__ u64 pair_dot(const u64* v, const u64* q, const u64* x2, const u64* xm2) {

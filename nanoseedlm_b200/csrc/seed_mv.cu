@@ -58,9 +58,9 @@ __device__ __forceinline__ u64 chunk_dot(const StreamTab& tab, const KConst& kc,
 #pragma unroll
     for (int bp = 0; bp < 4; ++bp) {
         u64 v[32], q[4];
-        pair_states(tab, sw[bp], kc, v);
+        pair_states(tab, sw[bp], v);
         pair_coefs(cw[bp], kc, q);
-        const u64 e2 = pack2(code_scale(k.cd, 2 * bp, kc), code_scale(k.cd, 2 * bp + 1, kc));
+        const u64 e2 = code_scale_pair(k.cd, bp, kc);
         acc2 = fma2(pair_dot(v, q, x2 + 8 * bp, xm2 + 4 * bp), e2, acc2);
     }
     return acc2;
@@ -79,7 +79,7 @@ __device__ __forceinline__ float group_sum(float v, int lpr) {
 template <int MODE>
 __device__ __forceinline__ void store_out(const MvParams& a, int pair, int r, float s, float su) {
     float* yo = a.y + (size_t) pair * a.ys + r;
-    if (MODE == MODE_GU) *yo = bf16_round(silu_bf(bf16_round(s)) * bf16_round(su));
+    if (MODE == MODE_GU) *yo = a.raw ? (s / (1.0f + expf(-s))) * su : bf16_round(silu_bf(bf16_round(s)) * bf16_round(su));
     else if (a.raw) *yo = s;
     else *yo = a.add ? bf16_round(*yo + bf16_round(s)) : bf16_round(s);   // engine/kernels_moe.cu:214
 }
@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) mv_regx_kernel(MvParams a, KCon
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
                 const float4 t = __ldg(xp + i);
-                x[4 * i] = t.x; x[4 * i + 1] = t.y; x[4 * i + 2] = t.z; x[4 * i + 3] = t.w;
+                x[4 * i] = t.x * NSL_XSCALE; x[4 * i + 1] = t.y * NSL_XSCALE; x[4 * i + 2] = t.z * NSL_XSCALE; x[4 * i + 3] = t.w * NSL_XSCALE;
             }
 #pragma unroll
             for (int b = 0; b < 8; ++b) block_offsets(x + 8 * b, xm + 4 * b);
@@ -185,7 +185,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) mv_smemx_kernel(MvParams a, KCo
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const float4 v4 = __ldg((const float4*) xp + j);
-                x[4 * j] = v4.x; x[4 * j + 1] = v4.y; x[4 * j + 2] = v4.z; x[4 * j + 3] = v4.w;
+                x[4 * j] = v4.x * NSL_XSCALE; x[4 * j + 1] = v4.y * NSL_XSCALE; x[4 * j + 2] = v4.z * NSL_XSCALE; x[4 * j + 3] = v4.w * NSL_XSCALE;
             }
             block_offsets(x, xm);
             block_offsets(x + 8, xm + 4);
@@ -217,9 +217,9 @@ __global__ void __launch_bounds__(MV_THREADS, 1) mv_smemx_kernel(MvParams a, KCo
 #pragma unroll
                         for (int bp = 0; bp < 4; ++bp) {
                             u64 v[32], q[4];
-                            pair_states(tab, sw[bp], kc, v);
+                            pair_states(tab, sw[bp], v);
                             pair_coefs(cw[bp], kc, q);
-                            const u64 e2 = pack2(code_scale(k.cd, 2 * bp, kc), code_scale(k.cd, 2 * bp + 1, kc));
+                            const u64 e2 = code_scale_pair(k.cd, bp, kc);
                             const int gbp = j * 4 + bp;
 #pragma unroll
                             for (int t = 0; t < NT; ++t) {
@@ -277,7 +277,7 @@ __global__ void __launch_bounds__(MV_THREADS) mv_generic_kernel(MvParams a, KCon
                 const uint32_t g = stream_bits(tab, seed);
                 const uint32_t aw = seed | (g << 16);
                 float v[32], q[4];
-                block_states(aw, g, kc, v);
+                block_states(aw, g, v);
                 block_coefs(cwi, kc, q);
                 const float e2 = __uint_as_float((code << 23) | 0x38000000u);
 #pragma unroll
@@ -286,7 +286,7 @@ __global__ void __launch_bounds__(MV_THREADS) mv_generic_kernel(MvParams a, KCon
                     const float* xp = a.x + (size_t) (dense ? t : pair / a.xdiv) * a.xs + (size_t) j * 8;
                     float xr[8], xo[4];
 #pragma unroll
-                    for (int c = 0; c < 8; ++c) xr[c] = __ldg(xp + c);
+                    for (int c = 0; c < 8; ++c) xr[c] = __ldg(xp + c) * NSL_XSCALE;
                     block_offsets(xr, xo);
                     const float d = states_dot(v, q, xr, xo);
                     if (half) su[t] = fmaf(d, e2, su[t]);
@@ -318,7 +318,7 @@ __global__ void __launch_bounds__(256) decode_kernel(WSlice w, KConst kc, int K,
         const int code = (((const uint8_t*) w.p[3])[gidx >> 1] >> ((gidx & 1) * 4)) & 15;
         const uint32_t g = stream_bits(tab, seed);
         float wv[8];
-        block_weights(seed | (g << 16), g, cw, exact_scale16(w.eb + code), kc, wv);
+        block_weights(seed | (g << 16), g, cw, exact_scale45(w.eb + code), kc, wv);
         if (BF16) {
             uint4 o;
             o.x = bf16_bits(wv[0]) | ((uint32_t) bf16_bits(wv[1]) << 16);
@@ -418,6 +418,12 @@ void nsl_mv_raw(cudaStream_t s, const WSlice* ws, int K, int R, const float* x, 
     MvParams a = {sel ? ws : NULL, NULL, WSlice{}, sel, x, y, G, K, R, P, xdiv > 0 ? xdiv : 1, xs, ys, 0, 1};
     if (!sel) a.w0 = *ws;   // dense: ws is a host pointer to the one slice
     launch_mv<MODE_ROUND>(s, a, sel ? 1 : P);
+}
+
+void nsl_mv_gu_raw(cudaStream_t s, const WSlice* wg, const WSlice* wu, int K, int R, const float* x, int xs, float* out,
+                   int ys, const int32_t* sel, int P, int xdiv, const uint32_t* G) {
+    MvParams a = {wg, wu, WSlice{}, sel, x, out, G, K, R, P, xdiv, xs, ys, 0, 1};
+    launch_mv<MODE_GU>(s, a, 1);
 }
 
 void nsl_decode_f32(cudaStream_t s, WSlice w, int K, int R, float* out, const uint32_t* G) {

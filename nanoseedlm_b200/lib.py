@@ -1,4 +1,4 @@
-"""ctypes view of libnslm_b200.so: the C ABI declared in include/nslm_kernels.h.
+"""ctypes view of libnslm_b200.so: the C ABI declared in include/nslm_kernels.h and include/nslm_moe.h.
 
 There is no fallback: if the library is missing the import of the kernels fails with instructions to build it, and
 every call goes to the CUDA kernels.  torch is used only for device memory and streams."""
@@ -56,12 +56,28 @@ PROTOTYPES = {
     "kc_cache_copy": (None, [_vp, C.POINTER(CachePool), _i]),
     "nsl_route": (None, [_vp, _i, _i, _vp, _i, _vp, _vp, _i]),
     "nsl_mv_raw": (None, [_vp, _vp, _i, _i, _vp, _i, _vp, _i, _vp, _i, _i, _vp]),
+    "nsl_mv_gu_raw": (None, [_vp, _vp, _vp, _i, _i, _vp, _i, _vp, _i, _vp, _i, _i, _vp]),
     "nsl_decode_f32": (None, [_vp, WSlice, _i, _i, _vp, _vp]),
     "nsl_decode_bf16": (None, [_vp, WSlice, _i, _i, _vp, _vp]),
     "nsl_stream_table": (None, [_vp]),
     "nsl_last_error": (C.c_char_p, []),
     "nsl_launch_count": (C.c_uint64, []),
     "nsl_sm_count": (_i, []),
+    # include/nslm_moe.h
+    "nsl_moe_create": (_vp, [_i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
+    "nsl_moe_destroy": (None, [_vp]),
+    "nsl_moe_set_layer": (None, [_vp, _vp, _vp, _vp]),
+    "nsl_moe_set_grouped_min_tokens": (None, [_vp, _i]),
+    "nsl_moe_forward_dev": (_i, [_vp, _vp, _vp, _vp, _i, _vp]),
+    "nsl_moe_forward_host": (_i, [_vp, _vp, _vp, _i, _vp, _vp]),
+    "nsl_moe_host_x": (_vp, [_vp]),
+    "nsl_moe_host_logits": (_vp, [_vp]),
+    "nsl_moe_host_out": (_vp, [_vp]),
+    "nsl_moe_forward_pinned": (_i, [_vp, _i]),
+    "nsl_moe_dev_ind": (_vp, [_vp]),
+    "nsl_moe_dev_wt": (_vp, [_vp]),
+    "nsl_moe_stream": (_vp, [_vp]),
+    "nsl_moe_set_rounding": (None, [_vp, _i]),
 }
 
 _lib = None

@@ -1,0 +1,86 @@
+"""One MoE expert layer through the C host layer (include/nslm_moe.h) against the oracle.
+
+Two comparisons: (1) with the engine's bf16 rounding points, against the oracle composed with the same points;
+(2) f32 throughout, against the CPU reference forward's arithmetic (double sums, no rounding) at the 1e-3 relative bar
+with identical top-k routing indices."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def engine_rounding_reference(oracle, h, x, logits, k):
+    """route -> per pair a = mv_gu, D = bf16(down a) -> out = sum_j wt_j D_j (plain f32), as the engine's kernels round."""
+    T = x.shape[0]
+    ind, wt = oracle.route(logits, k)
+    out = np.zeros((T, h.d), np.float32)
+    for t in range(T):
+        acc = np.zeros(h.d, np.float32)
+        for j in range(k):
+            e = int(ind[t, j])
+            a = oracle.mv_gu(h.matrix(oracle, "gate", e), h.matrix(oracle, "up", e), x[t])
+            D = oracle.mv(h.matrix(oracle, "down", e), a)[0]
+            acc = acc + wt[t, j] * D
+        out[t] = acc
+    return out, ind
+
+
+@pytest.mark.parametrize("d,ff,E,k,T", [(256, 64, 16, 4, 1), (256, 64, 16, 4, 8), (512, 128, 24, 8, 5), (2048, 512, 12, 8, 2)])
+def test_moe_layer_decode_rows(oracle, d, ff, E, k, T):
+    from nanoseedlm_b200 import moe
+    h = moe.HostLayer(oracle, d, ff, E, seed=d + T)
+    layer = moe.DeviceLayer.from_host(h)
+    m = moe.Moe(layer, k, 8)
+    x = oracle.normal(1 + T, T * d, bf16=True).reshape(T, d)
+    logits = oracle.normal(2 + T, T * E).reshape(T, E)
+    # (1) engine rounding points
+    out, ind = m.forward_host(x, logits)
+    ref, rind = engine_rounding_reference(oracle, h, x, logits, k)
+    assert np.array_equal(ind, rind)
+    scale = np.max(np.abs(ref))
+    assert np.max(np.abs(out - ref)) <= 4e-3 * scale        # a bf16 flip of one intermediate moves an output by < 1 bf16 ulp
+    assert np.mean(np.abs(out - ref) <= 1e-5 * scale) > 0.97
+    # (2) f32 throughout vs the CPU reference forward
+    m.set_rounding(False)
+    out32, ind32 = m.forward_host(x, logits)
+    ref64, rind64, _ = oracle.moe_layer(h, x, logits, k)
+    assert np.array_equal(ind32, rind64)
+    assert np.max(np.abs(out32 - ref64)) <= 1e-3 * np.max(np.abs(ref64))
+    assert np.max(np.abs(out32 - ref64)) <= 2e-5 * np.max(np.abs(ref64))   # what f32 accumulation actually gives
+    m.close()
+
+
+def test_moe_full_size_config1_properties(oracle):
+    """BASELINE config 1 at full size (hidden 2048, 128 experts of 512, top-8, M = 8): size-independent checks --
+    routing equals the oracle's, the layer is linear in the routing weights' experts (a token routed alone equals the
+    same token inside the batch, bit for bit), and one token's output equals the oracle's on its 8 experts."""
+    import torch
+    from nanoseedlm_b200 import moe
+    d, ff, E, k, M = 2048, 512, 128, 8, 8
+    gen = torch.Generator(device="cuda").manual_seed(7)
+    layer = moe.DeviceLayer.random_on_device(d, ff, E, gen)
+    m = moe.Moe(layer, k, M)
+    x = oracle.normal(11, M * d, bf16=True).reshape(M, d)
+    logits = oracle.normal(12, M * E).reshape(M, E)
+    out, ind = m.forward_host(x, logits)
+    rind, rwt = oracle.route(logits, k)
+    assert np.array_equal(ind, rind)
+    for t in (0, 5):
+        o1, i1 = m.forward_host(x[t:t + 1], logits[t:t + 1])
+        assert np.array_equal(i1[0], ind[t]) and np.array_equal(o1[0].view(np.uint32), out[t].view(np.uint32))
+    # token 3 against the oracle on the experts it routes to (weights copied back from the device)
+    t = 3
+    acc = np.zeros(d, np.float32)
+    for j in range(k):
+        e = int(ind[t, j])
+        mats = []
+        for st, (R, K) in ((layer.gate, (ff, d)), (layer.up, (ff, d)), (layer.down, (d, ff))):
+            mm = oracle.Matrix(R, K, 0, eb=st.eb[e])
+            mm.seeds[:] = st.seeds[e].cpu().numpy().view(np.uint16)
+            mm.coefs[:] = st.coefs[e].cpu().numpy().view(np.uint16)
+            mm.codes[:] = st.codes[e].cpu().numpy()
+            mats.append(mm)
+        a = oracle.mv_gu(mats[0], mats[1], x[t])
+        acc = acc + rwt[t, j] * oracle.mv(mats[2], a)[0]
+    assert np.max(np.abs(out[t] - acc)) <= 4e-3 * np.max(np.abs(acc))
+    m.close()
