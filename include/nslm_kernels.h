@@ -136,6 +136,10 @@ void nsl_mv_gu_raw(cudaStream_t s, const WSlice* wg, const WSlice* wu, int K, in
  * (nslm/lib_search4.c:22-31): bit-exact.  out is [R][K]. */
 void nsl_decode_f32(cudaStream_t s, WSlice w, int K, int R, float* out, const uint32_t* G);
 void nsl_decode_bf16(cudaStream_t s, WSlice w, int K, int R, uint16_t* out, const uint32_t* G);
+/* 0, or the code of the first bounded device-side wait that ran out in a GEMM block since the last call (1 a producer
+ * waiting for a free stage, 2 the epilogue waiting for the accumulator, 3 the MMA issuer waiting for a full stage); a
+ * block that gives up frees its tensor memory and returns without storing.  Call after synchronising the stream. */
+int nsl_mm_status(void);
 /* Fills a 65536-entry host array with the stream table the G arguments expect (lfsr_stream32 of every seed,
  * nslm/lfsr.h:53-59). */
 void nsl_stream_table(uint32_t* host_table);

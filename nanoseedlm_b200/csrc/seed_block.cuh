@@ -243,9 +243,10 @@ __device__ __forceinline__ u64 add2(u64 a, u64 b) {
 
 // The 32 state-value pairs of the blocks whose seeds are the two halves of sw: v[4c+p] = {even, odd}.
 __device__ __forceinline__ void pair_states(const StreamTab& tab, uint32_t sw, u64* v) {
-    const uint32_t s0 = sw & 0xFFFFu, s1 = sw >> 16;
-    const uint32_t g0 = stream_bits(tab, s0), g1 = stream_bits(tab, s1);
-    const uint32_t a0 = g0 * 65536u + s0, a1 = g1 * 65536u + s1;
+    // table indices and the two windows by byte permutes: one logic-pipe operation each
+    const uint32_t g0 = tab.lo[__byte_perm(sw, 0, 0x4440)] ^ tab.hi[__byte_perm(sw, 0, 0x4441)];
+    const uint32_t g1 = tab.lo[__byte_perm(sw, 0, 0x4442)] ^ tab.hi[__byte_perm(sw, 0, 0x4443)];
+    const uint32_t a0 = __byte_perm(sw, g0, 0x5410), a1 = __byte_perm(sw, g1, 0x5432);
 #define NSL_V2(C)                                                                  \
     {                                                                              \
         const uint32_t y0 = weight_word<C>(a0, g0), y1 = weight_word<C>(a1, g1);   \

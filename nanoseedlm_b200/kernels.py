@@ -84,6 +84,9 @@ class SeedWeight:
 def _done():
     torch.cuda.synchronize()
     L.check()
+    st = L.load().nsl_mm_status()
+    if st:
+        raise RuntimeError(f"a GEMM block gave up on a bounded wait (code {st})")
 
 
 def kt_decode(w, s=0, bf16=False):
