@@ -1,0 +1,45 @@
+/* nslm_ep.h - device steps of the expert-parallel dispatch / combine layer.
+ *
+ * The reference is single-GPU (engine/mova_cuda.c:590 selects device 0 and no collective exists in its tree): its
+ * experts are tiered between VRAM and host memory, never sharded.  This layer has therefore no counterpart in the
+ * reference; it follows the reference's kernel-call conventions (stream first, asynchronous, caller-owned buffers,
+ * nothing allocated) and sits between its router (kq4_route) and its combine (kq4_moe_combine).
+ *
+ * Experts are sharded evenly: rank r owns experts [r E/N, (r+1) E/N).  Every rank routes its own tokens; the token
+ * rows (packed bf16) and their routing travel to every rank in one all-to-all; each rank keeps the (token, expert)
+ * pairs it owns (nsl_ep_plan), runs them through the seed mat-vec kernels on the received rows (nsl_mv_gu_rows,
+ * nsl_mv_sel_rows), pre-sums each token's local experts (nsl_ep_combine); the partial rows go back in a second
+ * all-to-all and the source rank adds them in rank order (nsl_ep_reduce).  The collectives themselves are NCCL calls
+ * issued by the host layer; the kernels here read only local memory. */
+#pragma once
+#include "nslm_kernels.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Gathered routing of T = n_ranks * t_loc tokens: token (r, t) has its k expert ids at ind[r * rank_stride + t * k ..]
+ * and weights at wt[the same index] (rank_stride in 4-byte elements: the receive buffer's per-rank chunk).  Keeps the
+ * pairs whose expert lies in [lo, hi), in token order:  sel[p] = expert - lo,  xrow[p] = r * row_stride + t (the row of
+ * the received input buffer),  wsel[p] = the routing weight;  tok_off[g] = index of the first pair of token
+ * g = r * t_loc + t, tok_off[T] = *count = the number of pairs kept.  T * k <= 65536. */
+void nsl_ep_plan(cudaStream_t s, const int32_t* ind, const float* wt, int n_ranks, int t_loc, int k, int rank_stride,
+                 int row_stride, int lo, int hi, int32_t* sel, int32_t* xrow, float* wsel, int32_t* tok_off,
+                 int32_t* count);
+/* Gather mat-vecs over a compacted pair list whose length is on the device (see nsl_ep_plan): pair p uses slice
+ * sel[p]; the gate+up form reads input row xrow[p] of x (packed bf16 rows of stride xs elements when x_bf16, else f32),
+ * the second form reads row p.  max_pairs bounds the list, *count is its length, expected_pairs sizes the work items. */
+void nsl_mv_gu_rows(cudaStream_t s, const WSlice* wg, const WSlice* wu, int K, int R, const void* x, int xs, int x_bf16,
+                    float* a, int ys, const int32_t* sel, const int32_t* xrow, int max_pairs, const int32_t* count,
+                    int expected_pairs, const uint32_t* G);
+void nsl_mv_sel_rows(cudaStream_t s, const WSlice* ws, int K, int R, const float* x, int xs, float* y, int ys,
+                     const int32_t* sel, int max_pairs, const int32_t* count, int expected_pairs, const uint32_t* G);
+/* partial[g][:] = sum over pairs p in [tok_off[g], tok_off[g+1]) of wsel[p] * D[p][:], pairs ascending (zeros when the
+ * token has no expert here).  T tokens of width d. */
+void nsl_ep_combine(cudaStream_t s, const float* D, const float* wsel, const int32_t* tok_off, int T, int d, float* partial);
+/* out[t][:] = parts[0][t][:] + parts[1][t][:] + ... in rank order; parts is [n_ranks][t_loc][d]. */
+void nsl_ep_reduce(cudaStream_t s, const float* parts, int n_ranks, int t_loc, int d, float* out);
+
+#ifdef __cplusplus
+}
+#endif

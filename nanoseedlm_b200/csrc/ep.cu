@@ -1,0 +1,98 @@
+// Device steps of the expert-parallel layer (include/nslm_ep.h): the per-rank pair plan, the per-token pre-sum of the
+// local experts' outputs and the rank-order sum of the returned partial rows.  They read and write local memory only.
+#include "common.cuh"
+
+namespace nsl {
+
+constexpr uint32_t FULL = 0xFFFFFFFFu;
+
+// One block.  Pairs are visited in token order in rounds of 1024; a ballot prefix inside each warp and a scan of the
+// 32 warp counts give every kept pair its slot, so the compacted list keeps token order.
+__global__ void __launch_bounds__(1024) ep_plan_kernel(const int32_t* __restrict__ ind, const float* __restrict__ wt, int n_ranks,
+                                                       int t_loc, int k, int rank_stride, int row_stride, int lo, int hi,
+                                                       int32_t* __restrict__ sel, int32_t* __restrict__ xrow,
+                                                       float* __restrict__ wsel, int32_t* __restrict__ tok_off,
+                                                       int32_t* __restrict__ count) {
+    __shared__ int wsum[32];
+    __shared__ int base;
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    const int T = n_ranks * t_loc, n = T * k;
+    if (tid == 0) base = 0;
+    __syncthreads();
+    for (int c0 = 0; c0 < n; c0 += 1024) {
+        const int i = c0 + tid;
+        int e = -1, g = 0, r = 0, t = 0, j = 0;
+        float wv = 0.0f;
+        if (i < n) {
+            g = i / k; j = i % k; r = g / t_loc; t = g % t_loc;
+            const size_t at = (size_t) r * rank_stride + (size_t) t * k + j;
+            e = ind[at];
+            wv = wt[at];
+        }
+        const bool keep = e >= lo && e < hi;
+        const uint32_t m = __ballot_sync(FULL, keep);
+        if (lane == 0) wsum[w] = __popc(m);
+        __syncthreads();
+        int before = base, total = 0;
+        for (int q = 0; q < 32; ++q) { if (q < w) before += wsum[q]; total += wsum[q]; }
+        const int pos = before + __popc(m & ((1u << lane) - 1u));
+        if (keep) { sel[pos] = e - lo; xrow[pos] = r * row_stride + t; wsel[pos] = wv; }
+        if (i < n && j == 0) tok_off[g] = pos;   // pairs of token g start here (kept or not, the running position)
+        __syncthreads();
+        if (tid == 0) base += total;
+        __syncthreads();
+    }
+    if (tid == 0) { tok_off[T] = base; *count = base; }
+}
+
+__global__ void ep_combine_kernel(const float* __restrict__ D, const float* __restrict__ wsel, const int32_t* __restrict__ tok_off,
+                                  int d, float* __restrict__ partial) {
+    const int g = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= d) return;
+    const int p0 = tok_off[g], p1 = tok_off[g + 1];
+    float acc = 0.0f;
+    for (int p = p0; p < p1; ++p) acc += wsel[p] * D[(size_t) p * d + c];
+    partial[(size_t) g * d + c] = acc;
+}
+
+__global__ void ep_reduce_kernel(const float* __restrict__ parts, int n_ranks, int t_loc, int d, float* __restrict__ out) {
+    const size_t n = (size_t) t_loc * d;
+    for (size_t i = (size_t) blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t) gridDim.x * blockDim.x) {
+        float acc = parts[i];
+        for (int r = 1; r < n_ranks; ++r) acc += parts[(size_t) r * n + i];
+        out[i] = acc;
+    }
+}
+
+}   // namespace nsl
+
+using namespace nsl;
+
+extern "C" {
+
+void nsl_ep_plan(cudaStream_t s, const int32_t* ind, const float* wt, int n_ranks, int t_loc, int k, int rank_stride,
+                 int row_stride, int lo, int hi, int32_t* sel, int32_t* xrow, float* wsel, int32_t* tok_off,
+                 int32_t* count) {
+    if ((long long) n_ranks * t_loc * k > 65536 || n_ranks < 1 || t_loc < 1 || k < 1) {
+        set_error("nsl_ep_plan: %d ranks x %d tokens x top %d is out of range", n_ranks, t_loc, k);
+        return;
+    }
+    ep_plan_kernel<<<1, 1024, 0, s>>>(ind, wt, n_ranks, t_loc, k, rank_stride, row_stride, lo, hi, sel, xrow, wsel, tok_off, count);
+    count_launch();
+}
+
+void nsl_ep_combine(cudaStream_t s, const float* D, const float* wsel, const int32_t* tok_off, int T, int d, float* partial) {
+    if (T < 1 || d < 1) return;
+    ep_combine_kernel<<<dim3((unsigned) (d + 255) / 256, (unsigned) T), 256, 0, s>>>(D, wsel, tok_off, d, partial);
+    count_launch();
+}
+
+void nsl_ep_reduce(cudaStream_t s, const float* parts, int n_ranks, int t_loc, int d, float* out) {
+    if (n_ranks < 1 || t_loc < 1 || d < 1) return;
+    const size_t n = (size_t) t_loc * d;
+    const unsigned blocks = (unsigned) ((n + 255) / 256 < (size_t) sm_count() * 4 ? (n + 255) / 256 : (size_t) sm_count() * 4);
+    ep_reduce_kernel<<<blocks, 256, 0, s>>>(parts, n_ranks, t_loc, d, out);
+    count_launch();
+}
+
+}   // extern "C"

@@ -33,6 +33,9 @@ struct MvParams {
     float* y;
     const uint32_t* G;
     int K, R, P, xdiv, xs, ys, add, raw;
+    const int32_t* xrow;    // optional: pair p reads input row xrow[p] (instead of p / xdiv)
+    const int32_t* count;   // optional: the pair count is read on the device (<= P)
+    int xbf16;              // inputs are packed bf16 rows (row stride xs in bf16 elements)
 };
 
 __device__ __forceinline__ float silu_bf(float g) {   // each op rounded to bf16 (engine/kernels_moe.cu:28-31)
@@ -85,8 +88,10 @@ __device__ __forceinline__ void store_out(const MvParams& a, int pair, int r, fl
 }
 
 // ---- one token per pair, inputs in registers: rows of 1, 2, 4, .. 32 chunks (K = 64 .. 2048) -------------------------
-// Warps are dealt to pairs (P pairs share the grid's warps evenly); a warp loads its pair's inputs once and strides
-// over the pair's rows, prefetching the next row's streams while it expands the current one.
+// The work is the pair-major sequence of row steps (a step = the 32 / lanes-per-row rows a warp expands at once); every
+// warp of the grid takes one contiguous, equal share of it.  A share touches one or two pairs (more only when there are
+// more pairs than warps), so a warp loads a pair's inputs into registers at most that often, the shares differ by at
+// most one step, and inside a share the next row's streams are prefetched while the current row is expanded.
 template <int MODE>
 __global__ void __launch_bounds__(MV_THREADS, 1) mv_regx_kernel(MvParams a, KConst kc, int lpr_log2) {
     __shared__ StreamTab tab;
@@ -95,23 +100,43 @@ __global__ void __launch_bounds__(MV_THREADS, 1) mv_regx_kernel(MvParams a, KCon
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int lpr = 1 << lpr_log2, rpw = 32 >> lpr_log2;
     const int jc = lane & (lpr - 1), ro = lane >> lpr_log2;
-    const int nw = gridDim.x * MV_WARPS, gw = blockIdx.x * MV_WARPS + warp;
-    const int wpp = nw / a.P > 0 ? nw / a.P : 1;
-    const long long nvw = (long long) a.P * wpp;
-    for (long long vw = gw; vw < nvw; vw += nw) {
-        const int pair = (int) (vw / wpp), wi = (int) (vw % wpp);
+    const long long nw = (long long) gridDim.x * MV_WARPS, gw = (long long) blockIdx.x * MV_WARPS + warp;
+    const int P = a.count ? min(*a.count, a.P) : a.P;
+    const int rs = (a.R + rpw - 1) / rpw;                 // row steps per pair
+    const long long total = (long long) P * rs;
+    const long long begin = gw * total / nw, end = (gw + 1) * total / nw;
+    if (begin >= end) return;
+    const int p_first = (int) (begin / rs), p_last = (int) ((end - 1) / rs);
+    for (int pair = p_first; pair <= p_last; ++pair) {
+        const int s_lo = pair == p_first ? (int) (begin - (long long) pair * rs) : 0;
+        const int s_hi = pair == p_last ? (int) (end - (long long) pair * rs) : rs;
         const int slice = a.sel ? a.sel[pair] : 0;
         const WSlice wa = a.ws ? a.ws[slice] : a.w0;
         WSlice wb = wa;
         if (MODE == MODE_GU) wb = a.wu[slice];
         u64 x2[32], xm2[16];
         {
+            const int xr = a.xrow ? a.xrow[pair] : pair / a.xdiv;
             float x[64], xm[32];
-            const float4* xp = (const float4*) (a.x + (size_t) (pair / a.xdiv) * a.xs + (size_t) jc * 64);
+            if (a.xbf16) {
+                const uint4* xp = (const uint4*) ((const uint16_t*) a.x + (size_t) xr * a.xs + (size_t) jc * 64);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const float4 t = __ldg(xp + i);
-                x[4 * i] = t.x * NSL_XSCALE; x[4 * i + 1] = t.y * NSL_XSCALE; x[4 * i + 2] = t.z * NSL_XSCALE; x[4 * i + 3] = t.w * NSL_XSCALE;
+                for (int i = 0; i < 8; ++i) {
+                    const uint4 t = __ldg(xp + i);
+                    const uint32_t u[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        x[8 * i + 2 * j] = __uint_as_float(u[j] << 16) * NSL_XSCALE;
+                        x[8 * i + 2 * j + 1] = __uint_as_float(u[j] & 0xFFFF0000u) * NSL_XSCALE;
+                    }
+                }
+            } else {
+                const float4* xp = (const float4*) (a.x + (size_t) xr * a.xs + (size_t) jc * 64);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float4 t = __ldg(xp + i);
+                    x[4 * i] = t.x * NSL_XSCALE; x[4 * i + 1] = t.y * NSL_XSCALE; x[4 * i + 2] = t.z * NSL_XSCALE; x[4 * i + 3] = t.w * NSL_XSCALE;
+                }
             }
 #pragma unroll
             for (int b = 0; b < 8; ++b) block_offsets(x + 8 * b, xm + 4 * b);
@@ -124,18 +149,17 @@ __global__ void __launch_bounds__(MV_THREADS, 1) mv_regx_kernel(MvParams a, KCon
             }
         }
         const float sca = slice_scale(wa.eb), scb = slice_scale(wb.eb);
-        const int step = wpp * rpw;
-        int r = wi * rpw + ro;
+        int r = s_lo * rpw + ro;
         Chunk ka, kb;
         if (r < a.R) {
             ka = load_chunk(wa, (size_t) r * lpr + jc);
             if (MODE == MODE_GU) kb = load_chunk(wb, (size_t) r * lpr + jc);
         }
-        for (int rbase = wi * rpw; rbase < a.R; rbase += step, r += step) {
+        for (int st = s_lo; st < s_hi; ++st, r += rpw) {
             const bool ok = r < a.R;
-            const int rn = r + step;
+            const int rn = r + rpw;
             Chunk na, nb;
-            if (rn < a.R) {   // next row's streams in flight during this row's expansion
+            if (st + 1 < s_hi && rn < a.R) {   // next row's streams in flight during this row's expansion
                 na = load_chunk(wa, (size_t) rn * lpr + jc);
                 if (MODE == MODE_GU) nb = load_chunk(wb, (size_t) rn * lpr + jc);
             }
@@ -349,7 +373,7 @@ static void launch_smemx(cudaStream_t s, const MvParams& a, int lpr_log2, int de
 }
 
 template <int MODE>
-static void launch_mv(cudaStream_t s, const MvParams& a, int T) {
+static void launch_mv(cudaStream_t s, const MvParams& a, int T, int p_hint = 0) {
     if (a.R <= 0 || a.P <= 0 || T <= 0) return;
     if (a.K <= 0 || a.K % 8) { set_error("seed mat-vec: K = %d is not a multiple of 8", a.K); return; }
     if (T > MV_MAXT) { set_error("seed mat-vec: %d tokens, at most %d", T, MV_MAXT); return; }
@@ -359,6 +383,10 @@ static void launch_mv(cudaStream_t s, const MvParams& a, int T) {
     // every allocator the callers use, and a row's chunks are contiguous, so only the inputs are checked here.
     const bool chunked = a.K % 64 == 0 && aligned16(a.x) && a.xs % 4 == 0;
     const bool pow2 = ch > 0 && (ch & (ch - 1)) == 0;
+    if ((a.xrow || a.count || a.xbf16) && !(chunked && pow2 && ch <= 32)) {
+        set_error("seed mat-vec: the row-index / device-count / bf16-input forms need K = 64 * 2^j <= 2048 (K = %d)", a.K);
+        return;
+    }
     if (chunked && T == 1 && pow2 && ch <= 32) {
         mv_regx_kernel<MODE><<<sms, MV_THREADS, 0, s>>>(a, kconst(), log2_floor(ch));
         count_launch();
@@ -395,35 +423,49 @@ extern "C" {
 void kc_mv(cudaStream_t s, int fmt, WSlice w, int K, int R, const float* x, int xs, float* y, int ys, int T, int add,
            const uint32_t* G) {
     if (!seed_fmt(fmt, "kc_mv")) return;
-    MvParams a = {NULL, NULL, w, NULL, x, y, G, K, R, T, 1, xs, ys, add, 0};
+    MvParams a = {NULL, NULL, w, NULL, x, y, G, K, R, T, 1, xs, ys, add, 0, NULL, NULL, 0};
     launch_mv<MODE_ROUND>(s, a, T);
 }
 
 void kc_mv_sel(cudaStream_t s, int fmt, const WSlice* ws, int K, int R, const float* x, int xs, float* y, int ys,
                const int32_t* sel, int P, int xdiv, const uint32_t* G) {
     if (!seed_fmt(fmt, "kc_mv_sel")) return;
-    MvParams a = {ws, NULL, WSlice{}, sel, x, y, G, K, R, P, xdiv, xs, ys, 0, 0};
+    MvParams a = {ws, NULL, WSlice{}, sel, x, y, G, K, R, P, xdiv, xs, ys, 0, 0, NULL, NULL, 0};
     launch_mv<MODE_ROUND>(s, a, 1);
 }
 
 void kc_mv_gu(cudaStream_t s, int fmt, const WSlice* wg, const WSlice* wu, int K, int R, const float* x, int xs, float* out,
               int ys, const int32_t* sel, int P, int xdiv, const uint32_t* G) {
     if (!seed_fmt(fmt, "kc_mv_gu")) return;
-    MvParams a = {wg, wu, WSlice{}, sel, x, out, G, K, R, P, xdiv, xs, ys, 0, 0};
+    MvParams a = {wg, wu, WSlice{}, sel, x, out, G, K, R, P, xdiv, xs, ys, 0, 0, NULL, NULL, 0};
     launch_mv<MODE_GU>(s, a, 1);
 }
 
 void nsl_mv_raw(cudaStream_t s, const WSlice* ws, int K, int R, const float* x, int xs, float* y, int ys,
                 const int32_t* sel, int P, int xdiv, const uint32_t* G) {
-    MvParams a = {sel ? ws : NULL, NULL, WSlice{}, sel, x, y, G, K, R, P, xdiv > 0 ? xdiv : 1, xs, ys, 0, 1};
+    MvParams a = {sel ? ws : NULL, NULL, WSlice{}, sel, x, y, G, K, R, P, xdiv > 0 ? xdiv : 1, xs, ys, 0, 1, NULL, NULL, 0};
     if (!sel) a.w0 = *ws;   // dense: ws is a host pointer to the one slice
     launch_mv<MODE_ROUND>(s, a, sel ? 1 : P);
 }
 
 void nsl_mv_gu_raw(cudaStream_t s, const WSlice* wg, const WSlice* wu, int K, int R, const float* x, int xs, float* out,
                    int ys, const int32_t* sel, int P, int xdiv, const uint32_t* G) {
-    MvParams a = {wg, wu, WSlice{}, sel, x, out, G, K, R, P, xdiv, xs, ys, 0, 1};
+    MvParams a = {wg, wu, WSlice{}, sel, x, out, G, K, R, P, xdiv, xs, ys, 0, 1, NULL, NULL, 0};
     launch_mv<MODE_GU>(s, a, 1);
+}
+
+// Expert-parallel forms: a compacted pair list whose length lives on the device.  Pair p uses slice sel[p] and input
+// row xrow[p] of x, which holds packed bf16 rows when x_bf16 is set; at most max_pairs pairs, *count of them valid.
+void nsl_mv_gu_rows(cudaStream_t s, const WSlice* wg, const WSlice* wu, int K, int R, const void* x, int xs, int x_bf16,
+                    float* out, int ys, const int32_t* sel, const int32_t* xrow, int max_pairs, const int32_t* count,
+                    int expected_pairs, const uint32_t* G) {
+    MvParams a = {wg, wu, WSlice{}, sel, (const float*) x, out, G, K, R, max_pairs, 1, xs, ys, 0, 0, xrow, count, x_bf16};
+    launch_mv<MODE_GU>(s, a, 1, expected_pairs);
+}
+void nsl_mv_sel_rows(cudaStream_t s, const WSlice* ws, int K, int R, const float* x, int xs, float* y, int ys,
+                     const int32_t* sel, int max_pairs, const int32_t* count, int expected_pairs, const uint32_t* G) {
+    MvParams a = {ws, NULL, WSlice{}, sel, x, y, G, K, R, max_pairs, 1, xs, ys, 0, 0, NULL, count, 0};
+    launch_mv<MODE_ROUND>(s, a, 1, expected_pairs);
 }
 
 void nsl_decode_f32(cudaStream_t s, WSlice w, int K, int R, float* out, const uint32_t* G) {

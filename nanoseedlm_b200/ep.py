@@ -1,0 +1,123 @@
+"""Expert-parallel dispatch / combine layer: one process per GPU, experts sharded evenly, two all-to-alls per step.
+
+The reference is single-GPU and shards nothing (engine/mova_cuda.c:590); this layer is new and sits where its engine
+calls the routed experts (engine/qwen4_cuda.c:1071-1078).  Rank r owns experts [r E/N, (r+1) E/N) and t_loc tokens.
+
+A step, on every rank:
+  1. route the local tokens (top-k over all E experts) and pack their rows to bf16;
+  2. DISPATCH all-to-all: every rank receives every rank's chunk = [t_loc rows of bf16 | ids | weights] (at decode batch
+     sizes a token needs most ranks -- 5.9 of 8 at top-10 over 512 experts -- so the chunk carries all local rows);
+  3. plan: keep the (token, expert) pairs whose expert is local, in token order;
+  4. the local experts' gate+up+SwiGLU and down mat-vecs over those pairs, reading the received rows in place;
+  5. pre-sum each token's local experts into one partial row;
+  6. COMBINE all-to-all: the partial rows go back to the ranks that own the tokens;
+  7. the owner adds the N partial rows in rank order.
+Steps 1, 3-5 and 7 are supplied by a backend: CudaBackend calls the C ABI (include/nslm_ep.h); the tests' CPU backend
+does the same steps with the oracle so that the plumbing runs under gloo without a GPU."""
+import ctypes as C
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+
+def chunk_layout(t_loc, d, k):
+    """Byte layout of one rank's dispatch chunk, padded so that a chunk is a whole number of bf16 rows."""
+    row = 2 * d
+    x_bytes = t_loc * row
+    ind_off = x_bytes
+    wt_off = ind_off + 4 * t_loc * k
+    total = wt_off + 4 * t_loc * k
+    total = (total + row - 1) // row * row
+    return {"row": row, "ind_off": ind_off, "wt_off": wt_off, "bytes": total, "rows": total // row}
+
+
+class ExpertParallelMoe:
+    def __init__(self, backend, d, k, n_exp_total, t_loc, group=None):
+        self.be, self.d, self.k, self.E, self.t_loc, self.group = backend, d, k, n_exp_total, t_loc, group
+        self.N = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        assert n_exp_total % self.N == 0, "experts must divide evenly over the ranks"
+        self.e_loc = n_exp_total // self.N
+        self.lo, self.hi = self.rank * self.e_loc, (self.rank + 1) * self.e_loc
+        self.lay = chunk_layout(t_loc, d, k)
+        dev = backend.device
+        self.send = torch.zeros(self.N, self.lay["bytes"], dtype=torch.uint8, device=dev)
+        self.recv = torch.zeros(self.N, self.lay["bytes"], dtype=torch.uint8, device=dev)
+        self.partial = torch.zeros(self.N, t_loc, d, dtype=torch.float32, device=dev)
+        self.parts = torch.zeros(self.N, t_loc, d, dtype=torch.float32, device=dev)
+        self.out = torch.zeros(t_loc, d, dtype=torch.float32, device=dev)
+        backend.setup(self)
+
+    def _all_to_all(self, out, inp):
+        if self.N == 1:
+            out.copy_(inp)
+        else:
+            dist.all_to_all_single(out.view(-1), inp.view(-1), group=self.group)
+
+    def step(self, x, logits):
+        """x [t_loc][d] f32 (bf16-valued), logits [t_loc][E] -> out [t_loc][d] (this rank's tokens)."""
+        be = self.be
+        be.route_and_pack(self, x, logits)                 # fills send[0]
+        if self.N > 1:
+            self.send[1:] = self.send[0]
+        self._all_to_all(self.recv, self.send)             # dispatch
+        be.local_experts(self)                             # plan + mat-vecs + per-token pre-sum -> partial [N][t_loc][d]
+        self._all_to_all(self.parts, self.partial)         # combine
+        be.reduce(self)                                    # out = sum_r parts[r]
+        return self.out
+
+
+class CudaBackend:
+    """The steps on the GPU through the C ABI; layer = this rank's experts (moe.DeviceLayer with e_loc experts)."""
+
+    def __init__(self, layer, expected_pairs=0):
+        from . import lib as L
+        from .kernels import stream_table
+        self.L, self.lib, self.layer = L, L.load(), layer
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        self.G = stream_table()
+        self.expected_pairs = expected_pairs
+
+    def setup(self, ep):
+        T, k, d, ff = ep.N * ep.t_loc, ep.k, ep.d, self.layer.ff
+        P = T * k
+        z = lambda *s, dt=torch.float32: torch.zeros(*s, dtype=dt, device=self.device)
+        self.ind, self.wt = z(ep.t_loc, k, dt=torch.int32), z(ep.t_loc, k)
+        self.sel, self.xrow, self.wsel = z(P, dt=torch.int32), z(P, dt=torch.int32), z(P)
+        self.tok_off, self.count = z(T + 1, dt=torch.int32), z(1, dt=torch.int32)
+        self.A, self.D = z(P, ff), z(P, d)
+        if not self.expected_pairs:
+            self.expected_pairs = max(1, P // ep.N)
+
+    def set_layer(self, layer):
+        self.layer = layer
+
+    def _s(self):
+        return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def route_and_pack(self, ep, x, logits):
+        lib, s, lay = self.lib, self._s(), ep.lay
+        chunk = ep.send[0]
+        ind = chunk[lay["ind_off"]:lay["wt_off"]].view(torch.int32)
+        wt = chunk[lay["wt_off"]:lay["wt_off"] + 4 * ep.t_loc * ep.k].view(torch.float32)
+        lib.nsl_route(s, ep.E, ep.k, logits.data_ptr(), ep.E, ind.data_ptr(), wt.data_ptr(), ep.t_loc)
+        lib.kc_pack_input_bf16(s, x.data_ptr(), chunk.data_ptr(), ep.t_loc * ep.d)
+
+    def local_experts(self, ep):
+        lib, s, lay, lyr = self.lib, self._s(), ep.lay, self.layer
+        base = ep.recv.data_ptr()
+        T = ep.N * ep.t_loc
+        lib.nsl_ep_plan(s, base + lay["ind_off"], base + lay["wt_off"], ep.N, ep.t_loc, ep.k, lay["bytes"] // 4, lay["rows"],
+                        ep.lo, ep.hi, self.sel.data_ptr(), self.xrow.data_ptr(), self.wsel.data_ptr(),
+                        self.tok_off.data_ptr(), self.count.data_ptr())
+        P = T * ep.k
+        lib.nsl_mv_gu_rows(s, lyr.gate.table.data_ptr(), lyr.up.table.data_ptr(), lyr.d, lyr.ff, base, ep.d, 1,
+                           self.A.data_ptr(), lyr.ff, self.sel.data_ptr(), self.xrow.data_ptr(), P, self.count.data_ptr(),
+                           self.expected_pairs, self.G.data_ptr())
+        lib.nsl_mv_sel_rows(s, lyr.down.table.data_ptr(), lyr.ff, lyr.d, self.A.data_ptr(), lyr.ff, self.D.data_ptr(), lyr.d,
+                            self.sel.data_ptr(), P, self.count.data_ptr(), self.expected_pairs, self.G.data_ptr())
+        lib.nsl_ep_combine(s, self.D.data_ptr(), self.wsel.data_ptr(), self.tok_off.data_ptr(), T, ep.d, ep.partial.data_ptr())
+
+    def reduce(self, ep):
+        self.lib.nsl_ep_reduce(self._s(), ep.parts.data_ptr(), ep.N, ep.t_loc, ep.d, ep.out.data_ptr())

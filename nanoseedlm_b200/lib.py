@@ -79,6 +79,12 @@ PROTOTYPES = {
     "nsl_moe_dev_wt": (_vp, [_vp]),
     "nsl_moe_stream": (_vp, [_vp]),
     "nsl_moe_set_rounding": (None, [_vp, _i]),
+    # include/nslm_ep.h
+    "nsl_ep_plan": (None, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "nsl_mv_gu_rows": (None, [_vp, _vp, _vp, _i, _i, _vp, _i, _i, _vp, _i, _vp, _vp, _i, _vp, _i, _vp]),
+    "nsl_mv_sel_rows": (None, [_vp, _vp, _i, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp]),
+    "nsl_ep_combine": (None, [_vp, _vp, _vp, _vp, _i, _i, _vp]),
+    "nsl_ep_reduce": (None, [_vp, _vp, _i, _i, _i, _vp]),
 }
 
 _lib = None
