@@ -275,6 +275,132 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+EP_E, EP_K, EP_B = 512, 10, 64   # BASELINE config 3: 512 experts sharded over the ranks, 64 sequences x 1 token, top-10
+
+
+def ep_config(world, layers):
+    return {"workload": f"BASELINE config 3: expert-parallel synthetic MoE decode, {EP_E} seed-encoded experts (hidden {D}, "
+                        f"intermediate {FF}) sharded evenly over {world} GPU(s), {EP_B} sequences x 1 token, top-{EP_K}, "
+                        "dispatch/combine all-to-all of bf16 rows / f32 partial sums over NCCL",
+            "tokens": EP_B, "experts": EP_E, "top_k": EP_K, "hidden": D, "intermediate": FF, "parallelism": f"ep{world}",
+            "l2_policy": f"steps rotate over {layers} independent layers per rank ({layers * EP_E // world * 3 * BYTES_PER_MATRIX / 1e9:.2f} GB "
+                         "of packed streams per GPU), larger than the 126 MB L2"}
+
+
+def run_ep(args):
+    """Config 3 at any N (N = 1: all experts on one GPU, the base of the strong-scaling series)."""
+    import torch
+    import torch.distributed as dist
+    from nanoseedlm_b200 import ep, lib as L, moe
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    lib = L.load()
+    K, W = args.steps, max(args.warmup, 3)
+    e_loc, t_loc = EP_E // world, EP_B // world
+    NL = max(2, min(args.layers, int(6e9 // (e_loc * 3 * BYTES_PER_MATRIX))))
+    gen = torch.Generator(device="cuda").manual_seed(4321 + rank)
+    layers = [moe.DeviceLayer.random_on_device(D, FF, e_loc, gen) for _ in range(NL)]
+    be = ep.CudaBackend(layers[0])
+    epl = ep.ExpertParallelMoe(be, D, EP_K, EP_E, t_loc)
+    NB = 8
+    rng = np.random.default_rng(7 + rank)
+    hx = rng.standard_normal((NB, t_loc, D)).astype(np.float32)
+    hx = (hx.view(np.uint32) + 0x7FFF + ((hx.view(np.uint32) >> 16) & 1) & 0xFFFF0000).view(np.float32)
+    hl = rng.standard_normal((NB, t_loc, EP_E)).astype(np.float32)
+    dx, dl = torch.from_numpy(hx).cuda(), torch.from_numpy(hl).cuda()
+    px, pl = torch.from_numpy(hx).pin_memory(), torch.from_numpy(hl).pin_memory()
+    pout = torch.zeros(t_loc, D).pin_memory()
+    sx, sl = torch.zeros(t_loc, D, device="cuda"), torch.zeros(t_loc, EP_E, device="cuda")
+    stream = torch.cuda.Stream()
+    torch.cuda.synchronize()
+
+    def one(i):
+        be.set_layer(layers[i % NL])
+        epl.step(dx[i % NB], dl[i % NB])
+
+    with torch.cuda.stream(stream):
+        for i in range(W):
+            one(i)
+        stream.synchronize()
+        chunk = min(K, 100)
+        launches0 = lib.nsl_launch_count()
+        graph, captured = None, False
+        if world == 1 and not args.no_graph:   # with collectives in the step every launch is issued directly
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    for i in range(chunk):
+                        one(W + i)
+                captured = True
+            except Exception as ex:   # capture of the collectives not available: launch every step directly
+                graph, captured = None, False
+                sys.stderr.write(f"graph capture failed ({type(ex).__name__}); timing direct launches\n")
+        if not captured:
+            for i in range(chunk):
+                one(W + i)
+        launches = (lib.nsl_launch_count() - launches0) // chunk * K
+        if captured:
+            graph.replay()
+        stream.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local) as clocks:
+            e0.record(stream)
+            if captured:
+                for _ in range(K // chunk):
+                    graph.replay()
+                for i in range(K % chunk):
+                    one(W + i)
+            else:
+                for i in range(K):
+                    one(W + i)
+            e1.record(stream)
+            e1.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        # e2e: the rank's token rows and logits from pinned host memory, its output rows back, every step
+        KE = min(K, 500)
+        for i in range(W):
+            sx.copy_(px[i % NB], non_blocking=True); sl.copy_(pl[i % NB], non_blocking=True)
+            be.set_layer(layers[i % NL]); pout.copy_(epl.step(sx, sl), non_blocking=True); stream.synchronize()
+        if world > 1:
+            dist.barrier()
+        t0 = time.perf_counter()
+        for i in range(KE):
+            sx.copy_(px[(W + i) % NB], non_blocking=True); sl.copy_(pl[(W + i) % NB], non_blocking=True)
+            be.set_layer(layers[(W + i) % NL]); pout.copy_(epl.step(sx, sl), non_blocking=True); stream.synchronize()
+        e2e_s = (time.perf_counter() - t0) / KE
+    if world > 1:
+        t = torch.tensor([ms, e2e_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_s = float(t[0].item()), float(t[1].item())
+    L.check()
+    ms_per_step = ms / K
+    if rank == 0:
+        peaks, peak_kind = measured_peaks()
+        line = {"metric": "seed_decode_moe_gemv_tokens_per_s", "value": EP_B / (ms_per_step * 1e-3), "unit": "tok/s",
+                "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_per_step, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": ep_config(world, NL),
+                "gpu_launches": int(launches), "cuda_graph": captured, "clocks": clocks.summary(),
+                "e2e": {"value": EP_B / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": t_loc * D * 4 + t_loc * EP_E * 4,
+                        "d2h_bytes_per_step": t_loc * D * 4, "ms_per_step": e2e_s * 1e3},
+                "roofline": {"bound": "hbm", "kernel": "mv_regx_kernel<gate+up> over this rank's pairs", "achieved": None,
+                             "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": None, "peak_kind": peak_kind, "traffic": None,
+                             "note": "per-kernel roofline is reported by the 1-GPU config-1 line; this line is the end-to-end step"}}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -284,12 +410,20 @@ def main():
     ap.add_argument("--tokens", type=int, default=8, choices=[1, 2, 3, 4, 5, 6, 7, 8])
     ap.add_argument("--layers", type=int, default=20)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--workload", default=None, choices=["cfg1", "cfg3"],
+                    help="cfg1: one GPU's MoE decode layer (default at 1 GPU); cfg3: expert-parallel decode (default at >1)")
     args = ap.parse_args()
     if args.impl == "reference":
         if int(os.environ.get("RANK", "0")) == 0:
             run_reference(args)
         return
-    run_ours(args)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    workload = args.workload or ("cfg1" if world == 1 else "cfg3")
+    if workload == "cfg3":
+        run_ep(args)
+    else:
+        run_ours(args)
 
 
 if __name__ == "__main__":
