@@ -123,6 +123,16 @@ void kc_cache_admit(cudaStream_t s, const CachePool* p, int sl, const int32_t* i
 void kc_cache_copy(cudaStream_t s, const CachePool* p, int blocks);
 
 /* ---- additions (no counterpart in the reference's header) ---------------------------------------------------------- */
+/* No counterpart in the reference.  kc_bucket for callers that cannot allocate device memory: code running inside a
+ * host framework that owns the allocator, a plugin loaded after the memory pool was sized, a latency path that may not
+ * call cudaMalloc.  The 2n+3 ints of work memory that kc_bucket takes from its caller live in an array built into the
+ * library (8 KB, held by every GPU that loads the library until the process exits), so the caller passes inputs and
+ * outputs only: perm and tiles as kc_bucket, ntiles_out[0] = the tile count.  n <= BUCKET_MAX_EXPERTS, else nothing is
+ * launched and nsl_last_error() says why.  Nothing is allocated or freed.  The first call on a device looks up the
+ * array's address (a host-side query): make that call before any stream capture starts.  All calls on a device share
+ * the array, which keeps the last call's offsets: calls that overlap on the GPU (two streams) race. */
+void nsl_bucket_noalloc(cudaStream_t s, const int32_t* inds, int count, int n, int32_t* perm, MmTile* tiles,
+                        int32_t* ntiles_out);
 /* The router with its two sizes passed directly. */
 void nsl_route(cudaStream_t s, int n_exp, int top_k, const float* logits, int ld, int32_t* ind, float* wt, int T);
 /* Mat-vec with the f32 accumulator stored unrounded (the CPU seed path's result convention,

@@ -275,6 +275,33 @@ __global__ void __launch_bounds__(512) cache_copy_kernel(CachePool p) {
     }
 }
 
+
+// ---- grouping without caller-provided work memory ---------------------------------------------------------------------
+// The offsets that bucket_count_kernel hands to bucket_place_kernel (2 n + 3 ints) live here instead of in a buffer the
+// caller allocates.  One array per GPU that loads the library, held until the process exits; sized for the largest
+// expert count the grouping accepts.
+constexpr int BUCKET_SCRATCH_INTS = 2 * BUCKET_MAX_EXPERTS + 3;
+static __device__ __align__(256) int32_t g_bucket_scratch[BUCKET_SCRATCH_INTS];
+
+__global__ void bucket_publish_kernel(const int32_t* __restrict__ work, int32_t* __restrict__ ntiles_out) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) ntiles_out[0] = work[0];
+}
+
+// The array's device address on the current device.  In host code the symbol's name is only a host-side handle, not an
+// address a kernel can use, so the address is asked for once per device with that device current.
+static int32_t* bucket_scratch_ptr() {
+    static int32_t* ptr[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { set_error("nsl_bucket_noalloc: no current device"); return NULL; }
+    if (!ptr[dev]) {
+        void* p = NULL;
+        const cudaError_t rc = cudaGetSymbolAddress(&p, g_bucket_scratch);
+        if (rc != cudaSuccess || !p) { set_error("nsl_bucket_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(rc)); return NULL; }
+        ptr[dev] = (int32_t*) p;
+    }
+    return ptr[dev];
+}
+
 }   // namespace nsl
 
 using namespace nsl;
@@ -330,6 +357,20 @@ void kc_bucket(cudaStream_t s, const int32_t* inds, int count, int n, int32_t* p
     bucket_count_kernel<<<1, 1024, 0, s>>>(inds, count, n, ntiles);
     bucket_place_kernel<<<(unsigned) n, 1024, 0, s>>>(inds, count, ntiles, perm, tiles);
     count_launch(2);
+}
+
+void nsl_bucket_noalloc(cudaStream_t s, const int32_t* inds, int count, int n, int32_t* perm, MmTile* tiles, int32_t* ntiles_out) {
+    if (n < 1 || n > BUCKET_MAX_EXPERTS) {
+        set_error("nsl_bucket_noalloc: %d experts, the built-in work array holds at most %d", n, BUCKET_MAX_EXPERTS);
+        return;
+    }
+    int32_t* work = bucket_scratch_ptr();
+    if (!work) return;
+    // every entry the placement reads is rewritten by the count kernel, so nothing has to be cleared between calls
+    bucket_count_kernel<<<1, 1024, 0, s>>>(inds, count, n, work);
+    bucket_place_kernel<<<(unsigned) n, 1024, 0, s>>>(inds, count, work, perm, tiles);
+    bucket_publish_kernel<<<1, 32, 0, s>>>(work, ntiles_out);
+    count_launch(3);
 }
 
 void kc_cache_admit(cudaStream_t s, const CachePool* p, int sl, const int32_t* inds, int count, int flags) {

@@ -54,6 +54,7 @@ PROTOTYPES = {
     "kq4_moe_combine": (None, [_vp, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _i]),
     "kc_cache_admit": (None, [_vp, C.POINTER(CachePool), _i, _vp, _i, _i]),
     "kc_cache_copy": (None, [_vp, C.POINTER(CachePool), _i]),
+    "nsl_bucket_noalloc": (None, [_vp, _vp, _i, _i, _vp, _vp, _vp]),
     "nsl_route": (None, [_vp, _i, _i, _vp, _i, _vp, _vp, _i]),
     "nsl_mv_raw": (None, [_vp, _vp, _i, _i, _vp, _i, _vp, _i, _vp, _i, _i, _vp]),
     "nsl_mv_gu_raw": (None, [_vp, _vp, _vp, _i, _i, _vp, _i, _vp, _i, _vp, _i, _i, _vp]),
