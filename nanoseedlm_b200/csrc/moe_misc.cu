@@ -15,15 +15,16 @@ constexpr uint32_t FULL = 0xFFFFFFFFu;
 // One warp per row.  Lane l holds experts l, l+32, ..; k rounds of a warp arg-max where equal logits go to the higher
 // expert id; weights exp(l - max) renormalised over the k picked.
 constexpr int ROUTE_PER_LANE = 32;   // experts <= 1024
+template <int PER>                   // experts per lane held in registers: E <= 32 * PER
 __global__ void __launch_bounds__(128) route_kernel(int E, int k, const float* __restrict__ logits, int ld,
                                                     int32_t* __restrict__ ind, float* __restrict__ wt, int T) {
     const int lane = threadIdx.x & 31, t = blockIdx.x * 4 + (threadIdx.x >> 5);
     if (t >= T) return;
     const float* l = logits + (size_t) t * ld;
-    float v[ROUTE_PER_LANE];
+    float v[PER];
     float mx = -INFINITY;
 #pragma unroll
-    for (int j = 0; j < ROUTE_PER_LANE; ++j) {
+    for (int j = 0; j < PER; ++j) {
         const int e = lane + 32 * j;
         v[j] = e < E ? l[e] : -INFINITY;
         mx = fmaxf(mx, v[j]);
@@ -34,7 +35,7 @@ __global__ void __launch_bounds__(128) route_kernel(int E, int k, const float* _
         float bv = -INFINITY;
         int bi = -1;
 #pragma unroll
-        for (int j = 0; j < ROUTE_PER_LANE; ++j) {
+        for (int j = 0; j < PER; ++j) {
             const int e = lane + 32 * j;
             if (e < E && (v[j] > bv || (v[j] == bv && e > bi))) { bv = v[j]; bi = e; }
         }
@@ -44,7 +45,7 @@ __global__ void __launch_bounds__(128) route_kernel(int E, int k, const float* _
             if (ov > bv || (ov == bv && oi > bi)) { bv = ov; bi = oi; }
         }
 #pragma unroll
-        for (int j = 0; j < ROUTE_PER_LANE; ++j)
+        for (int j = 0; j < PER; ++j)
             if (lane + 32 * j == bi) v[j] = -INFINITY;
         const float w = expf(bv - mx);
         top += w;
@@ -314,7 +315,10 @@ void nsl_route(cudaStream_t s, int n_exp, int top_k, const float* logits, int ld
         set_error("router: %d experts (at most %d), top %d (at most 32)", n_exp, 32 * ROUTE_PER_LANE, top_k);
         return;
     }
-    route_kernel<<<(T + 3) / 4, 128, 0, s>>>(n_exp, top_k, logits, ld, ind, wt, T);
+    const dim3 grid((unsigned) (T + 3) / 4);
+    if (n_exp <= 128) route_kernel<4><<<grid, 128, 0, s>>>(n_exp, top_k, logits, ld, ind, wt, T);
+    else if (n_exp <= 512) route_kernel<16><<<grid, 128, 0, s>>>(n_exp, top_k, logits, ld, ind, wt, T);
+    else route_kernel<32><<<grid, 128, 0, s>>>(n_exp, top_k, logits, ld, ind, wt, T);
     count_launch();
 }
 void kq4_route_ld(cudaStream_t s, const void* cfg, const float* logits, int ld, int32_t* ind, float* wt, int T) {
