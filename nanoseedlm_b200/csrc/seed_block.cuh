@@ -279,4 +279,32 @@ __device__ __forceinline__ u64 pair_dot(const u64* v, const u64* q, const u64* x
     return fma2(q[3], d3, fma2(q[2], d2, fma2(q[1], d1, mul2(q[0], d0))));
 }
 
+
+// Exact form for two adjacent blocks at once (the GEMM's weight tiles): w2[c] = {weight c of the even block, of the odd
+// block}, bit for bit as block_weights gives them.  sc2 = {exact_scale45 of the even block, of the odd block}.
+__device__ __forceinline__ void pair_weights(const StreamTab& tab, uint32_t sw, uint32_t cw, u64 sc2, const KConst& k, u64* w2) {
+    u64 v[32], q[4];
+    pair_states(tab, sw, v);
+    const uint32_t c1 = cw >> 16;
+    q[0] = add2(and_xor_pair<0x000Fu>(cw, c1, k.cxor_x[0]), pack2(k.coff_x[0], k.coff_x[0]));
+    q[1] = add2(and_xor_pair<0x00F0u>(cw, c1, k.cxor_x[1]), pack2(k.coff_x[1], k.coff_x[1]));
+    q[2] = add2(and_xor_pair<0x0F00u>(cw, c1, k.cxor_x[2]), pack2(k.coff_x[2], k.coff_x[2]));
+    q[3] = add2(and_xor_pair<0xF000u>(cw, c1, k.cxor_x[3]), pack2(k.coff_x[3], k.coff_x[3]));
+    const u64 kq = fma2(q[3], pack2(-5.877471754111438e-39f, -5.877471754111438e-39f),
+                        fma2(q[2], pack2(-2.938735877055719e-39f, -2.938735877055719e-39f),
+                             fma2(q[1], pack2(-1.4693679385278594e-39f, -1.4693679385278594e-39f),
+                                  mul2(q[0], pack2(-7.346839692639297e-40f, -7.346839692639297e-40f)))));
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        const u64 t = fma2(q[3], v[4 * c + 3], fma2(q[2], v[4 * c + 2], fma2(q[1], v[4 * c + 1], mul2(q[0], v[4 * c]))));
+        w2[c] = mul2(add2(t, kq), sc2);
+    }
+}
+// Two f32 -> one word of two bf16 (round to nearest even), low half = a.
+__device__ __forceinline__ uint32_t bf16x2_bits(float a, float b) {
+    uint32_t d;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(b), "f"(a));
+    return d;
+}
+
 }   // namespace nsl

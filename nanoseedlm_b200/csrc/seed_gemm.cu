@@ -95,30 +95,36 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* v) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-struct BlockIn { uint32_t seed, cw, code; };
+// A thread's share of one K step: 4 consecutive blocks of its row = two block pairs (seed / coefficient words packed
+// two per 32-bit word, even block low) and their 4 exponent codes (one nibble each, block j at bits 4j).
+struct QuadIn { uint32_t sw[2], cw[2], codes; bool live; };
 
-__device__ __forceinline__ BlockIn load_block(const WSlice& w, int row, int kb, int R, int NB) {
-    BlockIn b = {0u, 0u, 0u};
-    if (row < R && kb < NB) {
-        const size_t g = (size_t) row * NB + kb;
-        b.seed = __ldg((const uint16_t*) w.p[0] + g);
-        b.cw = __ldg((const uint16_t*) w.p[1] + g);
-        b.code = (__ldg((const uint8_t*) w.p[3] + (g >> 1)) >> ((g & 1) * 4)) & 15u;
+__device__ __forceinline__ QuadIn load_quad(const WSlice& w, int row, int kb, int R, int NB, bool vec) {
+    QuadIn q = {{0u, 0u}, {0u, 0u}, 0u, false};
+    if (row >= R || kb >= NB) return q;
+    q.live = true;
+    const size_t g = (size_t) row * NB + kb;
+    if (vec) {   // NB % 4 == 0: the four blocks are one aligned 8-byte load per stream and two code bytes
+        const uint2 s2 = __ldg((const uint2*) ((const uint16_t*) w.p[0] + g));
+        const uint2 c2 = __ldg((const uint2*) ((const uint16_t*) w.p[1] + g));
+        q.sw[0] = s2.x; q.sw[1] = s2.y; q.cw[0] = c2.x; q.cw[1] = c2.y;
+        q.codes = __ldg((const uint16_t*) ((const uint8_t*) w.p[3] + (g >> 1)));
+    } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (kb + j >= NB) break;   // (a missing block keeps seed 0: its weights are forced to zero below)
+            const uint32_t sd = __ldg((const uint16_t*) w.p[0] + g + j), cf = __ldg((const uint16_t*) w.p[1] + g + j);
+            const uint32_t cd = (__ldg((const uint8_t*) w.p[3] + ((g + j) >> 1)) >> (((g + j) & 1) * 4)) & 15u;
+            q.sw[j >> 1] |= sd << (16 * (j & 1));
+            q.cw[j >> 1] |= cf << (16 * (j & 1));
+            q.codes |= cd << (4 * j);
+        }
     }
-    return b;
-}
-
-__device__ __forceinline__ uint4 pack8_bf16(const float* w) {
-    uint4 o;
-    o.x = bf16_bits(w[0]) | ((uint32_t) bf16_bits(w[1]) << 16);
-    o.y = bf16_bits(w[2]) | ((uint32_t) bf16_bits(w[3]) << 16);
-    o.z = bf16_bits(w[4]) | ((uint32_t) bf16_bits(w[5]) << 16);
-    o.w = bf16_bits(w[6]) | ((uint32_t) bf16_bits(w[7]) << 16);
-    return o;
+    return q;
 }
 
 template <int NT>
-__global__ void __launch_bounds__(GM_THREADS, 1) seed_gemm_kernel(MmParams a, KConst kc) {
+__global__ void __launch_bounds__(GM_THREADS, 2) seed_gemm_kernel(MmParams a, KConst kc) {
     if (a.ntiles && (int) blockIdx.y >= *a.ntiles) return;
     extern __shared__ uint8_t smem_raw[];
     __shared__ StreamTab tab;
@@ -178,16 +184,12 @@ __global__ void __launch_bounds__(GM_THREADS, 1) seed_gemm_kernel(MmParams a, KC
         // ---- producers: weight tile (thread = row, half of the 8 blocks) and input tile (thread = token, half of 64 k) --
         const int prow = tid >> 1, half = tid & 1;
         const int grow = r0 + prow;
-        BlockIn cur[4], nxt[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) cur[j] = load_block(w, grow, half * 4 + j, a.R, NB);
+        const bool vec = (NB & 3) == 0;
+        QuadIn cur = load_quad(w, grow, half * 4, a.R, NB, vec), nxt = cur;
         bool live = true;
         for (int kt = 0; kt < KT && live; ++kt) {
             const int s = kt % GM_STAGES;
-            if (kt + 1 < KT) {
-#pragma unroll
-                for (int j = 0; j < 4; ++j) nxt[j] = load_block(w, grow, (kt + 1) * 8 + half * 4 + j, a.R, NB);
-            }
+            if (kt + 1 < KT) nxt = load_quad(w, grow, (kt + 1) * 8 + half * 4, a.R, NB, vec);
             if (kt >= GM_STAGES && !mbar_wait(bar_empty + 8 * s, ((kt / GM_STAGES) - 1) & 1, &abort_flag)) {
                 abort_flag = 1;
                 atomicCAS(&g_mm_status, 0, 1);
@@ -195,57 +197,69 @@ __global__ void __launch_bounds__(GM_THREADS, 1) seed_gemm_kernel(MmParams a, KC
                 break;
             }
             uint8_t* stage = smem + (size_t) s * STAGE_BYTES;
-            // weights
+            // weights: two block pairs, expanded side by side
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int chunk = half * 4 + j;
-                float wv[8];
-                if (cur[j].seed) {
-                    const uint32_t g = stream_bits(tab, cur[j].seed);
-                    block_weights(cur[j].seed | (g << 16), g, cur[j].cw, exact_scale45(w.eb + (int) cur[j].code), kc, wv);
+            for (int bp = 0; bp < 2; ++bp) {
+                float wa[8], wb[8];
+                if (cur.live) {
+                    const uint32_t cd = cur.codes >> (8 * bp);
+                    const u64 sc2 = pack2(exact_scale45(w.eb + (int) (cd & 15u)), exact_scale45(w.eb + (int) ((cd >> 4) & 15u)));
+                    u64 w2[8];
+                    pair_weights(tab, cur.sw[bp], cur.cw[bp], sc2, kc, w2);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) unpack2(w2[i], wa[i], wb[i]);
+                    if (!vec) {   // a row whose block count is not a multiple of 4 ends inside a quad: blocks past it are zero
+                        const bool has_a = (cur.sw[bp] & 0xFFFFu) != 0u, has_b = (cur.sw[bp] >> 16) != 0u;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            if (!has_a) wa[i] = 0.0f;
+                            if (!has_b) wb[i] = 0.0f;
+                        }
+                    }
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) wv[i] = 0.0f;
+                    for (int i = 0; i < 8; ++i) wa[i] = wb[i] = 0.0f;
                 }
-                const uint32_t off = (uint32_t) prow * 128u + (uint32_t) ((chunk ^ (prow & 7)) << 4);
 #pragma unroll
-                for (int q = 0; q < NT; ++q) {   // term q = the bf16 value of what remains (exact subtraction)
-                    const uint4 o = pack8_bf16(wv);
-                    *(uint4*) (stage + (size_t) q * GM_TILE_BYTES + off) = o;
-                    if (q + 1 < NT) {
-                        wv[0] -= __uint_as_float(o.x << 16); wv[1] -= __uint_as_float(o.x & 0xFFFF0000u);
-                        wv[2] -= __uint_as_float(o.y << 16); wv[3] -= __uint_as_float(o.y & 0xFFFF0000u);
-                        wv[4] -= __uint_as_float(o.z << 16); wv[5] -= __uint_as_float(o.z & 0xFFFF0000u);
-                        wv[6] -= __uint_as_float(o.w << 16); wv[7] -= __uint_as_float(o.w & 0xFFFF0000u);
+                for (int e = 0; e < 2; ++e) {
+                    float* wv = e ? wb : wa;
+                    const int chunk = half * 4 + 2 * bp + e;
+                    const uint32_t off = (uint32_t) prow * 128u + (uint32_t) ((chunk ^ (prow & 7)) << 4);
+#pragma unroll
+                    for (int q = 0; q < NT; ++q) {   // term q = the bf16 value of what remains (exact subtraction)
+                        const uint4 o = make_uint4(bf16x2_bits(wv[0], wv[1]), bf16x2_bits(wv[2], wv[3]),
+                                                   bf16x2_bits(wv[4], wv[5]), bf16x2_bits(wv[6], wv[7]));
+                        *(uint4*) (stage + (size_t) q * GM_TILE_BYTES + off) = o;
+                        if (q + 1 < NT) {
+                            wv[0] -= __uint_as_float(o.x << 16); wv[1] -= __uint_as_float(o.x & 0xFFFF0000u);
+                            wv[2] -= __uint_as_float(o.y << 16); wv[3] -= __uint_as_float(o.y & 0xFFFF0000u);
+                            wv[4] -= __uint_as_float(o.z << 16); wv[5] -= __uint_as_float(o.z & 0xFFFF0000u);
+                            wv[6] -= __uint_as_float(o.w << 16); wv[7] -= __uint_as_float(o.w & 0xFFFF0000u);
+                        }
                     }
                 }
             }
-            // inputs: token prow (if inside the tile's rounded pair count), k = kt*64 + half*32 .. +31
-            if (prow < n_eff) {
+            // inputs: the n_eff x 64 tile as 16-byte chunks (8 values) dealt round-robin to the producer threads
+            {
                 uint8_t* bt = stage + (size_t) NT * GM_TILE_BYTES;
-                const int src = srow[prow];
-                const int k0 = kt * GM_BK + half * 32;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
+                for (int ci = tid; ci < n_eff * 8; ci += GM_PRODUCERS) {
+                    const int n = ci >> 3, chunk = ci & 7, src = srow[n], k = kt * GM_BK + 8 * chunk;
                     uint4 o = make_uint4(0u, 0u, 0u, 0u);
-                    const int k = k0 + 8 * j;
                     if (src >= 0 && k < a.K) {
                         if (a.packed) o = __ldg((const uint4*) ((const uint16_t*) a.X + (size_t) src * a.xs + k));
                         else {
                             const float4* xp = (const float4*) ((const float*) a.X + (size_t) src * a.xs + k);
                             const float4 x0 = __ldg(xp), x1 = __ldg(xp + 1);
-                            const float t8[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-                            o = pack8_bf16(t8);
+                            o = make_uint4(bf16x2_bits(x0.x, x0.y), bf16x2_bits(x0.z, x0.w), bf16x2_bits(x1.x, x1.y),
+                                           bf16x2_bits(x1.z, x1.w));
                         }
                     }
-                    const int chunk = half * 4 + j;
-                    *(uint4*) (bt + (uint32_t) prow * 128u + (uint32_t) ((chunk ^ (prow & 7)) << 4)) = o;
+                    *(uint4*) (bt + (uint32_t) n * 128u + (uint32_t) ((chunk ^ (n & 7)) << 4)) = o;
                 }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the MMA's reads
             mbar_arrive(bar_full + 8 * s);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) cur[j] = nxt[j];
+            cur = nxt;
         }
         // ---- epilogue: TMEM lane = weight row, column = token ----------------------------------------------------------
         if (live && !mbar_wait(bar_done, 0, &abort_flag)) {
