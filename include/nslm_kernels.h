@@ -150,6 +150,10 @@ void nsl_decode_bf16(cudaStream_t s, WSlice w, int K, int R, uint16_t* out, cons
  * waiting for a free stage, 2 the epilogue waiting for the accumulator, 3 the MMA issuer waiting for a full stage); a
  * block that gives up frees its tensor memory and returns without storing.  Call after synchronising the stream. */
 int nsl_mm_status(void);
+/* Which single-token mat-vec kernel serves kc_mv (T = 1), kc_mv_sel and kc_mv_gu when K = 64 * 2^j <= 2048:
+ * 1 (default) inputs staged in shared memory, two blocks of 8 warps per SM; 0 inputs held in registers, one block per
+ * SM.  Same arithmetic and order: the results are bit-identical.  Process-wide, like kc_seed_gemm_f32. */
+void nsl_mv_set_variant(int v);
 /* Fills a 65536-entry host array with the stream table the G arguments expect (lfsr_stream32 of every seed,
  * nslm/lfsr.h:53-59). */
 void nsl_stream_table(uint32_t* host_table);

@@ -177,6 +177,128 @@ __global__ void __launch_bounds__(MV_THREADS, 1) mv_regx_kernel(MvParams a, KCon
     }
 }
 
+// ---- one token per pair, inputs in shared memory, two blocks of 8 warps per SM ------------------------------------------
+// The same arithmetic, lane mapping and order as mv_regx_kernel (so results are bit-identical), but the pair's inputs
+// sit in shared memory as the f32x2 operands of pair_dot, laid out [block pair][operand pair][lane] so that a warp's
+// 16-byte loads are conflict-free.  Without 96 registers of inputs a thread fits in 128 registers and 16 warps per SM
+// hide the logic pipe's latencies.  Blocks take contiguous shares of the pair-major row-step sequence; inside a pair
+// the block's warps take its steps round-robin.
+template <int MODE>
+__global__ void __launch_bounds__(MV_THREADS, 2) mv_shx_kernel(MvParams a, KConst kc, int lpr_log2) {
+    __shared__ StreamTab tab;
+    __shared__ __align__(16) ulonglong2 sx[4 * 4 * 32];   // [bp][c / 2][lane] = {x2[c], x2[c + 1]}
+    __shared__ __align__(16) ulonglong2 sm[4 * 2 * 32];   // [bp][p / 2][lane] = {xm2[p], xm2[p + 1]}
+    load_stream_tab(tab, a.G, threadIdx.x, MV_THREADS);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int lpr = 1 << lpr_log2, rpw = 32 >> lpr_log2;
+    const int jc = lane & (lpr - 1), ro = lane >> lpr_log2;
+    const int P = a.count ? min(*a.count, a.P) : a.P;
+    const int rs = (a.R + rpw - 1) / rpw;
+    const long long total = (long long) P * rs;
+    const long long begin = (long long) blockIdx.x * total / gridDim.x, end = (long long) (blockIdx.x + 1) * total / gridDim.x;
+    if (begin >= end) return;
+    const int p_first = (int) (begin / rs), p_last = (int) ((end - 1) / rs);
+    for (int pair = p_first; pair <= p_last; ++pair) {
+        const int s_lo = pair == p_first ? (int) (begin - (long long) pair * rs) : 0;
+        const int s_hi = pair == p_last ? (int) (end - (long long) pair * rs) : rs;
+        const int slice = a.sel ? a.sel[pair] : 0;
+        const WSlice wa = a.ws ? a.ws[slice] : a.w0;
+        WSlice wb = wa;
+        if (MODE == MODE_GU) wb = a.wu[slice];
+        __syncthreads();   // the previous pair's inputs are no longer read (and the table is loaded)
+        if (threadIdx.x < lpr * 4) {
+            const int j = threadIdx.x & (lpr - 1), bp = threadIdx.x >> lpr_log2;
+            const int xr = a.xrow ? a.xrow[pair] : pair / a.xdiv;
+            float x[16], xm[8];
+            if (a.xbf16) {
+                const uint4* xp = (const uint4*) ((const uint16_t*) a.x + (size_t) xr * a.xs + (size_t) j * 64 + bp * 16);
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const uint4 t = __ldg(xp + i);
+                    const uint32_t u[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        x[8 * i + 2 * q] = __uint_as_float(u[q] << 16) * NSL_XSCALE;
+                        x[8 * i + 2 * q + 1] = __uint_as_float(u[q] & 0xFFFF0000u) * NSL_XSCALE;
+                    }
+                }
+            } else {
+                const float4* xp = (const float4*) (a.x + (size_t) xr * a.xs + (size_t) j * 64 + bp * 16);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float4 t = __ldg(xp + i);
+                    x[4 * i] = t.x * NSL_XSCALE; x[4 * i + 1] = t.y * NSL_XSCALE; x[4 * i + 2] = t.z * NSL_XSCALE; x[4 * i + 3] = t.w * NSL_XSCALE;
+                }
+            }
+            block_offsets(x, xm);
+            block_offsets(x + 8, xm + 4);
+#pragma unroll
+            for (int cq = 0; cq < 4; ++cq) {
+                ulonglong2 t;
+                t.x = pack2(x[2 * cq], x[8 + 2 * cq]);
+                t.y = pack2(x[2 * cq + 1], x[8 + 2 * cq + 1]);
+                sx[(bp * 4 + cq) * 32 + j] = t;
+            }
+#pragma unroll
+            for (int pq = 0; pq < 2; ++pq) {
+                ulonglong2 t;
+                t.x = pack2(xm[2 * pq], xm[4 + 2 * pq]);
+                t.y = pack2(xm[2 * pq + 1], xm[4 + 2 * pq + 1]);
+                sm[(bp * 2 + pq) * 32 + j] = t;
+            }
+        }
+        __syncthreads();
+        const float sca = slice_scale(wa.eb), scb = slice_scale(wb.eb);
+        int st = s_lo + warp;
+        int r = st * rpw + ro;
+        Chunk ka, kb;
+        if (st < s_hi && r < a.R) {
+            ka = load_chunk(wa, (size_t) r * lpr + jc);
+            if (MODE == MODE_GU) kb = load_chunk(wb, (size_t) r * lpr + jc);
+        }
+        for (; st < s_hi; st += MV_WARPS, r += MV_WARPS * rpw) {
+            const bool ok = r < a.R;
+            const int rn = r + MV_WARPS * rpw;
+            Chunk na, nb;
+            if (st + MV_WARPS < s_hi && rn < a.R) {
+                na = load_chunk(wa, (size_t) rn * lpr + jc);
+                if (MODE == MODE_GU) nb = load_chunk(wb, (size_t) rn * lpr + jc);
+            }
+            u64 acc = 0ull, accu = 0ull;
+            if (ok) {
+                const uint32_t swa[4] = {ka.s.x, ka.s.y, ka.s.z, ka.s.w}, cwa[4] = {ka.c.x, ka.c.y, ka.c.z, ka.c.w};
+                const uint32_t swb[4] = {kb.s.x, kb.s.y, kb.s.z, kb.s.w}, cwb[4] = {kb.c.x, kb.c.y, kb.c.z, kb.c.w};
+#pragma unroll
+                for (int bp = 0; bp < 4; ++bp) {
+                    u64 x2[8], xm2[4];
+#pragma unroll
+                    for (int cq = 0; cq < 4; ++cq) { const ulonglong2 t = sx[(bp * 4 + cq) * 32 + jc]; x2[2 * cq] = t.x; x2[2 * cq + 1] = t.y; }
+#pragma unroll
+                    for (int pq = 0; pq < 2; ++pq) { const ulonglong2 t = sm[(bp * 2 + pq) * 32 + jc]; xm2[2 * pq] = t.x; xm2[2 * pq + 1] = t.y; }
+                    {
+                        u64 v[32], q[4];
+                        pair_states(tab, swa[bp], v);
+                        pair_coefs(cwa[bp], kc, q);
+                        acc = fma2(pair_dot(v, q, x2, xm2), code_scale_pair(ka.cd, bp, kc), acc);
+                    }
+                    if (MODE == MODE_GU) {
+                        u64 v[32], q[4];
+                        pair_states(tab, swb[bp], v);
+                        pair_coefs(cwb[bp], kc, q);
+                        accu = fma2(pair_dot(v, q, x2, xm2), code_scale_pair(kb.cd, bp, kc), accu);
+                    }
+                }
+            }
+            const float s = group_sum(pair_total(acc), lpr) * sca;
+            float su = 0.0f;
+            if (MODE == MODE_GU) su = group_sum(pair_total(accu), lpr) * scb;
+            if (ok && jc == 0) store_out<MODE>(a, pair, r, s, su);
+            ka = na;
+            if (MODE == MODE_GU) kb = nb;
+        }
+    }
+}
+
 // ---- inputs in shared memory: NT tokens share each expansion (dense verify rows), or rows longer than 32 chunks ------
 // Dense: the P = NT tokens are staged once per block and the rows are split over every warp of the grid.  Gather
 // (NT = 1): blocks are dealt to pairs and stage their pair's input row.
@@ -357,6 +479,8 @@ __global__ void __launch_bounds__(256) decode_kernel(WSlice w, KConst kc, int K,
     }
 }
 
+static int g_mv_variant = 1;   // 1 (default): inputs in shared memory, 16 warps / SM; 0: inputs in registers, 8 warps / SM
+
 // ---- launch selection ---------------------------------------------------------------------------------------------------
 static int log2_floor(int v) { int l = 0; while ((2 << l) <= v) ++l; return l; }
 
@@ -388,7 +512,8 @@ static void launch_mv(cudaStream_t s, const MvParams& a, int T, int p_hint = 0) 
         return;
     }
     if (chunked && T == 1 && pow2 && ch <= 32) {
-        mv_regx_kernel<MODE><<<sms, MV_THREADS, 0, s>>>(a, kconst(), log2_floor(ch));
+        if (g_mv_variant == 1) mv_shx_kernel<MODE><<<sms * 2, MV_THREADS, 0, s>>>(a, kconst(), log2_floor(ch));
+        else mv_regx_kernel<MODE><<<sms, MV_THREADS, 0, s>>>(a, kconst(), log2_floor(ch));
         count_launch();
         return;
     }
@@ -467,6 +592,8 @@ void nsl_mv_sel_rows(cudaStream_t s, const WSlice* ws, int K, int R, const float
     MvParams a = {ws, NULL, WSlice{}, sel, x, y, G, K, R, max_pairs, 1, xs, ys, 0, 0, NULL, count, 0};
     launch_mv<MODE_ROUND>(s, a, 1, expected_pairs);
 }
+
+void nsl_mv_set_variant(int v) { g_mv_variant = v; }
 
 void nsl_decode_f32(cudaStream_t s, WSlice w, int K, int R, float* out, const uint32_t* G) {
     if (K <= 0 || K % 8 || R <= 0) { if (K % 8) set_error("nsl_decode_f32: K = %d is not a multiple of 8", K); return; }

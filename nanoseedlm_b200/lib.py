@@ -61,6 +61,7 @@ PROTOTYPES = {
     "nsl_decode_f32": (None, [_vp, WSlice, _i, _i, _vp, _vp]),
     "nsl_decode_bf16": (None, [_vp, WSlice, _i, _i, _vp, _vp]),
     "nsl_mm_status": (_i, []),
+    "nsl_mv_set_variant": (None, [_i]),
     "nsl_stream_table": (None, [_vp]),
     "nsl_last_error": (C.c_char_p, []),
     "nsl_launch_count": (C.c_uint64, []),

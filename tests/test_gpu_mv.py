@@ -144,3 +144,17 @@ def test_other_formats_are_refused_loudly(oracle):
     lib.load().kc_mv(None, 3, w.slice(0), 64, 8, C.c_void_p(x.data_ptr()), 64, C.c_void_p(y.data_ptr()), 8, 1, 0,
                      C.c_void_p(kernels.stream_table().data_ptr()))
     assert "format 3" in lib.last_error()
+
+
+def test_register_and_shared_memory_variants_are_bit_identical(oracle):
+    from nanoseedlm_b200 import kernels, lib
+    mats, w = weights(oracle, 3, 96, 2048, 7)
+    sel = [2, 0, 1, 2, 1, 0, 0]
+    x = oracle.normal(5, 4 * 2048, bf16=True).reshape(4, 2048)
+    outs = []
+    for v in (0, 1):
+        lib.load().nsl_mv_set_variant(v)
+        outs.append((kernels.kt_mv_sel(w, sel, 2, x), kernels.kt_mv_gu(w, w, sel, 2, x), kernels.kt_mv(w, x[0], 1)))
+    lib.load().nsl_mv_set_variant(1)
+    for a, b in zip(*outs):
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
