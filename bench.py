@@ -306,7 +306,7 @@ def run_ep(args):
     gen = torch.Generator(device="cuda").manual_seed(4321 + rank)
     layers = [moe.DeviceLayer.random_on_device(D, FF, e_loc, gen) for _ in range(NL)]
     be = ep.CudaBackend(layers[0])
-    epl = ep.ExpertParallelMoe(be, D, EP_K, EP_E, t_loc)
+    epl = ep.ExpertParallelMoe(be, D, EP_K, EP_E, t_loc, collectives=args.ep_collectives)
     NB = 8
     rng = np.random.default_rng(7 + rank)
     hx = rng.standard_normal((NB, t_loc, D)).astype(np.float32)
@@ -327,25 +327,20 @@ def run_ep(args):
         for i in range(W):
             one(i)
         stream.synchronize()
-        chunk = min(K, 100)
+        # one step = 9 kernels of this library + 2 all-to-alls; with --no-graph every launch is issued directly, else the
+        # kernels replay as three CUDA graphs per step with the collectives between them (see ep.GraphedSteps)
         launches0 = lib.nsl_launch_count()
-        graph, captured = None, False
-        if world == 1 and not args.no_graph:   # with collectives in the step every launch is issued directly
-            try:
-                graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph, stream=stream):
-                    for i in range(chunk):
-                        one(W + i)
-                captured = True
-            except Exception as ex:   # capture of the collectives not available: launch every step directly
-                graph, captured = None, False
-                sys.stderr.write(f"graph capture failed ({type(ex).__name__}); timing direct launches\n")
-        if not captured:
-            for i in range(chunk):
-                one(W + i)
-        launches = (lib.nsl_launch_count() - launches0) // chunk * K
+        one(W)
+        stream.synchronize()
+        launches = (lib.nsl_launch_count() - launches0) * K
+        captured = not args.no_graph
         if captured:
-            graph.replay()
+            gs = ep.GraphedSteps(epl, layers, [(dx[b], dl[b]) for b in range(NB)])
+            run_step = lambda i: gs.step(i % NB, i % NL)
+        else:
+            run_step = one
+        for i in range(W):
+            run_step(i)
         stream.synchronize()
         if world > 1:
             dist.barrier()
@@ -353,14 +348,8 @@ def run_ep(args):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with ClockSampler(local) as clocks:
             e0.record(stream)
-            if captured:
-                for _ in range(K // chunk):
-                    graph.replay()
-                for i in range(K % chunk):
-                    one(W + i)
-            else:
-                for i in range(K):
-                    one(W + i)
+            for i in range(K):
+                run_step(W + i)
             e1.record(stream)
             e1.synchronize()
         if world > 1:
@@ -390,7 +379,7 @@ def run_ep(args):
         line = {"metric": "seed_decode_moe_gemv_tokens_per_s", "value": EP_B / (ms_per_step * 1e-3), "unit": "tok/s",
                 "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_per_step, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": ep_config(world, NL),
-                "gpu_launches": int(launches), "cuda_graph": captured, "clocks": clocks.summary(),
+                "gpu_launches": int(launches), "cuda_graph": captured, "collectives": args.ep_collectives, "clocks": clocks.summary(),
                 "e2e": {"value": EP_B / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": t_loc * D * 4 + t_loc * EP_E * 4,
                         "d2h_bytes_per_step": t_loc * D * 4, "ms_per_step": e2e_s * 1e3},
                 "roofline": {"bound": "hbm", "kernel": "mv_regx_kernel<gate+up> over this rank's pairs", "achieved": None,
@@ -411,6 +400,8 @@ def main():
     ap.add_argument("--layers", type=int, default=20)
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--ep-collectives", default="a2a", choices=["a2a", "gather"],
+                    help="config 3: two all-to-alls (default) or all-gather + reduce-scatter")
     ap.add_argument("--workload", default=None, choices=["cfg1", "cfg3"],
                     help="cfg1: one GPU's MoE decode layer (default at 1 GPU); cfg3: expert-parallel decode (default at >1)")
     args = ap.parse_args()

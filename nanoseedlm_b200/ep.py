@@ -33,8 +33,12 @@ def chunk_layout(t_loc, d, k):
 
 
 class ExpertParallelMoe:
-    def __init__(self, backend, d, k, n_exp_total, t_loc, group=None):
+    def __init__(self, backend, d, k, n_exp_total, t_loc, group=None, collectives="a2a"):
+        """collectives: "a2a" -- two all-to-alls and a rank-order sum on the owner (the default); "gather" -- the same
+        data movement as an all-gather of the chunks and a reduce-scatter of the partial rows (the sum is then formed by
+        the collective, in its own order)."""
         self.be, self.d, self.k, self.E, self.t_loc, self.group = backend, d, k, n_exp_total, t_loc, group
+        self.collectives = collectives
         self.N = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         assert n_exp_total % self.N == 0, "experts must divide evenly over the ranks"
@@ -59,13 +63,69 @@ class ExpertParallelMoe:
         """x [t_loc][d] f32 (bf16-valued), logits [t_loc][E] -> out [t_loc][d] (this rank's tokens)."""
         be = self.be
         be.route_and_pack(self, x, logits)                 # fills send[0]
-        if self.N > 1:
-            self.send[1:] = self.send[0]
-        self._all_to_all(self.recv, self.send)             # dispatch
+        self.dispatch()
         be.local_experts(self)                             # plan + mat-vecs + per-token pre-sum -> partial [N][t_loc][d]
-        self._all_to_all(self.parts, self.partial)         # combine
-        be.reduce(self)                                    # out = sum_r parts[r]
+        self.combine()
         return self.out
+
+    def dispatch(self, replicate=True):
+        if self.N > 1 and self.collectives == "gather":
+            dist.all_gather_into_tensor(self.recv.view(-1), self.send[0], group=self.group)
+            return
+        if self.N > 1 and replicate:
+            self.send[1:] = self.send[0]
+        self._all_to_all(self.recv, self.send)
+
+    def combine(self, reduce=True):
+        if self.N > 1 and self.collectives == "gather":
+            dist.reduce_scatter_tensor(self.out.view(-1), self.partial.view(-1), group=self.group)
+            return
+        self._all_to_all(self.parts, self.partial)
+        if reduce:
+            self.be.reduce(self)                           # out = sum_r parts[r], rank order
+
+
+class GraphedSteps:
+    """The device work of a step as three CUDA graphs -- (route + pack + replicate), (plan + mat-vecs + pre-sum) and
+    (reduce) -- with the two all-to-alls issued between them as ordinary NCCL calls.  One first graph per input batch
+    and one second graph per resident layer are captured up front; a step then costs three graph launches and two
+    collective calls on the host instead of a dozen kernel launches.  (Capturing the collectives themselves into a graph
+    did not complete on this system, so they stay outside.)"""
+
+    def __init__(self, ep, layers, inputs):
+        self.ep, be = ep, ep.be
+        stream = torch.cuda.current_stream()
+
+        def capture(fn):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream, capture_error_mode="thread_local"):
+                fn()
+            return g
+
+        gather = ep.N > 1 and ep.collectives == "gather"
+
+        def first(x, logits):
+            be.route_and_pack(ep, x, logits)
+            if ep.N > 1 and not gather:
+                ep.send[1:] = ep.send[0]
+
+        def second(layer):
+            be.set_layer(layer)
+            be.local_experts(ep)
+
+        self.first = [capture(lambda x=x, l=l: first(x, l)) for x, l in inputs]
+        self.second = [capture(lambda layer=layer: second(layer)) for layer in layers]
+        self.third = None if gather else capture(lambda: be.reduce(ep))
+
+    def step(self, i_input, i_layer):
+        ep = self.ep
+        self.first[i_input].replay()
+        ep.dispatch(replicate=False)
+        self.second[i_layer].replay()
+        ep.combine(reduce=False)
+        if self.third is not None:
+            self.third.replay()
+        return ep.out
 
 
 class CudaBackend:
