@@ -302,16 +302,15 @@ __global__ void __launch_bounds__(MV_THREADS, 2) mv_shx_kernel(MvParams a, KCons
 // ---- inputs in shared memory: NT tokens share each expansion (dense verify rows), or rows longer than 32 chunks ------
 // Dense: the P = NT tokens are staged once per block and the rows are split over every warp of the grid.  Gather
 // (NT = 1): blocks are dealt to pairs and stage their pair's input row.
-// Shared layout, per token: xin2 [K/16 block pairs][8] float2 {x[16 bp + c], x[16 bp + 8 + c]}, then
-// xoff2 [K/16][4] float2 of the centring constants: the operands of pair_dot, loaded 16 bytes at a time.
+// Shared layout, per token (K * 6 bytes): the f32x2 operands of pair_dot as 16-byte units, inputs
+// [block pair in chunk 0..3][operand pair 0..3][chunk], then centring constants [0..3][0..1][chunk]: the lanes of a warp
+// hold consecutive chunks, so their 16-byte loads are consecutive (no bank conflicts).
 template <int MODE, int NT>
 __global__ void __launch_bounds__(MV_THREADS, 1) mv_smemx_kernel(MvParams a, KConst kc, int lpr_log2, int dense) {
     extern __shared__ __align__(16) float smem_f[];
     __shared__ StreamTab tab;
     load_stream_tab(tab, a.G, threadIdx.x, MV_THREADS);
     const int K = a.K, nbp = K / 16, ch = K / 64;
-    float* xin = smem_f;                           // [NT][K]
-    float* xoff = smem_f + (size_t) NT * K;        // [NT][K/2]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int lpr = 1 << lpr_log2, rpw = 32 >> lpr_log2;
     const int jc = lane & (lpr - 1), ro = lane >> lpr_log2;
@@ -335,12 +334,22 @@ __global__ void __launch_bounds__(MV_THREADS, 1) mv_smemx_kernel(MvParams a, KCo
             }
             block_offsets(x, xm);
             block_offsets(x + 8, xm + 4);
-            float2* xo = (float2*) (xin + (size_t) t * K) + 8 * bp;
-            float2* mo = (float2*) (xoff + (size_t) t * (K / 2)) + 4 * bp;
+            ulonglong2* tok = (ulonglong2*) smem_f + (size_t) t * ch * 24;
+            const int jch = bp >> 2, b4 = bp & 3;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) xo[c] = make_float2(x[c], x[8 + c]);
+            for (int cq = 0; cq < 4; ++cq) {
+                ulonglong2 v2;
+                v2.x = pack2(x[2 * cq], x[8 + 2 * cq]);
+                v2.y = pack2(x[2 * cq + 1], x[8 + 2 * cq + 1]);
+                tok[(b4 * 4 + cq) * ch + jch] = v2;
+            }
 #pragma unroll
-            for (int p = 0; p < 4; ++p) mo[p] = make_float2(xm[p], xm[4 + p]);
+            for (int pq = 0; pq < 2; ++pq) {
+                ulonglong2 v2;
+                v2.x = pack2(xm[2 * pq], xm[4 + 2 * pq]);
+                v2.y = pack2(xm[2 * pq + 1], xm[4 + 2 * pq + 1]);
+                tok[16 * ch + (b4 * 2 + pq) * ch + jch] = v2;
+            }
         }
         __syncthreads();
         const float sca = slice_scale(wa.eb), scb = slice_scale(wb.eb);
@@ -366,16 +375,14 @@ __global__ void __launch_bounds__(MV_THREADS, 1) mv_smemx_kernel(MvParams a, KCo
                             pair_states(tab, sw[bp], v);
                             pair_coefs(cw[bp], kc, q);
                             const u64 e2 = code_scale_pair(k.cd, bp, kc);
-                            const int gbp = j * 4 + bp;
 #pragma unroll
                             for (int t = 0; t < NT; ++t) {
                                 u64 x2[8], xm2[4];
-                                const ulonglong2* xs2 = (const ulonglong2*) ((const float2*) (xin + (size_t) t * K) + 8 * gbp);
-                                const ulonglong2* ms2 = (const ulonglong2*) ((const float2*) (xoff + (size_t) t * (K / 2)) + 4 * gbp);
+                                const ulonglong2* tok = (const ulonglong2*) smem_f + (size_t) t * ch * 24;
 #pragma unroll
-                                for (int c = 0; c < 4; ++c) { const ulonglong2 u = xs2[c]; x2[2 * c] = u.x; x2[2 * c + 1] = u.y; }
+                                for (int c = 0; c < 4; ++c) { const ulonglong2 u = tok[(bp * 4 + c) * ch + j]; x2[2 * c] = u.x; x2[2 * c + 1] = u.y; }
 #pragma unroll
-                                for (int p = 0; p < 2; ++p) { const ulonglong2 u = ms2[p]; xm2[2 * p] = u.x; xm2[2 * p + 1] = u.y; }
+                                for (int p = 0; p < 2; ++p) { const ulonglong2 u = tok[16 * ch + (bp * 2 + p) * ch + j]; xm2[2 * p] = u.x; xm2[2 * p + 1] = u.y; }
                                 const u64 d = pair_dot(v, q, x2, xm2);
                                 if (half) su2[t] = fma2(d, e2, su2[t]);
                                 else s2[t] = fma2(d, e2, s2[t]);
