@@ -45,14 +45,19 @@ CLONES static void rows_vec(const uint16_t* seeds, const uint16_t* coefs, const 
     const float r32 = 1.0f / 32767.0f;
     vf acc = {0};
     for (int b = 0; b < kb; ++b) {
-        vu s, t, cw, code;
+        uint32_t sa[LANES], ta[LANES], ca[LANES], ea[LANES];   // gathered into arrays, then loaded as vectors
         for (int i = 0; i < LANES; ++i) {
             const size_t g = (size_t) (r + i) * kb + b;
-            s[i] = seeds[g];
-            t[i] = table[seeds[g]];
-            cw[i] = coefs[g];
-            code[i] = (codes[g >> 1] >> ((g & 1) * 4)) & 15u;
+            sa[i] = seeds[g];
+            ta[i] = table[seeds[g]];
+            ca[i] = coefs[g];
+            ea[i] = (codes[g >> 1] >> ((g & 1) * 4)) & 15u;
         }
+        vu s, t, cw, code;
+        memcpy(&s, sa, sizeof s);
+        memcpy(&t, ta, sizeof t);
+        memcpy(&cw, ca, sizeof cw);
+        memcpy(&code, ea, sizeof code);
         const vu lo = s | (t << 16);
         vf a0 = {0}, a1 = {0}, a2 = {0}, a3 = {0};
         for (int c = 0; c < 8; ++c) {
