@@ -116,6 +116,37 @@ void kq4_route_ld(cudaStream_t s, const void* cfg, const float* logits, int ld, 
 void kq4_moe_combine(cudaStream_t s, int d, int k, const float* D, const float* wt, const float* sh, const float* sg,
                      int sgld, float* out, int T);
 
+/* ---- router of the MoVA engine --------------------------------------------------------------------------------------- */
+/* engine/kernels_moe.metal:72-76: field order is the ABI. */
+typedef struct {
+    int32_t d, n, top_k;   /* input width, experts, selected */
+    int32_t hw;            /* width of the first partition of the input (d / 2) */
+    float scale;           /* the weights' final factor */
+} RouterArgs;
+/* engine/kernels_cuda.h:120  W [n][d] and bias [n] are BF16.  logit = bf16(dot over inputs < hw) + bf16(dot over the
+ * rest); score = sigmoid(logit); sel = score + bias; the top_k largest sel, ties to the lowest id, best first;
+ * wts = score / sum of the picked scores * scale.  score and sel [T][n] are outputs too.  n <= 1024, top_k <= 64,
+ * d a multiple of 8. */
+void kc_router(cudaStream_t s, RouterArgs a, const uint16_t* W, const uint16_t* bias, const float* x, float* score,
+               float* sel, int32_t* inds, float* wts, int T);
+/* engine/kernels_cuda.h:123  the top-k step alone, from scores and selection scores. */
+void kc_router_topk(cudaStream_t s, RouterArgs a, const float* score, const float* sel, int32_t* inds, float* wts, int T);
+
+/* ---- per-head maps (the SEED4P4 branch) ------------------------------------------------------------------------------- */
+/* engine/kernels_moe.metal:111-114: field order is the ABI. */
+typedef struct {
+    int32_t H, O, I, xs, hs, gate;
+    int32_t pad[2];
+} HmvArgs;
+/* engine/kernels_cuda.h:142  y[t][h][o] = bf16(W_h[o] . x[t*xs + h*hs ..]); with a.gate, bf16(that *
+ * bf16(softplus(g[t][h][o]; beta = ln 2))).  W is one stacked matrix [H*O][I]: p[0] seeds, p[1] coefficient words,
+ * p[2] the heads' exponent biases (int32 [H], device memory), p[3] exponent codes.  I a multiple of 8; any T. */
+void kc_heads_mv(cudaStream_t s, HmvArgs a, int fmt, WSlice W, const uint32_t* G, const float* x, const float* g, float* y,
+                 int T);
+/* engine/kernels_cuda.h:145  the stacked matrix decoded to BF16 [H][O][I], each weight the exact f32 weight rounded to
+ * nearest even (what the GEMM feeds the tensor cores). */
+void kc_heads_deq(cudaStream_t s, int fmt, WSlice W, const uint32_t* G, int H, int O, int I, uint16_t* out);
+
 /* ---- expert cache -------------------------------------------------------------------------------------------------- */
 /* engine/kernels_cuda.h:53  LRU admit of the units selected by inds[count] of sparse layer sl. */
 void kc_cache_admit(cudaStream_t s, const CachePool* p, int sl, const int32_t* inds, int count, int flags);

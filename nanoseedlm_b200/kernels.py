@@ -167,6 +167,58 @@ def kt_route_cfg(logits, k):
     return ind.cpu().numpy(), wt.cpu().numpy()
 
 
+def kt_router(a, W, bias, x, T):
+    """kc_router (tests/kernel_backend_cuda.c:176-184): W [n][d], bias [n] BF16 bits; returns inds, wts, score, sel."""
+    Wd, bd, xd = dev(np.asarray(W, np.uint16)), dev(np.asarray(bias, np.uint16)), dev(np.asarray(x, np.float32))
+    score, sel = torch.zeros(T, a.n, device="cuda"), torch.zeros(T, a.n, device="cuda")
+    ind = torch.zeros(T, a.top_k, dtype=torch.int32, device="cuda")
+    wt = torch.zeros(T, a.top_k, device="cuda")
+    L.load().kc_router(_stream(), a, _ptr(Wd), _ptr(bd), _ptr(xd), _ptr(score), _ptr(sel), _ptr(ind), _ptr(wt), T)
+    _done()
+    return ind.cpu().numpy(), wt.cpu().numpy(), score.cpu().numpy(), sel.cpu().numpy()
+
+
+def kt_router_topk(a, score, sel, T):
+    """kc_router_topk (tests/kernel_backend_cuda.c:185-192)."""
+    sd, ed = dev(np.asarray(score, np.float32)), dev(np.asarray(sel, np.float32))
+    ind = torch.zeros(T, a.top_k, dtype=torch.int32, device="cuda")
+    wt = torch.zeros(T, a.top_k, device="cuda")
+    L.load().kc_router_topk(_stream(), a, _ptr(sd), _ptr(ed), _ptr(ind), _ptr(wt), T)
+    _done()
+    return ind.cpu().numpy(), wt.cpu().numpy()
+
+
+def _heads_slice(seeds, coefs, ebias, ecodes):
+    keep = [dev(np.asarray(seeds, np.uint16)), dev(np.asarray(coefs, np.uint16)), dev(np.asarray(ebias, np.int32)),
+            dev(np.asarray(ecodes, np.uint8))]
+    w = L.WSlice()
+    for i in range(4):
+        w.p[i] = keep[i].data_ptr()
+    w.eb = int(np.asarray(ebias).ravel()[0])
+    return w, keep
+
+
+def kt_heads_seed(H, O, I, seeds, coefs, ebias, ecodes, x, xs, hs, g, T):
+    """kc_heads_mv on a stacked SEED4P4 map [H][O][I] (tests/kernel_backend_cuda.c:546-562): y [T][H][O]."""
+    w, keep = _heads_slice(seeds, coefs, ebias, ecodes)
+    a = L.HmvArgs(H, O, I, xs, hs, int(g is not None))
+    xd = dev(np.asarray(x, np.float32))
+    gd = dev(np.asarray(g, np.float32)) if g is not None else None
+    y = torch.zeros(T, H, O, device="cuda")
+    L.load().kc_heads_mv(_stream(), a, L.MF_SEED4P4, w, _ptr(stream_table()), _ptr(xd), _ptr(gd), _ptr(y), T)
+    _done()
+    return y.cpu().numpy()
+
+
+def kt_heads_deq(H, O, I, seeds, coefs, ebias, ecodes):
+    """kc_heads_deq (tests/kernel_backend_cuda.c:564-565): the map as BF16 bits [H][O][I]."""
+    w, keep = _heads_slice(seeds, coefs, ebias, ecodes)
+    out = torch.zeros(H * O * I, dtype=torch.int16, device="cuda")
+    L.load().kc_heads_deq(_stream(), L.MF_SEED4P4, w, _ptr(stream_table()), H, O, I, _ptr(out))
+    _done()
+    return out.cpu().numpy().view(np.uint16).reshape(H, O, I)
+
+
 def kt_swiglu(g, u):
     gd, ud = dev(np.asarray(g, np.float32)), dev(np.asarray(u, np.float32))
     ad = torch.empty_like(gd)

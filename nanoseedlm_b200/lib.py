@@ -30,7 +30,16 @@ class CachePool(C.Structure):
                 ("misses", C.c_uint64)]
 
 
-assert C.sizeof(WSlice) == 48 and C.sizeof(MmTile) == 16
+class RouterArgs(C.Structure):
+    _fields_ = [("d", C.c_int32), ("n", C.c_int32), ("top_k", C.c_int32), ("hw", C.c_int32), ("scale", C.c_float)]
+
+
+class HmvArgs(C.Structure):
+    _fields_ = [("H", C.c_int32), ("O", C.c_int32), ("I", C.c_int32), ("xs", C.c_int32), ("hs", C.c_int32),
+                ("gate", C.c_int32), ("pad", C.c_int32 * 2)]
+
+
+assert C.sizeof(WSlice) == 48 and C.sizeof(MmTile) == 16 and C.sizeof(RouterArgs) == 20 and C.sizeof(HmvArgs) == 32
 
 _vp, _i, _sz = C.c_void_p, C.c_int, C.c_size_t
 
@@ -52,6 +61,10 @@ PROTOTYPES = {
     "kq4_route": (None, [_vp, _vp, _vp, _vp, _vp, _i]),
     "kq4_route_ld": (None, [_vp, _vp, _vp, _i, _vp, _vp, _i]),
     "kq4_moe_combine": (None, [_vp, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _i]),
+    "kc_router": (None, [_vp, RouterArgs, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i]),
+    "kc_router_topk": (None, [_vp, RouterArgs, _vp, _vp, _vp, _vp, _i]),
+    "kc_heads_mv": (None, [_vp, HmvArgs, _i, WSlice, _vp, _vp, _vp, _vp, _i]),
+    "kc_heads_deq": (None, [_vp, _i, WSlice, _vp, _i, _i, _i, _vp]),
     "kc_cache_admit": (None, [_vp, C.POINTER(CachePool), _i, _vp, _i, _i]),
     "kc_cache_copy": (None, [_vp, C.POINTER(CachePool), _i]),
     "nsl_bucket_noalloc": (None, [_vp, _vp, _i, _i, _vp, _vp, _vp]),

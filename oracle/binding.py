@@ -56,6 +56,10 @@ def _declare(L):
     L.orc_silu_bf.restype = C.c_float
     L.orc_silu_bf.argtypes = [C.c_float]
     L.orc_cpu_seed4_time.restype = C.c_double
+    L.orc_softplus_gate.restype = C.c_float
+    L.orc_softplus_gate.argtypes = [C.c_float]
+    L.orc_mova_topk.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_float, C.c_void_p, C.c_void_p]
+    L.orc_mova_router.argtypes = [C.c_int] * 4 + [C.c_float] + [C.c_void_p] * 7
     L.orc_bucket.restype = C.c_int
 
 
@@ -156,6 +160,39 @@ def route(logits, k):
     for t in range(T):
         lib().orc_route(_p(logits[t], f32), E, k, _p(ind[t], i32), _p(wt[t], f32))
     return ind, wt
+
+
+def f2bf(a):
+    """f32 array -> BF16 bit patterns, round to nearest even."""
+    u = np.ascontiguousarray(a, np.float32).view(np.uint32).astype(np.uint64)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def mova_topk(score, sel, k, scale):
+    score, sel = np.ascontiguousarray(score, np.float32), np.ascontiguousarray(sel, np.float32)
+    T, n = score.shape
+    ind, wt = np.zeros((T, k), np.int32), np.zeros((T, k), np.float32)
+    for t in range(T):
+        lib().orc_mova_topk(score[t].ctypes.data, sel[t].ctypes.data, n, k, scale, ind[t].ctypes.data, wt[t].ctypes.data)
+    return ind, wt
+
+
+def mova_router(W, bias, x, k, hw, scale):
+    """W [n][d] and bias [n] as BF16 bit patterns, x [T][d] f32 -> score, sel, inds, wts."""
+    W, bias = np.ascontiguousarray(W, np.uint16), np.ascontiguousarray(bias, np.uint16)
+    x = np.ascontiguousarray(x, np.float32)
+    (n, d), T = W.shape, x.shape[0]
+    score, sel = np.zeros((T, n), np.float32), np.zeros((T, n), np.float32)
+    ind, wt = np.zeros((T, k), np.int32), np.zeros((T, k), np.float32)
+    for t in range(T):
+        lib().orc_mova_router(d, hw, n, k, scale, W.ctypes.data, bias.ctypes.data, x[t].ctypes.data, score[t].ctypes.data,
+                              sel[t].ctypes.data, ind[t].ctypes.data, wt[t].ctypes.data)
+    return score, sel, ind, wt
+
+
+def softplus_gate(g):
+    g = np.ascontiguousarray(g, np.float32)
+    return np.array([lib().orc_softplus_gate(float(v)) for v in g.ravel()], np.float32).reshape(g.shape)
 
 
 def q4_moe_combine(D, wt, sh, sg, T, d, k):

@@ -231,6 +231,45 @@ void orc_route(const float* logits, int E, int k, int32_t* ind, float* wt) {
 
 static float sigm_f(float x) { return 1.0f / (1.0f + expf(-x)); }
 
+/* MoVA router of one row (nslm/lib_mova_ref.c:171-201): logit = bf16(dot over the first hw inputs) + bf16(dot over the
+ * rest), both sums in double over BF16 weights; score = f32 sigmoid; selection score = score + bf16 bias; the k largest
+ * selection scores with equal ones to the LOWEST id, best first; weight = score / sum of the picked scores * scale. */
+void orc_mova_topk(const float* score, const float* sel, int n, int k, float scale, int32_t* inds, float* wts) {
+    float* se = (float*) malloc(sizeof(float) * (size_t) n);
+    memcpy(se, sel, sizeof(float) * (size_t) n);
+    float sum = 0;
+    for (int j = 0; j < k; ++j) {
+        int best = -1;
+        for (int e = 0; e < n; ++e)
+            if (se[e] != -INFINITY && (best < 0 || se[e] > se[best])) best = e;
+        inds[j] = best;
+        sum += score[best];
+        se[best] = -INFINITY;
+    }
+    for (int j = 0; j < k; ++j) wts[j] = score[inds[j]] / sum * scale;
+    free(se);
+}
+
+void orc_mova_router(int d, int hw, int n, int k, float scale, const uint16_t* W, const uint16_t* bias, const float* x,
+                     float* score, float* sel, int32_t* inds, float* wts) {
+    for (int e = 0; e < n; ++e) {
+        double s0 = 0, s1 = 0;
+        for (int c = 0; c < d; ++c) {
+            const double v = (double) orc_bf2f(W[(size_t) e * d + c]) * x[c];
+            if (c < hw) s0 += v; else s1 += v;
+        }
+        score[e] = 1.0f / (1.0f + expf(-(orc_bfr((float) s0) + orc_bfr((float) s1))));
+        sel[e] = score[e] + orc_bf2f(bias[e]);
+    }
+    orc_mova_topk(score, sel, n, k, scale, inds, wts);
+}
+
+/* The gate of the per-head maps: softplus with beta = ln 2 in f32, then BF16 (engine/kernels_moe.cu:215-218). */
+float orc_softplus_gate(float g) {
+    const float gx = g * 0.69314718055994531f;
+    return orc_bfr((fmaxf(gx, 0.0f) + logf(1.0f + expf(-fabsf(gx)))) / 0.69314718055994531f);
+}
+
 /* out[t] = sigmoid(sg[t*sgld]) sh[t] + sum_j wt[t][j] D[t*k+j], plain f32, j ascending
  * (engine/kernels_qwen4.cu:506-512). */
 void orc_q4_moe_combine(int d, int k, const float* D, const float* wt, const float* sh, const float* sg, int sgld,

@@ -57,6 +57,10 @@ void orc_route(const float* logits, int E, int k, int32_t* ind, float* wt);
 void orc_q4_moe_combine(int d, int k, const float* D, const float* wt, const float* sh, const float* sg, int sgld,
                         float* out, int T);
 void orc_moe_combine(const float* D, const float* w, const float* shared, float* x, int d, int k, int T);
+void orc_mova_topk(const float* score, const float* sel, int n, int k, float scale, int32_t* inds, float* wts);
+void orc_mova_router(int d, int hw, int n, int k, float scale, const uint16_t* W, const uint16_t* bias, const float* x,
+                     float* score, float* sel, int32_t* inds, float* wts);
+float orc_softplus_gate(float g);
 
 /* ---- grouping ---- */
 typedef struct { int32_t slice, start, count, pad; } OrcTile;

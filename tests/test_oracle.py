@@ -128,3 +128,44 @@ def test_rounding_points(oracle):
     y = oracle.mv(m, x)
     assert np.all(np.abs(y[0] - y64[0]) <= np.abs(y64[0]) / 128 + 1e-30)   # one bf16 ulp
     assert np.array_equal(y.view(np.uint32) & 0xFFFF, np.zeros_like(y.view(np.uint32)))
+
+
+def test_mova_router_against_the_double_form(oracle):
+    """The oracle's MoVA router against the double-precision form the reference's kernel test checks its backends with
+    (tests/test_mova_kernels.c:386-411): n 20, top 4, two partitions, BF16 weights and bias, scale 2.5."""
+    rng = np.random.default_rng(11)
+    d, n, k, T = 512, 20, 4, 6
+    W = oracle.f2bf((rng.random((n, d), np.float32) * 2 - 1) * 0.05)
+    bias = oracle.f2bf((rng.random(n, np.float32) * 2 - 1) * 0.01)
+    x = rng.standard_normal((T, d)).astype(np.float32)
+    score, sel, ind, wt = oracle.mova_router(W, bias, x, k, d // 2, 2.5)
+    Wf = (W.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+    bf = (bias.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+
+    def bfr(v):
+        return (oracle.f2bf(np.asarray(v, np.float32)).astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+
+    for t in range(T):
+        s0 = Wf[:, :d // 2] @ x[t, :d // 2].astype(np.float64)
+        s1 = Wf[:, d // 2:] @ x[t, d // 2:].astype(np.float64)
+        sc = 1 / (1 + np.exp(-(bfr(s0) + bfr(s1))))
+        se = sc + bf
+        chosen = []
+        for _ in range(k):
+            best = -1
+            for e in range(n):
+                if e not in chosen and (best < 0 or se[e] > se[best]):
+                    best = e
+            chosen.append(best)
+        assert list(ind[t]) == chosen
+        assert np.abs(wt[t] - sc[chosen] / sc[chosen].sum() * 2.5).max() < 1e-5
+
+
+def test_mova_topk_ties_go_to_the_lowest_id(oracle):
+    sc = np.full((1, 8), 0.5, np.float32)
+    se = np.array([[0.25, 0.5, 0.5, 0.125, 0.5, 0.25, 0.75, 0.75]], np.float32)
+    ind, wt = oracle.mova_topk(sc, se, 5, 2.0)
+    assert list(ind[0]) == [6, 7, 1, 2, 4]
+    assert np.allclose(wt[0], 0.4)
+    g = oracle.softplus_gate(np.array([0.0, 3.0, -3.0], np.float32))
+    assert g[0] == 1.0 and g[1] > 3.0 and 0 < g[2] < 0.2   # softplus with beta ln 2: 1 at 0, ~x for large x
