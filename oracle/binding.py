@@ -280,3 +280,56 @@ def cpu_seed4_time(m, x, threads, reps):
     y = np.zeros(m.rows, np.float32)
     return lib().orc_cpu_seed4_time(_p(m.seeds, u16), _p(m.coefs, u16), _p(m.codes, u8), m.eb, _p(x, f32), m.rows,
                                     m.K // 8, _p(y, f32), threads, reps), y
+
+
+class Tiled:
+    """A Matrix in the CPU-tiled layout (16-row tiles, vector loads): the fastest CPU form of the path."""
+
+    def __init__(self, m):
+        L = lib()
+        L.orc_cpu_seed4_tile.restype = C.c_void_p
+        self.h = L.orc_cpu_seed4_tile(_p(m.seeds, u16), _p(m.coefs, u16), _p(m.codes, u8), m.eb, m.rows, m.K // 8)
+        if not self.h:
+            raise ValueError("the tiled layout needs an even number of blocks per row")
+        self.rows, self.K = m.rows, m.K
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            lib().orc_cpu_seed4_tiled_free(C.c_void_p(self.h))
+            self.h = None
+
+    def matmul(self, x, threads=1):
+        """x [ntok][K] (ntok <= 8) -> y [ntok][rows], unrounded f32."""
+        x = np.ascontiguousarray(x, np.float32).reshape(-1, self.K)
+        y = np.zeros((x.shape[0], self.rows), np.float32)
+        rc = lib().orc_cpu_seed4_tiled_matmul_mt(C.c_void_p(self.h), _p(table32(), u32), _p(x, f32), x.shape[0],
+                                                 _p(y, f32), threads)
+        if rc:
+            raise ValueError("1..8 tokens")
+        return y
+
+    def time(self, x, threads, reps):
+        x = np.ascontiguousarray(x, np.float32).reshape(-1, self.K)
+        y = np.zeros((x.shape[0], self.rows), np.float32)
+        L = lib()
+        L.orc_cpu_seed4_tiled_time.restype = C.c_double
+        return L.orc_cpu_seed4_tiled_time(C.c_void_p(self.h), _p(x, f32), x.shape[0], _p(y, f32), threads, reps), y
+
+
+class _TiledJob(C.Structure):
+    _fields_ = [("m", C.c_void_p), ("x", C.c_void_p), ("ntok", C.c_int), ("y", C.c_void_p)]
+
+
+def tiled_jobs(jobs, threads):
+    """jobs: list of (Tiled, x [ntok][K]); all of them in one parallel region; returns the list of y [ntok][rows]."""
+    arr = (_TiledJob * len(jobs))()
+    keep, ys = [], []
+    for i, (t, x) in enumerate(jobs):
+        x = np.ascontiguousarray(x, np.float32).reshape(-1, t.K)
+        y = np.zeros((x.shape[0], t.rows), np.float32)
+        keep.append(x)
+        ys.append(y)
+        arr[i] = _TiledJob(t.h, x.ctypes.data, x.shape[0], y.ctypes.data)
+    if lib().orc_cpu_seed4_tiled_jobs(arr, len(jobs), _p(table32(), u32), threads):
+        raise ValueError("a job has no matrix or more than 8 tokens")
+    return ys

@@ -90,6 +90,14 @@ void orc_cpu_seed4_matvec_scalar(const uint16_t* seeds, const uint16_t* coefs, c
 /* best-of-reps wall seconds for one call; fills y */
 double orc_cpu_seed4_time(const uint16_t* seeds, const uint16_t* coefs, const uint8_t* codes, int bias,
                           const float* x, int rows, int kb, float* y, int threads, int reps);
+/* the CPU-tiled layout (cpu_seed4_tiled.c): x [ntok][kb*8] -> y [ntok][rows], ntok <= 8, kb even */
+typedef struct OrcTiled OrcTiled;
+OrcTiled* orc_cpu_seed4_tile(const uint16_t* seeds, const uint16_t* coefs, const uint8_t* codes, int bias, int rows, int kb);
+void orc_cpu_seed4_tiled_free(OrcTiled* t);
+int orc_cpu_seed4_tiled_matmul_mt(const OrcTiled* m, const uint32_t* table, const float* x, int ntok, float* y, int threads);
+typedef struct { const OrcTiled* m; const float* x; int ntok; float* y; } OrcTiledJob;
+int orc_cpu_seed4_tiled_jobs(const OrcTiledJob* jobs, int njobs, const uint32_t* table, int threads);
+double orc_cpu_seed4_tiled_time(const OrcTiled* m, const float* x, int ntok, float* y, int threads, int reps);
 
 /* ---- seeded generator shared by host tests and device uploads (splitmix64) ---- */
 uint64_t orc_splitmix64(uint64_t* state);
