@@ -39,6 +39,10 @@ float* nsl_moe_host_x(NslMoe* m);
 float* nsl_moe_host_logits(NslMoe* m);
 float* nsl_moe_host_out(NslMoe* m);
 int nsl_moe_forward_pinned(NslMoe* m, int T);
+/* The same in two halves: submit enqueues the copies and the layer on the handle's stream and returns; wait blocks until
+ * the result is in the pinned output buffer.  Two handles used alternately keep two steps in flight. */
+int nsl_moe_submit_pinned(NslMoe* m, int T);
+int nsl_moe_wait(NslMoe* m);
 /* Routing of the last forward (device memory) and the layer's stream. */
 const int32_t* nsl_moe_dev_ind(NslMoe* m);
 const float* nsl_moe_dev_wt(NslMoe* m);

@@ -136,14 +136,22 @@ const float* nsl_moe_dev_wt(NslMoe* m) { return m->wt; }
 cudaStream_t nsl_moe_stream(NslMoe* m) { return m->stream; }
 
 // The same with inputs already in the pinned buffers and the result left there: H2D, the layer, D2H, one sync.
-int nsl_moe_forward_pinned(NslMoe* m, int T) {
+// nsl_moe_submit_pinned enqueues without waiting and nsl_moe_wait waits, so that a caller with two handles keeps two
+// steps in flight (one's copies and launch latency under the other's kernels).
+int nsl_moe_submit_pinned(NslMoe* m, int T) {
     if (T < 1 || T > m->max_tokens) { nsl::set_error("nsl_moe_forward: %d rows, at most %d", T, m->max_tokens); return -1; }
     const size_t xb = (size_t) T * m->d * 4, lb = (size_t) T * m->n_exp * 4;
     cudaMemcpyAsync(m->x, m->hx, xb, cudaMemcpyHostToDevice, m->stream);
     cudaMemcpyAsync(m->logits, m->hlogits, lb, cudaMemcpyHostToDevice, m->stream);
     if (nsl_moe_forward_dev(m, m->stream, m->x, m->logits, T, m->out)) return -1;
-    cudaMemcpyAsync(m->hout, m->out, xb, cudaMemcpyDeviceToHost, m->stream);
-    return cudaStreamSynchronize(m->stream) == cudaSuccess ? 0 : -1;
+    return cudaMemcpyAsync(m->hout, m->out, xb, cudaMemcpyDeviceToHost, m->stream) == cudaSuccess ? 0 : -1;
+}
+
+int nsl_moe_wait(NslMoe* m) { return cudaStreamSynchronize(m->stream) == cudaSuccess ? 0 : -1; }
+
+int nsl_moe_forward_pinned(NslMoe* m, int T) {
+    if (nsl_moe_submit_pinned(m, T)) return -1;
+    return nsl_moe_wait(m);
 }
 
 }   // extern "C"

@@ -137,6 +137,15 @@ class Moe:
         if self.lib.nsl_moe_forward_pinned(self.h, T):
             raise RuntimeError(L.last_error() or "nsl_moe_forward_pinned failed")
 
+    def submit_pinned(self, T):
+        """forward_pinned without the wait: pair with wait(); two Moe objects used alternately overlap their steps."""
+        if self.lib.nsl_moe_submit_pinned(self.h, T):
+            raise RuntimeError(L.last_error() or "nsl_moe_submit_pinned failed")
+
+    def wait(self):
+        if self.lib.nsl_moe_wait(self.h):
+            raise RuntimeError("nsl_moe_wait: the stream reported an error")
+
     def forward_dev(self, x, logits, out, stream=None):
         """Device tensors; enqueues launches on the given (or the current torch) stream."""
         s = stream if stream is not None else torch.cuda.current_stream().cuda_stream

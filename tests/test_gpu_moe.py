@@ -84,3 +84,33 @@ def test_moe_full_size_config1_properties(oracle):
         acc = acc + rwt[t, j] * oracle.mv(mats[2], a)[0]
     assert np.max(np.abs(out[t] - acc)) <= 4e-3 * np.max(np.abs(acc))
     m.close()
+
+
+def test_pinned_forward_in_two_halves_with_two_handles(oracle):
+    """submit + wait on two handles used alternately (two steps in flight) give forward_host's results bit for bit."""
+    from nanoseedlm_b200 import moe
+    d, ff, E, k, T = 256, 64, 16, 4, 6
+    h = moe.HostLayer(oracle, d, ff, E, seed=91)
+    layer = moe.DeviceLayer.from_host(h)
+    ms = (moe.Moe(layer, k, 8), moe.Moe(layer, k, 8))
+    xs = [oracle.normal(40 + i, T * d, bf16=True).reshape(T, d) for i in range(5)]
+    ls = [oracle.normal(50 + i, T * E).reshape(T, E) for i in range(5)]
+    want = [ms[0].forward_host(x, l)[0].copy() for x, l in zip(xs, ls)]
+    got = []
+
+    def submit(i):
+        m = ms[i & 1]
+        m.hx[:T], m.hlogits[:T] = xs[i], ls[i]
+        m.submit_pinned(T)
+
+    submit(0)
+    for i in range(1, 5):
+        submit(i)
+        ms[(i - 1) & 1].wait()
+        got.append(ms[(i - 1) & 1].hout[:T].copy())
+    ms[0].wait()
+    got.append(ms[0].hout[:T].copy())
+    for g, w in zip(got, want):
+        assert np.array_equal(g, w)
+    for m in ms:
+        m.close()
