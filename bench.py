@@ -204,6 +204,7 @@ def run_ours(args):
     layers = [moe.DeviceLayer.random_on_device(D, FF, E, gen) for _ in range(NL)]
     torch.cuda.synchronize()
     m = moe.Moe(layers[0], TOPK, M)
+    m.set_dependent_launch(not args.no_dependent_launch)
 
     # inputs: a pool of distinct batches (bf16-valued activations, N(0,1) logits), on the host and on the device
     NB = 16
@@ -313,6 +314,7 @@ def run_ours(args):
     # the same with two handles used alternately: step i + 1 is submitted (its H2D copies and launches) before the host
     # waits for step i's output, so copies and launch latency hide under the other step's kernels
     m2 = moe.Moe(layers[0], TOPK, M)
+    m2.set_dependent_launch(not args.no_dependent_launch)
     ms, checksum = (m, m2), 0.0
 
     def submit(i):
@@ -499,6 +501,8 @@ def main():
     ap.add_argument("--layers", type=int, default=20)
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-dependent-launch", action="store_true",
+                    help="config 1: ordinary launches instead of programmatic dependent launches (for comparison)")
     ap.add_argument("--ep-collectives", default="a2a", choices=["a2a", "gather"],
                     help="config 3: two all-to-alls (default) or all-gather + reduce-scatter")
     ap.add_argument("--workload", default=None, choices=["cfg1", "cfg2", "cfg3"],

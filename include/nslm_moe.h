@@ -29,6 +29,9 @@ void nsl_moe_set_grouped_min_tokens(NslMoe* m, int t);
  * kc_mv_sel do).  0: f32 throughout on the mat-vec path (nsl_mv_gu_raw, nsl_mv_raw), for comparison with the CPU
  * reference forward, which keeps f32 (nslm/lib_qwen4_ref.c:177-207). */
 void nsl_moe_set_rounding(NslMoe* m, int bf16_points);
+/* Programmatic dependent launch of the decode path's kernels (default on): each kernel's blocks become resident while
+ * the previous kernel drains and wait for its completion before they touch its results.  0 = ordinary launches. */
+void nsl_moe_set_dependent_launch(NslMoe* m, int on);
 /* x [T][d], logits [T][n_exp] and out [T][d] in device memory; launches only. */
 int nsl_moe_forward_dev(NslMoe* m, cudaStream_t s, const float* x, const float* logits, int T, float* out);
 /* The same with host buffers: staged through pinned memory, copied both ways on the layer's stream, synchronised.

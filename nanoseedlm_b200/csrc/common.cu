@@ -12,6 +12,7 @@ namespace nsl {
 static char g_err[256];
 static std::mutex g_err_mu;
 static std::atomic<uint64_t> g_launches{0};
+thread_local bool tl_pdl = false;
 
 void set_error(const char* fmt, ...) {
     std::lock_guard<std::mutex> lk(g_err_mu);

@@ -23,6 +23,7 @@ struct NslMoe {
     cudaStream_t stream;
     int grouped_min_tokens;       // rows from which the grouped prompt path is taken (MV_MAXT + 1)
     int raw;                      // 1: no bf16 rounding points on the mat-vec path
+    int pdl;                      // 1 (default): the decode path's kernels are programmatic dependent launches
 };
 
 static void* dalloc(size_t n) {
@@ -41,6 +42,7 @@ NslMoe* nsl_moe_create(int d, int ff, int n_exp, int top_k, int max_tokens, cons
     m->d = d; m->ff = ff; m->n_exp = n_exp; m->top_k = top_k; m->max_tokens = max_tokens;
     m->wg = wg; m->wu = wu; m->wd = wd; m->G = G;
     m->grouped_min_tokens = MV_MAXT + 1;
+    m->pdl = 1;
     const size_t T = (size_t) max_tokens, P = T * top_k;
     m->x = (float*) dalloc(T * d * 4);
     m->logits = (float*) dalloc(T * n_exp * 4);
@@ -71,6 +73,7 @@ NslMoe* nsl_moe_create(int d, int ff, int n_exp, int top_k, int max_tokens, cons
 void nsl_moe_set_layer(NslMoe* m, const WSlice* wg, const WSlice* wu, const WSlice* wd) { m->wg = wg; m->wu = wu; m->wd = wd; }
 void nsl_moe_set_grouped_min_tokens(NslMoe* m, int t) { m->grouped_min_tokens = t; }
 void nsl_moe_set_rounding(NslMoe* m, int bf16_points) { m->raw = !bf16_points; }
+void nsl_moe_set_dependent_launch(NslMoe* m, int on) { m->pdl = on != 0; }
 
 void nsl_moe_destroy(NslMoe* m) {
     if (!m) return;
@@ -95,7 +98,13 @@ int nsl_moe_forward_dev(NslMoe* m, cudaStream_t s, const float* x, const float* 
         kc_mm_grouped_dev(s, MF_SEED4P4, m->wu, d, ff, x, d, m->Ub, ff, k, m->perm, m->tiles, m->ntiles, mt, m->G);
         kc_swiglu(s, m->Gb, m->Ub, m->A, P * ff);
         kc_mm_grouped_dev(s, MF_SEED4P4, m->wd, ff, d, m->A, ff, m->Dx, d, 1, m->perm, m->tiles, m->ntiles, mt, m->G);
-    } else if (m->raw) {
+        kq4_moe_combine(s, d, k, m->Dx, m->wt, NULL, NULL, 0, out, T);
+        return 0;
+    }
+    // decode rows: the three kernels after the router are dependent launches (their blocks come in while the previous
+    // kernel drains and wait for its completion before touching its results)
+    nsl::PdlScope pdl(m->pdl);
+    if (m->raw) {
         nsl_mv_gu_raw(s, m->wg, m->wu, d, ff, x, d, m->A, ff, m->ind, P, k, m->G);
         nsl_mv_raw(s, m->wd, ff, d, m->A, ff, m->Dx, d, m->ind, P, 1, m->G);
     } else {

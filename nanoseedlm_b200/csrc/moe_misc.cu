@@ -19,6 +19,7 @@ template <int PER>                   // experts per lane held in registers: E <=
 __global__ void __launch_bounds__(128) route_kernel(int E, int k, const float* __restrict__ logits, int ld,
                                                     int32_t* __restrict__ ind, float* __restrict__ wt, int T) {
     const int lane = threadIdx.x & 31, t = blockIdx.x * 4 + (threadIdx.x >> 5);
+    grid_dependents_go();   // a dependent launch of the next kernel may bring its blocks in as these retire
     if (t >= T) return;
     const float* l = logits + (size_t) t * ld;
     float v[PER];
@@ -70,6 +71,8 @@ __global__ void swiglu_kernel(const float* __restrict__ g, const float* __restri
 __global__ void q4_combine_kernel(int d, int k, const float* __restrict__ D, const float* __restrict__ wt,
                                   const float* __restrict__ sh, const float* __restrict__ sg, int sgld, float* __restrict__ out) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
+    grid_dependents_go();
+    grid_dependency_wait();
     if (i >= d) return;
     float a = 0.0f;
     if (sh) a = (1.0f / (1.0f + expf(-sg[(size_t) t * sgld]))) * sh[(size_t) t * d + i];
@@ -332,7 +335,7 @@ void kq4_route(cudaStream_t s, const void* cfg, const float* logits, int32_t* in
 void kq4_moe_combine(cudaStream_t s, int d, int k, const float* D, const float* wt, const float* sh, const float* sg,
                      int sgld, float* out, int T) {
     if (T <= 0 || d <= 0) return;
-    q4_combine_kernel<<<dim3((unsigned) (d + 255) / 256, (unsigned) T), 256, 0, s>>>(d, k, D, wt, sh, sg, sgld, out);
+    launch(q4_combine_kernel, dim3((unsigned) (d + 255) / 256, (unsigned) T), 256, 0, s, d, k, D, wt, sh, sg, sgld, out);
     count_launch();
 }
 

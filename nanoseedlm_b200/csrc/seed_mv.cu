@@ -96,6 +96,8 @@ template <int MODE>
 __global__ void __launch_bounds__(MV_THREADS, 1) mv_regx_kernel(MvParams a, KConst kc, int lpr_log2) {
     __shared__ StreamTab tab;
     load_stream_tab(tab, a.G, threadIdx.x, MV_THREADS);
+    grid_dependents_go();
+    grid_dependency_wait();   // everything below may read what the previous kernel in the stream wrote
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int lpr = 1 << lpr_log2, rpw = 32 >> lpr_log2;
@@ -189,6 +191,8 @@ __global__ void __launch_bounds__(MV_THREADS, 2) mv_shx_kernel(MvParams a, KCons
     __shared__ __align__(16) ulonglong2 sx[4 * 4 * 32];   // [bp][c / 2][lane] = {x2[c], x2[c + 1]}
     __shared__ __align__(16) ulonglong2 sm[4 * 2 * 32];   // [bp][p / 2][lane] = {xm2[p], xm2[p + 1]}
     load_stream_tab(tab, a.G, threadIdx.x, MV_THREADS);
+    grid_dependents_go();
+    grid_dependency_wait();   // everything below may read what the previous kernel in the stream wrote
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int lpr = 1 << lpr_log2, rpw = 32 >> lpr_log2;
     const int jc = lane & (lpr - 1), ro = lane >> lpr_log2;
@@ -205,7 +209,15 @@ __global__ void __launch_bounds__(MV_THREADS, 2) mv_shx_kernel(MvParams a, KCons
         const WSlice wa = a.ws ? a.ws[slice] : a.w0;
         WSlice wb = wa;
         if (MODE == MODE_GU) wb = a.wu[slice];
-        __syncthreads();   // the previous pair's inputs are no longer read (and the table is loaded)
+        // this warp's first streams are requested before the inputs are staged: their DRAM latency runs under it
+        int st = s_lo + warp;
+        int r = st * rpw + ro;
+        Chunk ka, kb;
+        if (st < s_hi && r < a.R) {
+            ka = load_chunk(wa, (size_t) r * lpr + jc);
+            if (MODE == MODE_GU) kb = load_chunk(wb, (size_t) r * lpr + jc);
+        }
+        if (pair != p_first) __syncthreads();   // the previous pair's inputs are no longer read
         if (threadIdx.x < lpr * 4) {
             const int j = threadIdx.x & (lpr - 1), bp = threadIdx.x >> lpr_log2;
             const int xr = a.xrow ? a.xrow[pair] : pair / a.xdiv;
@@ -247,15 +259,8 @@ __global__ void __launch_bounds__(MV_THREADS, 2) mv_shx_kernel(MvParams a, KCons
                 sm[(bp * 2 + pq) * 32 + j] = t;
             }
         }
-        __syncthreads();
+        __syncthreads();   // inputs staged (and, for the block's first pair, the stream table loaded)
         const float sca = slice_scale(wa.eb), scb = slice_scale(wb.eb);
-        int st = s_lo + warp;
-        int r = st * rpw + ro;
-        Chunk ka, kb;
-        if (st < s_hi && r < a.R) {
-            ka = load_chunk(wa, (size_t) r * lpr + jc);
-            if (MODE == MODE_GU) kb = load_chunk(wb, (size_t) r * lpr + jc);
-        }
         for (; st < s_hi; st += MV_WARPS, r += MV_WARPS * rpw) {
             const bool ok = r < a.R;
             const int rn = r + MV_WARPS * rpw;
@@ -310,6 +315,8 @@ __global__ void __launch_bounds__(MV_THREADS, 1) mv_smemx_kernel(MvParams a, KCo
     extern __shared__ __align__(16) float smem_f[];
     __shared__ StreamTab tab;
     load_stream_tab(tab, a.G, threadIdx.x, MV_THREADS);
+    grid_dependents_go();
+    grid_dependency_wait();   // everything below may read what the previous kernel in the stream wrote
     const int K = a.K, nbp = K / 16, ch = K / 64;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int lpr = 1 << lpr_log2, rpw = 32 >> lpr_log2;
@@ -407,6 +414,8 @@ template <int MODE>
 __global__ void __launch_bounds__(MV_THREADS) mv_generic_kernel(MvParams a, KConst kc, int T) {
     __shared__ StreamTab tab;
     load_stream_tab(tab, a.G, threadIdx.x, MV_THREADS);
+    grid_dependents_go();
+    grid_dependency_wait();   // everything below may read what the previous kernel in the stream wrote
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int nb = a.K / 8, dense = a.sel == NULL;
@@ -500,7 +509,7 @@ static void launch_smemx(cudaStream_t s, const MvParams& a, int lpr_log2, int de
         cudaFuncSetAttribute(mv_smemx_kernel<MODE, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin() - 4096);
         attr_set[dev & 15] = true;
     }
-    mv_smemx_kernel<MODE, NT><<<grid, MV_THREADS, smem, s>>>(a, kconst(), lpr_log2, dense);
+    launch(mv_smemx_kernel<MODE, NT>, grid, MV_THREADS, smem, s, a, kconst(), lpr_log2, dense);
 }
 
 template <int MODE>
@@ -519,8 +528,8 @@ static void launch_mv(cudaStream_t s, const MvParams& a, int T, int p_hint = 0) 
         return;
     }
     if (chunked && T == 1 && pow2 && ch <= 32) {
-        if (g_mv_variant == 1) mv_shx_kernel<MODE><<<sms * 2, MV_THREADS, 0, s>>>(a, kconst(), log2_floor(ch));
-        else mv_regx_kernel<MODE><<<sms, MV_THREADS, 0, s>>>(a, kconst(), log2_floor(ch));
+        if (g_mv_variant == 1) launch(mv_shx_kernel<MODE>, sms * 2, MV_THREADS, 0, s, a, kconst(), log2_floor(ch));
+        else launch(mv_regx_kernel<MODE>, sms, MV_THREADS, 0, s, a, kconst(), log2_floor(ch));
         count_launch();
         return;
     }
@@ -536,7 +545,7 @@ static void launch_mv(cudaStream_t s, const MvParams& a, int T, int p_hint = 0) 
         count_launch();
         return;
     }
-    mv_generic_kernel<MODE><<<sms * 2, MV_THREADS, 0, s>>>(a, kconst(), dense ? T : 1);
+    launch(mv_generic_kernel<MODE>, sms * 2, MV_THREADS, 0, s, a, kconst(), dense ? T : 1);
     count_launch();
 }
 

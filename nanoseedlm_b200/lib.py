@@ -96,6 +96,7 @@ PROTOTYPES = {
     "nsl_moe_dev_wt": (_vp, [_vp]),
     "nsl_moe_stream": (_vp, [_vp]),
     "nsl_moe_set_rounding": (None, [_vp, _i]),
+    "nsl_moe_set_dependent_launch": (None, [_vp, _i]),
     # include/nslm_ep.h
     "nsl_ep_plan": (None, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "nsl_mv_gu_rows": (None, [_vp, _vp, _vp, _i, _i, _vp, _i, _i, _vp, _i, _vp, _vp, _i, _vp, _i, _vp]),

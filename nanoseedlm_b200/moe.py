@@ -119,6 +119,9 @@ class Moe:
     def set_rounding(self, bf16_points):
         self.lib.nsl_moe_set_rounding(self.h, int(bf16_points))
 
+    def set_dependent_launch(self, on):
+        self.lib.nsl_moe_set_dependent_launch(self.h, int(on))
+
     def forward_host(self, x, logits):
         """numpy x [T][d], logits [T][E] -> (out [T][d], ind [T][k]) through nsl_moe_forward_host."""
         x = np.ascontiguousarray(x, np.float32)

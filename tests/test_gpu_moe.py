@@ -114,3 +114,42 @@ def test_pinned_forward_in_two_halves_with_two_handles(oracle):
         assert np.array_equal(g, w)
     for m in ms:
         m.close()
+
+
+def test_dependent_launches_change_nothing(oracle):
+    """The decode path with programmatic dependent launches (the default) and with ordinary launches: the same bits,
+    directly and replayed from a CUDA graph of several steps."""
+    import torch
+    from nanoseedlm_b200 import moe
+    d, ff, E, k, T = 512, 128, 24, 8, 8
+    h = moe.HostLayer(oracle, d, ff, E, seed=17)
+    layer = moe.DeviceLayer.from_host(h)
+    m = moe.Moe(layer, k, 8)
+    xs = [oracle.normal(60 + i, T * d, bf16=True).reshape(T, d) for i in range(3)]
+    ls = [oracle.normal(70 + i, T * E).reshape(T, E) for i in range(3)]
+    m.set_dependent_launch(False)
+    plain = [m.forward_host(x, l)[0].copy() for x, l in zip(xs, ls)]
+    m.set_dependent_launch(True)
+    for x, l, w in zip(xs, ls, plain):
+        for _ in range(3):
+            assert np.array_equal(m.forward_host(x, l)[0], w)
+    dx = [torch.from_numpy(x).cuda() for x in xs]
+    dl = [torch.from_numpy(l).cuda() for l in ls]
+    outs = [torch.zeros(T, d, device="cuda") for _ in xs]
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for i in range(3):
+            m.forward_dev(dx[i], dl[i], outs[i], stream=stream.cuda_stream)
+        stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            for rep in range(2):
+                for i in range(3):
+                    m.forward_dev(dx[i], dl[i], outs[i], stream=stream.cuda_stream)
+        for o in outs:
+            o.zero_()
+        g.replay()
+        stream.synchronize()
+    for o, w in zip(outs, plain):
+        assert np.array_equal(o.cpu().numpy(), w)
+    m.close()
