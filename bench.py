@@ -474,6 +474,17 @@ def run_ep(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, e2e_s = float(t[0].item()), float(t[1].item())
     L.check()
+    p2p_status = None
+    if epl.window is not None:
+        p2p_status = epl.window.status()          # non-zero: a bounded wait on another rank ran out
+        if world > 1:
+            t = torch.tensor([p2p_status], device="cuda", dtype=torch.int64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            p2p_status = int(t.item())
+            dist.barrier()
+        epl.window.close()
+        if p2p_status:
+            raise SystemExit(f"expert-parallel p2p exchange: a wait ran out (status {p2p_status}); the timing is void")
     ms_per_step = ms / K
     if rank == 0:
         peaks, peak_kind = measured_peaks()
@@ -483,7 +494,7 @@ def run_ep(args):
                 "gpu_launches": int(launches), "cuda_graph": captured, "collectives": args.ep_collectives, "clocks": clocks.summary(),
                 "e2e": {"value": EP_B / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": t_loc * D * 4 + t_loc * EP_E * 4,
                         "d2h_bytes_per_step": t_loc * D * 4, "ms_per_step": e2e_s * 1e3},
-                "roofline": {"bound": "hbm", "kernel": "mv_regx_kernel<gate+up> over this rank's pairs", "achieved": None,
+                "roofline": {"bound": "hbm", "kernel": "mv_shx_kernel<gate+up> over this rank's pairs", "achieved": None,
                              "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": None, "peak_kind": peak_kind, "traffic": None,
                              "note": "per-kernel roofline is reported by the 1-GPU config-1 line; this line is the end-to-end step"}}
         print(json.dumps(line))
@@ -503,8 +514,9 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-dependent-launch", action="store_true",
                     help="config 1: ordinary launches instead of programmatic dependent launches (for comparison)")
-    ap.add_argument("--ep-collectives", default="a2a", choices=["a2a", "gather"],
-                    help="config 3: two all-to-alls (default) or all-gather + reduce-scatter")
+    ap.add_argument("--ep-collectives", default="a2a", choices=["a2a", "gather", "p2p"],
+                    help="config 3: two NCCL all-to-alls (default), all-gather + reduce-scatter, or p2p: no collective call, "
+                         "the kernels store into the other ranks' memory over NVLink and wait on flags")
     ap.add_argument("--workload", default=None, choices=["cfg1", "cfg2", "cfg3"],
                     help="cfg1: one GPU's MoE decode layer (default at 1 GPU); cfg2: the same layer on 512 prompt rows (grouped "
                          "tcgen05 GEMM); cfg3: expert-parallel decode (default at >1 GPU)")

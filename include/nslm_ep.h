@@ -9,8 +9,9 @@
  * rows (packed bf16) and their routing travel to every rank in one all-to-all; each rank keeps the (token, expert)
  * pairs it owns (nsl_ep_plan), runs them through the seed mat-vec kernels on the received rows (nsl_mv_gu_rows,
  * nsl_mv_sel_rows), pre-sums each token's local experts (nsl_ep_combine); the partial rows go back in a second
- * all-to-all and the source rank adds them in rank order (nsl_ep_reduce).  The collectives themselves are NCCL calls
- * issued by the host layer; the kernels here read only local memory. */
+ * all-to-all and the source rank adds them in rank order (nsl_ep_reduce).  The two exchanges are either collective calls
+ * issued by the host layer (the kernels of the first part read only local memory) or stores into peer memory by the
+ * kernels of the second part below. */
 #pragma once
 #include "nslm_kernels.h"
 
@@ -39,6 +40,44 @@ void nsl_mv_sel_rows(cudaStream_t s, const WSlice* ws, int K, int R, const float
 void nsl_ep_combine(cudaStream_t s, const float* D, const float* wsel, const int32_t* tok_off, int T, int d, float* partial);
 /* out[t][:] = parts[0][t][:] + parts[1][t][:] + ... in rank order; parts is [n_ranks][t_loc][d]. */
 void nsl_ep_reduce(cudaStream_t s, const float* parts, int n_ranks, int t_loc, int d, float* out);
+
+/* ---- dispatch and combine over peer memory ----------------------------------------------------------------------------
+ * Instead of two collective calls, the producer kernels store into the consumers' memory over NVLink and raise flags
+ * there; the consumer kernels wait (bounded, about two seconds) on flags in their own memory.  Every rank owns one
+ * WINDOW of device memory that all ranks of the node map (nsl_ep_window_alloc on the owner, the 64-byte handle carried
+ * to the others by any host transport, nsl_ep_window_open there).  All windows share one layout:
+ *   recv_off   n chunks of chunk_bytes: chunk r = rank r's token rows (bf16), expert ids and weights of this step
+ *   parts_off  n x t_loc x d floats: slot r = rank r's pre-summed rows for this rank's tokens
+ *   dflag_off, cflag_off   n flag words each, 128 bytes apart: the epoch of rank r's last dispatch / combine
+ *   local_off  64 bytes touched only by the owner: epoch, grid tickets, status
+ * A step on every rank, on one stream: nsl_route + kc_pack_input_bf16 into a local chunk; nsl_ep_p2p_dispatch;
+ * nsl_ep_p2p_wait_dispatch; nsl_ep_plan, nsl_mv_gu_rows, nsl_mv_sel_rows on the window's receive area;
+ * nsl_ep_p2p_combine; nsl_ep_p2p_reduce.  All ranks must run the same number of steps.  The kernels of different
+ * ranks wait on one another, so every rank needs its own GPU. */
+#define NSL_EP_MAX_RANKS 16
+typedef struct {
+    void* win[NSL_EP_MAX_RANKS];   /* every rank's window as mapped in this process; win[me] is the local one */
+    int32_t n, me;
+    uint64_t bytes;                /* size of a window */
+    uint64_t chunk_bytes, recv_off, parts_off, dflag_off, cflag_off, local_off;
+} NslEpWindow;
+/* Window memory: alloc (zeroed) + handle on the owner, open / close on the peers, free on the owner.  0 on success. */
+int nsl_ep_window_alloc(size_t bytes, void** ptr, void* handle64);
+int nsl_ep_window_open(const void* handle64, void** ptr);
+int nsl_ep_window_close(void* ptr);
+int nsl_ep_window_free(void* ptr);
+/* chunk (chunk_bytes, 16-byte aligned, local) -> slot `me` of every window's receive area, then dispatch flag `me`. */
+void nsl_ep_p2p_dispatch(cudaStream_t s, NslEpWindow w, const void* chunk);
+/* Returns (on the stream) when every rank's chunk of this step has landed in the local window. */
+void nsl_ep_p2p_wait_dispatch(cudaStream_t s, NslEpWindow w);
+/* nsl_ep_combine whose rows go to slot `me` of the owning rank's partial-row area, then combine flag `me`. */
+void nsl_ep_p2p_combine(cudaStream_t s, NslEpWindow w, const float* D, const float* wsel, const int32_t* tok_off, int t_loc,
+                        int d);
+/* Waits for every rank's partial rows, out[t][:] = their sum in rank order, and closes the step (epoch + 1). */
+void nsl_ep_p2p_reduce(cudaStream_t s, NslEpWindow w, int t_loc, int d, float* out);
+/* 0 when no wait has run out since the last call; else code * 256 + (rank waited for + 1), code 1 = dispatch,
+ * 2 = combine.  Synchronous (reads the window's status word); call it after the stream has drained. */
+int nsl_ep_p2p_status(NslEpWindow w);
 
 #ifdef __cplusplus
 }

@@ -194,6 +194,11 @@ const char* nsl_last_error(void);
 uint64_t nsl_launch_count(void);
 /* Multiprocessor count the persistent grids are sized for (queried once per device). */
 int nsl_sm_count(void);
+/* Programmatic dependent launch for the calling thread's next launches of the mat-vec kernels (kc_mv*, nsl_mv*),
+ * kq4_moe_combine and nsl_ep_combine: while on, such a kernel may become resident before the previous kernel in its
+ * stream has finished and waits on the device for its completion before it touches memory a neighbour writes.  Turn it
+ * on only between kernels of this library (the previous kernel in the stream must be one of them), and off again. */
+void nsl_dependent_launch(int on);
 
 #ifdef __cplusplus
 }

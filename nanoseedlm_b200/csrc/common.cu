@@ -58,6 +58,7 @@ const char* nsl_last_error(void) {
 
 uint64_t nsl_launch_count(void) { return nsl::g_launches.load(std::memory_order_relaxed); }
 int nsl_sm_count(void) { return nsl::sm_count(); }
+void nsl_dependent_launch(int on) { nsl::tl_pdl = on != 0; }
 
 // The 32 stream bits that follow each seed: bit k is the top bit of the (k+1)-th state of the 16-bit LFSR with taps
 // 0, 1, 3, 12 (reference: nslm/lfsr.h:20-23, 53-59).

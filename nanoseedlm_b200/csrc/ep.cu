@@ -17,6 +17,7 @@ __global__ void __launch_bounds__(1024) ep_plan_kernel(const int32_t* __restrict
     __shared__ int base;
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     const int T = n_ranks * t_loc, n = T * k;
+    grid_dependents_go();   // a dependent launch of the next kernel may bring its blocks in already
     if (tid == 0) base = 0;
     __syncthreads();
     for (int c0 = 0; c0 < n; c0 += 1024) {
@@ -48,6 +49,8 @@ __global__ void __launch_bounds__(1024) ep_plan_kernel(const int32_t* __restrict
 __global__ void ep_combine_kernel(const float* __restrict__ D, const float* __restrict__ wsel, const int32_t* __restrict__ tok_off,
                                   int d, float* __restrict__ partial) {
     const int g = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+    grid_dependents_go();
+    grid_dependency_wait();
     if (c >= d) return;
     const int p0 = tok_off[g], p1 = tok_off[g + 1];
     float acc = 0.0f;
@@ -83,7 +86,7 @@ void nsl_ep_plan(cudaStream_t s, const int32_t* ind, const float* wt, int n_rank
 
 void nsl_ep_combine(cudaStream_t s, const float* D, const float* wsel, const int32_t* tok_off, int T, int d, float* partial) {
     if (T < 1 || d < 1) return;
-    ep_combine_kernel<<<dim3((unsigned) (d + 255) / 256, (unsigned) T), 256, 0, s>>>(D, wsel, tok_off, d, partial);
+    launch(ep_combine_kernel, dim3((unsigned) (d + 255) / 256, (unsigned) T), 256, 0, s, D, wsel, tok_off, d, partial);
     count_launch();
 }
 

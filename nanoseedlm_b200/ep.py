@@ -32,15 +32,102 @@ def chunk_layout(t_loc, d, k):
     return {"row": row, "ind_off": ind_off, "wt_off": wt_off, "bytes": total, "rows": total // row}
 
 
+def window_layout(N, t_loc, d, k):
+    """Byte layout of a rank's peer-memory window (include/nslm_ep.h, NslEpWindow): receive chunks, partial rows, the two
+    flag arrays (one 128-byte line per rank) and the owner's private words."""
+    lay = chunk_layout(t_loc, d, k)
+    up = lambda v, a=256: (v + a - 1) // a * a
+    parts_off = up(N * lay["bytes"])
+    dflag_off = up(parts_off + N * t_loc * d * 4)
+    cflag_off = dflag_off + N * 128
+    local_off = cflag_off + N * 128
+    return {"chunk_bytes": lay["bytes"], "recv_off": 0, "parts_off": parts_off, "dflag_off": dflag_off,
+            "cflag_off": cflag_off, "local_off": local_off, "bytes": up(local_off + 128)}
+
+
+class P2PWindow:
+    """This rank's view of all ranks' windows: ptrs[r] = rank r's window as mapped in this process."""
+
+    def __init__(self, lib, ptrs, me, wl, owned, opened):
+        self.lib, self.ptrs, self.me, self.wl, self.owned, self.opened = lib, ptrs, me, wl, owned, opened
+
+    @classmethod
+    def create(cls, N, me, t_loc, d, k, group=None):
+        """One window per rank, allocated by its owner and opened by the others through CUDA inter-process handles that
+        travel over the process group."""
+        from . import lib as L
+        lib = L.load()
+        wl = window_layout(N, t_loc, d, k)
+        ptr, handle = C.c_void_p(), (C.c_ubyte * 64)()
+        if lib.nsl_ep_window_alloc(wl["bytes"], C.byref(ptr), handle):
+            raise RuntimeError(L.last_error() or "nsl_ep_window_alloc failed")
+        ptrs, opened = [0] * N, []
+        if N > 1:
+            handles = [None] * N
+            dist.all_gather_object(handles, bytes(handle), group=group)
+            for r in range(N):
+                if r == me:
+                    continue
+                q = C.c_void_p()
+                if lib.nsl_ep_window_open((C.c_ubyte * 64).from_buffer_copy(handles[r]), C.byref(q)):
+                    raise RuntimeError(L.last_error() or "nsl_ep_window_open failed")
+                ptrs[r] = q.value
+                opened.append(q.value)
+        ptrs[me] = ptr.value
+        return cls(lib, ptrs, me, wl, [ptr.value], opened)
+
+    @classmethod
+    def local_group(cls, N, t_loc, d, k):
+        """N windows inside this process (no handles): for driving N ranks' kernels from one stream on one GPU, every
+        rank's producers before any rank's consumers, so that no kernel waits for a later one."""
+        from . import lib as L
+        lib = L.load()
+        wl = window_layout(N, t_loc, d, k)
+        ptrs = []
+        for _ in range(N):
+            ptr = C.c_void_p()
+            if lib.nsl_ep_window_alloc(wl["bytes"], C.byref(ptr), None):
+                raise RuntimeError(L.last_error() or "nsl_ep_window_alloc failed")
+            ptrs.append(ptr.value)
+        return [cls(lib, ptrs, me, wl, ptrs if me == 0 else [], []) for me in range(N)]
+
+    def struct(self):
+        from . import lib as L
+        w, wl = L.NslEpWindow(), self.wl
+        for r, q in enumerate(self.ptrs):
+            w.win[r] = q
+        w.n, w.me, w.bytes = len(self.ptrs), self.me, wl["bytes"]
+        for f in ("chunk_bytes", "recv_off", "parts_off", "dflag_off", "cflag_off", "local_off"):
+            setattr(w, f, wl[f])
+        return w
+
+    def status(self):
+        """0, or the code of a wait that ran out (see nsl_ep_p2p_status).  Synchronises the device."""
+        torch.cuda.synchronize()
+        return self.lib.nsl_ep_p2p_status(self.struct())
+
+    def close(self):
+        for q in self.opened:
+            self.lib.nsl_ep_window_close(C.c_void_p(q))
+        for q in self.owned:
+            self.lib.nsl_ep_window_free(C.c_void_p(q))
+        self.opened, self.owned = [], []
+
+
 class ExpertParallelMoe:
-    def __init__(self, backend, d, k, n_exp_total, t_loc, group=None, collectives="a2a"):
-        """collectives: "a2a" -- two all-to-alls and a rank-order sum on the owner (the default); "gather" -- the same
-        data movement as an all-gather of the chunks and a reduce-scatter of the partial rows (the sum is then formed by
-        the collective, in its own order)."""
+    def __init__(self, backend, d, k, n_exp_total, t_loc, group=None, collectives="a2a", window=None):
+        """collectives: "a2a" -- two all-to-alls and a rank-order sum on the owner; "gather" -- the same data movement as
+        an all-gather of the chunks and a reduce-scatter of the partial rows (the sum is then formed by the collective,
+        in its own order); "p2p" -- no collective call: the kernels store into the other ranks' windows over NVLink and
+        wait on flags (window: a P2PWindow, made here when omitted; passing one of P2PWindow.local_group's lets one
+        process drive several ranks)."""
         self.be, self.d, self.k, self.E, self.t_loc, self.group = backend, d, k, n_exp_total, t_loc, group
         self.collectives = collectives
-        self.N = dist.get_world_size(group) if dist.is_initialized() else 1
-        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if window is not None:
+            self.N, self.rank = len(window.ptrs), window.me
+        else:
+            self.N = dist.get_world_size(group) if dist.is_initialized() else 1
+            self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         assert n_exp_total % self.N == 0, "experts must divide evenly over the ranks"
         self.e_loc = n_exp_total // self.N
         self.lo, self.hi = self.rank * self.e_loc, (self.rank + 1) * self.e_loc
@@ -51,6 +138,13 @@ class ExpertParallelMoe:
         self.partial = torch.zeros(self.N, t_loc, d, dtype=torch.float32, device=dev)
         self.parts = torch.zeros(self.N, t_loc, d, dtype=torch.float32, device=dev)
         self.out = torch.zeros(t_loc, d, dtype=torch.float32, device=dev)
+        self.window = None
+        if collectives == "p2p":
+            self.window = window or P2PWindow.create(self.N, self.rank, t_loc, d, k, group)
+            self.win = self.window.struct()
+            self.recv_ptr = self.window.ptrs[self.rank] + self.window.wl["recv_off"]
+        else:
+            self.recv_ptr = self.recv.data_ptr()
         backend.setup(self)
 
     def _all_to_all(self, out, inp):
@@ -63,6 +157,11 @@ class ExpertParallelMoe:
         """x [t_loc][d] f32 (bf16-valued), logits [t_loc][E] -> out [t_loc][d] (this rank's tokens)."""
         be = self.be
         be.route_and_pack(self, x, logits)                 # fills send[0]
+        if self.collectives == "p2p":
+            be.p2p_dispatch(self)
+            be.local_experts(self)
+            be.reduce(self)
+            return self.out
         self.dispatch()
         be.local_experts(self)                             # plan + mat-vecs + per-token pre-sum -> partial [N][t_loc][d]
         self.combine()
@@ -86,8 +185,10 @@ class ExpertParallelMoe:
 
 
 class GraphedSteps:
-    """The device work of a step as three CUDA graphs -- (route + pack + replicate), (plan + mat-vecs + pre-sum) and
-    (reduce) -- with the two all-to-alls issued between them as ordinary NCCL calls.  One first graph per input batch
+    """The device work of a step as CUDA graphs.  With the peer-memory exchange ("p2p") two graphs hold the whole step:
+    (route + pack + dispatch) per input batch and (wait + plan + mat-vecs + combine + reduce) per resident layer.  With
+    collective calls it is three graphs -- (route + pack + replicate), (plan + mat-vecs + pre-sum) and (reduce) -- with
+    the two all-to-alls issued between them as ordinary NCCL calls.  One first graph per input batch
     and one second graph per resident layer are captured up front; a step then costs three graph launches and two
     collective calls on the host instead of a dozen kernel launches.  (Capturing the collectives themselves into a graph
     did not complete on this system, so they stay outside.)"""
@@ -103,23 +204,31 @@ class GraphedSteps:
             return g
 
         gather = ep.N > 1 and ep.collectives == "gather"
+        self.p2p = ep.collectives == "p2p"
 
         def first(x, logits):
             be.route_and_pack(ep, x, logits)
-            if ep.N > 1 and not gather:
+            if self.p2p:
+                be.p2p_dispatch(ep)
+            elif ep.N > 1 and not gather:
                 ep.send[1:] = ep.send[0]
 
         def second(layer):
             be.set_layer(layer)
             be.local_experts(ep)
+            if self.p2p:
+                be.reduce(ep)
 
         self.first = [capture(lambda x=x, l=l: first(x, l)) for x, l in inputs]
         self.second = [capture(lambda layer=layer: second(layer)) for layer in layers]
-        self.third = None if gather else capture(lambda: be.reduce(ep))
+        self.third = None if gather or self.p2p else capture(lambda: be.reduce(ep))
 
     def step(self, i_input, i_layer):
         ep = self.ep
         self.first[i_input].replay()
+        if self.p2p:      # the exchanges are inside the graphs: two launches make a step
+            self.second[i_layer].replay()
+            return ep.out
         ep.dispatch(replicate=False)
         self.second[i_layer].replay()
         ep.combine(reduce=False)
@@ -166,18 +275,32 @@ class CudaBackend:
 
     def local_experts(self, ep):
         lib, s, lay, lyr = self.lib, self._s(), ep.lay, self.layer
-        base = ep.recv.data_ptr()
+        base = ep.recv_ptr
         T = ep.N * ep.t_loc
+        p2p = ep.collectives == "p2p"
+        if p2p:
+            lib.nsl_ep_p2p_wait_dispatch(s, ep.win)
         lib.nsl_ep_plan(s, base + lay["ind_off"], base + lay["wt_off"], ep.N, ep.t_loc, ep.k, lay["bytes"] // 4, lay["rows"],
                         ep.lo, ep.hi, self.sel.data_ptr(), self.xrow.data_ptr(), self.wsel.data_ptr(),
                         self.tok_off.data_ptr(), self.count.data_ptr())
         P = T * ep.k
+        lib.nsl_dependent_launch(1)   # the three kernels after the plan come in while their predecessor drains
         lib.nsl_mv_gu_rows(s, lyr.gate.table.data_ptr(), lyr.up.table.data_ptr(), lyr.d, lyr.ff, base, ep.d, 1,
                            self.A.data_ptr(), lyr.ff, self.sel.data_ptr(), self.xrow.data_ptr(), P, self.count.data_ptr(),
                            self.expected_pairs, self.G.data_ptr())
         lib.nsl_mv_sel_rows(s, lyr.down.table.data_ptr(), lyr.ff, lyr.d, self.A.data_ptr(), lyr.ff, self.D.data_ptr(), lyr.d,
                             self.sel.data_ptr(), P, self.count.data_ptr(), self.expected_pairs, self.G.data_ptr())
-        lib.nsl_ep_combine(s, self.D.data_ptr(), self.wsel.data_ptr(), self.tok_off.data_ptr(), T, ep.d, ep.partial.data_ptr())
+        if p2p:
+            lib.nsl_ep_p2p_combine(s, ep.win, self.D.data_ptr(), self.wsel.data_ptr(), self.tok_off.data_ptr(), ep.t_loc, ep.d)
+        else:
+            lib.nsl_ep_combine(s, self.D.data_ptr(), self.wsel.data_ptr(), self.tok_off.data_ptr(), T, ep.d, ep.partial.data_ptr())
+        lib.nsl_dependent_launch(0)
+
+    def p2p_dispatch(self, ep):
+        self.lib.nsl_ep_p2p_dispatch(self._s(), ep.win, ep.send.data_ptr())
 
     def reduce(self, ep):
-        self.lib.nsl_ep_reduce(self._s(), ep.parts.data_ptr(), ep.N, ep.t_loc, ep.d, ep.out.data_ptr())
+        if ep.collectives == "p2p":
+            self.lib.nsl_ep_p2p_reduce(self._s(), ep.win, ep.t_loc, ep.d, ep.out.data_ptr())
+        else:
+            self.lib.nsl_ep_reduce(self._s(), ep.parts.data_ptr(), ep.N, ep.t_loc, ep.d, ep.out.data_ptr())

@@ -39,6 +39,13 @@ class HmvArgs(C.Structure):
                 ("gate", C.c_int32), ("pad", C.c_int32 * 2)]
 
 
+class NslEpWindow(C.Structure):
+    _fields_ = [("win", C.c_void_p * 16), ("n", C.c_int32), ("me", C.c_int32), ("bytes", C.c_uint64),
+                ("chunk_bytes", C.c_uint64), ("recv_off", C.c_uint64), ("parts_off", C.c_uint64), ("dflag_off", C.c_uint64),
+                ("cflag_off", C.c_uint64), ("local_off", C.c_uint64)]
+
+
+assert C.sizeof(NslEpWindow) == 192
 assert C.sizeof(WSlice) == 48 and C.sizeof(MmTile) == 16 and C.sizeof(RouterArgs) == 20 and C.sizeof(HmvArgs) == 32
 
 _vp, _i, _sz = C.c_void_p, C.c_int, C.c_size_t
@@ -79,6 +86,7 @@ PROTOTYPES = {
     "nsl_last_error": (C.c_char_p, []),
     "nsl_launch_count": (C.c_uint64, []),
     "nsl_sm_count": (_i, []),
+    "nsl_dependent_launch": (None, [_i]),
     # include/nslm_moe.h
     "nsl_moe_create": (_vp, [_i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "nsl_moe_destroy": (None, [_vp]),
@@ -103,6 +111,15 @@ PROTOTYPES = {
     "nsl_mv_sel_rows": (None, [_vp, _vp, _i, _i, _vp, _i, _vp, _i, _vp, _i, _vp, _i, _vp]),
     "nsl_ep_combine": (None, [_vp, _vp, _vp, _vp, _i, _i, _vp]),
     "nsl_ep_reduce": (None, [_vp, _vp, _i, _i, _i, _vp]),
+    "nsl_ep_window_alloc": (_i, [_sz, C.POINTER(C.c_void_p), _vp]),
+    "nsl_ep_window_open": (_i, [_vp, C.POINTER(C.c_void_p)]),
+    "nsl_ep_window_close": (_i, [_vp]),
+    "nsl_ep_window_free": (_i, [_vp]),
+    "nsl_ep_p2p_dispatch": (None, [_vp, NslEpWindow, _vp]),
+    "nsl_ep_p2p_wait_dispatch": (None, [_vp, NslEpWindow]),
+    "nsl_ep_p2p_combine": (None, [_vp, NslEpWindow, _vp, _vp, _vp, _i, _i]),
+    "nsl_ep_p2p_reduce": (None, [_vp, NslEpWindow, _i, _i, _vp]),
+    "nsl_ep_p2p_status": (_i, [NslEpWindow]),
 }
 
 _lib = None

@@ -77,8 +77,9 @@ class DeviceLayer:
         self.d, self.ff, self.E = gate.K, gate.R, gate.E
 
     @classmethod
-    def from_host(cls, h):
-        mk = lambda s, R, K: ExpertStack.from_host(s["seeds"], s["coefs"], s["codes"], s["eb"], R, K)
+    def from_host(cls, h, lo=0, hi=None):
+        """The host layer's experts [lo, hi) (all of them by default) on the device."""
+        mk = lambda s, R, K: ExpertStack.from_host(s["seeds"][lo:hi], s["coefs"][lo:hi], s["codes"][lo:hi], s["eb"][lo:hi], R, K)
         return cls(mk(h.gate, h.ff, h.d), mk(h.up, h.ff, h.d), mk(h.down, h.d, h.ff))
 
     @classmethod

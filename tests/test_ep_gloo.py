@@ -61,3 +61,18 @@ def test_chunk_layout_is_whole_rows():
         lay = ep.chunk_layout(t_loc, d, k)
         assert lay["bytes"] % lay["row"] == 0 and lay["ind_off"] % 4 == 0 and lay["wt_off"] % 4 == 0
         assert lay["wt_off"] + 4 * t_loc * k <= lay["bytes"] and lay["rows"] * lay["row"] == lay["bytes"]
+
+
+def test_window_layout_is_aligned_and_disjoint():
+    """The peer-memory window: every area starts on its alignment, areas do not overlap, flags sit 128 bytes apart."""
+    from nanoseedlm_b200 import ep
+    for N, t_loc, d, k in [(1, 64, 2048, 10), (2, 32, 2048, 10), (8, 8, 2048, 10), (4, 6, 512, 10), (16, 4, 256, 3)]:
+        wl, lay = ep.window_layout(N, t_loc, d, k), ep.chunk_layout(t_loc, d, k)
+        assert wl["chunk_bytes"] == lay["bytes"] and wl["chunk_bytes"] % 16 == 0
+        areas = [(wl["recv_off"], N * wl["chunk_bytes"], 256), (wl["parts_off"], N * t_loc * d * 4, 256),
+                 (wl["dflag_off"], N * 128, 128), (wl["cflag_off"], N * 128, 128), (wl["local_off"], 64, 128)]
+        end = 0
+        for off, size, align in areas:
+            assert off % align == 0 and off >= end
+            end = off + size
+        assert end <= wl["bytes"]

@@ -57,3 +57,80 @@ def test_plan_keeps_local_pairs_in_token_order(oracle):
     assert int(cnt.item()) == n and off.cpu().tolist() == want_off + [n]
     assert sel.cpu().tolist()[:n] == want_sel and xrow.cpu().tolist()[:n] == want_row
     assert np.array_equal(wsel.cpu().numpy()[:n], np.array(want_w, np.float32))
+
+
+def test_p2p_exchange_single_rank_and_graphs(oracle):
+    """The peer-memory exchange with one rank (its own window): several steps, directly and as two CUDA graphs per
+    step, equal the plain MoE layer; no wait runs out."""
+    import torch
+    from nanoseedlm_b200 import ep, lib, moe
+    d, ff, E, k, T = 512, 128, 32, 10, 16
+    h = moe.HostLayer(oracle, d, ff, E, seed=29)
+    layer = moe.DeviceLayer.from_host(h)
+    m = moe.Moe(layer, k, T)
+    m.set_grouped_min_tokens(10 ** 6)
+    xs = [oracle.normal(30 + i, T * d, bf16=True).reshape(T, d) for i in range(3)]
+    ls = [oracle.normal(40 + i, T * E).reshape(T, E) for i in range(3)]
+    refs = [m.forward_host(x, l)[0].copy() for x, l in zip(xs, ls)]
+    epl = ep.ExpertParallelMoe(ep.CudaBackend(layer), d, k, E, T, collectives="p2p")
+    dx = [torch.from_numpy(x).cuda() for x in xs]
+    dl = [torch.from_numpy(l).cuda() for l in ls]
+    for i in (0, 1, 2, 0):
+        out = epl.step(dx[i], dl[i]).cpu().numpy()
+        assert np.max(np.abs(out - refs[i])) <= 1e-6 * np.max(np.abs(refs[i]))
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        g = ep.GraphedSteps(epl, [layer], list(zip(dx, dl)))
+        for i in (2, 1, 0, 1):
+            out = g.step(i, 0)
+            stream.synchronize()
+            assert np.max(np.abs(out.cpu().numpy() - refs[i])) <= 1e-6 * np.max(np.abs(refs[i]))
+    assert epl.window.status() == 0
+    lib.check()
+    epl.window.close()
+    m.close()
+
+
+def test_p2p_exchange_four_ranks_driven_from_one_stream(oracle):
+    """Four ranks' windows in one process, their kernels issued on one stream with every rank's producers before any
+    rank's consumers (so no kernel ever waits for a later one): dispatch slots, flags, epochs and the owner-indexed
+    partial rows all line up with the plain MoE layer over the whole batch, for several steps."""
+    import torch
+    from nanoseedlm_b200 import ep, lib, moe
+    N, d, ff, E, k, t_loc = 4, 512, 128, 32, 10, 6
+    T = N * t_loc
+    h = moe.HostLayer(oracle, d, ff, E, seed=31)
+    m = moe.Moe(moe.DeviceLayer.from_host(h), k, T)
+    m.set_grouped_min_tokens(10 ** 6)
+    wins = ep.P2PWindow.local_group(N, t_loc, d, k)
+    eps = [ep.ExpertParallelMoe(ep.CudaBackend(moe.DeviceLayer.from_host(h, r * E // N, (r + 1) * E // N)), d, k, E, t_loc,
+                                collectives="p2p", window=wins[r]) for r in range(N)]
+    for step in range(3):
+        x = oracle.normal(50 + step, T * d, bf16=True).reshape(T, d)
+        logits = oracle.normal(60 + step, T * E).reshape(T, E)
+        ref = m.forward_host(x, logits)[0]
+        dx, dl = torch.from_numpy(x).cuda(), torch.from_numpy(logits).cuda()
+        for r, e in enumerate(eps):
+            e.be.route_and_pack(e, dx[r * t_loc:(r + 1) * t_loc], dl[r * t_loc:(r + 1) * t_loc])
+            e.be.p2p_dispatch(e)
+        for e in eps:
+            e.be.local_experts(e)
+        for e in eps:
+            e.be.reduce(e)
+        torch.cuda.synchronize()
+        out = np.concatenate([e.out.cpu().numpy() for e in eps])
+        assert np.max(np.abs(out - ref)) <= 1e-5 * np.max(np.abs(ref))
+    assert all(w.status() == 0 for w in wins)
+    lib.check()
+    for w in wins:
+        w.close()
+    m.close()
+
+
+def test_p2p_refuses_an_inconsistent_window():
+    from nanoseedlm_b200 import ep, lib as L
+    w = L.NslEpWindow()
+    w.n, w.me, w.bytes, w.chunk_bytes = 2, 0, 1024, 64
+    L.load().nsl_ep_p2p_wait_dispatch(None, w)      # null windows: nothing is launched
+    with pytest.raises(RuntimeError, match="inconsistent"):
+        L.check()
