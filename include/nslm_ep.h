@@ -42,22 +42,23 @@ void nsl_ep_combine(cudaStream_t s, const float* D, const float* wsel, const int
 void nsl_ep_reduce(cudaStream_t s, const float* parts, int n_ranks, int t_loc, int d, float* out);
 
 /* ---- dispatch and combine over peer memory ----------------------------------------------------------------------------
- * Instead of two collective calls, the producer kernels store into the consumers' memory over NVLink and raise flags
- * there; the consumer kernels wait (bounded, about two seconds) on flags in their own memory.  Every rank owns one
+ * Instead of two collective calls, the producer kernels store into the consumers' memory over NVLink and bump counters
+ * there; the consumer kernels wait (bounded, about two seconds) on counters in their own memory.  Every rank owns one
  * WINDOW of device memory that all ranks of the node map (nsl_ep_window_alloc on the owner, the 64-byte handle carried
  * to the others by any host transport, nsl_ep_window_open there).  All windows share one layout:
- *   recv_off   n chunks of chunk_bytes: chunk r = rank r's token rows (bf16), expert ids and weights of this step
+ *   recv_off   n chunks of chunk_bytes: chunk r = rank r's t_loc token rows (bf16), expert ids and weights of this step
  *   parts_off  n x t_loc x d floats: slot r = rank r's pre-summed rows for this rank's tokens
- *   dflag_off, cflag_off   n flag words each, 128 bytes apart: the epoch of rank r's last dispatch / combine
- *   local_off  64 bytes touched only by the owner: epoch, grid tickets, status
- * A step on every rank, on one stream: nsl_route + kc_pack_input_bf16 into a local chunk; nsl_ep_p2p_dispatch;
- * nsl_ep_p2p_wait_dispatch; nsl_ep_plan, nsl_mv_gu_rows, nsl_mv_sel_rows on the window's receive area;
- * nsl_ep_p2p_combine; nsl_ep_p2p_reduce.  All ranks must run the same number of steps.  The kernels of different
- * ranks wait on one another, so every rank needs its own GPU. */
+ *   dflag_off, cflag_off   n counters each, 128 bytes apart: rows rank r has delivered here so far (dispatch / combine)
+ *   local_off  64 bytes touched only by the owner: epoch, a grid ticket, status
+ * A step on every rank, on one stream: nsl_ep_p2p_route_dispatch (or nsl_route + kc_pack_input_bf16 into a local chunk
+ * and nsl_ep_p2p_dispatch); nsl_ep_p2p_plan (waits for every rank's rows, then plans); nsl_mv_gu_rows and
+ * nsl_mv_sel_rows on the receive area; nsl_ep_p2p_combine; nsl_ep_p2p_reduce.  All ranks must run the same number of
+ * steps.  The kernels of different ranks wait on one another, so every rank needs its own GPU. */
 #define NSL_EP_MAX_RANKS 16
 typedef struct {
     void* win[NSL_EP_MAX_RANKS];   /* every rank's window as mapped in this process; win[me] is the local one */
     int32_t n, me;
+    int32_t t_loc, reserved;       /* token rows per rank and step */
     uint64_t bytes;                /* size of a window */
     uint64_t chunk_bytes, recv_off, parts_off, dflag_off, cflag_off, local_off;
 } NslEpWindow;
@@ -66,15 +67,24 @@ int nsl_ep_window_alloc(size_t bytes, void** ptr, void* handle64);
 int nsl_ep_window_open(const void* handle64, void** ptr);
 int nsl_ep_window_close(void* ptr);
 int nsl_ep_window_free(void* ptr);
-/* chunk (chunk_bytes, 16-byte aligned, local) -> slot `me` of every window's receive area, then dispatch flag `me`. */
+/* chunk (chunk_bytes, 16-byte aligned, local) -> slot `me` of every window's receive area; t_loc rows signalled. */
 void nsl_ep_p2p_dispatch(cudaStream_t s, NslEpWindow w, const void* chunk);
-/* Returns (on the stream) when every rank's chunk of this step has landed in the local window. */
+/* Router, bf16 packing and dispatch in one kernel: logits [t_loc][ld] and x [t_loc][d] (f32, local) -> each token's row,
+ * ids and weights in slot `me` of every window (ind_off / wt_off = byte offsets of ids and weights inside a chunk,
+ * rows first).  n_exp <= 1024, top_k <= 32, d a multiple of 8. */
+void nsl_ep_p2p_route_dispatch(cudaStream_t s, NslEpWindow w, int n_exp, int top_k, const float* logits, int ld, const float* x,
+                               int d, uint64_t ind_off, uint64_t wt_off);
+/* Returns (on the stream) when every rank's rows of this step have landed in the local window. */
 void nsl_ep_p2p_wait_dispatch(cudaStream_t s, NslEpWindow w);
-/* nsl_ep_combine whose rows go to slot `me` of the owning rank's partial-row area, then combine flag `me`. */
-void nsl_ep_p2p_combine(cudaStream_t s, NslEpWindow w, const float* D, const float* wsel, const int32_t* tok_off, int t_loc,
-                        int d);
+/* nsl_ep_plan on the window's receive area with the wait inside the kernel (replaces nsl_ep_p2p_wait_dispatch +
+ * nsl_ep_plan). */
+void nsl_ep_p2p_plan(cudaStream_t s, NslEpWindow w, uint64_t ind_off, uint64_t wt_off, int k, int row_stride, int lo, int hi,
+                     int32_t* sel, int32_t* xrow, float* wsel, int32_t* tok_off, int32_t* count);
+/* nsl_ep_combine whose rows go to slot `me` of the owning rank's partial-row area; one row signalled per token.
+ * d a multiple of 4. */
+void nsl_ep_p2p_combine(cudaStream_t s, NslEpWindow w, const float* D, const float* wsel, const int32_t* tok_off, int d);
 /* Waits for every rank's partial rows, out[t][:] = their sum in rank order, and closes the step (epoch + 1). */
-void nsl_ep_p2p_reduce(cudaStream_t s, NslEpWindow w, int t_loc, int d, float* out);
+void nsl_ep_p2p_reduce(cudaStream_t s, NslEpWindow w, int d, float* out);
 /* 0 when no wait has run out since the last call; else code * 256 + (rank waited for + 1), code 1 = dispatch,
  * 2 = combine.  Synchronous (reads the window's status word); call it after the stream has drained. */
 int nsl_ep_p2p_status(NslEpWindow w);

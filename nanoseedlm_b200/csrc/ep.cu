@@ -1,6 +1,6 @@
 // Device steps of the expert-parallel layer (include/nslm_ep.h): the per-rank pair plan, the per-token pre-sum of the
 // local experts' outputs and the rank-order sum of the returned partial rows.  They read and write local memory only.
-#include "common.cuh"
+#include "ep_sync.cuh"
 
 namespace nsl {
 
@@ -12,12 +12,13 @@ __global__ void __launch_bounds__(1024) ep_plan_kernel(const int32_t* __restrict
                                                        int t_loc, int k, int rank_stride, int row_stride, int lo, int hi,
                                                        int32_t* __restrict__ sel, int32_t* __restrict__ xrow,
                                                        float* __restrict__ wsel, int32_t* __restrict__ tok_off,
-                                                       int32_t* __restrict__ count) {
+                                                       int32_t* __restrict__ count, NslEpWindow win, int wait) {
     __shared__ int wsum[32];
     __shared__ int base;
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     const int T = n_ranks * t_loc, n = T * k;
     grid_dependents_go();   // a dependent launch of the next kernel may bring its blocks in already
+    if (wait) wait_flags(win, win.dflag_off, (local_words(win)[EPW_EPOCH] + 1) * (uint32_t) win.t_loc, 1);   // peer-memory form: every rank's chunk has landed
     if (tid == 0) base = 0;
     __syncthreads();
     for (int c0 = 0; c0 < n; c0 += 1024) {
@@ -80,7 +81,24 @@ void nsl_ep_plan(cudaStream_t s, const int32_t* ind, const float* wt, int n_rank
         set_error("nsl_ep_plan: %d ranks x %d tokens x top %d is out of range", n_ranks, t_loc, k);
         return;
     }
-    ep_plan_kernel<<<1, 1024, 0, s>>>(ind, wt, n_ranks, t_loc, k, rank_stride, row_stride, lo, hi, sel, xrow, wsel, tok_off, count);
+    ep_plan_kernel<<<1, 1024, 0, s>>>(ind, wt, n_ranks, t_loc, k, rank_stride, row_stride, lo, hi, sel, xrow, wsel, tok_off, count,
+                                      NslEpWindow{}, 0);
+    count_launch();
+}
+
+// The plan on the window's receive area, after waiting (inside the kernel) for every rank's dispatch of this step.
+void nsl_ep_p2p_plan(cudaStream_t s, NslEpWindow w, uint64_t ind_off, uint64_t wt_off, int k, int row_stride, int lo, int hi,
+                     int32_t* sel, int32_t* xrow, float* wsel, int32_t* tok_off, int32_t* count) {
+    if (w.n < 1 || w.n > NSL_EP_MAX_RANKS || w.me < 0 || w.me >= w.n || !w.win[w.me] || w.t_loc < 1 || k < 1 ||
+        (long long) w.n * w.t_loc * k > 65536 || ind_off % 4 || wt_off % 4 || w.chunk_bytes % 4 ||
+        ind_off + (uint64_t) w.t_loc * k * 4 > w.chunk_bytes || wt_off + (uint64_t) w.t_loc * k * 4 > w.chunk_bytes ||
+        w.recv_off + (uint64_t) w.n * w.chunk_bytes > w.bytes) {
+        set_error("nsl_ep_p2p_plan: window, offsets or sizes out of range");
+        return;
+    }
+    const char* recv = (const char*) w.win[w.me] + w.recv_off;
+    ep_plan_kernel<<<1, 1024, 0, s>>>((const int32_t*) (recv + ind_off), (const float*) (recv + wt_off), w.n, w.t_loc, k,
+                                      (int) (w.chunk_bytes / 4), row_stride, lo, hi, sel, xrow, wsel, tok_off, count, w, 1);
     count_launch();
 }
 

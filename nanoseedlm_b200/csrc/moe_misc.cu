@@ -5,55 +5,20 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "route.cuh"
 #include "seed_block.cuh"
 
 namespace nsl {
 
-constexpr uint32_t FULL = 0xFFFFFFFFu;
-
 // ---- router ------------------------------------------------------------------------------------------------------------
-// One warp per row.  Lane l holds experts l, l+32, ..; k rounds of a warp arg-max where equal logits go to the higher
-// expert id; weights exp(l - max) renormalised over the k picked.
-constexpr int ROUTE_PER_LANE = 32;   // experts <= 1024
+// One warp per row (route_row in route.cuh).
 template <int PER>                   // experts per lane held in registers: E <= 32 * PER
 __global__ void __launch_bounds__(128) route_kernel(int E, int k, const float* __restrict__ logits, int ld,
                                                     int32_t* __restrict__ ind, float* __restrict__ wt, int T) {
     const int lane = threadIdx.x & 31, t = blockIdx.x * 4 + (threadIdx.x >> 5);
     grid_dependents_go();   // a dependent launch of the next kernel may bring its blocks in as these retire
     if (t >= T) return;
-    const float* l = logits + (size_t) t * ld;
-    float v[PER];
-    float mx = -INFINITY;
-#pragma unroll
-    for (int j = 0; j < PER; ++j) {
-        const int e = lane + 32 * j;
-        v[j] = e < E ? l[e] : -INFINITY;
-        mx = fmaxf(mx, v[j]);
-    }
-    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(FULL, mx, o));
-    float top = 0.0f, mine = 0.0f;   // lane r keeps round r's unnormalised weight
-    for (int r = 0; r < k; ++r) {
-        float bv = -INFINITY;
-        int bi = -1;
-#pragma unroll
-        for (int j = 0; j < PER; ++j) {
-            const int e = lane + 32 * j;
-            if (e < E && (v[j] > bv || (v[j] == bv && e > bi))) { bv = v[j]; bi = e; }
-        }
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(FULL, bv, o);
-            const int oi = __shfl_xor_sync(FULL, bi, o);
-            if (ov > bv || (ov == bv && oi > bi)) { bv = ov; bi = oi; }
-        }
-#pragma unroll
-        for (int j = 0; j < PER; ++j)
-            if (lane + 32 * j == bi) v[j] = -INFINITY;
-        const float w = expf(bv - mx);
-        top += w;
-        if (lane == r) mine = w;
-        if (lane == 0) ind[(size_t) t * k + r] = bi;
-    }
-    if (lane < k) wt[(size_t) t * k + lane] = mine / top;
+    route_row<PER>(E, k, logits + (size_t) t * ld, lane, ind + (size_t) t * k, wt + (size_t) t * k);
 }
 
 // ---- elementwise --------------------------------------------------------------------------------------------------------

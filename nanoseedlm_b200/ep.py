@@ -41,7 +41,7 @@ def window_layout(N, t_loc, d, k):
     dflag_off = up(parts_off + N * t_loc * d * 4)
     cflag_off = dflag_off + N * 128
     local_off = cflag_off + N * 128
-    return {"chunk_bytes": lay["bytes"], "recv_off": 0, "parts_off": parts_off, "dflag_off": dflag_off,
+    return {"t_loc": t_loc, "chunk_bytes": lay["bytes"], "recv_off": 0, "parts_off": parts_off, "dflag_off": dflag_off,
             "cflag_off": cflag_off, "local_off": local_off, "bytes": up(local_off + 128)}
 
 
@@ -96,7 +96,7 @@ class P2PWindow:
         w, wl = L.NslEpWindow(), self.wl
         for r, q in enumerate(self.ptrs):
             w.win[r] = q
-        w.n, w.me, w.bytes = len(self.ptrs), self.me, wl["bytes"]
+        w.n, w.me, w.t_loc, w.bytes = len(self.ptrs), self.me, wl["t_loc"], wl["bytes"]
         for f in ("chunk_bytes", "recv_off", "parts_off", "dflag_off", "cflag_off", "local_off"):
             setattr(w, f, wl[f])
         return w
@@ -156,12 +156,12 @@ class ExpertParallelMoe:
     def step(self, x, logits):
         """x [t_loc][d] f32 (bf16-valued), logits [t_loc][E] -> out [t_loc][d] (this rank's tokens)."""
         be = self.be
-        be.route_and_pack(self, x, logits)                 # fills send[0]
         if self.collectives == "p2p":
-            be.p2p_dispatch(self)
+            be.route_pack_dispatch(self, x, logits)        # router + bf16 rows straight into every rank's window
             be.local_experts(self)
             be.reduce(self)
             return self.out
+        be.route_and_pack(self, x, logits)                 # fills send[0]
         self.dispatch()
         be.local_experts(self)                             # plan + mat-vecs + per-token pre-sum -> partial [N][t_loc][d]
         self.combine()
@@ -207,10 +207,11 @@ class GraphedSteps:
         self.p2p = ep.collectives == "p2p"
 
         def first(x, logits):
-            be.route_and_pack(ep, x, logits)
             if self.p2p:
-                be.p2p_dispatch(ep)
-            elif ep.N > 1 and not gather:
+                be.route_pack_dispatch(ep, x, logits)
+                return
+            be.route_and_pack(ep, x, logits)
+            if ep.N > 1 and not gather:
                 ep.send[1:] = ep.send[0]
 
         def second(layer):
@@ -278,11 +279,12 @@ class CudaBackend:
         base = ep.recv_ptr
         T = ep.N * ep.t_loc
         p2p = ep.collectives == "p2p"
-        if p2p:
-            lib.nsl_ep_p2p_wait_dispatch(s, ep.win)
-        lib.nsl_ep_plan(s, base + lay["ind_off"], base + lay["wt_off"], ep.N, ep.t_loc, ep.k, lay["bytes"] // 4, lay["rows"],
-                        ep.lo, ep.hi, self.sel.data_ptr(), self.xrow.data_ptr(), self.wsel.data_ptr(),
-                        self.tok_off.data_ptr(), self.count.data_ptr())
+        out = (self.sel.data_ptr(), self.xrow.data_ptr(), self.wsel.data_ptr(), self.tok_off.data_ptr(), self.count.data_ptr())
+        if p2p:      # the wait for every rank's chunk is the first thing the plan kernel does
+            lib.nsl_ep_p2p_plan(s, ep.win, lay["ind_off"], lay["wt_off"], ep.k, lay["rows"], ep.lo, ep.hi, *out)
+        else:
+            lib.nsl_ep_plan(s, base + lay["ind_off"], base + lay["wt_off"], ep.N, ep.t_loc, ep.k, lay["bytes"] // 4,
+                            lay["rows"], ep.lo, ep.hi, *out)
         P = T * ep.k
         lib.nsl_dependent_launch(1)   # the three kernels after the plan come in while their predecessor drains
         lib.nsl_mv_gu_rows(s, lyr.gate.table.data_ptr(), lyr.up.table.data_ptr(), lyr.d, lyr.ff, base, ep.d, 1,
@@ -291,16 +293,23 @@ class CudaBackend:
         lib.nsl_mv_sel_rows(s, lyr.down.table.data_ptr(), lyr.ff, lyr.d, self.A.data_ptr(), lyr.ff, self.D.data_ptr(), lyr.d,
                             self.sel.data_ptr(), P, self.count.data_ptr(), self.expected_pairs, self.G.data_ptr())
         if p2p:
-            lib.nsl_ep_p2p_combine(s, ep.win, self.D.data_ptr(), self.wsel.data_ptr(), self.tok_off.data_ptr(), ep.t_loc, ep.d)
+            lib.nsl_ep_p2p_combine(s, ep.win, self.D.data_ptr(), self.wsel.data_ptr(), self.tok_off.data_ptr(), ep.d)
         else:
             lib.nsl_ep_combine(s, self.D.data_ptr(), self.wsel.data_ptr(), self.tok_off.data_ptr(), T, ep.d, ep.partial.data_ptr())
         lib.nsl_dependent_launch(0)
 
     def p2p_dispatch(self, ep):
+        """The chunk route_and_pack left in send[0] -> every rank's window."""
         self.lib.nsl_ep_p2p_dispatch(self._s(), ep.win, ep.send.data_ptr())
+
+    def route_pack_dispatch(self, ep, x, logits):
+        """route_and_pack + p2p_dispatch as one kernel that stores straight into the windows."""
+        lay = ep.lay
+        self.lib.nsl_ep_p2p_route_dispatch(self._s(), ep.win, ep.E, ep.k, logits.data_ptr(), ep.E, x.data_ptr(), ep.d,
+                                           lay["ind_off"], lay["wt_off"])
 
     def reduce(self, ep):
         if ep.collectives == "p2p":
-            self.lib.nsl_ep_p2p_reduce(self._s(), ep.win, ep.t_loc, ep.d, ep.out.data_ptr())
+            self.lib.nsl_ep_p2p_reduce(self._s(), ep.win, ep.d, ep.out.data_ptr())
         else:
             self.lib.nsl_ep_reduce(self._s(), ep.parts.data_ptr(), ep.N, ep.t_loc, ep.d, ep.out.data_ptr())

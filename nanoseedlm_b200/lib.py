@@ -40,12 +40,13 @@ class HmvArgs(C.Structure):
 
 
 class NslEpWindow(C.Structure):
-    _fields_ = [("win", C.c_void_p * 16), ("n", C.c_int32), ("me", C.c_int32), ("bytes", C.c_uint64),
+    _fields_ = [("win", C.c_void_p * 16), ("n", C.c_int32), ("me", C.c_int32), ("t_loc", C.c_int32), ("reserved", C.c_int32),
+                ("bytes", C.c_uint64),
                 ("chunk_bytes", C.c_uint64), ("recv_off", C.c_uint64), ("parts_off", C.c_uint64), ("dflag_off", C.c_uint64),
                 ("cflag_off", C.c_uint64), ("local_off", C.c_uint64)]
 
 
-assert C.sizeof(NslEpWindow) == 192
+assert C.sizeof(NslEpWindow) == 200
 assert C.sizeof(WSlice) == 48 and C.sizeof(MmTile) == 16 and C.sizeof(RouterArgs) == 20 and C.sizeof(HmvArgs) == 32
 
 _vp, _i, _sz = C.c_void_p, C.c_int, C.c_size_t
@@ -117,8 +118,10 @@ PROTOTYPES = {
     "nsl_ep_window_free": (_i, [_vp]),
     "nsl_ep_p2p_dispatch": (None, [_vp, NslEpWindow, _vp]),
     "nsl_ep_p2p_wait_dispatch": (None, [_vp, NslEpWindow]),
-    "nsl_ep_p2p_combine": (None, [_vp, NslEpWindow, _vp, _vp, _vp, _i, _i]),
-    "nsl_ep_p2p_reduce": (None, [_vp, NslEpWindow, _i, _i, _vp]),
+    "nsl_ep_p2p_plan": (None, [_vp, NslEpWindow, C.c_uint64, C.c_uint64, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "nsl_ep_p2p_route_dispatch": (None, [_vp, NslEpWindow, _i, _i, _vp, _i, _vp, _i, C.c_uint64, C.c_uint64]),
+    "nsl_ep_p2p_combine": (None, [_vp, NslEpWindow, _vp, _vp, _vp, _i]),
+    "nsl_ep_p2p_reduce": (None, [_vp, NslEpWindow, _i, _vp]),
     "nsl_ep_p2p_status": (_i, [NslEpWindow]),
 }
 

@@ -91,7 +91,8 @@ def test_p2p_exchange_single_rank_and_graphs(oracle):
     m.close()
 
 
-def test_p2p_exchange_four_ranks_driven_from_one_stream(oracle):
+@pytest.mark.parametrize("fused", [False, True])
+def test_p2p_exchange_four_ranks_driven_from_one_stream(oracle, fused):
     """Four ranks' windows in one process, their kernels issued on one stream with every rank's producers before any
     rank's consumers (so no kernel ever waits for a later one): dispatch slots, flags, epochs and the owner-indexed
     partial rows all line up with the plain MoE layer over the whole batch, for several steps."""
@@ -111,8 +112,11 @@ def test_p2p_exchange_four_ranks_driven_from_one_stream(oracle):
         ref = m.forward_host(x, logits)[0]
         dx, dl = torch.from_numpy(x).cuda(), torch.from_numpy(logits).cuda()
         for r, e in enumerate(eps):
-            e.be.route_and_pack(e, dx[r * t_loc:(r + 1) * t_loc], dl[r * t_loc:(r + 1) * t_loc])
-            e.be.p2p_dispatch(e)
+            if fused:      # router + packing + dispatch in one kernel
+                e.be.route_pack_dispatch(e, dx[r * t_loc:(r + 1) * t_loc], dl[r * t_loc:(r + 1) * t_loc])
+            else:          # a ready-made chunk copied into the windows
+                e.be.route_and_pack(e, dx[r * t_loc:(r + 1) * t_loc], dl[r * t_loc:(r + 1) * t_loc])
+                e.be.p2p_dispatch(e)
         for e in eps:
             e.be.local_experts(e)
         for e in eps:
@@ -130,7 +134,7 @@ def test_p2p_exchange_four_ranks_driven_from_one_stream(oracle):
 def test_p2p_refuses_an_inconsistent_window():
     from nanoseedlm_b200 import ep, lib as L
     w = L.NslEpWindow()
-    w.n, w.me, w.bytes, w.chunk_bytes = 2, 0, 1024, 64
+    w.n, w.me, w.t_loc, w.bytes, w.chunk_bytes = 2, 0, 4, 1024, 64
     L.load().nsl_ep_p2p_wait_dispatch(None, w)      # null windows: nothing is launched
     with pytest.raises(RuntimeError, match="inconsistent"):
         L.check()
