@@ -194,6 +194,20 @@ const char* nsl_last_error(void);
 uint64_t nsl_launch_count(void);
 /* Multiprocessor count the persistent grids are sized for (queried once per device). */
 int nsl_sm_count(void);
+/* Work units: the pairs of a gather mat-vec grouped two by two per slice, so that two pairs that use the same expert
+ * share one expansion of its weights (results per pair are bit-identical to the ungrouped calls; only the logic-pipe
+ * work is shared).  nsl_mv_units builds the list on the device: sel[p] < n_slices for p < max_pairs (or < *count when
+ * count is given, device memory); units holds 4 ints per unit (max_pairs units at most), *n_units their number.
+ * max_pairs <= 4096, n_slices <= 1024.  nsl_mv_gu_units / nsl_mv_sel_units are kc_mv_gu / kc_mv_sel over such a list
+ * (K = 64 * 2^j <= 2048): xrow (optional) = input row per pair, else pair / xdiv; x_bf16: inputs are packed bf16 rows;
+ * raw: unrounded f32 outputs. */
+void nsl_mv_units(cudaStream_t s, const int32_t* sel, int max_pairs, const int32_t* count, int n_slices, int32_t* units,
+                  int32_t* n_units);
+void nsl_mv_gu_units(cudaStream_t s, const WSlice* wg, const WSlice* wu, int K, int R, const void* x, int xs, int x_bf16, float* out,
+                     int ys, const int32_t* sel, const int32_t* xrow, int xdiv, const int32_t* units, const int32_t* n_units,
+                     int max_pairs, int raw, const uint32_t* G);
+void nsl_mv_sel_units(cudaStream_t s, const WSlice* ws, int K, int R, const float* x, int xs, float* y, int ys, const int32_t* sel,
+                      const int32_t* units, const int32_t* n_units, int max_pairs, int raw, const uint32_t* G);
 /* Programmatic dependent launch for the calling thread's next launches of the mat-vec kernels (kc_mv*, nsl_mv*),
  * kq4_moe_combine and nsl_ep_combine: while on, such a kernel may become resident before the previous kernel in its
  * stream has finished and waits on the device for its completion before it touches memory a neighbour writes.  Turn it

@@ -36,6 +36,8 @@ struct MvParams {
     const int32_t* xrow;    // optional: pair p reads input row xrow[p] (instead of p / xdiv)
     const int32_t* count;   // optional: the pair count is read on the device (<= P)
     int xbf16;              // inputs are packed bf16 rows (row stride xs in bf16 elements)
+    const int32_t* units;   // optional: [n][4] work units = {pair, second pair or -1 (same slice), weight prefix, 0}
+    const int32_t* n_units; // their number, on the device
 };
 
 __device__ __forceinline__ float silu_bf(float g) {   // each op rounded to bf16 (engine/kernels_moe.cu:28-31)
@@ -179,6 +181,48 @@ __global__ void __launch_bounds__(MV_THREADS, 1) mv_regx_kernel(MvParams a, KCon
     }
 }
 
+// One thread's share of staging a pair's inputs: 16 inputs (two blocks: chunk j of the row, block pair bp), scaled, as
+// the f32x2 operands of pair_dot plus their centring constants.
+__device__ __forceinline__ void stage_inputs(const MvParams& a, int xr, int j, int bp, ulonglong2* sx, ulonglong2* sm) {
+    float x[16], xm[8];
+    if (a.xbf16) {
+        const uint4* xp = (const uint4*) ((const uint16_t*) a.x + (size_t) xr * a.xs + (size_t) j * 64 + bp * 16);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const uint4 t = __ldg(xp + i);
+            const uint32_t u[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                x[8 * i + 2 * q] = __uint_as_float(u[q] << 16) * NSL_XSCALE;
+                x[8 * i + 2 * q + 1] = __uint_as_float(u[q] & 0xFFFF0000u) * NSL_XSCALE;
+            }
+        }
+    } else {
+        const float4* xp = (const float4*) (a.x + (size_t) xr * a.xs + (size_t) j * 64 + bp * 16);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float4 t = __ldg(xp + i);
+            x[4 * i] = t.x * NSL_XSCALE; x[4 * i + 1] = t.y * NSL_XSCALE; x[4 * i + 2] = t.z * NSL_XSCALE; x[4 * i + 3] = t.w * NSL_XSCALE;
+        }
+    }
+    block_offsets(x, xm);
+    block_offsets(x + 8, xm + 4);
+#pragma unroll
+    for (int cq = 0; cq < 4; ++cq) {
+        ulonglong2 t;
+        t.x = pack2(x[2 * cq], x[8 + 2 * cq]);
+        t.y = pack2(x[2 * cq + 1], x[8 + 2 * cq + 1]);
+        sx[(bp * 4 + cq) * 32 + j] = t;
+    }
+#pragma unroll
+    for (int pq = 0; pq < 2; ++pq) {
+        ulonglong2 t;
+        t.x = pack2(xm[2 * pq], xm[4 + 2 * pq]);
+        t.y = pack2(xm[2 * pq + 1], xm[4 + 2 * pq + 1]);
+        sm[(bp * 2 + pq) * 32 + j] = t;
+    }
+}
+
 // ---- one token per pair, inputs in shared memory, two blocks of 8 warps per SM ------------------------------------------
 // The same arithmetic, lane mapping and order as mv_regx_kernel (so results are bit-identical), but the pair's inputs
 // sit in shared memory as the f32x2 operands of pair_dot, laid out [block pair][operand pair][lane] so that a warp's
@@ -220,44 +264,7 @@ __global__ void __launch_bounds__(MV_THREADS, 2) mv_shx_kernel(MvParams a, KCons
         if (pair != p_first) __syncthreads();   // the previous pair's inputs are no longer read
         if (threadIdx.x < lpr * 4) {
             const int j = threadIdx.x & (lpr - 1), bp = threadIdx.x >> lpr_log2;
-            const int xr = a.xrow ? a.xrow[pair] : pair / a.xdiv;
-            float x[16], xm[8];
-            if (a.xbf16) {
-                const uint4* xp = (const uint4*) ((const uint16_t*) a.x + (size_t) xr * a.xs + (size_t) j * 64 + bp * 16);
-#pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                    const uint4 t = __ldg(xp + i);
-                    const uint32_t u[4] = {t.x, t.y, t.z, t.w};
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        x[8 * i + 2 * q] = __uint_as_float(u[q] << 16) * NSL_XSCALE;
-                        x[8 * i + 2 * q + 1] = __uint_as_float(u[q] & 0xFFFF0000u) * NSL_XSCALE;
-                    }
-                }
-            } else {
-                const float4* xp = (const float4*) (a.x + (size_t) xr * a.xs + (size_t) j * 64 + bp * 16);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float4 t = __ldg(xp + i);
-                    x[4 * i] = t.x * NSL_XSCALE; x[4 * i + 1] = t.y * NSL_XSCALE; x[4 * i + 2] = t.z * NSL_XSCALE; x[4 * i + 3] = t.w * NSL_XSCALE;
-                }
-            }
-            block_offsets(x, xm);
-            block_offsets(x + 8, xm + 4);
-#pragma unroll
-            for (int cq = 0; cq < 4; ++cq) {
-                ulonglong2 t;
-                t.x = pack2(x[2 * cq], x[8 + 2 * cq]);
-                t.y = pack2(x[2 * cq + 1], x[8 + 2 * cq + 1]);
-                sx[(bp * 4 + cq) * 32 + j] = t;
-            }
-#pragma unroll
-            for (int pq = 0; pq < 2; ++pq) {
-                ulonglong2 t;
-                t.x = pack2(xm[2 * pq], xm[4 + 2 * pq]);
-                t.y = pack2(xm[2 * pq + 1], xm[4 + 2 * pq + 1]);
-                sm[(bp * 2 + pq) * 32 + j] = t;
-            }
+            stage_inputs(a, a.xrow ? a.xrow[pair] : pair / a.xdiv, j, bp, sx, sm);
         }
         __syncthreads();   // inputs staged (and, for the block's first pair, the stream table loaded)
         const float sca = slice_scale(wa.eb), scb = slice_scale(wb.eb);
@@ -409,6 +416,167 @@ __global__ void __launch_bounds__(MV_THREADS, 1) mv_smemx_kernel(MvParams a, KCo
     }
 }
 
+// ---- two pairs per expansion -----------------------------------------------------------------------------------------
+// mv_shx_kernel over work UNITS: a unit is one or two pairs that use the same slice, and a block pair's 32 states and
+// coefficients are expanded once for both.  Per pair the arithmetic and its order are those of mv_shx_kernel, so the
+// results are bit-identical; what changes is that the logic-pipe work (the expansion) is shared.
+// The next row step's streams travel global -> shared memory with cp.async (no registers held while they fly): one slot
+// per thread and matrix, read back only by the thread that requested it.
+struct ChunkSlots { uint4 s[MV_THREADS], c[MV_THREADS]; uint32_t cd[MV_THREADS]; };
+
+__device__ __forceinline__ void chunk_request(ChunkSlots& sl, const WSlice* __restrict__ w, size_t chunk_index) {
+    const unsigned long long* wp = (const unsigned long long*) w->p;   // the slice's stream addresses, re-read (L1) per request
+    const void* p0 = (const void*) __ldg(wp);
+    const void* p1 = (const void*) __ldg(wp + 1);
+    const void* p3 = (const void*) __ldg(wp + 3);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned) __cvta_generic_to_shared(&sl.s[threadIdx.x])),
+                 "l"((const uint4*) p0 + chunk_index) : "memory");
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned) __cvta_generic_to_shared(&sl.c[threadIdx.x])),
+                 "l"((const uint4*) p1 + chunk_index) : "memory");
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned) __cvta_generic_to_shared(&sl.cd[threadIdx.x])),
+                 "l"((const uint32_t*) p3 + chunk_index) : "memory");
+}
+__device__ __forceinline__ Chunk chunk_take(const ChunkSlots& sl) {
+    Chunk k;
+    k.s = sl.s[threadIdx.x];
+    k.c = sl.c[threadIdx.x];
+    k.cd = sl.cd[threadIdx.x];
+    return k;
+}
+
+// One matrix's share of a row step for a unit: four block pairs expanded once, dotted with one or two inputs.
+__device__ __forceinline__ void unit_chunk_dot(const StreamTab& tab, const KConst& kc, const Chunk& k, const ulonglong2 (*sx)[4 * 4 * 32],
+                                               const ulonglong2 (*sm)[4 * 2 * 32], int jc, bool two, u64& acc0, u64& acc1) {
+    const uint32_t sw[4] = {k.s.x, k.s.y, k.s.z, k.s.w}, cw[4] = {k.c.x, k.c.y, k.c.z, k.c.w};
+#pragma unroll
+    for (int bp = 0; bp < 4; ++bp) {
+        u64 v[32], q[4];
+        pair_states(tab, sw[bp], v);
+        pair_coefs(cw[bp], kc, q);
+        const u64 e2 = code_scale_pair(k.cd, bp, kc);
+        {
+            u64 x2[8], xm2[4];
+#pragma unroll
+            for (int cq = 0; cq < 4; ++cq) { const ulonglong2 t = sx[0][(bp * 4 + cq) * 32 + jc]; x2[2 * cq] = t.x; x2[2 * cq + 1] = t.y; }
+#pragma unroll
+            for (int pq = 0; pq < 2; ++pq) { const ulonglong2 t = sm[0][(bp * 2 + pq) * 32 + jc]; xm2[2 * pq] = t.x; xm2[2 * pq + 1] = t.y; }
+            acc0 = fma2(pair_dot(v, q, x2, xm2), e2, acc0);
+        }
+        if (two) {
+            u64 x2[8], xm2[4];
+#pragma unroll
+            for (int cq = 0; cq < 4; ++cq) { const ulonglong2 t = sx[1][(bp * 4 + cq) * 32 + jc]; x2[2 * cq] = t.x; x2[2 * cq + 1] = t.y; }
+#pragma unroll
+            for (int pq = 0; pq < 2; ++pq) { const ulonglong2 t = sm[1][(bp * 2 + pq) * 32 + jc]; xm2[2 * pq] = t.x; xm2[2 * pq + 1] = t.y; }
+            acc1 = fma2(pair_dot(v, q, x2, xm2), e2, acc1);
+        }
+    }
+}
+
+constexpr int UNIT_W1 = 3, UNIT_W2 = 4;   // relative cost of a row step for one pair and for two pairs sharing an expansion
+
+// Position x of the weighted (unit, step) sequence -> the unit that holds it and the step inside (floor).
+__device__ __forceinline__ void unit_position(const int32_t* __restrict__ units, int U, int rs, long long x, int& u, int& step) {
+    int lo = 0, hi = U;      // the last unit whose start (units[4u+2] * rs) is <= x
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if ((long long) units[4 * mid + 2] * rs <= x) lo = mid; else hi = mid;
+    }
+    const int w = units[4 * lo + 1] >= 0 ? UNIT_W2 : UNIT_W1;
+    const long long in = x - (long long) units[4 * lo + 2] * rs;
+    u = lo;
+    step = (int) (in / w);
+    if (step >= rs) { u = lo + 1; step = 0; }
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(MV_THREADS, 2) mv_shx2_kernel(MvParams a, KConst kc, int lpr_log2) {
+    constexpr int NM = MODE == MODE_GU ? 2 : 1;
+    __shared__ StreamTab tab;
+    __shared__ __align__(16) ulonglong2 sx[2][4 * 4 * 32];
+    __shared__ __align__(16) ulonglong2 sm[2][4 * 2 * 32];
+    __shared__ __align__(16) ChunkSlots slots[NM];
+    load_stream_tab(tab, a.G, threadIdx.x, MV_THREADS);
+    grid_dependents_go();
+    grid_dependency_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int lpr = 1 << lpr_log2, rpw = 32 >> lpr_log2;
+    const int jc = lane & (lpr - 1), ro = lane >> lpr_log2;
+    const int U = *a.n_units;
+    if (U <= 0) return;
+    const int rs = (a.R + rpw - 1) / rpw;
+    // Blocks take equal shares of the WEIGHTED sequence of (unit, row step): a step of a two-pair unit counts
+    // UNIT_W2, of a single UNIT_W1; units[4u + 2] = the weights of the units before u.
+    const long long wtotal = (long long) (a.units[4 * (U - 1) + 2] + (a.units[4 * (U - 1) + 1] >= 0 ? UNIT_W2 : UNIT_W1)) * rs;
+    const long long begin = (long long) blockIdx.x * wtotal / gridDim.x, end = (long long) (blockIdx.x + 1) * wtotal / gridDim.x;
+    if (begin >= end) return;
+    int u_first, s_first, u_last, s_last;     // [first, last) in (unit, step) order
+    bool staged = false;
+    unit_position(a.units, U, rs, begin, u_first, s_first);
+    unit_position(a.units, U, rs, end, u_last, s_last);
+    if (blockIdx.x == gridDim.x - 1) { u_last = U; s_last = 0; }
+    for (int u = u_first; u <= u_last; ++u) {
+        const int s_lo = u == u_first ? s_first : 0;
+        const int s_hi = u == u_last ? s_last : rs;
+        if (u >= U || s_lo >= s_hi) continue;
+        const int pa = a.units[4 * u], pb = a.units[4 * u + 1];
+        const bool two = pb >= 0;
+        const int slice = a.sel[pa];
+        const WSlice* wa = a.ws + slice;
+        const WSlice* wb = MODE == MODE_GU ? a.wu + slice : wa;
+        int st = s_lo + warp;
+        int r = st * rpw + ro;
+        if (st < s_hi && r < a.R) {      // this warp's first streams fly while the inputs are staged
+            chunk_request(slots[0], wa, (size_t) r * lpr + jc);
+            if (MODE == MODE_GU) chunk_request(slots[NM - 1], wb, (size_t) r * lpr + jc);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        if (staged) __syncthreads();   // the previous unit's inputs are no longer read
+        staged = true;
+        {
+            const int half = threadIdx.x >> 7, tl = threadIdx.x & 127;   // threads 0..127 stage the first pair, 128..255 the second
+            const int pair = half ? pb : pa;
+            if (tl < lpr * 4 && pair >= 0)
+                stage_inputs(a, a.xrow ? a.xrow[pair] : pair / a.xdiv, tl & (lpr - 1), tl >> lpr_log2, sx[half], sm[half]);
+        }
+        __syncthreads();
+        for (; st < s_hi; st += MV_WARPS, r += MV_WARPS * rpw) {
+            const bool ok = r < a.R;
+            const int rn = r + MV_WARPS * rpw;
+            const bool more = st + MV_WARPS < s_hi && rn < a.R;
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            u64 acc0 = 0ull, accu0 = 0ull, acc1 = 0ull, accu1 = 0ull;
+            {
+                Chunk k;
+                if (ok) k = chunk_take(slots[0]);
+                if (more) chunk_request(slots[0], wa, (size_t) rn * lpr + jc);   // the slot is free again: next step's streams
+                asm volatile("cp.async.commit_group;" ::: "memory");
+                if (ok) unit_chunk_dot(tab, kc, k, sx, sm, jc, two, acc0, acc1);
+            }
+            if (MODE == MODE_GU) {
+                Chunk k;
+                if (ok) k = chunk_take(slots[NM - 1]);
+                if (more) chunk_request(slots[NM - 1], wb, (size_t) rn * lpr + jc);
+                asm volatile("cp.async.commit_group;" ::: "memory");
+                if (ok) unit_chunk_dot(tab, kc, k, sx, sm, jc, two, accu0, accu1);
+            }
+            const float sca = slice_scale(__ldg(&wa->eb)), scb = slice_scale(__ldg(&wb->eb));
+            {
+                const float s0 = group_sum(pair_total(acc0), lpr) * sca;
+                float su0 = 0.0f;
+                if (MODE == MODE_GU) su0 = group_sum(pair_total(accu0), lpr) * scb;
+                if (ok && jc == 0) store_out<MODE>(a, pa, r, s0, su0);
+            }
+            if (two) {
+                const float s1 = group_sum(pair_total(acc1), lpr) * sca;
+                float su1 = 0.0f;
+                if (MODE == MODE_GU) su1 = group_sum(pair_total(accu1), lpr) * scb;
+                if (ok && jc == 0) store_out<MODE>(a, pb, r, s1, su1);
+            }
+        }
+    }
+}
+
 // ---- any K that is a multiple of 8, any alignment: one warp per (pair or dense, row), lanes over single blocks -------
 template <int MODE>
 __global__ void __launch_bounds__(MV_THREADS) mv_generic_kernel(MvParams a, KConst kc, int T) {
@@ -495,6 +663,54 @@ __global__ void __launch_bounds__(256) decode_kernel(WSlice w, KConst kc, int K,
     }
 }
 
+// ---- work units: pairs grouped two by two per slice -------------------------------------------------------------------
+// One block.  Pairs are counted per slice, a scan gives each slice its range of pairs and of units, pairs are placed
+// (in any order inside a slice: a pair's result does not depend on its partner) and every slice writes its units.
+constexpr int UNITS_MAX_PAIRS = 4096, UNITS_MAX_SLICES = 1024;
+__global__ void __launch_bounds__(1024) mv_units_kernel(const int32_t* __restrict__ sel, int max_pairs, const int32_t* __restrict__ count,
+                                                        int n_slices, int32_t* __restrict__ units, int32_t* __restrict__ n_units) {
+    __shared__ int cnt[UNITS_MAX_SLICES], poff[UNITS_MAX_SLICES], uoff[UNITS_MAX_SLICES], woff[UNITS_MAX_SLICES];
+    __shared__ int sorted[UNITS_MAX_PAIRS];
+    grid_dependents_go();
+    grid_dependency_wait();
+    const int tid = threadIdx.x;
+    const int P = count ? min(*count, max_pairs) : max_pairs;
+    cnt[tid] = 0;
+    __syncthreads();
+    for (int i = tid; i < P; i += 1024) atomicAdd(&cnt[sel[i]], 1);
+    __syncthreads();
+    const int n = tid < n_slices ? cnt[tid] : 0;
+    poff[tid] = n;
+    uoff[tid] = (n + 1) / 2;
+    woff[tid] = (n / 2) * UNIT_W2 + (n & 1) * UNIT_W1;
+    __syncthreads();
+    for (int o = 1; o < 1024; o <<= 1) {      // inclusive scans
+        const int a = tid >= o ? poff[tid - o] : 0, b = tid >= o ? uoff[tid - o] : 0, c = tid >= o ? woff[tid - o] : 0;
+        __syncthreads();
+        poff[tid] += a; uoff[tid] += b; woff[tid] += c;
+        __syncthreads();
+    }
+    const int p0 = poff[tid] - n, u0 = uoff[tid] - (n + 1) / 2, w0 = woff[tid] - ((n / 2) * UNIT_W2 + (n & 1) * UNIT_W1);
+    if (tid == 1023) *n_units = uoff[1023];
+    __syncthreads();
+    poff[tid] = p0;           // exclusive offsets; cnt becomes the placement cursor
+    cnt[tid] = 0;
+    __syncthreads();
+    for (int i = tid; i < P; i += 1024) {
+        const int e = sel[i];
+        sorted[poff[e] + atomicAdd(&cnt[e], 1)] = i;
+    }
+    __syncthreads();
+    for (int j = 0; 2 * j < n; ++j) {
+        const bool two = 2 * j + 1 < n;
+        int32_t* u = units + 4 * (u0 + j);
+        u[0] = sorted[p0 + 2 * j];
+        u[1] = two ? sorted[p0 + 2 * j + 1] : -1;
+        u[2] = w0 + j * UNIT_W2;     // units before it in this slice are all two-pair units
+        u[3] = 0;
+    }
+}
+
 static int g_mv_variant = 1;   // 1 (default): inputs in shared memory, 16 warps / SM; 0: inputs in registers, 8 warps / SM
 
 // ---- launch selection ---------------------------------------------------------------------------------------------------
@@ -523,12 +739,13 @@ static void launch_mv(cudaStream_t s, const MvParams& a, int T, int p_hint = 0) 
     // every allocator the callers use, and a row's chunks are contiguous, so only the inputs are checked here.
     const bool chunked = a.K % 64 == 0 && aligned16(a.x) && a.xs % 4 == 0;
     const bool pow2 = ch > 0 && (ch & (ch - 1)) == 0;
-    if ((a.xrow || a.count || a.xbf16) && !(chunked && pow2 && ch <= 32)) {
+    if ((a.xrow || a.count || a.xbf16 || a.units) && !(chunked && pow2 && ch <= 32 && T == 1)) {
         set_error("seed mat-vec: the row-index / device-count / bf16-input forms need K = 64 * 2^j <= 2048 (K = %d)", a.K);
         return;
     }
     if (chunked && T == 1 && pow2 && ch <= 32) {
-        if (g_mv_variant == 1) launch(mv_shx_kernel<MODE>, sms * 2, MV_THREADS, 0, s, a, kconst(), log2_floor(ch));
+        if (a.units) launch(mv_shx2_kernel<MODE>, sms * 2, MV_THREADS, 0, s, a, kconst(), log2_floor(ch));
+        else if (g_mv_variant == 1) launch(mv_shx_kernel<MODE>, sms * 2, MV_THREADS, 0, s, a, kconst(), log2_floor(ch));
         else launch(mv_regx_kernel<MODE>, sms, MV_THREADS, 0, s, a, kconst(), log2_floor(ch));
         count_launch();
         return;
@@ -564,34 +781,34 @@ extern "C" {
 void kc_mv(cudaStream_t s, int fmt, WSlice w, int K, int R, const float* x, int xs, float* y, int ys, int T, int add,
            const uint32_t* G) {
     if (!seed_fmt(fmt, "kc_mv")) return;
-    MvParams a = {NULL, NULL, w, NULL, x, y, G, K, R, T, 1, xs, ys, add, 0, NULL, NULL, 0};
+    MvParams a = {NULL, NULL, w, NULL, x, y, G, K, R, T, 1, xs, ys, add, 0, NULL, NULL, 0, NULL, NULL};
     launch_mv<MODE_ROUND>(s, a, T);
 }
 
 void kc_mv_sel(cudaStream_t s, int fmt, const WSlice* ws, int K, int R, const float* x, int xs, float* y, int ys,
                const int32_t* sel, int P, int xdiv, const uint32_t* G) {
     if (!seed_fmt(fmt, "kc_mv_sel")) return;
-    MvParams a = {ws, NULL, WSlice{}, sel, x, y, G, K, R, P, xdiv, xs, ys, 0, 0, NULL, NULL, 0};
+    MvParams a = {ws, NULL, WSlice{}, sel, x, y, G, K, R, P, xdiv, xs, ys, 0, 0, NULL, NULL, 0, NULL, NULL};
     launch_mv<MODE_ROUND>(s, a, 1);
 }
 
 void kc_mv_gu(cudaStream_t s, int fmt, const WSlice* wg, const WSlice* wu, int K, int R, const float* x, int xs, float* out,
               int ys, const int32_t* sel, int P, int xdiv, const uint32_t* G) {
     if (!seed_fmt(fmt, "kc_mv_gu")) return;
-    MvParams a = {wg, wu, WSlice{}, sel, x, out, G, K, R, P, xdiv, xs, ys, 0, 0, NULL, NULL, 0};
+    MvParams a = {wg, wu, WSlice{}, sel, x, out, G, K, R, P, xdiv, xs, ys, 0, 0, NULL, NULL, 0, NULL, NULL};
     launch_mv<MODE_GU>(s, a, 1);
 }
 
 void nsl_mv_raw(cudaStream_t s, const WSlice* ws, int K, int R, const float* x, int xs, float* y, int ys,
                 const int32_t* sel, int P, int xdiv, const uint32_t* G) {
-    MvParams a = {sel ? ws : NULL, NULL, WSlice{}, sel, x, y, G, K, R, P, xdiv > 0 ? xdiv : 1, xs, ys, 0, 1, NULL, NULL, 0};
+    MvParams a = {sel ? ws : NULL, NULL, WSlice{}, sel, x, y, G, K, R, P, xdiv > 0 ? xdiv : 1, xs, ys, 0, 1, NULL, NULL, 0, NULL, NULL};
     if (!sel) a.w0 = *ws;   // dense: ws is a host pointer to the one slice
     launch_mv<MODE_ROUND>(s, a, sel ? 1 : P);
 }
 
 void nsl_mv_gu_raw(cudaStream_t s, const WSlice* wg, const WSlice* wu, int K, int R, const float* x, int xs, float* out,
                    int ys, const int32_t* sel, int P, int xdiv, const uint32_t* G) {
-    MvParams a = {wg, wu, WSlice{}, sel, x, out, G, K, R, P, xdiv, xs, ys, 0, 1, NULL, NULL, 0};
+    MvParams a = {wg, wu, WSlice{}, sel, x, out, G, K, R, P, xdiv, xs, ys, 0, 1, NULL, NULL, 0, NULL, NULL};
     launch_mv<MODE_GU>(s, a, 1);
 }
 
@@ -600,13 +817,38 @@ void nsl_mv_gu_raw(cudaStream_t s, const WSlice* wg, const WSlice* wu, int K, in
 void nsl_mv_gu_rows(cudaStream_t s, const WSlice* wg, const WSlice* wu, int K, int R, const void* x, int xs, int x_bf16,
                     float* out, int ys, const int32_t* sel, const int32_t* xrow, int max_pairs, const int32_t* count,
                     int expected_pairs, const uint32_t* G) {
-    MvParams a = {wg, wu, WSlice{}, sel, (const float*) x, out, G, K, R, max_pairs, 1, xs, ys, 0, 0, xrow, count, x_bf16};
+    MvParams a = {wg, wu, WSlice{}, sel, (const float*) x, out, G, K, R, max_pairs, 1, xs, ys, 0, 0, xrow, count, x_bf16, NULL, NULL};
     launch_mv<MODE_GU>(s, a, 1, expected_pairs);
 }
 void nsl_mv_sel_rows(cudaStream_t s, const WSlice* ws, int K, int R, const float* x, int xs, float* y, int ys,
                      const int32_t* sel, int max_pairs, const int32_t* count, int expected_pairs, const uint32_t* G) {
     MvParams a = {ws, NULL, WSlice{}, sel, x, y, G, K, R, max_pairs, 1, xs, ys, 0, 0, NULL, count, 0};
     launch_mv<MODE_ROUND>(s, a, 1, expected_pairs);
+}
+
+// Work units over a pair list (see include/nslm_kernels.h): the grouping kernel and the two mat-vec forms that use it.
+void nsl_mv_units(cudaStream_t s, const int32_t* sel, int max_pairs, const int32_t* count, int n_slices, int32_t* units,
+                  int32_t* n_units) {
+    if (max_pairs < 1 || max_pairs > UNITS_MAX_PAIRS || n_slices < 1 || n_slices > UNITS_MAX_SLICES) {
+        set_error("nsl_mv_units: %d pairs (at most %d) or %d slices (at most %d)", max_pairs, UNITS_MAX_PAIRS, n_slices, UNITS_MAX_SLICES);
+        return;
+    }
+    launch(mv_units_kernel, 1, 1024, 0, s, sel, max_pairs, count, n_slices, units, n_units);
+    count_launch();
+}
+
+void nsl_mv_gu_units(cudaStream_t s, const WSlice* wg, const WSlice* wu, int K, int R, const void* x, int xs, int x_bf16, float* out,
+                     int ys, const int32_t* sel, const int32_t* xrow, int xdiv, const int32_t* units, const int32_t* n_units,
+                     int max_pairs, int raw, const uint32_t* G) {
+    MvParams a = {wg, wu, WSlice{}, sel, (const float*) x, out, G, K, R, max_pairs, xdiv > 0 ? xdiv : 1, xs, ys, 0, raw, xrow, NULL, x_bf16,
+                  units, n_units};
+    launch_mv<MODE_GU>(s, a, 1);
+}
+
+void nsl_mv_sel_units(cudaStream_t s, const WSlice* ws, int K, int R, const float* x, int xs, float* y, int ys, const int32_t* sel,
+                      const int32_t* units, const int32_t* n_units, int max_pairs, int raw, const uint32_t* G) {
+    MvParams a = {ws, NULL, WSlice{}, sel, x, y, G, K, R, max_pairs, 1, xs, ys, 0, raw, NULL, NULL, 0, units, n_units};
+    launch_mv<MODE_ROUND>(s, a, 1);
 }
 
 void nsl_mv_set_variant(int v) { g_mv_variant = v; }

@@ -88,6 +88,9 @@ PROTOTYPES = {
     "nsl_launch_count": (C.c_uint64, []),
     "nsl_sm_count": (_i, []),
     "nsl_dependent_launch": (None, [_i]),
+    "nsl_mv_units": (None, [_vp, _vp, _i, _vp, _i, _vp, _vp]),
+    "nsl_mv_gu_units": (None, [_vp, _vp, _vp, _i, _i, _vp, _i, _i, _vp, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _vp]),
+    "nsl_mv_sel_units": (None, [_vp, _vp, _i, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _vp]),
     # include/nslm_moe.h
     "nsl_moe_create": (_vp, [_i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "nsl_moe_destroy": (None, [_vp]),

@@ -158,3 +158,30 @@ def test_register_and_shared_memory_variants_are_bit_identical(oracle):
     lib.load().nsl_mv_set_variant(1)
     for a, b in zip(*outs):
         assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+@pytest.mark.parametrize("R,K,S,P", [(96, 2048, 5, 23), (512, 2048, 12, 64), (2048, 512, 12, 64), (40, 64, 3, 9), (64, 256, 20, 20)])
+def test_work_units_share_an_expansion_and_change_nothing(oracle, R, K, S, P):
+    """Pairs grouped two by two per slice (one expansion for both): every pair's row is bit-identical to the ungrouped
+    call, for the gate+up form (f32 and packed bf16 inputs, with and without a row index) and the gather form."""
+    from nanoseedlm_b200 import kernels
+    mats, w = weights(oracle, S, R, K, 11 * R + K, ebs=tuple(-22 + (i % 5) for i in range(S)))
+    _, w2 = weights(oracle, S, R, K, 13 * R + K, ebs=tuple(-21 + (i % 4) for i in range(S)))
+    rng = np.random.default_rng(P)
+    for sel in (rng.integers(0, S, P), np.zeros(P, np.int64) + (S - 1), np.arange(P) % S):
+        units, _, _ = kernels.kt_units(sel, S)
+        seen = sorted(int(p) for u in units for p in u[:2] if p >= 0)
+        assert seen == list(range(P))                                  # every pair in exactly one unit
+        assert all(u[1] < 0 or sel[u[0]] == sel[u[1]] for u in units)   # partners share the slice
+        counts = np.bincount(sel, minlength=S)
+        assert len(units) == int(((counts + 1) // 2).sum())
+        xdiv = 4
+        x = oracle.normal(31 + P, ((P + xdiv - 1) // xdiv) * K, bf16=True).reshape(-1, K)
+        assert np.array_equal(kernels.kt_mv_gu_units(w, w2, sel, xdiv, x), kernels.kt_mv_gu(w, w2, sel, xdiv, x))
+        xrow = rng.integers(0, x.shape[0], P)
+        ref = kernels.kt_mv_gu(w, w2, sel, 1, x[xrow])
+        assert np.array_equal(kernels.kt_mv_gu_units(w, w2, sel, 1, x, xrow=xrow), ref)
+        assert np.array_equal(kernels.kt_mv_gu_units(w, w2, sel, 1, x, xrow=xrow, bf16=True), ref)   # inputs are bf16 values
+        xp = oracle.normal(41 + P, P * K, bf16=True).reshape(P, K)
+        assert np.array_equal(kernels.kt_mv_sel_units(w, sel, xp), kernels.kt_mv_sel(w, sel, 1, xp))
+        assert np.array_equal(kernels.kt_mv_sel_units(w, sel, xp, raw=True), kernels.kt_mv_sel(w, sel, 1, xp, raw=True))
