@@ -382,7 +382,8 @@ EP_E, EP_K, EP_B = 512, 10, 64   # BASELINE config 3: 512 experts sharded over t
 def ep_config(world, layers):
     return {"workload": f"BASELINE config 3: expert-parallel synthetic MoE decode, {EP_E} seed-encoded experts (hidden {D}, "
                         f"intermediate {FF}) sharded evenly over {world} GPU(s), {EP_B} sequences x 1 token, top-{EP_K}, "
-                        "dispatch/combine all-to-all of bf16 rows / f32 partial sums over NCCL",
+                        "dispatch of bf16 rows and combine of f32 partial sums by the kernels themselves over NVLink peer memory "
+                        "(--ep-collectives a2a: NCCL all-to-alls)",
             "tokens": EP_B, "experts": EP_E, "top_k": EP_K, "hidden": D, "intermediate": FF, "parallelism": f"ep{world}",
             "l2_policy": f"steps rotate over {layers} independent layers per rank ({layers * EP_E // world * 3 * BYTES_PER_MATRIX / 1e9:.2f} GB "
                          "of packed streams per GPU), larger than the 126 MB L2"}
@@ -428,8 +429,8 @@ def run_ep(args):
         for i in range(W):
             one(i)
         stream.synchronize()
-        # one step = 9 kernels of this library + 2 all-to-alls; with --no-graph every launch is issued directly, else the
-        # kernels replay as three CUDA graphs per step with the collectives between them (see ep.GraphedSteps)
+        # one step = 6 kernels of this library with the peer-memory exchange (9 kernels + 2 collective calls otherwise); with
+        # --no-graph every launch is issued directly, else the kernels replay as CUDA graphs (see ep.GraphedSteps)
         launches0 = lib.nsl_launch_count()
         one(W)
         stream.synchronize()
@@ -514,9 +515,9 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-dependent-launch", action="store_true",
                     help="config 1: ordinary launches instead of programmatic dependent launches (for comparison)")
-    ap.add_argument("--ep-collectives", default="a2a", choices=["a2a", "gather", "p2p"],
-                    help="config 3: two NCCL all-to-alls (default), all-gather + reduce-scatter, or p2p: no collective call, "
-                         "the kernels store into the other ranks' memory over NVLink and wait on flags")
+    ap.add_argument("--ep-collectives", default="p2p", choices=["p2p", "a2a", "gather"],
+                    help="config 3: p2p (default): no collective call, the kernels store into the other ranks' memory over "
+                         "NVLink and wait on counters; a2a: two NCCL all-to-alls; gather: all-gather + reduce-scatter")
     ap.add_argument("--workload", default=None, choices=["cfg1", "cfg2", "cfg3"],
                     help="cfg1: one GPU's MoE decode layer (default at 1 GPU); cfg2: the same layer on 512 prompt rows (grouped "
                          "tcgen05 GEMM); cfg3: expert-parallel decode (default at >1 GPU)")

@@ -313,3 +313,45 @@ class CudaBackend:
             self.lib.nsl_ep_p2p_reduce(self._s(), ep.win, ep.d, ep.out.data_ptr())
         else:
             self.lib.nsl_ep_reduce(self._s(), ep.parts.data_ptr(), ep.N, ep.t_loc, ep.d, ep.out.data_ptr())
+
+
+def _emulate(ranks, steps, d=2048, ff=512, n_exp=512, k=10, batch=64):
+    """N ranks of the peer-memory step driven from ONE stream on ONE GPU (every rank's producers before any rank's
+    consumers, so that no kernel waits for a later one): each rank's kernels have the sizes of an N-GPU run, which makes
+    their durations readable from a profiler's launch list without N GPUs.  Prints the serial time per step."""
+    from . import lib as L, moe
+    t_loc = batch // ranks
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    wins = P2PWindow.local_group(ranks, t_loc, d, k)
+    eps = [ExpertParallelMoe(CudaBackend(moe.DeviceLayer.random_on_device(d, ff, n_exp // ranks, gen)), d, k, n_exp, t_loc,
+                             collectives="p2p", window=wins[r]) for r in range(ranks)]
+    x = torch.randn(batch, d, generator=gen, device="cuda")
+    logits = torch.randn(batch, n_exp, generator=gen, device="cuda")
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for s in range(steps + 1):
+        if s == 1:
+            e0.record()
+        for r, e in enumerate(eps):
+            e.be.route_pack_dispatch(e, x[r * t_loc:(r + 1) * t_loc], logits[r * t_loc:(r + 1) * t_loc])
+        for e in eps:
+            e.be.local_experts(e)
+        for e in eps:
+            e.be.reduce(e)
+    e1.record()
+    torch.cuda.synchronize()
+    status = [w.status() for w in wins]
+    L.check()
+    for w in wins:
+        w.close()
+    print(f"{ranks} emulated ranks, {steps} steps: {e0.elapsed_time(e1) * 1e3 / steps:.1f} us per step for all ranks in series "
+          f"({e0.elapsed_time(e1) * 1e3 / steps / ranks:.1f} us per rank); wait status {status}")
+
+
+if __name__ == "__main__":
+    import argparse
+    ap = argparse.ArgumentParser(description="the expert-parallel step of N ranks emulated on one GPU (kernel sizes of an N-GPU run)")
+    ap.add_argument("--ranks", type=int, default=8)
+    ap.add_argument("--steps", type=int, default=4)
+    a = ap.parse_args()
+    _emulate(a.ranks, a.steps)
