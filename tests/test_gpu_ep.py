@@ -138,3 +138,28 @@ def test_p2p_refuses_an_inconsistent_window():
     L.load().nsl_ep_p2p_wait_dispatch(None, w)      # null windows: nothing is launched
     with pytest.raises(RuntimeError, match="inconsistent"):
         L.check()
+
+
+def test_p2p_wait_runs_out_and_reports():
+    """A wait on a counter that nothing bumps (rank 1 of 2 never dispatches) ends by itself after its bound, records which
+    rank it waited for, and leaves the stream and the context usable."""
+    import time
+    import torch
+    from nanoseedlm_b200 import ep, lib as L
+    t_loc, d, k = 4, 256, 2
+    wins = ep.P2PWindow.local_group(2, t_loc, d, k)
+    w0 = wins[0].struct()
+    chunk = torch.zeros(wins[0].wl["chunk_bytes"], dtype=torch.uint8, device="cuda")
+    L.load().nsl_ep_p2p_dispatch(None, w0, chunk.data_ptr())          # rank 0's rows arrive; rank 1's never do
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    L.load().nsl_ep_p2p_wait_dispatch(None, w0)
+    torch.cuda.synchronize()
+    waited = time.perf_counter() - t0
+    assert 1.0 < waited < 10.0                                        # the bound is about two seconds
+    assert wins[0].status() == 1 * 256 + (1 + 1)                      # code 1 = dispatch, waited for rank 1
+    assert wins[0].status() == 0                                      # reading clears it
+    assert float((torch.ones(8, device="cuda") * 2).sum().item()) == 16.0
+    L.check()
+    for w in wins:
+        w.close()
