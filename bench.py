@@ -405,10 +405,17 @@ def run_ep(args):
     K, W = args.steps, max(args.warmup, 3)
     e_loc, t_loc = EP_E // world, EP_B // world
     NL = max(2, min(args.layers, int(6e9 // (e_loc * 3 * BYTES_PER_MATRIX))))
-    gen = torch.Generator(device="cuda").manual_seed(4321 + rank)
-    layers = [moe.DeviceLayer.random_on_device(D, FF, e_loc, gen) for _ in range(NL)]
+    mirror = bool(args.ep_mirror) and world % 2 == 0 and args.ep_collectives == "p2p"
+
+    def experts_of(r):      # rank r's experts of every layer: the same bytes on whichever rank generates them
+        g = torch.Generator(device="cuda").manual_seed(4321 + r)
+        return [moe.DeviceLayer.random_on_device(D, FF, e_loc, g) for _ in range(NL)]
+
+    layers = experts_of(rank)
+    if mirror:              # this rank also holds its partner's experts (own first, then the partner's)
+        layers = [moe.DeviceLayer.concat(a, b) for a, b in zip(layers, experts_of((rank + world // 2) % world))]
     be = ep.CudaBackend(layers[0])
-    epl = ep.ExpertParallelMoe(be, D, EP_K, EP_E, t_loc, collectives=args.ep_collectives)
+    epl = ep.ExpertParallelMoe(be, D, EP_K, EP_E, t_loc, collectives=args.ep_collectives, mirror=mirror)
     NB = 8
     rng = np.random.default_rng(7 + rank)
     hx = rng.standard_normal((NB, t_loc, D)).astype(np.float32)
@@ -492,7 +499,8 @@ def run_ep(args):
         line = {"metric": "seed_decode_moe_gemv_tokens_per_s", "value": EP_B / (ms_per_step * 1e-3), "unit": "tok/s",
                 "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_per_step, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": ep_config(world, NL),
-                "gpu_launches": int(launches), "cuda_graph": captured, "collectives": args.ep_collectives, "clocks": clocks.summary(),
+                "gpu_launches": int(launches), "cuda_graph": captured, "collectives": args.ep_collectives, "mirrored_ranks": mirror,
+                "clocks": clocks.summary(),
                 "e2e": {"value": EP_B / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": t_loc * D * 4 + t_loc * EP_E * 4,
                         "d2h_bytes_per_step": t_loc * D * 4, "ms_per_step": e2e_s * 1e3},
                 "roofline": {"bound": "hbm", "kernel": "mv_shx_kernel<gate+up> over this rank's pairs", "achieved": None,
@@ -518,6 +526,9 @@ def main():
     ap.add_argument("--ep-collectives", default="p2p", choices=["p2p", "a2a", "gather"],
                     help="config 3: p2p (default): no collective call, the kernels store into the other ranks' memory over "
                          "NVLink and wait on counters; a2a: two NCCL all-to-alls; gather: all-gather + reduce-scatter")
+    ap.add_argument("--ep-mirror", type=int, default=0,
+                    help="config 3, p2p, even rank counts: 1 = ranks r and r + N/2 hold each other's experts too and split their "
+                         "joint pairs in the middle (balance to within one pair; twice the expert bytes per GPU)")
     ap.add_argument("--workload", default=None, choices=["cfg1", "cfg2", "cfg3"],
                     help="cfg1: one GPU's MoE decode layer (default at 1 GPU); cfg2: the same layer on 512 prompt rows (grouped "
                          "tcgen05 GEMM); cfg3: expert-parallel decode (default at >1 GPU)")

@@ -77,9 +77,12 @@ void nsl_ep_p2p_route_dispatch(cudaStream_t s, NslEpWindow w, int n_exp, int top
 /* Returns (on the stream) when every rank's rows of this step have landed in the local window. */
 void nsl_ep_p2p_wait_dispatch(cudaStream_t s, NslEpWindow w);
 /* nsl_ep_plan on the window's receive area with the wait inside the kernel (replaces nsl_ep_p2p_wait_dispatch +
- * nsl_ep_plan). */
+ * nsl_ep_plan).  Mirrored ranks (lo2 < hi2; pass 0, 0, 0 otherwise): this rank also holds its partner's experts
+ * [lo2, hi2) after its own in its slice tables and the partner holds this rank's; both plan the pairs of either range
+ * in token order and split that list in the middle, the rank with upper = 0 taking the first ceil(n/2) pairs: the two
+ * shares differ by at most one pair whatever the routing.  sel = e - lo, or (hi - lo) + e - lo2 for the partner's. */
 void nsl_ep_p2p_plan(cudaStream_t s, NslEpWindow w, uint64_t ind_off, uint64_t wt_off, int k, int row_stride, int lo, int hi,
-                     int32_t* sel, int32_t* xrow, float* wsel, int32_t* tok_off, int32_t* count);
+                     int lo2, int hi2, int upper, int32_t* sel, int32_t* xrow, float* wsel, int32_t* tok_off, int32_t* count);
 /* nsl_ep_combine whose rows go to slot `me` of the owning rank's partial-row area; one row signalled per token.
  * d a multiple of 4. */
 void nsl_ep_p2p_combine(cudaStream_t s, NslEpWindow w, const float* D, const float* wsel, const int32_t* tok_off, int d);

@@ -115,12 +115,15 @@ class P2PWindow:
 
 
 class ExpertParallelMoe:
-    def __init__(self, backend, d, k, n_exp_total, t_loc, group=None, collectives="a2a", window=None):
+    def __init__(self, backend, d, k, n_exp_total, t_loc, group=None, collectives="a2a", window=None, mirror=False):
         """collectives: "a2a" -- two all-to-alls and a rank-order sum on the owner; "gather" -- the same data movement as
         an all-gather of the chunks and a reduce-scatter of the partial rows (the sum is then formed by the collective,
         in its own order); "p2p" -- no collective call: the kernels store into the other ranks' windows over NVLink and
         wait on flags (window: a P2PWindow, made here when omitted; passing one of P2PWindow.local_group's lets one
-        process drive several ranks)."""
+        process drive several ranks).
+        mirror (p2p only, an even number of ranks): rank r and rank r + N/2 hold each other's experts as well (the backend's
+        layer = the own experts followed by the partner's) and split the pairs of their joint expert set in the middle,
+        so that a pair of ranks is balanced to within one (token, expert) pair whatever the routing."""
         self.be, self.d, self.k, self.E, self.t_loc, self.group = backend, d, k, n_exp_total, t_loc, group
         self.collectives = collectives
         if window is not None:
@@ -132,6 +135,11 @@ class ExpertParallelMoe:
         self.e_loc = n_exp_total // self.N
         self.lo, self.hi = self.rank * self.e_loc, (self.rank + 1) * self.e_loc
         self.lay = chunk_layout(t_loc, d, k)
+        self.lo2, self.hi2, self.upper = 0, 0, 0
+        if mirror:
+            assert collectives == "p2p" and self.N % 2 == 0, "mirrored ranks need the peer-memory exchange and an even rank count"
+            partner = (self.rank + self.N // 2) % self.N
+            self.lo2, self.hi2, self.upper = partner * self.e_loc, (partner + 1) * self.e_loc, int(self.rank > partner)
         dev = backend.device
         self.send = torch.zeros(self.N, self.lay["bytes"], dtype=torch.uint8, device=dev)
         self.recv = torch.zeros(self.N, self.lay["bytes"], dtype=torch.uint8, device=dev)
@@ -281,7 +289,8 @@ class CudaBackend:
         p2p = ep.collectives == "p2p"
         out = (self.sel.data_ptr(), self.xrow.data_ptr(), self.wsel.data_ptr(), self.tok_off.data_ptr(), self.count.data_ptr())
         if p2p:      # the wait for every rank's chunk is the first thing the plan kernel does
-            lib.nsl_ep_p2p_plan(s, ep.win, lay["ind_off"], lay["wt_off"], ep.k, lay["rows"], ep.lo, ep.hi, *out)
+            lib.nsl_ep_p2p_plan(s, ep.win, lay["ind_off"], lay["wt_off"], ep.k, lay["rows"], ep.lo, ep.hi, ep.lo2, ep.hi2,
+                                ep.upper, *out)
         else:
             lib.nsl_ep_plan(s, base + lay["ind_off"], base + lay["wt_off"], ep.N, ep.t_loc, ep.k, lay["bytes"] // 4,
                             lay["rows"], ep.lo, ep.hi, *out)
@@ -315,7 +324,7 @@ class CudaBackend:
             self.lib.nsl_ep_reduce(self._s(), ep.parts.data_ptr(), ep.N, ep.t_loc, ep.d, ep.out.data_ptr())
 
 
-def _emulate(ranks, steps, d=2048, ff=512, n_exp=512, k=10, batch=64):
+def _emulate(ranks, steps, mirror=False, d=2048, ff=512, n_exp=512, k=10, batch=64):
     """N ranks of the peer-memory step driven from ONE stream on ONE GPU (every rank's producers before any rank's
     consumers, so that no kernel waits for a later one): each rank's kernels have the sizes of an N-GPU run, which makes
     their durations readable from a profiler's launch list without N GPUs.  Prints the serial time per step."""
@@ -323,8 +332,9 @@ def _emulate(ranks, steps, d=2048, ff=512, n_exp=512, k=10, batch=64):
     t_loc = batch // ranks
     gen = torch.Generator(device="cuda").manual_seed(1)
     wins = P2PWindow.local_group(ranks, t_loc, d, k)
-    eps = [ExpertParallelMoe(CudaBackend(moe.DeviceLayer.random_on_device(d, ff, n_exp // ranks, gen)), d, k, n_exp, t_loc,
-                             collectives="p2p", window=wins[r]) for r in range(ranks)]
+    held = (2 if mirror else 1) * n_exp // ranks      # timing only: the mirrored experts are random too
+    eps = [ExpertParallelMoe(CudaBackend(moe.DeviceLayer.random_on_device(d, ff, held, gen)), d, k, n_exp, t_loc,
+                             collectives="p2p", window=wins[r], mirror=mirror) for r in range(ranks)]
     x = torch.randn(batch, d, generator=gen, device="cuda")
     logits = torch.randn(batch, n_exp, generator=gen, device="cuda")
     torch.cuda.synchronize()
@@ -341,11 +351,12 @@ def _emulate(ranks, steps, d=2048, ff=512, n_exp=512, k=10, batch=64):
     e1.record()
     torch.cuda.synchronize()
     status = [w.status() for w in wins]
+    pairs = [int(e.be.count.item()) for e in eps]
     L.check()
     for w in wins:
         w.close()
     print(f"{ranks} emulated ranks, {steps} steps: {e0.elapsed_time(e1) * 1e3 / steps:.1f} us per step for all ranks in series "
-          f"({e0.elapsed_time(e1) * 1e3 / steps / ranks:.1f} us per rank); wait status {status}")
+          f"({e0.elapsed_time(e1) * 1e3 / steps / ranks:.1f} us per rank); pairs per rank {pairs}; wait status {status}")
 
 
 if __name__ == "__main__":
@@ -353,5 +364,6 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser(description="the expert-parallel step of N ranks emulated on one GPU (kernel sizes of an N-GPU run)")
     ap.add_argument("--ranks", type=int, default=8)
     ap.add_argument("--steps", type=int, default=4)
+    ap.add_argument("--mirror", action="store_true", help="ranks r and r + N/2 hold each other's experts and split their pairs")
     a = ap.parse_args()
-    _emulate(a.ranks, a.steps)
+    _emulate(a.ranks, a.steps, a.mirror)

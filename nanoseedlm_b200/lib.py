@@ -121,7 +121,7 @@ PROTOTYPES = {
     "nsl_ep_window_free": (_i, [_vp]),
     "nsl_ep_p2p_dispatch": (None, [_vp, NslEpWindow, _vp]),
     "nsl_ep_p2p_wait_dispatch": (None, [_vp, NslEpWindow]),
-    "nsl_ep_p2p_plan": (None, [_vp, NslEpWindow, C.c_uint64, C.c_uint64, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "nsl_ep_p2p_plan": (None, [_vp, NslEpWindow, C.c_uint64, C.c_uint64, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "nsl_ep_p2p_route_dispatch": (None, [_vp, NslEpWindow, _i, _i, _vp, _i, _vp, _i, C.c_uint64, C.c_uint64]),
     "nsl_ep_p2p_combine": (None, [_vp, NslEpWindow, _vp, _vp, _vp, _i]),
     "nsl_ep_p2p_reduce": (None, [_vp, NslEpWindow, _i, _vp]),

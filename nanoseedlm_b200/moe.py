@@ -83,6 +83,21 @@ class DeviceLayer:
         return cls(mk(h.gate, h.ff, h.d), mk(h.up, h.ff, h.d), mk(h.down, h.d, h.ff))
 
     @classmethod
+    def concat(cls, a, b):
+        """a's experts followed by b's (copies)."""
+        cat = lambda x, y: ExpertStack(torch.cat([x.seeds, y.seeds]), torch.cat([x.coefs, y.coefs]), torch.cat([x.codes, y.codes]),
+                                       x.eb + y.eb, x.R, x.K)
+        return cls(cat(a.gate, b.gate), cat(a.up, b.up), cat(a.down, b.down))
+
+    @classmethod
+    def from_host_ranges(cls, h, ranges):
+        """The host layer's experts of several [lo, hi) ranges, one after the other (a rank's own experts, then the
+        ones it mirrors)."""
+        pick = np.concatenate([np.arange(lo, hi) for lo, hi in ranges])
+        mk = lambda s, R, K: ExpertStack.from_host(s["seeds"][pick], s["coefs"][pick], s["codes"][pick], s["eb"][pick], R, K)
+        return cls(mk(h.gate, h.ff, h.d), mk(h.up, h.ff, h.d), mk(h.down, h.d, h.ff))
+
+    @classmethod
     def random_on_device(cls, d, ff, E, gen):
         return cls(ExpertStack.random_on_device(E, ff, d, gen), ExpertStack.random_on_device(E, ff, d, gen),
                    ExpertStack.random_on_device(E, d, ff, gen))

@@ -23,6 +23,9 @@ def main():
     lo, hi = rank * E // world, (rank + 1) * E // world
     mine = moe.DeviceLayer.from_host(h, lo, hi)
     p2p = ep.ExpertParallelMoe(ep.CudaBackend(mine), d, k, E, t_loc, collectives="p2p")
+    partner = (rank + world // 2) % world
+    both = moe.DeviceLayer.from_host_ranges(h, [(lo, hi), (partner * E // world, (partner + 1) * E // world)])
+    mir = ep.ExpertParallelMoe(ep.CudaBackend(both), d, k, E, t_loc, collectives="p2p", mirror=True) if world % 2 == 0 else None
     a2a = ep.ExpertParallelMoe(ep.CudaBackend(mine), d, k, E, t_loc, collectives="a2a")
     m = moe.Moe(moe.DeviceLayer.from_host(h), k, T)
     m.set_grouped_min_tokens(10 ** 6)
@@ -38,6 +41,10 @@ def main():
         assert torch.equal(o1, o2), f"rank {rank} step {step}: p2p and all-to-all results differ"
         ref = m.forward_host(x, logits)[0][sl]
         worst = max(worst, float(np.max(np.abs(o1.cpu().numpy() - ref)) / np.max(np.abs(ref))))
+        if mir is not None:      # mirrored pairs of ranks: another split of the same pairs, the same sums up to their order
+            o3 = mir.step(dx, dl).clone()
+            torch.cuda.synchronize()
+            worst = max(worst, float(np.max(np.abs(o3.cpu().numpy() - ref)) / np.max(np.abs(ref))))
     # the same steps replayed from CUDA graphs (two launches per step)
     stream = torch.cuda.Stream()
     x = oracle.normal(99, T * d, bf16=True).reshape(T, d)
@@ -53,10 +60,12 @@ def main():
             out = g.step(0, 0)
         stream.synchronize()
     assert torch.equal(out, want), f"rank {rank}: graphed p2p step differs"
-    status = p2p.window.status()
+    status = p2p.window.status() or (mir.window.status() if mir is not None else 0)
     lib.check()
     dist.barrier()
     p2p.window.close()
+    if mir is not None:
+        mir.window.close()
     assert status == 0, f"rank {rank}: a wait ran out (status {status})"
     assert worst <= 1e-5, worst
     if rank == 0:

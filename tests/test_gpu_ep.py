@@ -91,8 +91,8 @@ def test_p2p_exchange_single_rank_and_graphs(oracle):
     m.close()
 
 
-@pytest.mark.parametrize("fused", [False, True])
-def test_p2p_exchange_four_ranks_driven_from_one_stream(oracle, fused):
+@pytest.mark.parametrize("fused,mirror", [(False, False), (True, False), (True, True)])
+def test_p2p_exchange_four_ranks_driven_from_one_stream(oracle, fused, mirror):
     """Four ranks' windows in one process, their kernels issued on one stream with every rank's producers before any
     rank's consumers (so no kernel ever waits for a later one): dispatch slots, flags, epochs and the owner-indexed
     partial rows all line up with the plain MoE layer over the whole batch, for several steps."""
@@ -104,8 +104,10 @@ def test_p2p_exchange_four_ranks_driven_from_one_stream(oracle, fused):
     m = moe.Moe(moe.DeviceLayer.from_host(h), k, T)
     m.set_grouped_min_tokens(10 ** 6)
     wins = ep.P2PWindow.local_group(N, t_loc, d, k)
-    eps = [ep.ExpertParallelMoe(ep.CudaBackend(moe.DeviceLayer.from_host(h, r * E // N, (r + 1) * E // N)), d, k, E, t_loc,
-                                collectives="p2p", window=wins[r]) for r in range(N)]
+    rng = lambda r: (r * E // N, (r + 1) * E // N)
+    held = lambda r: [rng(r), rng((r + N // 2) % N)] if mirror else [rng(r)]     # mirrored: the partner's experts too
+    eps = [ep.ExpertParallelMoe(ep.CudaBackend(moe.DeviceLayer.from_host_ranges(h, held(r))), d, k, E, t_loc,
+                                collectives="p2p", window=wins[r], mirror=mirror) for r in range(N)]
     for step in range(3):
         x = oracle.normal(50 + step, T * d, bf16=True).reshape(T, d)
         logits = oracle.normal(60 + step, T * E).reshape(T, E)
@@ -124,6 +126,10 @@ def test_p2p_exchange_four_ranks_driven_from_one_stream(oracle, fused):
         torch.cuda.synchronize()
         out = np.concatenate([e.out.cpu().numpy() for e in eps])
         assert np.max(np.abs(out - ref)) <= 1e-5 * np.max(np.abs(ref))
+        counts = [int(e.be.count.item()) for e in eps]
+        assert sum(counts) == T * k
+        if mirror:      # a pair of ranks splits its joint list in the middle
+            assert all(0 <= counts[r] - counts[r + N // 2] <= 1 for r in range(N // 2))
     assert all(w.status() == 0 for w in wins)
     lib.check()
     for w in wins:
