@@ -511,6 +511,71 @@ def run_ep(args):
         dist.destroy_process_group()
 
 
+LM_V, LM_D = 151936, 2048   # the LM head of the reference's Qwen-class model (affine int4, groups of 64)
+
+
+def run_lmhead(args):
+    """Not the headline: the dense affine-int4 LM head (kc_mv with MF_Q4) + greedy arg-max, an HBM-bound kernel."""
+    import torch
+    from nanoseedlm_b200 import lib as L
+    lib = L.load()
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    T, K, W, NM = min(args.tokens, 8), args.steps, max(args.warmup, 3), 4
+    lib.nsl_q4_set_variant(int(os.environ.get("NSL_Q4_VARIANT", "1")))
+    gen = torch.Generator(device="cuda").manual_seed(77)
+    mats = []
+    for _ in range(NM):      # NM independent heads (0.7 GB), rotated so that every step reads HBM
+        codes = torch.randint(-2 ** 31, 2 ** 31 - 1, (LM_V, LM_D // 8), generator=gen, device="cuda", dtype=torch.int32)
+        sc = (torch.rand(LM_V, LM_D // 64, generator=gen, device="cuda") * 0.02 + 0.001).to(torch.bfloat16)
+        bi = (torch.rand(LM_V, LM_D // 64, generator=gen, device="cuda") * -0.2).to(torch.bfloat16)
+        w = L.WSlice()
+        w.p[0], w.p[1], w.p[2] = codes.data_ptr(), sc.data_ptr(), bi.data_ptr()
+        mats.append((w, codes, sc, bi))
+    x = torch.randn(T, LM_D, generator=gen, device="cuda").to(torch.bfloat16).float()
+    y = torch.zeros(T, LM_V, device="cuda")
+    tok = torch.zeros(T, dtype=torch.int32, device="cuda")
+    stream = torch.cuda.Stream()
+    s = C.c_void_p(stream.cuda_stream)
+
+    def step(i):
+        lib.kc_mv(s, L.MF_Q4, mats[i % NM][0], LM_D, LM_V, x.data_ptr(), LM_D, y.data_ptr(), LM_V, T, 0, None)
+        lib.kc_argmax(s, y.data_ptr(), tok.data_ptr(), LM_V, T)
+
+    with torch.cuda.stream(stream):
+        for i in range(W):
+            step(i)
+        stream.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(torch.cuda.current_device()) as clocks:
+            e0.record(stream)
+            for i in range(K):
+                step(W + i)
+            e1.record(stream)
+            e1.synchronize()
+        ms = e0.elapsed_time(e1) / K
+        evs = []
+        for i in range(min(K, 50)):
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record(stream)
+            lib.kc_mv(s, L.MF_Q4, mats[i % NM][0], LM_D, LM_V, x.data_ptr(), LM_D, y.data_ptr(), LM_V, T, 0, None)
+            a1.record(stream)
+            evs.append((a0, a1))
+        stream.synchronize()
+        mv_us = sum(a.elapsed_time(b) for a, b in evs) / len(evs) * 1e3
+    L.check()
+    peaks, kind = measured_peaks()
+    nbytes = LM_V * LM_D // 2 + 2 * LM_V * (LM_D // 64) * 2 + T * LM_D * 4 + T * LM_V * 4
+    gbs = nbytes / (mv_us * 1e-6) / 1e9
+    print(json.dumps({"metric": "lm_head_q4_tokens_per_s", "value": T / (ms * 1e-3), "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W,
+                      "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 x int4 -> f32",
+                      "data": "synthetic", "gpu_launches": 2 * K, "clocks": clocks.summary(),
+                      "config": {"workload": f"dense affine-int4 LM head {LM_V} x {LM_D} (groups of 64) + greedy arg-max, {T} tokens; "
+                                             f"{NM} heads rotated (0.7 GB) so that every step reads HBM", "tokens": T},
+                      "roofline": {"bound": "hbm", "kernel": "q4_mv_kernel (kc_mv, MF_Q4)", "achieved": gbs, "peak": peaks["hbm_gbs"],
+                                   "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"], "peak_kind": kind, "traffic": None,
+                                   "us_per_launch": mv_us, "bytes_per_launch": nbytes}}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -529,7 +594,7 @@ def main():
     ap.add_argument("--ep-mirror", type=int, default=0,
                     help="config 3, p2p, even rank counts: 1 = ranks r and r + N/2 hold each other's experts too and split their "
                          "joint pairs in the middle (balance to within one pair; twice the expert bytes per GPU)")
-    ap.add_argument("--workload", default=None, choices=["cfg1", "cfg2", "cfg3"],
+    ap.add_argument("--workload", default=None, choices=["cfg1", "cfg2", "cfg3", "lmhead"],
                     help="cfg1: one GPU's MoE decode layer (default at 1 GPU); cfg2: the same layer on 512 prompt rows (grouped "
                          "tcgen05 GEMM); cfg3: expert-parallel decode (default at >1 GPU)")
     args = ap.parse_args()
@@ -546,7 +611,9 @@ def main():
         args.tokens = 512 if workload == "cfg2" else 8
     if workload == "cfg1" and not 1 <= args.tokens <= 8:
         raise SystemExit("config 1 is the decode / verify batch: --tokens 1..8 (use --workload cfg2 for prompt rows)")
-    if workload == "cfg3":
+    if workload == "lmhead":
+        run_lmhead(args)
+    elif workload == "cfg3":
         run_ep(args)
     else:
         run_ours(args)

@@ -10,8 +10,8 @@
  * Conventions (engine/kernels_cuda.h:1-7; engine/qwen4_cuda.c:1219-1234): the first argument is the stream; calls
  * are asynchronous launches that return void and allocate nothing; the caller owns every buffer; errors surface at the
  * caller's cudaStreamSynchronize + cudaGetLastError.  Activations are f32 arrays of bf16-rounded values; xs / ys are
- * row strides in floats.  Only the SEED4P4 weight format (MF_SEED4P4) is implemented: a call with another format
- * launches nothing and records an error that nsl_last_error() returns. */
+ * row strides in floats.  The SEED4P4 weight format (MF_SEED4P4) is implemented everywhere, MF_Q4 in the dense kc_mv:
+ * a call with another format launches nothing and records an error that nsl_last_error() returns. */
 #pragma once
 #include <stddef.h>
 #include <stdint.h>
@@ -67,7 +67,10 @@ typedef struct {
 
 /* ---- mat-vec (decode and multi-token verify, T <= MV_MAXT) ---------------------------------------------------------- */
 /* engine/kernels_cuda.h:79  y[t][r] = bf16(W[r] . x[t]); add = 1: y = bf16(y + bf16(acc)).  G: the 65536-entry
- * lfsr_stream32 table in device memory.  A token's result does not depend on T. */
+ * lfsr_stream32 table in device memory.  A token's result does not depend on T.
+ * fmt = MF_Q4 (the LM head, engine/kernels_moe.cu:171-189) is served too: p[0] codes u32 [R][K/8] (value i of a word in
+ * bits 4i..4i+3), p[1] / p[2] bf16 scales / biases per group of 64 weights (gs 0 or 6), weight = s q + b; K a multiple of
+ * 64; activations must be bf16-valued (as every activation of the engine is): they enter the tensor cores as bf16. */
 void kc_mv(cudaStream_t s, int fmt, WSlice w, int K, int R, const float* x, int xs, float* y, int ys, int T, int add,
            const uint32_t* G);
 /* engine/kernels_cuda.h:82  pair p uses slice sel[p], input row p / xdiv, output row p. */
@@ -146,6 +149,16 @@ void kc_heads_mv(cudaStream_t s, HmvArgs a, int fmt, WSlice W, const uint32_t* G
 /* engine/kernels_cuda.h:145  the stacked matrix decoded to BF16 [H][O][I], each weight the exact f32 weight rounded to
  * nearest even (what the GEMM feeds the tensor cores). */
 void kc_heads_deq(cudaStream_t s, int fmt, WSlice W, const uint32_t* G, int H, int O, int I, uint16_t* out);
+
+/* ---- greedy decoding over the LM head's logits ------------------------------------------------------------------------ */
+/* engine/kernels_cuda.h:177-178  out[i] = arg max of row i of logits [n][V] (ties: the lowest id); prob[i] (optional) =
+ * its softmax probability. */
+void kc_argmax(cudaStream_t s, const float* logits, int32_t* out, int V, int n);
+void kc_argmax_p(cudaStream_t s, const float* logits, int32_t* out, float* prob, int V, int n);
+/* No counterpart in the reference: picks between the two shapes of the Q4 mat-vec's prefetch ring where both fit
+ * (1, the default: 8 warps per SM with three passes of eight groups in flight; 0: 16 warps with three passes of four).
+ * Results are identical; for timing. */
+void nsl_q4_set_variant(int v);
 
 /* ---- expert cache -------------------------------------------------------------------------------------------------- */
 /* engine/kernels_cuda.h:53  LRU admit of the units selected by inds[count] of sparse layer sl. */

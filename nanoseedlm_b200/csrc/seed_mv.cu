@@ -766,6 +766,8 @@ static void launch_mv(cudaStream_t s, const MvParams& a, int T, int p_hint = 0) 
     count_launch();
 }
 
+bool launch_q4_mv(cudaStream_t s, const WSlice& w, int K, int R, const float* x, int xs, float* y, int ys, int T, int add);
+
 static bool seed_fmt(int fmt, const char* who) {
     if (fmt == MF_SEED4P4) return true;
     set_error("%s: weight format %d is not served by this library (SEED4P4 = %d only)", who, fmt, (int) MF_SEED4P4);
@@ -780,6 +782,7 @@ extern "C" {
 
 void kc_mv(cudaStream_t s, int fmt, WSlice w, int K, int R, const float* x, int xs, float* y, int ys, int T, int add,
            const uint32_t* G) {
+    if (fmt == MF_Q4) { launch_q4_mv(s, w, K, R, x, xs, y, ys, T, add); return; }   // the LM head's affine int4 (q4_head.cu)
     if (!seed_fmt(fmt, "kc_mv")) return;
     MvParams a = {NULL, NULL, w, NULL, x, y, G, K, R, T, 1, xs, ys, add, 0, NULL, NULL, 0, NULL, NULL};
     launch_mv<MODE_ROUND>(s, a, T);

@@ -186,6 +186,30 @@ def kt_mv_gu_units(wg, wu, sel, xdiv, x, xrow=None, bf16=False):
     return ad.cpu().numpy()
 
 
+def kt_mv_q4(codes, scales, biases, x, T, add=0, y0=None):
+    """kc_mv with fmt MF_Q4 (the LM head): codes u32 [R][K/8], scales / biases bf16 bits per group of 64."""
+    codes = np.ascontiguousarray(codes, np.uint32)
+    R, K = codes.shape[0], codes.shape[1] * 8
+    keep = [dev(codes), dev(np.asarray(scales, np.uint16)), dev(np.asarray(biases, np.uint16))]
+    w = L.WSlice()
+    w.p[0], w.p[1], w.p[2] = (t.data_ptr() for t in keep)
+    xd = dev(np.asarray(x, np.float32).reshape(T, K))
+    yd = dev(np.asarray(y0, np.float32).reshape(T, R)) if y0 is not None else torch.zeros(T, R, device="cuda")
+    L.load().kc_mv(_stream(), L.MF_Q4, w, K, R, _ptr(xd), K, _ptr(yd), R, T, add, None)
+    _done()
+    return yd.cpu().numpy()
+
+
+def kt_argmax(logits, prob=False):
+    ld = dev(np.asarray(logits, np.float32))
+    n, V = ld.shape
+    out = torch.zeros(n, dtype=torch.int32, device="cuda")
+    pr = torch.zeros(n, device="cuda") if prob else None
+    L.load().kc_argmax_p(_stream(), _ptr(ld), _ptr(out), _ptr(pr), V, n)
+    _done()
+    return (out.cpu().numpy(), pr.cpu().numpy()) if prob else out.cpu().numpy()
+
+
 def kt_route(logits, k):
     logits = np.asarray(logits, np.float32)
     T, E = logits.shape

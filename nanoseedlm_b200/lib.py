@@ -9,6 +9,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libnslm_b200.so")
 
 MF_SEED4P4 = 4
+MF_Q4 = 3
 MV_MAXT = 8
 MMT_BN = 128
 MMT_BM = 64
@@ -73,6 +74,9 @@ PROTOTYPES = {
     "kc_router_topk": (None, [_vp, RouterArgs, _vp, _vp, _vp, _vp, _i]),
     "kc_heads_mv": (None, [_vp, HmvArgs, _i, WSlice, _vp, _vp, _vp, _vp, _i]),
     "kc_heads_deq": (None, [_vp, _i, WSlice, _vp, _i, _i, _i, _vp]),
+    "nsl_q4_set_variant": (None, [_i]),
+    "kc_argmax": (None, [_vp, _vp, _vp, _i, _i]),
+    "kc_argmax_p": (None, [_vp, _vp, _vp, _vp, _i, _i]),
     "kc_cache_admit": (None, [_vp, C.POINTER(CachePool), _i, _vp, _i, _i]),
     "kc_cache_copy": (None, [_vp, C.POINTER(CachePool), _i]),
     "nsl_bucket_noalloc": (None, [_vp, _vp, _i, _i, _vp, _vp, _vp]),

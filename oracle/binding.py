@@ -333,3 +333,28 @@ def tiled_jobs(jobs, threads):
     if lib().orc_cpu_seed4_tiled_jobs(arr, len(jobs), _p(table32(), u32), threads):
         raise ValueError("a job has no matrix or more than 8 tokens")
     return ys
+
+
+def q4_mv(codes, scales, biases, x, add=0, y0=None):
+    """The LM head's affine int4 mat-vec: codes u32 [R][K/8], scales / biases bf16 bits [R][K/64], x [T][K] ->
+    (y [T][R] bf16-rounded, mag [T][R] = sum |w x|)."""
+    codes = np.ascontiguousarray(codes, np.uint32)
+    R, K = codes.shape[0], codes.shape[1] * 8
+    x = np.ascontiguousarray(x, np.float32).reshape(-1, K)
+    T = x.shape[0]
+    y = np.zeros((T, R), np.float32) if y0 is None else np.array(y0, np.float32).reshape(T, R).copy()
+    mag = np.zeros((T, R), np.float64)
+    s, b = np.ascontiguousarray(scales, np.uint16), np.ascontiguousarray(biases, np.uint16)
+    lib().orc_q4_mv(codes.ctypes.data_as(C.c_void_p), s.ctypes.data_as(C.c_void_p), b.ctypes.data_as(C.c_void_p), K, R,
+                    x.ctypes.data_as(C.c_void_p), T, int(add), y.ctypes.data_as(C.c_void_p), mag.ctypes.data_as(C.c_void_p))
+    return y, mag
+
+
+def argmax(logits):
+    logits = np.ascontiguousarray(logits, np.float32)
+    n, V = logits.shape
+    out, prob = np.zeros(n, np.int32), np.zeros(n, np.float64)
+    for i in range(n):
+        lib().orc_argmax(logits[i].ctypes.data_as(C.c_void_p), V, out[i:].ctypes.data_as(C.c_void_p),
+                         prob[i:].ctypes.data_as(C.c_void_p))
+    return out, prob

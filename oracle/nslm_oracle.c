@@ -377,6 +377,41 @@ void orc_moe_layer(const OrcMoe* m, const float* x, const float* logits, int T, 
 }
 
 /* ------------------------------------------------------------------------------------------------------------------
+ * The affine int4 dense mat-vec of the LM head, in the form the reference's kernel test states it
+ * (tests/test_mova_kernels.c:146-157, 181-199): weight (r, c) = bf16 scale[(r K + c) / 64] * code + bf16 bias[same group],
+ * code = bits 4 (i % 8) .. of word i / 8; y = bf16(sum in double), or with add bf16(y0 + bf16(sum)).  mag (optional) gets
+ * sum |w x| per output for the f32-accumulation bound. */
+void orc_q4_mv(const uint32_t* codes, const uint16_t* scales, const uint16_t* biases, int K, int R, const float* x, int T,
+               int add, float* y, double* mag) {
+    for (int t = 0; t < T; ++t)
+        for (int r = 0; r < R; ++r) {
+            double acc = 0, m = 0;
+            for (int c = 0; c < K; ++c) {
+                const size_t i = (size_t) r * K + c;
+                const double w = (double) orc_bf2f(scales[i / 64]) * (double) ((codes[i / 8] >> (4 * (i % 8))) & 15u) +
+                                 (double) orc_bf2f(biases[i / 64]);
+                const double v = w * (double) x[(size_t) t * K + c];
+                acc += v;
+                m += fabs(v);
+            }
+            float* yo = y + (size_t) t * R + r;
+            *yo = add ? orc_bfr(*yo + orc_bfr((float) acc)) : orc_bfr((float) acc);
+            if (mag) mag[(size_t) t * R + r] = m;
+        }
+}
+
+/* Greedy arg-max (ties: the lowest id) and the softmax probability of the winner (engine/kernels_moe.cu:2115-2151). */
+void orc_argmax(const float* logits, int V, int32_t* out, double* prob) {
+    int best = 0;
+    for (int i = 1; i < V; ++i)
+        if (logits[i] > logits[best]) best = i;
+    double tot = 0;
+    for (int i = 0; i < V; ++i) tot += exp((double) logits[i] - (double) logits[best]);
+    *out = best;
+    if (prob) *prob = 1.0 / tot;
+}
+
+/* ------------------------------------------------------------------------------------------------------------------
  * Seeded inputs: splitmix64 (the reference's nslm/rng.h:7-14 uses the same public generator), seeds in [1,65535],
  * coefficient words = 16 random bits (four int4 in [-8,7]), codes in [0,15] two per byte, low nibble first. */
 uint64_t orc_splitmix64(uint64_t* state) {

@@ -141,9 +141,9 @@ def test_other_formats_are_refused_loudly(oracle):
     mats, w = weights(oracle, 1, 8, 64, 2)
     x = torch.zeros(64, device="cuda")
     y = torch.zeros(8, device="cuda")
-    lib.load().kc_mv(None, 3, w.slice(0), 64, 8, C.c_void_p(x.data_ptr()), 64, C.c_void_p(y.data_ptr()), 8, 1, 0,
-                     C.c_void_p(kernels.stream_table().data_ptr()))
-    assert "format 3" in lib.last_error()
+    lib.load().kc_mv(None, 2, w.slice(0), 64, 8, C.c_void_p(x.data_ptr()), 64, C.c_void_p(y.data_ptr()), 8, 1, 0,
+                     C.c_void_p(kernels.stream_table().data_ptr()))      # 2 = MF_Q8
+    assert "format 2" in lib.last_error()
 
 
 def test_register_and_shared_memory_variants_are_bit_identical(oracle):

@@ -169,3 +169,22 @@ def test_mova_topk_ties_go_to_the_lowest_id(oracle):
     assert np.allclose(wt[0], 0.4)
     g = oracle.softplus_gate(np.array([0.0, 3.0, -3.0], np.float32))
     assert g[0] == 1.0 and g[1] > 3.0 and 0 < g[2] < 0.2   # softplus with beta ln 2: 1 at 0, ~x for large x
+
+
+def test_q4_reference_form(oracle):
+    """The oracle's affine int4 mat-vec against a direct numpy statement of weight = s q + b per group of 64."""
+    rng = np.random.default_rng(5)
+    R, K, T = 6, 128, 2
+    codes = rng.integers(0, 2 ** 32, (R, K // 8), dtype=np.uint64).astype(np.uint32)
+    s = oracle.f2bf(rng.random((R, K // 64), np.float32) * 0.02 + 0.001)
+    b = oracle.f2bf(rng.random((R, K // 64), np.float32) * -0.2)
+    x = rng.standard_normal((T, K)).astype(np.float32)
+    q = ((codes[:, :, None] >> (4 * np.arange(8, dtype=np.uint32))) & 15).reshape(R, K).astype(np.float64)
+    tof = lambda h: (h.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+    w = np.repeat(tof(s), 64, axis=1) * q + np.repeat(tof(b), 64, axis=1)
+    want = x.astype(np.float64) @ w.T
+    y, mag = oracle.q4_mv(codes, s, b, x)
+    assert np.all(np.abs(y - want) <= np.abs(want) / 128 + 1e-12)       # the oracle rounds to bf16
+    assert np.allclose(mag, np.abs(x.astype(np.float64)) @ np.abs(w.T))
+    out, prob = oracle.argmax(np.array([[0.0, 2.0, 2.0, -1.0]], np.float32))
+    assert out[0] == 1 and abs(prob[0] - 1 / (2 + np.exp(-2) + np.exp(-3))) < 1e-12
