@@ -155,9 +155,10 @@ void kc_heads_deq(cudaStream_t s, int fmt, WSlice W, const uint32_t* G, int H, i
  * its softmax probability. */
 void kc_argmax(cudaStream_t s, const float* logits, int32_t* out, int V, int n);
 void kc_argmax_p(cudaStream_t s, const float* logits, int32_t* out, float* prob, int V, int n);
-/* No counterpart in the reference: picks between the two shapes of the Q4 mat-vec's prefetch ring where both fit
- * (1, the default: 8 warps per SM with three passes of eight groups in flight; 0: 16 warps with three passes of four).
- * Results are identical; for timing. */
+/* No counterpart in the reference: picks the form of the Q4 mat-vec where several fit (results within the same bound;
+ * for timing): 1, the default: K split over a block's warps, the inputs' fragments in registers (K = 1024, 2048, 4096),
+ * else as 2; 2: every warp walks all of K through a ring of eight-group passes, 8 warps per SM; 0: the same with four-
+ * group passes and 16 warps per SM. */
 void nsl_q4_set_variant(int v);
 
 /* ---- expert cache -------------------------------------------------------------------------------------------------- */

@@ -302,6 +302,160 @@ __global__ void __launch_bounds__(32 * WARPS, 1) q4_mv_ring_kernel(const uint32_
     asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
 
+// The ring kernel is bound by the shared-memory pipe (ncu: l1tex 87 % busy, DRAM 34 %): per 16-row tile it moves 72 KB
+// through shared memory, 32 KB of it the inputs' MMA fragments that every warp re-reads for every tile.  Here the K
+// dimension is split over the block's warps instead: warp w owns groups 4 w .. 4 w + 3 for EVERY tile of its block,
+// so its 32 fragment registers and 8 input sums are loaded once and stay in registers; per tile a warp streams
+// 16 rows x 128 bytes of codes (+ 8 scales, 8 biases per row) through its cp.async ring, runs 16 MMAs, and the warps'
+// partial sums meet in shared memory (8 KB per tile), where they are added in warp order.  K = 256 x WARPS.
+template <int WARPS, int NST>
+__global__ void __launch_bounds__(32 * WARPS, 1) q4_mv_ksplit_kernel(const uint32_t* __restrict__ codes, const uint16_t* __restrict__ S,
+                                                                     const uint16_t* __restrict__ B, int K, int R,
+                                                                     const float* __restrict__ x, int xs, float* __restrict__ y,
+                                                                     int ys, int T, int add) {
+    constexpr int ROW = Q4Ring<4>::ROW, STAGE = Q4Ring<4>::STAGE;
+    extern __shared__ __align__(16) uint32_t q4_smem[];
+    const int G = K / Q4_GROUP;      // = 4 * WARPS
+    uint32_t* xb = q4_smem;
+    float* xsum = (float*) (q4_smem + (size_t) G * 256);
+    float* part = xsum + G * 8;                                                  // [2][WARPS][32][4]
+    unsigned char* ring = (unsigned char*) (part + 2 * WARPS * 128) + (size_t) (threadIdx.x >> 5) * NST * STAGE;
+    grid_dependents_go();
+    grid_dependency_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, q = lane & 3, rr = lane >> 2;
+    const int tiles = (R + 15) / 16;
+    const int my_tiles = (int) blockIdx.x < tiles ? (tiles - (int) blockIdx.x + (int) gridDim.x - 1) / (int) gridDim.x : 0;
+
+    auto issue = [&](int idx) {      // tile number idx of this block: this warp's 128-byte slice of its 16 rows
+        if (idx < my_tiles) {
+            const int tile = blockIdx.x + idx * gridDim.x;
+            unsigned char* st = ring + (size_t) (idx % NST) * STAGE;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int lr = 4 * i + (lane >> 3), piece = lane & 7, row = min(tile * 16 + lr, R - 1);
+                cp_async16(st + lr * ROW + piece * 16, (const unsigned char*) (codes + (size_t) row * (K / 8) + warp * 32) + piece * 16);
+            }
+            const int lr = lane & 15, row = min(tile * 16 + lr, R - 1);
+            cp_async8(st + lr * ROW + 128 + (lane >> 4) * 8, (lane >> 4 ? B : S) + (size_t) row * G + warp * 4);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+#pragma unroll
+    for (int i = 0; i < NST - 1; ++i) issue(i);
+
+    const bool vec = (xs & 3) == 0 && aligned16_dev(x);
+    for (int i = threadIdx.x; i < G * 32; i += 32 * WARPS) {
+        const int g = i >> 5, sq = (i >> 3) & 3, n = i & 7;
+        uint32_t* dst = xb + (size_t) i * 8;
+        float v[16];
+        if (n < T) {
+            const float* xp = x + (size_t) n * xs + g * 64 + sq * 16;
+            if (vec) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float4 t = __ldg((const float4*) xp + j);
+                    v[4 * j] = t.x; v[4 * j + 1] = t.y; v[4 * j + 2] = t.z; v[4 * j + 3] = t.w;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] = __ldg(xp + j);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+        }
+        float psum = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) { v[j] = bf16_round(v[j]); psum += v[j]; }
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+            dst[2 * m] = bf16_bits(v[m]) | ((uint32_t) bf16_bits(v[m + 4]) << 16);
+            dst[2 * m + 1] = bf16_bits(v[8 + m]) | ((uint32_t) bf16_bits(v[12 + m]) << 16);
+        }
+        psum += __shfl_xor_sync(0xFFFFFFFFu, psum, 8);
+        psum += __shfl_xor_sync(0xFFFFFFFFu, psum, 16);
+        if (sq == 0) xsum[g * 8 + n] = psum;
+    }
+    __syncthreads();
+    // this warp's four groups of inputs: fragments and sums, in registers for the whole kernel
+    uint32_t breg[4][8];
+    float xg[4][2];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int g = warp * 4 + j;
+        const uint4 lo = *(const uint4*) (xb + ((size_t) (g * 4 + q) * 8 + rr) * 8), hi = *(const uint4*) (xb + ((size_t) (g * 4 + q) * 8 + rr) * 8 + 4);
+        breg[j][0] = lo.x; breg[j][1] = lo.y; breg[j][2] = lo.z; breg[j][3] = lo.w;
+        breg[j][4] = hi.x; breg[j][5] = hi.y; breg[j][6] = hi.z; breg[j][7] = hi.w;
+        xg[j][0] = xsum[g * 8 + 2 * q];
+        xg[j][1] = xsum[g * 8 + 2 * q + 1];
+    }
+
+    for (int idx = 0; idx < my_tiles; ++idx) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(NST - 2) : "memory");
+        __syncwarp();
+        const int tile = blockIdx.x + idx * gridDim.x;
+        const unsigned char* st = ring + (size_t) (idx % NST) * STAGE;
+        const unsigned char* row0 = st + rr * ROW, *row1 = st + (rr + 8) * ROW;
+        const uint4 t0 = *(const uint4*) (row0 + 128), t2 = *(const uint4*) (row1 + 128);      // {4 scales, 4 biases}
+        const uint32_t sa0[2] = {t0.x, t0.y}, ba0[2] = {t0.z, t0.w}, sa1[2] = {t2.x, t2.y}, ba1[2] = {t2.z, t2.w};
+        float out[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int sh = (j & 1) * 16;
+            const uint2 w0 = *(const uint2*) (row0 + j * 32 + q * 8), w1 = *(const uint2*) (row1 + j * 32 + q * 8);
+            uint32_t a0[8], a1[8];
+            unpack8(w0.x, a0); unpack8(w0.y, a0 + 4);
+            unpack8(w1.x, a1); unpack8(w1.y, a1 + 4);
+            float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            const uint32_t f0[4] = {a0[0], a1[0], a0[4], a1[4]}, f1[4] = {a0[1], a1[1], a0[5], a1[5]};
+            const uint32_t f2[4] = {a0[2], a1[2], a0[6], a1[6]}, f3[4] = {a0[3], a1[3], a0[7], a1[7]};
+            mma_bf16_16x8x16(c, f0, breg[j][0], breg[j][1]);
+            mma_bf16_16x8x16(c, f1, breg[j][2], breg[j][3]);
+            mma_bf16_16x8x16(c, f2, breg[j][4], breg[j][5]);
+            mma_bf16_16x8x16(c, f3, breg[j][6], breg[j][7]);
+            const float s0 = bf16_to_f32((uint16_t) (sa0[j >> 1] >> sh)), s1 = bf16_to_f32((uint16_t) (sa1[j >> 1] >> sh));
+            const float e0 = fmaf(8.0f, s0, bf16_to_f32((uint16_t) (ba0[j >> 1] >> sh)));
+            const float e1 = fmaf(8.0f, s1, bf16_to_f32((uint16_t) (ba1[j >> 1] >> sh)));
+            out[0] += fmaf(s0, c[0], e0 * xg[j][0]);
+            out[1] += fmaf(s0, c[1], e0 * xg[j][1]);
+            out[2] += fmaf(s1, c[2], e1 * xg[j][0]);
+            out[3] += fmaf(s1, c[3], e1 * xg[j][1]);
+        }
+        __syncwarp();
+        issue(idx + NST - 1);
+        float* pb = part + (size_t) (idx & 1) * WARPS * 128;
+        *(float4*) (pb + (warp * 32 + lane) * 4) = make_float4(out[0], out[1], out[2], out[3]);
+        __syncthreads();      // the block's partial sums of this tile are in; the other buffer is free for the next tile
+        // the tile's 128 outputs (32 lane slots x 4) are shared out over the warps; each is the warps' sum in warp order
+        for (int e = warp * 32 + lane; e < 128; e += 32 * WARPS) {
+            float acc = pb[e];
+#pragma unroll
+            for (int w = 1; w < WARPS; ++w) acc += pb[w * 128 + e];
+            const int sl = e >> 2, i = e & 3;      // the lane slot (rr, q) and its output i
+            const int row = tile * 16 + (sl >> 2) + (i >> 1) * 8, t = 2 * (sl & 3) + (i & 1);
+            if (row < R && t < T) {
+                float* yo = y + (size_t) t * ys + row;
+                *yo = add ? bf16_round(*yo + bf16_round(acc)) : bf16_round(acc);
+            }
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
+template <int WARPS, int NST>
+static void launch_q4_ksplit(cudaStream_t s, size_t total, int blocks, const WSlice& w, int K, int R, const float* x, int xs, float* y,
+                             int ys, int T, int add) {
+    static bool attr_set[16];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_set[dev & 15]) {
+        cudaFuncSetAttribute(q4_mv_ksplit_kernel<WARPS, NST>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin() - 1024);
+        attr_set[dev & 15] = true;
+    }
+    launch(q4_mv_ksplit_kernel<WARPS, NST>, (unsigned) blocks, 32 * WARPS, total, s, (const uint32_t*) w.p[0], (const uint16_t*) w.p[1],
+           (const uint16_t*) w.p[2], K, R, x, xs, y, ys, T, add);
+}
+
 template <int NST, int WARPS, int GPP>
 static void launch_q4_ring(cudaStream_t s, size_t total, int blocks, const WSlice& w, int K, int R, const float* x, int xs, float* y,
                            int ys, int T, int add) {
@@ -361,7 +515,8 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
     }
 }
 
-static int g_q4_variant = 1;   // 1 (default): 8 warps x 4 stages of 8 groups; 0: 16 warps x 4 stages of 4 groups (when it fits)
+static int g_q4_variant = 1;   // 1 (default): K split over the warps where K allows, else the ring with 8 warps; 2: the ring with
+                               // 8 warps x 4 stages of 8 groups; 0: the ring with 16 warps x 4 stages of 4 groups
 
 // Called by kc_mv for fmt == MF_Q4.  Returns false (with the error recorded) when the shape is not served.
 bool launch_q4_mv(cudaStream_t s, const WSlice& w, int K, int R, const float* x, int xs, float* y, int ys, int T, int add) {
@@ -383,10 +538,22 @@ bool launch_q4_mv(cudaStream_t s, const WSlice& w, int K, int R, const float* x,
         attr_set[dev & 15] = true;
     }
     const size_t budget = (size_t) max_smem_optin() - 1024;
+    if (g_q4_variant == 1 && aligned16(w.p[0]) && (K == 1024 || K == 2048 || K == 4096)) {      // K split over the block's warps
+        const int warps = K / 256, nst = warps == 16 ? 3 : 6;      // stages per warp: what fits beside 16 warps' rings
+        const size_t total = smem + (size_t) 2 * warps * 512 + (size_t) warps * nst * Q4Ring<4>::STAGE;
+        if (total <= budget) {
+            const int blocks = tiles < sm_count() ? tiles : sm_count();
+            if (warps == 4) launch_q4_ksplit<4, 6>(s, total, blocks, w, K, R, x, xs, y, ys, T, add);
+            else if (warps == 8) launch_q4_ksplit<8, 6>(s, total, blocks, w, K, R, x, xs, y, ys, T, add);
+            else launch_q4_ksplit<16, 3>(s, total, blocks, w, K, R, x, xs, y, ys, T, add);
+            count_launch();
+            return true;
+        }
+    }
     if (K % 512 == 0 && aligned16(w.p[0]) && smem + (size_t) 8 * 2 * Q4Ring<8>::STAGE <= budget) {      // streams through shared memory
         // 8 warps with three passes of eight groups in flight each (measured faster than 16 warps with three passes of four:
         // 66.9 against 77.2 us on the 151936 x 2048 head), or 8 warps with one pass in flight when shared memory is short
-        const int variant = smem + (size_t) 16 * 4 * Q4Ring<4>::STAGE <= budget ? g_q4_variant
+        const int variant = smem + (size_t) 16 * 4 * Q4Ring<4>::STAGE <= budget ? (g_q4_variant == 0 ? 0 : 1)
                           : smem + (size_t) 8 * 4 * Q4Ring<8>::STAGE <= budget ? 1 : 2;
         const int warps = variant == 0 ? 16 : 8;
         int blocks = (tiles + warps - 1) / warps;
@@ -425,6 +592,6 @@ void kc_argmax_p(cudaStream_t s, const float* logits, int32_t* out, float* prob,
 void kc_argmax(cudaStream_t s, const float* logits, int32_t* out, int V, int n) { kc_argmax_p(s, logits, out, NULL, V, n); }
 
 // Picks between the two ring shapes of the Q4 mat-vec where both fit (1, the default: 8 warps; 0: 16 warps): for timing.
-void nsl_q4_set_variant(int v) { g_q4_variant = v ? 1 : 0; }
+void nsl_q4_set_variant(int v) { g_q4_variant = v < 0 || v > 2 ? 1 : v; }
 
 }   // extern "C"
