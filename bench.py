@@ -503,9 +503,17 @@ def run_ep(args):
                 "clocks": clocks.summary(),
                 "e2e": {"value": EP_B / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": t_loc * D * 4 + t_loc * EP_E * 4,
                         "d2h_bytes_per_step": t_loc * D * 4, "ms_per_step": e2e_s * 1e3},
-                "roofline": {"bound": "hbm", "kernel": "mv_shx_kernel<gate+up> over this rank's pairs", "achieved": None,
-                             "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": None, "peak_kind": peak_kind, "traffic": None,
-                             "note": "per-kernel roofline is reported by the 1-GPU config-1 line; this line is the end-to-end step"}}
+                "roofline": None}
+        # the whole step against the packed-bytes roofline: the experts a step touches, in expectation over the routing
+        # (E (1 - (1 - k/E)^B) distinct experts of 3 matrices each), read once by whichever rank owns them
+        distinct = EP_E * (1.0 - (1.0 - EP_K / EP_E) ** EP_B)
+        step_bytes = distinct * 3 * BYTES_PER_MATRIX
+        gbs = step_bytes / (ms_per_step * 1e-3) / 1e9
+        line["roofline"] = {"bound": "hbm", "kernel": "the step's seed mat-vecs (mv_shx_kernel: gate+up and down over the ranks' pairs)",
+                            "achieved": gbs, "peak": peaks["hbm_gbs"] * world, "unit": "GB/s", "frac": gbs / (peaks["hbm_gbs"] * world),
+                            "peak_kind": peak_kind, "traffic": None, "expected_distinct_experts": distinct,
+                            "note": "whole step (mat-vecs + exchange) over the aggregate HBM peak of the ranks; the kernels are bound by "
+                                    "the logic pipe, see the 1-GPU config-1 line for the per-kernel roofline"}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

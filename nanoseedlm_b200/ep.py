@@ -296,16 +296,18 @@ class CudaBackend:
                             lay["rows"], ep.lo, ep.hi, *out)
         P = T * ep.k
         lib.nsl_dependent_launch(1)   # the three kernels after the plan come in while their predecessor drains
-        lib.nsl_mv_gu_rows(s, lyr.gate.table.data_ptr(), lyr.up.table.data_ptr(), lyr.d, lyr.ff, base, ep.d, 1,
-                           self.A.data_ptr(), lyr.ff, self.sel.data_ptr(), self.xrow.data_ptr(), P, self.count.data_ptr(),
-                           self.expected_pairs, self.G.data_ptr())
-        lib.nsl_mv_sel_rows(s, lyr.down.table.data_ptr(), lyr.ff, lyr.d, self.A.data_ptr(), lyr.ff, self.D.data_ptr(), lyr.d,
-                            self.sel.data_ptr(), P, self.count.data_ptr(), self.expected_pairs, self.G.data_ptr())
-        if p2p:
-            lib.nsl_ep_p2p_combine(s, ep.win, self.D.data_ptr(), self.wsel.data_ptr(), self.tok_off.data_ptr(), ep.d)
-        else:
-            lib.nsl_ep_combine(s, self.D.data_ptr(), self.wsel.data_ptr(), self.tok_off.data_ptr(), T, ep.d, ep.partial.data_ptr())
-        lib.nsl_dependent_launch(0)
+        try:
+            lib.nsl_mv_gu_rows(s, lyr.gate.table.data_ptr(), lyr.up.table.data_ptr(), lyr.d, lyr.ff, base, ep.d, 1,
+                               self.A.data_ptr(), lyr.ff, self.sel.data_ptr(), self.xrow.data_ptr(), P, self.count.data_ptr(),
+                               self.expected_pairs, self.G.data_ptr())
+            lib.nsl_mv_sel_rows(s, lyr.down.table.data_ptr(), lyr.ff, lyr.d, self.A.data_ptr(), lyr.ff, self.D.data_ptr(), lyr.d,
+                                self.sel.data_ptr(), P, self.count.data_ptr(), self.expected_pairs, self.G.data_ptr())
+            if p2p:
+                lib.nsl_ep_p2p_combine(s, ep.win, self.D.data_ptr(), self.wsel.data_ptr(), self.tok_off.data_ptr(), ep.d)
+            else:
+                lib.nsl_ep_combine(s, self.D.data_ptr(), self.wsel.data_ptr(), self.tok_off.data_ptr(), T, ep.d, ep.partial.data_ptr())
+        finally:
+            lib.nsl_dependent_launch(0)
 
     def p2p_dispatch(self, ep):
         """The chunk route_and_pack left in send[0] -> every rank's window."""
