@@ -113,6 +113,11 @@ PROTOTYPES = {
     "nsl_moe_stream": (_vp, [_vp]),
     "nsl_moe_set_rounding": (None, [_vp, _i]),
     "nsl_moe_set_dependent_launch": (None, [_vp, _i]),
+    # include/nslm_pack.h
+    "nsl_blk4_bytes": (_sz, [_i, _i, _i]),
+    "nsl_blk4_split": (_i, [_vp, _sz, _i, _i, _i, _vp, _vp, _vp, _vp]),
+    "nsl_blk4_join": (_i, [_vp, _sz, _i, _i, _i, _vp, _vp, _vp, _vp]),
+    "nsl_wslice_table": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     # include/nslm_ep.h
     "nsl_ep_plan": (None, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "nsl_mv_gu_rows": (None, [_vp, _vp, _vp, _i, _i, _vp, _i, _i, _vp, _i, _vp, _vp, _i, _vp, _i, _vp]),

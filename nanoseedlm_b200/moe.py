@@ -35,6 +35,27 @@ class ExpertStack:
                    eb, R, K)
 
     @classmethod
+    def from_blk4(cls, image, E, R, K):
+        """A .blk4 expert bank (bytes or a uint8 array) -> its experts on the device, through the library's own ingestion:
+        nsl_blk4_split for the streams and nsl_wslice_table for the slice table."""
+        lib = L.load()
+        img = np.frombuffer(bytes(image), np.uint8) if not isinstance(image, np.ndarray) else np.ascontiguousarray(image, np.uint8)
+        nb = R * K // 8
+        seeds, coefs = np.zeros((E, nb), np.uint16), np.zeros((E, nb), np.uint16)
+        bias, codes = np.zeros(E, np.int32), np.zeros((E, nb // 2), np.uint8)
+        if lib.nsl_blk4_split(img.ctypes.data, img.size, E, R, K, seeds.ctypes.data, coefs.ctypes.data, bias.ctypes.data, codes.ctypes.data):
+            raise ValueError("not a .blk4 bank of this shape")
+        st = cls.__new__(cls)
+        st.E, st.R, st.K = E, R, K
+        st.seeds, st.coefs, st.codes, st.eb = dev(seeds), dev(coefs), dev(codes), [int(b) for b in bias]
+        table = (L.WSlice * E)()
+        if lib.nsl_wslice_table(st.seeds.data_ptr(), st.coefs.data_ptr(), st.codes.data_ptr(), bias.ctypes.data, E, R, K, table):
+            raise ValueError(L.last_error())
+        st.table = torch.empty(E * C.sizeof(L.WSlice), dtype=torch.uint8, device="cuda")
+        st.table.copy_(torch.frombuffer(bytearray(bytes(table)), dtype=torch.uint8))
+        return st
+
+    @classmethod
     def random_on_device(cls, E, R, K, gen, eb=-22):
         nb = R * K // 8
         seeds = torch.randint(1, 65536, (E, nb), generator=gen, device="cuda", dtype=torch.int32).to(torch.int16)
