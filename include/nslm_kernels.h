@@ -10,8 +10,10 @@
  * Conventions (engine/kernels_cuda.h:1-7; engine/qwen4_cuda.c:1219-1234): the first argument is the stream; calls
  * are asynchronous launches that return void and allocate nothing; the caller owns every buffer; errors surface at the
  * caller's cudaStreamSynchronize + cudaGetLastError.  Activations are f32 arrays of bf16-rounded values; xs / ys are
- * row strides in floats.  The SEED4P4 weight format (MF_SEED4P4) is implemented everywhere, MF_Q4 in the dense kc_mv:
- * a call with another format launches nothing and records an error that nsl_last_error() returns. */
+ * row strides in floats.  The SEED4P4 weight format (MF_SEED4P4) is implemented everywhere; the mat-vec entry points
+ * (kc_mv, kc_mv_sel, kc_mv_gu) also serve MF_SEED4 (P = 3: p[0] seeds, p[1] nibble words -- exponent code in bits 0-3,
+ * coefficient p in bits 4p+4..4p+7 --, eb the exponent bias, G the 24- or 32-bit stream table) and the dense kc_mv
+ * MF_Q4: a call with another format launches nothing and records an error that nsl_last_error() returns. */
 #pragma once
 #include <stddef.h>
 #include <stdint.h>
@@ -208,6 +210,9 @@ const char* nsl_last_error(void);
 uint64_t nsl_launch_count(void);
 /* Multiprocessor count the persistent grids are sized for (queried once per device). */
 int nsl_sm_count(void);
+/* nsl_decode_f32 / nsl_decode_bf16 for a P = 3 (MF_SEED4) slice. */
+void nsl_decode3_f32(cudaStream_t s, WSlice w, int K, int R, float* out, const uint32_t* G);
+void nsl_decode3_bf16(cudaStream_t s, WSlice w, int K, int R, uint16_t* out, const uint32_t* G);
 /* Work units: the pairs of a gather mat-vec grouped two by two per slice, so that two pairs that use the same expert
  * share one expansion of its weights (results per pair are bit-identical to the ungrouped calls; only the logic-pipe
  * work is shared).  nsl_mv_units builds the list on the device: sel[p] < n_slices for p < max_pairs (or < *count when

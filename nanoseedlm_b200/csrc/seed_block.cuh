@@ -218,6 +218,64 @@ __device__ __forceinline__ float exact_scale45(int e) {
     return __uint_as_float(__float_as_uint(1.0f / 32767.0f) + ((uint32_t) (e + 45) << 23));
 }
 
+// ---- P = 3 blocks (format SEED4: nslm/lfsr.h:82-124) ----------------------------------------------------------------------
+// 24 states; weight c uses states 3c+1 .. 3c+3.  The nibble word holds the exponent code in bits 0-3 and coefficient p
+// in bits 4p+4 .. 4p+7, i.e. where the P = 4 coefficient word holds coefficient p + 1: the same conversions apply with
+// the constants of position p + 1, which leaves every product half as large as in the P = 4 forms; the callers
+// fold the missing factor 2 into the block scale (an exponent increment: exact).
+// The shifted copy for weight c: stream bit 3c+1 at bit 4.  a = stream bits 0..31, g = bits 16..47.
+template <int C>
+__device__ __forceinline__ uint32_t weight_word3(uint32_t a, uint32_t g) {
+    if (C == 0) return a * 8u;
+    if (C == 1) return a;
+    if (C <= 4) return a >> (3 * C - 3);
+    if (C == 5) return g * 16u;
+    if (C == 6) return g * 2u;
+    return g >> 2;
+}
+// The 24 state values v[3c+p] = state_(3c+p+1) * 2^(p-145).
+__device__ __forceinline__ void block_states3(uint32_t a, uint32_t g, float* v) {
+#define NSL_V3(C)                                     \
+    {                                                 \
+        const uint32_t y = weight_word3<C>(a, g);     \
+        v[3 * C + 0] = state_value<0>(y);             \
+        v[3 * C + 1] = state_value<1>(y);             \
+        v[3 * C + 2] = state_value<2>(y);             \
+    }
+    NSL_V3(0) NSL_V3(1) NSL_V3(2) NSL_V3(3) NSL_V3(4) NSL_V3(5) NSL_V3(6) NSL_V3(7)
+#undef NSL_V3
+}
+__device__ __forceinline__ void block_coefs3(uint32_t nib, const KConst& k, float* q) {   // q'_p = q_p 2^(64-p)
+    q[0] = coef_raw<1>(nib, k.cxor[1]) + k.coff[1];
+    q[1] = coef_raw<2>(nib, k.cxor[2]) + k.coff[2];
+    q[2] = coef_raw<3>(nib, k.cxor[3]) + k.coff[3];
+}
+// sum_c x_c isum_c / 2^17 from scaled inputs (xm from block_offsets: its first three entries).
+__device__ __forceinline__ float states_dot3(const float* v, const float* q, const float* x, const float* xm) {
+    float d0 = xm[0], d1 = xm[1], d2 = xm[2];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        d0 = fmaf(x[c], v[3 * c + 0], d0);
+        d1 = fmaf(x[c], v[3 * c + 1], d1);
+        d2 = fmaf(x[c], v[3 * c + 2], d2);
+    }
+    return fmaf(q[2], d2, fmaf(q[1], d1, q[0] * d0));
+}
+// The eight weights bit for bit: q"_p = q_p 2^(99-p), products in units of 2^-46, sc46 = fl(R32 2^e) * 2^46.
+__device__ __forceinline__ void block_weights3(uint32_t a, uint32_t g, uint32_t nib, float sc46, const KConst& k, float* w) {
+    float v[24], q[3];
+    block_states3(a, g, v);
+    q[0] = coef_raw<1>(nib, k.cxor_x[1]) + k.coff_x[1];
+    q[1] = coef_raw<2>(nib, k.cxor_x[2]) + k.coff_x[2];
+    q[2] = coef_raw<3>(nib, k.cxor_x[3]) + k.coff_x[3];
+    const float kq = __fmaf_rn(q[2], -2.938735877055719e-39f, __fmaf_rn(q[1], -1.4693679385278594e-39f, __fmul_rn(q[0], -7.346839692639297e-40f)));
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        const float t = __fmaf_rn(q[2], v[3 * c + 2], __fmaf_rn(q[1], v[3 * c + 1], __fmul_rn(q[0], v[3 * c])));
+        w[c] = __fmul_rn(__fadd_rn(t, kq), sc46);
+    }
+}
+
 // ---- two adjacent blocks as f32x2 pairs {even block, odd block} ----------------------------------------------------
 __device__ __forceinline__ u64 pack2(float lo, float hi) {
     u64 r;

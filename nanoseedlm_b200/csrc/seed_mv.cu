@@ -578,7 +578,8 @@ __global__ void __launch_bounds__(MV_THREADS, 2) mv_shx2_kernel(MvParams a, KCon
 }
 
 // ---- any K that is a multiple of 8, any alignment: one warp per (pair or dense, row), lanes over single blocks -------
-template <int MODE>
+// P = 4 (SEED4P4) or 3 (SEED4: the exponent code rides in the nibble word, there is no code stream).
+template <int MODE, int P>
 __global__ void __launch_bounds__(MV_THREADS) mv_generic_kernel(MvParams a, KConst kc, int T) {
     __shared__ StreamTab tab;
     load_stream_tab(tab, a.G, threadIdx.x, MV_THREADS);
@@ -603,12 +604,12 @@ __global__ void __launch_bounds__(MV_THREADS) mv_generic_kernel(MvParams a, KCon
             for (int half = 0; half < (MODE == MODE_GU ? 2 : 1); ++half) {
                 const WSlice& w = half ? wb : wa;
                 const uint32_t seed = ((const uint16_t*) w.p[0])[gidx], cwi = ((const uint16_t*) w.p[1])[gidx];
-                const uint32_t code = (((const uint8_t*) w.p[3])[gidx >> 1] >> ((gidx & 1) * 4)) & 15u;
+                const uint32_t code = P == 4 ? (((const uint8_t*) w.p[3])[gidx >> 1] >> ((gidx & 1) * 4)) & 15u : cwi & 15u;
                 const uint32_t g = stream_bits(tab, seed);
                 const uint32_t aw = seed | (g << 16);
                 float v[32], q[4];
-                block_states(aw, g, v);
-                block_coefs(cwi, kc, q);
+                if (P == 4) { block_states(aw, g, v); block_coefs(cwi, kc, q); }
+                else { block_states3(aw, g, v); block_coefs3(cwi, kc, q); }
                 const float e2 = __uint_as_float((code << 23) | 0x38000000u);
 #pragma unroll
                 for (int t = 0; t < MV_MAXT; ++t) {
@@ -618,13 +619,13 @@ __global__ void __launch_bounds__(MV_THREADS) mv_generic_kernel(MvParams a, KCon
 #pragma unroll
                     for (int c = 0; c < 8; ++c) xr[c] = __ldg(xp + c) * NSL_XSCALE;
                     block_offsets(xr, xo);
-                    const float d = states_dot(v, q, xr, xo);
+                    const float d = P == 4 ? states_dot(v, q, xr, xo) : states_dot3(v, q, xr, xo);
                     if (half) su[t] = fmaf(d, e2, su[t]);
                     else s[t] = fmaf(d, e2, s[t]);
                 }
             }
         }
-        const float sca = slice_scale(wa.eb), scb = slice_scale(wb.eb);
+        const float sca = slice_scale(wa.eb + (4 - P)), scb = slice_scale(wb.eb + (4 - P));   // P = 3 products are half as large
 #pragma unroll
         for (int t = 0; t < MV_MAXT; ++t) {
             if (t >= T) break;
@@ -637,7 +638,7 @@ __global__ void __launch_bounds__(MV_THREADS) mv_generic_kernel(MvParams a, KCon
 }
 
 // ---- bit-exact decode: one thread per block ---------------------------------------------------------------------------
-template <bool BF16>
+template <bool BF16, int P>
 __global__ void __launch_bounds__(256) decode_kernel(WSlice w, KConst kc, int K, int R, void* out, const uint32_t* G) {
     __shared__ StreamTab tab;
     load_stream_tab(tab, G, threadIdx.x, 256);
@@ -645,10 +646,11 @@ __global__ void __launch_bounds__(256) decode_kernel(WSlice w, KConst kc, int K,
     const size_t nblk = (size_t) R * (K / 8);
     for (size_t gidx = (size_t) blockIdx.x * 256 + threadIdx.x; gidx < nblk; gidx += (size_t) gridDim.x * 256) {
         const uint32_t seed = ((const uint16_t*) w.p[0])[gidx], cw = ((const uint16_t*) w.p[1])[gidx];
-        const int code = (((const uint8_t*) w.p[3])[gidx >> 1] >> ((gidx & 1) * 4)) & 15;
+        const int code = P == 4 ? (((const uint8_t*) w.p[3])[gidx >> 1] >> ((gidx & 1) * 4)) & 15 : (int) (cw & 15u);
         const uint32_t g = stream_bits(tab, seed);
         float wv[8];
-        block_weights(seed | (g << 16), g, cw, exact_scale45(w.eb + code), kc, wv);
+        if (P == 4) block_weights(seed | (g << 16), g, cw, exact_scale45(w.eb + code), kc, wv);
+        else block_weights3(seed | (g << 16), g, cw, exact_scale45(w.eb + code + 1), kc, wv);
         if (BF16) {
             uint4 o;
             o.x = bf16_bits(wv[0]) | ((uint32_t) bf16_bits(wv[1]) << 16);
@@ -762,15 +764,25 @@ static void launch_mv(cudaStream_t s, const MvParams& a, int T, int p_hint = 0) 
         count_launch();
         return;
     }
-    launch(mv_generic_kernel<MODE>, sms * 2, MV_THREADS, 0, s, a, kconst(), dense ? T : 1);
+    launch(mv_generic_kernel<MODE, 4>, sms * 2, MV_THREADS, 0, s, a, kconst(), dense ? T : 1);
+    count_launch();
+}
+
+// P = 3 (SEED4): the any-shape kernel serves every form.
+template <int MODE>
+static void launch_mv3(cudaStream_t s, const MvParams& a, int T) {
+    if (a.R <= 0 || a.P <= 0 || T <= 0) return;
+    if (a.K <= 0 || a.K % 8) { set_error("seed mat-vec: K = %d is not a multiple of 8", a.K); return; }
+    if (T > MV_MAXT) { set_error("seed mat-vec: %d tokens, at most %d", T, MV_MAXT); return; }
+    launch(mv_generic_kernel<MODE, 3>, sm_count() * 2, MV_THREADS, 0, s, a, kconst(), a.sel ? 1 : T);
     count_launch();
 }
 
 bool launch_q4_mv(cudaStream_t s, const WSlice& w, int K, int R, const float* x, int xs, float* y, int ys, int T, int add);
 
-static bool seed_fmt(int fmt, const char* who) {
-    if (fmt == MF_SEED4P4) return true;
-    set_error("%s: weight format %d is not served by this library (SEED4P4 = %d only)", who, fmt, (int) MF_SEED4P4);
+static bool seed_fmt(int fmt, const char* who) {      // the mat-vec entry points: P = 4 and P = 3 seeds
+    if (fmt == MF_SEED4P4 || fmt == MF_SEED4) return true;
+    set_error("%s: weight format %d is not served by this library (SEED4P4 = %d, SEED4 = %d)", who, fmt, (int) MF_SEED4P4, (int) MF_SEED4);
     return false;
 }
 
@@ -785,21 +797,24 @@ void kc_mv(cudaStream_t s, int fmt, WSlice w, int K, int R, const float* x, int 
     if (fmt == MF_Q4) { launch_q4_mv(s, w, K, R, x, xs, y, ys, T, add); return; }   // the LM head's affine int4 (q4_head.cu)
     if (!seed_fmt(fmt, "kc_mv")) return;
     MvParams a = {NULL, NULL, w, NULL, x, y, G, K, R, T, 1, xs, ys, add, 0, NULL, NULL, 0, NULL, NULL};
-    launch_mv<MODE_ROUND>(s, a, T);
+    if (fmt == MF_SEED4) launch_mv3<MODE_ROUND>(s, a, T);
+    else launch_mv<MODE_ROUND>(s, a, T);
 }
 
 void kc_mv_sel(cudaStream_t s, int fmt, const WSlice* ws, int K, int R, const float* x, int xs, float* y, int ys,
                const int32_t* sel, int P, int xdiv, const uint32_t* G) {
     if (!seed_fmt(fmt, "kc_mv_sel")) return;
     MvParams a = {ws, NULL, WSlice{}, sel, x, y, G, K, R, P, xdiv, xs, ys, 0, 0, NULL, NULL, 0, NULL, NULL};
-    launch_mv<MODE_ROUND>(s, a, 1);
+    if (fmt == MF_SEED4) launch_mv3<MODE_ROUND>(s, a, 1);
+    else launch_mv<MODE_ROUND>(s, a, 1);
 }
 
 void kc_mv_gu(cudaStream_t s, int fmt, const WSlice* wg, const WSlice* wu, int K, int R, const float* x, int xs, float* out,
               int ys, const int32_t* sel, int P, int xdiv, const uint32_t* G) {
     if (!seed_fmt(fmt, "kc_mv_gu")) return;
     MvParams a = {wg, wu, WSlice{}, sel, x, out, G, K, R, P, xdiv, xs, ys, 0, 0, NULL, NULL, 0, NULL, NULL};
-    launch_mv<MODE_GU>(s, a, 1);
+    if (fmt == MF_SEED4) launch_mv3<MODE_GU>(s, a, 1);
+    else launch_mv<MODE_GU>(s, a, 1);
 }
 
 void nsl_mv_raw(cudaStream_t s, const WSlice* ws, int K, int R, const float* x, int xs, float* y, int ys,
@@ -860,7 +875,7 @@ void nsl_decode_f32(cudaStream_t s, WSlice w, int K, int R, float* out, const ui
     if (K <= 0 || K % 8 || R <= 0) { if (K % 8) set_error("nsl_decode_f32: K = %d is not a multiple of 8", K); return; }
     const size_t nblk = (size_t) R * (K / 8);
     const int grid = (int) ((nblk + 255) / 256 < (size_t) sm_count() * 8 ? (nblk + 255) / 256 : (size_t) sm_count() * 8);
-    decode_kernel<false><<<grid, 256, 0, s>>>(w, kconst(), K, R, out, G);
+    decode_kernel<false, 4><<<grid, 256, 0, s>>>(w, kconst(), K, R, out, G);
     count_launch();
 }
 
@@ -868,7 +883,24 @@ void nsl_decode_bf16(cudaStream_t s, WSlice w, int K, int R, uint16_t* out, cons
     if (K <= 0 || K % 8 || R <= 0) { if (K % 8) set_error("nsl_decode_bf16: K = %d is not a multiple of 8", K); return; }
     const size_t nblk = (size_t) R * (K / 8);
     const int grid = (int) ((nblk + 255) / 256 < (size_t) sm_count() * 8 ? (nblk + 255) / 256 : (size_t) sm_count() * 8);
-    decode_kernel<true><<<grid, 256, 0, s>>>(w, kconst(), K, R, out, G);
+    decode_kernel<true, 4><<<grid, 256, 0, s>>>(w, kconst(), K, R, out, G);
+    count_launch();
+}
+
+// P = 3 (SEED4) slices decoded bit for bit: w.p[0] seeds, w.p[1] nibble words, w.eb the exponent bias.
+void nsl_decode3_f32(cudaStream_t s, WSlice w, int K, int R, float* out, const uint32_t* G) {
+    if (K <= 0 || K % 8 || R <= 0) { if (K % 8) set_error("nsl_decode3_f32: K = %d is not a multiple of 8", K); return; }
+    const size_t nblk = (size_t) R * (K / 8);
+    const int grid = (int) ((nblk + 255) / 256 < (size_t) sm_count() * 8 ? (nblk + 255) / 256 : (size_t) sm_count() * 8);
+    decode_kernel<false, 3><<<grid, 256, 0, s>>>(w, kconst(), K, R, out, G);
+    count_launch();
+}
+
+void nsl_decode3_bf16(cudaStream_t s, WSlice w, int K, int R, uint16_t* out, const uint32_t* G) {
+    if (K <= 0 || K % 8 || R <= 0) { if (K % 8) set_error("nsl_decode3_bf16: K = %d is not a multiple of 8", K); return; }
+    const size_t nblk = (size_t) R * (K / 8);
+    const int grid = (int) ((nblk + 255) / 256 < (size_t) sm_count() * 8 ? (nblk + 255) / 256 : (size_t) sm_count() * 8);
+    decode_kernel<true, 3><<<grid, 256, 0, s>>>(w, kconst(), K, R, out, G);
     count_launch();
 }
 

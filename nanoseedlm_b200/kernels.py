@@ -81,6 +81,65 @@ class SeedWeight:
         return self.seeds.numel() * 2 + self.coefs.numel() * 2 + self.codes.numel()
 
 
+class SeedWeight3:
+    """S slices of an R x K P = 3 (MF_SEED4) tensor on the device and the device table of their WSlice entries."""
+
+    def __init__(self, mats):
+        self.S, self.R, self.K = len(mats), mats[0].rows, mats[0].K
+        self.seeds = dev(np.stack([m.seeds for m in mats]).reshape(self.S, -1))
+        self.nibs = dev(np.stack([m.nibs for m in mats]).reshape(self.S, -1))
+        self.eb = [int(m.eb) for m in mats]
+        arr = (L.WSlice * self.S)()
+        for s in range(self.S):
+            arr[s] = self.slice(s)
+        self.table = torch.empty(self.S * C.sizeof(L.WSlice), dtype=torch.uint8, device="cuda")
+        self.table.copy_(torch.frombuffer(bytearray(bytes(arr)), dtype=torch.uint8))
+
+    def slice(self, s):
+        w = L.WSlice()
+        w.p[0], w.p[1] = self.seeds[s].data_ptr(), self.nibs[s].data_ptr()
+        w.eb = self.eb[s]
+        return w
+
+
+def kt_decode3(w, s=0, bf16=False):
+    out = torch.empty(w.R * w.K, dtype=torch.int16 if bf16 else torch.float32, device="cuda")
+    fn = L.load().nsl_decode3_bf16 if bf16 else L.load().nsl_decode3_f32
+    fn(_stream(), w.slice(s), w.K, w.R, _ptr(out), _ptr(stream_table()))
+    _done()
+    o = out.cpu().numpy()
+    return (o.view(np.uint16) if bf16 else o).reshape(w.R, w.K)
+
+
+def kt_mv3(w, x, T, add=0, y0=None, s=0):
+    """kc_mv with MF_SEED4 on slice s."""
+    xd = dev(np.asarray(x, np.float32).reshape(T, w.K))
+    yd = dev(np.asarray(y0, np.float32).reshape(T, w.R)) if y0 is not None else torch.zeros(T, w.R, device="cuda")
+    L.load().kc_mv(_stream(), L.MF_SEED4, w.slice(s), w.K, w.R, _ptr(xd), w.K, _ptr(yd), w.R, T, add, _ptr(stream_table()))
+    _done()
+    return yd.cpu().numpy()
+
+
+def kt_mv3_sel(w, sel, xdiv, x):
+    sel = np.asarray(sel, np.int32)
+    xd, seld = dev(np.asarray(x, np.float32).reshape(-1, w.K)), dev(sel)
+    yd = torch.zeros(sel.size, w.R, device="cuda")
+    L.load().kc_mv_sel(_stream(), L.MF_SEED4, _ptr(w.table), w.K, w.R, _ptr(xd), w.K, _ptr(yd), w.R, _ptr(seld), sel.size, xdiv,
+                       _ptr(stream_table()))
+    _done()
+    return yd.cpu().numpy()
+
+
+def kt_mv3_gu(wg, wu, sel, xdiv, x):
+    sel = np.asarray(sel, np.int32)
+    xd, seld = dev(np.asarray(x, np.float32).reshape(-1, wg.K)), dev(sel)
+    ad = torch.zeros(sel.size, wg.R, device="cuda")
+    L.load().kc_mv_gu(_stream(), L.MF_SEED4, _ptr(wg.table), _ptr(wu.table), wg.K, wg.R, _ptr(xd), wg.K, _ptr(ad), wg.R,
+                      _ptr(seld), sel.size, xdiv, _ptr(stream_table()))
+    _done()
+    return ad.cpu().numpy()
+
+
 def _done():
     torch.cuda.synchronize()
     L.check()

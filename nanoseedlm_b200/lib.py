@@ -9,6 +9,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libnslm_b200.so")
 
 MF_SEED4P4 = 4
+MF_SEED4 = 1
 MF_Q4 = 3
 MV_MAXT = 8
 MMT_BN = 128
@@ -85,6 +86,8 @@ PROTOTYPES = {
     "nsl_mv_gu_raw": (None, [_vp, _vp, _vp, _i, _i, _vp, _i, _vp, _i, _vp, _i, _i, _vp]),
     "nsl_decode_f32": (None, [_vp, WSlice, _i, _i, _vp, _vp]),
     "nsl_decode_bf16": (None, [_vp, WSlice, _i, _i, _vp, _vp]),
+    "nsl_decode3_f32": (None, [_vp, WSlice, _i, _i, _vp, _vp]),
+    "nsl_decode3_bf16": (None, [_vp, WSlice, _i, _i, _vp, _vp]),
     "nsl_mm_status": (_i, []),
     "nsl_mv_set_variant": (None, [_i]),
     "nsl_stream_table": (None, [_vp]),

@@ -358,3 +358,31 @@ def argmax(logits):
         lib().orc_argmax(logits[i].ctypes.data_as(C.c_void_p), V, out[i:].ctypes.data_as(C.c_void_p),
                          prob[i:].ctypes.data_as(C.c_void_p))
     return out, prob
+
+
+class Matrix3:
+    """A seeded P = 3 (SEED4) matrix: seeds and nibble words [rows][K/8] (code in bits 0-3, three int4 coefficients above)."""
+
+    def __init__(self, rows, K, seed, eb=-22):
+        rng = np.random.default_rng(seed)
+        self.rows, self.K, self.eb = rows, K, eb
+        self.seeds = rng.integers(1, 65536, (rows, K // 8)).astype(np.uint16)
+        self.nibs = rng.integers(0, 65536, (rows, K // 8)).astype(np.uint16)
+
+
+def decode3_block_bf16(seed, nib, bias):
+    out = np.zeros(8, np.uint16)
+    lib().orc_decode3_block_bf16(C.c_uint16(int(seed)), C.c_uint16(int(nib)), int(bias), out.ctypes.data_as(C.c_void_p))
+    return out
+
+
+def decode3_rows_f32(m):
+    out = np.zeros((m.rows, m.K), np.float32)
+    lib().orc_decode3_rows_f32(m.seeds.ctypes.data_as(C.c_void_p), m.nibs.ctypes.data_as(C.c_void_p), m.eb, m.rows, m.K,
+                               out.ctypes.data_as(C.c_void_p))
+    return out
+
+
+def bfr(a):
+    """f32 values rounded to bf16 (round to nearest even), as f32."""
+    return (f2bf(np.asarray(a, np.float32)).astype(np.uint32) << 16).view(np.float32)

@@ -377,6 +377,34 @@ void orc_moe_layer(const OrcMoe* m, const float* x, const float* logits, int T, 
 }
 
 /* ------------------------------------------------------------------------------------------------------------------
+ * P = 3 blocks (format SEED4; nslm/lfsr.h:82-124, nslm/lib_rows.c:49-76): 8 weights = u16 seed + u16 nibble word whose
+ * bits 0-3 are the exponent code and bits 4p+4..4p+7 the int4 coefficient q_p, p = 0..2; states 1..24 after the seed;
+ * isum_c = sum_p (state_(3c+p+1) - 32768) q_p; weight = fl((float) isum_c * fl(R32 2^(bias + code))). */
+static int q3(uint16_t nib, int p) {
+    const int v = (nib >> (4 + 4 * p)) & 15;
+    return v >= 8 ? v - 16 : v;
+}
+void orc_decode3_block_f32(uint16_t seed, uint16_t nib, int bias, float out[8]) {
+    uint16_t st[24];
+    orc_lfsr_states(seed, 24, st);
+    const float sc = orc_scale(bias + (nib & 15));
+    for (int c = 0; c < 8; ++c) {
+        int32_t isum = 0;
+        for (int p = 0; p < 3; ++p) isum += ((int32_t) st[3 * c + p] - 32768) * q3(nib, p);
+        out[c] = (float) isum * sc;
+    }
+}
+void orc_decode3_block_bf16(uint16_t seed, uint16_t nib, int bias, uint16_t out[8]) {
+    float w[8];
+    orc_decode3_block_f32(seed, nib, bias, w);
+    for (int c = 0; c < 8; ++c) out[c] = orc_f2bf(w[c]);
+}
+void orc_decode3_rows_f32(const uint16_t* seeds, const uint16_t* nibs, int bias, int rows, int K, float* out) {
+    const size_t nb = (size_t) rows * (K / 8);
+    for (size_t g = 0; g < nb; ++g) orc_decode3_block_f32(seeds[g], nibs[g], bias, out + g * 8);
+}
+
+/* ------------------------------------------------------------------------------------------------------------------
  * The affine int4 dense mat-vec of the LM head, in the form the reference's kernel test states it
  * (tests/test_mova_kernels.c:146-157, 181-199): weight (r, c) = bf16 scale[(r K + c) / 64] * code + bf16 bias[same group],
  * code = bits 4 (i % 8) .. of word i / 8; y = bf16(sum in double), or with add bf16(y0 + bf16(sum)).  mag (optional) gets

@@ -61,6 +61,9 @@ void orc_mova_topk(const float* score, const float* sel, int n, int k, float sca
 void orc_mova_router(int d, int hw, int n, int k, float scale, const uint16_t* W, const uint16_t* bias, const float* x,
                      float* score, float* sel, int32_t* inds, float* wts);
 float orc_softplus_gate(float g);
+void orc_decode3_block_f32(uint16_t seed, uint16_t nib, int bias, float out[8]);
+void orc_decode3_block_bf16(uint16_t seed, uint16_t nib, int bias, uint16_t out[8]);
+void orc_decode3_rows_f32(const uint16_t* seeds, const uint16_t* nibs, int bias, int rows, int K, float* out);
 void orc_q4_mv(const uint32_t* codes, const uint16_t* scales, const uint16_t* biases, int K, int R, const float* x, int T,
                int add, float* y, double* mag);
 void orc_argmax(const float* logits, int V, int32_t* out, double* prob);

@@ -33,6 +33,24 @@ void ref_row_f32(const uint16_t* seeds, const uint16_t* coefs, const uint8_t* co
     ns_row_f32(&tables, &t, 0, row, 0, out);
 }
 
+/* P = 3 (SEED4): the spec's block decode and a row through the reference's weight reader. */
+void ref_decode3_block(uint16_t seed, uint16_t nib, int bias, uint16_t* out) { nslm_decode_block(seed, nib, bias, out); }
+void ref_row3_f32(const uint16_t* seeds, const uint16_t* nibs, int32_t eb, int rows, int K, int row, float* out) {
+    static NsRows tables;
+    static int ready;
+    if (!ready) { ns_rows_init(&tables); ready = 1; }
+    NsTensor t;
+    memset(&t, 0, sizeof t);
+    t.enc = NS_SEED4;
+    t.slices = 1;
+    t.rows = rows;
+    t.cols = K;
+    t.s[0].p = (const uint8_t*) seeds;
+    t.s[1].p = (const uint8_t*) nibs;
+    t.s[2].p = (const uint8_t*) &eb;
+    ns_row_f32(&tables, &t, 0, row, 0, out);
+}
+
 void ref_route(int E, int k, const float* logits, int32_t* ind, float* wt) {
     Qwen4Cfg c;
     memset(&c, 0, sizeof c);

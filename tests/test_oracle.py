@@ -188,3 +188,16 @@ def test_q4_reference_form(oracle):
     assert np.allclose(mag, np.abs(x.astype(np.float64)) @ np.abs(w.T))
     out, prob = oracle.argmax(np.array([[0.0, 2.0, 2.0, -1.0]], np.float32))
     assert out[0] == 1 and abs(prob[0] - 1 / (2 + np.exp(-2) + np.exp(-3))) < 1e-12
+
+
+def test_p3_decode_matches_reference_fixture(oracle):
+    """P = 3 (SEED4) blocks and rows against outputs of the reference's own code (tests/golden/make_golden_p3.py)."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "seed4_p3_golden.npz"))
+    for i in range(len(g["blk_seed"])):
+        got = oracle.decode3_block_bf16(g["blk_seed"][i], g["blk_nib"][i], g["blk_bias"][i])
+        assert np.array_equal(got, g["blk_bf16"][i]), i
+    rows, K, eb = (int(v) for v in g["row_shape"])
+    m = oracle.Matrix3(rows, K, 0, eb=eb)
+    m.seeds, m.nibs = g["row_seeds"], g["row_nibs"]
+    assert np.array_equal(oracle.decode3_rows_f32(m).view(np.uint32), g["row_f32"].view(np.uint32))
