@@ -584,6 +584,65 @@ def run_lmhead(args):
                                    "us_per_launch": mv_us, "bytes_per_launch": nbytes}}))
 
 
+def run_attn(args):
+    """Not the headline: decode attention of the reference's config 4 (GQA 16 query / 2 KV heads of 128, BF16 cache of 4096
+    positions, 32 sequences = 134 MB of K and V per layer), an HBM-bound kernel."""
+    import torch
+    from nanoseedlm_b200 import lib as L
+    lib = L.load()
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    NH, NKV, CTX, NSEQ, NS, NL = 16, 2, 4096, 32, 8, 3
+    K, W = args.steps, max(args.warmup, 3)
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    caches = [(torch.randn(NSEQ * CTX, NKV, 128, generator=gen, device="cuda").to(torch.bfloat16),
+               torch.randn(NSEQ * CTX, NKV, 128, generator=gen, device="cuda").to(torch.bfloat16)) for _ in range(NL)]
+    q = torch.randn(NSEQ, NH, 128, generator=gen, device="cuda").to(torch.bfloat16).float()
+    g = torch.randn(NSEQ, NH, 128, generator=gen, device="cuda").to(torch.bfloat16).float()
+    o = torch.zeros(NSEQ, NH, 128, device="cuda")
+    part = torch.zeros(NSEQ * NH * NS * 130, device="cuda")
+    ri = (L.RowInfo * NSEQ)()
+    for t in range(NSEQ):
+        ri[t].pos, ri[t].kv0 = CTX - 1, t * CTX
+    rid = torch.empty(NSEQ * 16, dtype=torch.uint8, device="cuda")
+    rid.copy_(torch.frombuffer(bytearray(bytes(ri)), dtype=torch.uint8))
+    a = L.AttnArgs(NH, NKV, CTX // NS, NS, float(1 / np.sqrt(128.0)))
+    views = []
+    for kc, vc in caches:
+        kv = L.KvView()
+        kv.a.k, kv.a.v, kv.nv, kv.fmt = kc.data_ptr(), vc.data_ptr(), NSEQ * CTX, 0
+        views.append(kv)
+    stream = torch.cuda.Stream()
+    s = C.c_void_p(stream.cuda_stream)
+
+    def step(i):
+        lib.kc_attn(s, a, q.data_ptr(), views[i % NL], rid.data_ptr(), part.data_ptr(), g.data_ptr(), o.data_ptr(), NSEQ)
+
+    with torch.cuda.stream(stream):
+        for i in range(W):
+            step(i)
+        stream.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(torch.cuda.current_device()) as clocks:
+            e0.record(stream)
+            for i in range(K):
+                step(W + i)
+            e1.record(stream)
+            e1.synchronize()
+        ms = e0.elapsed_time(e1) / K
+    L.check()
+    peaks, kind = measured_peaks()
+    nbytes = 2 * NSEQ * CTX * NKV * 128 * 2 + 3 * NSEQ * NH * 128 * 4
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    print(json.dumps({"metric": "decode_attention_tokens_per_s", "value": NSEQ / (ms * 1e-3), "unit": "tok/s", "n_gpus": 1, "steps": K,
+                      "warmup": W, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 cache, f32 math",
+                      "data": "synthetic", "gpu_launches": 2 * K, "clocks": clocks.summary(),
+                      "config": {"workload": f"decode attention, {NH} query / {NKV} KV heads of 128, BF16 cache of {CTX} positions x {NSEQ} "
+                                             f"sequences ({nbytes / 1e6:.0f} MB per layer), {NS} splits; {NL} layers rotated", "tokens": NSEQ},
+                      "roofline": {"bound": "hbm", "kernel": "attn_split_kernel + attn_reduce_kernel (kc_attn)", "achieved": gbs,
+                                   "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"], "peak_kind": kind, "traffic": None,
+                                   "bytes_per_step": nbytes}}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -602,7 +661,7 @@ def main():
     ap.add_argument("--ep-mirror", type=int, default=0,
                     help="config 3, p2p, even rank counts: 1 = ranks r and r + N/2 hold each other's experts too and split their "
                          "joint pairs in the middle (balance to within one pair; twice the expert bytes per GPU)")
-    ap.add_argument("--workload", default=None, choices=["cfg1", "cfg2", "cfg3", "lmhead"],
+    ap.add_argument("--workload", default=None, choices=["cfg1", "cfg2", "cfg3", "lmhead", "attn"],
                     help="cfg1: one GPU's MoE decode layer (default at 1 GPU); cfg2: the same layer on 512 prompt rows (grouped "
                          "tcgen05 GEMM); cfg3: expert-parallel decode (default at >1 GPU)")
     args = ap.parse_args()
@@ -619,7 +678,9 @@ def main():
         args.tokens = 512 if workload == "cfg2" else 8
     if workload == "cfg1" and not 1 <= args.tokens <= 8:
         raise SystemExit("config 1 is the decode / verify batch: --tokens 1..8 (use --workload cfg2 for prompt rows)")
-    if workload == "lmhead":
+    if workload == "attn":
+        run_attn(args)
+    elif workload == "lmhead":
         run_lmhead(args)
     elif workload == "cfg3":
         run_ep(args)

@@ -269,6 +269,32 @@ def kt_argmax(logits, prob=False):
     return (out.cpu().numpy(), pr.cpu().numpy()) if prob else out.cpu().numpy()
 
 
+def kt_attn(a, q, Kc, Vc, pos, kv0, g=None, nv=None):
+    """kc_attn on a BF16 cache (tests/kernel_backend_cuda.c: kt_attn): Kc / Vc bf16 bits [rows][n_kv][128]; rows of the
+    cache below nv (default: all) sit in segment a, the rest in segment b."""
+    T = len(pos)
+    Kc, Vc = np.asarray(Kc, np.uint16), np.asarray(Vc, np.uint16)
+    nv = Kc.shape[0] if nv is None else nv
+    keep = [dev(Kc[:nv]), dev(Vc[:nv]), dev(Kc[nv:]) if nv < Kc.shape[0] else None, dev(Vc[nv:]) if nv < Kc.shape[0] else None]
+    kv = L.KvView()
+    kv.a.k, kv.a.v = keep[0].data_ptr(), keep[1].data_ptr()
+    if keep[2] is not None:
+        kv.b.k, kv.b.v = keep[2].data_ptr(), keep[3].data_ptr()
+    kv.nv, kv.fmt = nv, 0
+    ri = (L.RowInfo * T)()
+    for t in range(T):
+        ri[t].pos, ri[t].kv0 = int(pos[t]), int(kv0[t])
+    rid = torch.empty(T * 16, dtype=torch.uint8, device="cuda")
+    rid.copy_(torch.frombuffer(bytearray(bytes(ri)), dtype=torch.uint8))
+    qd = dev(np.asarray(q, np.float32))
+    gd = dev(np.asarray(g, np.float32)) if g is not None else None
+    part = torch.zeros(T * a.n_head * a.n_splits * 130, device="cuda")
+    o = torch.zeros(T, a.n_head, 128, device="cuda")
+    L.load().kc_attn(_stream(), a, _ptr(qd), kv, _ptr(rid), _ptr(part), _ptr(gd), _ptr(o), T)
+    _done()
+    return o.cpu().numpy()
+
+
 def kt_route(logits, k):
     logits = np.asarray(logits, np.float32)
     T, E = logits.shape

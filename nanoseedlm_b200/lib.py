@@ -41,6 +41,25 @@ class HmvArgs(C.Structure):
                 ("gate", C.c_int32), ("pad", C.c_int32 * 2)]
 
 
+class AttnArgs(C.Structure):
+    _fields_ = [("n_head", C.c_int32), ("n_kv", C.c_int32), ("chunk", C.c_int32), ("n_splits", C.c_int32), ("scale", C.c_float)]
+
+
+class RowInfo(C.Structure):
+    _fields_ = [("pos", C.c_int32), ("kv0", C.c_int32), ("pad", C.c_int32 * 2)]
+
+
+class KvSeg(C.Structure):
+    _fields_ = [("k", C.c_void_p), ("v", C.c_void_p), ("ks", C.c_void_p), ("vs", C.c_void_p)]
+
+
+class KvView(C.Structure):
+    _fields_ = [("a", KvSeg), ("b", KvSeg), ("nv", C.c_int32), ("fmt", C.c_int32)]
+
+
+assert C.sizeof(AttnArgs) == 20 and C.sizeof(RowInfo) == 16 and C.sizeof(KvView) == 72
+
+
 class NslEpWindow(C.Structure):
     _fields_ = [("win", C.c_void_p * 16), ("n", C.c_int32), ("me", C.c_int32), ("t_loc", C.c_int32), ("reserved", C.c_int32),
                 ("bytes", C.c_uint64),
@@ -75,6 +94,7 @@ PROTOTYPES = {
     "kc_router_topk": (None, [_vp, RouterArgs, _vp, _vp, _vp, _vp, _i]),
     "kc_heads_mv": (None, [_vp, HmvArgs, _i, WSlice, _vp, _vp, _vp, _vp, _i]),
     "kc_heads_deq": (None, [_vp, _i, WSlice, _vp, _i, _i, _i, _vp]),
+    "kc_attn": (None, [_vp, AttnArgs, _vp, KvView, _vp, _vp, _vp, _vp, _i]),
     "nsl_q4_set_variant": (None, [_i]),
     "kc_argmax": (None, [_vp, _vp, _vp, _i, _i]),
     "kc_argmax_p": (None, [_vp, _vp, _vp, _vp, _i, _i]),

@@ -386,3 +386,25 @@ def decode3_rows_f32(m):
 def bfr(a):
     """f32 values rounded to bf16 (round to nearest even), as f32."""
     return (f2bf(np.asarray(a, np.float32)).astype(np.uint32) << 16).view(np.float32)
+
+
+def attn_decode(q, Kc, Vc, pos, kv0, n_kv, scale, g=None):
+    """Decode attention in double precision, as the reference's kernel test states it (tests/test_mova_kernels.c:684-712):
+    q [T][n_head][128] f32, Kc / Vc bf16 bits [rows][n_kv][128]; row t attends cache rows kv0[t] .. kv0[t] + pos[t]; returns
+    the gated, bf16-rounded outputs the kernels are compared with and the ungated double values."""
+    q = np.asarray(q, np.float64)
+    T, n_head, _ = q.shape
+    K = (np.asarray(Kc, np.uint16).astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+    V = (np.asarray(Vc, np.uint16).astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+    att = np.zeros((T, n_head, 128))
+    for t in range(T):
+        rows = slice(int(kv0[t]), int(kv0[t]) + int(pos[t]) + 1)
+        for h in range(n_head):
+            kvh = h // (n_head // n_kv)
+            s = (K[rows, kvh] @ (q[t, h] * np.float64(np.float32(scale))))
+            w = np.exp(s - s.max())
+            att[t, h] = (w / w.sum()) @ V[rows, kvh]
+    out = bfr(att.astype(np.float32))
+    if g is not None:
+        out = bfr(out * softplus_gate(np.asarray(g, np.float32)))
+    return out, att

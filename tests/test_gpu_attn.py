@@ -1,0 +1,54 @@
+"""Decode attention over a BF16 KV cache (kc_attn) against a double-precision reference.
+
+The first case is the reference's own kernel test (tests/test_mova_kernels.c:660-715): GQA 8/2, three rows at
+positions 300, 299, 37 in sequence slots based at cache rows 0, 310, 600, five splits; bound |o - ref| <= |ref| / 128 + 2e-6."""
+import numpy as np
+import pytest
+
+from oracle import binding as B
+
+pytestmark = pytest.mark.gpu
+
+
+def run_case(nh, nkv, NP, pos, kv0, ns, chunk, gate=True, nv=None, seed=21):
+    from nanoseedlm_b200 import kernels, lib as L
+    rng = np.random.default_rng(seed)
+    T = len(pos)
+    q = B.bfr((rng.random((T, nh, 128), np.float32) * 2 - 1) * 2)
+    g = B.bfr((rng.random((T, nh, 128), np.float32) * 2 - 1) * 3)
+    Kc = B.f2bf((rng.random((NP, nkv, 128), np.float32) * 2 - 1) * 2)
+    Vc = B.f2bf(rng.random((NP, nkv, 128), np.float32) * 2 - 1)
+    scale = np.float32(1 / np.sqrt(128.0))
+    a = L.AttnArgs(nh, nkv, chunk, ns, float(scale))
+    o = kernels.kt_attn(a, q, Kc, Vc, pos, kv0, g if gate else None, nv)
+    ref, _ = B.attn_decode(q, Kc, Vc, pos, kv0, nkv, scale, g if gate else None)
+    bad = np.abs(o - ref) > np.abs(ref) / 128 + 2e-6
+    assert not bad.any(), (int(bad.sum()), float(np.max(np.abs(o - ref))))
+
+
+def test_reference_case_gqa_8_over_2():
+    run_case(8, 2, 640, [300, 299, 37], [0, 310, 600], 5, (301 + 4) // 5)
+
+
+@pytest.mark.parametrize("nh,nkv", [(16, 2), (4, 4), (32, 2), (3, 1)])
+def test_group_sizes(nh, nkv):
+    run_case(nh, nkv, 700, [511, 0, 33, 64], [0, 600, 620, 512], 4, 128, seed=nh)
+
+
+def test_one_split_no_gate_and_two_segments():
+    run_case(8, 2, 640, [300, 299, 37], [0, 310, 600], 1, 0, gate=False)
+    run_case(8, 2, 640, [300, 299, 37], [0, 310, 600], 3, 64, nv=320, seed=5)      # positions >= 320 live in segment b
+
+
+def test_refuses_other_cache_formats_and_groups():
+    import torch
+    from nanoseedlm_b200 import lib as L
+    kv = L.KvView()
+    kv.fmt = 1
+    L.load().kc_attn(None, L.AttnArgs(8, 2, 64, 2, 0.1), None, kv, None, None, None, None, 1)
+    with pytest.raises(RuntimeError, match="format 1"):
+        L.check()
+    kv.fmt = 0
+    L.load().kc_attn(None, L.AttnArgs(64, 2, 64, 2, 0.1), None, kv, None, None, None, None, 1)
+    with pytest.raises(RuntimeError, match="groups of"):
+        L.check()
