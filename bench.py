@@ -592,6 +592,7 @@ def run_attn(args):
     lib = L.load()
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     NH, NKV, CTX, NSEQ, NS, NL = 16, 2, 4096, 32, int(os.environ.get("NSL_ATTN_SPLITS", "16")), 3
+    lib.nsl_attn_set_variant(int(os.environ.get("NSL_ATTN_VARIANT", "1")))
     K, W = args.steps, max(args.warmup, 3)
     gen = torch.Generator(device="cuda").manual_seed(5)
     caches = [(torch.randn(NSEQ * CTX, NKV, 128, generator=gen, device="cuda").to(torch.bfloat16),

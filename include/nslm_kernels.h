@@ -168,6 +168,9 @@ typedef struct { KvSeg a, b; int32_t nv, fmt; } KvView;             /* positions
  * bf16(bf16(softmax(scale q.K) V) * bf16(softplus(g; beta = ln 2))) (g NULL: no gate).  BF16 caches only (kv.fmt =
  * KV_BF16); any group size n_head / n_kv up to 16. */
 void kc_attn(cudaStream_t s, AttnArgs a, const float* q, KvView kv, const RowInfo* ri, float* part, const float* g, float* o, int T);
+/* No counterpart in the reference: the form of kc_attn's split pass (1, the default: all heads of a KV head as the rows
+ * of tensor-core products, the softmax weights entering the second product as bf16; 0: scalar, one warp per head). */
+void nsl_attn_set_variant(int v);
 
 /* ---- greedy decoding over the LM head's logits ------------------------------------------------------------------------ */
 /* engine/kernels_cuda.h:177-178  out[i] = arg max of row i of logits [n][V] (ties: the lowest id); prob[i] (optional) =

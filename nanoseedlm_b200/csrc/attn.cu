@@ -110,6 +110,163 @@ __global__ void __launch_bounds__(32 * ATT_MAX_GROUP) attn_split_kernel(AttnArgs
     pp[2 + lane * 4 + 0] = acc.x; pp[2 + lane * 4 + 1] = acc.y; pp[2 + lane * 4 + 2] = acc.z; pp[2 + lane * 4 + 3] = acc.w;
 }
 
+// ---- the same pass on the tensor cores -------------------------------------------------------------------------------------
+// One warp serves ALL query heads of the KV head: they are the 16 rows of an mma.sync.m16n8k16 (bf16 in, f32 accumulate;
+// rows beyond the group are zero).  Queries are bf16-valued, so the score products are exact and the softmax scale is
+// applied to the f32 sums; the weights enter the second product as two bf16 terms (hi + lo: 16 significant bits; their
+// sum l is kept in f32).  Per step of 32 keys a warp issues 32 MMAs for the scores and 64 for the values instead of
+// ~5000 scalar instructions for the group.  The warps of a block take the split's steps in turn, each with its own running (m, l, acc) and its own K / V
+// stage in shared memory (rows 272 bytes apart: the fragment reads and ldmatrix touch distinct banks); at the end the
+// warps' states are merged through the same shared memory.
+constexpr int ATT_MMA_WARPS = 4, ATT_VROW = 272, ATT_STAGE = ATT_TILE * (ATT_KROW + ATT_VROW);
+
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) { return bf16_bits(lo) | ((uint32_t) bf16_bits(hi) << 16); }
+
+__global__ void __launch_bounds__(32 * ATT_MMA_WARPS) attn_split_mma_kernel(AttnArgs a, const float* __restrict__ q, KvView kv,
+                                                                            const RowInfo* __restrict__ ri, float* __restrict__ part) {
+    extern __shared__ __align__(16) unsigned char att_smem[];      // ATT_MMA_WARPS stages, later the warps' states
+    const int split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, q4 = lane & 3, r0 = lane >> 2;
+    const int group = a.n_head / a.n_kv;
+    unsigned char* stage = att_smem + (size_t) warp * ATT_STAGE;
+    unsigned char* kt = stage, *vt = stage + ATT_TILE * ATT_KROW;
+    grid_dependents_go();
+    grid_dependency_wait();
+    // the group's queries as the A fragments of the 8 steps over the 128 dims: rows r0 and r0 + 8 (zero beyond the group)
+    uint32_t qa[8][4];
+    {
+        const float* q0 = q + ((size_t) t * a.n_head + kvh * group + r0) * ATT_HD;
+        const float* q1 = q0 + 8 * ATT_HD;
+        const bool h0 = r0 < group, h1 = r0 + 8 < group;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int d = 16 * j + 2 * q4;
+            const float2 z = make_float2(0.0f, 0.0f);
+            const float2 x0 = h0 ? *(const float2*) (q0 + d) : z, x1 = h1 ? *(const float2*) (q1 + d) : z;
+            const float2 x2 = h0 ? *(const float2*) (q0 + d + 8) : z, x3 = h1 ? *(const float2*) (q1 + d + 8) : z;
+            qa[j][0] = pack_bf16x2(x0.x, x0.y); qa[j][1] = pack_bf16x2(x1.x, x1.y);
+            qa[j][2] = pack_bf16x2(x2.x, x2.y); qa[j][3] = pack_bf16x2(x3.x, x3.y);
+        }
+    }
+    const int pos = ri[t].pos, kv0 = ri[t].kv0;
+    const int nsr = a.chunk > 0 ? min(a.n_splits, (pos + a.chunk) / a.chunk) : 1;
+    const int chunk = (pos + nsr) / nsr;
+    const int p0 = split * chunk, p1 = min(pos + 1, p0 + chunk);
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
+    float o[16][4];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    for (int p = p0 + warp * ATT_TILE; p < p1; p += ATT_MMA_WARPS * ATT_TILE) {
+        __syncwarp();      // the previous step's reads of the stage are done
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {      // 32 rows x 16 pieces of K, the same of V
+            const int idx = i * 32 + lane, r = idx >> 4, piece = idx & 15;
+            const int row = kv0 + min(p + r, p1 - 1);
+            attn_cp16(kt + r * ATT_KROW + piece * 16, kv_row(kv, 0, row, a.n_kv, kvh) + piece * 8);
+            attn_cp16(vt + r * ATT_VROW + piece * 16, kv_row(kv, 1, row, a.n_kv, kvh) + piece * 8);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncwarp();
+        // scores: four tiles of 8 keys, rows = heads
+        float sfr[4][4];
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            sfr[nt][0] = sfr[nt][1] = sfr[nt][2] = sfr[nt][3] = 0.0f;
+            const unsigned char* kr = kt + (nt * 8 + r0) * ATT_KROW + 4 * q4;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) mma_bf16(sfr[nt], qa[j], *(const uint32_t*) (kr + 32 * j), *(const uint32_t*) (kr + 32 * j + 16));
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            const int key = p + nt * 8 + 2 * q4;
+            const bool v0 = key < p1, v1 = key + 1 < p1;
+            sfr[nt][0] = v0 ? sfr[nt][0] * a.scale : -INFINITY; sfr[nt][1] = v1 ? sfr[nt][1] * a.scale : -INFINITY;
+            sfr[nt][2] = v0 ? sfr[nt][2] * a.scale : -INFINITY; sfr[nt][3] = v1 ? sfr[nt][3] * a.scale : -INFINITY;
+            mx0 = fmaxf(mx0, fmaxf(sfr[nt][0], sfr[nt][1]));
+            mx1 = fmaxf(mx1, fmaxf(sfr[nt][2], sfr[nt][3]));
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xFFFFFFFFu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xFFFFFFFFu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xFFFFFFFFu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xFFFFFFFFu, mx1, 2));
+        mx0 = fmaxf(mx0, m0); mx1 = fmaxf(mx1, m1);      // finite: a step's first key is always valid
+        const float cor0 = expf(m0 - mx0), cor1 = expf(m1 - mx1);
+        m0 = mx0; m1 = mx1;
+        l0 *= cor0; l1 *= cor1;
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            sfr[nt][0] = expf(sfr[nt][0] - mx0); sfr[nt][1] = expf(sfr[nt][1] - mx0);
+            sfr[nt][2] = expf(sfr[nt][2] - mx1); sfr[nt][3] = expf(sfr[nt][3] - mx1);
+            l0 += sfr[nt][0] + sfr[nt][1];
+            l1 += sfr[nt][2] + sfr[nt][3];
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) { o[i][0] *= cor0; o[i][1] *= cor0; o[i][2] *= cor1; o[i][3] *= cor1; }
+        // values: two steps of 16 keys; the weights' C fragments are the A fragments
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) {
+            // a weight as two bf16 terms, hi + lo (16 significant bits): one bf16 term alone moves an output by up to a third
+            // of its own bf16 unit, which after the two roundings of the gate shows as two-unit differences
+            uint32_t pa[4], pb[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float x0 = sfr[2 * ks + (i >> 1)][2 * (i & 1)], x1 = sfr[2 * ks + (i >> 1)][2 * (i & 1) + 1];
+                const float h0 = bf16_round(x0), h1 = bf16_round(x1);
+                pa[i] = pack_bf16x2(h0, h1);
+                pb[i] = pack_bf16x2(x0 - h0, x1 - h1);
+            }
+            // lane -> the row of the 8 x 8 block it addresses: blocks 0 / 1 = keys 0-7 / 8-15 of dims n0..n0+7, 2 / 3 of n0+8..
+            const unsigned char* vr = vt + (16 * ks + (lane & 7) + ((lane >> 3) & 1) * 8) * ATT_VROW + (lane >> 4) * 16;
+#pragma unroll
+            for (int nd = 0; nd < 16; nd += 2) {
+                uint32_t b0, b1, b2, b3;
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3)
+                             : "r"((unsigned) __cvta_generic_to_shared(vr + nd * 16)));
+                mma_bf16(o[nd], pa, b0, b1);
+                mma_bf16(o[nd], pb, b0, b1);
+                mma_bf16(o[nd + 1], pa, b2, b3);
+                mma_bf16(o[nd + 1], pb, b2, b3);
+            }
+        }
+    }
+    l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 1); l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 2);
+    l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 1); l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 2);
+    // the warp's state into its own stage: [16 heads][130] = m, l, acc
+    __syncwarp();
+    float* mine = (float*) stage;
+    if (q4 == 0) { mine[r0 * 130] = m0; mine[r0 * 130 + 1] = l0; mine[(r0 + 8) * 130] = m1; mine[(r0 + 8) * 130 + 1] = l1; }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const int d = 8 * i + 2 * q4;
+        mine[r0 * 130 + 2 + d] = o[i][0]; mine[r0 * 130 + 2 + d + 1] = o[i][1];
+        mine[(r0 + 8) * 130 + 2 + d] = o[i][2]; mine[(r0 + 8) * 130 + 2 + d + 1] = o[i][3];
+    }
+    __syncthreads();
+    // merge the warps' states: thread d of the block handles dim d of every head
+    const int d = threadIdx.x;
+    for (int h = 0; h < group; ++h) {
+        float m = -INFINITY;
+        for (int w = 0; w < ATT_MMA_WARPS; ++w) m = fmaxf(m, ((const float*) (att_smem + (size_t) w * ATT_STAGE))[h * 130]);
+        float l = 0.0f, acc = 0.0f;
+        for (int w = 0; w < ATT_MMA_WARPS; ++w) {
+            const float* st = (const float*) (att_smem + (size_t) w * ATT_STAGE) + h * 130;
+            if (st[0] == -INFINITY) continue;
+            const float c = expf(st[0] - m);
+            l = fmaf(st[1], c, l);
+            acc = fmaf(st[2 + d], c, acc);
+        }
+        float* pp = part + (((size_t) t * a.n_head + kvh * group + h) * a.n_splits + split) * (ATT_HD + 2);
+        if (d == 0) { pp[0] = m; pp[1] = l; }
+        pp[2 + d] = acc;
+    }
+}
+
 __device__ __forceinline__ float softplus_ln2(float g) {   // softplus with beta = ln 2 in f32, then BF16
     const float gx = g * 0.69314718055994531f;
     return bf16_round((fmaxf(gx, 0.0f) + logf(1.0f + expf(-fabsf(gx)))) / 0.69314718055994531f);
@@ -140,7 +297,13 @@ __global__ void __launch_bounds__(ATT_HD) attn_reduce_kernel(AttnArgs a, const f
 
 using namespace nsl;
 
+static int g_attn_variant = 1;   // 1 (default): the tensor-core pass; 0: the scalar pass (one warp per query head)
+
 extern "C" {
+
+// Picks the form of kc_attn's split pass (1, the default: tensor cores; 0: scalar).  Both meet the same bound; for tests
+// and timing.
+void nsl_attn_set_variant(int v) { g_attn_variant = v ? 1 : 0; }
 
 void kc_attn(cudaStream_t s, AttnArgs a, const float* q, KvView kv, const RowInfo* ri, float* part, const float* g, float* o, int T) {
     if (T < 1) return;
@@ -152,7 +315,19 @@ void kc_attn(cudaStream_t s, AttnArgs a, const float* q, KvView kv, const RowInf
                   a.n_kv, (int) ATT_MAX_GROUP, a.n_splits, a.chunk);
         return;
     }
-    launch(attn_split_kernel, dim3((unsigned) a.n_splits, (unsigned) a.n_kv, (unsigned) T), 32 * group, 0, s, a, q, kv, ri, part);
+    if (g_attn_variant == 1) {
+        static bool attr_set[16];
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (!attr_set[dev & 15]) {
+            cudaFuncSetAttribute(attn_split_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_MMA_WARPS * ATT_STAGE);
+            attr_set[dev & 15] = true;
+        }
+        launch(attn_split_mma_kernel, dim3((unsigned) a.n_splits, (unsigned) a.n_kv, (unsigned) T), 32 * ATT_MMA_WARPS,
+               (size_t) ATT_MMA_WARPS * ATT_STAGE, s, a, q, kv, ri, part);
+    } else {
+        launch(attn_split_kernel, dim3((unsigned) a.n_splits, (unsigned) a.n_kv, (unsigned) T), 32 * group, 0, s, a, q, kv, ri, part);
+    }
     PdlScope chain(true);      // the reduction's blocks come in while the split pass drains
     launch(attn_reduce_kernel, dim3((unsigned) a.n_head, (unsigned) T), ATT_HD, 0, s, a, (const float*) part, g, o);
     count_launch(2);
