@@ -584,6 +584,10 @@ def run_lmhead(args):
                                    "us_per_launch": mv_us, "bytes_per_launch": nbytes}}))
 
 
+ATTN_FORMS = {0: "attn_split_kernel", 1: "attn_flat_mma_kernel<2>", 2: "attn_split_mma_kernel<2>", 3: "attn_flat_mma_kernel<3>",
+              4: "attn_flat_mma_kernel<2>, two blocks an SM"}
+
+
 def run_attn(args):
     """Not the headline: decode attention of the reference's config 4 (GQA 16 query / 2 KV heads of 128, BF16 cache of 4096
     positions, 32 sequences = 134 MB of K and V per layer), an HBM-bound kernel."""
@@ -591,8 +595,9 @@ def run_attn(args):
     from nanoseedlm_b200 import lib as L
     lib = L.load()
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
-    NH, NKV, CTX, NSEQ, NS, NL = 16, 2, 4096, 32, int(os.environ.get("NSL_ATTN_SPLITS", "16")), 3
-    lib.nsl_attn_set_variant(int(os.environ.get("NSL_ATTN_VARIANT", "1")))
+    NH, NKV, CTX, NSEQ, NS, NL = 16, 2, 4096, 32, int(os.environ.get("NSL_ATTN_SPLITS", "32")), 3      # 32 splits: the reference host's choice for 32 rows of 4096 keys
+    variant = int(os.environ.get("NSL_ATTN_VARIANT", "1"))
+    lib.nsl_attn_set_variant(variant)
     K, W = args.steps, max(args.warmup, 3)
     gen = torch.Generator(device="cuda").manual_seed(5)
     caches = [(torch.randn(NSEQ * CTX, NKV, 128, generator=gen, device="cuda").to(torch.bfloat16),
@@ -639,7 +644,7 @@ def run_attn(args):
                       "data": "synthetic", "gpu_launches": 2 * K, "clocks": clocks.summary(),
                       "config": {"workload": f"decode attention, {NH} query / {NKV} KV heads of 128, BF16 cache of {CTX} positions x {NSEQ} "
                                              f"sequences ({nbytes / 1e6:.0f} MB per layer), {NS} splits; {NL} layers rotated", "tokens": NSEQ},
-                      "roofline": {"bound": "hbm", "kernel": "attn_split_kernel + attn_reduce_kernel (kc_attn)", "achieved": gbs,
+                      "roofline": {"bound": "hbm", "kernel": ATTN_FORMS.get(variant, ATTN_FORMS[1]) + " + attn_reduce_kernel (kc_attn)", "achieved": gbs,
                                    "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"], "peak_kind": kind, "traffic": None,
                                    "bytes_per_step": nbytes}}))
 

@@ -114,30 +114,79 @@ __global__ void __launch_bounds__(32 * ATT_MAX_GROUP) attn_split_kernel(AttnArgs
 // One warp serves ALL query heads of the KV head: they are the 16 rows of an mma.sync.m16n8k16 (bf16 in, f32 accumulate;
 // rows beyond the group are zero).  Queries are bf16-valued, so the score products are exact and the softmax scale is
 // applied to the f32 sums; the weights enter the second product as two bf16 terms (hi + lo: 16 significant bits; their
-// sum l is kept in f32).  Per step of 32 keys a warp issues 32 MMAs for the scores and 64 for the values instead of
-// ~5000 scalar instructions for the group.  The warps of a block take the split's steps in turn, each with its own running (m, l, acc) and its own K / V
-// stage in shared memory (rows 272 bytes apart: the fragment reads and ldmatrix touch distinct banks); at the end the
-// warps' states are merged through the same shared memory.
-constexpr int ATT_MMA_WARPS = 4, ATT_VROW = 272, ATT_STAGE = ATT_TILE * (ATT_KROW + ATT_VROW);
+// sum l is kept in f32).  Per step of 16 keys a warp issues 16 MMAs for the scores and 32 for the values instead of
+// ~2500 scalar instructions for the group.  The warps of a block take the split's steps in turn, each with its own running
+// (m, l, acc) and its own two-slot ring of K / V rows in shared memory (the next step's rows fly while this one is
+// computed; rows 272 bytes apart: the fragment reads and ldmatrix touch distinct banks); at the end the warps' states are
+// merged through the same shared memory.
+constexpr int ATT_MMA_WARPS = 4, ATT_VROW = 272, ATT_MT = 16, ATT_SLOT = ATT_MT * (ATT_KROW + ATT_VROW);
+constexpr int ATT_MAX_ROWS = 1024;      // rows of a step in the balanced form (the reference's rows x splits <= 1024)
+static_assert(2 * ATT_SLOT >= ATT_MAX_GROUP * 130 * 4, "a warp's ring holds its final state");
+static_assert(32 * ATT_MMA_WARPS == ATT_HD, "the merge gives a thread one dim");
 
 __device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
     asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) { return bf16_bits(lo) | ((uint32_t) bf16_bits(hi) << 16); }
+// Two f32 to a bf16 pair, round to nearest even (lo in bits 0-15).
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+__device__ __forceinline__ float ex2_approx(float x) {      // 2^x, relative error 2^-22; 2^-inf = 0
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ void attn_cp16s(unsigned smem, const void* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem), "l"(gmem) : "memory");
+}
 
-__global__ void __launch_bounds__(32 * ATT_MMA_WARPS) attn_split_mma_kernel(AttnArgs a, const float* __restrict__ q, KvView kv,
-                                                                            const RowInfo* __restrict__ ri, float* __restrict__ part) {
-    extern __shared__ __align__(16) unsigned char att_smem[];      // ATT_MMA_WARPS stages, later the warps' states
-    const int split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
+// The 16 K rows and 16 V rows of the step at key p into a slot: 32 lanes x 8 pieces of 16 bytes each (rows beyond the range
+// repeat its last row; their scores are masked).  Always one cp.async group, empty when the step lies beyond the range.
+__device__ __forceinline__ void attn_fill_slot(unsigned char* slot, const KvView& kv, int n_kv, int kvh, int kv0, int p, int p1, int lane) {
+    if (p < p1) {
+        const int rl = lane >> 4, piece = lane & 15;
+        const unsigned sk = (unsigned) __cvta_generic_to_shared(slot) + rl * ATT_KROW + piece * 16, sv = sk + ATT_MT * ATT_KROW;
+        const int row0 = kv0 + p;
+        if (p + ATT_MT <= p1 && (row0 + ATT_MT <= kv.nv || row0 >= kv.nv)) {      // 16 whole rows of one segment: one address, strides
+            const unsigned char* kb = (const unsigned char*) (kv_row(kv, 0, row0 + rl, n_kv, kvh) + piece * 8);
+            const unsigned char* vb = (const unsigned char*) (kv_row(kv, 1, row0 + rl, n_kv, kvh) + piece * 8);
+            const size_t two_rows = (size_t) n_kv * (2 * ATT_HD * 2);
+#pragma unroll
+            for (int i = 0; i < ATT_MT / 2; ++i) {
+                attn_cp16s(sk + i * 2 * ATT_KROW, kb + i * two_rows);
+                attn_cp16s(sv + i * 2 * ATT_VROW, vb + i * two_rows);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < ATT_MT / 2; ++i) {
+                const int row = kv0 + min(p + 2 * i + rl, p1 - 1);
+                attn_cp16s(sk + i * 2 * ATT_KROW, kv_row(kv, 0, row, n_kv, kvh) + piece * 8);
+                attn_cp16s(sv + i * 2 * ATT_VROW, kv_row(kv, 1, row, n_kv, kvh) + piece * 8);
+            }
+        }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+// Keys [p0, p1) of row t's cache for the query heads of KV head kvh, by the whole block: the warps take the steps of 16 keys
+// in turn, merge their states and write the group's partials (m, l, acc[128]) at pp, pp + head_stride, ...
+// NSLOT = slots of a warp's ring (steps in flight + the one in use).  Ends with the block in step (shared memory reusable).
+template <int NSLOT>
+__device__ __forceinline__ void attn_keys(const AttnArgs& a, const float* __restrict__ q, const KvView& kv, int t, int kvh, int kv0,
+                                          int p0, int p1, unsigned char* att_smem, float* pp, size_t head_stride) {
+    constexpr int STAGE = NSLOT * ATT_SLOT, STRIDE = ATT_MMA_WARPS * ATT_MT;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, q4 = lane & 3, r0 = lane >> 2;
     const int group = a.n_head / a.n_kv;
-    unsigned char* stage = att_smem + (size_t) warp * ATT_STAGE;
-    unsigned char* kt = stage, *vt = stage + ATT_TILE * ATT_KROW;
-    grid_dependents_go();
-    grid_dependency_wait();
-    // the group's queries as the A fragments of the 8 steps over the 128 dims: rows r0 and r0 + 8 (zero beyond the group)
+    unsigned char* stage = att_smem + (size_t) warp * STAGE;
+    int p = p0 + warp * ATT_MT;
+#pragma unroll
+    for (int i = 0; i < NSLOT - 1; ++i) attn_fill_slot(stage + i * ATT_SLOT, kv, a.n_kv, kvh, kv0, p + i * STRIDE, p1, lane);
+    // the group's queries as the A fragments of the 8 steps over the 128 dims: rows r0 and r0 + 8 (zero beyond the group);
+    // the first rows of K and V fly meanwhile
     uint32_t qa[8][4];
     {
         const float* q0 = q + ((size_t) t * a.n_head + kvh * group + r0) * ATT_HD;
@@ -153,94 +202,98 @@ __global__ void __launch_bounds__(32 * ATT_MMA_WARPS) attn_split_mma_kernel(Attn
             qa[j][2] = pack_bf16x2(x2.x, x2.y); qa[j][3] = pack_bf16x2(x3.x, x3.y);
         }
     }
-    const int pos = ri[t].pos, kv0 = ri[t].kv0;
-    const int nsr = a.chunk > 0 ? min(a.n_splits, (pos + a.chunk) / a.chunk) : 1;
-    const int chunk = (pos + nsr) / nsr;
-    const int p0 = split * chunk, p1 = min(pos + 1, p0 + chunk);
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
     float o[16][4];
 #pragma unroll
     for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
-    for (int p = p0 + warp * ATT_TILE; p < p1; p += ATT_MMA_WARPS * ATT_TILE) {
-        __syncwarp();      // the previous step's reads of the stage are done
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {      // 32 rows x 16 pieces of K, the same of V
-            const int idx = i * 32 + lane, r = idx >> 4, piece = idx & 15;
-            const int row = kv0 + min(p + r, p1 - 1);
-            attn_cp16(kt + r * ATT_KROW + piece * 16, kv_row(kv, 0, row, a.n_kv, kvh) + piece * 8);
-            attn_cp16(vt + r * ATT_VROW + piece * 16, kv_row(kv, 1, row, a.n_kv, kvh) + piece * 8);
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
+    const float scale2 = a.scale * 1.4426950408889634f;
+    int cur = 0, nxt = NSLOT - 1;      // the slot in use; the slot the step NSLOT - 1 ahead goes to (its reads ended with the
+                                       // previous step's closing __syncwarp)
+    for (; p < p1; p += STRIDE) {
+        attn_fill_slot(stage + nxt * ATT_SLOT, kv, a.n_kv, kvh, kv0, p + (NSLOT - 1) * STRIDE, p1, lane);
+        asm volatile("cp.async.wait_group %0;" ::"n"(NSLOT - 1) : "memory");
         __syncwarp();
-        // scores: four tiles of 8 keys, rows = heads
-        float sfr[4][4];
+        const unsigned char* kt = stage + cur * ATT_SLOT, *vt = kt + ATT_MT * ATT_KROW;
+        nxt = cur;
+        cur = cur + 1 == NSLOT ? 0 : cur + 1;
+        // scores: two tiles of 8 keys, rows = heads; two accumulation chains a tile (even and odd dim steps)
+        float sfr[2][4];
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt) {
+        for (int nt = 0; nt < 2; ++nt) {
+            float odd[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             sfr[nt][0] = sfr[nt][1] = sfr[nt][2] = sfr[nt][3] = 0.0f;
             const unsigned char* kr = kt + (nt * 8 + r0) * ATT_KROW + 4 * q4;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) mma_bf16(sfr[nt], qa[j], *(const uint32_t*) (kr + 32 * j), *(const uint32_t*) (kr + 32 * j + 16));
+            for (int j = 0; j < 8; j += 2) {
+                mma_bf16(sfr[nt], qa[j], *(const uint32_t*) (kr + 32 * j), *(const uint32_t*) (kr + 32 * j + 16));
+                mma_bf16(odd, qa[j + 1], *(const uint32_t*) (kr + 32 * j + 32), *(const uint32_t*) (kr + 32 * j + 48));
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) sfr[nt][i] += odd[i];
         }
+        // softmax in the base-2 domain: t = score * scale * log2(e); m0 / m1 are the running maxima of t
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt) {
+        for (int nt = 0; nt < 2; ++nt) {
             const int key = p + nt * 8 + 2 * q4;
             const bool v0 = key < p1, v1 = key + 1 < p1;
-            sfr[nt][0] = v0 ? sfr[nt][0] * a.scale : -INFINITY; sfr[nt][1] = v1 ? sfr[nt][1] * a.scale : -INFINITY;
-            sfr[nt][2] = v0 ? sfr[nt][2] * a.scale : -INFINITY; sfr[nt][3] = v1 ? sfr[nt][3] * a.scale : -INFINITY;
+            sfr[nt][0] = v0 ? sfr[nt][0] * scale2 : -INFINITY; sfr[nt][1] = v1 ? sfr[nt][1] * scale2 : -INFINITY;
+            sfr[nt][2] = v0 ? sfr[nt][2] * scale2 : -INFINITY; sfr[nt][3] = v1 ? sfr[nt][3] * scale2 : -INFINITY;
             mx0 = fmaxf(mx0, fmaxf(sfr[nt][0], sfr[nt][1]));
             mx1 = fmaxf(mx1, fmaxf(sfr[nt][2], sfr[nt][3]));
         }
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xFFFFFFFFu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xFFFFFFFFu, mx0, 2));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xFFFFFFFFu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xFFFFFFFFu, mx1, 2));
         mx0 = fmaxf(mx0, m0); mx1 = fmaxf(mx1, m1);      // finite: a step's first key is always valid
-        const float cor0 = expf(m0 - mx0), cor1 = expf(m1 - mx1);
+        const float cor0 = ex2_approx(m0 - mx0), cor1 = ex2_approx(m1 - mx1);
         m0 = mx0; m1 = mx1;
         l0 *= cor0; l1 *= cor1;
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt) {
-            sfr[nt][0] = expf(sfr[nt][0] - mx0); sfr[nt][1] = expf(sfr[nt][1] - mx0);
-            sfr[nt][2] = expf(sfr[nt][2] - mx1); sfr[nt][3] = expf(sfr[nt][3] - mx1);
+        for (int nt = 0; nt < 2; ++nt) {
+            sfr[nt][0] = ex2_approx(sfr[nt][0] - mx0); sfr[nt][1] = ex2_approx(sfr[nt][1] - mx0);
+            sfr[nt][2] = ex2_approx(sfr[nt][2] - mx1); sfr[nt][3] = ex2_approx(sfr[nt][3] - mx1);
             l0 += sfr[nt][0] + sfr[nt][1];
             l1 += sfr[nt][2] + sfr[nt][3];
         }
+        if (cor0 != 1.0f || cor1 != 1.0f) {      // the running maxima rarely move after a range's first steps
 #pragma unroll
-        for (int i = 0; i < 16; ++i) { o[i][0] *= cor0; o[i][1] *= cor0; o[i][2] *= cor1; o[i][3] *= cor1; }
-        // values: two steps of 16 keys; the weights' C fragments are the A fragments
-#pragma unroll
-        for (int ks = 0; ks < 2; ++ks) {
-            // a weight as two bf16 terms, hi + lo (16 significant bits): one bf16 term alone moves an output by up to a third
-            // of its own bf16 unit, which after the two roundings of the gate shows as two-unit differences
-            uint32_t pa[4], pb[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float x0 = sfr[2 * ks + (i >> 1)][2 * (i & 1)], x1 = sfr[2 * ks + (i >> 1)][2 * (i & 1) + 1];
-                const float h0 = bf16_round(x0), h1 = bf16_round(x1);
-                pa[i] = pack_bf16x2(h0, h1);
-                pb[i] = pack_bf16x2(x0 - h0, x1 - h1);
-            }
-            // lane -> the row of the 8 x 8 block it addresses: blocks 0 / 1 = keys 0-7 / 8-15 of dims n0..n0+7, 2 / 3 of n0+8..
-            const unsigned char* vr = vt + (16 * ks + (lane & 7) + ((lane >> 3) & 1) * 8) * ATT_VROW + (lane >> 4) * 16;
-#pragma unroll
-            for (int nd = 0; nd < 16; nd += 2) {
-                uint32_t b0, b1, b2, b3;
-                asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
-                             : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3)
-                             : "r"((unsigned) __cvta_generic_to_shared(vr + nd * 16)));
-                mma_bf16(o[nd], pa, b0, b1);
-                mma_bf16(o[nd], pb, b0, b1);
-                mma_bf16(o[nd + 1], pa, b2, b3);
-                mma_bf16(o[nd + 1], pb, b2, b3);
-            }
+            for (int i = 0; i < 16; ++i) { o[i][0] *= cor0; o[i][1] *= cor0; o[i][2] *= cor1; o[i][3] *= cor1; }
         }
+        // values: the 16 keys are one MMA step; the weights' C fragments are the A fragments, as two bf16 terms, hi + lo
+        // (16 significant bits): one bf16 term alone moves an output by up to a third of its own bf16 unit, which after the
+        // two roundings of the gate shows as two-unit differences
+        uint32_t pa[4], pb[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float x0 = sfr[i >> 1][2 * (i & 1)], x1 = sfr[i >> 1][2 * (i & 1) + 1];
+            pa[i] = pack_bf16x2(x0, x1);
+            pb[i] = pack_bf16x2(x0 - bf_lo(pa[i]), x1 - bf_hi(pa[i]));
+        }
+        // lane -> the row of the 8 x 8 block it addresses: blocks 0 / 1 = keys 0-7 / 8-15 of dims n0..n0+7, 2 / 3 of n0+8..
+        const unsigned char* vr = vt + ((lane & 7) + ((lane >> 3) & 1) * 8) * ATT_VROW + (lane >> 4) * 16;
+#pragma unroll
+        for (int nd = 0; nd < 16; nd += 2) {
+            uint32_t b0, b1, b2, b3;
+            asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3)
+                         : "r"((unsigned) __cvta_generic_to_shared(vr + nd * 16)));
+            mma_bf16(o[nd], pa, b0, b1);
+            mma_bf16(o[nd], pb, b0, b1);
+            mma_bf16(o[nd + 1], pa, b2, b3);
+            mma_bf16(o[nd + 1], pb, b2, b3);
+        }
+        __syncwarp();      // this slot's reads are done before a later step refills it
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");      // only empty groups are left
     l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 1); l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 2);
     l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 1); l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 2);
-    // the warp's state into its own stage: [16 heads][130] = m, l, acc
+    // the warp's state into its own ring: [16 heads][130] = m, l, acc
     __syncwarp();
     float* mine = (float*) stage;
-    if (q4 == 0) { mine[r0 * 130] = m0; mine[r0 * 130 + 1] = l0; mine[(r0 + 8) * 130] = m1; mine[(r0 + 8) * 130 + 1] = l1; }
+    if (q4 == 0) {      // the maxima back in natural units (-inf stays -inf)
+        mine[r0 * 130] = m0 * 0.69314718055994531f; mine[r0 * 130 + 1] = l0;
+        mine[(r0 + 8) * 130] = m1 * 0.69314718055994531f; mine[(r0 + 8) * 130 + 1] = l1;
+    }
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
         const int d = 8 * i + 2 * q4;
@@ -252,18 +305,122 @@ __global__ void __launch_bounds__(32 * ATT_MMA_WARPS) attn_split_mma_kernel(Attn
     const int d = threadIdx.x;
     for (int h = 0; h < group; ++h) {
         float m = -INFINITY;
-        for (int w = 0; w < ATT_MMA_WARPS; ++w) m = fmaxf(m, ((const float*) (att_smem + (size_t) w * ATT_STAGE))[h * 130]);
+        for (int w = 0; w < ATT_MMA_WARPS; ++w) m = fmaxf(m, ((const float*) (att_smem + (size_t) w * STAGE))[h * 130]);
         float l = 0.0f, acc = 0.0f;
         for (int w = 0; w < ATT_MMA_WARPS; ++w) {
-            const float* st = (const float*) (att_smem + (size_t) w * ATT_STAGE) + h * 130;
+            const float* st = (const float*) (att_smem + (size_t) w * STAGE) + h * 130;
             if (st[0] == -INFINITY) continue;
             const float c = expf(st[0] - m);
             l = fmaf(st[1], c, l);
             acc = fmaf(st[2 + d], c, acc);
         }
-        float* pp = part + (((size_t) t * a.n_head + kvh * group + h) * a.n_splits + split) * (ATT_HD + 2);
-        if (d == 0) { pp[0] = m; pp[1] = l; }
-        pp[2 + d] = acc;
+        float* ph = pp + h * head_stride;
+        if (d == 0) { ph[0] = m; ph[1] = l; }
+        ph[2 + d] = acc;
+    }
+    __syncthreads();
+}
+
+// One block per (split, KV head, row): the split's keys as the reference cuts them.
+template <int NSLOT>
+__global__ void __launch_bounds__(32 * ATT_MMA_WARPS) attn_split_mma_kernel(AttnArgs a, const float* __restrict__ q, KvView kv,
+                                                                            const RowInfo* __restrict__ ri, float* __restrict__ part) {
+    extern __shared__ __align__(16) unsigned char att_smem[];      // the warps' rings, later their states
+    const int split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
+    const int group = a.n_head / a.n_kv;
+    grid_dependents_go();
+    grid_dependency_wait();
+    const int pos = ri[t].pos, kv0 = ri[t].kv0;
+    const int nsr = a.chunk > 0 ? min(a.n_splits, (pos + a.chunk) / a.chunk) : 1;
+    const int chunk = (pos + nsr) / nsr;
+    const int p0 = split * chunk, p1 = min(pos + 1, p0 + chunk);
+    attn_keys<NSLOT>(a, q, kv, t, kvh, kv0, p0, p1, att_smem, part + (((size_t) t * a.n_head + kvh * group) * a.n_splits + split) * (ATT_HD + 2),
+                     (size_t) a.n_splits * (ATT_HD + 2));
+}
+
+// ---- the balanced form ------------------------------------------------------------------------------------------------
+// The step's work is cut into units of 16 keys, numbered row by row, KV head by KV head; block b takes units
+// [b * per, (b + 1) * per), whichever rows they belong to, so every block reads the same number of bytes whatever the
+// rows' lengths and the caller's split count.  A (row, KV head) pair's units lie in consecutive blocks; the j-th of them
+// writes the pair's partial j, and `per` is raised until no pair has more partials than the caller's buffer holds
+// (n_splits per head).  Both kernels derive the same plan from the rows' positions.
+struct AttnPlan {
+    int total;      // units of the step (all rows, all KV heads)
+    int per;        // units per block
+};
+
+// u(t) = units of row t; pre[t] = u(0) + ... + u(t - 1), pre[T] = their sum.  Called by all threads of a 128-thread block.
+__device__ __forceinline__ AttnPlan attn_plan(const RowInfo* __restrict__ ri, int T, int n_kv, int n_splits, int n_blocks, int* pre) {
+    __shared__ int wsum[ATT_MMA_WARPS], wmax[ATT_MMA_WARPS];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int each = (T + 32 * ATT_MMA_WARPS - 1) / (32 * ATT_MMA_WARPS);      // <= 8 rows a thread
+    int sum = 0, mx = 0;
+    for (int i = 0; i < each; ++i) {
+        const int r = tid * each + i;
+        const int u = r < T ? (max(ri[r].pos, 0) + ATT_MT) / ATT_MT : 0;
+        sum += u;
+        mx = max(mx, u);
+    }
+    int incl = sum;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const int v = __shfl_up_sync(0xFFFFFFFFu, incl, off);
+        if (lane >= off) incl += v;
+        mx = max(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, off));
+    }
+    if (lane == 31) { wsum[warp] = incl; wmax[warp] = mx; }
+    __syncthreads();
+    int before = 0, rows_total = 0, max_u = 0;
+#pragma unroll
+    for (int w = 0; w < ATT_MMA_WARPS; ++w) {
+        if (w < warp) before += wsum[w];
+        rows_total += wsum[w];
+        max_u = max(max_u, wmax[w]);
+    }
+    int run = before + incl - sum;
+    for (int i = 0; i < each; ++i) {
+        const int r = tid * each + i;
+        if (r < T) {
+            pre[r] = run;
+            run += (max(ri[r].pos, 0) + ATT_MT) / ATT_MT;
+        }
+    }
+    if (tid == 0) pre[T] = rows_total;
+    __syncthreads();
+    AttnPlan pl;
+    pl.total = rows_total * n_kv;
+    pl.per = max((pl.total + n_blocks - 1) / n_blocks, ATT_MMA_WARPS);                   // every warp of a block has a step
+    pl.per = max(pl.per, (max_u - 1 + n_splits - 3) / (n_splits - 2));                    // a pair: <= (u - 1) / per + 2 partials
+    return pl;
+}
+
+template <int NSLOT>
+__global__ void __launch_bounds__(32 * ATT_MMA_WARPS) attn_flat_mma_kernel(AttnArgs a, const float* __restrict__ q, KvView kv,
+                                                                           const RowInfo* __restrict__ ri, float* __restrict__ part, int T) {
+    extern __shared__ __align__(16) unsigned char att_smem[];
+    __shared__ int pre[ATT_MAX_ROWS + 1];
+    const int group = a.n_head / a.n_kv;
+    grid_dependents_go();
+    grid_dependency_wait();
+    const AttnPlan pl = attn_plan(ri, T, a.n_kv, a.n_splits, (int) gridDim.x, pre);
+    int x = (int) blockIdx.x * pl.per;
+    const int xe = min(pl.total, x + pl.per);
+    while (x < xe) {
+        // the row of unit x: the last t with n_kv * pre[t] <= x
+        int lo = 0, hi = T - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (a.n_kv * pre[mid] <= x) lo = mid; else hi = mid - 1;
+        }
+        const int t = lo, u = pre[t + 1] - pre[t];
+        const int kvh = (x - a.n_kv * pre[t]) / u;
+        const int first = a.n_kv * pre[t] + kvh * u;      // the pair's first unit
+        const int end = min(xe, first + u);
+        const int pos = max(ri[t].pos, 0), kv0 = ri[t].kv0;
+        const int slot = (int) blockIdx.x - first / pl.per;
+        attn_keys<NSLOT>(a, q, kv, t, kvh, kv0, (x - first) * ATT_MT, min(pos + 1, (end - first) * ATT_MT), att_smem,
+                         part + (((size_t) t * a.n_head + kvh * group) * a.n_splits + slot) * (ATT_HD + 2), (size_t) a.n_splits * (ATT_HD + 2));
+        x = end;
     }
 }
 
@@ -272,21 +429,42 @@ __device__ __forceinline__ float softplus_ln2(float g) {   // softplus with beta
     return bf16_round((fmaxf(gx, 0.0f) + logf(1.0f + expf(-fabsf(gx)))) / 0.69314718055994531f);
 }
 
+// Merges a head's partials and applies the gate.  n_blocks = 0: the split form's n_splits partials (unused ones carry
+// m = -inf); otherwise the balanced form's, as many as the pair's units touch blocks.
 __global__ void __launch_bounds__(ATT_HD) attn_reduce_kernel(AttnArgs a, const float* __restrict__ part, const float* __restrict__ g,
-                                                             float* __restrict__ o) {
+                                                             float* __restrict__ o, const RowInfo* __restrict__ ri, int T, int n_blocks) {
+    __shared__ int pre[ATT_MAX_ROWS + 1];
     const int h = blockIdx.x, t = blockIdx.y, d = threadIdx.x;
     grid_dependents_go();
+    int n = a.n_splits;
+    if (n_blocks > 0) {      // the plan reads the rows' positions only: before the wait for the partials
+        const AttnPlan pl = attn_plan(ri, T, a.n_kv, a.n_splits, n_blocks, pre);
+        const int u = pre[t + 1] - pre[t], first = a.n_kv * pre[t] + (h / (a.n_head / a.n_kv)) * u;
+        n = (first + u - 1) / pl.per - first / pl.per + 1;
+    }
     grid_dependency_wait();
     const float* pp = part + ((size_t) t * a.n_head + h) * a.n_splits * (ATT_HD + 2);
-    float m = -INFINITY;
-    for (int s = 0; s < a.n_splits; ++s) m = fmaxf(m, pp[s * (ATT_HD + 2)]);
-    float l = 0.0f, acc = 0.0f;
-    for (int s = 0; s < a.n_splits; ++s) {
-        const float ms = pp[s * (ATT_HD + 2)];
-        if (ms == -INFINITY) continue;
-        const float c = expf(ms - m);
-        l = fmaf(pp[s * (ATT_HD + 2) + 1], c, l);
-        acc = fmaf(pp[s * (ATT_HD + 2) + 2 + d], c, acc);
+    __shared__ float pm[ATT_HD], pl[ATT_HD];      // the partials' (m, l): one load each, side by side
+    float m = -INFINITY, l = 0.0f, acc = 0.0f;
+    if (n <= ATT_HD) {
+        if (d < n) { pm[d] = pp[d * (ATT_HD + 2)]; pl[d] = pp[d * (ATT_HD + 2) + 1]; }
+        __syncthreads();
+        for (int s = 0; s < n; ++s) m = fmaxf(m, pm[s]);
+#pragma unroll 4
+        for (int s = 0; s < n; ++s) {      // an unused partial carries m = -inf, l = 0, acc = 0
+            const float c = pm[s] == -INFINITY ? 0.0f : expf(pm[s] - m);
+            l = fmaf(pl[s], c, l);
+            acc = fmaf(pp[s * (ATT_HD + 2) + 2 + d], c, acc);
+        }
+    } else {
+        for (int s = 0; s < n; ++s) m = fmaxf(m, pp[s * (ATT_HD + 2)]);
+        for (int s = 0; s < n; ++s) {
+            const float ms = pp[s * (ATT_HD + 2)];
+            if (ms == -INFINITY) continue;
+            const float c = expf(ms - m);
+            l = fmaf(pp[s * (ATT_HD + 2) + 1], c, l);
+            acc = fmaf(pp[s * (ATT_HD + 2) + 2 + d], c, acc);
+        }
     }
     const float att = bf16_round(acc / l);
     const size_t i = ((size_t) t * a.n_head + h) * ATT_HD + d;
@@ -297,13 +475,32 @@ __global__ void __launch_bounds__(ATT_HD) attn_reduce_kernel(AttnArgs a, const f
 
 using namespace nsl;
 
-static int g_attn_variant = 1;   // 1 (default): the tensor-core pass; 0: the scalar pass (one warp per query head)
+static int g_attn_variant = 1;   // 1 (default): tensor cores, balanced over the blocks; 2: tensor cores, one block per split;
+                                 // 3: as 1 with three-slot rings (two blocks an SM); 4: as 1 with two blocks an SM;
+                                 // 0: the scalar pass (one warp per query head)
+
+template <typename K>
+static void attn_smem_attr(K kernel, int bytes, bool* done) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!done[dev & 15]) {
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        done[dev & 15] = true;
+    }
+}
+
+static int attn_sm_count() {
+    static int n[16];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!n[dev & 15]) cudaDeviceGetAttribute(&n[dev & 15], cudaDevAttrMultiProcessorCount, dev);
+    return n[dev & 15] > 0 ? n[dev & 15] : 148;
+}
 
 extern "C" {
 
-// Picks the form of kc_attn's split pass (1, the default: tensor cores; 0: scalar).  Both meet the same bound; for tests
-// and timing.
-void nsl_attn_set_variant(int v) { g_attn_variant = v ? 1 : 0; }
+// Picks the form of kc_attn's first pass (see g_attn_variant).  All forms meet the same bound; for tests and timing.
+void nsl_attn_set_variant(int v) { g_attn_variant = v >= 0 && v <= 4 ? v : 1; }
 
 void kc_attn(cudaStream_t s, AttnArgs a, const float* q, KvView kv, const RowInfo* ri, float* part, const float* g, float* o, int T) {
     if (T < 1) return;
@@ -315,21 +512,29 @@ void kc_attn(cudaStream_t s, AttnArgs a, const float* q, KvView kv, const RowInf
                   a.n_kv, (int) ATT_MAX_GROUP, a.n_splits, a.chunk);
         return;
     }
-    if (g_attn_variant == 1) {
-        static bool attr_set[16];
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (!attr_set[dev & 15]) {
-            cudaFuncSetAttribute(attn_split_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_MMA_WARPS * ATT_STAGE);
-            attr_set[dev & 15] = true;
-        }
-        launch(attn_split_mma_kernel, dim3((unsigned) a.n_splits, (unsigned) a.n_kv, (unsigned) T), 32 * ATT_MMA_WARPS,
-               (size_t) ATT_MMA_WARPS * ATT_STAGE, s, a, q, kv, ri, part);
+    constexpr int SM2 = ATT_MMA_WARPS * 2 * ATT_SLOT, SM3 = ATT_MMA_WARPS * 3 * ATT_SLOT;
+    const bool flat = (g_attn_variant == 1 || g_attn_variant >= 3) && a.n_splits >= 3 && a.chunk > 0 && T <= ATT_MAX_ROWS;
+    int n_blocks = 0;
+    if (flat && g_attn_variant != 3) {
+        static bool done[16];
+        attn_smem_attr(attn_flat_mma_kernel<2>, SM2, done);
+        n_blocks = (g_attn_variant == 4 ? 2 : 3) * attn_sm_count();      // three blocks of 70 KB and 168 registers a thread fit an SM
+        launch(attn_flat_mma_kernel<2>, dim3((unsigned) n_blocks), 32 * ATT_MMA_WARPS, (size_t) SM2, s, a, q, kv, ri, part, T);
+    } else if (flat) {
+        static bool done[16];
+        attn_smem_attr(attn_flat_mma_kernel<3>, SM3, done);
+        n_blocks = 2 * attn_sm_count();
+        launch(attn_flat_mma_kernel<3>, dim3((unsigned) n_blocks), 32 * ATT_MMA_WARPS, (size_t) SM3, s, a, q, kv, ri, part, T);
+    } else if (g_attn_variant != 0) {
+        static bool done[16];
+        attn_smem_attr(attn_split_mma_kernel<2>, SM2, done);
+        launch(attn_split_mma_kernel<2>, dim3((unsigned) a.n_splits, (unsigned) a.n_kv, (unsigned) T), 32 * ATT_MMA_WARPS, (size_t) SM2, s,
+               a, q, kv, ri, part);
     } else {
         launch(attn_split_kernel, dim3((unsigned) a.n_splits, (unsigned) a.n_kv, (unsigned) T), 32 * group, 0, s, a, q, kv, ri, part);
     }
-    PdlScope chain(true);      // the reduction's blocks come in while the split pass drains
-    launch(attn_reduce_kernel, dim3((unsigned) a.n_head, (unsigned) T), ATT_HD, 0, s, a, (const float*) part, g, o);
+    PdlScope chain(true);      // the reduction's blocks come in while the first pass drains
+    launch(attn_reduce_kernel, dim3((unsigned) a.n_head, (unsigned) T), ATT_HD, 0, s, a, (const float*) part, g, o, ri, T, n_blocks);
     count_launch(2);
 }
 

@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 
 
 def run_case(nh, nkv, NP, pos, kv0, ns, chunk, gate=True, nv=None, seed=21):
-    for variant in (1, 0):      # the tensor-core pass and the scalar pass
+    for variant in (1, 2, 3, 4, 0):      # tensor cores (balanced blocks; a block per split; three-slot rings; two blocks an SM), the scalar pass
         run_variant(variant, nh, nkv, NP, pos, kv0, ns, chunk, gate, nv, seed)
 
 
@@ -45,6 +45,16 @@ def test_reference_case_gqa_8_over_2():
 @pytest.mark.parametrize("nh,nkv", [(16, 2), (4, 4), (32, 2), (3, 1)])
 def test_group_sizes(nh, nkv):
     run_case(nh, nkv, 700, [511, 0, 33, 64], [0, 600, 620, 512], 4, 128, seed=nh)
+
+
+def test_ragged_rows_as_the_reference_host_splits_them():
+    """12 rows of very different lengths, 32 splits of >= 128 keys (engine/mova_cuda.c:1040-1045): in the balanced form a
+    block's units span several rows and a long row's units many blocks."""
+    rng = np.random.default_rng(3)
+    pos = [2999, 0, 15, 16, 1500, 127, 128, 2047, 700, 31, 2998, 5]
+    run_case(8, 2, 12 * 3008, pos, [3008 * i for i in range(12)], 32, 128, seed=9)
+    for variant in (1, 3):
+        run_variant(variant, 16, 1, 6000, [5999], [0], 32, 188, True, None, 4)      # one row, one KV head: its units over 30 blocks
 
 
 def test_one_split_no_gate_and_two_segments():
