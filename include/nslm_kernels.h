@@ -168,8 +168,11 @@ typedef struct { KvSeg a, b; int32_t nv, fmt; } KvView;             /* positions
  * bf16(bf16(softmax(scale q.K) V) * bf16(softplus(g; beta = ln 2))) (g NULL: no gate).  BF16 caches only (kv.fmt =
  * KV_BF16); any group size n_head / n_kv up to 16. */
 void kc_attn(cudaStream_t s, AttnArgs a, const float* q, KvView kv, const RowInfo* ri, float* part, const float* g, float* o, int T);
-/* No counterpart in the reference: the form of kc_attn's split pass (1, the default: all heads of a KV head as the rows
- * of tensor-core products, the softmax weights entering the second product as bf16; 0: scalar, one warp per head). */
+/* No counterpart in the reference: the form of kc_attn's first pass.  1 (default): tensor cores (all heads of a KV head
+ * as the rows of the products), the step's keys dealt evenly to the blocks whatever a.n_splits asks (used when
+ * a.n_splits >= 3 and T <= 1024; otherwise form 2); 2: tensor cores, one block per (split, KV head, row); 3 and 4: form 1
+ * with three-slot rings / two blocks an SM; 0: scalar, one warp per head.  The partials' use of `part` is internal to
+ * the two kernels in every form and never exceeds the size above. */
 void nsl_attn_set_variant(int v);
 
 /* ---- greedy decoding over the LM head's logits ------------------------------------------------------------------------ */
