@@ -172,10 +172,30 @@ __device__ __forceinline__ void attn_fill_slot(unsigned char* slot, const KvView
     asm volatile("cp.async.commit_group;" ::: "memory");
 }
 
+__device__ __forceinline__ void ldsm_x4(uint32_t* r, const unsigned char* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((unsigned) __cvta_generic_to_shared(p)));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t* r, const unsigned char* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((unsigned) __cvta_generic_to_shared(p)));
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {      // an 8 x 8 tile of 16-bit values, transposed across the warp
+    uint32_t r;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(x));
+    return r;
+}
+
 // Keys [p0, p1) of row t's cache for the query heads of KV head kvh, by the whole block: the warps take the steps of 16 keys
 // in turn, merge their states and write the group's partials (m, l, acc[128]) at pp, pp + head_stride, ...
-// NSLOT = slots of a warp's ring (steps in flight + the one in use).  Ends with the block in step (shared memory reusable).
-template <int NSLOT>
+// NSLOT = slots of a warp's ring (steps in flight + the one in use); NT = tiles of 8 heads (1: groups of <= 8; 2: <= 16).
+// The products are the transposed ones, so that the 8 columns of a tile are heads and nothing is computed for absent rows:
+//   S^T [16 keys][8 heads]   = K [16 keys][128] . Q^T      A = K rows by ldmatrix, B = Q^T in registers (16 per tile)
+//   O^T [128 dims][8 heads] += V^T [dims][16 keys] . P^T   A = V rows by ldmatrix.trans, B = P^T: the C fragments of S^T
+//                                                          as bf16 pairs, transposed across the warp by movmatrix
+// A lane holds keys r0 and r0 + 8 of heads 2 q4 and 2 q4 + 1 of each tile: the maxima and sums of a head run over the 8
+// lanes of equal q4.  Ends with the block in step (shared memory reusable).
+template <int NSLOT, int NT>
 __device__ __forceinline__ void attn_keys(const AttnArgs& a, const float* __restrict__ q, const KvView& kv, int t, int kvh, int kv0,
                                           int p0, int p1, unsigned char* att_smem, float* pp, size_t head_stride) {
     constexpr int STAGE = NSLOT * ATT_SLOT, STRIDE = ATT_MMA_WARPS * ATT_MT;
@@ -185,144 +205,146 @@ __device__ __forceinline__ void attn_keys(const AttnArgs& a, const float* __rest
     int p = p0 + warp * ATT_MT;
 #pragma unroll
     for (int i = 0; i < NSLOT - 1; ++i) attn_fill_slot(stage + i * ATT_SLOT, kv, a.n_kv, kvh, kv0, p + i * STRIDE, p1, lane);
-    // the group's queries as the A fragments of the 8 steps over the 128 dims: rows r0 and r0 + 8 (zero beyond the group);
+    // Q^T as the B fragments of the 8 steps over the 128 dims: column r0 of a tile = head 8 nt + r0 (zero beyond the group);
     // the first rows of K and V fly meanwhile
-    uint32_t qa[8][4];
-    {
-        const float* q0 = q + ((size_t) t * a.n_head + kvh * group + r0) * ATT_HD;
-        const float* q1 = q0 + 8 * ATT_HD;
-        const bool h0 = r0 < group, h1 = r0 + 8 < group;
+    uint32_t qb[NT][8][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        const int head = 8 * nt + r0;
+        const float* qh = q + ((size_t) t * a.n_head + kvh * group + head) * ATT_HD;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const int d = 16 * j + 2 * q4;
             const float2 z = make_float2(0.0f, 0.0f);
-            const float2 x0 = h0 ? *(const float2*) (q0 + d) : z, x1 = h1 ? *(const float2*) (q1 + d) : z;
-            const float2 x2 = h0 ? *(const float2*) (q0 + d + 8) : z, x3 = h1 ? *(const float2*) (q1 + d + 8) : z;
-            qa[j][0] = pack_bf16x2(x0.x, x0.y); qa[j][1] = pack_bf16x2(x1.x, x1.y);
-            qa[j][2] = pack_bf16x2(x2.x, x2.y); qa[j][3] = pack_bf16x2(x3.x, x3.y);
+            const float2 x = head < group ? *(const float2*) (qh + d) : z, y = head < group ? *(const float2*) (qh + d + 8) : z;
+            qb[nt][j][0] = pack_bf16x2(x.x, x.y);
+            qb[nt][j][1] = pack_bf16x2(y.x, y.y);
         }
     }
-    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
-    float o[16][4];
+    float m[NT][2], l[NT][2], ot[NT][8][4];      // [.][0]: head 2 q4 of the tile, [.][1]: head 2 q4 + 1; m in base-2 units
 #pragma unroll
-    for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    for (int nt = 0; nt < NT; ++nt) {
+        m[nt][0] = m[nt][1] = -INFINITY;
+        l[nt][0] = l[nt][1] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ot[nt][i][0] = ot[nt][i][1] = ot[nt][i][2] = ot[nt][i][3] = 0.0f;
+    }
     const float scale2 = a.scale * 1.4426950408889634f;
+    // lane -> the row it addresses of the four 8 x 8 tiles of an ldmatrix.x4:
+    //   K (A = keys x dims):   tiles (keys 0-7 | 8-15) x (dims +0 | +8) in the order a0 a1 a2 a3 = (k lo, d lo) (k hi, d lo) (k lo, d hi) (k hi, d hi)
+    //   V (A = dims x keys, transposed on load): (d lo, k lo) (d hi, k lo) (d lo, k hi) (d hi, k hi)
+    const int k_off = ((lane & 7) + ((lane >> 3) & 1) * 8) * ATT_KROW + (lane >> 4) * 16;
+    const int v_off = ATT_MT * ATT_KROW + ((lane & 7) + (lane >> 4) * 8) * ATT_VROW + ((lane >> 3) & 1) * 16;
     int cur = 0, nxt = NSLOT - 1;      // the slot in use; the slot the step NSLOT - 1 ahead goes to (its reads ended with the
                                        // previous step's closing __syncwarp)
     for (; p < p1; p += STRIDE) {
         attn_fill_slot(stage + nxt * ATT_SLOT, kv, a.n_kv, kvh, kv0, p + (NSLOT - 1) * STRIDE, p1, lane);
         asm volatile("cp.async.wait_group %0;" ::"n"(NSLOT - 1) : "memory");
         __syncwarp();
-        const unsigned char* kt = stage + cur * ATT_SLOT, *vt = kt + ATT_MT * ATT_KROW;
+        const unsigned char* slot = stage + cur * ATT_SLOT;
         nxt = cur;
         cur = cur + 1 == NSLOT ? 0 : cur + 1;
-        // scores: two tiles of 8 keys, rows = heads; two accumulation chains a tile (even and odd dim steps)
-        float sfr[2][4];
+        // scores: two accumulation chains a tile (even and odd dim steps)
+        float s[NT][4], s2[NT][4];
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-            float odd[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            sfr[nt][0] = sfr[nt][1] = sfr[nt][2] = sfr[nt][3] = 0.0f;
-            const unsigned char* kr = kt + (nt * 8 + r0) * ATT_KROW + 4 * q4;
+        for (int nt = 0; nt < NT; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = s2[nt][0] = s2[nt][1] = s2[nt][2] = s2[nt][3] = 0.0f;
 #pragma unroll
-            for (int j = 0; j < 8; j += 2) {
-                mma_bf16(sfr[nt], qa[j], *(const uint32_t*) (kr + 32 * j), *(const uint32_t*) (kr + 32 * j + 16));
-                mma_bf16(odd, qa[j + 1], *(const uint32_t*) (kr + 32 * j + 32), *(const uint32_t*) (kr + 32 * j + 48));
+        for (int j = 0; j < 8; ++j) {
+            uint32_t ka[4];
+            ldsm_x4(ka, slot + k_off + 32 * j);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) mma_bf16((j & 1) ? s2[nt] : s[nt], ka, qb[nt][j][0], qb[nt][j][1]);
+        }
+        // softmax in the base-2 domain: x = score * scale * log2(e); keys r0 (elements 0, 1) and r0 + 8 (2, 3)
+        const bool v0 = p + r0 < p1, v1 = p + r0 + 8 < p1;
+        uint32_t ph[NT][2], pl[NT][2];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            s[nt][0] = v0 ? (s[nt][0] + s2[nt][0]) * scale2 : -INFINITY; s[nt][1] = v0 ? (s[nt][1] + s2[nt][1]) * scale2 : -INFINITY;
+            s[nt][2] = v1 ? (s[nt][2] + s2[nt][2]) * scale2 : -INFINITY; s[nt][3] = v1 ? (s[nt][3] + s2[nt][3]) * scale2 : -INFINITY;
+            float mxa = fmaxf(s[nt][0], s[nt][2]), mxb = fmaxf(s[nt][1], s[nt][3]);
+#pragma unroll
+            for (int off = 4; off < 32; off <<= 1) {
+                mxa = fmaxf(mxa, __shfl_xor_sync(0xFFFFFFFFu, mxa, off));
+                mxb = fmaxf(mxb, __shfl_xor_sync(0xFFFFFFFFu, mxb, off));
             }
+            mxa = fmaxf(mxa, m[nt][0]); mxb = fmaxf(mxb, m[nt][1]);      // finite: a step's first key is always valid
+            const float cora = ex2_approx(m[nt][0] - mxa), corb = ex2_approx(m[nt][1] - mxb);
+            m[nt][0] = mxa; m[nt][1] = mxb;
+            s[nt][0] = ex2_approx(s[nt][0] - mxa); s[nt][2] = ex2_approx(s[nt][2] - mxa);
+            s[nt][1] = ex2_approx(s[nt][1] - mxb); s[nt][3] = ex2_approx(s[nt][3] - mxb);
+            l[nt][0] = fmaf(l[nt][0], cora, s[nt][0] + s[nt][2]);
+            l[nt][1] = fmaf(l[nt][1], corb, s[nt][1] + s[nt][3]);
+            if (cora != 1.0f || corb != 1.0f) {      // the running maxima rarely move after a range's first steps
 #pragma unroll
-            for (int i = 0; i < 4; ++i) sfr[nt][i] += odd[i];
+                for (int i = 0; i < 8; ++i) { ot[nt][i][0] *= cora; ot[nt][i][1] *= corb; ot[nt][i][2] *= cora; ot[nt][i][3] *= corb; }
+            }
+            // the weights as two bf16 terms, hi + lo (16 significant bits): one bf16 term alone moves an output by up to a third
+            // of its own bf16 unit, which after the two roundings of the gate shows as two-unit differences
+            const uint32_t h01 = pack_bf16x2(s[nt][0], s[nt][1]), h23 = pack_bf16x2(s[nt][2], s[nt][3]);
+            const uint32_t l01 = pack_bf16x2(s[nt][0] - bf_lo(h01), s[nt][1] - bf_hi(h01));
+            const uint32_t l23 = pack_bf16x2(s[nt][2] - bf_lo(h23), s[nt][3] - bf_hi(h23));
+            ph[nt][0] = movmatrix_trans(h01); ph[nt][1] = movmatrix_trans(h23);
+            pl[nt][0] = movmatrix_trans(l01); pl[nt][1] = movmatrix_trans(l23);
         }
-        // softmax in the base-2 domain: t = score * scale * log2(e); m0 / m1 are the running maxima of t
-        float mx0 = -INFINITY, mx1 = -INFINITY;
+        // values: 8 tiles of 16 dims
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-            const int key = p + nt * 8 + 2 * q4;
-            const bool v0 = key < p1, v1 = key + 1 < p1;
-            sfr[nt][0] = v0 ? sfr[nt][0] * scale2 : -INFINITY; sfr[nt][1] = v1 ? sfr[nt][1] * scale2 : -INFINITY;
-            sfr[nt][2] = v0 ? sfr[nt][2] * scale2 : -INFINITY; sfr[nt][3] = v1 ? sfr[nt][3] * scale2 : -INFINITY;
-            mx0 = fmaxf(mx0, fmaxf(sfr[nt][0], sfr[nt][1]));
-            mx1 = fmaxf(mx1, fmaxf(sfr[nt][2], sfr[nt][3]));
-        }
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xFFFFFFFFu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xFFFFFFFFu, mx0, 2));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xFFFFFFFFu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xFFFFFFFFu, mx1, 2));
-        mx0 = fmaxf(mx0, m0); mx1 = fmaxf(mx1, m1);      // finite: a step's first key is always valid
-        const float cor0 = ex2_approx(m0 - mx0), cor1 = ex2_approx(m1 - mx1);
-        m0 = mx0; m1 = mx1;
-        l0 *= cor0; l1 *= cor1;
+        for (int i = 0; i < 8; ++i) {
+            uint32_t va[4];
+            ldsm_x4_trans(va, slot + v_off + 32 * i);
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-            sfr[nt][0] = ex2_approx(sfr[nt][0] - mx0); sfr[nt][1] = ex2_approx(sfr[nt][1] - mx0);
-            sfr[nt][2] = ex2_approx(sfr[nt][2] - mx1); sfr[nt][3] = ex2_approx(sfr[nt][3] - mx1);
-            l0 += sfr[nt][0] + sfr[nt][1];
-            l1 += sfr[nt][2] + sfr[nt][3];
-        }
-        if (cor0 != 1.0f || cor1 != 1.0f) {      // the running maxima rarely move after a range's first steps
-#pragma unroll
-            for (int i = 0; i < 16; ++i) { o[i][0] *= cor0; o[i][1] *= cor0; o[i][2] *= cor1; o[i][3] *= cor1; }
-        }
-        // values: the 16 keys are one MMA step; the weights' C fragments are the A fragments, as two bf16 terms, hi + lo
-        // (16 significant bits): one bf16 term alone moves an output by up to a third of its own bf16 unit, which after the
-        // two roundings of the gate shows as two-unit differences
-        uint32_t pa[4], pb[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float x0 = sfr[i >> 1][2 * (i & 1)], x1 = sfr[i >> 1][2 * (i & 1) + 1];
-            pa[i] = pack_bf16x2(x0, x1);
-            pb[i] = pack_bf16x2(x0 - bf_lo(pa[i]), x1 - bf_hi(pa[i]));
-        }
-        // lane -> the row of the 8 x 8 block it addresses: blocks 0 / 1 = keys 0-7 / 8-15 of dims n0..n0+7, 2 / 3 of n0+8..
-        const unsigned char* vr = vt + ((lane & 7) + ((lane >> 3) & 1) * 8) * ATT_VROW + (lane >> 4) * 16;
-#pragma unroll
-        for (int nd = 0; nd < 16; nd += 2) {
-            uint32_t b0, b1, b2, b3;
-            asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3)
-                         : "r"((unsigned) __cvta_generic_to_shared(vr + nd * 16)));
-            mma_bf16(o[nd], pa, b0, b1);
-            mma_bf16(o[nd], pb, b0, b1);
-            mma_bf16(o[nd + 1], pa, b2, b3);
-            mma_bf16(o[nd + 1], pb, b2, b3);
+            for (int nt = 0; nt < NT; ++nt) {
+                mma_bf16(ot[nt][i], va, ph[nt][0], ph[nt][1]);
+                mma_bf16(ot[nt][i], va, pl[nt][0], pl[nt][1]);
+            }
         }
         __syncwarp();      // this slot's reads are done before a later step refills it
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");      // only empty groups are left
-    l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 1); l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 2);
-    l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 1); l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 2);
-    // the warp's state into its own ring: [16 heads][130] = m, l, acc
+    // the warp's state into its own ring: [16 heads][130] = m (natural units; -inf stays -inf), l, acc
     __syncwarp();
     float* mine = (float*) stage;
-    if (q4 == 0) {      // the maxima back in natural units (-inf stays -inf)
-        mine[r0 * 130] = m0 * 0.69314718055994531f; mine[r0 * 130 + 1] = l0;
-        mine[(r0 + 8) * 130] = m1 * 0.69314718055994531f; mine[(r0 + 8) * 130 + 1] = l1;
-    }
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        const int d = 8 * i + 2 * q4;
-        mine[r0 * 130 + 2 + d] = o[i][0]; mine[r0 * 130 + 2 + d + 1] = o[i][1];
-        mine[(r0 + 8) * 130 + 2 + d] = o[i][2]; mine[(r0 + 8) * 130 + 2 + d + 1] = o[i][3];
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+        for (int off = 4; off < 32; off <<= 1) {
+            l[nt][0] += __shfl_xor_sync(0xFFFFFFFFu, l[nt][0], off);
+            l[nt][1] += __shfl_xor_sync(0xFFFFFFFFu, l[nt][1], off);
+        }
+        float* ha = mine + (8 * nt + 2 * q4) * 130, *hb = ha + 130;
+        if (r0 == 0) {
+            ha[0] = m[nt][0] * 0.69314718055994531f; ha[1] = l[nt][0];
+            hb[0] = m[nt][1] * 0.69314718055994531f; hb[1] = l[nt][1];
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int d = 2 + 16 * i + r0;
+            ha[d] = ot[nt][i][0]; hb[d] = ot[nt][i][1]; ha[d + 8] = ot[nt][i][2]; hb[d + 8] = ot[nt][i][3];
+        }
     }
     __syncthreads();
     // merge the warps' states: thread d of the block handles dim d of every head
     const int d = threadIdx.x;
     for (int h = 0; h < group; ++h) {
-        float m = -INFINITY;
-        for (int w = 0; w < ATT_MMA_WARPS; ++w) m = fmaxf(m, ((const float*) (att_smem + (size_t) w * STAGE))[h * 130]);
-        float l = 0.0f, acc = 0.0f;
+        float mm = -INFINITY;
+        for (int w = 0; w < ATT_MMA_WARPS; ++w) mm = fmaxf(mm, ((const float*) (att_smem + (size_t) w * STAGE))[h * 130]);
+        float ll = 0.0f, acc = 0.0f;
         for (int w = 0; w < ATT_MMA_WARPS; ++w) {
             const float* st = (const float*) (att_smem + (size_t) w * STAGE) + h * 130;
             if (st[0] == -INFINITY) continue;
-            const float c = expf(st[0] - m);
-            l = fmaf(st[1], c, l);
+            const float c = expf(st[0] - mm);
+            ll = fmaf(st[1], c, ll);
             acc = fmaf(st[2 + d], c, acc);
         }
         float* ph = pp + h * head_stride;
-        if (d == 0) { ph[0] = m; ph[1] = l; }
+        if (d == 0) { ph[0] = mm; ph[1] = ll; }
         ph[2 + d] = acc;
     }
     __syncthreads();
 }
 
 // One block per (split, KV head, row): the split's keys as the reference cuts them.
-template <int NSLOT>
+template <int NSLOT, int NT>
 __global__ void __launch_bounds__(32 * ATT_MMA_WARPS) attn_split_mma_kernel(AttnArgs a, const float* __restrict__ q, KvView kv,
                                                                             const RowInfo* __restrict__ ri, float* __restrict__ part) {
     extern __shared__ __align__(16) unsigned char att_smem[];      // the warps' rings, later their states
@@ -334,7 +356,7 @@ __global__ void __launch_bounds__(32 * ATT_MMA_WARPS) attn_split_mma_kernel(Attn
     const int nsr = a.chunk > 0 ? min(a.n_splits, (pos + a.chunk) / a.chunk) : 1;
     const int chunk = (pos + nsr) / nsr;
     const int p0 = split * chunk, p1 = min(pos + 1, p0 + chunk);
-    attn_keys<NSLOT>(a, q, kv, t, kvh, kv0, p0, p1, att_smem, part + (((size_t) t * a.n_head + kvh * group) * a.n_splits + split) * (ATT_HD + 2),
+    attn_keys<NSLOT, NT>(a, q, kv, t, kvh, kv0, p0, p1, att_smem, part + (((size_t) t * a.n_head + kvh * group) * a.n_splits + split) * (ATT_HD + 2),
                      (size_t) a.n_splits * (ATT_HD + 2));
 }
 
@@ -394,7 +416,7 @@ __device__ __forceinline__ AttnPlan attn_plan(const RowInfo* __restrict__ ri, in
     return pl;
 }
 
-template <int NSLOT>
+template <int NSLOT, int NT>
 __global__ void __launch_bounds__(32 * ATT_MMA_WARPS) attn_flat_mma_kernel(AttnArgs a, const float* __restrict__ q, KvView kv,
                                                                            const RowInfo* __restrict__ ri, float* __restrict__ part, int T) {
     extern __shared__ __align__(16) unsigned char att_smem[];
@@ -418,7 +440,7 @@ __global__ void __launch_bounds__(32 * ATT_MMA_WARPS) attn_flat_mma_kernel(AttnA
         const int end = min(xe, first + u);
         const int pos = max(ri[t].pos, 0), kv0 = ri[t].kv0;
         const int slot = (int) blockIdx.x - first / pl.per;
-        attn_keys<NSLOT>(a, q, kv, t, kvh, kv0, (x - first) * ATT_MT, min(pos + 1, (end - first) * ATT_MT), att_smem,
+        attn_keys<NSLOT, NT>(a, q, kv, t, kvh, kv0, (x - first) * ATT_MT, min(pos + 1, (end - first) * ATT_MT), att_smem,
                          part + (((size_t) t * a.n_head + kvh * group) * a.n_splits + slot) * (ATT_HD + 2), (size_t) a.n_splits * (ATT_HD + 2));
         x = end;
     }
@@ -497,6 +519,23 @@ static int attn_sm_count() {
     return n[dev & 15] > 0 ? n[dev & 15] : 148;
 }
 
+template <int NSLOT, int NT>
+static void launch_attn_flat(cudaStream_t s, int n_blocks, const AttnArgs& a, const float* q, const KvView& kv, const RowInfo* ri, float* part, int T) {
+    static bool done[16];
+    constexpr int SMEM = ATT_MMA_WARPS * NSLOT * ATT_SLOT;
+    attn_smem_attr(attn_flat_mma_kernel<NSLOT, NT>, SMEM, done);
+    launch(attn_flat_mma_kernel<NSLOT, NT>, dim3((unsigned) n_blocks), 32 * ATT_MMA_WARPS, (size_t) SMEM, s, a, q, kv, ri, part, T);
+}
+
+template <int NT>
+static void launch_attn_split(cudaStream_t s, const AttnArgs& a, const float* q, const KvView& kv, const RowInfo* ri, float* part, int T) {
+    static bool done[16];
+    constexpr int SMEM = ATT_MMA_WARPS * 2 * ATT_SLOT;
+    attn_smem_attr(attn_split_mma_kernel<2, NT>, SMEM, done);
+    launch(attn_split_mma_kernel<2, NT>, dim3((unsigned) a.n_splits, (unsigned) a.n_kv, (unsigned) T), 32 * ATT_MMA_WARPS, (size_t) SMEM, s,
+           a, q, kv, ri, part);
+}
+
 extern "C" {
 
 // Picks the form of kc_attn's first pass (see g_attn_variant).  All forms meet the same bound; for tests and timing.
@@ -512,24 +551,18 @@ void kc_attn(cudaStream_t s, AttnArgs a, const float* q, KvView kv, const RowInf
                   a.n_kv, (int) ATT_MAX_GROUP, a.n_splits, a.chunk);
         return;
     }
-    constexpr int SM2 = ATT_MMA_WARPS * 2 * ATT_SLOT, SM3 = ATT_MMA_WARPS * 3 * ATT_SLOT;
     const bool flat = (g_attn_variant == 1 || g_attn_variant >= 3) && a.n_splits >= 3 && a.chunk > 0 && T <= ATT_MAX_ROWS;
     int n_blocks = 0;
-    if (flat && g_attn_variant != 3) {
-        static bool done[16];
-        attn_smem_attr(attn_flat_mma_kernel<2>, SM2, done);
-        n_blocks = (g_attn_variant == 4 ? 2 : 3) * attn_sm_count();      // three blocks of 70 KB and 168 registers a thread fit an SM
-        launch(attn_flat_mma_kernel<2>, dim3((unsigned) n_blocks), 32 * ATT_MMA_WARPS, (size_t) SM2, s, a, q, kv, ri, part, T);
-    } else if (flat) {
-        static bool done[16];
-        attn_smem_attr(attn_flat_mma_kernel<3>, SM3, done);
-        n_blocks = 2 * attn_sm_count();
-        launch(attn_flat_mma_kernel<3>, dim3((unsigned) n_blocks), 32 * ATT_MMA_WARPS, (size_t) SM3, s, a, q, kv, ri, part, T);
+    if (flat) {
+        const int slots = g_attn_variant == 3 ? 3 : 2;
+        n_blocks = (g_attn_variant == 1 ? 3 : 2) * attn_sm_count();      // three blocks of 70 KB of shared memory fit an SM
+        if (slots == 2 && group <= 8) launch_attn_flat<2, 1>(s, n_blocks, a, q, kv, ri, part, T);
+        else if (slots == 2) launch_attn_flat<2, 2>(s, n_blocks, a, q, kv, ri, part, T);
+        else if (group <= 8) launch_attn_flat<3, 1>(s, n_blocks, a, q, kv, ri, part, T);
+        else launch_attn_flat<3, 2>(s, n_blocks, a, q, kv, ri, part, T);
     } else if (g_attn_variant != 0) {
-        static bool done[16];
-        attn_smem_attr(attn_split_mma_kernel<2>, SM2, done);
-        launch(attn_split_mma_kernel<2>, dim3((unsigned) a.n_splits, (unsigned) a.n_kv, (unsigned) T), 32 * ATT_MMA_WARPS, (size_t) SM2, s,
-               a, q, kv, ri, part);
+        if (group <= 8) launch_attn_split<1>(s, a, q, kv, ri, part, T);
+        else launch_attn_split<2>(s, a, q, kv, ri, part, T);
     } else {
         launch(attn_split_kernel, dim3((unsigned) a.n_splits, (unsigned) a.n_kv, (unsigned) T), 32 * group, 0, s, a, q, kv, ri, part);
     }
