@@ -168,12 +168,15 @@ typedef struct { KvSeg a, b; int32_t nv, fmt; } KvView;             /* positions
  * bf16(bf16(softmax(scale q.K) V) * bf16(softplus(g; beta = ln 2))) (g NULL: no gate).  BF16 caches only (kv.fmt =
  * KV_BF16); any group size n_head / n_kv up to 16. */
 void kc_attn(cudaStream_t s, AttnArgs a, const float* q, KvView kv, const RowInfo* ri, float* part, const float* g, float* o, int T);
-/* No counterpart in the reference: the form of kc_attn's first pass.  1 (default): tensor cores (all heads of a KV head
- * as the rows of the products), the step's keys dealt evenly to the blocks whatever a.n_splits asks (used when
+/* No counterpart in the reference: the form of kc_attn's first pass.  1 (default): tensor cores (heads of a KV head as
+ * the columns of the products), the step's keys dealt evenly to the blocks whatever a.n_splits asks (used when
  * a.n_splits >= 3 and T <= 1024; otherwise form 2); 2: tensor cores, one block per (split, KV head, row); 3 and 4: form 1
- * with three-slot rings / two blocks an SM; 0: scalar, one warp per head.  The partials' use of `part` is internal to
- * the two kernels in every form and never exceeds the size above. */
+ * with three-slot rings / two blocks an SM; 5 and 6: forms 1 and 3 with the K and V rows brought by the copy engine
+ * (cp.async.bulk); 0: scalar, one warp per head.  The partials' use of `part` is internal to the two kernels in every
+ * form and never exceeds the size above.  nsl_attn_status: 0, or 1 once a bounded wait for rows ran out in forms 5 / 6
+ * (that call's outputs are invalid; never expected); synchronises the device. */
 void nsl_attn_set_variant(int v);
+int nsl_attn_status(void);
 
 /* ---- greedy decoding over the LM head's logits ------------------------------------------------------------------------ */
 /* engine/kernels_cuda.h:177-178  out[i] = arg max of row i of logits [n][V] (ties: the lowest id); prob[i] (optional) =

@@ -172,6 +172,56 @@ __device__ __forceinline__ void attn_fill_slot(unsigned char* slot, const KvView
     asm volatile("cp.async.commit_group;" ::: "memory");
 }
 
+// ---- K / V rows by the copy engine (cp.async.bulk, one 256-byte row per lane) ------------------------------------------
+// A warp's slot has an mbarrier: lane 0 announces the step's 8192 bytes, every lane issues one row (lanes 0-15 K, 16-31 V),
+// the copies count their bytes down and the wait ends when all have landed.  No per-16-byte load-store requests: the
+// requests a step keeps in flight no longer go through the SM's load-store path.
+__device__ int g_attn_wait_failed;      // set when a wait for a slot's rows ran out (never expected: the copies always land)
+
+__device__ __forceinline__ unsigned long long attn_now_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned) __cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded: gives up after one second (or 2^24 polls) and reports it.
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = attn_now_ns();
+    for (unsigned i = 1; i < (1u << 24); ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 255u) == 0 && attn_now_ns() - t0 > 1000000000ull) break;
+    }
+    return false;
+}
+__device__ __forceinline__ void bulk_row(unsigned dst, const void* src, unsigned bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(2 * ATT_HD), "r"(bar) : "memory");
+}
+// The step at key p into a slot, if it lies in the range.  All 32 lanes call it.
+__device__ __forceinline__ void attn_fill_slot_bulk(unsigned char* slot, unsigned bar, const KvView& kv, int n_kv, int kvh, int kv0, int p,
+                                                    int p1, int lane) {
+    if (p < p1) {
+        if (lane == 0) mbar_expect_tx(bar, 2 * ATT_MT * 2 * ATT_HD);
+        __syncwarp();
+        const int r = lane & 15, is_v = lane >> 4;
+        const int row = kv0 + min(p + r, p1 - 1);      // rows beyond the range repeat its last row; their scores are masked
+        bulk_row(smem_u32(slot) + is_v * ATT_MT * ATT_KROW + r * ATT_KROW, kv_row(kv, is_v, row, n_kv, kvh), bar);
+    }
+}
+
 __device__ __forceinline__ void ldsm_x4(uint32_t* r, const unsigned char* p) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((unsigned) __cvta_generic_to_shared(p)));
@@ -195,16 +245,26 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {      // an 8 x
 //                                                          as bf16 pairs, transposed across the warp by movmatrix
 // A lane holds keys r0 and r0 + 8 of heads 2 q4 and 2 q4 + 1 of each tile: the maxima and sums of a head run over the 8
 // lanes of equal q4.  Ends with the block in step (shared memory reusable).
-template <int NSLOT, int NT>
+// BULK: the rows come by the copy engine (bars = the warp's NSLOT mbarriers; ring = the slots' phase bits, bit 31 set once
+// a wait ran out, after which the warp computes nothing more); otherwise by cp.async.
+template <int NSLOT, int NT, bool BULK>
 __device__ __forceinline__ void attn_keys(const AttnArgs& a, const float* __restrict__ q, const KvView& kv, int t, int kvh, int kv0,
-                                          int p0, int p1, unsigned char* att_smem, float* pp, size_t head_stride) {
+                                          int p0, int p1, unsigned char* att_smem, float* pp, size_t head_stride, unsigned bars,
+                                          unsigned& ring) {
     constexpr int STAGE = NSLOT * ATT_SLOT, STRIDE = ATT_MMA_WARPS * ATT_MT;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, q4 = lane & 3, r0 = lane >> 2;
     const int group = a.n_head / a.n_kv;
     unsigned char* stage = att_smem + (size_t) warp * STAGE;
     int p = p0 + warp * ATT_MT;
+    if (BULK) {
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the ring held a state (plain stores) before
+        if (ring >> 31) p = p1;
 #pragma unroll
-    for (int i = 0; i < NSLOT - 1; ++i) attn_fill_slot(stage + i * ATT_SLOT, kv, a.n_kv, kvh, kv0, p + i * STRIDE, p1, lane);
+        for (int i = 0; i < NSLOT - 1; ++i) attn_fill_slot_bulk(stage + i * ATT_SLOT, bars + 8 * i, kv, a.n_kv, kvh, kv0, p + i * STRIDE, p1, lane);
+    } else {
+#pragma unroll
+        for (int i = 0; i < NSLOT - 1; ++i) attn_fill_slot(stage + i * ATT_SLOT, kv, a.n_kv, kvh, kv0, p + i * STRIDE, p1, lane);
+    }
     // Q^T as the B fragments of the 8 steps over the 128 dims: column r0 of a tile = head 8 nt + r0 (zero beyond the group);
     // the first rows of K and V fly meanwhile
     uint32_t qb[NT][8][2];
@@ -238,8 +298,19 @@ __device__ __forceinline__ void attn_keys(const AttnArgs& a, const float* __rest
     int cur = 0, nxt = NSLOT - 1;      // the slot in use; the slot the step NSLOT - 1 ahead goes to (its reads ended with the
                                        // previous step's closing __syncwarp)
     for (; p < p1; p += STRIDE) {
-        attn_fill_slot(stage + nxt * ATT_SLOT, kv, a.n_kv, kvh, kv0, p + (NSLOT - 1) * STRIDE, p1, lane);
-        asm volatile("cp.async.wait_group %0;" ::"n"(NSLOT - 1) : "memory");
+        if (BULK) {
+            attn_fill_slot_bulk(stage + nxt * ATT_SLOT, bars + 8 * nxt, kv, a.n_kv, kvh, kv0, p + (NSLOT - 1) * STRIDE, p1, lane);
+            const bool landed = __all_sync(0xFFFFFFFFu, mbar_wait(bars + 8 * cur, (ring >> cur) & 1u));
+            ring ^= 1u << cur;
+            if (!landed) {      // give up: the flag tells the host, the rest of the range is skipped
+                if (lane == 0) atomicExch(&g_attn_wait_failed, 1);
+                ring |= 1u << 31;
+                break;
+            }
+        } else {
+            attn_fill_slot(stage + nxt * ATT_SLOT, kv, a.n_kv, kvh, kv0, p + (NSLOT - 1) * STRIDE, p1, lane);
+            asm volatile("cp.async.wait_group %0;" ::"n"(NSLOT - 1) : "memory");
+        }
         __syncwarp();
         const unsigned char* slot = stage + cur * ATT_SLOT;
         nxt = cur;
@@ -300,7 +371,7 @@ __device__ __forceinline__ void attn_keys(const AttnArgs& a, const float* __rest
         }
         __syncwarp();      // this slot's reads are done before a later step refills it
     }
-    asm volatile("cp.async.wait_group 0;" ::: "memory");      // only empty groups are left
+    if (!BULK) asm volatile("cp.async.wait_group 0;" ::: "memory");      // only empty groups are left
     // the warp's state into its own ring: [16 heads][130] = m (natural units; -inf stays -inf), l, acc
     __syncwarp();
     float* mine = (float*) stage;
@@ -356,8 +427,9 @@ __global__ void __launch_bounds__(32 * ATT_MMA_WARPS) attn_split_mma_kernel(Attn
     const int nsr = a.chunk > 0 ? min(a.n_splits, (pos + a.chunk) / a.chunk) : 1;
     const int chunk = (pos + nsr) / nsr;
     const int p0 = split * chunk, p1 = min(pos + 1, p0 + chunk);
-    attn_keys<NSLOT, NT>(a, q, kv, t, kvh, kv0, p0, p1, att_smem, part + (((size_t) t * a.n_head + kvh * group) * a.n_splits + split) * (ATT_HD + 2),
-                     (size_t) a.n_splits * (ATT_HD + 2));
+    unsigned ring = 0;
+    attn_keys<NSLOT, NT, false>(a, q, kv, t, kvh, kv0, p0, p1, att_smem, part + (((size_t) t * a.n_head + kvh * group) * a.n_splits + split) * (ATT_HD + 2),
+                                (size_t) a.n_splits * (ATT_HD + 2), 0u, ring);
 }
 
 // ---- the balanced form ------------------------------------------------------------------------------------------------
@@ -416,12 +488,20 @@ __device__ __forceinline__ AttnPlan attn_plan(const RowInfo* __restrict__ ri, in
     return pl;
 }
 
-template <int NSLOT, int NT>
+template <int NSLOT, int NT, bool BULK>
 __global__ void __launch_bounds__(32 * ATT_MMA_WARPS) attn_flat_mma_kernel(AttnArgs a, const float* __restrict__ q, KvView kv,
                                                                            const RowInfo* __restrict__ ri, float* __restrict__ part, int T) {
     extern __shared__ __align__(16) unsigned char att_smem[];
     __shared__ int pre[ATT_MAX_ROWS + 1];
+    __shared__ __align__(8) unsigned long long att_bars[ATT_MMA_WARPS][4];      // a warp's slots' mbarriers (BULK)
     const int group = a.n_head / a.n_kv;
+    const unsigned bars = smem_u32(&att_bars[threadIdx.x >> 5][0]);
+    unsigned ring = 0;
+    if (BULK) {
+        if ((threadIdx.x & 31) < NSLOT) mbar_init(bars + 8 * (threadIdx.x & 31), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        __syncwarp();
+    }
     grid_dependents_go();
     grid_dependency_wait();
     const AttnPlan pl = attn_plan(ri, T, a.n_kv, a.n_splits, (int) gridDim.x, pre);
@@ -440,8 +520,9 @@ __global__ void __launch_bounds__(32 * ATT_MMA_WARPS) attn_flat_mma_kernel(AttnA
         const int end = min(xe, first + u);
         const int pos = max(ri[t].pos, 0), kv0 = ri[t].kv0;
         const int slot = (int) blockIdx.x - first / pl.per;
-        attn_keys<NSLOT, NT>(a, q, kv, t, kvh, kv0, (x - first) * ATT_MT, min(pos + 1, (end - first) * ATT_MT), att_smem,
-                         part + (((size_t) t * a.n_head + kvh * group) * a.n_splits + slot) * (ATT_HD + 2), (size_t) a.n_splits * (ATT_HD + 2));
+        attn_keys<NSLOT, NT, BULK>(a, q, kv, t, kvh, kv0, (x - first) * ATT_MT, min(pos + 1, (end - first) * ATT_MT), att_smem,
+                                   part + (((size_t) t * a.n_head + kvh * group) * a.n_splits + slot) * (ATT_HD + 2),
+                                   (size_t) a.n_splits * (ATT_HD + 2), bars, ring);
         x = end;
     }
 }
@@ -499,6 +580,7 @@ using namespace nsl;
 
 static int g_attn_variant = 1;   // 1 (default): tensor cores, balanced over the blocks; 2: tensor cores, one block per split;
                                  // 3: as 1 with three-slot rings (two blocks an SM); 4: as 1 with two blocks an SM;
+                                 // 5 / 6: as 1 / 3 with the K and V rows brought by the copy engine (cp.async.bulk);
                                  // 0: the scalar pass (one warp per query head)
 
 template <typename K>
@@ -519,12 +601,19 @@ static int attn_sm_count() {
     return n[dev & 15] > 0 ? n[dev & 15] : 148;
 }
 
-template <int NSLOT, int NT>
+template <int NSLOT, int NT, bool BULK>
 static void launch_attn_flat(cudaStream_t s, int n_blocks, const AttnArgs& a, const float* q, const KvView& kv, const RowInfo* ri, float* part, int T) {
     static bool done[16];
     constexpr int SMEM = ATT_MMA_WARPS * NSLOT * ATT_SLOT;
-    attn_smem_attr(attn_flat_mma_kernel<NSLOT, NT>, SMEM, done);
-    launch(attn_flat_mma_kernel<NSLOT, NT>, dim3((unsigned) n_blocks), 32 * ATT_MMA_WARPS, (size_t) SMEM, s, a, q, kv, ri, part, T);
+    attn_smem_attr(attn_flat_mma_kernel<NSLOT, NT, BULK>, SMEM, done);
+    launch(attn_flat_mma_kernel<NSLOT, NT, BULK>, dim3((unsigned) n_blocks), 32 * ATT_MMA_WARPS, (size_t) SMEM, s, a, q, kv, ri, part, T);
+}
+
+template <int NSLOT, bool BULK>
+static void launch_attn_flat_group(cudaStream_t s, int n_blocks, int group, const AttnArgs& a, const float* q, const KvView& kv, const RowInfo* ri,
+                                   float* part, int T) {
+    if (group <= 8) launch_attn_flat<NSLOT, 1, BULK>(s, n_blocks, a, q, kv, ri, part, T);
+    else launch_attn_flat<NSLOT, 2, BULK>(s, n_blocks, a, q, kv, ri, part, T);
 }
 
 template <int NT>
@@ -539,7 +628,15 @@ static void launch_attn_split(cudaStream_t s, const AttnArgs& a, const float* q,
 extern "C" {
 
 // Picks the form of kc_attn's first pass (see g_attn_variant).  All forms meet the same bound; for tests and timing.
-void nsl_attn_set_variant(int v) { g_attn_variant = v >= 0 && v <= 4 ? v : 1; }
+void nsl_attn_set_variant(int v) { g_attn_variant = v >= 0 && v <= 6 ? v : 1; }
+
+// 0, or 1 once a bounded wait for a step's K / V rows ran out in the copy-engine forms (the outputs of that call are
+// invalid).  Synchronises the device.
+int nsl_attn_status(void) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_attn_wait_failed, sizeof v) != cudaSuccess) return -1;
+    return v;
+}
 
 void kc_attn(cudaStream_t s, AttnArgs a, const float* q, KvView kv, const RowInfo* ri, float* part, const float* g, float* o, int T) {
     if (T < 1) return;
@@ -554,12 +651,13 @@ void kc_attn(cudaStream_t s, AttnArgs a, const float* q, KvView kv, const RowInf
     const bool flat = (g_attn_variant == 1 || g_attn_variant >= 3) && a.n_splits >= 3 && a.chunk > 0 && T <= ATT_MAX_ROWS;
     int n_blocks = 0;
     if (flat) {
-        const int slots = g_attn_variant == 3 ? 3 : 2;
-        n_blocks = (g_attn_variant == 1 ? 3 : 2) * attn_sm_count();      // three blocks of 70 KB of shared memory fit an SM
-        if (slots == 2 && group <= 8) launch_attn_flat<2, 1>(s, n_blocks, a, q, kv, ri, part, T);
-        else if (slots == 2) launch_attn_flat<2, 2>(s, n_blocks, a, q, kv, ri, part, T);
-        else if (group <= 8) launch_attn_flat<3, 1>(s, n_blocks, a, q, kv, ri, part, T);
-        else launch_attn_flat<3, 2>(s, n_blocks, a, q, kv, ri, part, T);
+        const bool three = g_attn_variant == 3 || g_attn_variant == 6, bulk = g_attn_variant >= 5;
+        // three blocks with two-slot rings (70 KB of shared memory) fit an SM, two with three-slot rings
+        n_blocks = (three || g_attn_variant == 4 ? 2 : 3) * attn_sm_count();
+        if (!three && !bulk) launch_attn_flat_group<2, false>(s, n_blocks, group, a, q, kv, ri, part, T);
+        else if (!three) launch_attn_flat_group<2, true>(s, n_blocks, group, a, q, kv, ri, part, T);
+        else if (!bulk) launch_attn_flat_group<3, false>(s, n_blocks, group, a, q, kv, ri, part, T);
+        else launch_attn_flat_group<3, true>(s, n_blocks, group, a, q, kv, ri, part, T);
     } else if (g_attn_variant != 0) {
         if (group <= 8) launch_attn_split<1>(s, a, q, kv, ri, part, T);
         else launch_attn_split<2>(s, a, q, kv, ri, part, T);
