@@ -601,8 +601,15 @@ def run_attn(args):
     lib.nsl_attn_set_variant(variant)
     K, W = args.steps, max(args.warmup, 3)
     gen = torch.Generator(device="cuda").manual_seed(5)
-    caches = [(torch.randn(NSEQ * CTX, NKV, 128, generator=gen, device="cuda").to(torch.bfloat16),
-               torch.randn(NSEQ * CTX, NKV, 128, generator=gen, device="cuda").to(torch.bfloat16)) for _ in range(NL)]
+    q8 = os.environ.get("NSL_ATTN_KV", "bf16") == "q8"      # the 8-bit cache: int8 codes and one f32 scale per (row, KV head)
+    if q8:
+        caches = [(torch.randint(-127, 128, (NSEQ * CTX, NKV, 128), generator=gen, device="cuda", dtype=torch.int8),
+                   torch.randint(-127, 128, (NSEQ * CTX, NKV, 128), generator=gen, device="cuda", dtype=torch.int8)) for _ in range(NL)]
+        scales = [(torch.rand(NSEQ * CTX, NKV, generator=gen, device="cuda") / 64 + 0.01,
+                   torch.rand(NSEQ * CTX, NKV, generator=gen, device="cuda") / 64 + 0.01) for _ in range(NL)]
+    else:
+        caches = [(torch.randn(NSEQ * CTX, NKV, 128, generator=gen, device="cuda").to(torch.bfloat16),
+                   torch.randn(NSEQ * CTX, NKV, 128, generator=gen, device="cuda").to(torch.bfloat16)) for _ in range(NL)]
     q = torch.randn(NSEQ, NH, 128, generator=gen, device="cuda").to(torch.bfloat16).float()
     g = torch.randn(NSEQ, NH, 128, generator=gen, device="cuda").to(torch.bfloat16).float()
     o = torch.zeros(NSEQ, NH, 128, device="cuda")
@@ -614,9 +621,11 @@ def run_attn(args):
     rid.copy_(torch.frombuffer(bytearray(bytes(ri)), dtype=torch.uint8))
     a = L.AttnArgs(NH, NKV, CTX // NS, NS, float(1 / np.sqrt(128.0)))
     views = []
-    for kc, vc in caches:
+    for i, (kc, vc) in enumerate(caches):
         kv = L.KvView()
-        kv.a.k, kv.a.v, kv.nv, kv.fmt = kc.data_ptr(), vc.data_ptr(), NSEQ * CTX, 0
+        kv.a.k, kv.a.v, kv.nv, kv.fmt = kc.data_ptr(), vc.data_ptr(), NSEQ * CTX, 1 if q8 else 0
+        if q8:
+            kv.a.ks, kv.a.vs = scales[i][0].data_ptr(), scales[i][1].data_ptr()
         views.append(kv)
     stream = torch.cuda.Stream()
     s = C.c_void_p(stream.cuda_stream)
@@ -638,12 +647,12 @@ def run_attn(args):
         ms = e0.elapsed_time(e1) / K
     L.check()
     peaks, kind = measured_peaks()
-    nbytes = 2 * NSEQ * CTX * NKV * 128 * 2 + 3 * NSEQ * NH * 128 * 4
+    nbytes = 2 * NSEQ * CTX * NKV * ((128 + 4) if q8 else 128 * 2) + 3 * NSEQ * NH * 128 * 4
     gbs = nbytes / (ms * 1e-3) / 1e9
     print(json.dumps({"metric": "decode_attention_tokens_per_s", "value": NSEQ / (ms * 1e-3), "unit": "tok/s", "n_gpus": 1, "steps": K,
-                      "warmup": W, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 cache, f32 math",
+                      "warmup": W, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": ("int8" if q8 else "bf16") + " cache, f32 math",
                       "data": "synthetic", "gpu_launches": 2 * K, "clocks": clocks.summary(),
-                      "config": {"workload": f"decode attention, {NH} query / {NKV} KV heads of 128, BF16 cache of {CTX} positions x {NSEQ} "
+                      "config": {"workload": f"decode attention, {NH} query / {NKV} KV heads of 128, {'8-bit' if q8 else 'BF16'} cache of {CTX} positions x {NSEQ} "
                                              f"sequences ({nbytes / 1e6:.0f} MB per layer), {NS} splits; {NL} layers rotated", "tokens": NSEQ},
                       "roofline": {"bound": "hbm", "kernel": ATTN_FORMS.get(variant, ATTN_FORMS[1]) + " + attn_reduce_kernel (kc_attn)", "achieved": gbs,
                                    "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"], "peak_kind": kind, "traffic": None,

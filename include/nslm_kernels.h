@@ -152,7 +152,7 @@ void kc_heads_mv(cudaStream_t s, HmvArgs a, int fmt, WSlice W, const uint32_t* G
  * nearest even (what the GEMM feeds the tensor cores). */
 void kc_heads_deq(cudaStream_t s, int fmt, WSlice W, const uint32_t* G, int H, int O, int I, uint16_t* out);
 
-/* ---- decode attention over a BF16 KV cache ----------------------------------------------------------------------------- */
+/* ---- decode attention over a BF16 or 8-bit KV cache -------------------------------------------------------------------- */
 /* engine/kernels_moe.metal:78-84, engine/kernels_cuda.h:56-72: field order is the ABI. */
 typedef struct {
     int32_t n_head, n_kv, chunk, n_splits;   /* chunk: target keys per split; a row at position pos uses
@@ -165,8 +165,9 @@ typedef struct { void* k; void* v; float* ks; float* vs; } KvSeg;   /* rows of n
 typedef struct { KvSeg a, b; int32_t nv, fmt; } KvView;             /* positions [0, nv) in a, the rest in b */
 /* engine/kernels_cuda.h:130  q [T][n_head][128] (f32), row t attends cache rows kv0 .. kv0 + pos of its KV head
  * (head h uses KV head h / (n_head / n_kv)); part: T x n_head x n_splits x 130 floats of partials; o [T][n_head][128] =
- * bf16(bf16(softmax(scale q.K) V) * bf16(softplus(g; beta = ln 2))) (g NULL: no gate).  BF16 caches only (kv.fmt =
- * KV_BF16); any group size n_head / n_kv up to 16. */
+ * bf16(bf16(softmax(scale q.K) V) * bf16(softplus(g; beta = ln 2))) (g NULL: no gate).  kv.fmt = KV_BF16, or KV_Q8 (int8
+ * codes, ks / vs [rows][n_kv] f32: a value is bf16(code * scale), engine/kernels_moe.cu:807-824); FP8 / FP4 are refused.
+ * Any group size n_head / n_kv up to 16. */
 void kc_attn(cudaStream_t s, AttnArgs a, const float* q, KvView kv, const RowInfo* ri, float* part, const float* g, float* o, int T);
 /* No counterpart in the reference: the form of kc_attn's first pass.  1 (default): tensor cores (heads of a KV head as
  * the columns of the products), the step's keys dealt evenly to the blocks whatever a.n_splits asks (used when

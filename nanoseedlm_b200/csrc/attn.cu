@@ -1,7 +1,9 @@
-// Decode attention over a BF16 KV cache with grouped query heads: split-key partial passes and their reduction with the
-// softplus output gate (engine/kernels_moe.cu:887-952, 2421-2426; engine/kernels_cuda.h:56-72, 130-131).
+// Decode attention over a BF16 or 8-bit KV cache with grouped query heads: split-key partial passes and their reduction
+// with the softplus output gate (engine/kernels_moe.cu:887-952, 2421-2426; engine/kernels_cuda.h:56-72, 130-131).
+// Three forms of the first pass: scalar (below), tensor cores with a block per caller split, tensor cores with the
+// step's keys dealt evenly to the blocks (the default; further down).
 //
-// One block per (split, KV head, row); one warp per query head of the KV head (any group size up to 16, where the
+// The scalar form (BF16 caches): one block per (split, KV head, row); one warp per query head of the KV head (any group size up to 16, where the
 // reference fixes 4).  The two halves of a step of 32 keys use two thread layouts, so that neither needs a reduction
 // per key:
 //   scores   lane = key: a lane walks its own key's 128 values against the head's scaled query in shared memory;
@@ -111,14 +113,14 @@ __global__ void __launch_bounds__(32 * ATT_MAX_GROUP) attn_split_kernel(AttnArgs
 }
 
 // ---- the same pass on the tensor cores -------------------------------------------------------------------------------------
-// One warp serves ALL query heads of the KV head: they are the 16 rows of an mma.sync.m16n8k16 (bf16 in, f32 accumulate;
-// rows beyond the group are zero).  Queries are bf16-valued, so the score products are exact and the softmax scale is
-// applied to the f32 sums; the weights enter the second product as two bf16 terms (hi + lo: 16 significant bits; their
-// sum l is kept in f32).  Per step of 16 keys a warp issues 16 MMAs for the scores and 32 for the values instead of
-// ~2500 scalar instructions for the group.  The warps of a block take the split's steps in turn, each with its own running
-// (m, l, acc) and its own two-slot ring of K / V rows in shared memory (the next step's rows fly while this one is
-// computed; rows 272 bytes apart: the fragment reads and ldmatrix touch distinct banks); at the end the warps' states are
-// merged through the same shared memory.
+// One warp serves ALL query heads of the KV head: they are the columns of mma.sync.m16n8k16 products (bf16 in, f32
+// accumulate; 8 heads a tile, columns beyond the group are zero; see attn_keys for the two products).  Queries are
+// bf16-valued, so the score products are exact and the softmax scale is applied to the f32 sums; the weights enter the
+// second product as two bf16 terms (hi + lo: 16 significant bits; their sum l is kept in f32).  Per step of 16 keys a warp
+// issues 8 MMAs for the scores and 16 for the values of a tile instead of ~2500 scalar instructions for the group.  The
+// warps of a block take a key range's steps in turn, each with its own running (m, l, acc) and its own ring of K / V rows
+// in shared memory (the next step's rows fly while this one is computed; rows 272 bytes apart: ldmatrix touches distinct
+// banks); at the end the warps' states are merged through the same shared memory.
 constexpr int ATT_MMA_WARPS = 4, ATT_VROW = 272, ATT_MT = 16, ATT_SLOT = ATT_MT * (ATT_KROW + ATT_VROW);
 constexpr int ATT_MAX_ROWS = 1024;      // rows of a step in the balanced form (the reference's rows x splits <= 1024)
 static_assert(2 * ATT_SLOT >= ATT_MAX_GROUP * 130 * 4, "a warp's ring holds its final state");
@@ -222,6 +224,60 @@ __device__ __forceinline__ void attn_fill_slot_bulk(unsigned char* slot, unsigne
     }
 }
 
+// ---- the 8-bit cache (KV_Q8: int8 codes, one f32 scale per row and KV head; engine/kernels_cuda.h:58-59) ------------------
+// A warp's ring holds the raw rows of two steps (16 K rows and 16 V rows of 128 bytes, then their 32 scales); before a step
+// is used its rows are expanded into the one BF16 slot the products read: bf16(code * scale), the value the reference's
+// kernels read (engine/kernels_moe.cu:807-824).
+constexpr int ATT_RAW_V = ATT_MT * ATT_HD, ATT_RAW_SCALES = 2 * ATT_RAW_V, ATT_RAW = ATT_RAW_SCALES + 2 * ATT_MT * 4;
+static_assert(ATT_SLOT + 2 * ATT_RAW <= 2 * ATT_SLOT, "the BF16 slot and two raw slots fit a two-slot ring");
+
+__device__ __forceinline__ void attn_cp4s(unsigned smem, const void* gmem) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ const KvSeg& kv_seg_of(const KvView& kv, int abs_pos, int& row) {
+    const bool first = abs_pos < kv.nv;
+    row = first ? abs_pos : abs_pos - kv.nv;
+    return first ? kv.a : kv.b;
+}
+// The step at key p, raw: 256 pieces of 16 bytes (8 a lane) and 32 scales (one a lane).  Always one cp.async group.
+__device__ __forceinline__ void attn_fill_raw(unsigned char* raw, const KvView& kv, int n_kv, int kvh, int kv0, int p, int p1, int lane) {
+    if (p < p1) {
+        const unsigned base = smem_u32(raw);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int id = i * 32 + lane, is_v = id >> 7, r = (id >> 3) & 15, piece = id & 7;
+            int row;
+            const KvSeg& sg = kv_seg_of(kv, kv0 + min(p + r, p1 - 1), row);
+            attn_cp16s(base + is_v * ATT_RAW_V + r * ATT_HD + piece * 16,
+                       (const unsigned char*) (is_v ? sg.v : sg.k) + ((size_t) row * n_kv + kvh) * ATT_HD + piece * 16);
+        }
+        const int is_v = lane >> 4, r = lane & 15;
+        int row;
+        const KvSeg& sg = kv_seg_of(kv, kv0 + min(p + r, p1 - 1), row);
+        attn_cp4s(base + ATT_RAW_SCALES + lane * 4, (is_v ? sg.vs : sg.ks) + (size_t) row * n_kv + kvh);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t q8_pair(uint32_t u, int i, float s) {      // codes i and i + 1 of a word as a bf16 pair
+    const float a = (float) (int) (signed char) ((u >> (8 * i)) & 255u) * s, b = (float) (int) (signed char) ((u >> (8 * i + 8)) & 255u) * s;
+    return pack_bf16x2(a, b);
+}
+// Raw rows -> the BF16 slot (rows 272 bytes apart, K then V).
+__device__ __forceinline__ void attn_expand_raw(unsigned char* slot, const unsigned char* raw, int lane) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int id = i * 32 + lane, is_v = id >> 7, r = (id >> 3) & 15, piece = id & 7;
+        const uint4 u = *(const uint4*) (raw + is_v * ATT_RAW_V + r * ATT_HD + piece * 16);
+        const float sc = *(const float*) (raw + ATT_RAW_SCALES + (is_v * ATT_MT + r) * 4);
+        uint4 lo, hi;
+        lo.x = q8_pair(u.x, 0, sc); lo.y = q8_pair(u.x, 2, sc); lo.z = q8_pair(u.y, 0, sc); lo.w = q8_pair(u.y, 2, sc);
+        hi.x = q8_pair(u.z, 0, sc); hi.y = q8_pair(u.z, 2, sc); hi.z = q8_pair(u.w, 0, sc); hi.w = q8_pair(u.w, 2, sc);
+        uint4* dst = (uint4*) (slot + is_v * ATT_MT * ATT_KROW + r * ATT_KROW + piece * 32);
+        dst[0] = lo;
+        dst[1] = hi;
+    }
+}
+
 __device__ __forceinline__ void ldsm_x4(uint32_t* r, const unsigned char* p) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((unsigned) __cvta_generic_to_shared(p)));
@@ -245,9 +301,11 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {      // an 8 x
 //                                                          as bf16 pairs, transposed across the warp by movmatrix
 // A lane holds keys r0 and r0 + 8 of heads 2 q4 and 2 q4 + 1 of each tile: the maxima and sums of a head run over the 8
 // lanes of equal q4.  Ends with the block in step (shared memory reusable).
-// BULK: the rows come by the copy engine (bars = the warp's NSLOT mbarriers; ring = the slots' phase bits, bit 31 set once
-// a wait ran out, after which the warp computes nothing more); otherwise by cp.async.
-template <int NSLOT, int NT, bool BULK>
+// SRC: how the rows come.  ATT_SRC_ASYNC: BF16 rows by cp.async; ATT_SRC_BULK: BF16 rows by the copy engine (bars = the
+// warp's NSLOT mbarriers; ring = the slots' phase bits, bit 31 set once a wait ran out, after which the warp computes
+// nothing more); ATT_SRC_Q8: the 8-bit cache (NSLOT = 2: one BF16 slot and two raw slots).
+enum { ATT_SRC_ASYNC = 0, ATT_SRC_BULK = 1, ATT_SRC_Q8 = 2 };
+template <int NSLOT, int NT, int SRC>
 __device__ __forceinline__ void attn_keys(const AttnArgs& a, const float* __restrict__ q, const KvView& kv, int t, int kvh, int kv0,
                                           int p0, int p1, unsigned char* att_smem, float* pp, size_t head_stride, unsigned bars,
                                           unsigned& ring) {
@@ -255,12 +313,17 @@ __device__ __forceinline__ void attn_keys(const AttnArgs& a, const float* __rest
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, q4 = lane & 3, r0 = lane >> 2;
     const int group = a.n_head / a.n_kv;
     unsigned char* stage = att_smem + (size_t) warp * STAGE;
+    constexpr bool BULK = SRC == ATT_SRC_BULK, Q8 = SRC == ATT_SRC_Q8;
+    static_assert(!Q8 || NSLOT == 2, "the 8-bit cache's ring has two raw slots");
+    unsigned char* raw = stage + ATT_SLOT;      // Q8: the two raw slots behind the BF16 slot
     int p = p0 + warp * ATT_MT;
     if (BULK) {
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the ring held a state (plain stores) before
         if (ring >> 31) p = p1;
 #pragma unroll
         for (int i = 0; i < NSLOT - 1; ++i) attn_fill_slot_bulk(stage + i * ATT_SLOT, bars + 8 * i, kv, a.n_kv, kvh, kv0, p + i * STRIDE, p1, lane);
+    } else if (Q8) {
+        attn_fill_raw(raw, kv, a.n_kv, kvh, kv0, p, p1, lane);
     } else {
 #pragma unroll
         for (int i = 0; i < NSLOT - 1; ++i) attn_fill_slot(stage + i * ATT_SLOT, kv, a.n_kv, kvh, kv0, p + i * STRIDE, p1, lane);
@@ -307,12 +370,17 @@ __device__ __forceinline__ void attn_keys(const AttnArgs& a, const float* __rest
                 ring |= 1u << 31;
                 break;
             }
+        } else if (Q8) {
+            attn_fill_raw(raw + nxt * ATT_RAW, kv, a.n_kv, kvh, kv0, p + STRIDE, p1, lane);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+            __syncwarp();
+            attn_expand_raw(stage, raw + cur * ATT_RAW, lane);      // the BF16 slot's reads ended with the previous step's __syncwarp
         } else {
             attn_fill_slot(stage + nxt * ATT_SLOT, kv, a.n_kv, kvh, kv0, p + (NSLOT - 1) * STRIDE, p1, lane);
             asm volatile("cp.async.wait_group %0;" ::"n"(NSLOT - 1) : "memory");
         }
         __syncwarp();
-        const unsigned char* slot = stage + cur * ATT_SLOT;
+        const unsigned char* slot = Q8 ? stage : stage + cur * ATT_SLOT;
         nxt = cur;
         cur = cur + 1 == NSLOT ? 0 : cur + 1;
         // scores: two accumulation chains a tile (even and odd dim steps)
@@ -415,7 +483,7 @@ __device__ __forceinline__ void attn_keys(const AttnArgs& a, const float* __rest
 }
 
 // One block per (split, KV head, row): the split's keys as the reference cuts them.
-template <int NSLOT, int NT>
+template <int NSLOT, int NT, int SRC>
 __global__ void __launch_bounds__(32 * ATT_MMA_WARPS) attn_split_mma_kernel(AttnArgs a, const float* __restrict__ q, KvView kv,
                                                                             const RowInfo* __restrict__ ri, float* __restrict__ part) {
     extern __shared__ __align__(16) unsigned char att_smem[];      // the warps' rings, later their states
@@ -428,7 +496,7 @@ __global__ void __launch_bounds__(32 * ATT_MMA_WARPS) attn_split_mma_kernel(Attn
     const int chunk = (pos + nsr) / nsr;
     const int p0 = split * chunk, p1 = min(pos + 1, p0 + chunk);
     unsigned ring = 0;
-    attn_keys<NSLOT, NT, false>(a, q, kv, t, kvh, kv0, p0, p1, att_smem, part + (((size_t) t * a.n_head + kvh * group) * a.n_splits + split) * (ATT_HD + 2),
+    attn_keys<NSLOT, NT, SRC>(a, q, kv, t, kvh, kv0, p0, p1, att_smem, part + (((size_t) t * a.n_head + kvh * group) * a.n_splits + split) * (ATT_HD + 2),
                                 (size_t) a.n_splits * (ATT_HD + 2), 0u, ring);
 }
 
@@ -488,7 +556,7 @@ __device__ __forceinline__ AttnPlan attn_plan(const RowInfo* __restrict__ ri, in
     return pl;
 }
 
-template <int NSLOT, int NT, bool BULK>
+template <int NSLOT, int NT, int SRC>
 __global__ void __launch_bounds__(32 * ATT_MMA_WARPS) attn_flat_mma_kernel(AttnArgs a, const float* __restrict__ q, KvView kv,
                                                                            const RowInfo* __restrict__ ri, float* __restrict__ part, int T) {
     extern __shared__ __align__(16) unsigned char att_smem[];
@@ -497,7 +565,7 @@ __global__ void __launch_bounds__(32 * ATT_MMA_WARPS) attn_flat_mma_kernel(AttnA
     const int group = a.n_head / a.n_kv;
     const unsigned bars = smem_u32(&att_bars[threadIdx.x >> 5][0]);
     unsigned ring = 0;
-    if (BULK) {
+    if (SRC == ATT_SRC_BULK) {
         if ((threadIdx.x & 31) < NSLOT) mbar_init(bars + 8 * (threadIdx.x & 31), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         __syncwarp();
@@ -520,9 +588,9 @@ __global__ void __launch_bounds__(32 * ATT_MMA_WARPS) attn_flat_mma_kernel(AttnA
         const int end = min(xe, first + u);
         const int pos = max(ri[t].pos, 0), kv0 = ri[t].kv0;
         const int slot = (int) blockIdx.x - first / pl.per;
-        attn_keys<NSLOT, NT, BULK>(a, q, kv, t, kvh, kv0, (x - first) * ATT_MT, min(pos + 1, (end - first) * ATT_MT), att_smem,
-                                   part + (((size_t) t * a.n_head + kvh * group) * a.n_splits + slot) * (ATT_HD + 2),
-                                   (size_t) a.n_splits * (ATT_HD + 2), bars, ring);
+        attn_keys<NSLOT, NT, SRC>(a, q, kv, t, kvh, kv0, (x - first) * ATT_MT, min(pos + 1, (end - first) * ATT_MT), att_smem,
+                                  part + (((size_t) t * a.n_head + kvh * group) * a.n_splits + slot) * (ATT_HD + 2),
+                                  (size_t) a.n_splits * (ATT_HD + 2), bars, ring);
         x = end;
     }
 }
@@ -601,27 +669,27 @@ static int attn_sm_count() {
     return n[dev & 15] > 0 ? n[dev & 15] : 148;
 }
 
-template <int NSLOT, int NT, bool BULK>
+template <int NSLOT, int NT, int SRC>
 static void launch_attn_flat(cudaStream_t s, int n_blocks, const AttnArgs& a, const float* q, const KvView& kv, const RowInfo* ri, float* part, int T) {
     static bool done[16];
     constexpr int SMEM = ATT_MMA_WARPS * NSLOT * ATT_SLOT;
-    attn_smem_attr(attn_flat_mma_kernel<NSLOT, NT, BULK>, SMEM, done);
-    launch(attn_flat_mma_kernel<NSLOT, NT, BULK>, dim3((unsigned) n_blocks), 32 * ATT_MMA_WARPS, (size_t) SMEM, s, a, q, kv, ri, part, T);
+    attn_smem_attr(attn_flat_mma_kernel<NSLOT, NT, SRC>, SMEM, done);
+    launch(attn_flat_mma_kernel<NSLOT, NT, SRC>, dim3((unsigned) n_blocks), 32 * ATT_MMA_WARPS, (size_t) SMEM, s, a, q, kv, ri, part, T);
 }
 
-template <int NSLOT, bool BULK>
+template <int NSLOT, int SRC>
 static void launch_attn_flat_group(cudaStream_t s, int n_blocks, int group, const AttnArgs& a, const float* q, const KvView& kv, const RowInfo* ri,
                                    float* part, int T) {
-    if (group <= 8) launch_attn_flat<NSLOT, 1, BULK>(s, n_blocks, a, q, kv, ri, part, T);
-    else launch_attn_flat<NSLOT, 2, BULK>(s, n_blocks, a, q, kv, ri, part, T);
+    if (group <= 8) launch_attn_flat<NSLOT, 1, SRC>(s, n_blocks, a, q, kv, ri, part, T);
+    else launch_attn_flat<NSLOT, 2, SRC>(s, n_blocks, a, q, kv, ri, part, T);
 }
 
-template <int NT>
+template <int NT, int SRC>
 static void launch_attn_split(cudaStream_t s, const AttnArgs& a, const float* q, const KvView& kv, const RowInfo* ri, float* part, int T) {
     static bool done[16];
     constexpr int SMEM = ATT_MMA_WARPS * 2 * ATT_SLOT;
-    attn_smem_attr(attn_split_mma_kernel<2, NT>, SMEM, done);
-    launch(attn_split_mma_kernel<2, NT>, dim3((unsigned) a.n_splits, (unsigned) a.n_kv, (unsigned) T), 32 * ATT_MMA_WARPS, (size_t) SMEM, s,
+    attn_smem_attr(attn_split_mma_kernel<2, NT, SRC>, SMEM, done);
+    launch(attn_split_mma_kernel<2, NT, SRC>, dim3((unsigned) a.n_splits, (unsigned) a.n_kv, (unsigned) T), 32 * ATT_MMA_WARPS, (size_t) SMEM, s,
            a, q, kv, ri, part);
 }
 
@@ -640,27 +708,36 @@ int nsl_attn_status(void) {
 
 void kc_attn(cudaStream_t s, AttnArgs a, const float* q, KvView kv, const RowInfo* ri, float* part, const float* g, float* o, int T) {
     if (T < 1) return;
-    if (kv.fmt != KV_BF16) { set_error("kc_attn: KV cache format %d is not served by this library (BF16 = %d only)", kv.fmt, (int) KV_BF16); return; }
-    const int group = a.n_kv > 0 ? a.n_head / a.n_kv : 0;
-    if (a.n_kv < 1 || a.n_head % a.n_kv || group < 1 || group > ATT_MAX_GROUP || a.n_splits < 1 || a.chunk < 0 || (a.chunk == 0 && a.n_splits > 1) || !aligned16(q) ||
-        !aligned16(kv.a.k) || !aligned16(kv.a.v) || (kv.b.k && (!aligned16(kv.b.k) || !aligned16(kv.b.v)))) {
-        set_error("kc_attn: %d query heads over %d KV heads (groups of 1..%d), %d splits of %d keys, or unaligned buffers", a.n_head,
-                  a.n_kv, (int) ATT_MAX_GROUP, a.n_splits, a.chunk);
+    if (kv.fmt != KV_BF16 && kv.fmt != KV_Q8) {
+        set_error("kc_attn: KV cache format %d is not served by this library (BF16 = %d and Q8 = %d only)", kv.fmt, (int) KV_BF16, (int) KV_Q8);
         return;
     }
-    const bool flat = (g_attn_variant == 1 || g_attn_variant >= 3) && a.n_splits >= 3 && a.chunk > 0 && T <= ATT_MAX_ROWS;
+    const bool q8 = kv.fmt == KV_Q8;
+    const int group = a.n_kv > 0 ? a.n_head / a.n_kv : 0;
+    if (a.n_kv < 1 || a.n_head % a.n_kv || group < 1 || group > ATT_MAX_GROUP || a.n_splits < 1 || a.chunk < 0 || (a.chunk == 0 && a.n_splits > 1) || !aligned16(q) ||
+        !aligned16(kv.a.k) || !aligned16(kv.a.v) || (kv.b.k && (!aligned16(kv.b.k) || !aligned16(kv.b.v))) ||
+        (q8 && (!kv.a.ks || !kv.a.vs || (kv.b.k && (!kv.b.ks || !kv.b.vs))))) {
+        set_error("kc_attn: %d query heads over %d KV heads (groups of 1..%d), %d splits of %d keys, unaligned buffers or an 8-bit cache without scales",
+                  a.n_head, a.n_kv, (int) ATT_MAX_GROUP, a.n_splits, a.chunk);
+        return;
+    }
+    const int variant = q8 && (g_attn_variant == 0 || g_attn_variant == 3 || g_attn_variant >= 5) ? 1 : g_attn_variant;      // Q8: forms 1, 2, 4
+    const bool flat = (variant == 1 || variant >= 3) && a.n_splits >= 3 && a.chunk > 0 && T <= ATT_MAX_ROWS;
     int n_blocks = 0;
     if (flat) {
-        const bool three = g_attn_variant == 3 || g_attn_variant == 6, bulk = g_attn_variant >= 5;
+        const bool three = variant == 3 || variant == 6, bulk = variant >= 5;
         // three blocks with two-slot rings (70 KB of shared memory) fit an SM, two with three-slot rings
-        n_blocks = (three || g_attn_variant == 4 ? 2 : 3) * attn_sm_count();
-        if (!three && !bulk) launch_attn_flat_group<2, false>(s, n_blocks, group, a, q, kv, ri, part, T);
-        else if (!three) launch_attn_flat_group<2, true>(s, n_blocks, group, a, q, kv, ri, part, T);
-        else if (!bulk) launch_attn_flat_group<3, false>(s, n_blocks, group, a, q, kv, ri, part, T);
-        else launch_attn_flat_group<3, true>(s, n_blocks, group, a, q, kv, ri, part, T);
-    } else if (g_attn_variant != 0) {
-        if (group <= 8) launch_attn_split<1>(s, a, q, kv, ri, part, T);
-        else launch_attn_split<2>(s, a, q, kv, ri, part, T);
+        n_blocks = (three || variant == 4 ? 2 : 3) * attn_sm_count();
+        if (q8) launch_attn_flat_group<2, ATT_SRC_Q8>(s, n_blocks, group, a, q, kv, ri, part, T);
+        else if (!three && !bulk) launch_attn_flat_group<2, ATT_SRC_ASYNC>(s, n_blocks, group, a, q, kv, ri, part, T);
+        else if (!three) launch_attn_flat_group<2, ATT_SRC_BULK>(s, n_blocks, group, a, q, kv, ri, part, T);
+        else if (!bulk) launch_attn_flat_group<3, ATT_SRC_ASYNC>(s, n_blocks, group, a, q, kv, ri, part, T);
+        else launch_attn_flat_group<3, ATT_SRC_BULK>(s, n_blocks, group, a, q, kv, ri, part, T);
+    } else if (variant != 0) {
+        if (q8 && group <= 8) launch_attn_split<1, ATT_SRC_Q8>(s, a, q, kv, ri, part, T);
+        else if (q8) launch_attn_split<2, ATT_SRC_Q8>(s, a, q, kv, ri, part, T);
+        else if (group <= 8) launch_attn_split<1, ATT_SRC_ASYNC>(s, a, q, kv, ri, part, T);
+        else launch_attn_split<2, ATT_SRC_ASYNC>(s, a, q, kv, ri, part, T);
     } else {
         launch(attn_split_kernel, dim3((unsigned) a.n_splits, (unsigned) a.n_kv, (unsigned) T), 32 * group, 0, s, a, q, kv, ri, part);
     }

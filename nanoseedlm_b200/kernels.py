@@ -269,18 +269,27 @@ def kt_argmax(logits, prob=False):
     return (out.cpu().numpy(), pr.cpu().numpy()) if prob else out.cpu().numpy()
 
 
-def kt_attn(a, q, Kc, Vc, pos, kv0, g=None, nv=None):
-    """kc_attn on a BF16 cache (tests/kernel_backend_cuda.c: kt_attn): Kc / Vc bf16 bits [rows][n_kv][128]; rows of the
-    cache below nv (default: all) sit in segment a, the rest in segment b."""
+def kt_attn(a, q, Kc, Vc, pos, kv0, g=None, nv=None, scales=None):
+    """kc_attn (tests/kernel_backend_cuda.c: kt_attn, kt_attn_q8): Kc / Vc [rows][n_kv][128] as bf16 bits, or int8 codes
+    with scales = (ks, vs) [rows][n_kv] f32 (the 8-bit cache); rows of the cache below nv (default: all) sit in segment a,
+    the rest in segment b."""
     T = len(pos)
-    Kc, Vc = np.asarray(Kc, np.uint16), np.asarray(Vc, np.uint16)
+    q8 = scales is not None
+    Kc, Vc = np.asarray(Kc, np.int8 if q8 else np.uint16), np.asarray(Vc, np.int8 if q8 else np.uint16)
     nv = Kc.shape[0] if nv is None else nv
-    keep = [dev(Kc[:nv]), dev(Vc[:nv]), dev(Kc[nv:]) if nv < Kc.shape[0] else None, dev(Vc[nv:]) if nv < Kc.shape[0] else None]
+    two = nv < Kc.shape[0]
+    keep = [dev(Kc[:nv]), dev(Vc[:nv]), dev(Kc[nv:]) if two else None, dev(Vc[nv:]) if two else None]
     kv = L.KvView()
     kv.a.k, kv.a.v = keep[0].data_ptr(), keep[1].data_ptr()
-    if keep[2] is not None:
+    if two:
         kv.b.k, kv.b.v = keep[2].data_ptr(), keep[3].data_ptr()
-    kv.nv, kv.fmt = nv, 0
+    if q8:
+        ks, vs = (np.asarray(x, np.float32) for x in scales)
+        keep += [dev(ks[:nv]), dev(vs[:nv]), dev(ks[nv:]) if two else None, dev(vs[nv:]) if two else None]
+        kv.a.ks, kv.a.vs = keep[4].data_ptr(), keep[5].data_ptr()
+        if two:
+            kv.b.ks, kv.b.vs = keep[6].data_ptr(), keep[7].data_ptr()
+    kv.nv, kv.fmt = nv, 1 if q8 else 0
     ri = (L.RowInfo * T)()
     for t in range(T):
         ri[t].pos, ri[t].kv0 = int(pos[t]), int(kv0[t])

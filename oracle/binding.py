@@ -408,3 +408,17 @@ def attn_decode(q, Kc, Vc, pos, kv0, n_kv, scale, g=None):
     if g is not None:
         out = bfr(out * softplus_gate(np.asarray(g, np.float32)))
     return out, att
+
+
+def kv_q8_cache(bits):
+    """A BF16 cache [rows][n_kv][128] (bit patterns) quantized to the 8-bit KV format as the reference's kernel test does it
+    (tests/test_mova_kernels.c:584-604): per (row, head) scale = max|x| / 127 (1 if the row is zero), code = lrintf(x /
+    scale), all in f32.  Returns (codes int8, scales f32 [rows][n_kv], the BF16 bits of code * scale: the values a kernel
+    reads from this cache)."""
+    x = (np.asarray(bits, np.uint16).astype(np.uint32) << 16).view(np.float32)
+    m = np.max(np.abs(x), axis=-1)
+    sc = np.where(m > 0, (m / np.float32(127.0)).astype(np.float32), np.float32(1.0)).astype(np.float32)
+    codes = np.rint((x / sc[..., None]).astype(np.float32)).astype(np.int8)      # rint: halves to even, as lrintf
+    deq = (codes.astype(np.float32) * sc[..., None]).astype(np.float32)
+    return codes, sc, f2bf(deq).reshape(x.shape)
+

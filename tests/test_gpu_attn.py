@@ -1,8 +1,9 @@
-"""Decode attention over a BF16 KV cache (kc_attn) against a double-precision reference.
+"""Decode attention over a BF16 or 8-bit KV cache (kc_attn) against a double-precision reference.
 
 The first case is the reference's own kernel test (tests/test_mova_kernels.c:660-715): GQA 8/2, three rows at
 positions 300, 299, 37 in sequence slots based at cache rows 0, 310, 600, five splits; bound |o - ref| <= |ref| / 128 + 2e-6
-(met by at least 999 outputs in 1000, twice the bound by all: see run_variant)."""
+(met by at least 999 outputs in 1000, twice the bound by all: see run_variant).  Every case also runs on the 8-bit cache
+built from the same values as the reference's test builds it (tests/test_mova_kernels.c:584-604, 688)."""
 import numpy as np
 import pytest
 
@@ -15,9 +16,11 @@ def run_case(nh, nkv, NP, pos, kv0, ns, chunk, gate=True, nv=None, seed=21):
     for variant in (1, 2, 3, 4, 5, 6, 0):      # tensor cores (balanced blocks; a block per split; three-slot rings; two blocks an
                                                # SM; rows by the copy engine with two and three slots), the scalar pass
         run_variant(variant, nh, nkv, NP, pos, kv0, ns, chunk, gate, nv, seed)
+    for variant in (1, 2, 4):                  # the 8-bit cache: balanced blocks, a block per split, two blocks an SM
+        run_variant(variant, nh, nkv, NP, pos, kv0, ns, chunk, gate, nv, seed, q8=True)
 
 
-def run_variant(variant, nh, nkv, NP, pos, kv0, ns, chunk, gate, nv, seed):
+def run_variant(variant, nh, nkv, NP, pos, kv0, ns, chunk, gate, nv, seed, q8=False):
     from nanoseedlm_b200 import kernels, lib as L
     L.load().nsl_attn_set_variant(variant)
     rng = np.random.default_rng(seed)
@@ -28,7 +31,12 @@ def run_variant(variant, nh, nkv, NP, pos, kv0, ns, chunk, gate, nv, seed):
     Vc = B.f2bf(rng.random((NP, nkv, 128), np.float32) * 2 - 1)
     scale = np.float32(1 / np.sqrt(128.0))
     a = L.AttnArgs(nh, nkv, chunk, ns, float(scale))
-    o = kernels.kt_attn(a, q, Kc, Vc, pos, kv0, g if gate else None, nv)
+    if q8:      # the cache quantized per (row, head); the reference sees the values the kernel reads, bf16(code * scale)
+        kq, ks, Kc = B.kv_q8_cache(Kc)
+        vq, vs, Vc = B.kv_q8_cache(Vc)
+        o = kernels.kt_attn(a, q, kq, vq, pos, kv0, g if gate else None, nv, scales=(ks, vs))
+    else:
+        o = kernels.kt_attn(a, q, Kc, Vc, pos, kv0, g if gate else None, nv)
     ref, _ = B.attn_decode(q, Kc, Vc, pos, kv0, nkv, scale, g if gate else None)
     L.load().nsl_attn_set_variant(1)
     assert L.load().nsl_attn_status() == 0      # no wait for K / V rows ran out
@@ -68,9 +76,9 @@ def test_refuses_other_cache_formats_and_groups():
     import torch
     from nanoseedlm_b200 import lib as L
     kv = L.KvView()
-    kv.fmt = 1
+    kv.fmt = 2      # FP8: the MLA caches' format
     L.load().kc_attn(None, L.AttnArgs(8, 2, 64, 2, 0.1), None, kv, None, None, None, None, 1)
-    with pytest.raises(RuntimeError, match="format 1"):
+    with pytest.raises(RuntimeError, match="format 2"):
         L.check()
     kv.fmt = 0
     L.load().kc_attn(None, L.AttnArgs(64, 2, 64, 2, 0.1), None, kv, None, None, None, None, 1)
