@@ -586,7 +586,7 @@ def run_lmhead(args):
 
 ATTN_FORMS = {0: "attn_split_kernel", 1: "attn_flat_mma_kernel<2>", 2: "attn_split_mma_kernel<2>", 3: "attn_flat_mma_kernel<3>",
               4: "attn_flat_mma_kernel<2>, two blocks an SM", 5: "attn_flat_mma_kernel<2, bulk copies>",
-              6: "attn_flat_mma_kernel<3, bulk copies>"}
+              6: "attn_flat_mma_kernel<3, bulk copies>", 7: "attn_flat_mma_kernel<2, two warps a ring>"}
 
 
 def run_attn(args):

@@ -169,13 +169,14 @@ typedef struct { KvSeg a, b; int32_t nv, fmt; } KvView;             /* positions
  * codes, ks / vs [rows][n_kv] f32: a value is bf16(code * scale), engine/kernels_moe.cu:807-824); FP8 / FP4 are refused.
  * Any group size n_head / n_kv up to 16. */
 void kc_attn(cudaStream_t s, AttnArgs a, const float* q, KvView kv, const RowInfo* ri, float* part, const float* g, float* o, int T);
-/* No counterpart in the reference: the form of kc_attn's first pass.  1 (default): tensor cores (heads of a KV head as
- * the columns of the products), the step's keys dealt evenly to the blocks whatever a.n_splits asks (used when
- * a.n_splits >= 3 and T <= 1024; otherwise form 2); 2: tensor cores, one block per (split, KV head, row); 3 and 4: form 1
- * with three-slot rings / two blocks an SM; 5 and 6: forms 1 and 3 with the K and V rows brought by the copy engine
- * (cp.async.bulk); 0: scalar, one warp per head.  The partials' use of `part` is internal to the two kernels in every
- * form and never exceeds the size above.  nsl_attn_status: 0, or 1 once a bounded wait for rows ran out in forms 5 / 6
- * (that call's outputs are invalid; never expected); synchronises the device. */
+/* No counterpart in the reference: the form of kc_attn's first pass.  Tensor cores (heads of a KV head as the columns of
+ * the products) with the step's keys dealt evenly to the blocks whatever a.n_splits asks (used when a.n_splits >= 3 and
+ * T <= 1024; otherwise form 2): 1 (default) one warp per ring of K / V rows, 7 two warps per ring (groups of <= 8; larger
+ * groups run form 1), 3 and 4 form 1 with three-slot rings / two blocks an SM, 5 and 6 forms 1 and 3 with the rows
+ * brought by the copy engine (cp.async.bulk).  2: tensor cores, one block per (split, KV head, row).  0: scalar, one warp
+ * per head (BF16 caches).  The partials' use of `part` is internal to the two kernels in every form and never exceeds
+ * the size above.  nsl_attn_status: 0, or 1 once a bounded wait for rows ran out in forms 5 / 6 (that call's outputs are
+ * invalid; never expected); synchronises the device. */
 void nsl_attn_set_variant(int v);
 int nsl_attn_status(void);
 

@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(32 * ATT_MAX_GROUP) attn_split_kernel(AttnArgs
 constexpr int ATT_MMA_WARPS = 4, ATT_VROW = 272, ATT_MT = 16, ATT_SLOT = ATT_MT * (ATT_KROW + ATT_VROW);
 constexpr int ATT_MAX_ROWS = 1024;      // rows of a step in the balanced form (the reference's rows x splits <= 1024)
 static_assert(2 * ATT_SLOT >= ATT_MAX_GROUP * 130 * 4, "a warp's ring holds its final state");
-static_assert(32 * ATT_MMA_WARPS == ATT_HD, "the merge gives a thread one dim");
+static_assert(32 * ATT_MMA_WARPS == ATT_HD && ATT_MMA_WARPS == 4, "the merge gives a thread one dim; ring_sync numbers four rings");
 
 __device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
     asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
@@ -148,24 +148,26 @@ __device__ __forceinline__ void attn_cp16s(unsigned smem, const void* gmem) {
 
 // The 16 K rows and 16 V rows of the step at key p into a slot: 32 lanes x 8 pieces of 16 bytes each (rows beyond the range
 // repeat its last row; their scores are masked).  Always one cp.async group, empty when the step lies beyond the range.
-__device__ __forceinline__ void attn_fill_slot(unsigned char* slot, const KvView& kv, int n_kv, int kvh, int kv0, int p, int p1, int lane) {
+// N of the step's 8 row pairs, from pair i0 on (a ring's warps share a step's copies).
+template <int N = ATT_MT / 2>
+__device__ __forceinline__ void attn_fill_slot(unsigned char* slot, const KvView& kv, int n_kv, int kvh, int kv0, int p, int p1, int lane, int i0 = 0) {
     if (p < p1) {
         const int rl = lane >> 4, piece = lane & 15;
-        const unsigned sk = (unsigned) __cvta_generic_to_shared(slot) + rl * ATT_KROW + piece * 16, sv = sk + ATT_MT * ATT_KROW;
+        const unsigned sk = (unsigned) __cvta_generic_to_shared(slot) + (2 * i0 + rl) * ATT_KROW + piece * 16, sv = sk + ATT_MT * ATT_KROW;
         const int row0 = kv0 + p;
         if (p + ATT_MT <= p1 && (row0 + ATT_MT <= kv.nv || row0 >= kv.nv)) {      // 16 whole rows of one segment: one address, strides
-            const unsigned char* kb = (const unsigned char*) (kv_row(kv, 0, row0 + rl, n_kv, kvh) + piece * 8);
-            const unsigned char* vb = (const unsigned char*) (kv_row(kv, 1, row0 + rl, n_kv, kvh) + piece * 8);
+            const unsigned char* kb = (const unsigned char*) (kv_row(kv, 0, row0 + 2 * i0 + rl, n_kv, kvh) + piece * 8);
+            const unsigned char* vb = (const unsigned char*) (kv_row(kv, 1, row0 + 2 * i0 + rl, n_kv, kvh) + piece * 8);
             const size_t two_rows = (size_t) n_kv * (2 * ATT_HD * 2);
 #pragma unroll
-            for (int i = 0; i < ATT_MT / 2; ++i) {
+            for (int i = 0; i < N; ++i) {
                 attn_cp16s(sk + i * 2 * ATT_KROW, kb + i * two_rows);
                 attn_cp16s(sv + i * 2 * ATT_VROW, vb + i * two_rows);
             }
         } else {
 #pragma unroll
-            for (int i = 0; i < ATT_MT / 2; ++i) {
-                const int row = kv0 + min(p + 2 * i + rl, p1 - 1);
+            for (int i = 0; i < N; ++i) {
+                const int row = kv0 + min(p + 2 * (i0 + i) + rl, p1 - 1);
                 attn_cp16s(sk + i * 2 * ATT_KROW, kv_row(kv, 0, row, n_kv, kvh) + piece * 8);
                 attn_cp16s(sv + i * 2 * ATT_VROW, kv_row(kv, 1, row, n_kv, kvh) + piece * 8);
             }
@@ -239,22 +241,26 @@ __device__ __forceinline__ const KvSeg& kv_seg_of(const KvView& kv, int abs_pos,
     row = first ? abs_pos : abs_pos - kv.nv;
     return first ? kv.a : kv.b;
 }
-// The step at key p, raw: 256 pieces of 16 bytes (8 a lane) and 32 scales (one a lane).  Always one cp.async group.
-__device__ __forceinline__ void attn_fill_raw(unsigned char* raw, const KvView& kv, int n_kv, int kvh, int kv0, int p, int p1, int lane) {
+// The step at key p, raw: 256 pieces of 16 bytes (8 rounds of 32) and 32 scales.  This warp takes N rounds from round i0 on
+// (and the scales when i0 = 0).  Always one cp.async group.
+template <int N = 8>
+__device__ __forceinline__ void attn_fill_raw(unsigned char* raw, const KvView& kv, int n_kv, int kvh, int kv0, int p, int p1, int lane, int i0 = 0) {
     if (p < p1) {
         const unsigned base = smem_u32(raw);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int id = i * 32 + lane, is_v = id >> 7, r = (id >> 3) & 15, piece = id & 7;
+        for (int i = 0; i < N; ++i) {
+            const int id = (i0 + i) * 32 + lane, is_v = id >> 7, r = (id >> 3) & 15, piece = id & 7;
             int row;
             const KvSeg& sg = kv_seg_of(kv, kv0 + min(p + r, p1 - 1), row);
             attn_cp16s(base + is_v * ATT_RAW_V + r * ATT_HD + piece * 16,
                        (const unsigned char*) (is_v ? sg.v : sg.k) + ((size_t) row * n_kv + kvh) * ATT_HD + piece * 16);
         }
-        const int is_v = lane >> 4, r = lane & 15;
-        int row;
-        const KvSeg& sg = kv_seg_of(kv, kv0 + min(p + r, p1 - 1), row);
-        attn_cp4s(base + ATT_RAW_SCALES + lane * 4, (is_v ? sg.vs : sg.ks) + (size_t) row * n_kv + kvh);
+        if (i0 == 0) {
+            const int is_v = lane >> 4, r = lane & 15;
+            int row;
+            const KvSeg& sg = kv_seg_of(kv, kv0 + min(p + r, p1 - 1), row);
+            attn_cp4s(base + ATT_RAW_SCALES + lane * 4, (is_v ? sg.vs : sg.ks) + (size_t) row * n_kv + kvh);
+        }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
 }
@@ -262,11 +268,12 @@ __device__ __forceinline__ uint32_t q8_pair(uint32_t u, int i, float s) {      /
     const float a = (float) (int) (signed char) ((u >> (8 * i)) & 255u) * s, b = (float) (int) (signed char) ((u >> (8 * i + 8)) & 255u) * s;
     return pack_bf16x2(a, b);
 }
-// Raw rows -> the BF16 slot (rows 272 bytes apart, K then V).
-__device__ __forceinline__ void attn_expand_raw(unsigned char* slot, const unsigned char* raw, int lane) {
+// Raw rows -> the BF16 slot (rows 272 bytes apart, K then V): N of the 8 rounds from round i0 on.
+template <int N = 8>
+__device__ __forceinline__ void attn_expand_raw(unsigned char* slot, const unsigned char* raw, int lane, int i0 = 0) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const int id = i * 32 + lane, is_v = id >> 7, r = (id >> 3) & 15, piece = id & 7;
+    for (int i = 0; i < N; ++i) {
+        const int id = (i0 + i) * 32 + lane, is_v = id >> 7, r = (id >> 3) & 15, piece = id & 7;
         const uint4 u = *(const uint4*) (raw + is_v * ATT_RAW_V + r * ATT_HD + piece * 16);
         const float sc = *(const float*) (raw + ATT_RAW_SCALES + (is_v * ATT_MT + r) * 4);
         uint4 lo, hi;
@@ -304,29 +311,49 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {      // an 8 x
 // SRC: how the rows come.  ATT_SRC_ASYNC: BF16 rows by cp.async; ATT_SRC_BULK: BF16 rows by the copy engine (bars = the
 // warp's NSLOT mbarriers; ring = the slots' phase bits, bit 31 set once a wait ran out, after which the warp computes
 // nothing more); ATT_SRC_Q8: the 8-bit cache (NSLOT = 2: one BF16 slot and two raw slots).
+// PW: warps per ring (block = 4 rings x PW warps).  2: the ring's two warps share a step: each copies half its rows, both
+// compute the scores and the softmax (identical values), each takes 64 of the 128 dims of the value product; they meet at a
+// named barrier of their own.  Twice the warps on the same shared memory, for the latency of a warp's own step.
 enum { ATT_SRC_ASYNC = 0, ATT_SRC_BULK = 1, ATT_SRC_Q8 = 2 };
-template <int NSLOT, int NT, int SRC>
+template <int PW>
+__device__ __forceinline__ void ring_sync(int ring) {
+    if (PW == 1) {
+        __syncwarp();
+    } else if (ring == 0) {      // literal barrier numbers: the kernel then reserves 5 barriers, not all 16
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * PW) : "memory");
+    } else if (ring == 1) {
+        asm volatile("bar.sync 2, %0;" ::"n"(32 * PW) : "memory");
+    } else if (ring == 2) {
+        asm volatile("bar.sync 3, %0;" ::"n"(32 * PW) : "memory");
+    } else {
+        asm volatile("bar.sync 4, %0;" ::"n"(32 * PW) : "memory");
+    }
+}
+template <int NSLOT, int NT, int SRC, int PW = 1>
 __device__ __forceinline__ void attn_keys(const AttnArgs& a, const float* __restrict__ q, const KvView& kv, int t, int kvh, int kv0,
                                           int p0, int p1, unsigned char* att_smem, float* pp, size_t head_stride, unsigned bars,
                                           unsigned& ring) {
     constexpr int STAGE = NSLOT * ATT_SLOT, STRIDE = ATT_MMA_WARPS * ATT_MT;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, q4 = lane & 3, r0 = lane >> 2;
+    const int lane = threadIdx.x & 31, ring_id = (threadIdx.x >> 5) / PW, half = (threadIdx.x >> 5) % PW, q4 = lane & 3, r0 = lane >> 2;
     const int group = a.n_head / a.n_kv;
-    unsigned char* stage = att_smem + (size_t) warp * STAGE;
+    unsigned char* stage = att_smem + (size_t) ring_id * STAGE;
     constexpr bool BULK = SRC == ATT_SRC_BULK, Q8 = SRC == ATT_SRC_Q8;
+    constexpr int DT = 8 / PW;      // tiles of 16 dims of the value product a warp takes
     static_assert(!Q8 || NSLOT == 2, "the 8-bit cache's ring has two raw slots");
+    static_assert(PW == 1 || (PW == 2 && !BULK), "rings of two warps copy with cp.async");
     unsigned char* raw = stage + ATT_SLOT;      // Q8: the two raw slots behind the BF16 slot
-    int p = p0 + warp * ATT_MT;
+    int p = p0 + ring_id * ATT_MT;
     if (BULK) {
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the ring held a state (plain stores) before
         if (ring >> 31) p = p1;
 #pragma unroll
         for (int i = 0; i < NSLOT - 1; ++i) attn_fill_slot_bulk(stage + i * ATT_SLOT, bars + 8 * i, kv, a.n_kv, kvh, kv0, p + i * STRIDE, p1, lane);
     } else if (Q8) {
-        attn_fill_raw(raw, kv, a.n_kv, kvh, kv0, p, p1, lane);
+        attn_fill_raw<8 / PW>(raw, kv, a.n_kv, kvh, kv0, p, p1, lane, half * (8 / PW));
     } else {
 #pragma unroll
-        for (int i = 0; i < NSLOT - 1; ++i) attn_fill_slot(stage + i * ATT_SLOT, kv, a.n_kv, kvh, kv0, p + i * STRIDE, p1, lane);
+        for (int i = 0; i < NSLOT - 1; ++i)
+            attn_fill_slot<8 / PW>(stage + i * ATT_SLOT, kv, a.n_kv, kvh, kv0, p + i * STRIDE, p1, lane, half * (8 / PW));
     }
     // Q^T as the B fragments of the 8 steps over the 128 dims: column r0 of a tile = head 8 nt + r0 (zero beyond the group);
     // the first rows of K and V fly meanwhile
@@ -344,22 +371,22 @@ __device__ __forceinline__ void attn_keys(const AttnArgs& a, const float* __rest
             qb[nt][j][1] = pack_bf16x2(y.x, y.y);
         }
     }
-    float m[NT][2], l[NT][2], ot[NT][8][4];      // [.][0]: head 2 q4 of the tile, [.][1]: head 2 q4 + 1; m in base-2 units
+    float m[NT][2], l[NT][2], ot[NT][DT][4];      // [.][0]: head 2 q4 of the tile, [.][1]: head 2 q4 + 1; m in base-2 units
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
         m[nt][0] = m[nt][1] = -INFINITY;
         l[nt][0] = l[nt][1] = 0.0f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) ot[nt][i][0] = ot[nt][i][1] = ot[nt][i][2] = ot[nt][i][3] = 0.0f;
+        for (int i = 0; i < DT; ++i) ot[nt][i][0] = ot[nt][i][1] = ot[nt][i][2] = ot[nt][i][3] = 0.0f;
     }
     const float scale2 = a.scale * 1.4426950408889634f;
     // lane -> the row it addresses of the four 8 x 8 tiles of an ldmatrix.x4:
     //   K (A = keys x dims):   tiles (keys 0-7 | 8-15) x (dims +0 | +8) in the order a0 a1 a2 a3 = (k lo, d lo) (k hi, d lo) (k lo, d hi) (k hi, d hi)
     //   V (A = dims x keys, transposed on load): (d lo, k lo) (d hi, k lo) (d lo, k hi) (d hi, k hi)
     const int k_off = ((lane & 7) + ((lane >> 3) & 1) * 8) * ATT_KROW + (lane >> 4) * 16;
-    const int v_off = ATT_MT * ATT_KROW + ((lane & 7) + (lane >> 4) * 8) * ATT_VROW + ((lane >> 3) & 1) * 16;
+    const int v_off = ATT_MT * ATT_KROW + ((lane & 7) + (lane >> 4) * 8) * ATT_VROW + ((lane >> 3) & 1) * 16 + half * DT * 32;
     int cur = 0, nxt = NSLOT - 1;      // the slot in use; the slot the step NSLOT - 1 ahead goes to (its reads ended with the
-                                       // previous step's closing __syncwarp)
+                                       // previous step's closing ring_sync)
     for (; p < p1; p += STRIDE) {
         if (BULK) {
             attn_fill_slot_bulk(stage + nxt * ATT_SLOT, bars + 8 * nxt, kv, a.n_kv, kvh, kv0, p + (NSLOT - 1) * STRIDE, p1, lane);
@@ -371,15 +398,16 @@ __device__ __forceinline__ void attn_keys(const AttnArgs& a, const float* __rest
                 break;
             }
         } else if (Q8) {
-            attn_fill_raw(raw + nxt * ATT_RAW, kv, a.n_kv, kvh, kv0, p + STRIDE, p1, lane);
+            attn_fill_raw<8 / PW>(raw + nxt * ATT_RAW, kv, a.n_kv, kvh, kv0, p + STRIDE, p1, lane, half * (8 / PW));
             asm volatile("cp.async.wait_group 1;" ::: "memory");
-            __syncwarp();
-            attn_expand_raw(stage, raw + cur * ATT_RAW, lane);      // the BF16 slot's reads ended with the previous step's __syncwarp
+            ring_sync<PW>(ring_id);
+            // the BF16 slot's reads ended with the previous step's closing ring_sync
+            attn_expand_raw<8 / PW>(stage, raw + cur * ATT_RAW, lane, half * (8 / PW));
         } else {
-            attn_fill_slot(stage + nxt * ATT_SLOT, kv, a.n_kv, kvh, kv0, p + (NSLOT - 1) * STRIDE, p1, lane);
+            attn_fill_slot<8 / PW>(stage + nxt * ATT_SLOT, kv, a.n_kv, kvh, kv0, p + (NSLOT - 1) * STRIDE, p1, lane, half * (8 / PW));
             asm volatile("cp.async.wait_group %0;" ::"n"(NSLOT - 1) : "memory");
         }
-        __syncwarp();
+        ring_sync<PW>(ring_id);
         const unsigned char* slot = Q8 ? stage : stage + cur * ATT_SLOT;
         nxt = cur;
         cur = cur + 1 == NSLOT ? 0 : cur + 1;
@@ -416,7 +444,7 @@ __device__ __forceinline__ void attn_keys(const AttnArgs& a, const float* __rest
             l[nt][1] = fmaf(l[nt][1], corb, s[nt][1] + s[nt][3]);
             if (cora != 1.0f || corb != 1.0f) {      // the running maxima rarely move after a range's first steps
 #pragma unroll
-                for (int i = 0; i < 8; ++i) { ot[nt][i][0] *= cora; ot[nt][i][1] *= corb; ot[nt][i][2] *= cora; ot[nt][i][3] *= corb; }
+                for (int i = 0; i < DT; ++i) { ot[nt][i][0] *= cora; ot[nt][i][1] *= corb; ot[nt][i][2] *= cora; ot[nt][i][3] *= corb; }
             }
             // the weights as two bf16 terms, hi + lo (16 significant bits): one bf16 term alone moves an output by up to a third
             // of its own bf16 unit, which after the two roundings of the gate shows as two-unit differences
@@ -426,9 +454,9 @@ __device__ __forceinline__ void attn_keys(const AttnArgs& a, const float* __rest
             ph[nt][0] = movmatrix_trans(h01); ph[nt][1] = movmatrix_trans(h23);
             pl[nt][0] = movmatrix_trans(l01); pl[nt][1] = movmatrix_trans(l23);
         }
-        // values: 8 tiles of 16 dims
+        // values: this warp's tiles of 16 dims
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
+        for (int i = 0; i < DT; ++i) {
             uint32_t va[4];
             ldsm_x4_trans(va, slot + v_off + 32 * i);
 #pragma unroll
@@ -437,11 +465,11 @@ __device__ __forceinline__ void attn_keys(const AttnArgs& a, const float* __rest
                 mma_bf16(ot[nt][i], va, pl[nt][0], pl[nt][1]);
             }
         }
-        __syncwarp();      // this slot's reads are done before a later step refills it
+        ring_sync<PW>(ring_id);      // this slot's reads are done before a later step refills it
     }
     if (!BULK) asm volatile("cp.async.wait_group 0;" ::: "memory");      // only empty groups are left
-    // the warp's state into its own ring: [16 heads][130] = m (natural units; -inf stays -inf), l, acc
-    __syncwarp();
+    // the ring's state into the ring: [16 heads][130] = m (natural units; -inf stays -inf), l, acc (each warp its dims)
+    ring_sync<PW>(ring_id);
     float* mine = (float*) stage;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
@@ -451,32 +479,42 @@ __device__ __forceinline__ void attn_keys(const AttnArgs& a, const float* __rest
             l[nt][1] += __shfl_xor_sync(0xFFFFFFFFu, l[nt][1], off);
         }
         float* ha = mine + (8 * nt + 2 * q4) * 130, *hb = ha + 130;
-        if (r0 == 0) {
+        if (r0 == 0 && half == 0) {
             ha[0] = m[nt][0] * 0.69314718055994531f; ha[1] = l[nt][0];
             hb[0] = m[nt][1] * 0.69314718055994531f; hb[1] = l[nt][1];
         }
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int d = 2 + 16 * i + r0;
+        for (int i = 0; i < DT; ++i) {
+            const int d = 2 + 16 * (i + half * DT) + r0;
             ha[d] = ot[nt][i][0]; hb[d] = ot[nt][i][1]; ha[d + 8] = ot[nt][i][2]; hb[d + 8] = ot[nt][i][3];
         }
     }
     __syncthreads();
-    // merge the warps' states: thread d of the block handles dim d of every head
-    const int d = threadIdx.x;
-    for (int h = 0; h < group; ++h) {
+    // merge the rings' states.  A head's four weights exp(m_ring - max) are the same for all 128 dims: thread h computes
+    // them once (and the head's m and l), then a thread handles dim d of every PW-th head.
+    __shared__ float merge_c[ATT_MMA_WARPS][ATT_MAX_GROUP], merge_m[ATT_MAX_GROUP], merge_l[ATT_MAX_GROUP];
+    if (threadIdx.x < group) {
+        const int h = threadIdx.x;
         float mm = -INFINITY;
         for (int w = 0; w < ATT_MMA_WARPS; ++w) mm = fmaxf(mm, ((const float*) (att_smem + (size_t) w * STAGE))[h * 130]);
-        float ll = 0.0f, acc = 0.0f;
+        float ll = 0.0f;
         for (int w = 0; w < ATT_MMA_WARPS; ++w) {
             const float* st = (const float*) (att_smem + (size_t) w * STAGE) + h * 130;
-            if (st[0] == -INFINITY) continue;
-            const float c = expf(st[0] - mm);
+            const float c = st[0] == -INFINITY ? 0.0f : expf(st[0] - mm);      // a ring without keys: weight 0 (its l and acc are 0)
+            merge_c[w][h] = c;
             ll = fmaf(st[1], c, ll);
-            acc = fmaf(st[2 + d], c, acc);
         }
+        merge_m[h] = mm;
+        merge_l[h] = ll;
+    }
+    __syncthreads();
+    const int d = threadIdx.x & (ATT_HD - 1);
+    for (int h = threadIdx.x / ATT_HD; h < group; h += PW) {
+        float acc = 0.0f;
+#pragma unroll
+        for (int w = 0; w < ATT_MMA_WARPS; ++w) acc = fmaf(((const float*) (att_smem + (size_t) w * STAGE))[h * 130 + 2 + d], merge_c[w][h], acc);
         float* ph = pp + h * head_stride;
-        if (d == 0) { ph[0] = mm; ph[1] = ll; }
+        if (d == 0) { ph[0] = merge_m[h]; ph[1] = merge_l[h]; }
         ph[2 + d] = acc;
     }
     __syncthreads();
@@ -511,11 +549,12 @@ struct AttnPlan {
     int per;        // units per block
 };
 
-// u(t) = units of row t; pre[t] = u(0) + ... + u(t - 1), pre[T] = their sum.  Called by all threads of a 128-thread block.
+// u(t) = units of row t; pre[t] = u(0) + ... + u(t - 1), pre[T] = their sum.  Called by all threads of a block of NW warps.
+template <int NW>
 __device__ __forceinline__ AttnPlan attn_plan(const RowInfo* __restrict__ ri, int T, int n_kv, int n_splits, int n_blocks, int* pre) {
-    __shared__ int wsum[ATT_MMA_WARPS], wmax[ATT_MMA_WARPS];
+    __shared__ int wsum[NW], wmax[NW];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int each = (T + 32 * ATT_MMA_WARPS - 1) / (32 * ATT_MMA_WARPS);      // <= 8 rows a thread
+    const int each = (T + 32 * NW - 1) / (32 * NW);      // <= 8 rows a thread
     int sum = 0, mx = 0;
     for (int i = 0; i < each; ++i) {
         const int r = tid * each + i;
@@ -534,7 +573,7 @@ __device__ __forceinline__ AttnPlan attn_plan(const RowInfo* __restrict__ ri, in
     __syncthreads();
     int before = 0, rows_total = 0, max_u = 0;
 #pragma unroll
-    for (int w = 0; w < ATT_MMA_WARPS; ++w) {
+    for (int w = 0; w < NW; ++w) {
         if (w < warp) before += wsum[w];
         rows_total += wsum[w];
         max_u = max(max_u, wmax[w]);
@@ -556,14 +595,14 @@ __device__ __forceinline__ AttnPlan attn_plan(const RowInfo* __restrict__ ri, in
     return pl;
 }
 
-template <int NSLOT, int NT, int SRC>
-__global__ void __launch_bounds__(32 * ATT_MMA_WARPS) attn_flat_mma_kernel(AttnArgs a, const float* __restrict__ q, KvView kv,
-                                                                           const RowInfo* __restrict__ ri, float* __restrict__ part, int T) {
+template <int NSLOT, int NT, int SRC, int PW>
+__global__ void __launch_bounds__(32 * ATT_MMA_WARPS * PW, NT == 2 && SRC == ATT_SRC_Q8 ? 2 : 3)      // three blocks an SM: <= 168 / 85 registers
+attn_flat_mma_kernel(AttnArgs a, const float* __restrict__ q, KvView kv, const RowInfo* __restrict__ ri, float* __restrict__ part, int T) {
     extern __shared__ __align__(16) unsigned char att_smem[];
     __shared__ int pre[ATT_MAX_ROWS + 1];
     __shared__ __align__(8) unsigned long long att_bars[ATT_MMA_WARPS][4];      // a warp's slots' mbarriers (BULK)
     const int group = a.n_head / a.n_kv;
-    const unsigned bars = smem_u32(&att_bars[threadIdx.x >> 5][0]);
+    const unsigned bars = smem_u32(&att_bars[(threadIdx.x >> 5) / PW][0]);
     unsigned ring = 0;
     if (SRC == ATT_SRC_BULK) {
         if ((threadIdx.x & 31) < NSLOT) mbar_init(bars + 8 * (threadIdx.x & 31), 1);
@@ -572,7 +611,7 @@ __global__ void __launch_bounds__(32 * ATT_MMA_WARPS) attn_flat_mma_kernel(AttnA
     }
     grid_dependents_go();
     grid_dependency_wait();
-    const AttnPlan pl = attn_plan(ri, T, a.n_kv, a.n_splits, (int) gridDim.x, pre);
+    const AttnPlan pl = attn_plan<ATT_MMA_WARPS * PW>(ri, T, a.n_kv, a.n_splits, (int) gridDim.x, pre);
     int x = (int) blockIdx.x * pl.per;
     const int xe = min(pl.total, x + pl.per);
     while (x < xe) {
@@ -588,7 +627,7 @@ __global__ void __launch_bounds__(32 * ATT_MMA_WARPS) attn_flat_mma_kernel(AttnA
         const int end = min(xe, first + u);
         const int pos = max(ri[t].pos, 0), kv0 = ri[t].kv0;
         const int slot = (int) blockIdx.x - first / pl.per;
-        attn_keys<NSLOT, NT, SRC>(a, q, kv, t, kvh, kv0, (x - first) * ATT_MT, min(pos + 1, (end - first) * ATT_MT), att_smem,
+        attn_keys<NSLOT, NT, SRC, PW>(a, q, kv, t, kvh, kv0, (x - first) * ATT_MT, min(pos + 1, (end - first) * ATT_MT), att_smem,
                                   part + (((size_t) t * a.n_head + kvh * group) * a.n_splits + slot) * (ATT_HD + 2),
                                   (size_t) a.n_splits * (ATT_HD + 2), bars, ring);
         x = end;
@@ -609,23 +648,24 @@ __global__ void __launch_bounds__(ATT_HD) attn_reduce_kernel(AttnArgs a, const f
     grid_dependents_go();
     int n = a.n_splits;
     if (n_blocks > 0) {      // the plan reads the rows' positions only: before the wait for the partials
-        const AttnPlan pl = attn_plan(ri, T, a.n_kv, a.n_splits, n_blocks, pre);
+        const AttnPlan pl = attn_plan<ATT_HD / 32>(ri, T, a.n_kv, a.n_splits, n_blocks, pre);
         const int u = pre[t + 1] - pre[t], first = a.n_kv * pre[t] + (h / (a.n_head / a.n_kv)) * u;
         n = (first + u - 1) / pl.per - first / pl.per + 1;
     }
     grid_dependency_wait();
     const float* pp = part + ((size_t) t * a.n_head + h) * a.n_splits * (ATT_HD + 2);
-    __shared__ float pm[ATT_HD], pl[ATT_HD];      // the partials' (m, l): one load each, side by side
+    __shared__ float pm[ATT_HD], pl[ATT_HD], pc[ATT_HD];      // the partials' (m, l): one load each, side by side; their weights
     float m = -INFINITY, l = 0.0f, acc = 0.0f;
     if (n <= ATT_HD) {
         if (d < n) { pm[d] = pp[d * (ATT_HD + 2)]; pl[d] = pp[d * (ATT_HD + 2) + 1]; }
         __syncthreads();
         for (int s = 0; s < n; ++s) m = fmaxf(m, pm[s]);
+        if (d < n) pc[d] = pm[d] == -INFINITY ? 0.0f : expf(pm[d] - m);      // an unused partial carries m = -inf, l = 0, acc = 0
+        __syncthreads();
 #pragma unroll 4
-        for (int s = 0; s < n; ++s) {      // an unused partial carries m = -inf, l = 0, acc = 0
-            const float c = pm[s] == -INFINITY ? 0.0f : expf(pm[s] - m);
-            l = fmaf(pl[s], c, l);
-            acc = fmaf(pp[s * (ATT_HD + 2) + 2 + d], c, acc);
+        for (int s = 0; s < n; ++s) {
+            l = fmaf(pl[s], pc[s], l);
+            acc = fmaf(pp[s * (ATT_HD + 2) + 2 + d], pc[s], acc);
         }
     } else {
         for (int s = 0; s < n; ++s) m = fmaxf(m, pp[s * (ATT_HD + 2)]);
@@ -646,10 +686,11 @@ __global__ void __launch_bounds__(ATT_HD) attn_reduce_kernel(AttnArgs a, const f
 
 using namespace nsl;
 
-static int g_attn_variant = 1;   // 1 (default): tensor cores, balanced over the blocks; 2: tensor cores, one block per split;
-                                 // 3: as 1 with three-slot rings (two blocks an SM); 4: as 1 with two blocks an SM;
-                                 // 5 / 6: as 1 / 3 with the K and V rows brought by the copy engine (cp.async.bulk);
-                                 // 0: the scalar pass (one warp per query head)
+static int g_attn_variant = 1;   // the first pass.  Tensor cores, the step's keys dealt evenly to the blocks: 1 (default): one
+                                 // warp a ring; 7: two warps a ring (groups of <= 8; larger groups run form 1); 3: as 1 with
+                                 // three-slot rings (two blocks an SM); 4: as 1 with two blocks an SM; 5 / 6: as 1 / 3 with
+                                 // the K and V rows brought by the copy engine (cp.async.bulk).  2: tensor cores, one block
+                                 // per caller split.  0: the scalar pass (one warp per query head)
 
 template <typename K>
 static void attn_smem_attr(K kernel, int bytes, bool* done) {
@@ -669,12 +710,12 @@ static int attn_sm_count() {
     return n[dev & 15] > 0 ? n[dev & 15] : 148;
 }
 
-template <int NSLOT, int NT, int SRC>
+template <int NSLOT, int NT, int SRC, int PW = 1>
 static void launch_attn_flat(cudaStream_t s, int n_blocks, const AttnArgs& a, const float* q, const KvView& kv, const RowInfo* ri, float* part, int T) {
     static bool done[16];
     constexpr int SMEM = ATT_MMA_WARPS * NSLOT * ATT_SLOT;
-    attn_smem_attr(attn_flat_mma_kernel<NSLOT, NT, SRC>, SMEM, done);
-    launch(attn_flat_mma_kernel<NSLOT, NT, SRC>, dim3((unsigned) n_blocks), 32 * ATT_MMA_WARPS, (size_t) SMEM, s, a, q, kv, ri, part, T);
+    attn_smem_attr(attn_flat_mma_kernel<NSLOT, NT, SRC, PW>, SMEM, done);
+    launch(attn_flat_mma_kernel<NSLOT, NT, SRC, PW>, dim3((unsigned) n_blocks), 32 * ATT_MMA_WARPS * PW, (size_t) SMEM, s, a, q, kv, ri, part, T);
 }
 
 template <int NSLOT, int SRC>
@@ -696,7 +737,7 @@ static void launch_attn_split(cudaStream_t s, const AttnArgs& a, const float* q,
 extern "C" {
 
 // Picks the form of kc_attn's first pass (see g_attn_variant).  All forms meet the same bound; for tests and timing.
-void nsl_attn_set_variant(int v) { g_attn_variant = v >= 0 && v <= 6 ? v : 1; }
+void nsl_attn_set_variant(int v) { g_attn_variant = v >= 0 && v <= 7 ? v : 1; }
 
 // 0, or 1 once a bounded wait for a step's K / V rows ran out in the copy-engine forms (the outputs of that call are
 // invalid).  Synchronises the device.
@@ -721,15 +762,17 @@ void kc_attn(cudaStream_t s, AttnArgs a, const float* q, KvView kv, const RowInf
                   a.n_head, a.n_kv, (int) ATT_MAX_GROUP, a.n_splits, a.chunk);
         return;
     }
-    const int variant = q8 && (g_attn_variant == 0 || g_attn_variant == 3 || g_attn_variant >= 5) ? 1 : g_attn_variant;      // Q8: forms 1, 2, 4
+    const int variant = q8 && (g_attn_variant == 0 || g_attn_variant == 3 || g_attn_variant == 5 || g_attn_variant == 6) ? 1 : g_attn_variant;      // Q8: forms 1, 2, 4, 7
     const bool flat = (variant == 1 || variant >= 3) && a.n_splits >= 3 && a.chunk > 0 && T <= ATT_MAX_ROWS;
     int n_blocks = 0;
     if (flat) {
-        const bool three = variant == 3 || variant == 6, bulk = variant >= 5;
+        const bool three = variant == 3 || variant == 6, bulk = variant == 5 || variant == 6;
         // three blocks with two-slot rings (70 KB of shared memory) fit an SM, two with three-slot rings
         n_blocks = (three || variant == 4 ? 2 : 3) * attn_sm_count();
-        if (q8) launch_attn_flat_group<2, ATT_SRC_Q8>(s, n_blocks, group, a, q, kv, ri, part, T);
-        else if (!three && !bulk) launch_attn_flat_group<2, ATT_SRC_ASYNC>(s, n_blocks, group, a, q, kv, ri, part, T);
+        if (variant == 7 && group <= 8 && q8) launch_attn_flat<2, 1, ATT_SRC_Q8, 2>(s, n_blocks, a, q, kv, ri, part, T);
+        else if (variant == 7 && group <= 8) launch_attn_flat<2, 1, ATT_SRC_ASYNC, 2>(s, n_blocks, a, q, kv, ri, part, T);
+        else if (q8) launch_attn_flat_group<2, ATT_SRC_Q8>(s, n_blocks, group, a, q, kv, ri, part, T);
+        else if (!three && !bulk || variant == 7) launch_attn_flat_group<2, ATT_SRC_ASYNC>(s, n_blocks, group, a, q, kv, ri, part, T);
         else if (!three) launch_attn_flat_group<2, ATT_SRC_BULK>(s, n_blocks, group, a, q, kv, ri, part, T);
         else if (!bulk) launch_attn_flat_group<3, ATT_SRC_ASYNC>(s, n_blocks, group, a, q, kv, ri, part, T);
         else launch_attn_flat_group<3, ATT_SRC_BULK>(s, n_blocks, group, a, q, kv, ri, part, T);

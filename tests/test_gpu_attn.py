@@ -13,10 +13,10 @@ pytestmark = pytest.mark.gpu
 
 
 def run_case(nh, nkv, NP, pos, kv0, ns, chunk, gate=True, nv=None, seed=21):
-    for variant in (1, 2, 3, 4, 5, 6, 0):      # tensor cores (balanced blocks; a block per split; three-slot rings; two blocks an
-                                               # SM; rows by the copy engine with two and three slots), the scalar pass
+    for variant in (1, 2, 3, 4, 5, 6, 7, 0):   # tensor cores (balanced blocks; a block per split; three-slot rings; two blocks an
+                                               # SM; rows by the copy engine with two and three slots; two warps a ring), the scalar pass
         run_variant(variant, nh, nkv, NP, pos, kv0, ns, chunk, gate, nv, seed)
-    for variant in (1, 2, 4):                  # the 8-bit cache: balanced blocks, a block per split, two blocks an SM
+    for variant in (1, 2, 4, 7):               # the 8-bit cache: balanced blocks, a block per split, two blocks an SM, two warps a ring
         run_variant(variant, nh, nkv, NP, pos, kv0, ns, chunk, gate, nv, seed, q8=True)
 
 
@@ -38,7 +38,7 @@ def run_variant(variant, nh, nkv, NP, pos, kv0, ns, chunk, gate, nv, seed, q8=Fa
     else:
         o = kernels.kt_attn(a, q, Kc, Vc, pos, kv0, g if gate else None, nv)
     ref, _ = B.attn_decode(q, Kc, Vc, pos, kv0, nkv, scale, g if gate else None)
-    L.load().nsl_attn_set_variant(1)
+    L.load().nsl_attn_set_variant(1)      # back to the default
     assert L.load().nsl_attn_status() == 0      # no wait for K / V rows ran out
     # the reference's bound; an output whose attention value sits on a bf16 rounding boundary can land one unit further
     # after the gate's second rounding: at most one element in a thousand, and never beyond twice the bound
@@ -63,7 +63,7 @@ def test_ragged_rows_as_the_reference_host_splits_them():
     rng = np.random.default_rng(3)
     pos = [2999, 0, 15, 16, 1500, 127, 128, 2047, 700, 31, 2998, 5]
     run_case(8, 2, 12 * 3008, pos, [3008 * i for i in range(12)], 32, 128, seed=9)
-    for variant in (1, 3, 5, 6):
+    for variant in (1, 3, 5, 6, 7):
         run_variant(variant, 16, 1, 6000, [5999], [0], 32, 188, True, None, 4)      # one row, one KV head: its units over 30 blocks
 
 
