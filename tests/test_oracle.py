@@ -201,3 +201,52 @@ def test_p3_decode_matches_reference_fixture(oracle):
     m = oracle.Matrix3(rows, K, 0, eb=eb)
     m.seeds, m.nibs = g["row_seeds"], g["row_nibs"]
     assert np.array_equal(oracle.decode3_rows_f32(m).view(np.uint32), g["row_f32"].view(np.uint32))
+
+
+def test_kv_q8_cache_follows_the_reference_tests_quantizer(oracle):
+    """tests/test_mova_kernels.c:584-604: per (row, head) scale = max|x| / 127 (1 for a zero row), code = lrintf(x / scale),
+    and the values a kernel reads from the cache are bf16(code * scale)."""
+    rng = np.random.default_rng(8)
+    bits = oracle.f2bf((rng.random((40, 2, 128), np.float32) * 2 - 1) * 2)
+    bits[5, 1] = 0                                                      # a zero row: scale 1, codes 0
+    x = (bits.astype(np.uint32) << 16).view(np.float32)
+    codes, sc, deq = oracle.kv_q8_cache(bits)
+    assert codes.dtype == np.int8 and sc.dtype == np.float32 and deq.dtype == np.uint16 and deq.shape == bits.shape
+    assert sc[5, 1] == 1 and not codes[5, 1].any() and not deq[5, 1].any()
+    m = np.abs(x).max(-1)
+    live = m > 0
+    assert np.array_equal(sc[live], (m[live] / np.float32(127)).astype(np.float32))
+    assert np.abs(codes.astype(np.int32)).max() == 127                   # every live row reaches +-127 at its largest value
+    for r, h in [(0, 0), (7, 1), (39, 0)]:                               # scalar restatement of the C loop
+        for e in range(128):
+            q = int(np.rint(np.float32(x[r, h, e]) / sc[r, h]))
+            assert q == codes[r, h, e]
+            assert oracle.f2bf(np.float32(np.float32(q) * sc[r, h]))[()] == deq[r, h, e]
+    back = (deq.astype(np.uint32) << 16).view(np.float32)
+    assert np.all(np.abs(back - x) <= sc[..., None] / 2 + np.abs(x) / 256 + 1e-30)   # half a step + the BF16 rounding
+
+
+def test_attn_decode_reference_form(oracle):
+    """The double-precision statement the attention kernels are compared with (tests/test_mova_kernels.c:690-712): one head
+    against an explicit loop, the GQA head -> KV head map, and the gate's two roundings."""
+    rng = np.random.default_rng(2)
+    nh, nkv, NP = 4, 2, 50
+    q = oracle.bfr(rng.standard_normal((2, nh, 128)).astype(np.float32))
+    g = oracle.bfr(rng.standard_normal((2, nh, 128)).astype(np.float32))
+    Kc = oracle.f2bf(rng.standard_normal((NP, nkv, 128)).astype(np.float32))
+    Vc = oracle.f2bf(rng.standard_normal((NP, nkv, 128)).astype(np.float32))
+    K = (Kc.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+    V = (Vc.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+    pos, kv0, scale = [20, 0], [3, 40], np.float32(1 / np.sqrt(128.0))
+    out, att = oracle.attn_decode(q, Kc, Vc, pos, kv0, nkv, scale, g)
+    t, h = 0, 3
+    kvh = h // (nh // nkv)
+    s = np.array([np.dot(q[t, h].astype(np.float64) * np.float64(scale), K[kv0[t] + p, kvh]) for p in range(pos[t] + 1)])
+    w = np.exp(s - s.max())
+    ref = sum(w[p] / w.sum() * V[kv0[t] + p, kvh] for p in range(pos[t] + 1))
+    assert np.allclose(att[t, h], ref, rtol=1e-12, atol=1e-14)
+    assert np.array_equal(att[1, 0], V[40, 0])                            # a row at position 0 returns its only value row
+    want = oracle.bfr(oracle.bfr(att.astype(np.float32)) * oracle.softplus_gate(g))
+    assert np.array_equal(out.view(np.uint32), want.view(np.uint32))
+    plain, _ = oracle.attn_decode(q, Kc, Vc, pos, kv0, nkv, scale, None)
+    assert np.array_equal(plain.view(np.uint32), oracle.bfr(att.astype(np.float32)).view(np.uint32))
