@@ -29,12 +29,12 @@ void nsl_ep_plan(cudaStream_t s, const int32_t* ind, const float* wt, int n_rank
                  int32_t* count);
 /* Gather mat-vecs over a compacted pair list whose length is on the device (see nsl_ep_plan): pair p uses slice
  * sel[p]; the gate+up form reads input row xrow[p] of x (packed bf16 rows of stride xs elements when x_bf16, else f32),
- * the second form reads row p.  max_pairs bounds the list, *count is its length, expected_pairs sizes the work items. */
+ * the second form reads row p.  max_pairs bounds the list, *count is its length, raw = 1 stores unrounded f32 (no bf16 rounding points). */
 void nsl_mv_gu_rows(cudaStream_t s, const WSlice* wg, const WSlice* wu, int K, int R, const void* x, int xs, int x_bf16,
                     float* a, int ys, const int32_t* sel, const int32_t* xrow, int max_pairs, const int32_t* count,
-                    int expected_pairs, const uint32_t* G);
+                    int raw, const uint32_t* G);
 void nsl_mv_sel_rows(cudaStream_t s, const WSlice* ws, int K, int R, const float* x, int xs, float* y, int ys,
-                     const int32_t* sel, int max_pairs, const int32_t* count, int expected_pairs, const uint32_t* G);
+                     const int32_t* sel, int max_pairs, const int32_t* count, int raw, const uint32_t* G);
 /* partial[g][:] = sum over pairs p in [tok_off[g], tok_off[g+1]) of wsel[p] * D[p][:], pairs ascending (zeros when the
  * token has no expert here).  T tokens of width d. */
 void nsl_ep_combine(cudaStream_t s, const float* D, const float* wsel, const int32_t* tok_off, int T, int d, float* partial);
@@ -71,9 +71,10 @@ int nsl_ep_window_free(void* ptr);
 void nsl_ep_p2p_dispatch(cudaStream_t s, NslEpWindow w, const void* chunk);
 /* Router, bf16 packing and dispatch in one kernel: logits [t_loc][ld] and x [t_loc][d] (f32, local) -> each token's row,
  * ids and weights in slot `me` of every window (ind_off / wt_off = byte offsets of ids and weights inside a chunk,
- * rows first).  n_exp <= 1024, top_k <= 32, d a multiple of 8. */
+ * rows first).  n_exp <= 1024, top_k <= 32, d a multiple of 8.  ind_out / wt_out (device, [t_loc][top_k], optional): the
+ * caller's own copy of its tokens' routing. */
 void nsl_ep_p2p_route_dispatch(cudaStream_t s, NslEpWindow w, int n_exp, int top_k, const float* logits, int ld, const float* x,
-                               int d, uint64_t ind_off, uint64_t wt_off);
+                               int d, uint64_t ind_off, uint64_t wt_off, int32_t* ind_out, float* wt_out);
 /* Returns (on the stream) when every rank's rows of this step have landed in the local window. */
 void nsl_ep_p2p_wait_dispatch(cudaStream_t s, NslEpWindow w);
 /* nsl_ep_plan on the window's receive area with the wait inside the kernel (replaces nsl_ep_p2p_wait_dispatch +

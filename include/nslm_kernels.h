@@ -225,10 +225,6 @@ void nsl_decode_bf16(cudaStream_t s, WSlice w, int K, int R, uint16_t* out, cons
  * waiting for a free stage, 2 the epilogue waiting for the accumulator, 3 the MMA issuer waiting for a full stage); a
  * block that gives up frees its tensor memory and returns without storing.  Call after synchronising the stream. */
 int nsl_mm_status(void);
-/* Which single-token mat-vec kernel serves kc_mv (T = 1), kc_mv_sel and kc_mv_gu when K = 64 * 2^j <= 2048:
- * 1 (default) inputs staged in shared memory, two blocks of 8 warps per SM; 0 inputs held in registers, one block per
- * SM.  Same arithmetic and order: the results are bit-identical.  Process-wide, like kc_seed_gemm_f32. */
-void nsl_mv_set_variant(int v);
 /* Fills a 65536-entry host array with the stream table the G arguments expect (lfsr_stream32 of every seed,
  * nslm/lfsr.h:53-59). */
 void nsl_stream_table(uint32_t* host_table);
@@ -241,24 +237,17 @@ int nsl_sm_count(void);
 /* nsl_decode_f32 / nsl_decode_bf16 for a P = 3 (MF_SEED4) slice. */
 void nsl_decode3_f32(cudaStream_t s, WSlice w, int K, int R, float* out, const uint32_t* G);
 void nsl_decode3_bf16(cudaStream_t s, WSlice w, int K, int R, uint16_t* out, const uint32_t* G);
-/* Work units: the pairs of a gather mat-vec grouped two by two per slice, so that two pairs that use the same expert
- * share one expansion of its weights (results per pair are bit-identical to the ungrouped calls; only the logic-pipe
- * work is shared).  nsl_mv_units builds the list on the device: sel[p] < n_slices for p < max_pairs (or < *count when
- * count is given, device memory); units holds 4 ints per unit (max_pairs units at most), *n_units their number.
- * max_pairs <= 4096, n_slices <= 1024.  nsl_mv_gu_units / nsl_mv_sel_units are kc_mv_gu / kc_mv_sel over such a list
- * (K = 64 * 2^j <= 2048): xrow (optional) = input row per pair, else pair / xdiv; x_bf16: inputs are packed bf16 rows;
- * raw: unrounded f32 outputs. */
-void nsl_mv_units(cudaStream_t s, const int32_t* sel, int max_pairs, const int32_t* count, int n_slices, int32_t* units,
-                  int32_t* n_units);
-void nsl_mv_gu_units(cudaStream_t s, const WSlice* wg, const WSlice* wu, int K, int R, const void* x, int xs, int x_bf16, float* out,
-                     int ys, const int32_t* sel, const int32_t* xrow, int xdiv, const int32_t* units, const int32_t* n_units,
-                     int max_pairs, int raw, const uint32_t* G);
-void nsl_mv_sel_units(cudaStream_t s, const WSlice* ws, int K, int R, const float* x, int xs, float* y, int ys, const int32_t* sel,
-                      const int32_t* units, const int32_t* n_units, int max_pairs, int raw, const uint32_t* G);
+/* kc_mv_gu with the router folded into its prologue (one launch less on the decode path): T <= MV_MAXT rows of logits
+ * [T][ld] -> ind / wt [T][top_k] as kq4_route gives them, and a [T * top_k][R] as kc_mv_gu gives it for sel = ind,
+ * xdiv = top_k.  K = 64 * 2^j <= 2048; raw: unrounded f32 outputs.  n_exp <= 1024, top_k <= 32. */
+void nsl_mv_gu_routed(cudaStream_t s, const WSlice* wg, const WSlice* wu, int K, int R, const float* x, int xs, float* a, int ys,
+                      int n_exp, int top_k, const float* logits, int ld, int T, int32_t* ind, float* wt, int raw,
+                      const uint32_t* G);
 /* Programmatic dependent launch for the calling thread's next launches of the mat-vec kernels (kc_mv*, nsl_mv*),
  * kq4_moe_combine and nsl_ep_combine: while on, such a kernel may become resident before the previous kernel in its
  * stream has finished and waits on the device for its completion before it touches memory a neighbour writes.  Turn it
- * on only between kernels of this library (the previous kernel in the stream must be one of them), and off again. */
+ * A kernel launched this way reads and writes nothing a neighbour touches before that wait, so it is safe after any
+ * kernel; after a copy or another kind of node it is an ordinary launch. */
 void nsl_dependent_launch(int on);
 
 #ifdef __cplusplus

@@ -646,13 +646,13 @@ __global__ void __launch_bounds__(ATT_HD) attn_reduce_kernel(AttnArgs a, const f
     __shared__ int pre[ATT_MAX_ROWS + 1];
     const int h = blockIdx.x, t = blockIdx.y, d = threadIdx.x;
     grid_dependents_go();
+    grid_dependency_wait();      // the rows' positions may come from the kernel before kc_attn: nothing is read earlier
     int n = a.n_splits;
-    if (n_blocks > 0) {      // the plan reads the rows' positions only: before the wait for the partials
+    if (n_blocks > 0) {
         const AttnPlan pl = attn_plan<ATT_HD / 32>(ri, T, a.n_kv, a.n_splits, n_blocks, pre);
         const int u = pre[t + 1] - pre[t], first = a.n_kv * pre[t] + (h / (a.n_head / a.n_kv)) * u;
         n = (first + u - 1) / pl.per - first / pl.per + 1;
     }
-    grid_dependency_wait();
     const float* pp = part + ((size_t) t * a.n_head + h) * a.n_splits * (ATT_HD + 2);
     __shared__ float pm[ATT_HD], pl[ATT_HD], pc[ATT_HD];      // the partials' (m, l): one load each, side by side; their weights
     float m = -INFINITY, l = 0.0f, acc = 0.0f;
@@ -743,7 +743,9 @@ void nsl_attn_set_variant(int v) { g_attn_variant = v >= 0 && v <= 7 ? v : 1; }
 // invalid).  Synchronises the device.
 int nsl_attn_status(void) {
     int v = 0;
+    const int zero = 0;
     if (cudaMemcpyFromSymbol(&v, g_attn_wait_failed, sizeof v) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(g_attn_wait_failed, &zero, sizeof zero);      // reading clears it, as the other status calls do
     return v;
 }
 

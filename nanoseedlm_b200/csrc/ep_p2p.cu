@@ -48,7 +48,8 @@ __global__ void __launch_bounds__(1024) ep_dispatch_kernel(NslEpWindow w, const 
 template <int PER>
 __global__ void __launch_bounds__(256) ep_route_dispatch_kernel(NslEpWindow w, const float* __restrict__ logits, int ld,
                                                                const float* __restrict__ x, int E, int k, int d,
-                                                               uint64_t ind_off, uint64_t wt_off) {
+                                                               uint64_t ind_off, uint64_t wt_off, int32_t* __restrict__ ind_out,
+                                                               float* __restrict__ wt_out) {
     __shared__ int32_t s_ind[32];
     __shared__ float s_wt[32];
     grid_dependents_go();
@@ -73,6 +74,10 @@ __global__ void __launch_bounds__(256) ep_route_dispatch_kernel(NslEpWindow w, c
         char* slot = recv_slot(w, r);
         ((int32_t*) (slot + ind_off))[t * k + j] = s_ind[j];
         ((float*) (slot + wt_off))[t * k + j] = s_wt[j];
+    }
+    if (ind_out && (int) threadIdx.x < k) {      // the caller's own copy of its tokens' routing
+        ind_out[t * k + threadIdx.x] = s_ind[threadIdx.x];
+        wt_out[t * k + threadIdx.x] = s_wt[threadIdx.x];
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -193,7 +198,7 @@ void nsl_ep_p2p_dispatch(cudaStream_t s, NslEpWindow w, const void* chunk) {
 }
 
 void nsl_ep_p2p_route_dispatch(cudaStream_t s, NslEpWindow w, int n_exp, int top_k, const float* logits, int ld, const float* x,
-                               int d, uint64_t ind_off, uint64_t wt_off) {
+                               int d, uint64_t ind_off, uint64_t wt_off, int32_t* ind_out, float* wt_out) {
     if (!window_ok(w, "nsl_ep_p2p_route_dispatch")) return;
     const uint64_t meta = (uint64_t) w.t_loc * top_k * 4;
     if (n_exp < 1 || n_exp > 1024 || top_k < 1 || top_k > 32 || top_k > n_exp || d < 8 || d % 8 || !aligned16(x) ||
@@ -204,9 +209,9 @@ void nsl_ep_p2p_route_dispatch(cudaStream_t s, NslEpWindow w, int n_exp, int top
         return;
     }
     const unsigned grid = (unsigned) w.t_loc;
-    if (n_exp <= 128) ep_route_dispatch_kernel<4><<<grid, 256, 0, s>>>(w, logits, ld, x, n_exp, top_k, d, ind_off, wt_off);
-    else if (n_exp <= 512) ep_route_dispatch_kernel<16><<<grid, 256, 0, s>>>(w, logits, ld, x, n_exp, top_k, d, ind_off, wt_off);
-    else ep_route_dispatch_kernel<32><<<grid, 256, 0, s>>>(w, logits, ld, x, n_exp, top_k, d, ind_off, wt_off);
+    if (n_exp <= 128) ep_route_dispatch_kernel<4><<<grid, 256, 0, s>>>(w, logits, ld, x, n_exp, top_k, d, ind_off, wt_off, ind_out, wt_out);
+    else if (n_exp <= 512) ep_route_dispatch_kernel<16><<<grid, 256, 0, s>>>(w, logits, ld, x, n_exp, top_k, d, ind_off, wt_off, ind_out, wt_out);
+    else ep_route_dispatch_kernel<32><<<grid, 256, 0, s>>>(w, logits, ld, x, n_exp, top_k, d, ind_off, wt_off, ind_out, wt_out);
     count_launch();
 }
 

@@ -32,6 +32,8 @@ static void* dalloc(size_t n) {
     return p;
 }
 
+void nsl_moe_destroy(NslMoe* m);
+
 NslMoe* nsl_moe_create(int d, int ff, int n_exp, int top_k, int max_tokens, const WSlice* wg, const WSlice* wu,
                        const WSlice* wd, const uint32_t* G) {
     if (d % 8 || ff % 8 || n_exp < 1 || n_exp > BUCKET_MAX_EXPERTS || top_k < 1 || top_k > 32 || max_tokens < 1) {
@@ -63,8 +65,9 @@ NslMoe* nsl_moe_create(int d, int ff, int n_exp, int top_k, int max_tokens, cons
     cudaHostAlloc((void**) &m->hind, P * 4, cudaHostAllocDefault);
     cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking);
     if (!m->x || !m->logits || !m->wt || !m->ind || !m->A || !m->Dx || !m->out || !m->perm || !m->tiles || !m->ntiles ||
-        !m->hx || !m->hlogits || !m->hout || !m->hind || (big && (!m->Gb || !m->Ub))) {
+        !m->hx || !m->hlogits || !m->hout || !m->hind || !m->stream || (big && (!m->Gb || !m->Ub))) {
         nsl::set_error("nsl_moe_create: out of memory");
+        nsl_moe_destroy(m);      // frees whatever was obtained
         return NULL;
     }
     return m;
@@ -81,7 +84,7 @@ void nsl_moe_destroy(NslMoe* m) {
     for (void* p : dv) if (p) cudaFree(p);
     void* hv[] = {m->hx, m->hlogits, m->hout, m->hind};
     for (void* p : hv) if (p) cudaFreeHost(p);
-    cudaStreamDestroy(m->stream);
+    if (m->stream) cudaStreamDestroy(m->stream);
     free(m);
 }
 
@@ -90,9 +93,9 @@ void nsl_moe_destroy(NslMoe* m) {
 int nsl_moe_forward_dev(NslMoe* m, cudaStream_t s, const float* x, const float* logits, int T, float* out) {
     if (T < 1 || T > m->max_tokens) { nsl::set_error("nsl_moe_forward: %d rows, at most %d", T, m->max_tokens); return -1; }
     const int k = m->top_k, P = T * k, d = m->d, ff = m->ff;
-    nsl_route(s, m->n_exp, k, logits, m->n_exp, m->ind, m->wt, T);
     if (T >= m->grouped_min_tokens) {
         const int mt = P / MMT_BN + m->n_exp;
+        nsl_route(s, m->n_exp, k, logits, m->n_exp, m->ind, m->wt, T);
         kc_bucket(s, m->ind, P, m->n_exp, m->perm, m->tiles, m->ntiles);
         kc_mm_grouped_dev(s, MF_SEED4P4, m->wg, d, ff, x, d, m->Gb, ff, k, m->perm, m->tiles, m->ntiles, mt, m->G);
         kc_mm_grouped_dev(s, MF_SEED4P4, m->wu, d, ff, x, d, m->Ub, ff, k, m->perm, m->tiles, m->ntiles, mt, m->G);
@@ -101,16 +104,19 @@ int nsl_moe_forward_dev(NslMoe* m, cudaStream_t s, const float* x, const float* 
         kq4_moe_combine(s, d, k, m->Dx, m->wt, NULL, NULL, 0, out, T);
         return 0;
     }
-    // decode rows: the three kernels after the router are dependent launches (their blocks come in while the previous
-    // kernel drains and wait for its completion before touching its results)
+    // decode rows: three launches -- router + gate + up + SwiGLU (the router runs in that kernel's prologue), down, combine --
+    // as dependent launches (a kernel's blocks come in while the previous kernel drains and wait for its completion
+    // before touching anything a neighbour writes)
     nsl::PdlScope pdl(m->pdl);
-    if (m->raw) {
-        nsl_mv_gu_raw(s, m->wg, m->wu, d, ff, x, d, m->A, ff, m->ind, P, k, m->G);
-        nsl_mv_raw(s, m->wd, ff, d, m->A, ff, m->Dx, d, m->ind, P, 1, m->G);
-    } else {
-        kc_mv_gu(s, MF_SEED4P4, m->wg, m->wu, d, ff, x, d, m->A, ff, m->ind, P, k, m->G);
-        kc_mv_sel(s, MF_SEED4P4, m->wd, ff, d, m->A, ff, m->Dx, d, m->ind, P, 1, m->G);
+    const bool fused = T <= MV_MAXT && d % 64 == 0 && d <= 2048 && (d & (d - 1)) == 0;
+    if (fused) nsl_mv_gu_routed(s, m->wg, m->wu, d, ff, x, d, m->A, ff, m->n_exp, k, logits, m->n_exp, T, m->ind, m->wt, m->raw, m->G);
+    else {
+        nsl_route(s, m->n_exp, k, logits, m->n_exp, m->ind, m->wt, T);
+        if (m->raw) nsl_mv_gu_raw(s, m->wg, m->wu, d, ff, x, d, m->A, ff, m->ind, P, k, m->G);
+        else kc_mv_gu(s, MF_SEED4P4, m->wg, m->wu, d, ff, x, d, m->A, ff, m->ind, P, k, m->G);
     }
+    if (m->raw) nsl_mv_raw(s, m->wd, ff, d, m->A, ff, m->Dx, d, m->ind, P, 1, m->G);
+    else kc_mv_sel(s, MF_SEED4P4, m->wd, ff, d, m->A, ff, m->Dx, d, m->ind, P, 1, m->G);
     kq4_moe_combine(s, d, k, m->Dx, m->wt, NULL, NULL, 0, out, T);
     return 0;
 }

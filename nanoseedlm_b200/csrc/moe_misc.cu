@@ -141,106 +141,169 @@ __global__ void __launch_bounds__(1024) bucket_place_kernel(const int32_t* __res
 }
 
 // ---- expert cache -----------------------------------------------------------------------------------------------------
-// Admit (one block): mark the units this call needs; hits get the new tick; misses, in expert order, each take the least
-// recently used slot (ties: lowest slot) that this call has not touched and, with CACHE_PROTECT_PREV, that the previous
-// admit did not touch; the unit's slice tables are pointed at the slot and a (unit, slot) copy job is queued.  When no
-// slot may be replaced the remaining misses are left out (njobs = admitted count).
-__global__ void __launch_bounds__(CACHE_MAX_PER_LAYER) cache_admit_kernel(CachePool p, int sl, const int32_t* __restrict__ inds,
-                                                                         int count, int flags) {
-    __shared__ int need[CACHE_MAX_PER_LAYER];
-    __shared__ int misses[CACHE_MAX_PER_LAYER];
-    __shared__ int wmiss[32], wneed[32];
-    __shared__ unsigned long long best;
-    __shared__ int nmiss;
-    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+// Policy (engine/kernels_cuda.h:26-55): the units a call needs are marked; hits get the new tick; misses, in expert order,
+// take the least recently used slots (ties: lowest slot) among those this call has not touched and, with
+// CACHE_PROTECT_PREV, the previous admit did not touch; a taken slot's old unit is evicted, the unit's slice tables are
+// pointed at the slot and a (unit, slot) copy job is queued.  When fewer slots may be replaced than there are misses,
+// the remaining misses are left out (njobs = admitted count).
+//
+// How it is computed here (one block, no serial loop over the misses).  Taking the LRU slot m times in a row is the
+// same as taking the m smallest (last use, slot) keys among the replaceable slots, in order.  So: (1) an MSB-first
+// radix select over the 32-bit last-use ticks finds the tick of the m-th victim and how many slots lie below it;
+// (2) one ordered pass in slot order collects the victims: every replaceable slot below that tick, and of those equal to
+// it the lowest slots that are still needed; (3) the victims (at most 1024, in shared memory) are ranked by counting;
+// (4) thread r pairs the r-th miss with the victim of rank r and rewrites the tables for it -- all misses at once.
+constexpr int ADMIT_T = CACHE_MAX_PER_LAYER;   // threads of the block = the most units one layer has
+
+__device__ __forceinline__ bool slot_replaceable(uint32_t last, uint32_t now, uint32_t prev) { return last != now && last != prev; }
+
+// Exclusive position of this thread's flag among the block's flags (thread order) and their total; `carry` is shared.
+__device__ __forceinline__ int block_rank(bool flag, int* wsum, int& total) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const uint32_t m = __ballot_sync(FULL, flag);
+    __syncthreads();            // wsum may still be read from the previous call
+    if (lane == 0) wsum[w] = __popc(m);
+    __syncthreads();
+    int before = 0, all = 0;
+    for (int q = 0; q < ADMIT_T / 32; ++q) { const int c = wsum[q]; if (q < w) before += c; all += c; }
+    total = all;
+    return before + __popc(m & ((1u << lane) - 1u));
+}
+
+__global__ void __launch_bounds__(ADMIT_T) cache_admit_kernel(CachePool p, int sl, const int32_t* __restrict__ inds,
+                                                              int count, int flags) {
+    __shared__ int need[ADMIT_T];                    // expert -> needed by this call
+    __shared__ int miss_of[ADMIT_T];                 // r -> the r-th missing expert (ascending)
+    __shared__ unsigned long long vict[ADMIT_T];     // victims' (last use, slot) keys, in slot order
+    __shared__ int hist[256];
+    __shared__ int wsum[ADMIT_T / 32];
+    __shared__ uint32_t sel_prefix;
+    __shared__ int sel_remaining;
+    const int tid = threadIdx.x;
     const uint32_t prev = (flags & CACHE_PROTECT_PREV) ? p.tick[0] : 0xFFFFFFFFu;
     const uint32_t now = p.tick[0] + 1;
     need[tid] = 0;
     __syncthreads();
-    for (int i = tid; i < count; i += CACHE_MAX_PER_LAYER) {
+    for (int i = tid; i < count; i += ADMIT_T) {
         const int e = inds[i];
         if (e >= 0 && e < p.per_layer) need[e] = 1;
     }
     __syncthreads();
-    const bool is_need = tid < p.per_layer && need[tid];
-    const int slot0 = is_need ? p.unit_slot[(size_t) sl * p.per_layer + tid] : -1;
-    const bool is_miss = is_need && slot0 < 0;
-    if (is_need && slot0 >= 0) p.slot_last[slot0] = now;
-    const uint32_t mb = __ballot_sync(FULL, is_miss), nb = __ballot_sync(FULL, is_need);
-    if (lane == 0) { wmiss[w] = __popc(mb); wneed[w] = __popc(nb); }
+    // hits are touched, misses listed in expert order
+    const bool wanted = tid < p.per_layer && need[tid];
+    const int held = wanted ? p.unit_slot[(size_t) sl * p.per_layer + tid] : -1;
+    if (wanted && held >= 0) p.slot_last[held] = now;
+    int n_need, n_miss;
+    block_rank(wanted, wsum, n_need);
+    const bool missing = wanted && held < 0;
+    const int mpos = block_rank(missing, wsum, n_miss);
+    if (missing) miss_of[mpos] = tid;
+    __syncthreads();          // the hits' new ticks are visible to the whole block from here on
+    // how many slots may be replaced
+    int mine = 0;
+    for (int s = tid; s < p.slots; s += ADMIT_T) mine += slot_replaceable(p.slot_last[s], now, prev);
+    if (tid < 256) hist[tid] = 0;
     __syncthreads();
-    if (is_miss) {
-        int at = __popc(mb & ((1u << lane) - 1u));
-        for (int q = 0; q < w; ++q) at += wmiss[q];
-        misses[at] = tid;
-    }
+    if (mine) atomicAdd(&hist[0], mine);
+    __syncthreads();
+    const int n_free = hist[0];
+    const int n_adm = n_miss < n_free ? n_miss : n_free;      // victims wanted
     if (tid == 0) {
-        int nm = 0, nn = 0;
-        for (int q = 0; q < 32; ++q) { nm += wmiss[q]; nn += wneed[q]; }
-        nmiss = nm;
         p.tick[0] = now;
-        p.stats[0] += (uint32_t) (nn - nm);
-        p.stats[1] += (uint32_t) nm;
-        *p.njobs = nm;
-        best = ~0ull;
+        p.stats[0] += (uint32_t) (n_need - n_miss);
+        p.stats[1] += (uint32_t) n_miss;
+        *p.njobs = n_adm;
+        sel_prefix = 0u;
+        sel_remaining = n_adm;
     }
     __syncthreads();
-    const int nm = nmiss;
-    for (int m = 0; m < nm; ++m) {
-        unsigned long long key = ~0ull;   // (last use, slot): the minimum is the LRU slot, lowest index on ties
-        for (int s = tid; s < p.slots; s += CACHE_MAX_PER_LAYER) {
+    if (n_adm == 0) return;
+    // (1) the tick of the n_adm-th smallest replaceable slot, one byte per pass from the top
+    uint32_t known = 0u;      // mask of the bits already fixed
+    for (int shift = 24; shift >= 0; shift -= 8) {
+        if (tid < 256) hist[tid] = 0;
+        __syncthreads();
+        const uint32_t prefix = sel_prefix;
+        for (int s = tid; s < p.slots; s += ADMIT_T) {
             const uint32_t last = p.slot_last[s];
-            if (last == now || last == prev) continue;
-            const unsigned long long k2 = ((unsigned long long) last << 32) | (uint32_t) s;
-            key = k2 < key ? k2 : key;
+            if (slot_replaceable(last, now, prev) && (last & known) == prefix) atomicAdd(&hist[(last >> shift) & 255u], 1);
         }
-        for (int o = 16; o > 0; o >>= 1) {
-            const unsigned long long k2 = __shfl_xor_sync(FULL, key, o);
-            key = k2 < key ? k2 : key;
-        }
-        if (lane == 0 && key != ~0ull) atomicMin(&best, key);
         __syncthreads();
-        const unsigned long long got = best;
-        __syncthreads();
-        if (got == ~0ull) {   // nothing may be replaced: stop admitting
-            if (tid == 0) *p.njobs = m;
-            break;
-        }
         if (tid == 0) {
-            const int slot = (int) (got & 0xFFFFFFFFu), x = misses[m], u = sl * p.per_layer + x, old = p.slot_unit[slot];
-            if (old >= 0) p.unit_slot[old] = -1;
-            p.slot_unit[slot] = u;
-            p.unit_slot[u] = slot;
-            p.slot_last[slot] = now;
-            p.jobs[2 * m] = u;
-            p.jobs[2 * m + 1] = slot;
-            uint8_t* base = p.vram + (uint64_t) slot * p.unit_bytes;
-            for (int i = 0; i < p.ntens; ++i) {
-                WSlice* t = p.tab + ((size_t) sl * p.ntens + i) * p.per_layer + x;
-                for (int st = 0; st < 4; ++st)
-                    if (p.off[i][st] != 0xFFFFFFFFu) t->p[st] = base + p.off[i][st];
-            }
-            best = ~0ull;
-            __threadfence_block();
+            int left = sel_remaining, b = 0;
+            while (b < 255 && hist[b] < left) left -= hist[b++];
+            sel_remaining = left;                 // rank inside bin b, 1-based
+            sel_prefix = prefix | ((uint32_t) b << shift);
         }
+        known |= 255u << shift;
         __syncthreads();
+    }
+    const uint32_t cut = sel_prefix;               // every replaceable slot older than `cut` is a victim,
+    const int want_eq = sel_remaining;             // and the `want_eq` lowest slots whose tick equals it
+    // (2) the victims, gathered in slot order
+    int n_lt = 0, n_eq = 0;
+    for (int base = 0; base < p.slots; base += ADMIT_T) {
+        const int s = base + tid;
+        const uint32_t last = s < p.slots ? p.slot_last[s] : now;
+        const bool ok = s < p.slots && slot_replaceable(last, now, prev);
+        int t_lt, t_eq;
+        const int r_lt = block_rank(ok && last < cut, wsum, t_lt);
+        const int r_eq = block_rank(ok && last == cut, wsum, t_eq);
+        const unsigned long long key = ((unsigned long long) last << 32) | (uint32_t) s;
+        // older slots fill the list's front part from the left, equal ones its last want_eq entries
+        if (ok && last < cut) vict[n_lt + r_lt] = key;
+        if (ok && last == cut && n_eq + r_eq < want_eq) vict[(n_adm - want_eq) + n_eq + r_eq] = key;
+        n_lt += t_lt;
+        n_eq += t_eq;
+    }
+    __syncthreads();
+    // (3) + (4): thread t owns victim t, finds its rank among the victims and serves the miss of that rank
+    if (tid < n_adm) {
+        const unsigned long long key = vict[tid];
+        int rank = 0;
+        for (int j = 0; j < n_adm; ++j) rank += vict[j] < key;
+        const int slot = (int) (key & 0xFFFFFFFFu), x = miss_of[rank], u = sl * p.per_layer + x;
+        const int old = p.slot_unit[slot];
+        if (old >= 0) p.unit_slot[old] = -1;
+        p.slot_unit[slot] = u;
+        p.unit_slot[u] = slot;
+        p.slot_last[slot] = now;
+        p.jobs[2 * rank] = u;
+        p.jobs[2 * rank + 1] = slot;
+        uint8_t* base = p.vram + (uint64_t) slot * p.unit_bytes;
+        for (int i = 0; i < p.ntens; ++i) {
+            WSlice* t = p.tab + ((size_t) sl * p.ntens + i) * p.per_layer + x;
+            for (int st = 0; st < 4; ++st)
+                if (p.off[i][st] != 0xFFFFFFFFu) t->p[st] = base + p.off[i][st];
+        }
     }
 }
 
-// Copy (grid = the caller's block count): every queued unit from the host arena (mapped pinned memory, read over PCIe by
-// the kernel) into its slot, 16 bytes per thread per step with four loads in flight per thread.
+// Copy (grid = the caller's block count): the queued units, as one long run of 16-byte words (job after job), are dealt
+// to the blocks in contiguous shares, so a block streams a few long host ranges (mapped pinned memory, read over PCIe by
+// the kernel itself) instead of striding over every unit; eight loads in flight per thread.
 __global__ void __launch_bounds__(512) cache_copy_kernel(CachePool p) {
     const int nj = *p.njobs;
-    const uint64_t words = p.unit_bytes / 16, stride = (uint64_t) gridDim.x * blockDim.x;
-    for (int j = 0; j < nj; ++j) {
-        const uint4* src = (const uint4*) (p.host + (uint64_t) p.jobs[2 * j] * p.unit_bytes);
-        uint4* dst = (uint4*) (p.vram + (uint64_t) p.jobs[2 * j + 1] * p.unit_bytes);
-        uint64_t i = (uint64_t) blockIdx.x * blockDim.x + threadIdx.x;
-        for (; i + 3 * stride < words; i += 4 * stride) {
-            const uint4 a = src[i], b = src[i + stride], c = src[i + 2 * stride], d = src[i + 3 * stride];
-            dst[i] = a; dst[i + stride] = b; dst[i + 2 * stride] = c; dst[i + 3 * stride] = d;
+    if (nj <= 0) return;
+    const uint64_t per_unit = p.unit_bytes / 16, total = per_unit * (uint64_t) nj;
+    const uint64_t lo = total * blockIdx.x / gridDim.x, hi = total * (blockIdx.x + 1) / gridDim.x;
+    uint64_t at = lo;
+    while (at < hi) {
+        const int j = (int) (at / per_unit);
+        const uint64_t w0 = at - (uint64_t) j * per_unit;
+        const uint64_t n = (hi - at) < (per_unit - w0) ? (hi - at) : (per_unit - w0);     // words of job j in this share
+        const uint4* src = (const uint4*) (p.host + (uint64_t) p.jobs[2 * j] * p.unit_bytes) + w0;
+        uint4* dst = (uint4*) (p.vram + (uint64_t) p.jobs[2 * j + 1] * p.unit_bytes) + w0;
+        uint64_t i = threadIdx.x;
+        for (; i + 7 * 512 < n; i += 8 * 512) {
+            uint4 v[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) v[q] = src[i + q * 512];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) dst[i + q * 512] = v[q];
         }
-        for (; i < words; i += stride) dst[i] = src[i];
+        for (; i < n; i += 512) dst[i] = src[i];
+        at += n;
     }
 }
 

@@ -16,6 +16,7 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "route.cuh"
 #include "seed_block.cuh"
 
 namespace nsl {
@@ -36,8 +37,6 @@ struct MvParams {
     const int32_t* xrow;    // optional: pair p reads input row xrow[p] (instead of p / xdiv)
     const int32_t* count;   // optional: the pair count is read on the device (<= P)
     int xbf16;              // inputs are packed bf16 rows (row stride xs in bf16 elements)
-    const int32_t* units;   // optional: [n][4] work units = {pair, second pair or -1 (same slice), weight prefix, 0}
-    const int32_t* n_units; // their number, on the device
 };
 
 __device__ __forceinline__ float silu_bf(float g) {   // each op rounded to bf16 (engine/kernels_moe.cu:28-31)
@@ -89,98 +88,6 @@ __device__ __forceinline__ void store_out(const MvParams& a, int pair, int r, fl
     else *yo = a.add ? bf16_round(*yo + bf16_round(s)) : bf16_round(s);   // engine/kernels_moe.cu:214
 }
 
-// ---- one token per pair, inputs in registers: rows of 1, 2, 4, .. 32 chunks (K = 64 .. 2048) -------------------------
-// The work is the pair-major sequence of row steps (a step = the 32 / lanes-per-row rows a warp expands at once); every
-// warp of the grid takes one contiguous, equal share of it.  A share touches one or two pairs (more only when there are
-// more pairs than warps), so a warp loads a pair's inputs into registers at most that often, the shares differ by at
-// most one step, and inside a share the next row's streams are prefetched while the current row is expanded.
-template <int MODE>
-__global__ void __launch_bounds__(MV_THREADS, 1) mv_regx_kernel(MvParams a, KConst kc, int lpr_log2) {
-    __shared__ StreamTab tab;
-    load_stream_tab(tab, a.G, threadIdx.x, MV_THREADS);
-    grid_dependents_go();
-    grid_dependency_wait();   // everything below may read what the previous kernel in the stream wrote
-    __syncthreads();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int lpr = 1 << lpr_log2, rpw = 32 >> lpr_log2;
-    const int jc = lane & (lpr - 1), ro = lane >> lpr_log2;
-    const long long nw = (long long) gridDim.x * MV_WARPS, gw = (long long) blockIdx.x * MV_WARPS + warp;
-    const int P = a.count ? min(*a.count, a.P) : a.P;
-    const int rs = (a.R + rpw - 1) / rpw;                 // row steps per pair
-    const long long total = (long long) P * rs;
-    const long long begin = gw * total / nw, end = (gw + 1) * total / nw;
-    if (begin >= end) return;
-    const int p_first = (int) (begin / rs), p_last = (int) ((end - 1) / rs);
-    for (int pair = p_first; pair <= p_last; ++pair) {
-        const int s_lo = pair == p_first ? (int) (begin - (long long) pair * rs) : 0;
-        const int s_hi = pair == p_last ? (int) (end - (long long) pair * rs) : rs;
-        const int slice = a.sel ? a.sel[pair] : 0;
-        const WSlice wa = a.ws ? a.ws[slice] : a.w0;
-        WSlice wb = wa;
-        if (MODE == MODE_GU) wb = a.wu[slice];
-        u64 x2[32], xm2[16];
-        {
-            const int xr = a.xrow ? a.xrow[pair] : pair / a.xdiv;
-            float x[64], xm[32];
-            if (a.xbf16) {
-                const uint4* xp = (const uint4*) ((const uint16_t*) a.x + (size_t) xr * a.xs + (size_t) jc * 64);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const uint4 t = __ldg(xp + i);
-                    const uint32_t u[4] = {t.x, t.y, t.z, t.w};
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        x[8 * i + 2 * j] = __uint_as_float(u[j] << 16) * NSL_XSCALE;
-                        x[8 * i + 2 * j + 1] = __uint_as_float(u[j] & 0xFFFF0000u) * NSL_XSCALE;
-                    }
-                }
-            } else {
-                const float4* xp = (const float4*) (a.x + (size_t) xr * a.xs + (size_t) jc * 64);
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const float4 t = __ldg(xp + i);
-                    x[4 * i] = t.x * NSL_XSCALE; x[4 * i + 1] = t.y * NSL_XSCALE; x[4 * i + 2] = t.z * NSL_XSCALE; x[4 * i + 3] = t.w * NSL_XSCALE;
-                }
-            }
-#pragma unroll
-            for (int b = 0; b < 8; ++b) block_offsets(x + 8 * b, xm + 4 * b);
-#pragma unroll
-            for (int bp = 0; bp < 4; ++bp) {
-#pragma unroll
-                for (int c = 0; c < 8; ++c) x2[8 * bp + c] = pack2(x[16 * bp + c], x[16 * bp + 8 + c]);
-#pragma unroll
-                for (int p = 0; p < 4; ++p) xm2[4 * bp + p] = pack2(xm[8 * bp + p], xm[8 * bp + 4 + p]);
-            }
-        }
-        const float sca = slice_scale(wa.eb), scb = slice_scale(wb.eb);
-        int r = s_lo * rpw + ro;
-        Chunk ka, kb;
-        if (r < a.R) {
-            ka = load_chunk(wa, (size_t) r * lpr + jc);
-            if (MODE == MODE_GU) kb = load_chunk(wb, (size_t) r * lpr + jc);
-        }
-        for (int st = s_lo; st < s_hi; ++st, r += rpw) {
-            const bool ok = r < a.R;
-            const int rn = r + rpw;
-            Chunk na, nb;
-            if (st + 1 < s_hi && rn < a.R) {   // next row's streams in flight during this row's expansion
-                na = load_chunk(wa, (size_t) rn * lpr + jc);
-                if (MODE == MODE_GU) nb = load_chunk(wb, (size_t) rn * lpr + jc);
-            }
-            float s = 0.0f, su = 0.0f;
-            if (ok) {
-                s = pair_total(chunk_dot(tab, kc, ka, x2, xm2, 0ull));
-                if (MODE == MODE_GU) su = pair_total(chunk_dot(tab, kc, kb, x2, xm2, 0ull));
-            }
-            s = group_sum(s, lpr) * sca;
-            if (MODE == MODE_GU) su = group_sum(su, lpr) * scb;
-            if (ok && jc == 0) store_out<MODE>(a, pair, r, s, su);
-            ka = na;
-            if (MODE == MODE_GU) kb = nb;
-        }
-    }
-}
-
 // One thread's share of staging a pair's inputs: 16 inputs (two blocks: chunk j of the row, block pair bp), scaled, as
 // the f32x2 operands of pair_dot plus their centring constants.
 __device__ __forceinline__ void stage_inputs(const MvParams& a, int xr, int j, int bp, ulonglong2* sx, ulonglong2* sm) {
@@ -223,60 +130,90 @@ __device__ __forceinline__ void stage_inputs(const MvParams& a, int xr, int j, i
     }
 }
 
-// ---- one token per pair, inputs in shared memory, two blocks of 8 warps per SM ------------------------------------------
-// The same arithmetic, lane mapping and order as mv_regx_kernel (so results are bit-identical), but the pair's inputs
-// sit in shared memory as the f32x2 operands of pair_dot, laid out [block pair][operand pair][lane] so that a warp's
-// 16-byte loads are conflict-free.  Without 96 registers of inputs a thread fits in 128 registers and 16 warps per SM
-// hide the logic pipe's latencies.  Blocks take contiguous shares of the pair-major row-step sequence; inside a pair
-// the block's warps take its steps round-robin.
-template <int MODE>
-__global__ void __launch_bounds__(MV_THREADS, 2) mv_shx_kernel(MvParams a, KConst kc, int lpr_log2) {
-    __shared__ StreamTab tab;
-    __shared__ __align__(16) ulonglong2 sx[4 * 4 * 32];   // [bp][c / 2][lane] = {x2[c], x2[c + 1]}
-    __shared__ __align__(16) ulonglong2 sm[4 * 2 * 32];   // [bp][p / 2][lane] = {xm2[p], xm2[p + 1]}
-    load_stream_tab(tab, a.G, threadIdx.x, MV_THREADS);
-    grid_dependents_go();
-    grid_dependency_wait();   // everything below may read what the previous kernel in the stream wrote
+
+// ---- pairs grouped by expert: one expansion per distinct slice ---------------------------------------------------------
+// Rows of 1, 2, 4, .. 32 chunks (K = 64 .. 2048).  Every block builds the same plan in its prologue: the pair list is
+// sorted by slice in shared memory, runs of pairs that use the same slice are cut into UNITS of at most GRP_NT pairs, and
+// a unit's rows are expanded once for all its pairs (the logic-pipe work is shared; each pair keeps its own sums, formed in
+// the same order as when it is alone, so a pair's result does not depend on its partners).  The work is the sequence of
+// (unit, row step) items, an item of a unit with n pairs weighing GRP_W[n]; blocks take contiguous equal shares of the
+// weighted sequence, inside a unit the block's warps take its row steps round-robin, a row step being the 32 /
+// lanes-per-row rows a warp expands at once.  A unit's inputs sit in shared memory as the f32x2 operands of pair_dot,
+// laid out [pair][block pair][operand pair][lane] so that a warp's 16-byte loads are conflict-free.
+//
+// Optionally the block first ROUTES: with logits given, warp t picks token t's top-k experts (route.cuh) and the pair
+// list is the T * top_k (token, expert) pairs; block 0 also stores ids and weights for the kernels that follow.
+#ifndef NSL_GRP_NT
+#define NSL_GRP_NT 4
+#endif
+constexpr int GRP_NT = NSL_GRP_NT;                         // pairs that share one expansion at most
+constexpr int GRP_MAX_PAIRS = 1024;               // pairs a block can sort; longer lists run ungrouped
+__device__ constexpr int GRP_W[5] = {0, 8, 9, 11, 13};   // relative cost of a row step for a unit of n pairs
+constexpr int GRP_SX = 4 * 4 * 32, GRP_SM = 4 * 2 * 32;           // ulonglong2 entries of one pair's inputs / centring constants
+
+struct GrpShared {
+    StreamTab tab;
+    uint32_t key[GRP_MAX_PAIRS];                  // sorted (slice << 10 | pair)
+    int32_t prefix[GRP_MAX_PAIRS + 1];            // weight of the units that start before sorted position i
+    int32_t r_ind[256];                           // the fused router's picks
+    float r_wt[256];
+    __align__(16) ulonglong2 sx[GRP_NT][GRP_SX];
+    __align__(16) ulonglong2 sm[GRP_NT][GRP_SM];
+};
+
+struct RouteFuse {        // the router folded into the prologue (logits == NULL: the pair list comes from MvParams.sel)
+    const float* logits;
+    int ld, n_exp, top_k, T;
+    int32_t* ind_out;
+    float* wt_out;
+};
+
+// One row step of one matrix for NT pairs: four block pairs expanded once each, dotted with every pair's inputs.
+template <int NT>
+__device__ __forceinline__ void unit_chunk(const StreamTab& tab, const KConst& kc, const Chunk& k, const ulonglong2 (*sx)[GRP_SX],
+                                           const ulonglong2 (*sm)[GRP_SM], int jc, u64* acc) {
+    const uint32_t sw[4] = {k.s.x, k.s.y, k.s.z, k.s.w}, cw[4] = {k.c.x, k.c.y, k.c.z, k.c.w};
+#pragma unroll
+    for (int bp = 0; bp < 4; ++bp) {
+        u64 v[32], q[4];
+        pair_states(tab, sw[bp], v);
+        pair_coefs(cw[bp], kc, q);
+        const u64 e2 = code_scale_pair(k.cd, bp, kc);
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+            u64 x2[8], xm2[4];
+#pragma unroll
+            for (int cq = 0; cq < 4; ++cq) { const ulonglong2 u = sx[t][(bp * 4 + cq) * 32 + jc]; x2[2 * cq] = u.x; x2[2 * cq + 1] = u.y; }
+#pragma unroll
+            for (int pq = 0; pq < 2; ++pq) { const ulonglong2 u = sm[t][(bp * 2 + pq) * 32 + jc]; xm2[2 * pq] = u.x; xm2[2 * pq + 1] = u.y; }
+            acc[t] = fma2(pair_dot(v, q, x2, xm2), e2, acc[t]);
+        }
+    }
+}
+
+// The row steps [s_lo, s_hi) of a unit of NT pairs that fall to this warp.  ka / kb: the streams of its first step,
+// requested by the caller before the unit's inputs were staged.
+template <int MODE, int NT>
+__device__ __forceinline__ void unit_rows(const MvParams& a, const KConst& kc, const GrpShared& sh, const WSlice& wa, const WSlice& wb,
+                                          const int* pid, int s_lo, int s_hi, int lpr_log2, Chunk ka, Chunk kb) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int lpr = 1 << lpr_log2, rpw = 32 >> lpr_log2;
     const int jc = lane & (lpr - 1), ro = lane >> lpr_log2;
-    const int P = a.count ? min(*a.count, a.P) : a.P;
-    const int rs = (a.R + rpw - 1) / rpw;
-    const long long total = (long long) P * rs;
-    const long long begin = (long long) blockIdx.x * total / gridDim.x, end = (long long) (blockIdx.x + 1) * total / gridDim.x;
-    if (begin >= end) return;
-    const int p_first = (int) (begin / rs), p_last = (int) ((end - 1) / rs);
-    for (int pair = p_first; pair <= p_last; ++pair) {
-        const int s_lo = pair == p_first ? (int) (begin - (long long) pair * rs) : 0;
-        const int s_hi = pair == p_last ? (int) (end - (long long) pair * rs) : rs;
-        const int slice = a.sel ? a.sel[pair] : 0;
-        const WSlice wa = a.ws ? a.ws[slice] : a.w0;
-        WSlice wb = wa;
-        if (MODE == MODE_GU) wb = a.wu[slice];
-        // this warp's first streams are requested before the inputs are staged: their DRAM latency runs under it
-        int st = s_lo + warp;
-        int r = st * rpw + ro;
-        Chunk ka, kb;
-        if (st < s_hi && r < a.R) {
-            ka = load_chunk(wa, (size_t) r * lpr + jc);
-            if (MODE == MODE_GU) kb = load_chunk(wb, (size_t) r * lpr + jc);
-        }
-        if (pair != p_first) __syncthreads();   // the previous pair's inputs are no longer read
-        if (threadIdx.x < lpr * 4) {
-            const int j = threadIdx.x & (lpr - 1), bp = threadIdx.x >> lpr_log2;
-            stage_inputs(a, a.xrow ? a.xrow[pair] : pair / a.xdiv, j, bp, sx, sm);
-        }
-        __syncthreads();   // inputs staged (and, for the block's first pair, the stream table loaded)
-        const float sca = slice_scale(wa.eb), scb = slice_scale(wb.eb);
-        for (; st < s_hi; st += MV_WARPS, r += MV_WARPS * rpw) {
-            const bool ok = r < a.R;
-            const int rn = r + MV_WARPS * rpw;
+    const float sca = slice_scale(wa.eb), scb = slice_scale(wb.eb);
+    int st = s_lo + warp, r = st * rpw + ro;
+    for (; st < s_hi; st += MV_WARPS, r += MV_WARPS * rpw) {
+        const bool ok = r < a.R;
+        const int rn = r + MV_WARPS * rpw;
+        const bool more = st + MV_WARPS < s_hi && rn < a.R;
+        u64 acc[NT], accu[NT];
+#pragma unroll
+        for (int t = 0; t < NT; ++t) acc[t] = accu[t] = 0ull;
+        if (NT == 1 && MODE == MODE_GU) {      // one pair: its inputs are read once per block pair for both matrices
             Chunk na, nb;
-            if (st + MV_WARPS < s_hi && rn < a.R) {
+            if (more) {   // the next step's streams fly during this step's expansion
                 na = load_chunk(wa, (size_t) rn * lpr + jc);
-                if (MODE == MODE_GU) nb = load_chunk(wb, (size_t) rn * lpr + jc);
+                nb = load_chunk(wb, (size_t) rn * lpr + jc);
             }
-            u64 acc = 0ull, accu = 0ull;
             if (ok) {
                 const uint32_t swa[4] = {ka.s.x, ka.s.y, ka.s.z, ka.s.w}, cwa[4] = {ka.c.x, ka.c.y, ka.c.z, ka.c.w};
                 const uint32_t swb[4] = {kb.s.x, kb.s.y, kb.s.z, kb.s.w}, cwb[4] = {kb.c.x, kb.c.y, kb.c.z, kb.c.w};
@@ -284,30 +221,187 @@ __global__ void __launch_bounds__(MV_THREADS, 2) mv_shx_kernel(MvParams a, KCons
                 for (int bp = 0; bp < 4; ++bp) {
                     u64 x2[8], xm2[4];
 #pragma unroll
-                    for (int cq = 0; cq < 4; ++cq) { const ulonglong2 t = sx[(bp * 4 + cq) * 32 + jc]; x2[2 * cq] = t.x; x2[2 * cq + 1] = t.y; }
+                    for (int cq = 0; cq < 4; ++cq) { const ulonglong2 u = sh.sx[0][(bp * 4 + cq) * 32 + jc]; x2[2 * cq] = u.x; x2[2 * cq + 1] = u.y; }
 #pragma unroll
-                    for (int pq = 0; pq < 2; ++pq) { const ulonglong2 t = sm[(bp * 2 + pq) * 32 + jc]; xm2[2 * pq] = t.x; xm2[2 * pq + 1] = t.y; }
+                    for (int pq = 0; pq < 2; ++pq) { const ulonglong2 u = sh.sm[0][(bp * 2 + pq) * 32 + jc]; xm2[2 * pq] = u.x; xm2[2 * pq + 1] = u.y; }
                     {
                         u64 v[32], q[4];
-                        pair_states(tab, swa[bp], v);
+                        pair_states(sh.tab, swa[bp], v);
                         pair_coefs(cwa[bp], kc, q);
-                        acc = fma2(pair_dot(v, q, x2, xm2), code_scale_pair(ka.cd, bp, kc), acc);
+                        acc[0] = fma2(pair_dot(v, q, x2, xm2), code_scale_pair(ka.cd, bp, kc), acc[0]);
                     }
-                    if (MODE == MODE_GU) {
+                    {
                         u64 v[32], q[4];
-                        pair_states(tab, swb[bp], v);
+                        pair_states(sh.tab, swb[bp], v);
                         pair_coefs(cwb[bp], kc, q);
-                        accu = fma2(pair_dot(v, q, x2, xm2), code_scale_pair(kb.cd, bp, kc), accu);
+                        accu[0] = fma2(pair_dot(v, q, x2, xm2), code_scale_pair(kb.cd, bp, kc), accu[0]);
                     }
                 }
             }
-            const float s = group_sum(pair_total(acc), lpr) * sca;
-            float su = 0.0f;
-            if (MODE == MODE_GU) su = group_sum(pair_total(accu), lpr) * scb;
-            if (ok && jc == 0) store_out<MODE>(a, pair, r, s, su);
             ka = na;
-            if (MODE == MODE_GU) kb = nb;
+            kb = nb;
+        } else {
+            // several pairs (or one matrix): a matrix's streams for the next step are requested as soon as this step has
+            // used them up, into the registers they leave free, so no second set of stream registers is held
+            if (ok) unit_chunk<NT>(sh.tab, kc, ka, sh.sx, sh.sm, jc, acc);
+            if (more) ka = load_chunk(wa, (size_t) rn * lpr + jc);
+            if (MODE == MODE_GU) {
+                if (ok) unit_chunk<NT>(sh.tab, kc, kb, sh.sx, sh.sm, jc, accu);
+                if (more) kb = load_chunk(wb, (size_t) rn * lpr + jc);
+            }
         }
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+            const float s = group_sum(pair_total(acc[t]), lpr) * sca;
+            float su = 0.0f;
+            if (MODE == MODE_GU) su = group_sum(pair_total(accu[t]), lpr) * scb;
+            if (ok && jc == 0) store_out<MODE>(a, pid[t], r, s, su);
+        }
+    }
+}
+
+// Ascending bitonic sort of n (a power of two) keys in shared memory by the whole block.
+__device__ __forceinline__ void block_sort(uint32_t* key, int n) {
+    for (int k = 2; k <= n; k <<= 1)
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            for (int i = threadIdx.x; i < n; i += MV_THREADS) {
+                const int o = i ^ j;
+                if (o > i) {
+                    const uint32_t x = key[i], y = key[o];
+                    if ((x > y) == ((i & k) == 0)) { key[i] = y; key[o] = x; }
+                }
+            }
+            __syncthreads();
+        }
+}
+
+// In-place exclusive prefix sum of a[0..n) by the whole block, a[n] = the total (n <= GRP_MAX_PAIRS).
+__device__ __forceinline__ void block_exclusive_scan(int32_t* a, int n) {
+    __shared__ int wtot[MV_WARPS];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int per = (n + MV_THREADS - 1) / MV_THREADS, lo = threadIdx.x * per;      // a contiguous run per thread
+    int sum = 0;
+    for (int i = lo; i < lo + per && i < n; ++i) sum += a[i];
+    int inc = sum;
+    for (int o = 1; o < 32; o <<= 1) { const int v = __shfl_up_sync(0xFFFFFFFFu, inc, o); if (lane >= o) inc += v; }
+    if (lane == 31) wtot[warp] = inc;
+    __syncthreads();
+    int base = inc - sum;
+    for (int w = 0; w < warp; ++w) base += wtot[w];
+    for (int i = lo; i < lo + per && i < n; ++i) { const int v = a[i]; a[i] = base; base += v; }
+    if (threadIdx.x == MV_THREADS - 1) { int t = 0; for (int w = 0; w < MV_WARPS; ++w) t += wtot[w]; a[n] = t; }
+    __syncthreads();
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(MV_THREADS, 2) mv_grp_kernel(MvParams a, KConst kc, int lpr_log2, RouteFuse rf) {
+    extern __shared__ __align__(16) unsigned char grp_smem[];
+    GrpShared& sh = *reinterpret_cast<GrpShared*>(grp_smem);
+    load_stream_tab(sh.tab, a.G, threadIdx.x, MV_THREADS);
+    grid_dependents_go();
+    grid_dependency_wait();   // everything below may read what the previous kernel in the stream wrote
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int lpr = 1 << lpr_log2, rpw = 32 >> lpr_log2;
+    const int jc = lane & (lpr - 1), ro = lane >> lpr_log2;
+    int P = a.count ? min(*a.count, a.P) : a.P;
+    if (rf.logits) {          // the router: one warp per token, every block the same picks
+        if (warp < rf.T) {
+            const float* l = rf.logits + (size_t) warp * rf.ld;
+            if (rf.n_exp <= 128) route_row<4>(rf.n_exp, rf.top_k, l, lane, sh.r_ind + warp * rf.top_k, sh.r_wt + warp * rf.top_k);
+            else if (rf.n_exp <= 512) route_row<16>(rf.n_exp, rf.top_k, l, lane, sh.r_ind + warp * rf.top_k, sh.r_wt + warp * rf.top_k);
+            else route_row<32>(rf.n_exp, rf.top_k, l, lane, sh.r_ind + warp * rf.top_k, sh.r_wt + warp * rf.top_k);
+        }
+        P = rf.T * rf.top_k;
+        __syncthreads();
+        if (blockIdx.x == 0 && (int) threadIdx.x < P) {
+            rf.ind_out[threadIdx.x] = sh.r_ind[threadIdx.x];
+            rf.wt_out[threadIdx.x] = sh.r_wt[threadIdx.x];
+        }
+    }
+    if (P <= 0) return;
+    const int rs = (a.R + rpw - 1) / rpw;             // row steps per unit
+    const bool grouped = P <= GRP_MAX_PAIRS;
+    long long total;
+    if (grouped) {
+        int n = 32;
+        while (n < P) n <<= 1;
+        for (int i = threadIdx.x; i < n; i += MV_THREADS) {
+            const int slice = rf.logits ? sh.r_ind[i < P ? i : 0] : (a.sel ? a.sel[i < P ? i : 0] : 0);
+            sh.key[i] = i < P ? ((uint32_t) slice << 10) | (uint32_t) i : 0xFFFFFFFFu;
+        }
+        __syncthreads();
+        block_sort(sh.key, n);
+        // a sorted position starts a unit when it is a multiple of GRP_NT pairs into its slice's run
+        for (int i = threadIdx.x; i < P; i += MV_THREADS) {
+            const uint32_t first = sh.key[i] & ~1023u;          // the smallest key of this slice
+            int lo = 0, hi = i;                                  // lower bound of `first`
+            while (lo < hi) { const int mid = (lo + hi) >> 1; if (sh.key[mid] < first) lo = mid + 1; else hi = mid; }
+            int w = 0;
+            if ((i - lo) % GRP_NT == 0) {
+                int cnt = 1;
+                while (cnt < GRP_NT && i + cnt < P && (sh.key[i + cnt] >> 10) == (sh.key[i] >> 10)) ++cnt;
+                w = GRP_W[cnt];
+            }
+            sh.prefix[i] = w;
+        }
+        __syncthreads();
+        block_exclusive_scan(sh.prefix, P);
+        total = (long long) sh.prefix[P] * rs;
+    } else {
+        __syncthreads();
+        total = (long long) P * GRP_W[1] * rs;
+    }
+    const long long begin = (long long) blockIdx.x * total / gridDim.x, end = (long long) (blockIdx.x + 1) * total / gridDim.x;
+    if (begin >= end) return;
+    // position in the weighted sequence -> (sorted position of the unit's first pair, row step)
+    auto locate = [&](long long x, int& u, int& step) {
+        if (!grouped) { u = (int) (x / ((long long) GRP_W[1] * rs)); step = (int) ((x - (long long) u * GRP_W[1] * rs) / GRP_W[1]); return; }
+        int lo = 0, hi = P;                                      // the last position whose prefix * rs <= x
+        while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if ((long long) sh.prefix[mid] * rs <= x) lo = mid; else hi = mid; }
+        u = lo;
+        step = (int) ((x - (long long) sh.prefix[lo] * rs) / (sh.prefix[lo + 1] - sh.prefix[lo]));
+    };
+    int u_first, s_first, u_last, s_last;
+    locate(begin, u_first, s_first);
+    if (end >= total) { u_last = P; s_last = 0; } else locate(end, u_last, s_last);
+    bool staged = false;
+    for (int u = u_first; u <= u_last && u < P;) {
+        int n = 1, pid[GRP_NT], slice = 0;
+#pragma unroll
+        for (int t = 0; t < GRP_NT; ++t) pid[t] = u;
+        if (grouped) {
+            const int w = sh.prefix[u + 1] - sh.prefix[u];
+            n = w == GRP_W[1] ? 1 : w == GRP_W[2] ? 2 : w == GRP_W[3] ? 3 : 4;
+#pragma unroll
+            for (int t = 0; t < GRP_NT; ++t) pid[t] = (int) (sh.key[u + (t < n ? t : 0)] & 1023u);
+            slice = (int) (sh.key[u] >> 10);
+        } else slice = a.sel ? a.sel[u] : 0;
+        const int s_lo = u == u_first ? s_first : 0, s_hi = u == u_last ? s_last : rs;
+        if (s_lo < s_hi) {
+            const WSlice wa = a.ws ? a.ws[slice] : a.w0;
+            WSlice wb = wa;
+            if (MODE == MODE_GU) wb = a.wu[slice];
+            // this warp's first streams are requested before the inputs are staged: their latency runs under the staging
+            const int st0 = s_lo + warp, r0 = st0 * rpw + ro;
+            Chunk ka, kb;
+            if (st0 < s_hi && r0 < a.R) {
+                ka = load_chunk(wa, (size_t) r0 * lpr + jc);
+                if (MODE == MODE_GU) kb = load_chunk(wb, (size_t) r0 * lpr + jc);
+            }
+            if (staged) __syncthreads();   // the previous unit's inputs are no longer read
+            staged = true;
+            for (int i = threadIdx.x; i < n * lpr * 4; i += MV_THREADS) {
+                const int t = i / (lpr * 4), rem = i - t * lpr * 4;
+                const int p = grouped ? (int) (sh.key[u + t] & 1023u) : u;
+                stage_inputs(a, a.xrow ? a.xrow[p] : p / a.xdiv, rem & (lpr - 1), rem >> lpr_log2, sh.sx[t], sh.sm[t]);
+            }
+            __syncthreads();
+            if (GRP_NT >= 4 && n == 4) unit_rows<MODE, GRP_NT >= 4 ? 4 : 1>(a, kc, sh, wa, wb, pid, s_lo, s_hi, lpr_log2, ka, kb);
+            else if (GRP_NT >= 3 && n == 3) unit_rows<MODE, GRP_NT >= 3 ? 3 : 1>(a, kc, sh, wa, wb, pid, s_lo, s_hi, lpr_log2, ka, kb);
+            else if (GRP_NT >= 2 && n == 2) unit_rows<MODE, GRP_NT >= 2 ? 2 : 1>(a, kc, sh, wa, wb, pid, s_lo, s_hi, lpr_log2, ka, kb);
+            else unit_rows<MODE, 1>(a, kc, sh, wa, wb, pid, s_lo, s_hi, lpr_log2, ka, kb);
+        }
+        u += n;
     }
 }
 
@@ -416,167 +510,6 @@ __global__ void __launch_bounds__(MV_THREADS, 1) mv_smemx_kernel(MvParams a, KCo
     }
 }
 
-// ---- two pairs per expansion -----------------------------------------------------------------------------------------
-// mv_shx_kernel over work UNITS: a unit is one or two pairs that use the same slice, and a block pair's 32 states and
-// coefficients are expanded once for both.  Per pair the arithmetic and its order are those of mv_shx_kernel, so the
-// results are bit-identical; what changes is that the logic-pipe work (the expansion) is shared.
-// The next row step's streams travel global -> shared memory with cp.async (no registers held while they fly): one slot
-// per thread and matrix, read back only by the thread that requested it.
-struct ChunkSlots { uint4 s[MV_THREADS], c[MV_THREADS]; uint32_t cd[MV_THREADS]; };
-
-__device__ __forceinline__ void chunk_request(ChunkSlots& sl, const WSlice* __restrict__ w, size_t chunk_index) {
-    const unsigned long long* wp = (const unsigned long long*) w->p;   // the slice's stream addresses, re-read (L1) per request
-    const void* p0 = (const void*) __ldg(wp);
-    const void* p1 = (const void*) __ldg(wp + 1);
-    const void* p3 = (const void*) __ldg(wp + 3);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned) __cvta_generic_to_shared(&sl.s[threadIdx.x])),
-                 "l"((const uint4*) p0 + chunk_index) : "memory");
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned) __cvta_generic_to_shared(&sl.c[threadIdx.x])),
-                 "l"((const uint4*) p1 + chunk_index) : "memory");
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned) __cvta_generic_to_shared(&sl.cd[threadIdx.x])),
-                 "l"((const uint32_t*) p3 + chunk_index) : "memory");
-}
-__device__ __forceinline__ Chunk chunk_take(const ChunkSlots& sl) {
-    Chunk k;
-    k.s = sl.s[threadIdx.x];
-    k.c = sl.c[threadIdx.x];
-    k.cd = sl.cd[threadIdx.x];
-    return k;
-}
-
-// One matrix's share of a row step for a unit: four block pairs expanded once, dotted with one or two inputs.
-__device__ __forceinline__ void unit_chunk_dot(const StreamTab& tab, const KConst& kc, const Chunk& k, const ulonglong2 (*sx)[4 * 4 * 32],
-                                               const ulonglong2 (*sm)[4 * 2 * 32], int jc, bool two, u64& acc0, u64& acc1) {
-    const uint32_t sw[4] = {k.s.x, k.s.y, k.s.z, k.s.w}, cw[4] = {k.c.x, k.c.y, k.c.z, k.c.w};
-#pragma unroll
-    for (int bp = 0; bp < 4; ++bp) {
-        u64 v[32], q[4];
-        pair_states(tab, sw[bp], v);
-        pair_coefs(cw[bp], kc, q);
-        const u64 e2 = code_scale_pair(k.cd, bp, kc);
-        {
-            u64 x2[8], xm2[4];
-#pragma unroll
-            for (int cq = 0; cq < 4; ++cq) { const ulonglong2 t = sx[0][(bp * 4 + cq) * 32 + jc]; x2[2 * cq] = t.x; x2[2 * cq + 1] = t.y; }
-#pragma unroll
-            for (int pq = 0; pq < 2; ++pq) { const ulonglong2 t = sm[0][(bp * 2 + pq) * 32 + jc]; xm2[2 * pq] = t.x; xm2[2 * pq + 1] = t.y; }
-            acc0 = fma2(pair_dot(v, q, x2, xm2), e2, acc0);
-        }
-        if (two) {
-            u64 x2[8], xm2[4];
-#pragma unroll
-            for (int cq = 0; cq < 4; ++cq) { const ulonglong2 t = sx[1][(bp * 4 + cq) * 32 + jc]; x2[2 * cq] = t.x; x2[2 * cq + 1] = t.y; }
-#pragma unroll
-            for (int pq = 0; pq < 2; ++pq) { const ulonglong2 t = sm[1][(bp * 2 + pq) * 32 + jc]; xm2[2 * pq] = t.x; xm2[2 * pq + 1] = t.y; }
-            acc1 = fma2(pair_dot(v, q, x2, xm2), e2, acc1);
-        }
-    }
-}
-
-constexpr int UNIT_W1 = 3, UNIT_W2 = 4;   // relative cost of a row step for one pair and for two pairs sharing an expansion
-
-// Position x of the weighted (unit, step) sequence -> the unit that holds it and the step inside (floor).
-__device__ __forceinline__ void unit_position(const int32_t* __restrict__ units, int U, int rs, long long x, int& u, int& step) {
-    int lo = 0, hi = U;      // the last unit whose start (units[4u+2] * rs) is <= x
-    while (hi - lo > 1) {
-        const int mid = (lo + hi) >> 1;
-        if ((long long) units[4 * mid + 2] * rs <= x) lo = mid; else hi = mid;
-    }
-    const int w = units[4 * lo + 1] >= 0 ? UNIT_W2 : UNIT_W1;
-    const long long in = x - (long long) units[4 * lo + 2] * rs;
-    u = lo;
-    step = (int) (in / w);
-    if (step >= rs) { u = lo + 1; step = 0; }
-}
-
-template <int MODE>
-__global__ void __launch_bounds__(MV_THREADS, 2) mv_shx2_kernel(MvParams a, KConst kc, int lpr_log2) {
-    constexpr int NM = MODE == MODE_GU ? 2 : 1;
-    __shared__ StreamTab tab;
-    __shared__ __align__(16) ulonglong2 sx[2][4 * 4 * 32];
-    __shared__ __align__(16) ulonglong2 sm[2][4 * 2 * 32];
-    __shared__ __align__(16) ChunkSlots slots[NM];
-    load_stream_tab(tab, a.G, threadIdx.x, MV_THREADS);
-    grid_dependents_go();
-    grid_dependency_wait();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int lpr = 1 << lpr_log2, rpw = 32 >> lpr_log2;
-    const int jc = lane & (lpr - 1), ro = lane >> lpr_log2;
-    const int U = *a.n_units;
-    if (U <= 0) return;
-    const int rs = (a.R + rpw - 1) / rpw;
-    // Blocks take equal shares of the WEIGHTED sequence of (unit, row step): a step of a two-pair unit counts
-    // UNIT_W2, of a single UNIT_W1; units[4u + 2] = the weights of the units before u.
-    const long long wtotal = (long long) (a.units[4 * (U - 1) + 2] + (a.units[4 * (U - 1) + 1] >= 0 ? UNIT_W2 : UNIT_W1)) * rs;
-    const long long begin = (long long) blockIdx.x * wtotal / gridDim.x, end = (long long) (blockIdx.x + 1) * wtotal / gridDim.x;
-    if (begin >= end) return;
-    int u_first, s_first, u_last, s_last;     // [first, last) in (unit, step) order
-    bool staged = false;
-    unit_position(a.units, U, rs, begin, u_first, s_first);
-    unit_position(a.units, U, rs, end, u_last, s_last);
-    if (blockIdx.x == gridDim.x - 1) { u_last = U; s_last = 0; }
-    for (int u = u_first; u <= u_last; ++u) {
-        const int s_lo = u == u_first ? s_first : 0;
-        const int s_hi = u == u_last ? s_last : rs;
-        if (u >= U || s_lo >= s_hi) continue;
-        const int pa = a.units[4 * u], pb = a.units[4 * u + 1];
-        const bool two = pb >= 0;
-        const int slice = a.sel[pa];
-        const WSlice* wa = a.ws + slice;
-        const WSlice* wb = MODE == MODE_GU ? a.wu + slice : wa;
-        int st = s_lo + warp;
-        int r = st * rpw + ro;
-        if (st < s_hi && r < a.R) {      // this warp's first streams fly while the inputs are staged
-            chunk_request(slots[0], wa, (size_t) r * lpr + jc);
-            if (MODE == MODE_GU) chunk_request(slots[NM - 1], wb, (size_t) r * lpr + jc);
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        if (staged) __syncthreads();   // the previous unit's inputs are no longer read
-        staged = true;
-        {
-            const int half = threadIdx.x >> 7, tl = threadIdx.x & 127;   // threads 0..127 stage the first pair, 128..255 the second
-            const int pair = half ? pb : pa;
-            if (tl < lpr * 4 && pair >= 0)
-                stage_inputs(a, a.xrow ? a.xrow[pair] : pair / a.xdiv, tl & (lpr - 1), tl >> lpr_log2, sx[half], sm[half]);
-        }
-        __syncthreads();
-        for (; st < s_hi; st += MV_WARPS, r += MV_WARPS * rpw) {
-            const bool ok = r < a.R;
-            const int rn = r + MV_WARPS * rpw;
-            const bool more = st + MV_WARPS < s_hi && rn < a.R;
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-            u64 acc0 = 0ull, accu0 = 0ull, acc1 = 0ull, accu1 = 0ull;
-            {
-                Chunk k;
-                if (ok) k = chunk_take(slots[0]);
-                if (more) chunk_request(slots[0], wa, (size_t) rn * lpr + jc);   // the slot is free again: next step's streams
-                asm volatile("cp.async.commit_group;" ::: "memory");
-                if (ok) unit_chunk_dot(tab, kc, k, sx, sm, jc, two, acc0, acc1);
-            }
-            if (MODE == MODE_GU) {
-                Chunk k;
-                if (ok) k = chunk_take(slots[NM - 1]);
-                if (more) chunk_request(slots[NM - 1], wb, (size_t) rn * lpr + jc);
-                asm volatile("cp.async.commit_group;" ::: "memory");
-                if (ok) unit_chunk_dot(tab, kc, k, sx, sm, jc, two, accu0, accu1);
-            }
-            const float sca = slice_scale(__ldg(&wa->eb)), scb = slice_scale(__ldg(&wb->eb));
-            {
-                const float s0 = group_sum(pair_total(acc0), lpr) * sca;
-                float su0 = 0.0f;
-                if (MODE == MODE_GU) su0 = group_sum(pair_total(accu0), lpr) * scb;
-                if (ok && jc == 0) store_out<MODE>(a, pa, r, s0, su0);
-            }
-            if (two) {
-                const float s1 = group_sum(pair_total(acc1), lpr) * sca;
-                float su1 = 0.0f;
-                if (MODE == MODE_GU) su1 = group_sum(pair_total(accu1), lpr) * scb;
-                if (ok && jc == 0) store_out<MODE>(a, pb, r, s1, su1);
-            }
-        }
-    }
-}
-
 // ---- any K that is a multiple of 8, any alignment: one warp per (pair or dense, row), lanes over single blocks -------
 // P = 4 (SEED4P4) or 3 (SEED4: the exponent code rides in the nibble word, there is no code stream).
 template <int MODE, int P>
@@ -665,90 +598,56 @@ __global__ void __launch_bounds__(256) decode_kernel(WSlice w, KConst kc, int K,
     }
 }
 
-// ---- work units: pairs grouped two by two per slice -------------------------------------------------------------------
-// One block.  Pairs are counted per slice, a scan gives each slice its range of pairs and of units, pairs are placed
-// (in any order inside a slice: a pair's result does not depend on its partner) and every slice writes its units.
-constexpr int UNITS_MAX_PAIRS = 4096, UNITS_MAX_SLICES = 1024;
-__global__ void __launch_bounds__(1024) mv_units_kernel(const int32_t* __restrict__ sel, int max_pairs, const int32_t* __restrict__ count,
-                                                        int n_slices, int32_t* __restrict__ units, int32_t* __restrict__ n_units) {
-    __shared__ int cnt[UNITS_MAX_SLICES], poff[UNITS_MAX_SLICES], uoff[UNITS_MAX_SLICES], woff[UNITS_MAX_SLICES];
-    __shared__ int sorted[UNITS_MAX_PAIRS];
-    grid_dependents_go();
-    grid_dependency_wait();
-    const int tid = threadIdx.x;
-    const int P = count ? min(*count, max_pairs) : max_pairs;
-    cnt[tid] = 0;
-    __syncthreads();
-    for (int i = tid; i < P; i += 1024) atomicAdd(&cnt[sel[i]], 1);
-    __syncthreads();
-    const int n = tid < n_slices ? cnt[tid] : 0;
-    poff[tid] = n;
-    uoff[tid] = (n + 1) / 2;
-    woff[tid] = (n / 2) * UNIT_W2 + (n & 1) * UNIT_W1;
-    __syncthreads();
-    for (int o = 1; o < 1024; o <<= 1) {      // inclusive scans
-        const int a = tid >= o ? poff[tid - o] : 0, b = tid >= o ? uoff[tid - o] : 0, c = tid >= o ? woff[tid - o] : 0;
-        __syncthreads();
-        poff[tid] += a; uoff[tid] += b; woff[tid] += c;
-        __syncthreads();
-    }
-    const int p0 = poff[tid] - n, u0 = uoff[tid] - (n + 1) / 2, w0 = woff[tid] - ((n / 2) * UNIT_W2 + (n & 1) * UNIT_W1);
-    if (tid == 1023) *n_units = uoff[1023];
-    __syncthreads();
-    poff[tid] = p0;           // exclusive offsets; cnt becomes the placement cursor
-    cnt[tid] = 0;
-    __syncthreads();
-    for (int i = tid; i < P; i += 1024) {
-        const int e = sel[i];
-        sorted[poff[e] + atomicAdd(&cnt[e], 1)] = i;
-    }
-    __syncthreads();
-    for (int j = 0; 2 * j < n; ++j) {
-        const bool two = 2 * j + 1 < n;
-        int32_t* u = units + 4 * (u0 + j);
-        u[0] = sorted[p0 + 2 * j];
-        u[1] = two ? sorted[p0 + 2 * j + 1] : -1;
-        u[2] = w0 + j * UNIT_W2;     // units before it in this slice are all two-pair units
-        u[3] = 0;
-    }
-}
-
-static int g_mv_variant = 1;   // 1 (default): inputs in shared memory, 16 warps / SM; 0: inputs in registers, 8 warps / SM
-
 // ---- launch selection ---------------------------------------------------------------------------------------------------
 static int log2_floor(int v) { int l = 0; while ((2 << l) <= v) ++l; return l; }
 
-template <int MODE, int NT>
-static void launch_smemx(cudaStream_t s, const MvParams& a, int lpr_log2, int dense, int grid, size_t smem) {
-    static bool attr_set[16];   // per device
+template <typename K>
+static void allow_smem(K kernel, bool* done, size_t bytes) {      // once per device and kernel
     int dev = 0;
     cudaGetDevice(&dev);
-    if (!attr_set[dev & 15]) {
-        cudaFuncSetAttribute(mv_smemx_kernel<MODE, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin() - 4096);
-        attr_set[dev & 15] = true;
+    if (!done[dev & 15]) {
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) bytes);
+        done[dev & 15] = true;
     }
+}
+
+template <int MODE, int NT>
+static void launch_smemx(cudaStream_t s, const MvParams& a, int lpr_log2, int dense, int grid, size_t smem) {
+    static bool attr_set[16];
+    allow_smem(mv_smemx_kernel<MODE, NT>, attr_set, (size_t) max_smem_optin() - 4096);
     launch(mv_smemx_kernel<MODE, NT>, grid, MV_THREADS, smem, s, a, kconst(), lpr_log2, dense);
 }
 
 template <int MODE>
-static void launch_mv(cudaStream_t s, const MvParams& a, int T, int p_hint = 0) {
+static void launch_grp(cudaStream_t s, const MvParams& a, int lpr_log2, const RouteFuse& rf) {
+    static bool attr_set[16];
+    allow_smem(mv_grp_kernel<MODE>, attr_set, sizeof(GrpShared));
+    launch(mv_grp_kernel<MODE>, sm_count() * 2, MV_THREADS, sizeof(GrpShared), s, a, kconst(), lpr_log2, rf);
+}
+
+// The streams of a slice given by value (a dense call) can be checked on the host; slices in a device table are the
+// table builder's to check (nsl_wslice_table does).
+static bool slice_aligned(const WSlice& w) {
+    return aligned16(w.p[0]) && aligned16(w.p[1]) && ((uintptr_t) w.p[3] & 3u) == 0;
+}
+
+template <int MODE>
+static void launch_mv(cudaStream_t s, const MvParams& a, int T, const RouteFuse& rf = RouteFuse{}) {
     if (a.R <= 0 || a.P <= 0 || T <= 0) return;
     if (a.K <= 0 || a.K % 8) { set_error("seed mat-vec: K = %d is not a multiple of 8", a.K); return; }
     if (T > MV_MAXT) { set_error("seed mat-vec: %d tokens, at most %d", T, MV_MAXT); return; }
-    const int dense = a.sel == NULL, sms = sm_count();
+    const int dense = a.sel == NULL && rf.logits == NULL, sms = sm_count();
     const int ch = a.K / 64;
-    // The chunked kernels need whole chunks and 16-byte aligned rows of inputs; streams come 16-byte aligned from
-    // every allocator the callers use, and a row's chunks are contiguous, so only the inputs are checked here.
-    const bool chunked = a.K % 64 == 0 && aligned16(a.x) && a.xs % 4 == 0;
+    // The chunked kernels read whole chunks with 16-byte loads: rows of inputs and (checked where the slice is on the
+    // host) the streams must be aligned for that; anything else goes to the any-shape kernel.
+    const bool chunked = a.K % 64 == 0 && aligned16(a.x) && a.xs % (a.xbf16 ? 8 : 4) == 0 && (a.ws != NULL || slice_aligned(a.w0));
     const bool pow2 = ch > 0 && (ch & (ch - 1)) == 0;
-    if ((a.xrow || a.count || a.xbf16 || a.units) && !(chunked && pow2 && ch <= 32 && T == 1)) {
-        set_error("seed mat-vec: the row-index / device-count / bf16-input forms need K = 64 * 2^j <= 2048 (K = %d)", a.K);
+    if ((a.xrow || a.count || a.xbf16 || rf.logits) && !(chunked && pow2 && ch <= 32 && T == 1)) {
+        set_error("seed mat-vec: the routed / row-index / device-count / bf16-input forms need K = 64 * 2^j <= 2048 and aligned rows (K = %d)", a.K);
         return;
     }
     if (chunked && T == 1 && pow2 && ch <= 32) {
-        if (a.units) launch(mv_shx2_kernel<MODE>, sms * 2, MV_THREADS, 0, s, a, kconst(), log2_floor(ch));
-        else if (g_mv_variant == 1) launch(mv_shx_kernel<MODE>, sms * 2, MV_THREADS, 0, s, a, kconst(), log2_floor(ch));
-        else launch(mv_regx_kernel<MODE>, sms, MV_THREADS, 0, s, a, kconst(), log2_floor(ch));
+        launch_grp<MODE>(s, a, log2_floor(ch), rf);
         count_launch();
         return;
     }
@@ -796,7 +695,7 @@ void kc_mv(cudaStream_t s, int fmt, WSlice w, int K, int R, const float* x, int 
            const uint32_t* G) {
     if (fmt == MF_Q4) { launch_q4_mv(s, w, K, R, x, xs, y, ys, T, add); return; }   // the LM head's affine int4 (q4_head.cu)
     if (!seed_fmt(fmt, "kc_mv")) return;
-    MvParams a = {NULL, NULL, w, NULL, x, y, G, K, R, T, 1, xs, ys, add, 0, NULL, NULL, 0, NULL, NULL};
+    MvParams a = {NULL, NULL, w, NULL, x, y, G, K, R, T, 1, xs, ys, add, 0, NULL, NULL, 0};
     if (fmt == MF_SEED4) launch_mv3<MODE_ROUND>(s, a, T);
     else launch_mv<MODE_ROUND>(s, a, T);
 }
@@ -804,7 +703,7 @@ void kc_mv(cudaStream_t s, int fmt, WSlice w, int K, int R, const float* x, int 
 void kc_mv_sel(cudaStream_t s, int fmt, const WSlice* ws, int K, int R, const float* x, int xs, float* y, int ys,
                const int32_t* sel, int P, int xdiv, const uint32_t* G) {
     if (!seed_fmt(fmt, "kc_mv_sel")) return;
-    MvParams a = {ws, NULL, WSlice{}, sel, x, y, G, K, R, P, xdiv, xs, ys, 0, 0, NULL, NULL, 0, NULL, NULL};
+    MvParams a = {ws, NULL, WSlice{}, sel, x, y, G, K, R, P, xdiv, xs, ys, 0, 0, NULL, NULL, 0};
     if (fmt == MF_SEED4) launch_mv3<MODE_ROUND>(s, a, 1);
     else launch_mv<MODE_ROUND>(s, a, 1);
 }
@@ -812,64 +711,52 @@ void kc_mv_sel(cudaStream_t s, int fmt, const WSlice* ws, int K, int R, const fl
 void kc_mv_gu(cudaStream_t s, int fmt, const WSlice* wg, const WSlice* wu, int K, int R, const float* x, int xs, float* out,
               int ys, const int32_t* sel, int P, int xdiv, const uint32_t* G) {
     if (!seed_fmt(fmt, "kc_mv_gu")) return;
-    MvParams a = {wg, wu, WSlice{}, sel, x, out, G, K, R, P, xdiv, xs, ys, 0, 0, NULL, NULL, 0, NULL, NULL};
+    MvParams a = {wg, wu, WSlice{}, sel, x, out, G, K, R, P, xdiv, xs, ys, 0, 0, NULL, NULL, 0};
     if (fmt == MF_SEED4) launch_mv3<MODE_GU>(s, a, 1);
     else launch_mv<MODE_GU>(s, a, 1);
 }
 
 void nsl_mv_raw(cudaStream_t s, const WSlice* ws, int K, int R, const float* x, int xs, float* y, int ys,
                 const int32_t* sel, int P, int xdiv, const uint32_t* G) {
-    MvParams a = {sel ? ws : NULL, NULL, WSlice{}, sel, x, y, G, K, R, P, xdiv > 0 ? xdiv : 1, xs, ys, 0, 1, NULL, NULL, 0, NULL, NULL};
+    MvParams a = {sel ? ws : NULL, NULL, WSlice{}, sel, x, y, G, K, R, P, xdiv > 0 ? xdiv : 1, xs, ys, 0, 1, NULL, NULL, 0};
     if (!sel) a.w0 = *ws;   // dense: ws is a host pointer to the one slice
     launch_mv<MODE_ROUND>(s, a, sel ? 1 : P);
 }
 
 void nsl_mv_gu_raw(cudaStream_t s, const WSlice* wg, const WSlice* wu, int K, int R, const float* x, int xs, float* out,
                    int ys, const int32_t* sel, int P, int xdiv, const uint32_t* G) {
-    MvParams a = {wg, wu, WSlice{}, sel, x, out, G, K, R, P, xdiv, xs, ys, 0, 1, NULL, NULL, 0, NULL, NULL};
+    MvParams a = {wg, wu, WSlice{}, sel, x, out, G, K, R, P, xdiv, xs, ys, 0, 1, NULL, NULL, 0};
     launch_mv<MODE_GU>(s, a, 1);
+}
+
+// kc_mv_gu with the router folded into its prologue: T <= MV_MAXT rows of logits -> ind / wt [T][top_k] and
+// a [T * top_k][R]; pair t * top_k + j uses expert ind[t][j] and input row t.
+void nsl_mv_gu_routed(cudaStream_t s, const WSlice* wg, const WSlice* wu, int K, int R, const float* x, int xs, float* out, int ys,
+                      int n_exp, int top_k, const float* logits, int ld, int T, int32_t* ind, float* wt, int raw, const uint32_t* G) {
+    if (T <= 0) return;
+    if (T > MV_MAXT || n_exp < 1 || n_exp > 32 * ROUTE_PER_LANE || top_k < 1 || top_k > 32 || top_k > n_exp) {
+        set_error("nsl_mv_gu_routed: %d rows (at most %d), %d experts (at most %d), top %d (at most 32)", T, MV_MAXT, n_exp,
+                  32 * ROUTE_PER_LANE, top_k);
+        return;
+    }
+    MvParams a = {wg, wu, WSlice{}, NULL, x, out, G, K, R, T * top_k, top_k, xs, ys, 0, raw, NULL, NULL, 0};
+    const RouteFuse rf = {logits, ld, n_exp, top_k, T, ind, wt};
+    launch_mv<MODE_GU>(s, a, 1, rf);
 }
 
 // Expert-parallel forms: a compacted pair list whose length lives on the device.  Pair p uses slice sel[p] and input
 // row xrow[p] of x, which holds packed bf16 rows when x_bf16 is set; at most max_pairs pairs, *count of them valid.
 void nsl_mv_gu_rows(cudaStream_t s, const WSlice* wg, const WSlice* wu, int K, int R, const void* x, int xs, int x_bf16,
                     float* out, int ys, const int32_t* sel, const int32_t* xrow, int max_pairs, const int32_t* count,
-                    int expected_pairs, const uint32_t* G) {
-    MvParams a = {wg, wu, WSlice{}, sel, (const float*) x, out, G, K, R, max_pairs, 1, xs, ys, 0, 0, xrow, count, x_bf16, NULL, NULL};
-    launch_mv<MODE_GU>(s, a, 1, expected_pairs);
-}
-void nsl_mv_sel_rows(cudaStream_t s, const WSlice* ws, int K, int R, const float* x, int xs, float* y, int ys,
-                     const int32_t* sel, int max_pairs, const int32_t* count, int expected_pairs, const uint32_t* G) {
-    MvParams a = {ws, NULL, WSlice{}, sel, x, y, G, K, R, max_pairs, 1, xs, ys, 0, 0, NULL, count, 0};
-    launch_mv<MODE_ROUND>(s, a, 1, expected_pairs);
-}
-
-// Work units over a pair list (see include/nslm_kernels.h): the grouping kernel and the two mat-vec forms that use it.
-void nsl_mv_units(cudaStream_t s, const int32_t* sel, int max_pairs, const int32_t* count, int n_slices, int32_t* units,
-                  int32_t* n_units) {
-    if (max_pairs < 1 || max_pairs > UNITS_MAX_PAIRS || n_slices < 1 || n_slices > UNITS_MAX_SLICES) {
-        set_error("nsl_mv_units: %d pairs (at most %d) or %d slices (at most %d)", max_pairs, UNITS_MAX_PAIRS, n_slices, UNITS_MAX_SLICES);
-        return;
-    }
-    launch(mv_units_kernel, 1, 1024, 0, s, sel, max_pairs, count, n_slices, units, n_units);
-    count_launch();
-}
-
-void nsl_mv_gu_units(cudaStream_t s, const WSlice* wg, const WSlice* wu, int K, int R, const void* x, int xs, int x_bf16, float* out,
-                     int ys, const int32_t* sel, const int32_t* xrow, int xdiv, const int32_t* units, const int32_t* n_units,
-                     int max_pairs, int raw, const uint32_t* G) {
-    MvParams a = {wg, wu, WSlice{}, sel, (const float*) x, out, G, K, R, max_pairs, xdiv > 0 ? xdiv : 1, xs, ys, 0, raw, xrow, NULL, x_bf16,
-                  units, n_units};
+                    int raw, const uint32_t* G) {
+    MvParams a = {wg, wu, WSlice{}, sel, (const float*) x, out, G, K, R, max_pairs, 1, xs, ys, 0, raw, xrow, count, x_bf16};
     launch_mv<MODE_GU>(s, a, 1);
 }
-
-void nsl_mv_sel_units(cudaStream_t s, const WSlice* ws, int K, int R, const float* x, int xs, float* y, int ys, const int32_t* sel,
-                      const int32_t* units, const int32_t* n_units, int max_pairs, int raw, const uint32_t* G) {
-    MvParams a = {ws, NULL, WSlice{}, sel, x, y, G, K, R, max_pairs, 1, xs, ys, 0, raw, NULL, NULL, 0, units, n_units};
+void nsl_mv_sel_rows(cudaStream_t s, const WSlice* ws, int K, int R, const float* x, int xs, float* y, int ys,
+                     const int32_t* sel, int max_pairs, const int32_t* count, int raw, const uint32_t* G) {
+    MvParams a = {ws, NULL, WSlice{}, sel, x, y, G, K, R, max_pairs, 1, xs, ys, 0, raw, NULL, count, 0};
     launch_mv<MODE_ROUND>(s, a, 1);
 }
-
-void nsl_mv_set_variant(int v) { g_mv_variant = v; }
 
 void nsl_decode_f32(cudaStream_t s, WSlice w, int K, int R, float* out, const uint32_t* G) {
     if (K <= 0 || K % 8 || R <= 0) { if (K % 8) set_error("nsl_decode_f32: K = %d is not a multiple of 8", K); return; }

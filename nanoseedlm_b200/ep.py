@@ -249,13 +249,13 @@ class GraphedSteps:
 class CudaBackend:
     """The steps on the GPU through the C ABI; layer = this rank's experts (moe.DeviceLayer with e_loc experts)."""
 
-    def __init__(self, layer, expected_pairs=0):
+    def __init__(self, layer, rounding=True):
         from . import lib as L
         from .kernels import stream_table
         self.L, self.lib, self.layer = L, L.load(), layer
         self.device = torch.device("cuda", torch.cuda.current_device())
         self.G = stream_table()
-        self.expected_pairs = expected_pairs
+        self.raw = int(not rounding)      # 1: f32 throughout (no bf16 rounding points), for comparison with the CPU forward
 
     def setup(self, ep):
         T, k, d, ff = ep.N * ep.t_loc, ep.k, ep.d, self.layer.ff
@@ -265,8 +265,6 @@ class CudaBackend:
         self.sel, self.xrow, self.wsel = z(P, dt=torch.int32), z(P, dt=torch.int32), z(P)
         self.tok_off, self.count = z(T + 1, dt=torch.int32), z(1, dt=torch.int32)
         self.A, self.D = z(P, ff), z(P, d)
-        if not self.expected_pairs:
-            self.expected_pairs = max(1, P // ep.N)
 
     def set_layer(self, layer):
         self.layer = layer
@@ -299,9 +297,9 @@ class CudaBackend:
         try:
             lib.nsl_mv_gu_rows(s, lyr.gate.table.data_ptr(), lyr.up.table.data_ptr(), lyr.d, lyr.ff, base, ep.d, 1,
                                self.A.data_ptr(), lyr.ff, self.sel.data_ptr(), self.xrow.data_ptr(), P, self.count.data_ptr(),
-                               self.expected_pairs, self.G.data_ptr())
+                               self.raw, self.G.data_ptr())
             lib.nsl_mv_sel_rows(s, lyr.down.table.data_ptr(), lyr.ff, lyr.d, self.A.data_ptr(), lyr.ff, self.D.data_ptr(), lyr.d,
-                                self.sel.data_ptr(), P, self.count.data_ptr(), self.expected_pairs, self.G.data_ptr())
+                                self.sel.data_ptr(), P, self.count.data_ptr(), self.raw, self.G.data_ptr())
             if p2p:
                 lib.nsl_ep_p2p_combine(s, ep.win, self.D.data_ptr(), self.wsel.data_ptr(), self.tok_off.data_ptr(), ep.d)
             else:
@@ -317,7 +315,7 @@ class CudaBackend:
         """route_and_pack + p2p_dispatch as one kernel that stores straight into the windows."""
         lay = ep.lay
         self.lib.nsl_ep_p2p_route_dispatch(self._s(), ep.win, ep.E, ep.k, logits.data_ptr(), ep.E, x.data_ptr(), ep.d,
-                                           lay["ind_off"], lay["wt_off"])
+                                           lay["ind_off"], lay["wt_off"], self.ind.data_ptr(), self.wt.data_ptr())
 
     def reduce(self, ep):
         if ep.collectives == "p2p":

@@ -201,46 +201,35 @@ def kt_mv_gu(wg, wu, sel, xdiv, x):
     return ad.cpu().numpy()
 
 
-def kt_units(sel, n_slices):
-    """nsl_mv_units: the work-unit list of a pair list -> (units [n][4] as numpy, device tensors units / n_units)."""
-    seld = dev(np.asarray(sel, np.int32))
-    P = seld.numel()
-    units = torch.full((P, 4), -7, dtype=torch.int32, device="cuda")
-    n_units = torch.zeros(1, dtype=torch.int32, device="cuda")
-    L.load().nsl_mv_units(_stream(), _ptr(seld), P, None, n_slices, _ptr(units), _ptr(n_units))
+def kt_mv_gu_routed(wg, wu, logits, k, x, raw=False):
+    """nsl_mv_gu_routed: the router and the gate + up + SwiGLU mat-vec in one launch -> (a [T*k][R], ind, wt)."""
+    logits = np.asarray(logits, np.float32)
+    T, E = logits.shape
+    xd, ld = dev(np.asarray(x, np.float32).reshape(T, wg.K)), dev(logits)
+    ad = torch.zeros(T * k, wg.R, device="cuda")
+    ind = torch.zeros(T, k, dtype=torch.int32, device="cuda")
+    wt = torch.zeros(T, k, device="cuda")
+    L.load().nsl_mv_gu_routed(_stream(), _ptr(wg.table), _ptr(wu.table), wg.K, wg.R, _ptr(xd), wg.K, _ptr(ad), wg.R, E, k,
+                              _ptr(ld), E, T, _ptr(ind), _ptr(wt), int(raw), _ptr(stream_table()))
     _done()
-    return units.cpu().numpy()[:int(n_units.item())], units, n_units
+    return ad.cpu().numpy(), ind.cpu().numpy(), wt.cpu().numpy()
 
 
-def kt_mv_sel_units(w, sel, x, raw=False):
-    """kt_mv_sel (input row = pair) through work units: pairs that share a slice share its expansion."""
+def kt_mv_gu_rows(wg, wu, sel, xrow, x, bf16=False, count=None, raw=False):
+    """nsl_mv_gu_rows: pair p uses slice sel[p] and input row xrow[p]; bf16 packs the inputs first; count (optional) = the
+    number of valid pairs, read on the device."""
     sel = np.asarray(sel, np.int32)
     P = sel.size
-    _, units, n_units = kt_units(sel, w.S)
-    xd = dev(np.asarray(x, np.float32).reshape(-1, w.K))
-    yd = torch.zeros(P, w.R, device="cuda")
-    seld = dev(sel)
-    L.load().nsl_mv_sel_units(_stream(), _ptr(w.table), w.K, w.R, _ptr(xd), w.K, _ptr(yd), w.R, _ptr(seld), _ptr(units),
-                              _ptr(n_units), P, int(raw), _ptr(stream_table()))
-    _done()
-    return yd.cpu().numpy()
-
-
-def kt_mv_gu_units(wg, wu, sel, xdiv, x, xrow=None, bf16=False):
-    """kt_mv_gu through work units; xrow (optional) picks each pair's input row, bf16 packs the inputs first."""
-    sel = np.asarray(sel, np.int32)
-    P = sel.size
-    _, units, n_units = kt_units(sel, wg.S)
     xd = dev(np.asarray(x, np.float32).reshape(-1, wg.K))
     if bf16:
         packed = torch.zeros(xd.numel(), dtype=torch.int16, device="cuda")
         L.load().kc_pack_input_bf16(_stream(), _ptr(xd), _ptr(packed), xd.numel())
         xd = packed
     ad = torch.zeros(P, wg.R, device="cuda")
-    seld = dev(sel)
-    rowd = dev(np.asarray(xrow, np.int32)) if xrow is not None else None
-    L.load().nsl_mv_gu_units(_stream(), _ptr(wg.table), _ptr(wu.table), wg.K, wg.R, _ptr(xd), wg.K, int(bf16), _ptr(ad), wg.R,
-                             _ptr(seld), _ptr(rowd), xdiv, _ptr(units), _ptr(n_units), P, 0, _ptr(stream_table()))
+    seld, rowd = dev(sel), dev(np.asarray(xrow, np.int32))
+    cnt = dev(np.array([P if count is None else count], np.int32))
+    L.load().nsl_mv_gu_rows(_stream(), _ptr(wg.table), _ptr(wu.table), wg.K, wg.R, _ptr(xd), wg.K, int(bf16), _ptr(ad), wg.R,
+                            _ptr(seld), _ptr(rowd), P, _ptr(cnt), int(raw), _ptr(stream_table()))
     _done()
     return ad.cpu().numpy()
 

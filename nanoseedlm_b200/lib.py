@@ -111,15 +111,12 @@ PROTOTYPES = {
     "nsl_decode3_f32": (None, [_vp, WSlice, _i, _i, _vp, _vp]),
     "nsl_decode3_bf16": (None, [_vp, WSlice, _i, _i, _vp, _vp]),
     "nsl_mm_status": (_i, []),
-    "nsl_mv_set_variant": (None, [_i]),
     "nsl_stream_table": (None, [_vp]),
     "nsl_last_error": (C.c_char_p, []),
     "nsl_launch_count": (C.c_uint64, []),
     "nsl_sm_count": (_i, []),
     "nsl_dependent_launch": (None, [_i]),
-    "nsl_mv_units": (None, [_vp, _vp, _i, _vp, _i, _vp, _vp]),
-    "nsl_mv_gu_units": (None, [_vp, _vp, _vp, _i, _i, _vp, _i, _i, _vp, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _vp]),
-    "nsl_mv_sel_units": (None, [_vp, _vp, _i, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _vp]),
+    "nsl_mv_gu_routed": (None, [_vp, _vp, _vp, _i, _i, _vp, _i, _vp, _i, _i, _i, _vp, _i, _i, _vp, _vp, _i, _vp]),
     # include/nslm_moe.h
     "nsl_moe_create": (_vp, [_i, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "nsl_moe_destroy": (None, [_vp]),
@@ -156,7 +153,7 @@ PROTOTYPES = {
     "nsl_ep_p2p_dispatch": (None, [_vp, NslEpWindow, _vp]),
     "nsl_ep_p2p_wait_dispatch": (None, [_vp, NslEpWindow]),
     "nsl_ep_p2p_plan": (None, [_vp, NslEpWindow, C.c_uint64, C.c_uint64, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
-    "nsl_ep_p2p_route_dispatch": (None, [_vp, NslEpWindow, _i, _i, _vp, _i, _vp, _i, C.c_uint64, C.c_uint64]),
+    "nsl_ep_p2p_route_dispatch": (None, [_vp, NslEpWindow, _i, _i, _vp, _i, _vp, _i, C.c_uint64, C.c_uint64, _vp, _vp]),
     "nsl_ep_p2p_combine": (None, [_vp, NslEpWindow, _vp, _vp, _vp, _i]),
     "nsl_ep_p2p_reduce": (None, [_vp, NslEpWindow, _i, _vp]),
     "nsl_ep_p2p_status": (_i, [NslEpWindow]),

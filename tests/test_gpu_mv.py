@@ -146,42 +146,77 @@ def test_other_formats_are_refused_loudly(oracle):
     assert "format 2" in lib.last_error()
 
 
-def test_register_and_shared_memory_variants_are_bit_identical(oracle):
-    from nanoseedlm_b200 import kernels, lib
-    mats, w = weights(oracle, 3, 96, 2048, 7)
-    sel = [2, 0, 1, 2, 1, 0, 0]
-    x = oracle.normal(5, 4 * 2048, bf16=True).reshape(4, 2048)
-    outs = []
-    for v in (0, 1):
-        lib.load().nsl_mv_set_variant(v)
-        outs.append((kernels.kt_mv_sel(w, sel, 2, x), kernels.kt_mv_gu(w, w, sel, 2, x), kernels.kt_mv(w, x[0], 1)))
-    lib.load().nsl_mv_set_variant(1)
-    for a, b in zip(*outs):
-        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
-
-
-@pytest.mark.parametrize("R,K,S,P", [(96, 2048, 5, 23), (512, 2048, 12, 64), (2048, 512, 12, 64), (40, 64, 3, 9), (64, 256, 20, 20)])
-def test_work_units_share_an_expansion_and_change_nothing(oracle, R, K, S, P):
-    """Pairs grouped two by two per slice (one expansion for both): every pair's row is bit-identical to the ungrouped
-    call, for the gate+up form (f32 and packed bf16 inputs, with and without a row index) and the gather form."""
+@pytest.mark.parametrize("R,K,S,P", [(96, 2048, 5, 23), (512, 2048, 12, 64), (2048, 512, 12, 64), (40, 64, 3, 9), (64, 256, 20, 20),
+                                     (16, 128, 7, 1300)])
+def test_pairs_that_share_a_slice_share_its_expansion_and_change_nothing(oracle, R, K, S, P):
+    """The kernels sort a call's pairs by slice and expand a slice's rows once for up to four pairs (lists of more than 1024
+    pairs run ungrouped).  Every pair's row must equal the same pair computed ALONE, bit for bit, whatever pairs share
+    the call: for the gate+up form (f32 and packed bf16 inputs, input row by pair / xdiv or by a row index, a device-side
+    pair count) and the gather form (rounded and raw)."""
     from nanoseedlm_b200 import kernels
     mats, w = weights(oracle, S, R, K, 11 * R + K, ebs=tuple(-22 + (i % 5) for i in range(S)))
     _, w2 = weights(oracle, S, R, K, 13 * R + K, ebs=tuple(-21 + (i % 4) for i in range(S)))
     rng = np.random.default_rng(P)
     for sel in (rng.integers(0, S, P), np.zeros(P, np.int64) + (S - 1), np.arange(P) % S):
-        units, _, _ = kernels.kt_units(sel, S)
-        seen = sorted(int(p) for u in units for p in u[:2] if p >= 0)
-        assert seen == list(range(P))                                  # every pair in exactly one unit
-        assert all(u[1] < 0 or sel[u[0]] == sel[u[1]] for u in units)   # partners share the slice
-        counts = np.bincount(sel, minlength=S)
-        assert len(units) == int(((counts + 1) // 2).sum())
         xdiv = 4
         x = oracle.normal(31 + P, ((P + xdiv - 1) // xdiv) * K, bf16=True).reshape(-1, K)
-        assert np.array_equal(kernels.kt_mv_gu_units(w, w2, sel, xdiv, x), kernels.kt_mv_gu(w, w2, sel, xdiv, x))
+        sample = sorted(set(rng.integers(0, P, 12).tolist() + [0, P - 1]))
+        gu = kernels.kt_mv_gu(w, w2, sel, xdiv, x)
+        for p in sample:      # the pair alone: one pair, its slice, its input row
+            alone = kernels.kt_mv_gu(w, w2, [sel[p]], 1, x[p // xdiv])
+            assert np.array_equal(gu[p].view(np.uint32), alone[0].view(np.uint32)), (p, sel[p])
         xrow = rng.integers(0, x.shape[0], P)
         ref = kernels.kt_mv_gu(w, w2, sel, 1, x[xrow])
-        assert np.array_equal(kernels.kt_mv_gu_units(w, w2, sel, 1, x, xrow=xrow), ref)
-        assert np.array_equal(kernels.kt_mv_gu_units(w, w2, sel, 1, x, xrow=xrow, bf16=True), ref)   # inputs are bf16 values
+        assert np.array_equal(kernels.kt_mv_gu_rows(w, w2, sel, xrow, x), ref)
+        assert np.array_equal(kernels.kt_mv_gu_rows(w, w2, sel, xrow, x, bf16=True), ref)   # inputs are bf16 values
+        part = kernels.kt_mv_gu_rows(w, w2, sel, xrow, x, count=P // 2)                     # only the first P // 2 pairs are valid
+        assert np.array_equal(part[:P // 2], ref[:P // 2]) and not part[P // 2:].any()
         xp = oracle.normal(41 + P, P * K, bf16=True).reshape(P, K)
-        assert np.array_equal(kernels.kt_mv_sel_units(w, sel, xp), kernels.kt_mv_sel(w, sel, 1, xp))
-        assert np.array_equal(kernels.kt_mv_sel_units(w, sel, xp, raw=True), kernels.kt_mv_sel(w, sel, 1, xp, raw=True))
+        dn, dn_raw = kernels.kt_mv_sel(w, sel, 1, xp), kernels.kt_mv_sel(w, sel, 1, xp, raw=True)
+        for p in sample:
+            assert np.array_equal(dn[p], kernels.kt_mv_sel(w, [sel[p]], 1, xp[p])[0])
+            assert np.array_equal(dn_raw[p], kernels.kt_mv_sel(w, [sel[p]], 1, xp[p], raw=True)[0])
+
+
+@pytest.mark.parametrize("T,E,k,R,K", [(1, 128, 8, 64, 2048), (8, 128, 8, 64, 2048), (5, 512, 10, 48, 512), (3, 40, 1, 24, 256), (8, 1024, 32, 8, 64)])
+def test_router_folded_into_the_gate_up_kernel(oracle, T, E, k, R, K):
+    """nsl_mv_gu_routed = the router + kc_mv_gu in one launch: ids identical to the oracle's, weights and activations
+    identical to the two separate calls."""
+    from nanoseedlm_b200 import kernels
+    S = min(E, 24)      # experts draw their matrices from a pool (ids stay the router's)
+    pool, _ = weights(oracle, S, R, K, 17 * R + K)
+    pool2, _ = weights(oracle, S, R, K, 19 * R + K)
+    wg = kernels.SeedWeight.from_matrices([pool[e % S] for e in range(E)])
+    wu = kernels.SeedWeight.from_matrices([pool2[e % S] for e in range(E)])
+    logits = oracle.normal(7 * T + E, T * E).reshape(T, E)
+    x = oracle.normal(9 * T + E, T * K, bf16=True).reshape(T, K)
+    a, ind, wt = kernels.kt_mv_gu_routed(wg, wu, logits, k, x)
+    ri, rw = oracle.route(logits, k)
+    i2, w2 = kernels.kt_route(logits, k)
+    assert np.array_equal(ind, ri) and np.array_equal(ind, i2) and np.array_equal(wt, w2)
+    assert np.max(np.abs(wt - rw) / rw) < 1e-5
+    assert np.array_equal(a, kernels.kt_mv_gu(wg, wu, ind.ravel(), k, x))
+
+
+def test_misaligned_streams_of_a_dense_slice_take_the_any_shape_kernel(oracle):
+    """A dense call whose streams do not start on the boundaries the chunked kernels' 16-byte loads need (a slice cut out of
+    a larger buffer at an odd offset) is served by the any-shape kernel: same results as the aligned copy."""
+    import torch
+    from nanoseedlm_b200 import kernels, lib as L
+    mats, w = weights(oracle, 1, 40, 256, 3)
+    x = oracle.normal(77, 256, bf16=True)
+    want = kernels.kt_mv(w, x, 1, raw=True)
+    nb = 40 * 256 // 8
+    seeds = torch.zeros(nb + 8, dtype=torch.int16, device="cuda")
+    seeds[1:nb + 1] = w.seeds[0]                                   # two bytes off a 16-byte boundary
+    sl = w.slice(0)
+    sl.p[0] = seeds.data_ptr() + 2
+    xd, yd = kernels.dev(x.reshape(1, 256)), torch.zeros(1, 40, device="cuda")
+    one = (L.WSlice * 1)(sl)
+    import ctypes as C
+    L.load().nsl_mv_raw(None, C.cast(one, C.c_void_p), 256, 40, C.c_void_p(xd.data_ptr()), 256, C.c_void_p(yd.data_ptr()), 40, None, 1, 1,
+                        C.c_void_p(kernels.stream_table().data_ptr()))
+    torch.cuda.synchronize()
+    L.check()
+    y64, mag = oracle.matvec_f64(mats[0], x)
+    assert np.max(np.abs(yd.cpu().numpy()[0] - y64[0]) / mag[0]) < 2e-6 and np.max(np.abs(want[0] - y64[0]) / mag[0]) < 2e-6

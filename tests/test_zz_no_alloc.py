@@ -33,7 +33,8 @@ def test_two_calls_in_a_row_match_kc_bucket():
     from nanoseedlm_b200 import kernels
     rng = np.random.default_rng(5)
     cases = [(128, rng.integers(0, 128, 512 * 8)), (40, rng.integers(0, 40, 300) * rng.integers(0, 2, 300)),
-             (1024, rng.integers(0, 1024, 64 * 10))]
+             (1024, rng.integers(0, 1024, 64 * 10)), (1, np.zeros(200, np.int64)), (7, np.zeros(0, np.int64)),
+             (16, rng.integers(0, 16, 33))]      # also: one expert only, and an empty pair list (no tiles)
     for n, inds in cases:   # back to back: the second and third calls find the previous call's offsets in the array
         perm, tiles, nt = _noalloc(inds, n)
         rperm, rtiles, rnt = kernels.kt_bucket(inds, n)
