@@ -1,18 +1,27 @@
 #!/usr/bin/env python
-"""Benchmark of the seed-decode MoE expert layer (BASELINE.json config 1) on B200.
+"""Benchmark of the seed-decode MoE hot path on B200 (BASELINE.json: seed-decode MoE GEMV tokens/s and GB/s against the
+roofline at 1 / 2 / 4 / 8 GPUs, next to the CPU seed path timed on the same host).
 
-    python bench.py --gpus 1 --steps 200 --warmup 10              # this library (CUDA kernels behind the C ABI)
-    python bench.py --impl reference --steps 3 --warmup 1          # the CPU seed path on the host cores
+    python bench.py --gpus 1 --steps 2000 --warmup 10           # this library (CUDA kernels behind the C ABI)
+    python bench.py --impl reference --steps 3 --warmup 1        # the CPU seed path on the host cores
+    torchrun --nproc-per-node N ... bench.py --gpus N            # expert-parallel decode (config 3) on N GPUs
 
-A step is one pass of the hot path over one batch: router top-8 over 128 experts, the routed experts' gate + up +
-SwiGLU and down projections regenerated from their seeds, and the weighted combine, for M tokens (default 8, the
-multi-token-prediction verify batch; --tokens 1 or 4 give the other rows of config 1).  Steps rotate over enough
-independent synthetic layers that every step's packed streams come from HBM, not L2.
+N = 1.  The headline is BASELINE config 1 at M = 8 (the multi-token-prediction verify batch): a step = router top-8 over
+128 experts (in the prologue of the gate+up kernel), the routed experts' gate + up + SwiGLU and down projections
+regenerated from their seeds, one expansion per distinct expert, and the weighted combine.  Steps rotate over enough
+independent synthetic layers that every step's packed streams come from HBM, not L2.  The same JSON line carries
+`workloads` (config 0, config 1 at M = 1 and 4, config 2, the LM head, decode attention: time per step and roofline
+each) and `ep_base` = config 3 with all 512 experts on the one GPU, the base of the strong-scaling series that the N > 1
+lines continue.
 
-One JSON line is printed (rank 0).  value = tokens/s with inputs resident in HBM; e2e = the same through
-nsl_moe_forward_pinned with host buffers (H2D of the step's inputs from pinned memory, D2H of its output, every step);
-roofline = the dominant kernel (gate+up mat-vec) against the measured HBM copy peak; cpu_baseline = the CPU
-restatement of the reference's seed mat-vec timed on this host."""
+N > 1.  Config 3: 512 experts sharded over the ranks, 64 sequences x 1 token, top-10, dispatch and combine by the kernels
+themselves over NVLink peer memory.  Before the timed region one step on seeded inputs is compared with the one-GPU layer
+(`parity`).
+
+value = tokens/s with inputs resident in HBM (CUDA events, max over ranks); e2e = the same through the C host layer with
+HOST buffers (H2D of the step's inputs from pinned memory, D2H of its output, one step in flight); roofline = the dominant
+kernel against the measured HBM peak and against the logic-pipe floor that actually bounds it; cpu_baseline = the CPU
+restatement of the reference's seed mat-vec on the host cores, on the same bytes as one timed step."""
 import argparse
 import ctypes as C
 import json
@@ -29,7 +38,14 @@ sys.path.insert(0, ROOT)
 
 D, FF, E, TOPK = 2048, 512, 128, 8
 BYTES_PER_MATRIX = D * FF // 8 * 4 + D * FF // 16        # 589,824: seeds + coefficient words + exponent codes
-WEIGHTS_PER_TOKEN = TOPK * 3 * D * FF                      # 25,165,824
+BLOCKS_PER_MATRIX = D * FF // 8                           # 131,072 blocks of 8 weights
+ALU_FLOOR = 53 / 64        # clocks per block per SM: 53 logic-pipe operations per block, 64 logic lanes per SM and clock
+                           # (profiles/logic_pipe_rates.md)
+METRIC = "seed_decode_moe_gemv_tokens_per_s"
+# DRAM bytes per launch of the gate+up kernel from ncu (profiles/mv_grp_gate_up_config1_M8.md): per distinct expert
+# (gate + up streams) and the rest (activations, tables)
+NCU_TRAFFIC_PER_DISTINCT = 1.114e6
+NCU_TRAFFIC_FIXED = 0.9e6
 
 
 def measured_peaks():
@@ -37,6 +53,11 @@ def measured_peaks():
     if os.path.exists(path):
         return json.load(open(path)), "measured"
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+def bf16r(a):
+    a = np.ascontiguousarray(a, np.float32)
+    return (a.view(np.uint32) + 0x7FFF + ((a.view(np.uint32) >> 16) & 1) & 0xFFFF0000).view(np.float32)
 
 
 class ClockSampler:
@@ -76,18 +97,23 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
+# ---- the CPU path ---------------------------------------------------------------------------------------------------------
 class CpuMoe:
     """One MoE step on the host cores with the CPU seed kernels (the gcc restatement of nslm/lib_cpu_seed4.c) in their
     fastest form: the CPU-tiled layout, the rows that share an expert multiplied together (up to 8 per call, the
     kernel's limit), every routed expert's gate and up products in one parallel region over all host threads, then
-    every down product in a second one.  Experts draw their matrices from a pool of `pool` distinct ones."""
+    every down product in a second one.  experts: {id: (gate, up, down) oracle matrices}; ids outside it draw from a pool
+    of seeded matrices (timing only)."""
 
-    def __init__(self, n_exp, top_k, threads, pool=8):
+    def __init__(self, n_exp, top_k, threads, experts=None, pool=24):
         from oracle import binding as B
         self.B, self.n_exp, self.top_k, self.threads = B, n_exp, top_k, threads
-        self.gate = [B.Tiled(B.Matrix(FF, D, 300 + i)) for i in range(pool)]
-        self.up = [B.Tiled(B.Matrix(FF, D, 400 + i)) for i in range(pool)]
-        self.down = [B.Tiled(B.Matrix(D, FF, 500 + i)) for i in range(pool)]
+        self.own = {e: tuple(B.Tiled(m) for m in ms) for e, ms in (experts or {}).items()}
+        self.pool = None if experts else [(B.Tiled(B.Matrix(FF, D, 300 + i)), B.Tiled(B.Matrix(FF, D, 400 + i)),
+                                           B.Tiled(B.Matrix(D, FF, 500 + i))) for i in range(pool)]
+
+    def mats(self, e):
+        return self.own[e] if e in self.own else self.pool[e % len(self.pool)]
 
     def groups(self, logits):
         ind, wt = self.B.route(logits, self.top_k)
@@ -103,13 +129,13 @@ class CpuMoe:
 
     def run(self, x, groups):
         """The groups' share of the layer output; returns (out [M][D], pairs done)."""
-        B, P = self.B, len(self.gate)
+        B = self.B
         xs = [x[[t for t, _ in rows]] for _, rows in groups]
-        gu = B.tiled_jobs([(self.gate[e % P], xe) for (e, _), xe in zip(groups, xs)] +
-                          [(self.up[e % P], xe) for (e, _), xe in zip(groups, xs)], self.threads)
+        gu = B.tiled_jobs([(self.mats(e)[0], xe) for (e, _), xe in zip(groups, xs)] +
+                          [(self.mats(e)[1], xe) for (e, _), xe in zip(groups, xs)], self.threads)
         n = len(groups)
         act = [g / (1.0 + np.exp(-g)) * u for g, u in zip(gu[:n], gu[n:])]
-        dn = B.tiled_jobs([(self.down[e % P], a) for (e, _), a in zip(groups, act)], self.threads)
+        dn = B.tiled_jobs([(self.mats(e)[2], a) for (e, _), a in zip(groups, act)], self.threads)
         out = np.zeros_like(x)
         for (_, rows), y in zip(groups, dn):
             for i, (t, w) in enumerate(rows):
@@ -119,27 +145,71 @@ class CpuMoe:
 
 def cpu_inputs(M, n_exp, seed=99):
     rng = np.random.default_rng(seed)
-    return rng.standard_normal((M, D)).astype(np.float32), rng.standard_normal((M, n_exp)).astype(np.float32)
+    return bf16r(rng.standard_normal((M, D)).astype(np.float32)), rng.standard_normal((M, n_exp)).astype(np.float32)
 
 
-def cpu_baseline(threads, M, n_exp=E, top_k=TOPK, seconds=12.0):
-    """The CPU path on a bounded sample: whole steps of the same workload, repeated for about `seconds`."""
-    cpu = CpuMoe(n_exp, top_k, threads)
-    x, logits = cpu_inputs(M, n_exp)
+def host_experts(layer, ids):
+    """The streams of a device layer's experts `ids` copied back to the host as oracle matrices (the same bytes the GPU reads)."""
+    from oracle import binding as B
+    out = {}
+    for e in ids:
+        ms = []
+        for st, (R, K) in ((layer.gate, (FF, D)), (layer.up, (FF, D)), (layer.down, (D, FF))):
+            m = B.Matrix(R, K, 0, eb=st.eb[e])
+            m.seeds[:] = st.seeds[e].cpu().numpy().view(np.uint16)
+            m.coefs[:] = st.coefs[e].cpu().numpy().view(np.uint16)
+            m.codes[:] = st.codes[e].cpu().numpy()
+            ms.append(m)
+        out[e] = tuple(ms)
+    return out
+
+
+def cpu_baseline_cfg1(threads, M, layer=None, x=None, logits=None, gpu_out=None, seconds=12.0):
+    """The CPU path on a bounded sample: whole steps of the headline's workload, repeated for about `seconds`.  With a
+    device layer given, the CPU works on the SAME bytes as one of the GPU's timed steps (the routed experts' streams
+    copied back) and its output is compared with the GPU's."""
+    from oracle import binding as B
+    if x is None:
+        x, logits = cpu_inputs(M, E)
+    ind, _ = B.route(logits, TOPK)
+    ids = sorted(set(ind.ravel().tolist()))
+    cpu = CpuMoe(E, TOPK, threads, host_experts(layer, ids) if layer is not None else None)
     groups = cpu.groups(logits)
-    cpu.run(x, groups)   # warm-up
+    out, _ = cpu.run(x, groups)   # warm-up
     times, t_end = [], time.perf_counter() + seconds
     while len(times) < 3 or (time.perf_counter() < t_end and len(times) < 200):
         t0 = time.perf_counter()
         cpu.run(x, groups)
         times.append(time.perf_counter() - t0)
     dt = float(np.median(times))
-    distinct = len({e for e, _ in groups})
-    return {"value": M / dt, "unit": "tok/s", "cores": threads, "kind": "port", "ms_per_step": dt * 1e3,
-            "gweights_per_s": distinct * 3 * D * FF / dt / 1e9,
-            "sample": f"{len(times)} whole steps (median) of {M} rows x top-{top_k} of {n_exp} experts = {distinct} distinct experts x "
-                      f"(gate, up, down) on {threads} host threads: CPU-tiled layout, rows sharing an expert multiplied together; "
-                      "the reference's own kernel needs Clang, this is its gcc restatement (oracle/cpu_seed4_tiled.c)"}
+    res = {"value": M / dt, "unit": "tok/s", "cores": threads, "kind": "port", "ms_per_step": dt * 1e3,
+           "gweights_per_s": len(ids) * 3 * D * FF / dt / 1e9,
+           "sample": f"{len(times)} whole steps (median) of {M} rows x top-{TOPK} of {E} experts = {len(ids)} distinct experts x "
+                     f"(gate, up, down) on {threads} host threads, on the bytes of one of the GPU's timed steps: CPU-tiled layout, "
+                     "rows sharing an expert multiplied together; the reference's own kernel needs Clang, this is its gcc "
+                     "restatement (oracle/cpu_seed4_tiled.c)"}
+    if gpu_out is not None:
+        res["gpu_vs_cpu_max_rel"] = float(np.max(np.abs(gpu_out - out)) / np.max(np.abs(out)))
+    return res
+
+
+def cpu_cfg0_protocol():
+    """BASELINE config 0 on the host cores by the reference bench's protocol (harness/nslm-cpu-seed-bench.c:22, 46-49, 57-66):
+    N = 2048 x K = 4096, one token, threads 1 and all, best of 20 after a warm-up, CLOCK_MONOTONIC, nproc and the load
+    average printed, the largest error against the double-precision spec relative to sum |w x|."""
+    from oracle import binding as B
+    m = B.Matrix(2048, 4096, 42, eb=-22)
+    x = B.normal(43, 4096)
+    y64, mag = B.matvec_f64(m, x)
+    tiled = B.Tiled(m)
+    nproc = os.cpu_count() or 1
+    res = {"shape": "2048 x 4096, 1 token", "nproc": nproc, "loadavg": open("/proc/loadavg").read().split()[:3], "protocol": "best of 20 after one warm-up call",
+           "threads": {}}
+    for th in sorted({1, nproc}):
+        dt, y = tiled.time(x, th, 20)
+        res["threads"][str(th)] = {"ms": dt * 1e3, "gweights_per_s": 2048 * 4096 / dt / 1e9, "packed_gbs": 2048 * 4096 * 0.5625 / dt / 1e9,
+                                   "max_err_vs_f64_spec": float(np.max(np.abs(y[0] - y64[0]) / mag[0]))}
+    return res
 
 
 def run_reference(args, workload):
@@ -162,10 +232,10 @@ def run_reference(args, workload):
         done += cpu.run(x, [groups[(i * take + g) % len(groups)] for g in range(take)])[1]
     dt = (time.perf_counter() - t0) / args.steps
     value = M * (done / args.steps / pairs) / dt      # rows/s of whole steps at the sampled (row, expert) pair rate
-    cfg = ep_config(args.gpus, args.layers) if workload == "cfg3" else workload_config(M)
-    line = {"impl": "reference", "metric": "seed_decode_moe_gemv_tokens_per_s", "value": value, "unit": "tok/s",
+    cfg = ep_config(args.gpus) if workload == "cfg3" else workload_config(M)
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "tok/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
-            "higher_is_better": True, "scaling": "strong" if workload == "cfg3" else "weak", "vs_baseline": None,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic", "config": cfg,
             "cpu_baseline": {"value": value, "unit": "tok/s", "cores": threads, "kind": "port",
                              "sample": f"each step = {take} of the step's {len(groups)} (expert, <= 8 rows) groups "
@@ -176,54 +246,56 @@ def run_reference(args, workload):
     print(json.dumps(line))
 
 
-def workload_config(M, layers=None):
+def workload_config(M):
     which = "config 1: synthetic MoE expert layer at decode" if M <= 8 else "config 2: synthetic MoE prefill / continuous-batching grouped GEMM"
-    c = {"workload": f"BASELINE {which}, hidden {D}, {E} seed-encoded (SEED4P4) "
-                     f"SwiGLU experts of intermediate {FF}, softmax top-{TOPK}, M={M} tokens, all experts resident",
-         "tokens": M, "experts": E, "top_k": TOPK, "hidden": D, "intermediate": FF}
-    if layers:
-        c["l2_policy"] = (f"steps rotate over {layers} independent layers ({layers * E * 3 * BYTES_PER_MATRIX / 1e9:.1f} GB of "
-                          "packed streams, far larger than the 126 MB L2), so each step's experts are read from HBM")
-    return c
+    return {"workload": f"BASELINE {which}, hidden {D}, {E} seed-encoded (SEED4P4) "
+                        f"SwiGLU experts of intermediate {FF}, softmax top-{TOPK}, M={M} tokens, all experts resident",
+            "tokens": M, "experts": E, "top_k": TOPK, "hidden": D, "intermediate": FF}
 
 
-def run_ours(args):
-    import torch
-    import torch.distributed as dist
-    from nanoseedlm_b200 import lib as L, moe
+def l2_policy(layers, n_exp=E):
+    return (f"steps rotate over {layers} independent layers ({layers * n_exp * 3 * BYTES_PER_MATRIX / 1e9:.1f} GB of packed streams, "
+            "far larger than the 126 MB L2), so each step's experts are read from HBM")
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    lib = L.load()
-    M, K, W, NL = args.tokens, args.steps, max(args.warmup, 3), args.layers
-    gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
-    layers = [moe.DeviceLayer.random_on_device(D, FF, E, gen) for _ in range(NL)]
-    torch.cuda.synchronize()
-    m = moe.Moe(layers[0], TOPK, M)
-    m.set_dependent_launch(not args.no_dependent_launch)
 
-    # inputs: a pool of distinct batches (bf16-valued activations, N(0,1) logits), on the host and on the device
+# ---- config 1 / config 2: one GPU's MoE layer ---------------------------------------------------------------------------
+class Cfg1:
+    """The resident synthetic layers and input batches shared by the config-1 / config-2 measurements."""
+
+    def __init__(self, NL, rank=0):
+        import torch
+        from nanoseedlm_b200 import lib as L, moe
+        self.torch, self.L, self.moe, self.lib = torch, L, moe, L.load()
+        gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
+        self.layers = [moe.DeviceLayer.random_on_device(D, FF, E, gen) for _ in range(NL)]
+        self.NL, self.rank = NL, rank
+        self.stream = torch.cuda.Stream()
+        torch.cuda.synchronize()
+
+    def inputs(self, M, NB=16):
+        rng = np.random.default_rng(99 + self.rank + 1000 * M)
+        hx = bf16r(rng.standard_normal((NB, M, D)).astype(np.float32))
+        hl = rng.standard_normal((NB, M, E)).astype(np.float32)
+        distinct = [len(set(np.argsort(-hl[b], axis=1, kind="stable")[:, :TOPK].ravel().tolist())) for b in range(NB)]
+        return hx, hl, distinct
+
+
+def measure_layer(c, M, K, W, sample_clocks=True, with_e2e=True, dependent_launch=True):
+    """Config 1 (M <= 8) or config 2 (M = 512) on one GPU: tokens/s of whole steps (CUDA graph of `chunk` steps replayed),
+    the dominant kernel timed launch by launch, and the end-to-end forms."""
+    torch, L, lib, layers, NL, stream = c.torch, c.L, c.lib, c.layers, c.NL, c.stream
     NB = 16
-    rng = np.random.default_rng(99 + rank)
-    hx = rng.standard_normal((NB, M, D)).astype(np.float32)
-    hx = (hx.view(np.uint32) + 0x7FFF + ((hx.view(np.uint32) >> 16) & 1) & 0xFFFF0000).view(np.float32)
-    hl = rng.standard_normal((NB, M, E)).astype(np.float32)
+    hx, hl, distinct = c.inputs(M, NB)
     dx, dl = torch.from_numpy(hx).cuda(), torch.from_numpy(hl).cuda()
     dout = torch.zeros(M, D, device="cuda")
-    distinct = [len(set(np.argsort(-hl[b], axis=1, kind="stable")[:, :TOPK].ravel().tolist())) for b in range(NB)]
-
-    stream = torch.cuda.Stream()
-    peaks, peak_kind = measured_peaks()
+    m = c.moe.Moe(layers[0], TOPK, M)
+    m.set_dependent_launch(dependent_launch)
+    res = {"tokens": M}
 
     def enqueue(step, s):
         m.set_layer(layers[step % NL])
         m.forward_dev(dx[step % NB], dl[step % NB], dout, stream=s.cuda_stream)
 
-    # ---- value: inputs resident in HBM; the K steps are captured once as a CUDA graph and replayed ------------------
     with torch.cuda.stream(stream):
         for i in range(W):
             enqueue(i, stream)
@@ -239,158 +311,301 @@ def run_ours(args):
         launches = (lib.nsl_launch_count() - launches0) // chunk * K
         graph.replay()   # one untimed replay: graph upload
         stream.synchronize()
-        if world > 1:
-            dist.barrier()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with ClockSampler(local) as clocks:
-            e0.record(stream)
-            for _ in range(K // chunk):
-                graph.replay()
-            for i in range(K % chunk):
-                enqueue(W + i, stream)
-            e1.record(stream)
-            e1.synchronize()
-        if world > 1:
-            dist.barrier()
+        sampler = ClockSampler(torch.cuda.current_device()) if sample_clocks else None
+        if sampler:
+            sampler.__enter__()
+        e0.record(stream)
+        for _ in range(K // chunk):
+            graph.replay()
+        for i in range(K % chunk):
+            enqueue(W + i, stream)
+        e1.record(stream)
+        e1.synchronize()
+        if sampler:
+            sampler.__exit__()
+            res["clocks"] = sampler.summary()
         torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    ms_per_step = ms / K
-    value = world * M / (ms_per_step * 1e-3)
+    ms_per_step = e0.elapsed_time(e1) / K
+    res.update(ms_per_step=ms_per_step, value=M / (ms_per_step * 1e-3), gpu_launches=int(launches),
+               packed_gbs=sum(distinct[(W + i) % NB] for i in range(K)) / K * 3 * BYTES_PER_MATRIX / (ms_per_step * 1e-3) / 1e9)
 
-    # ---- roofline of the dominant kernel (gate+up mat-vec): CUDA events around each of its launches ------------------
+    # ---- the dominant kernel, CUDA events around each of its launches on the launching stream --------------------------
     G = m.G
-    A = torch.zeros(M * TOPK, FF, device="cuda")
-    ind = torch.zeros(M * TOPK, dtype=torch.int32, device="cuda")
-    wt = torch.zeros(M * TOPK, device="cuda")
-    perm = torch.zeros(M * TOPK, dtype=torch.int32, device="cuda")
-    tiles = torch.zeros((M * TOPK // 128 + E + 1) * 4, dtype=torch.int32, device="cuda")
+    P = M * TOPK
+    A = torch.zeros(P, FF, device="cuda")
+    ind = torch.zeros(P, dtype=torch.int32, device="cuda")
+    wt = torch.zeros(P, device="cuda")
+    perm = torch.zeros(P, dtype=torch.int32, device="cuda")
+    tiles = torch.zeros((P // 128 + E + 1) * 4, dtype=torch.int32, device="cuda")
     work = torch.zeros(2 * E + 3, dtype=torch.int32, device="cuda")
-    gu_ms, gu_bytes = 0.0, 0.0
     with torch.cuda.stream(stream):
         evs = []
-        KR = min(K, 400)   # launches of the dominant kernel timed one by one
+        KR = min(K, 400)
         for i in range(KR):
             lay, b = layers[(W + i) % NL], (W + i) % NB
-            lib.nsl_route(stream.cuda_stream, E, TOPK, dl[b].data_ptr(), E, ind.data_ptr(), wt.data_ptr(), M)
             if M > 8:
-                lib.kc_bucket(stream.cuda_stream, ind.data_ptr(), M * TOPK, E, perm.data_ptr(), tiles.data_ptr(), work.data_ptr())
+                lib.nsl_route(stream.cuda_stream, E, TOPK, dl[b].data_ptr(), E, ind.data_ptr(), wt.data_ptr(), M)
+                lib.kc_bucket(stream.cuda_stream, ind.data_ptr(), P, E, perm.data_ptr(), tiles.data_ptr(), work.data_ptr())
             a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a0.record(stream)
             if M > 8:
                 lib.kc_mm_grouped_dev(stream.cuda_stream, L.MF_SEED4P4, lay.gate.table.data_ptr(), D, FF, dx[b].data_ptr(), D,
-                                      A.data_ptr(), FF, TOPK, perm.data_ptr(), tiles.data_ptr(), work.data_ptr(),
-                                      M * TOPK // 128 + E, G.data_ptr())
+                                      A.data_ptr(), FF, TOPK, perm.data_ptr(), tiles.data_ptr(), work.data_ptr(), P // 128 + E, G.data_ptr())
             else:
-                lib.kc_mv_gu(stream.cuda_stream, L.MF_SEED4P4, lay.gate.table.data_ptr(), lay.up.table.data_ptr(), D, FF,
-                             dx[b].data_ptr(), D, A.data_ptr(), FF, ind.data_ptr(), M * TOPK, TOPK, G.data_ptr())
+                lib.nsl_mv_gu_routed(stream.cuda_stream, lay.gate.table.data_ptr(), lay.up.table.data_ptr(), D, FF, dx[b].data_ptr(), D,
+                                     A.data_ptr(), FF, E, TOPK, dl[b].data_ptr(), E, M, ind.data_ptr(), wt.data_ptr(), 0, G.data_ptr())
             a1.record(stream)
             evs.append((a0, a1, b))
         stream.synchronize()
-        for a0, a1, b in evs:
-            gu_ms += a0.elapsed_time(a1)
-            gu_bytes += distinct[b] * (1 if M > 8 else 2) * BYTES_PER_MATRIX + M * D * 4 + M * TOPK * FF * 4
-    gu_us = gu_ms * 1e3 / KR
-    achieved = gu_bytes / KR / (gu_us * 1e-6) / 1e9
+        k_ms = sum(a0.elapsed_time(a1) for a0, a1, _ in evs)
+        k_distinct = sum(distinct[b] for _, _, b in evs) / KR
+    k_us = k_ms * 1e3 / KR
+    res["kernel"] = {"us_per_launch": k_us, "distinct_experts_per_launch": k_distinct, "launches_timed": KR}
 
-    # ---- e2e: host buffers through the C host layer, H2D and D2H inside every step -----------------------------------
-    for i in range(W):
-        m.set_layer(layers[i % NL])
-        m.hx[:M], m.hlogits[:M] = hx[i % NB], hl[i % NB]
-        m.forward_pinned(M)
-    if world > 1:
-        dist.barrier()
-    KE = min(K, 2000)
-    t0 = time.perf_counter()
-    for i in range(KE):
-        m.set_layer(layers[(W + i) % NL])
-        m.hx[:M], m.hlogits[:M] = hx[(W + i) % NB], hl[(W + i) % NB]
-        m.forward_pinned(M)
-    e2e_sync_s = (time.perf_counter() - t0) / KE
-    # the same with two handles used alternately: step i + 1 is submitted (its H2D copies and launches) before the host
-    # waits for step i's output, so copies and launch latency hide under the other step's kernels
-    m2 = moe.Moe(layers[0], TOPK, M)
-    m2.set_dependent_launch(not args.no_dependent_launch)
-    ms, checksum = (m, m2), 0.0
+    # ---- e2e: host buffers through the C host layer, H2D and D2H inside every step -------------------------------------
+    if with_e2e:
+        for i in range(W):
+            m.set_layer(layers[i % NL])
+            m.hx[:M], m.hlogits[:M] = hx[i % NB], hl[i % NB]
+            m.forward_pinned(M)
+        KE = min(K, 2000)
+        t0 = time.perf_counter()
+        for i in range(KE):
+            m.set_layer(layers[(W + i) % NL])
+            m.hx[:M], m.hlogits[:M] = hx[(W + i) % NB], hl[(W + i) % NB]
+            m.forward_pinned(M)
+        e2e_sync_s = (time.perf_counter() - t0) / KE
+        # two independent batches on two handles used alternately: step i + 1 is submitted (its H2D copies and launches)
+        # before the host waits for step i's output.  Only independent batches can do this (a decoder's layer L + 1 needs
+        # layer L), so it is reported beside the headline, not as it.
+        m2 = c.moe.Moe(layers[0], TOPK, M)
+        m2.set_dependent_launch(dependent_launch)
+        ms, checksum = (m, m2), 0.0
 
-    def submit(i):
-        h = ms[i & 1]
-        h.set_layer(layers[(W + i) % NL])
-        h.hx[:M], h.hlogits[:M] = hx[(W + i) % NB], hl[(W + i) % NB]
-        h.submit_pinned(M)
+        def submit(i):
+            h = ms[i & 1]
+            h.set_layer(layers[(W + i) % NL])
+            h.hx[:M], h.hlogits[:M] = hx[(W + i) % NB], hl[(W + i) % NB]
+            h.submit_pinned(M)
 
-    for i in range(4):
-        submit(i)
-        ms[i & 1].wait()
-    t0 = time.perf_counter()
-    submit(0)
-    for i in range(1, KE):
-        submit(i)
-        ms[(i - 1) & 1].wait()
-        checksum += float(ms[(i - 1) & 1].hout[0, 0])     # the host reads every step's result
-    ms[(KE - 1) & 1].wait()
-    e2e_s = (time.perf_counter() - t0) / KE
-    if world > 1:
-        t = torch.tensor([e2e_s], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
+        for i in range(4):
+            submit(i)
+            ms[i & 1].wait()
+        t0 = time.perf_counter()
+        submit(0)
+        for i in range(1, KE):
+            submit(i)
+            ms[(i - 1) & 1].wait()
+            checksum += float(ms[(i - 1) & 1].hout[0, 0])     # the host reads every step's result
+        ms[(KE - 1) & 1].wait()
+        e2e_two_s = (time.perf_counter() - t0) / KE
+        m2.close()
+        res["e2e"] = {"value": M / e2e_sync_s, "unit": "tok/s", "h2d_bytes_per_step": M * D * 4 + M * E * 4, "d2h_bytes_per_step": M * D * 4,
+                      "ms_per_step": e2e_sync_s * 1e3, "steps_in_flight": 1,
+                      "two_independent_batches": {"value": M / e2e_two_s, "ms_per_step": e2e_two_s * 1e3}}
+    # one timed step's inputs and output, for the CPU baseline's comparison on the same bytes
+    m.set_layer(layers[0])
+    out0, _ = m.forward_host(hx[0], hl[0])
+    res["step0"] = (hx[0], hl[0], out0)
     L.check()
-
-    if rank == 0:
-        line = {"metric": "seed_decode_moe_gemv_tokens_per_s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": K,
-                "warmup": W, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-                "dtype": "f32", "data": "synthetic", "config": workload_config(M, NL),
-                "packed_gbs": world * sum(distinct[(W + i) % NB] for i in range(K)) / K * 3 * BYTES_PER_MATRIX / (ms_per_step * 1e-3) / 1e9,
-                "gpu_launches": int(launches), "clocks": clocks.summary(),
-                "e2e": {"value": world * M / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": M * D * 4 + M * E * 4,
-                        "d2h_bytes_per_step": M * D * 4, "ms_per_step": e2e_s * 1e3, "steps_in_flight": 2,
-                        "one_step_in_flight": {"value": world * M / e2e_sync_s, "ms_per_step": e2e_sync_s * 1e3}},
-                "roofline": {"bound": "hbm", "kernel": "mv_shx_kernel<gate+up> (kc_mv_gu)", "achieved": achieved, "peak": peaks["hbm_gbs"],
-                             "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_kind": peak_kind, "traffic": 57.5e6 if M == 8 else None,
-                             "us_per_launch": gu_us,
-                             "note": "the kernel is bound by the integer/logic pipe (LFSR expansion: 53 logic ops per 8 weights), "
-                                     "at about 65 % of that roofline; HBM traffic equals the algorithmic bytes (ncu, profiles/)"}}
-        if M <= 8 and line["clocks"].get("sm_mhz"):
-            # the second roofline of this kernel: the logic pipe.  Each (row, expert) pair expands gate and up once:
-            # 2 * FF * D / 8 blocks of 8 weights; an SM retires 64 logic lane-ops per clock and a block needs 53 of them
-            blocks = M * TOPK * 2 * FF * D // 8
-            clk = gu_us * 1e-6 * line["clocks"]["sm_mhz"] * 1e6 * lib.nsl_sm_count() / blocks
-            line["roofline"]["alu"] = {"blocks_per_launch": blocks, "clk_per_block_per_sm": clk, "floor_clk_per_block_per_sm": 53 / 64,
-                                       "frac": 53 / 64 / clk, "bytes_time_us": gu_bytes / KR / (peaks["hbm_gbs"] * 1e9) * 1e6,
-                                       "alu_floor_time_us": gu_us * 53 / 64 / clk}
-        if M > 8:   # prompt rows: the dominant kernel is the grouped tcgen05 GEMM (gate projection timed)
-            tf = 2.0 * M * TOPK * FF * D / (gu_us * 1e-6) / 1e12
-            line["roofline"] = {"bound": "tensor", "kernel": "seed_gemm_kernel<1> (kc_mm_grouped_dev, gate projection)", "achieved": tf,
-                                "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": tf / peaks["bf16_tflops"], "peak_kind": peak_kind,
-                                "traffic": None, "us_per_launch": gu_us, "packed_gbs": achieved,
-                                "note": "producer-bound: regenerating a weight tile costs ~100 instructions per 8 weights, the tensor "
-                                        "pipe idles by construction (ncu: sm__pipe_tensor_cycles_active 3 %)"}
-        if world == 1 and not args.no_cpu:
-            line["cpu_baseline"] = cpu_baseline(os.cpu_count() or 1, M)
-        print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
+    m.close()
+    return res
 
 
-EP_E, EP_K, EP_B = 512, 10, 64   # BASELINE config 3: 512 experts sharded over the ranks, 64 sequences x 1 token, top-10
+def alu_roofline(us, blocks, sm_mhz, sms):
+    """Clocks per expanded block per SM against the logic pipe's floor."""
+    clk = us * 1e-6 * sm_mhz * 1e6 * sms / blocks
+    return {"blocks_expanded_per_launch": blocks, "clk_per_block_per_sm": clk, "floor_clk_per_block_per_sm": ALU_FLOOR,
+            "frac": ALU_FLOOR / clk, "alu_floor_time_us": us * ALU_FLOOR / clk}
 
 
-def ep_config(world, layers):
+def layer_roofline(r, M, sm_mhz, sms, peaks, peak_kind):
+    """The roofline object of a config-1 / config-2 measurement: HBM fraction of the dominant kernel and, since the kernel
+    is bound by the integer / logic pipe, that pipe's floor (one expansion per DISTINCT expert)."""
+    k = r["kernel"]
+    mats = 1 if M > 8 else 2      # config 2 times the gate GEMM, config 1 the gate+up mat-vec
+    nbytes = k["distinct_experts_per_launch"] * mats * BYTES_PER_MATRIX + M * D * 4 + M * TOPK * FF * 4
+    achieved = nbytes / (k["us_per_launch"] * 1e-6) / 1e9
+    name = "seed_gemm_kernel (kc_mm_grouped_dev, gate projection)" if M > 8 else "mv_grp_kernel<gate+up> with the router in its prologue (nsl_mv_gu_routed)"
+    out = {"bound": "hbm", "kernel": name, "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+           "peak_kind": peak_kind, "us_per_launch": k["us_per_launch"], "algorithmic_bytes_per_launch": nbytes,
+           "traffic": (k["distinct_experts_per_launch"] * NCU_TRAFFIC_PER_DISTINCT + NCU_TRAFFIC_FIXED) if M <= 8 else None,
+           "traffic_source": "ncu dram bytes per launch at M = 8 (profiles/), scaled by the launch's distinct experts" if M <= 8 else None,
+           "note": "bound by the integer / logic pipe (LFSR expansion: 53 logic operations per 8 weights), not by HBM: see alu"}
+    if sm_mhz:
+        blocks = k["distinct_experts_per_launch"] * mats * BLOCKS_PER_MATRIX
+        out["alu"] = alu_roofline(k["us_per_launch"], blocks, sm_mhz, sms)
+        out["alu"]["bytes_time_us"] = nbytes / (peaks["hbm_gbs"] * 1e9) * 1e6
+        if M <= 8:
+            out["alu"]["frac_if_every_pair_expanded"] = out["alu"]["frac"] * M * TOPK / k["distinct_experts_per_launch"]
+        else:
+            tf = 2.0 * M * TOPK * FF * D / (k["us_per_launch"] * 1e-6) / 1e12
+            out["tensor"] = {"achieved_tflops": tf, "peak_tflops": peaks["bf16_tflops"], "frac": tf / peaks["bf16_tflops"],
+                             "note": "the tensor pipe idles by construction: regenerating a weight tile is the work"}
+    return out
+
+
+def measure_cfg0(K, W):
+    """BASELINE config 0: one dense seed mat-vec, 2048 outputs x 4096 inputs, one token (raw f32 output as the CPU path gives
+    it); 32 matrices rotated (151 MB) so that every launch reads HBM."""
+    import torch
+    from nanoseedlm_b200 import kernels, lib as L
+    lib = L.load()
+    R, Kd, NM = 2048, 4096, 32
+    gen = torch.Generator(device="cuda").manual_seed(42)
+    nb = R * Kd // 8
+    seeds = torch.randint(1, 65536, (NM, nb), generator=gen, device="cuda", dtype=torch.int32).to(torch.int16)
+    coefs = torch.randint(0, 65536, (NM, nb), generator=gen, device="cuda", dtype=torch.int32).to(torch.int16)
+    codes = torch.randint(0, 256, (NM, nb // 2), generator=gen, device="cuda", dtype=torch.int32).to(torch.uint8)
+    slices = []
+    for i in range(NM):
+        w = L.WSlice()
+        w.p[0], w.p[1], w.p[3], w.eb = seeds[i].data_ptr(), coefs[i].data_ptr(), codes[i].data_ptr(), -22
+        slices.append((L.WSlice * 1)(w))
+    x = torch.randn(1, Kd, generator=gen, device="cuda")
+    y = torch.zeros(1, R, device="cuda")
+    G = kernels.stream_table()
+    stream = torch.cuda.Stream()
+    torch.cuda.synchronize()
+
+    def step(i):
+        lib.nsl_mv_raw(stream.cuda_stream, C.cast(slices[i % NM], C.c_void_p), Kd, R, x.data_ptr(), Kd, y.data_ptr(), R, None, 1, 1, G.data_ptr())
+
+    with torch.cuda.stream(stream):
+        for i in range(W):
+            step(i)
+        stream.synchronize()
+        chunk = min(K, 256)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            for i in range(chunk):
+                step(i)
+        g.replay()
+        stream.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(max(1, K // chunk)):
+            g.replay()
+        e1.record(stream)
+        e1.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (max(1, K // chunk) * chunk)
+    L.check()
+    return {"us": us, "bytes": nb * 4 + nb // 2 + Kd * 4 + R * 4, "blocks": nb, "weights": R * Kd}
+
+
+LM_V, LM_D = 151936, 2048   # the LM head of the reference's Qwen-class model (affine int4, groups of 64)
+
+
+def measure_lmhead(T, K, W):
+    """The dense affine-int4 LM head (kc_mv with MF_Q4) + greedy arg-max, an HBM-bound kernel."""
+    import torch
+    from nanoseedlm_b200 import lib as L
+    lib = L.load()
+    NM = 4
+    gen = torch.Generator(device="cuda").manual_seed(77)
+    mats = []
+    for _ in range(NM):      # NM independent heads (0.7 GB), rotated so that every step reads HBM
+        codes = torch.randint(-2 ** 31, 2 ** 31 - 1, (LM_V, LM_D // 8), generator=gen, device="cuda", dtype=torch.int32)
+        sc = (torch.rand(LM_V, LM_D // 64, generator=gen, device="cuda") * 0.02 + 0.001).to(torch.bfloat16)
+        bi = (torch.rand(LM_V, LM_D // 64, generator=gen, device="cuda") * -0.2).to(torch.bfloat16)
+        w = L.WSlice()
+        w.p[0], w.p[1], w.p[2] = codes.data_ptr(), sc.data_ptr(), bi.data_ptr()
+        mats.append((w, codes, sc, bi))
+    x = torch.randn(T, LM_D, generator=gen, device="cuda").to(torch.bfloat16).float()
+    y = torch.zeros(T, LM_V, device="cuda")
+    tok = torch.zeros(T, dtype=torch.int32, device="cuda")
+    stream = torch.cuda.Stream()
+    s = C.c_void_p(stream.cuda_stream)
+
+    def step(i):
+        lib.kc_mv(s, L.MF_Q4, mats[i % NM][0], LM_D, LM_V, x.data_ptr(), LM_D, y.data_ptr(), LM_V, T, 0, None)
+        lib.kc_argmax(s, y.data_ptr(), tok.data_ptr(), LM_V, T)
+
+    torch.cuda.synchronize()
+    with torch.cuda.stream(stream):
+        for i in range(W):
+            step(i)
+        stream.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(K):
+            step(W + i)
+        e1.record(stream)
+        e1.synchronize()
+        ms = e0.elapsed_time(e1) / K
+        evs = []
+        for i in range(min(K, 50)):
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record(stream)
+            lib.kc_mv(s, L.MF_Q4, mats[i % NM][0], LM_D, LM_V, x.data_ptr(), LM_D, y.data_ptr(), LM_V, T, 0, None)
+            a1.record(stream)
+            evs.append((a0, a1))
+        stream.synchronize()
+        mv_us = sum(a.elapsed_time(b) for a, b in evs) / len(evs) * 1e3
+    L.check()
+    nbytes = LM_V * LM_D // 2 + 2 * LM_V * (LM_D // 64) * 2 + T * LM_D * 4 + T * LM_V * 4
+    return {"ms_per_step": ms, "tokens": T, "mv_us": mv_us, "bytes": nbytes}
+
+
+def measure_attn(K, W):
+    """Decode attention of BASELINE config 4's shape (GQA 16 query / 2 KV heads of 128, BF16 cache of 4096 positions, 32
+    sequences = 134 MB of K and V per layer), an HBM-bound kernel; 3 layers rotated."""
+    import torch
+    from nanoseedlm_b200 import lib as L
+    lib = L.load()
+    NH, NKV, CTX, NSEQ, NS, NL = 16, 2, 4096, 32, 32, 3      # 32 splits: the reference host's choice for 32 rows of 4096 keys
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    caches = [(torch.randn(NSEQ * CTX, NKV, 128, generator=gen, device="cuda").to(torch.bfloat16),
+               torch.randn(NSEQ * CTX, NKV, 128, generator=gen, device="cuda").to(torch.bfloat16)) for _ in range(NL)]
+    q = torch.randn(NSEQ, NH, 128, generator=gen, device="cuda").to(torch.bfloat16).float()
+    g = torch.randn(NSEQ, NH, 128, generator=gen, device="cuda").to(torch.bfloat16).float()
+    o = torch.zeros(NSEQ, NH, 128, device="cuda")
+    part = torch.zeros(NSEQ * NH * NS * 130, device="cuda")
+    ri = (L.RowInfo * NSEQ)()
+    for t in range(NSEQ):
+        ri[t].pos, ri[t].kv0 = CTX - 1, t * CTX
+    rid = torch.empty(NSEQ * 16, dtype=torch.uint8, device="cuda")
+    rid.copy_(torch.frombuffer(bytearray(bytes(ri)), dtype=torch.uint8))
+    a = L.AttnArgs(NH, NKV, CTX // NS, NS, float(1 / np.sqrt(128.0)))
+    views = []
+    for kc, vc in caches:
+        kv = L.KvView()
+        kv.a.k, kv.a.v, kv.nv, kv.fmt = kc.data_ptr(), vc.data_ptr(), NSEQ * CTX, 0
+        views.append(kv)
+    stream = torch.cuda.Stream()
+    s = C.c_void_p(stream.cuda_stream)
+    torch.cuda.synchronize()
+    with torch.cuda.stream(stream):
+        for i in range(W):
+            lib.kc_attn(s, a, q.data_ptr(), views[i % NL], rid.data_ptr(), part.data_ptr(), g.data_ptr(), o.data_ptr(), NSEQ)
+        stream.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(K):
+            lib.kc_attn(s, a, q.data_ptr(), views[(W + i) % NL], rid.data_ptr(), part.data_ptr(), g.data_ptr(), o.data_ptr(), NSEQ)
+        e1.record(stream)
+        e1.synchronize()
+        ms = e0.elapsed_time(e1) / K
+    L.check()
+    return {"ms_per_step": ms, "tokens": NSEQ, "bytes": 2 * NSEQ * CTX * NKV * 128 * 2 + 3 * NSEQ * NH * 128 * 4}
+
+
+# ---- config 3: expert-parallel decode ---------------------------------------------------------------------------------------
+EP_E, EP_K, EP_B = 512, 10, 64   # BASELINE config 3: 512 routed experts sharded over the ranks, 64 sequences x 1 token, top-10
+
+
+def ep_config(world):
     return {"workload": f"BASELINE config 3: expert-parallel synthetic MoE decode, {EP_E} seed-encoded experts (hidden {D}, "
                         f"intermediate {FF}) sharded evenly over {world} GPU(s), {EP_B} sequences x 1 token, top-{EP_K}, "
                         "dispatch of bf16 rows and combine of f32 partial sums by the kernels themselves over NVLink peer memory "
                         "(--ep-collectives a2a: NCCL all-to-alls)",
-            "tokens": EP_B, "experts": EP_E, "top_k": EP_K, "hidden": D, "intermediate": FF, "parallelism": f"ep{world}",
-            "l2_policy": f"steps rotate over {layers} independent layers per rank ({layers * EP_E // world * 3 * BYTES_PER_MATRIX / 1e9:.2f} GB "
-                         "of packed streams per GPU), larger than the 126 MB L2"}
+            "tokens": EP_B, "experts": EP_E, "top_k": EP_K, "hidden": D, "intermediate": FF, "parallelism": f"ep{world}"}
 
 
-def run_ep(args):
-    """Config 3 at any N (N = 1: all experts on one GPU, the base of the strong-scaling series)."""
+def measure_ep(args, K, W, quiet_clocks=False):
+    """Config 3 at any N (N = 1: all experts on one GPU, the base of the strong-scaling series).  Returns rank 0's result."""
     import torch
     import torch.distributed as dist
     from nanoseedlm_b200 import ep, lib as L, moe
@@ -398,18 +613,14 @@ def run_ep(args):
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     lib = L.load()
-    K, W = args.steps, max(args.warmup, 3)
     e_loc, t_loc = EP_E // world, EP_B // world
     NL = max(2, min(args.layers, int(6e9 // (e_loc * 3 * BYTES_PER_MATRIX))))
     mirror = bool(args.ep_mirror) and world % 2 == 0 and args.ep_collectives == "p2p"
 
-    def experts_of(r):      # rank r's experts of every layer: the same bytes on whichever rank generates them
+    def experts_of(r, n_layers=NL):      # rank r's experts of every layer: the same bytes on whichever rank generates them
         g = torch.Generator(device="cuda").manual_seed(4321 + r)
-        return [moe.DeviceLayer.random_on_device(D, FF, e_loc, g) for _ in range(NL)]
+        return [moe.DeviceLayer.random_on_device(D, FF, e_loc, g) for _ in range(n_layers)]
 
     layers = experts_of(rank)
     if mirror:              # this rank also holds its partner's experts (own first, then the partner's)
@@ -417,10 +628,11 @@ def run_ep(args):
     be = ep.CudaBackend(layers[0])
     epl = ep.ExpertParallelMoe(be, D, EP_K, EP_E, t_loc, collectives=args.ep_collectives, mirror=mirror)
     NB = 8
-    rng = np.random.default_rng(7 + rank)
-    hx = rng.standard_normal((NB, t_loc, D)).astype(np.float32)
-    hx = (hx.view(np.uint32) + 0x7FFF + ((hx.view(np.uint32) >> 16) & 1) & 0xFFFF0000).view(np.float32)
-    hl = rng.standard_normal((NB, t_loc, EP_E)).astype(np.float32)
+    rng = np.random.default_rng(7)      # the whole batch on every rank; a rank takes its rows
+    gx = bf16r(rng.standard_normal((NB, EP_B, D)).astype(np.float32))
+    gl = rng.standard_normal((NB, EP_B, EP_E)).astype(np.float32)
+    rows = slice(rank * t_loc, (rank + 1) * t_loc)
+    hx, hl = np.ascontiguousarray(gx[:, rows]), np.ascontiguousarray(gl[:, rows])
     dx, dl = torch.from_numpy(hx).cuda(), torch.from_numpy(hl).cuda()
     px, pl = torch.from_numpy(hx).pin_memory(), torch.from_numpy(hl).pin_memory()
     pout = torch.zeros(t_loc, D).pin_memory()
@@ -430,14 +642,41 @@ def run_ep(args):
 
     def one(i):
         be.set_layer(layers[i % NL])
-        epl.step(dx[i % NB], dl[i % NB])
+        return epl.step(dx[i % NB], dl[i % NB])
+
+    # ---- parity, before anything is timed: one step on batch 0 and layer 0 against the ONE-GPU layer over all 512 experts
+    # (rank 0 regenerates every rank's experts of layer 0 from their seeds and runs the plain mat-vec path on all 64 rows)
+    parity = None
+    with torch.cuda.stream(stream):
+        mine = one(0).clone()
+        stream.synchronize()
+    if world > 1:
+        allout = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(allout, mine)
+        got = torch.cat(allout).cpu().numpy()
+    else:
+        got = mine.cpu().numpy()
+    if rank == 0:
+        whole = layers[0] if world == 1 and not mirror else None
+        if whole is None:
+            parts = [experts_of(r, 1)[0] for r in range(world)]
+            whole = parts[0]
+            for p in parts[1:]:
+                whole = moe.DeviceLayer.concat(whole, p)
+        m1 = moe.Moe(whole, EP_K, EP_B)
+        m1.set_grouped_min_tokens(10 ** 6)
+        want, _ = m1.forward_host(gx[0], gl[0])
+        m1.close()
+        del whole
+        rel = float(np.max(np.abs(got - want)) / np.max(np.abs(want)))
+        parity = {"checked": True, "max_rel": rel, "bar": 1e-5, "against": "the one-GPU MoE layer (all 512 experts, plain mat-vec path) on the same "
+                  "seeded batch and layer; the partial sums are added per rank first, so the order of the f32 sums differs"}
+    torch.cuda.empty_cache()
 
     with torch.cuda.stream(stream):
         for i in range(W):
             one(i)
         stream.synchronize()
-        # one step = 6 kernels of this library with the peer-memory exchange (9 kernels + 2 collective calls otherwise); with
-        # --no-graph every launch is issued directly, else the kernels replay as CUDA graphs (see ep.GraphedSteps)
         launches0 = lib.nsl_launch_count()
         one(W)
         stream.synchronize()
@@ -477,6 +716,7 @@ def run_ep(args):
             sx.copy_(px[(W + i) % NB], non_blocking=True); sl.copy_(pl[(W + i) % NB], non_blocking=True)
             be.set_layer(layers[(W + i) % NL]); pout.copy_(epl.step(sx, sl), non_blocking=True); stream.synchronize()
         e2e_s = (time.perf_counter() - t0) / KE
+    pairs = int(be.count.item())
     if world > 1:
         t = torch.tensor([ms, e2e_s], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -491,172 +731,37 @@ def run_ep(args):
             p2p_status = int(t.item())
             dist.barrier()
         epl.window.close()
-        if p2p_status:
-            raise SystemExit(f"expert-parallel p2p exchange: a wait ran out (status {p2p_status}); the timing is void")
+    del layers, be, epl
+    torch.cuda.empty_cache()
+    if p2p_status:
+        raise SystemExit(f"expert-parallel p2p exchange: a wait ran out (status {p2p_status}); the timing is void")
     ms_per_step = ms / K
-    if rank == 0:
-        peaks, peak_kind = measured_peaks()
-        line = {"metric": "seed_decode_moe_gemv_tokens_per_s", "value": EP_B / (ms_per_step * 1e-3), "unit": "tok/s",
-                "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_per_step, "higher_is_better": True,
-                "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": ep_config(world, NL),
-                "gpu_launches": int(launches), "cuda_graph": captured, "collectives": args.ep_collectives, "mirrored_ranks": mirror,
-                "clocks": clocks.summary(),
-                "e2e": {"value": EP_B / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": t_loc * D * 4 + t_loc * EP_E * 4,
-                        "d2h_bytes_per_step": t_loc * D * 4, "ms_per_step": e2e_s * 1e3},
-                "roofline": None}
-        # the whole step against the packed-bytes roofline: the experts a step touches, in expectation over the routing
-        # (E (1 - (1 - k/E)^B) distinct experts of 3 matrices each), read once by whichever rank owns them
-        distinct = EP_E * (1.0 - (1.0 - EP_K / EP_E) ** EP_B)
-        step_bytes = distinct * 3 * BYTES_PER_MATRIX
-        gbs = step_bytes / (ms_per_step * 1e-3) / 1e9
-        line["roofline"] = {"bound": "hbm", "kernel": "the step's seed mat-vecs (mv_shx_kernel: gate+up and down over the ranks' pairs)",
-                            "achieved": gbs, "peak": peaks["hbm_gbs"] * world, "unit": "GB/s", "frac": gbs / (peaks["hbm_gbs"] * world),
-                            "peak_kind": peak_kind, "traffic": None, "expected_distinct_experts": distinct,
-                            "note": "whole step (mat-vecs + exchange) over the aggregate HBM peak of the ranks; the kernels are bound by "
-                                    "the logic pipe, see the 1-GPU config-1 line for the per-kernel roofline"}
-        print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
-
-
-LM_V, LM_D = 151936, 2048   # the LM head of the reference's Qwen-class model (affine int4, groups of 64)
-
-
-def run_lmhead(args):
-    """Not the headline: the dense affine-int4 LM head (kc_mv with MF_Q4) + greedy arg-max, an HBM-bound kernel."""
-    import torch
-    from nanoseedlm_b200 import lib as L
-    lib = L.load()
-    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
-    T, K, W, NM = min(args.tokens, 8), args.steps, max(args.warmup, 3), 4
-    lib.nsl_q4_set_variant(int(os.environ.get("NSL_Q4_VARIANT", "1")))
-    gen = torch.Generator(device="cuda").manual_seed(77)
-    mats = []
-    for _ in range(NM):      # NM independent heads (0.7 GB), rotated so that every step reads HBM
-        codes = torch.randint(-2 ** 31, 2 ** 31 - 1, (LM_V, LM_D // 8), generator=gen, device="cuda", dtype=torch.int32)
-        sc = (torch.rand(LM_V, LM_D // 64, generator=gen, device="cuda") * 0.02 + 0.001).to(torch.bfloat16)
-        bi = (torch.rand(LM_V, LM_D // 64, generator=gen, device="cuda") * -0.2).to(torch.bfloat16)
-        w = L.WSlice()
-        w.p[0], w.p[1], w.p[2] = codes.data_ptr(), sc.data_ptr(), bi.data_ptr()
-        mats.append((w, codes, sc, bi))
-    x = torch.randn(T, LM_D, generator=gen, device="cuda").to(torch.bfloat16).float()
-    y = torch.zeros(T, LM_V, device="cuda")
-    tok = torch.zeros(T, dtype=torch.int32, device="cuda")
-    stream = torch.cuda.Stream()
-    s = C.c_void_p(stream.cuda_stream)
-
-    def step(i):
-        lib.kc_mv(s, L.MF_Q4, mats[i % NM][0], LM_D, LM_V, x.data_ptr(), LM_D, y.data_ptr(), LM_V, T, 0, None)
-        lib.kc_argmax(s, y.data_ptr(), tok.data_ptr(), LM_V, T)
-
-    with torch.cuda.stream(stream):
-        for i in range(W):
-            step(i)
-        stream.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with ClockSampler(torch.cuda.current_device()) as clocks:
-            e0.record(stream)
-            for i in range(K):
-                step(W + i)
-            e1.record(stream)
-            e1.synchronize()
-        ms = e0.elapsed_time(e1) / K
-        evs = []
-        for i in range(min(K, 50)):
-            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a0.record(stream)
-            lib.kc_mv(s, L.MF_Q4, mats[i % NM][0], LM_D, LM_V, x.data_ptr(), LM_D, y.data_ptr(), LM_V, T, 0, None)
-            a1.record(stream)
-            evs.append((a0, a1))
-        stream.synchronize()
-        mv_us = sum(a.elapsed_time(b) for a, b in evs) / len(evs) * 1e3
-    L.check()
-    peaks, kind = measured_peaks()
-    nbytes = LM_V * LM_D // 2 + 2 * LM_V * (LM_D // 64) * 2 + T * LM_D * 4 + T * LM_V * 4
-    gbs = nbytes / (mv_us * 1e-6) / 1e9
-    print(json.dumps({"metric": "lm_head_q4_tokens_per_s", "value": T / (ms * 1e-3), "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W,
-                      "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 x int4 -> f32",
-                      "data": "synthetic", "gpu_launches": 2 * K, "clocks": clocks.summary(),
-                      "config": {"workload": f"dense affine-int4 LM head {LM_V} x {LM_D} (groups of 64) + greedy arg-max, {T} tokens; "
-                                             f"{NM} heads rotated (0.7 GB) so that every step reads HBM", "tokens": T},
-                      "roofline": {"bound": "hbm", "kernel": "q4_mv_kernel (kc_mv, MF_Q4)", "achieved": gbs, "peak": peaks["hbm_gbs"],
-                                   "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"], "peak_kind": kind, "traffic": None,
-                                   "us_per_launch": mv_us, "bytes_per_launch": nbytes}}))
-
-
-ATTN_FORMS = {0: "attn_split_kernel", 1: "attn_flat_mma_kernel<2>", 2: "attn_split_mma_kernel<2>", 3: "attn_flat_mma_kernel<3>",
-              4: "attn_flat_mma_kernel<2>, two blocks an SM", 5: "attn_flat_mma_kernel<2, bulk copies>",
-              6: "attn_flat_mma_kernel<3, bulk copies>", 7: "attn_flat_mma_kernel<2, two warps a ring>"}
-
-
-def run_attn(args):
-    """Not the headline: decode attention of the reference's config 4 (GQA 16 query / 2 KV heads of 128, BF16 cache of 4096
-    positions, 32 sequences = 134 MB of K and V per layer), an HBM-bound kernel."""
-    import torch
-    from nanoseedlm_b200 import lib as L
-    lib = L.load()
-    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
-    NH, NKV, CTX, NSEQ, NS, NL = 16, 2, 4096, 32, int(os.environ.get("NSL_ATTN_SPLITS", "32")), 3      # 32 splits: the reference host's choice for 32 rows of 4096 keys
-    variant = int(os.environ.get("NSL_ATTN_VARIANT", "1"))
-    lib.nsl_attn_set_variant(variant)
-    K, W = args.steps, max(args.warmup, 3)
-    gen = torch.Generator(device="cuda").manual_seed(5)
-    q8 = os.environ.get("NSL_ATTN_KV", "bf16") == "q8"      # the 8-bit cache: int8 codes and one f32 scale per (row, KV head)
-    if q8:
-        caches = [(torch.randint(-127, 128, (NSEQ * CTX, NKV, 128), generator=gen, device="cuda", dtype=torch.int8),
-                   torch.randint(-127, 128, (NSEQ * CTX, NKV, 128), generator=gen, device="cuda", dtype=torch.int8)) for _ in range(NL)]
-        scales = [(torch.rand(NSEQ * CTX, NKV, generator=gen, device="cuda") / 64 + 0.01,
-                   torch.rand(NSEQ * CTX, NKV, generator=gen, device="cuda") / 64 + 0.01) for _ in range(NL)]
-    else:
-        caches = [(torch.randn(NSEQ * CTX, NKV, 128, generator=gen, device="cuda").to(torch.bfloat16),
-                   torch.randn(NSEQ * CTX, NKV, 128, generator=gen, device="cuda").to(torch.bfloat16)) for _ in range(NL)]
-    q = torch.randn(NSEQ, NH, 128, generator=gen, device="cuda").to(torch.bfloat16).float()
-    g = torch.randn(NSEQ, NH, 128, generator=gen, device="cuda").to(torch.bfloat16).float()
-    o = torch.zeros(NSEQ, NH, 128, device="cuda")
-    part = torch.zeros(NSEQ * NH * NS * 130, device="cuda")
-    ri = (L.RowInfo * NSEQ)()
-    for t in range(NSEQ):
-        ri[t].pos, ri[t].kv0 = CTX - 1, t * CTX
-    rid = torch.empty(NSEQ * 16, dtype=torch.uint8, device="cuda")
-    rid.copy_(torch.frombuffer(bytearray(bytes(ri)), dtype=torch.uint8))
-    a = L.AttnArgs(NH, NKV, CTX // NS, NS, float(1 / np.sqrt(128.0)))
-    views = []
-    for i, (kc, vc) in enumerate(caches):
-        kv = L.KvView()
-        kv.a.k, kv.a.v, kv.nv, kv.fmt = kc.data_ptr(), vc.data_ptr(), NSEQ * CTX, 1 if q8 else 0
-        if q8:
-            kv.a.ks, kv.a.vs = scales[i][0].data_ptr(), scales[i][1].data_ptr()
-        views.append(kv)
-    stream = torch.cuda.Stream()
-    s = C.c_void_p(stream.cuda_stream)
-
-    def step(i):
-        lib.kc_attn(s, a, q.data_ptr(), views[i % NL], rid.data_ptr(), part.data_ptr(), g.data_ptr(), o.data_ptr(), NSEQ)
-
-    with torch.cuda.stream(stream):
-        for i in range(W):
-            step(i)
-        stream.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with ClockSampler(torch.cuda.current_device()) as clocks:
-            e0.record(stream)
-            for i in range(K):
-                step(W + i)
-            e1.record(stream)
-            e1.synchronize()
-        ms = e0.elapsed_time(e1) / K
-    L.check()
-    peaks, kind = measured_peaks()
-    nbytes = 2 * NSEQ * CTX * NKV * ((128 + 4) if q8 else 128 * 2) + 3 * NSEQ * NH * 128 * 4
-    gbs = nbytes / (ms * 1e-3) / 1e9
-    print(json.dumps({"metric": "decode_attention_tokens_per_s", "value": NSEQ / (ms * 1e-3), "unit": "tok/s", "n_gpus": 1, "steps": K,
-                      "warmup": W, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": ("int8" if q8 else "bf16") + " cache, f32 math",
-                      "data": "synthetic", "gpu_launches": 2 * K, "clocks": clocks.summary(),
-                      "config": {"workload": f"decode attention, {NH} query / {NKV} KV heads of 128, {'8-bit' if q8 else 'BF16'} cache of {CTX} positions x {NSEQ} "
-                                             f"sequences ({nbytes / 1e6:.0f} MB per layer), {NS} splits; {NL} layers rotated", "tokens": NSEQ},
-                      "roofline": {"bound": "hbm", "kernel": ATTN_FORMS.get(variant, ATTN_FORMS[1]) + " + attn_reduce_kernel (kc_attn)", "achieved": gbs,
-                                   "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"], "peak_kind": kind, "traffic": None,
-                                   "bytes_per_step": nbytes}}))
+    if rank != 0:
+        return None
+    if parity is not None:
+        parity["status"] = p2p_status or 0
+        if not parity["max_rel"] <= parity["bar"]:
+            raise SystemExit(f"expert-parallel step differs from the one-GPU layer: max relative error {parity['max_rel']:.3e}; the timing is void")
+    peaks, peak_kind = measured_peaks()
+    # the whole step against the packed-bytes roofline: the experts a step touches, in expectation over the routing
+    # (E (1 - (1 - k/E)^B) distinct experts of 3 matrices each), read once by whichever rank owns them
+    distinct = EP_E * (1.0 - (1.0 - EP_K / EP_E) ** EP_B)
+    gbs = distinct * 3 * BYTES_PER_MATRIX / (ms_per_step * 1e-3) / 1e9
+    res = {"value": EP_B / (ms_per_step * 1e-3), "ms_per_step": ms_per_step, "gpu_launches": int(launches), "cuda_graph": captured,
+           "collectives": args.ep_collectives, "mirrored_ranks": mirror, "clocks": clocks.summary(), "l2_policy": l2_policy(NL, e_loc),
+           "pairs_on_rank0_last_step": pairs, "parity": parity,
+           "e2e": {"value": EP_B / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": t_loc * D * 4 + t_loc * EP_E * 4,
+                   "d2h_bytes_per_step": t_loc * D * 4, "ms_per_step": e2e_s * 1e3, "steps_in_flight": 1},
+           "roofline": {"bound": "hbm", "kernel": "the step's seed mat-vecs (mv_grp_kernel: gate+up and down over the ranks' pairs)",
+                        "achieved": gbs, "peak": peaks["hbm_gbs"] * world, "unit": "GB/s", "frac": gbs / (peaks["hbm_gbs"] * world),
+                        "peak_kind": peak_kind, "traffic": None, "expected_distinct_experts": distinct,
+                        "note": "whole step (mat-vecs + exchange) over the aggregate HBM peak of the ranks; the kernels are bound by "
+                                "the logic pipe, see the 1-GPU line for the per-kernel roofline"}}
+    sm = res["clocks"].get("sm_mhz")
+    if sm:      # the logic-pipe floor of the step: every distinct expert's three matrices expanded once, over all the ranks' SMs
+        blocks = distinct * 3 * BLOCKS_PER_MATRIX
+        res["roofline"]["alu"] = alu_roofline(ms_per_step * 1e3, blocks, sm, lib.nsl_sm_count() * world)
+    return res
 
 
 def main():
@@ -668,6 +773,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=None, help="config 1: 1..8 (default 8); config 2: prompt rows (default 512)")
     ap.add_argument("--layers", type=int, default=20)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="N = 1: the headline only, without the `workloads` and `ep_base` objects")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-dependent-launch", action="store_true",
                     help="config 1: ordinary launches instead of programmatic dependent launches (for comparison)")
@@ -677,31 +783,111 @@ def main():
     ap.add_argument("--ep-mirror", type=int, default=0,
                     help="config 3, p2p, even rank counts: 1 = ranks r and r + N/2 hold each other's experts too and split their "
                          "joint pairs in the middle (balance to within one pair; twice the expert bytes per GPU)")
-    ap.add_argument("--workload", default=None, choices=["cfg1", "cfg2", "cfg3", "lmhead", "attn"],
-                    help="cfg1: one GPU's MoE decode layer (default at 1 GPU); cfg2: the same layer on 512 prompt rows (grouped "
-                         "tcgen05 GEMM); cfg3: expert-parallel decode (default at >1 GPU)")
+    ap.add_argument("--workload", default=None, choices=["cfg0", "cfg1", "cfg2", "cfg3", "lmhead", "attn"],
+                    help="one workload alone as the line (profiling): cfg1 one GPU's MoE decode layer; cfg2 the same layer on 512 "
+                         "prompt rows (grouped tcgen05 GEMM); cfg3 expert-parallel decode (the default at >1 GPU); cfg0 / lmhead / attn")
     args = ap.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
     if args.impl == "reference":
-        world = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
-        workload = args.workload or ("cfg1" if world == 1 else "cfg3")
+        workload = args.workload or ("cfg1" if max(world, args.gpus) == 1 else "cfg3")
         args.tokens = args.tokens or (512 if workload == "cfg2" else 8)
-        if int(os.environ.get("RANK", "0")) == 0:
+        if rank == 0:
             run_reference(args, workload)
         return
-    world = int(os.environ.get("WORLD_SIZE", "1"))
+    import torch
+    import torch.distributed as dist
+    from nanoseedlm_b200 import lib as L
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    lib = L.load()
+    peaks, peak_kind = measured_peaks()
+    sms = lib.nsl_sm_count()
+    K, W = args.steps, max(args.warmup, 3)
     workload = args.workload or ("cfg1" if world == 1 else "cfg3")
-    if args.tokens is None:
-        args.tokens = 512 if workload == "cfg2" else 8
-    if workload == "cfg1" and not 1 <= args.tokens <= 8:
+    base = {"metric": METRIC, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic"}
+
+    if workload == "cfg3":
+        r = measure_ep(args, K, W)
+        if rank == 0:
+            line = dict(base, value=r.pop("value"), ms_per_step=r.pop("ms_per_step"), config=ep_config(world), workload_id="cfg3", **r)
+            print(json.dumps(line))
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    if workload in ("cfg0", "lmhead", "attn"):      # one secondary workload alone
+        print(json.dumps(dict(base, **secondary(workload, K, W, peaks, peak_kind, sms, args))))
+        return
+
+    M = args.tokens or (512 if workload == "cfg2" else 8)
+    if workload == "cfg1" and not 1 <= M <= 8:
         raise SystemExit("config 1 is the decode / verify batch: --tokens 1..8 (use --workload cfg2 for prompt rows)")
-    if workload == "attn":
-        run_attn(args)
-    elif workload == "lmhead":
-        run_lmhead(args)
-    elif workload == "cfg3":
-        run_ep(args)
-    else:
-        run_ours(args)
+    c = Cfg1(args.layers)
+    r = measure_layer(c, M, K, W, dependent_launch=not args.no_dependent_launch)
+    clocks = r["clocks"]
+    line = dict(base, value=r["value"], ms_per_step=r["ms_per_step"], config=workload_config(M), workload_id=f"cfg1_m{M}" if M <= 8 else "cfg2",
+                l2_policy=l2_policy(args.layers), packed_gbs=r["packed_gbs"], gpu_launches=r["gpu_launches"], clocks=clocks, e2e=r["e2e"],
+                roofline=layer_roofline(r, M, clocks.get("sm_mhz"), sms, peaks, peak_kind))
+    extra = args.workload is None and not args.no_extra
+    if extra:
+        Kx = min(K, 1000)
+        wl = {}
+        for m_ in (1, 4):
+            rr = measure_layer(c, m_, Kx, W, sample_clocks=False)
+            wl[f"cfg1_m{m_}"] = {"ms_per_step": rr["ms_per_step"], "value": rr["value"], "unit": "tok/s", "e2e": rr["e2e"],
+                                 "roofline": layer_roofline(rr, m_, clocks.get("sm_mhz"), sms, peaks, peak_kind)}
+        rr = measure_layer(c, 512, min(K, 200), W, sample_clocks=False)
+        wl["cfg2"] = {"ms_per_step": rr["ms_per_step"], "value": rr["value"], "unit": "tok/s", "e2e": rr["e2e"],
+                      "roofline": layer_roofline(rr, 512, clocks.get("sm_mhz"), sms, peaks, peak_kind),
+                      "layer_alu": alu_roofline(rr["ms_per_step"] * 1e3, 3 * E * BLOCKS_PER_MATRIX, clocks.get("sm_mhz") or 1965.0, sms)}
+        line["workloads"] = wl
+    step0 = r["step0"]
+    layer0 = c.layers[0]
+    if not args.no_cpu:
+        line["cpu_baseline"] = cpu_baseline_cfg1(os.cpu_count() or 1, M, layer0 if M <= 8 else None, step0[0], step0[1], step0[2] if M <= 8 else None)
+    del c, r
+    torch.cuda.empty_cache()
+    if extra:
+        for name in ("cfg0", "lmhead", "attn"):
+            line["workloads"][name] = secondary(name, min(K, 1000), W, peaks, peak_kind, sms, args, sm_mhz=clocks.get("sm_mhz"))
+            torch.cuda.empty_cache()
+        rr = measure_ep(args, min(K, 400), W)
+        line["ep_base"] = {"workload": ep_config(1)["workload"], "value": rr["value"], "unit": "tok/s", "ms_per_step": rr["ms_per_step"],
+                           "e2e": rr["e2e"], "parity": rr["parity"], "roofline": rr["roofline"],
+                           "note": "config 3 with all 512 experts on this one GPU: the base of the strong-scaling series the N > 1 lines "
+                                   "continue (speed-up at N = this ms_per_step / the N-GPU line's ms_per_step)"}
+    print(json.dumps(line))
+
+
+def secondary(name, K, W, peaks, peak_kind, sms, args, sm_mhz=None):
+    """cfg0, the LM head or decode attention as a result object with its roofline."""
+    if name == "cfg0":
+        r = measure_cfg0(K, W)
+        gbs = r["bytes"] / (r["us"] * 1e-6) / 1e9
+        out = {"workload": "BASELINE config 0: dense seed mat-vec, 2048 outputs x 4096 inputs, 1 token, raw f32 output; 32 matrices rotated (151 MB)",
+               "ms_per_step": r["us"] * 1e-3, "value": 1.0 / (r["us"] * 1e-6), "unit_note": "mat-vecs / s", "gweights_per_s": r["weights"] / (r["us"] * 1e-6) / 1e9,
+               "roofline": {"bound": "hbm", "kernel": "mv_smemx_kernel (nsl_mv_raw / kc_mv)", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                            "frac": gbs / peaks["hbm_gbs"], "peak_kind": peak_kind, "alu": alu_roofline(r["us"], r["blocks"], sm_mhz or 1965.0, sms)}}
+        if not args.no_cpu:
+            out["cpu_baseline"] = cpu_cfg0_protocol()
+        return out
+    if name == "lmhead":
+        r = measure_lmhead(8, min(K, 300), W)
+        gbs = r["bytes"] / (r["mv_us"] * 1e-6) / 1e9
+        return {"workload": f"dense affine-int4 LM head {LM_V} x {LM_D} (groups of 64) + greedy arg-max, 8 tokens; 4 heads rotated (0.7 GB)",
+                "ms_per_step": r["ms_per_step"], "value": r["tokens"] / (r["ms_per_step"] * 1e-3), "unit": "tok/s",
+                "roofline": {"bound": "hbm", "kernel": "q4_mv_ksplit_kernel (kc_mv, MF_Q4)", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                             "frac": gbs / peaks["hbm_gbs"], "peak_kind": peak_kind, "us_per_launch": r["mv_us"], "bytes_per_launch": r["bytes"]}}
+    r = measure_attn(min(K, 500), W)
+    gbs = r["bytes"] / (r["ms_per_step"] * 1e-3) / 1e9
+    return {"workload": "decode attention, 16 query / 2 KV heads of 128, BF16 cache of 4096 positions x 32 sequences (134 MB per layer), 32 splits; 3 layers rotated",
+            "ms_per_step": r["ms_per_step"], "value": r["tokens"] / (r["ms_per_step"] * 1e-3), "unit": "tok/s",
+            "roofline": {"bound": "hbm", "kernel": "attn_flat_mma_kernel + attn_reduce_kernel (kc_attn)", "achieved": gbs, "peak": peaks["hbm_gbs"],
+                         "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"], "peak_kind": peak_kind, "bytes_per_step": r["bytes"]}}
 
 
 if __name__ == "__main__":

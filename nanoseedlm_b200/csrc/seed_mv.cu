@@ -46,6 +46,44 @@ __device__ __forceinline__ float silu_bf(float g) {   // each op rounded to bf16
 
 struct Chunk { uint4 s, c; uint32_t cd; };
 
+// The conversion constants (seed_block.cuh: KConst) as a module constant for code outside the kernels' own bodies: a
+// function that is not inlined cannot take them as constant-bank kernel arguments.
+constexpr float pow2_f(int e) {
+    float v = 1.0f;
+    for (int i = 0; i < (e < 0 ? -e : e); ++i) v = e < 0 ? v * 0.5f : v * 2.0f;
+    return v;
+}
+constexpr KConst kconst_static() {
+    KConst k = {};
+    for (int p = 0; p < 4; ++p) {
+        k.cxor[p] = ((uint32_t) (215 - 5 * p) << 23) | (8u << (4 * p));
+        k.coff[p] = -(pow2_f(88 - 5 * p) + pow2_f(68 - p));
+        k.cxor_x[p] = ((uint32_t) (250 - 5 * p) << 23) | (8u << (4 * p));
+        k.coff_x[p] = -(pow2_f(123 - 5 * p) + pow2_f(103 - p));
+    }
+    k.cor = 112u << 23;
+    return k;
+}
+__constant__ KConst c_kc = kconst_static();
+
+// What a unit's row loop needs, by value (it runs in a function of its own: see unit_rows).
+struct UnitArgs {
+    const uint4 *sa, *ca, *sb, *cb;      // seeds and coefficient words of the (gate or only) matrix and of the up matrix
+    const uint32_t *da, *db;              // their exponent codes
+    int eba, ebb;
+    float* y;
+    int ys, R, raw, add;
+    int pid[4];                           // the unit's pairs (output rows)
+    int s_lo, s_hi, lpr_log2;
+};
+__device__ __forceinline__ Chunk load_chunk3(const uint4* s, const uint4* c, const uint32_t* d, size_t chunk_index) {
+    Chunk k;
+    k.s = __ldg(s + chunk_index);
+    k.c = __ldg(c + chunk_index);
+    k.cd = __ldg(d + chunk_index);
+    return k;
+}
+
 __device__ __forceinline__ Chunk load_chunk(const WSlice& w, size_t chunk_index) {
     Chunk k;
     k.s = __ldg((const uint4*) w.p[0] + chunk_index);
@@ -89,8 +127,61 @@ __device__ __forceinline__ void store_out(const MvParams& a, int pair, int r, fl
 }
 
 // One thread's share of staging a pair's inputs: 16 inputs (two blocks: chunk j of the row, block pair bp), scaled, as
+// the f32x2 operands of pair_dot plus the two blocks' input sums (2^-64 of them), from which the consumer forms the
+// centring constants: xm[p] = -2^(p-66) * sum, an exact scaling, so the bits are those of block_offsets.
+__device__ __forceinline__ float block_sum(const float* xs) {      // the order of block_offsets
+    return (((xs[0] + xs[4]) + (xs[1] + xs[5])) + ((xs[2] + xs[6]) + (xs[3] + xs[7]))) * 5.421010862427522e-20f;   // 2^-64
+}
+__device__ __forceinline__ void offsets_from_sum(u64 s2, u64* xm2) {
+    xm2[0] = mul2(s2, pack2(-1.3552527156068805e-20f, -1.3552527156068805e-20f));   // -2^-66
+    xm2[1] = mul2(s2, pack2(-2.710505431213761e-20f, -2.710505431213761e-20f));     // -2^-65
+    xm2[2] = mul2(s2, pack2(-5.421010862427522e-20f, -5.421010862427522e-20f));     // -2^-64
+    xm2[3] = mul2(s2, pack2(-1.0842021724855044e-19f, -1.0842021724855044e-19f));   // -2^-63
+}
+__device__ __forceinline__ void stage_load(const MvParams& a, int xr, int j, int bp, float* x) {
+    if (a.xbf16) {
+        const uint4* xp = (const uint4*) ((const uint16_t*) a.x + (size_t) xr * a.xs + (size_t) j * 64 + bp * 16);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const uint4 t = __ldg(xp + i);
+            const uint32_t u[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                x[8 * i + 2 * q] = __uint_as_float(u[q] << 16) * NSL_XSCALE;
+                x[8 * i + 2 * q + 1] = __uint_as_float(u[q] & 0xFFFF0000u) * NSL_XSCALE;
+            }
+        }
+    } else {
+        const float4* xp = (const float4*) (a.x + (size_t) xr * a.xs + (size_t) j * 64 + bp * 16);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float4 t = __ldg(xp + i);
+            x[4 * i] = t.x * NSL_XSCALE; x[4 * i + 1] = t.y * NSL_XSCALE; x[4 * i + 2] = t.z * NSL_XSCALE; x[4 * i + 3] = t.w * NSL_XSCALE;
+        }
+    }
+}
+__device__ __forceinline__ void stage_store(const float* x, int j, int bp, ulonglong2* sx, u64* ss) {
+#pragma unroll
+    for (int cq = 0; cq < 4; ++cq) {
+        ulonglong2 t;
+        t.x = pack2(x[2 * cq], x[8 + 2 * cq]);
+        t.y = pack2(x[2 * cq + 1], x[8 + 2 * cq + 1]);
+        sx[(bp * 4 + cq) * 32 + j] = t;
+    }
+    ss[bp * 32 + j] = pack2(block_sum(x), block_sum(x + 8));
+}
+
+
+struct RouteFuse {        // the router folded into the prologue (logits == NULL: the pair list comes from MvParams.sel)
+    const float* logits;
+    int ld, n_exp, top_k, T;
+    int32_t* ind_out;
+    float* wt_out;
+};
+
+// One thread's share of staging a pair's inputs: 16 inputs (two blocks: chunk j of the row, block pair bp), scaled, as
 // the f32x2 operands of pair_dot plus their centring constants.
-__device__ __forceinline__ void stage_inputs(const MvParams& a, int xr, int j, int bp, ulonglong2* sx, ulonglong2* sm) {
+__device__ __forceinline__ void stage_pair_inputs(const MvParams& a, int xr, int j, int bp, ulonglong2* sx, ulonglong2* sm) {
     float x[16], xm[8];
     if (a.xbf16) {
         const uint4* xp = (const uint4*) ((const uint16_t*) a.x + (size_t) xr * a.xs + (size_t) j * 64 + bp * 16);
@@ -130,6 +221,112 @@ __device__ __forceinline__ void stage_inputs(const MvParams& a, int xr, int j, i
     }
 }
 
+// ---- one expansion per pair, inputs in shared memory, two blocks of 8 warps per SM ----------------------------------------
+// Rows of 1, 2, 4, .. 32 chunks (K = 64 .. 2048).  The pair's inputs sit in shared memory as the f32x2 operands of pair_dot,
+// laid out [block pair][operand pair][lane] so that a warp's 16-byte loads are conflict-free; a thread fits in 128
+// registers and 16 warps per SM hide the logic pipe's latencies.  The work is the pair-major sequence of row steps (a
+// step = the 32 / lanes-per-row rows a warp expands at once); blocks take contiguous equal shares of it, inside a pair the
+// block's warps take its steps round-robin, and the next row's streams are prefetched while the current row is expanded.
+// Optionally the block first ROUTES: with logits given, warp t picks token t's top-k experts (route.cuh) and the pair
+// list is the T * top_k (token, expert) pairs; block 0 also stores ids and weights for the kernels that follow.
+template <int MODE>
+__global__ void __launch_bounds__(MV_THREADS, 2) mv_pair_kernel(MvParams a, KConst kc, int lpr_log2, RouteFuse rf) {
+    __shared__ StreamTab tab;
+    __shared__ int32_t r_ind[256];   // the fused router's picks
+    __shared__ float r_wt[256];
+    __shared__ __align__(16) ulonglong2 sx[4 * 4 * 32];   // [bp][c / 2][lane] = {x2[c], x2[c + 1]}
+    __shared__ __align__(16) ulonglong2 sm[4 * 2 * 32];   // [bp][p / 2][lane] = {xm2[p], xm2[p + 1]}
+    load_stream_tab(tab, a.G, threadIdx.x, MV_THREADS);
+    grid_dependents_go();
+    grid_dependency_wait();   // everything below may read what the previous kernel in the stream wrote
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int lpr = 1 << lpr_log2, rpw = 32 >> lpr_log2;
+    const int jc = lane & (lpr - 1), ro = lane >> lpr_log2;
+    int P = a.count ? min(*a.count, a.P) : a.P;
+    if (rf.logits) {          // the router: one warp per token, every block the same picks; block 0 stores them
+        if (warp < rf.T) {
+            const float* l = rf.logits + (size_t) warp * rf.ld;
+            if (rf.n_exp <= 128) route_row<4>(rf.n_exp, rf.top_k, l, lane, r_ind + warp * rf.top_k, r_wt + warp * rf.top_k);
+            else if (rf.n_exp <= 512) route_row<16>(rf.n_exp, rf.top_k, l, lane, r_ind + warp * rf.top_k, r_wt + warp * rf.top_k);
+            else route_row<32>(rf.n_exp, rf.top_k, l, lane, r_ind + warp * rf.top_k, r_wt + warp * rf.top_k);
+        }
+        P = rf.T * rf.top_k;
+        __syncthreads();
+        if (blockIdx.x == 0 && (int) threadIdx.x < P) {
+            rf.ind_out[threadIdx.x] = r_ind[threadIdx.x];
+            rf.wt_out[threadIdx.x] = r_wt[threadIdx.x];
+        }
+    }
+    const int rs = (a.R + rpw - 1) / rpw;
+    const long long total = (long long) P * rs;
+    const long long begin = (long long) blockIdx.x * total / gridDim.x, end = (long long) (blockIdx.x + 1) * total / gridDim.x;
+    if (begin >= end) return;
+    const int p_first = (int) (begin / rs), p_last = (int) ((end - 1) / rs);
+    for (int pair = p_first; pair <= p_last; ++pair) {
+        const int s_lo = pair == p_first ? (int) (begin - (long long) pair * rs) : 0;
+        const int s_hi = pair == p_last ? (int) (end - (long long) pair * rs) : rs;
+        const int slice = rf.logits ? r_ind[pair] : (a.sel ? a.sel[pair] : 0);
+        const WSlice wa = a.ws ? a.ws[slice] : a.w0;
+        WSlice wb = wa;
+        if (MODE == MODE_GU) wb = a.wu[slice];
+        // this warp's first streams are requested before the inputs are staged: their DRAM latency runs under it
+        int st = s_lo + warp;
+        int r = st * rpw + ro;
+        Chunk ka, kb;
+        if (st < s_hi && r < a.R) {
+            ka = load_chunk(wa, (size_t) r * lpr + jc);
+            if (MODE == MODE_GU) kb = load_chunk(wb, (size_t) r * lpr + jc);
+        }
+        if (pair != p_first) __syncthreads();   // the previous pair's inputs are no longer read
+        if (threadIdx.x < lpr * 4) {
+            const int j = threadIdx.x & (lpr - 1), bp = threadIdx.x >> lpr_log2;
+            stage_pair_inputs(a, a.xrow ? a.xrow[pair] : pair / a.xdiv, j, bp, sx, sm);
+        }
+        __syncthreads();   // inputs staged (and, for the block's first pair, the stream table loaded)
+        const float sca = slice_scale(wa.eb), scb = slice_scale(wb.eb);
+        for (; st < s_hi; st += MV_WARPS, r += MV_WARPS * rpw) {
+            const bool ok = r < a.R;
+            const int rn = r + MV_WARPS * rpw;
+            Chunk na, nb;
+            if (st + MV_WARPS < s_hi && rn < a.R) {
+                na = load_chunk(wa, (size_t) rn * lpr + jc);
+                if (MODE == MODE_GU) nb = load_chunk(wb, (size_t) rn * lpr + jc);
+            }
+            u64 acc = 0ull, accu = 0ull;
+            if (ok) {
+                const uint32_t swa[4] = {ka.s.x, ka.s.y, ka.s.z, ka.s.w}, cwa[4] = {ka.c.x, ka.c.y, ka.c.z, ka.c.w};
+                const uint32_t swb[4] = {kb.s.x, kb.s.y, kb.s.z, kb.s.w}, cwb[4] = {kb.c.x, kb.c.y, kb.c.z, kb.c.w};
+#pragma unroll
+                for (int bp = 0; bp < 4; ++bp) {
+                    u64 x2[8], xm2[4];
+#pragma unroll
+                    for (int cq = 0; cq < 4; ++cq) { const ulonglong2 t = sx[(bp * 4 + cq) * 32 + jc]; x2[2 * cq] = t.x; x2[2 * cq + 1] = t.y; }
+#pragma unroll
+                    for (int pq = 0; pq < 2; ++pq) { const ulonglong2 t = sm[(bp * 2 + pq) * 32 + jc]; xm2[2 * pq] = t.x; xm2[2 * pq + 1] = t.y; }
+                    {
+                        u64 v[32], q[4];
+                        pair_states(tab, swa[bp], v);
+                        pair_coefs(cwa[bp], kc, q);
+                        acc = fma2(pair_dot(v, q, x2, xm2), code_scale_pair(ka.cd, bp, kc), acc);
+                    }
+                    if (MODE == MODE_GU) {
+                        u64 v[32], q[4];
+                        pair_states(tab, swb[bp], v);
+                        pair_coefs(cwb[bp], kc, q);
+                        accu = fma2(pair_dot(v, q, x2, xm2), code_scale_pair(kb.cd, bp, kc), accu);
+                    }
+                }
+            }
+            const float s = group_sum(pair_total(acc), lpr) * sca;
+            float su = 0.0f;
+            if (MODE == MODE_GU) su = group_sum(pair_total(accu), lpr) * scb;
+            if (ok && jc == 0) store_out<MODE>(a, pair, r, s, su);
+            ka = na;
+            if (MODE == MODE_GU) kb = nb;
+        }
+    }
+}
+
 
 // ---- pairs grouped by expert: one expansion per distinct slice ---------------------------------------------------------
 // Rows of 1, 2, 4, .. 32 chunks (K = 64 .. 2048).  Every block builds the same plan in its prologue: the pair list is
@@ -144,75 +341,139 @@ __device__ __forceinline__ void stage_inputs(const MvParams& a, int xr, int j, i
 // Optionally the block first ROUTES: with logits given, warp t picks token t's top-k experts (route.cuh) and the pair
 // list is the T * top_k (token, expert) pairs; block 0 also stores ids and weights for the kernels that follow.
 #ifndef NSL_GRP_NT
-#define NSL_GRP_NT 4
+#define NSL_GRP_NT 2
 #endif
 constexpr int GRP_NT = NSL_GRP_NT;                         // pairs that share one expansion at most
 constexpr int GRP_MAX_PAIRS = 1024;               // pairs a block can sort; longer lists run ungrouped
-__device__ constexpr int GRP_W[5] = {0, 8, 9, 11, 13};   // relative cost of a row step for a unit of n pairs
-constexpr int GRP_SX = 4 * 4 * 32, GRP_SM = 4 * 2 * 32;           // ulonglong2 entries of one pair's inputs / centring constants
+constexpr int GRP_SMALL = 128;                    // lists up to this length are ranked by counting (no sorting network)
+#ifndef NSL_GRP_W2
+#define NSL_GRP_W2 12
+#define NSL_GRP_W3 18
+#define NSL_GRP_W4 23
+#endif
+#ifndef NSL_GRP_MINB
+#define NSL_GRP_MINB 2
+#endif
+__device__ constexpr int GRP_W[5] = {0, 8, NSL_GRP_W2, NSL_GRP_W3, NSL_GRP_W4};   // relative cost of a row step for a unit of n pairs
+constexpr int GRP_SX = 4 * 4 * 32, GRP_SS = 4 * 32;               // entries of one pair's inputs (ulonglong2) / block sums (u64)
 
 struct GrpShared {
     StreamTab tab;
     uint32_t key[GRP_MAX_PAIRS];                  // sorted (slice << 10 | pair)
     int32_t prefix[GRP_MAX_PAIRS + 1];            // weight of the units that start before sorted position i
+    uint32_t tmp[GRP_SMALL];                      // short lists: unsorted keys, then unit weights
     int32_t r_ind[256];                           // the fused router's picks
     float r_wt[256];
     __align__(16) ulonglong2 sx[GRP_NT][GRP_SX];
-    __align__(16) ulonglong2 sm[GRP_NT][GRP_SM];
+    __align__(16) u64 ss[GRP_NT][GRP_SS];
 };
 
-struct RouteFuse {        // the router folded into the prologue (logits == NULL: the pair list comes from MvParams.sel)
-    const float* logits;
-    int ld, n_exp, top_k, T;
-    int32_t* ind_out;
-    float* wt_out;
-};
 
 // One row step of one matrix for NT pairs: four block pairs expanded once each, dotted with every pair's inputs.
+// The state-value pairs of weights 4H .. 4H+3 of two adjacent blocks (half of pair_states): v[4 (c - 4H) + p].
+template <int H>
+__device__ __forceinline__ void half_states(uint32_t a0, uint32_t a1, uint32_t g0, uint32_t g1, u64* v) {
+#define NSL_VH(C)                                                                                \
+    {                                                                                            \
+        const uint32_t y0 = weight_word<4 * H + C>(a0, g0), y1 = weight_word<4 * H + C>(a1, g1);  \
+        v[4 * C + 0] = pack2(state_value<0>(y0), state_value<0>(y1));                            \
+        v[4 * C + 1] = pack2(state_value<1>(y0), state_value<1>(y1));                            \
+        v[4 * C + 2] = pack2(state_value<2>(y0), state_value<2>(y1));                            \
+        v[4 * C + 3] = pack2(state_value<3>(y0), state_value<3>(y1));                            \
+    }
+    NSL_VH(0) NSL_VH(1) NSL_VH(2) NSL_VH(3)
+#undef NSL_VH
+}
+
+// One row step of one matrix for NT pairs: each block pair is expanded once, half of its weights at a time (so that only
+// 16 state-value pairs are held while every pair's inputs pass), and dotted with every pair's inputs.  Per pair the
+// operations and their order are those of pair_dot.
 template <int NT>
 __device__ __forceinline__ void unit_chunk(const StreamTab& tab, const KConst& kc, const Chunk& k, const ulonglong2 (*sx)[GRP_SX],
-                                           const ulonglong2 (*sm)[GRP_SM], int jc, u64* acc) {
+                                           const u64 (*ss)[GRP_SS], int jc, u64* acc) {
     const uint32_t sw[4] = {k.s.x, k.s.y, k.s.z, k.s.w}, cw[4] = {k.c.x, k.c.y, k.c.z, k.c.w};
 #pragma unroll
     for (int bp = 0; bp < 4; ++bp) {
-        u64 v[32], q[4];
-        pair_states(tab, sw[bp], v);
+        const uint32_t g0 = tab.lo[__byte_perm(sw[bp], 0, 0x4440)] ^ tab.hi[__byte_perm(sw[bp], 0, 0x4441)];
+        const uint32_t g1 = tab.lo[__byte_perm(sw[bp], 0, 0x4442)] ^ tab.hi[__byte_perm(sw[bp], 0, 0x4443)];
+        const uint32_t a0 = __byte_perm(sw[bp], g0, 0x5410), a1 = __byte_perm(sw[bp], g1, 0x5432);
+        u64 d[NT][4];
+#pragma unroll
+        for (int t = 0; t < NT; ++t) offsets_from_sum(ss[t][bp * 32 + jc], d[t]);
+        {
+            u64 v[16];
+            half_states<0>(a0, a1, g0, g1, v);
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+#pragma unroll
+                for (int cq = 0; cq < 2; ++cq) {
+                    const ulonglong2 u = sx[t][(bp * 4 + cq) * 32 + jc];
+#pragma unroll
+                    for (int p = 0; p < 4; ++p) d[t][p] = fma2(u.x, v[8 * cq + p], d[t][p]);
+#pragma unroll
+                    for (int p = 0; p < 4; ++p) d[t][p] = fma2(u.y, v[8 * cq + 4 + p], d[t][p]);
+                }
+            }
+        }
+        {
+            u64 v[16];
+            half_states<1>(a0, a1, g0, g1, v);
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+#pragma unroll
+                for (int cq = 0; cq < 2; ++cq) {
+                    const ulonglong2 u = sx[t][(bp * 4 + 2 + cq) * 32 + jc];
+#pragma unroll
+                    for (int p = 0; p < 4; ++p) d[t][p] = fma2(u.x, v[8 * cq + p], d[t][p]);
+#pragma unroll
+                    for (int p = 0; p < 4; ++p) d[t][p] = fma2(u.y, v[8 * cq + 4 + p], d[t][p]);
+                }
+            }
+        }
+        u64 q[4];
         pair_coefs(cw[bp], kc, q);
         const u64 e2 = code_scale_pair(k.cd, bp, kc);
 #pragma unroll
-        for (int t = 0; t < NT; ++t) {
-            u64 x2[8], xm2[4];
-#pragma unroll
-            for (int cq = 0; cq < 4; ++cq) { const ulonglong2 u = sx[t][(bp * 4 + cq) * 32 + jc]; x2[2 * cq] = u.x; x2[2 * cq + 1] = u.y; }
-#pragma unroll
-            for (int pq = 0; pq < 2; ++pq) { const ulonglong2 u = sm[t][(bp * 2 + pq) * 32 + jc]; xm2[2 * pq] = u.x; xm2[2 * pq + 1] = u.y; }
-            acc[t] = fma2(pair_dot(v, q, x2, xm2), e2, acc[t]);
-        }
+        for (int t = 0; t < NT; ++t)
+            acc[t] = fma2(fma2(q[3], d[t][3], fma2(q[2], d[t][2], fma2(q[1], d[t][1], mul2(q[0], d[t][0])))), e2, acc[t]);
     }
 }
 
 // The row steps [s_lo, s_hi) of a unit of NT pairs that fall to this warp.  ka / kb: the streams of its first step,
 // requested by the caller before the unit's inputs were staged.
+template <int MODE>
+__device__ __forceinline__ void store_unit(const UnitArgs& ua, int pair, int r, float s, float su) {
+    float* yo = ua.y + (size_t) pair * ua.ys + r;
+    if (MODE == MODE_GU) *yo = ua.raw ? (s / (1.0f + expf(-s))) * su : bf16_round(silu_bf(bf16_round(s)) * bf16_round(su));
+    else if (ua.raw) *yo = s;
+    else *yo = ua.add ? bf16_round(*yo + bf16_round(s)) : bf16_round(s);   // engine/kernels_moe.cu:214
+}
+
 template <int MODE, int NT>
-__device__ __forceinline__ void unit_rows(const MvParams& a, const KConst& kc, const GrpShared& sh, const WSlice& wa, const WSlice& wb,
-                                          const int* pid, int s_lo, int s_hi, int lpr_log2, Chunk ka, Chunk kb) {
+__device__ __noinline__ void unit_rows(UnitArgs ua, Chunk ka, Chunk kb) {
+    // Not inlined on purpose: each unit size gets a register allocation of its own (inlined into one body, the larger
+    // sizes' pressure spilled the single-pair loop too).  Shared memory and the constants are reached by name.
+    extern __shared__ __align__(16) unsigned char grp_smem[];
+    const GrpShared& sh = *reinterpret_cast<const GrpShared*>(grp_smem);
+    const KConst& kc = c_kc;
+    const int s_lo = ua.s_lo, s_hi = ua.s_hi, lpr_log2 = ua.lpr_log2;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int lpr = 1 << lpr_log2, rpw = 32 >> lpr_log2;
     const int jc = lane & (lpr - 1), ro = lane >> lpr_log2;
-    const float sca = slice_scale(wa.eb), scb = slice_scale(wb.eb);
+    const float sca = slice_scale(ua.eba), scb = slice_scale(ua.ebb);
     int st = s_lo + warp, r = st * rpw + ro;
     for (; st < s_hi; st += MV_WARPS, r += MV_WARPS * rpw) {
-        const bool ok = r < a.R;
+        const bool ok = r < ua.R;
         const int rn = r + MV_WARPS * rpw;
-        const bool more = st + MV_WARPS < s_hi && rn < a.R;
+        const bool more = st + MV_WARPS < s_hi && rn < ua.R;
         u64 acc[NT], accu[NT];
 #pragma unroll
         for (int t = 0; t < NT; ++t) acc[t] = accu[t] = 0ull;
         if (NT == 1 && MODE == MODE_GU) {      // one pair: its inputs are read once per block pair for both matrices
             Chunk na, nb;
             if (more) {   // the next step's streams fly during this step's expansion
-                na = load_chunk(wa, (size_t) rn * lpr + jc);
-                nb = load_chunk(wb, (size_t) rn * lpr + jc);
+                na = load_chunk3(ua.sa, ua.ca, ua.da, (size_t) rn * lpr + jc);
+                nb = load_chunk3(ua.sb, ua.cb, ua.db, (size_t) rn * lpr + jc);
             }
             if (ok) {
                 const uint32_t swa[4] = {ka.s.x, ka.s.y, ka.s.z, ka.s.w}, cwa[4] = {ka.c.x, ka.c.y, ka.c.z, ka.c.w};
@@ -222,8 +483,7 @@ __device__ __forceinline__ void unit_rows(const MvParams& a, const KConst& kc, c
                     u64 x2[8], xm2[4];
 #pragma unroll
                     for (int cq = 0; cq < 4; ++cq) { const ulonglong2 u = sh.sx[0][(bp * 4 + cq) * 32 + jc]; x2[2 * cq] = u.x; x2[2 * cq + 1] = u.y; }
-#pragma unroll
-                    for (int pq = 0; pq < 2; ++pq) { const ulonglong2 u = sh.sm[0][(bp * 2 + pq) * 32 + jc]; xm2[2 * pq] = u.x; xm2[2 * pq + 1] = u.y; }
+                    offsets_from_sum(sh.ss[0][bp * 32 + jc], xm2);
                     {
                         u64 v[32], q[4];
                         pair_states(sh.tab, swa[bp], v);
@@ -243,11 +503,16 @@ __device__ __forceinline__ void unit_rows(const MvParams& a, const KConst& kc, c
         } else {
             // several pairs (or one matrix): a matrix's streams for the next step are requested as soon as this step has
             // used them up, into the registers they leave free, so no second set of stream registers is held
-            if (ok) unit_chunk<NT>(sh.tab, kc, ka, sh.sx, sh.sm, jc, acc);
-            if (more) ka = load_chunk(wa, (size_t) rn * lpr + jc);
             if (MODE == MODE_GU) {
-                if (ok) unit_chunk<NT>(sh.tab, kc, kb, sh.sx, sh.sm, jc, accu);
-                if (more) kb = load_chunk(wb, (size_t) rn * lpr + jc);
+                if (ok) unit_chunk<NT>(sh.tab, kc, ka, sh.sx, sh.ss, jc, acc);
+                if (more) ka = load_chunk3(ua.sa, ua.ca, ua.da, (size_t) rn * lpr + jc);
+                if (ok) unit_chunk<NT>(sh.tab, kc, kb, sh.sx, sh.ss, jc, accu);
+                if (more) kb = load_chunk3(ua.sb, ua.cb, ua.db, (size_t) rn * lpr + jc);
+            } else {      // one matrix: its next streams are requested before this step's expansion (a second set of registers)
+                Chunk na;
+                if (more) na = load_chunk3(ua.sa, ua.ca, ua.da, (size_t) rn * lpr + jc);
+                if (ok) unit_chunk<NT>(sh.tab, kc, ka, sh.sx, sh.ss, jc, acc);
+                ka = na;
             }
         }
 #pragma unroll
@@ -255,7 +520,7 @@ __device__ __forceinline__ void unit_rows(const MvParams& a, const KConst& kc, c
             const float s = group_sum(pair_total(acc[t]), lpr) * sca;
             float su = 0.0f;
             if (MODE == MODE_GU) su = group_sum(pair_total(accu[t]), lpr) * scb;
-            if (ok && jc == 0) store_out<MODE>(a, pid[t], r, s, su);
+            if (ok && jc == 0) store_unit<MODE>(ua, ua.pid[t], r, s, su);
         }
     }
 }
@@ -293,8 +558,9 @@ __device__ __forceinline__ void block_exclusive_scan(int32_t* a, int n) {
     __syncthreads();
 }
 
+
 template <int MODE>
-__global__ void __launch_bounds__(MV_THREADS, 2) mv_grp_kernel(MvParams a, KConst kc, int lpr_log2, RouteFuse rf) {
+__global__ void __launch_bounds__(MV_THREADS, NSL_GRP_MINB) mv_grp_kernel(MvParams a, KConst kc, int lpr_log2, RouteFuse rf) {
     extern __shared__ __align__(16) unsigned char grp_smem[];
     GrpShared& sh = *reinterpret_cast<GrpShared*>(grp_smem);
     load_stream_tab(sh.tab, a.G, threadIdx.x, MV_THREADS);
@@ -320,17 +586,41 @@ __global__ void __launch_bounds__(MV_THREADS, 2) mv_grp_kernel(MvParams a, KCons
     }
     if (P <= 0) return;
     const int rs = (a.R + rpw - 1) / rpw;             // row steps per unit
+#ifdef NSL_GRP_FORCE_PLAIN
+    const bool grouped = false;
+#else
     const bool grouped = P <= GRP_MAX_PAIRS;
+#endif
     long long total;
     if (grouped) {
-        int n = 32;
-        while (n < P) n <<= 1;
-        for (int i = threadIdx.x; i < n; i += MV_THREADS) {
-            const int slice = rf.logits ? sh.r_ind[i < P ? i : 0] : (a.sel ? a.sel[i < P ? i : 0] : 0);
-            sh.key[i] = i < P ? ((uint32_t) slice << 10) | (uint32_t) i : 0xFFFFFFFFu;
+        const bool small = P <= GRP_SMALL;
+        auto slice_of = [&](int i) { return rf.logits ? sh.r_ind[i] : (a.sel ? a.sel[i] : 0); };
+        if (small) {      // every thread ranks one key among all: two barriers instead of a sorting network's dozens
+            const int i = threadIdx.x;
+            uint32_t mine = 0xFFFFFFFFu;
+            if (i < P) {
+                const int sl = slice_of(i);
+                mine = ((uint32_t) sl << 10) | (uint32_t) i;
+                sh.tmp[i] = mine;
+                if (a.ws) {      // the slice's table entries on their way into L2 while the plan is made
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(a.ws + sl));
+                    if (MODE == MODE_GU) asm volatile("prefetch.global.L2 [%0];" ::"l"(a.wu + sl));
+                }
+            }
+            __syncthreads();
+            if (i < P) {
+                int rank = 0;
+                for (int j = 0; j < P; ++j) rank += sh.tmp[j] < mine;
+                sh.key[rank] = mine;
+            }
+            __syncthreads();
+        } else {
+            int n = 32;
+            while (n < P) n <<= 1;
+            for (int i = threadIdx.x; i < n; i += MV_THREADS) sh.key[i] = i < P ? ((uint32_t) slice_of(i) << 10) | (uint32_t) i : 0xFFFFFFFFu;
+            __syncthreads();
+            block_sort(sh.key, n);
         }
-        __syncthreads();
-        block_sort(sh.key, n);
         // a sorted position starts a unit when it is a multiple of GRP_NT pairs into its slice's run
         for (int i = threadIdx.x; i < P; i += MV_THREADS) {
             const uint32_t first = sh.key[i] & ~1023u;          // the smallest key of this slice
@@ -342,10 +632,17 @@ __global__ void __launch_bounds__(MV_THREADS, 2) mv_grp_kernel(MvParams a, KCons
                 while (cnt < GRP_NT && i + cnt < P && (sh.key[i + cnt] >> 10) == (sh.key[i] >> 10)) ++cnt;
                 w = GRP_W[cnt];
             }
-            sh.prefix[i] = w;
+            if (small) sh.tmp[i] = (uint32_t) w; else sh.prefix[i] = w;
         }
         __syncthreads();
-        block_exclusive_scan(sh.prefix, P);
+        if (small) {
+            for (int i = threadIdx.x; i <= P; i += MV_THREADS) {
+                int before = 0;
+                for (int j = 0; j < i; ++j) before += (int) sh.tmp[j];
+                sh.prefix[i] = before;
+            }
+            __syncthreads();
+        } else block_exclusive_scan(sh.prefix, P);
         total = (long long) sh.prefix[P] * rs;
     } else {
         __syncthreads();
@@ -375,13 +672,21 @@ __global__ void __launch_bounds__(MV_THREADS, 2) mv_grp_kernel(MvParams a, KCons
 #pragma unroll
             for (int t = 0; t < GRP_NT; ++t) pid[t] = (int) (sh.key[u + (t < n ? t : 0)] & 1023u);
             slice = (int) (sh.key[u] >> 10);
-        } else slice = a.sel ? a.sel[u] : 0;
+        } else slice = rf.logits ? sh.r_ind[u] : (a.sel ? a.sel[u] : 0);
         const int s_lo = u == u_first ? s_first : 0, s_hi = u == u_last ? s_last : rs;
         if (s_lo < s_hi) {
+            // Two chains of dependent loads start here and run side by side: pair -> input row -> inputs (this thread's share of
+            // the staging, held in registers), and slice -> stream addresses -> this warp's first streams.
+            const int per = lpr * 4, n_stage = n * per;
+            float xin[16];
+            int e0 = threadIdx.x, t0 = e0 / per, rem0 = e0 - t0 * per;
+            if (e0 < n_stage) {
+                const int p = grouped ? (int) (sh.key[u + t0] & 1023u) : u;
+                stage_load(a, a.xrow ? a.xrow[p] : p / a.xdiv, rem0 & (lpr - 1), rem0 >> lpr_log2, xin);
+            }
             const WSlice wa = a.ws ? a.ws[slice] : a.w0;
             WSlice wb = wa;
             if (MODE == MODE_GU) wb = a.wu[slice];
-            // this warp's first streams are requested before the inputs are staged: their latency runs under the staging
             const int st0 = s_lo + warp, r0 = st0 * rpw + ro;
             Chunk ka, kb;
             if (st0 < s_hi && r0 < a.R) {
@@ -390,16 +695,25 @@ __global__ void __launch_bounds__(MV_THREADS, 2) mv_grp_kernel(MvParams a, KCons
             }
             if (staged) __syncthreads();   // the previous unit's inputs are no longer read
             staged = true;
-            for (int i = threadIdx.x; i < n * lpr * 4; i += MV_THREADS) {
-                const int t = i / (lpr * 4), rem = i - t * lpr * 4;
+            if (e0 < n_stage) stage_store(xin, rem0 & (lpr - 1), rem0 >> lpr_log2, sh.sx[t0], sh.ss[t0]);
+            for (int i = threadIdx.x + MV_THREADS; i < n_stage; i += MV_THREADS) {      // units of more than two pairs
+                const int t = i / per, rem = i - t * per;
                 const int p = grouped ? (int) (sh.key[u + t] & 1023u) : u;
-                stage_inputs(a, a.xrow ? a.xrow[p] : p / a.xdiv, rem & (lpr - 1), rem >> lpr_log2, sh.sx[t], sh.sm[t]);
+                stage_load(a, a.xrow ? a.xrow[p] : p / a.xdiv, rem & (lpr - 1), rem >> lpr_log2, xin);
+                stage_store(xin, rem & (lpr - 1), rem >> lpr_log2, sh.sx[t], sh.ss[t]);
             }
             __syncthreads();
-            if (GRP_NT >= 4 && n == 4) unit_rows<MODE, GRP_NT >= 4 ? 4 : 1>(a, kc, sh, wa, wb, pid, s_lo, s_hi, lpr_log2, ka, kb);
-            else if (GRP_NT >= 3 && n == 3) unit_rows<MODE, GRP_NT >= 3 ? 3 : 1>(a, kc, sh, wa, wb, pid, s_lo, s_hi, lpr_log2, ka, kb);
-            else if (GRP_NT >= 2 && n == 2) unit_rows<MODE, GRP_NT >= 2 ? 2 : 1>(a, kc, sh, wa, wb, pid, s_lo, s_hi, lpr_log2, ka, kb);
-            else unit_rows<MODE, 1>(a, kc, sh, wa, wb, pid, s_lo, s_hi, lpr_log2, ka, kb);
+            UnitArgs ua;
+            ua.sa = (const uint4*) wa.p[0]; ua.ca = (const uint4*) wa.p[1]; ua.da = (const uint32_t*) wa.p[3]; ua.eba = wa.eb;
+            ua.sb = (const uint4*) wb.p[0]; ua.cb = (const uint4*) wb.p[1]; ua.db = (const uint32_t*) wb.p[3]; ua.ebb = wb.eb;
+            ua.y = a.y; ua.ys = a.ys; ua.R = a.R; ua.raw = a.raw; ua.add = a.add;
+#pragma unroll
+            for (int t = 0; t < 4; ++t) ua.pid[t] = pid[t < GRP_NT ? t : 0];
+            ua.s_lo = s_lo; ua.s_hi = s_hi; ua.lpr_log2 = lpr_log2;
+            if (GRP_NT >= 4 && n == 4) unit_rows<MODE, GRP_NT >= 4 ? 4 : 1>(ua, ka, kb);
+            else if (GRP_NT >= 3 && n == 3) unit_rows<MODE, GRP_NT >= 3 ? 3 : 1>(ua, ka, kb);
+            else if (GRP_NT >= 2 && n == 2) unit_rows<MODE, GRP_NT >= 2 ? 2 : 1>(ua, ka, kb);
+            else unit_rows<MODE, 1>(ua, ka, kb);
         }
         u += n;
     }
@@ -618,11 +932,21 @@ static void launch_smemx(cudaStream_t s, const MvParams& a, int lpr_log2, int de
     launch(mv_smemx_kernel<MODE, NT>, grid, MV_THREADS, smem, s, a, kconst(), lpr_log2, dense);
 }
 
+// Lists of more than GRP_MIN_PAIRS pairs go to the grouped kernel (one expansion per distinct slice, up to GRP_NT pairs a
+// unit): its plan and its costlier second pair pay once a good share of the pairs meet on a slice -- an expert-parallel
+// rank's list or all of a 64-row batch; a decode step's 8 .. 64 pairs over 128 experts run faster pair by pair.
+constexpr int GRP_MIN_PAIRS = 64;
+static int g_grp_min_pairs = GRP_MIN_PAIRS;
+
 template <int MODE>
 static void launch_grp(cudaStream_t s, const MvParams& a, int lpr_log2, const RouteFuse& rf) {
+    if (a.P <= g_grp_min_pairs || rf.logits) {
+        launch(mv_pair_kernel<MODE>, sm_count() * 2, MV_THREADS, 0, s, a, kconst(), lpr_log2, rf);
+        return;
+    }
     static bool attr_set[16];
     allow_smem(mv_grp_kernel<MODE>, attr_set, sizeof(GrpShared));
-    launch(mv_grp_kernel<MODE>, sm_count() * 2, MV_THREADS, sizeof(GrpShared), s, a, kconst(), lpr_log2, rf);
+    launch(mv_grp_kernel<MODE>, sm_count() * NSL_GRP_MINB, MV_THREADS, sizeof(GrpShared), s, a, kconst(), lpr_log2, rf);
 }
 
 // The streams of a slice given by value (a dense call) can be checked on the host; slices in a device table are the
@@ -757,6 +1081,7 @@ void nsl_mv_sel_rows(cudaStream_t s, const WSlice* ws, int K, int R, const float
     MvParams a = {ws, NULL, WSlice{}, sel, x, y, G, K, R, max_pairs, 1, xs, ys, 0, raw, NULL, count, 0};
     launch_mv<MODE_ROUND>(s, a, 1);
 }
+
 
 void nsl_decode_f32(cudaStream_t s, WSlice w, int K, int R, float* out, const uint32_t* G) {
     if (K <= 0 || K % 8 || R <= 0) { if (K % 8) set_error("nsl_decode_f32: K = %d is not a multiple of 8", K); return; }

@@ -157,6 +157,20 @@ PROTOTYPES = {
     "nsl_ep_p2p_combine": (None, [_vp, NslEpWindow, _vp, _vp, _vp, _i]),
     "nsl_ep_p2p_reduce": (None, [_vp, NslEpWindow, _i, _vp]),
     "nsl_ep_p2p_status": (_i, [NslEpWindow]),
+    # include/nslm_cache.h
+    "nsl_xcache_create": (_vp, [_i, _i, _vp, _i]),
+    "nsl_xcache_destroy": (None, [_vp]),
+    "nsl_xcache_host_unit": (_vp, [_vp, _i]),
+    "nsl_xcache_offset": (C.c_uint32, [_vp, _i, _i]),
+    "nsl_xcache_unit_bytes": (C.c_uint64, [_vp]),
+    "nsl_xcache_finish": (_i, [_vp, _vp]),
+    "nsl_xcache_table": (_vp, [_vp, _i, _i]),
+    "nsl_xcache_pool": (_vp, [_vp]),
+    "nsl_xcache_fetch": (_i, [_vp, _vp, _i, _vp, _i, _i]),
+    "nsl_xcache_prefetch": (_i, [_vp, _vp, _i, _i]),
+    "nsl_xcache_layer_start": (_i, [_vp, _vp, _i, _i]),
+    "nsl_xcache_stats": (_i, [_vp, _vp, _vp, _vp, _vp, _vp]),
+    "nsl_xcache_set_ops": (None, [_vp]),
 }
 
 _lib = None

@@ -103,7 +103,7 @@ def test_config2_layer_rows_against_oracle(oracle, cfg2):
             acc = acc + wt[t, j] * dn
         scale = np.max(np.abs(acc))
         assert np.max(np.abs(out[t] - acc)) <= 4e-3 * scale       # a bf16 flip of one intermediate moves an output by < 1 bf16 ulp
-        assert np.mean(np.abs(out[t] - acc) <= 1e-5 * scale) > 0.97
+        assert np.mean(np.abs(out[t] - acc) <= 1e-5 * scale) > 0.85   # four bf16 stores in a row over K = 2048: more flips than at decode
     # and against the CPU reference forward (f32 weights, no rounding points): the prompt path's bf16 weights and stores
     ref, rind, _ = oracle.moe_layer(h, x[:2], logits[:2], k)
     assert np.array_equal(rind, ind[:2])

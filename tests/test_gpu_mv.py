@@ -147,10 +147,10 @@ def test_other_formats_are_refused_loudly(oracle):
 
 
 @pytest.mark.parametrize("R,K,S,P", [(96, 2048, 5, 23), (512, 2048, 12, 64), (2048, 512, 12, 64), (40, 64, 3, 9), (64, 256, 20, 20),
-                                     (16, 128, 7, 1300)])
+                                     (96, 2048, 5, 200), (256, 512, 40, 330), (16, 128, 7, 1300)])
 def test_pairs_that_share_a_slice_share_its_expansion_and_change_nothing(oracle, R, K, S, P):
-    """The kernels sort a call's pairs by slice and expand a slice's rows once for up to four pairs (lists of more than 1024
-    pairs run ungrouped).  Every pair's row must equal the same pair computed ALONE, bit for bit, whatever pairs share
+    """Lists of more than 64 pairs are sorted by slice and a slice's rows expanded once for two pairs at a time (shorter lists
+    run pair by pair, lists of more than 1024 pairs ungrouped).  Every pair's row must equal the same pair computed ALONE, bit for bit, whatever pairs share
     the call: for the gate+up form (f32 and packed bf16 inputs, input row by pair / xdiv or by a row index, a device-side
     pair count) and the gather form (rounded and raw)."""
     from nanoseedlm_b200 import kernels
