@@ -592,6 +592,46 @@ def measure_attn(K, W):
     return {"ms_per_step": ms, "tokens": NSEQ, "bytes": 2 * NSEQ * CTX * NKV * 128 * 2 + 3 * NSEQ * NH * 128 * 4}
 
 
+def measure_upload(K, W):
+    """The expert cache's upload paths on config 1's shape: 4 layers x 128 experts in the pinned arena (0.9 GB), 256 slots in
+    VRAM; every step asks for 52 experts (a config-1 verify batch's distinct experts) of the next layer, so that nearly all
+    of them are misses; time on the consumer stream from before the admit until the units are usable."""
+    import torch
+    from nanoseedlm_b200 import cache, lib as L
+    NL, SL, NREQ = 4, 256, 52
+    xc = cache.ExpertCache.random(NL, E, D, FF, SL)
+    rng = np.random.default_rng(3)
+    reqs = [torch.from_numpy(np.sort(rng.choice(E, NREQ, replace=False)).astype(np.int32)).cuda() for _ in range(16)]
+    stream = torch.cuda.Stream()
+    out = {"workload": f"expert-cache upload: {NL} layers x {E} experts of {xc.unit_bytes} B pinned on the host, {SL} VRAM slots, "
+                       f"{NREQ} experts of the next layer requested per step", "unit_bytes": int(xc.unit_bytes)}
+    with torch.cuda.stream(stream):
+        for mode, name in ((cache.KERNEL, "copy_kernel"), (cache.DMA, "dma_side_stream")):
+            steps = max(8, min(K, 40))
+            for i in range(W):
+                xc.fetch(stream.cuda_stream, i % NL, reqs[i % 16].data_ptr(), NREQ, mode)
+            stream.synchronize()
+            st0 = xc.stats()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0 = time.perf_counter()
+            e0.record(stream)
+            for i in range(steps):
+                xc.fetch(stream.cuda_stream, (W + i) % NL, reqs[(W + i) % 16].data_ptr(), NREQ, mode)
+            e1.record(stream)
+            e1.synchronize()
+            wall = time.perf_counter() - t0
+            st1 = xc.stats()
+            units, nbytes = st1["units"] - st0["units"] if mode == cache.DMA else st1["misses"] - st0["misses"], 0
+            nbytes = units * xc.unit_bytes
+            ms = e0.elapsed_time(e1)
+            out[name] = {"steps": steps, "units_uploaded": int(units), "us_per_unit": ms * 1e3 / max(units, 1), "pcie_gbs": nbytes / (ms * 1e-3) / 1e9,
+                         "ms_per_step": ms / steps, "host_ms_per_step": wall * 1e3 / steps,
+                         "runs": int(st1["runs"] - st0["runs"]) if mode == cache.DMA else None}
+    L.check()
+    xc.close()
+    return out
+
+
 # ---- config 3: expert-parallel decode ---------------------------------------------------------------------------------------
 EP_E, EP_K, EP_B = 512, 10, 64   # BASELINE config 3: 512 routed experts sharded over the ranks, 64 sequences x 1 token, top-10
 
@@ -783,7 +823,7 @@ def main():
     ap.add_argument("--ep-mirror", type=int, default=0,
                     help="config 3, p2p, even rank counts: 1 = ranks r and r + N/2 hold each other's experts too and split their "
                          "joint pairs in the middle (balance to within one pair; twice the expert bytes per GPU)")
-    ap.add_argument("--workload", default=None, choices=["cfg0", "cfg1", "cfg2", "cfg3", "lmhead", "attn"],
+    ap.add_argument("--workload", default=None, choices=["cfg0", "cfg1", "cfg2", "cfg3", "lmhead", "attn", "upload"],
                     help="one workload alone as the line (profiling): cfg1 one GPU's MoE decode layer; cfg2 the same layer on 512 "
                          "prompt rows (grouped tcgen05 GEMM); cfg3 expert-parallel decode (the default at >1 GPU); cfg0 / lmhead / attn")
     args = ap.parse_args()
@@ -819,7 +859,7 @@ def main():
             dist.destroy_process_group()
         return
 
-    if workload in ("cfg0", "lmhead", "attn"):      # one secondary workload alone
+    if workload in ("cfg0", "lmhead", "attn", "upload"):      # one secondary workload alone
         print(json.dumps(dict(base, **secondary(workload, K, W, peaks, peak_kind, sms, args))))
         return
 
@@ -852,7 +892,7 @@ def main():
     del c, r
     torch.cuda.empty_cache()
     if extra:
-        for name in ("cfg0", "lmhead", "attn"):
+        for name in ("cfg0", "lmhead", "attn", "upload"):
             line["workloads"][name] = secondary(name, min(K, 1000), W, peaks, peak_kind, sms, args, sm_mhz=clocks.get("sm_mhz"))
             torch.cuda.empty_cache()
         rr = measure_ep(args, min(K, 400), W)
@@ -875,6 +915,8 @@ def secondary(name, K, W, peaks, peak_kind, sms, args, sm_mhz=None):
         if not args.no_cpu:
             out["cpu_baseline"] = cpu_cfg0_protocol()
         return out
+    if name == "upload":
+        return measure_upload(K, W)
     if name == "lmhead":
         r = measure_lmhead(8, min(K, 300), W)
         gbs = r["bytes"] / (r["mv_us"] * 1e-6) / 1e9

@@ -11,6 +11,29 @@ KERNEL, DMA = 0, 1
 
 
 class ExpertCache:
+    @classmethod
+    def random(cls, layers, E, d, ff, slots, seed=0):
+        """A cache whose arena holds random bytes (timing of the upload paths; no oracle involved)."""
+        self = cls.__new__(cls)
+        self.lib = L.load()
+        self.layers, self.E, self.d, self.ff = layers, E, d, ff
+        lens = np.zeros((3, 4), np.uint64)
+        for i, (R, K) in enumerate(((ff, d), (ff, d), (d, ff))):
+            lens[i] = [R * K // 8 * 2, R * K // 8 * 2, 0, R * K // 16]
+        self.h = self.lib.nsl_xcache_create(layers, E, lens.ctypes.data, slots)
+        if not self.h:
+            raise RuntimeError(L.last_error() or "nsl_xcache_create failed")
+        ub = self.unit_bytes = self.lib.nsl_xcache_unit_bytes(self.h)
+        rng = np.random.default_rng(seed)
+        whole = np.ctypeslib.as_array(C.cast(self.lib.nsl_xcache_host_unit(self.h, 0), C.POINTER(C.c_uint8)), (ub * layers * E,))
+        block = rng.integers(0, 256, 1 << 24, dtype=np.uint8)
+        for o in range(0, whole.size, block.size):
+            n = min(block.size, whole.size - o)
+            whole[o:o + n] = block[:n]
+        if self.lib.nsl_xcache_finish(self.h, None):
+            raise RuntimeError(L.last_error() or "nsl_xcache_finish failed")
+        return self
+
     def __init__(self, host_layers, slots):
         """host_layers: moe.HostLayer objects of one shape (every expert's gate / up / down streams on the host)."""
         self.lib = L.load()
