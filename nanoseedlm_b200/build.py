@@ -7,7 +7,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libnslm_b200.so")
-SOURCES = ["common.cu", "seed_mv.cu", "moe_misc.cu", "seed_gemm.cu", "moe_host.cu", "ep.cu", "ep_p2p.cu", "mova.cu", "q4_head.cu", "pack.cu", "attn.cu", "xcache.cu"]
+SOURCES = ["common.cu", "seed_mv.cu", "moe_misc.cu", "seed_gemm.cu", "moe_host.cu", "ep.cu", "ep_p2p.cu", "mova.cu", "q4_head.cu", "pack.cu", "attn.cu", "xcache.cu", "decoder_ops.cu", "decoder.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
               "-Xptxas", "-v"]
 
@@ -26,7 +26,7 @@ def _stale(target, deps):
 def build_library(force=False, verbose=False):
     """Compile every .cu under csrc/ to an object (in parallel) and link the shared library.  Returns its path."""
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
-    headers += [os.path.join(HERE, "..", "include", h) for h in ("nslm_kernels.h", "nslm_moe.h", "nslm_ep.h", "nslm_pack.h", "nslm_cache.h")]
+    headers += [os.path.join(HERE, "..", "include", h) for h in ("nslm_kernels.h", "nslm_moe.h", "nslm_ep.h", "nslm_pack.h", "nslm_cache.h", "nslm_decoder.h")]
     objdir = os.path.join(HERE, "build")
     os.makedirs(objdir, exist_ok=True)
     procs, objs = [], []

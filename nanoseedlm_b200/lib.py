@@ -157,6 +157,19 @@ PROTOTYPES = {
     "nsl_ep_p2p_combine": (None, [_vp, NslEpWindow, _vp, _vp, _vp, _i]),
     "nsl_ep_p2p_reduce": (None, [_vp, NslEpWindow, _i, _vp]),
     "nsl_ep_p2p_status": (_i, [NslEpWindow]),
+    # include/nslm_decoder.h
+    "nsl_decoder_create": (_vp, [_vp, _vp, WSlice, _vp, WSlice, _vp, _vp]),
+    "nsl_decoder_destroy": (None, [_vp]),
+    "nsl_decoder_step": (_i, [_vp, _vp, _vp, _vp, _i, _vp]),
+    "nsl_decoder_hidden": (_vp, [_vp]),
+    "nsl_decoder_logits": (_vp, [_vp]),
+    "nsl_decoder_copy_out": (_i, [_vp, _i, _i, _vp]),
+    "nsl_decoder_kcache": (_vp, [_vp, _i]),
+    "nsl_decoder_vcache": (_vp, [_vp, _i]),
+    "nsl_residual_add": (None, [_vp, _vp, _vp, _sz]),
+    "kc_embed": (None, [_vp, _i, WSlice, _i, _vp, _vp, _i]),
+    "kc_gnorm": (None, [_vp, _i, C.c_float, _vp, _vp, _vp, _i]),
+    "kc_rope_kv": (None, [_vp, _vp, _vp, _vp, KvView, _vp, _vp, _i, _i, _i]),
     # include/nslm_cache.h
     "nsl_xcache_create": (_vp, [_i, _i, _vp, _i]),
     "nsl_xcache_destroy": (None, [_vp]),
