@@ -632,6 +632,121 @@ def measure_upload(K, W):
     return out
 
 
+# ---- config 4: the whole synthetic decoder ---------------------------------------------------------------------------------
+C4 = dict(n_layer=48, d=D, n_head=16, n_kv=2, n_exp=512, top_k=10, ff_exp=FF, ff_shared=FF, vocab=151936, ctx=4096)
+C4_BATCH = 32
+
+
+def c4_config(world, layers):
+    return {"workload": f"BASELINE config 4: random-init synthetic MoE decoder, {layers} layers, hidden {D}, GQA 16 query / 2 KV heads of 128, BF16 KV "
+                        f"cache with 4096 prefilled positions, 512 seed-encoded routed experts (top-10) + 1 shared expert per layer, vocab 151936 "
+                        f"with an affine int4 LM head, decode at batch {C4_BATCH}, experts sharded over {world} GPU(s)",
+            "tokens": C4_BATCH, "experts": 512, "top_k": 10, "hidden": D, "intermediate": FF, "layers": layers, "parallelism": f"ep{world}"}
+
+
+def measure_cfg4(args, K, W):
+    """One decode step of the whole decoder for 32 sequences at position 4095 (the rows split over the ranks, the routed experts
+    sharded over them), replayed as a CUDA graph; tokens/s = 32 / the step time (max over ranks)."""
+    import torch
+    import torch.distributed as dist
+    from nanoseedlm_b200 import decoder, ep, lib as L
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    c = dict(C4, n_layer=args.c4_layers)
+    T = C4_BATCH // world
+    e_loc = c["n_exp"] // world
+    cfg = decoder.make_cfg(max_rows=T, exp_lo=rank * e_loc, exp_hi=(rank + 1) * e_loc, **c)
+    win = ep.P2PWindow.create(world, rank, T, D, c["top_k"]) if world > 1 else None
+    dec = decoder.random_decoder(cfg, seed=11, win=win)
+    gen = torch.Generator(device="cuda").manual_seed(100 + rank)
+    n = T * c["ctx"] * c["n_kv"] * 128
+    for l in range(c["n_layer"]):      # the prefilled context
+        kk = torch.randn(n, generator=gen, device="cuda").to(torch.bfloat16)
+        dec.fill_cache(l, kk, kk.flip(0))
+    del kk
+    pos, kv0 = [c["ctx"] - 1] * T, [t * c["ctx"] for t in range(T)]
+    ri = decoder.row_info(pos, kv0)
+    hid = torch.randint(0, c["vocab"], (8, T), generator=gen, device="cuda", dtype=torch.int32)
+    pin = hid.cpu().pin_memory()
+    ids = torch.zeros(T, dtype=torch.int32, device="cuda")
+    nxt = torch.zeros(T, dtype=torch.int32, device="cuda")
+    pnext = torch.zeros(T, dtype=torch.int32).pin_memory()
+    stream = torch.cuda.Stream()
+    lib = L.load()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    with torch.cuda.stream(stream):
+        launches0 = lib.nsl_launch_count()
+        dec.step(ids, ri, T, nxt, stream.cuda_stream)
+        stream.synchronize()
+        launches = lib.nsl_launch_count() - launches0
+        for _ in range(W):
+            dec.step(ids, ri, T, nxt, stream.cuda_stream)
+        stream.synchronize()
+        captured = not args.no_graph
+        if captured:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream, capture_error_mode="thread_local"):
+                dec.step(ids, ri, T, nxt, stream.cuda_stream)
+            run = g.replay
+        else:
+            run = lambda: dec.step(ids, ri, T, nxt, stream.cuda_stream)
+        run()
+        stream.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local) as clocks:
+            e0.record(stream)
+            for i in range(K):
+                ids.copy_(hid[i % 8], non_blocking=True)
+                run()
+            e1.record(stream)
+            e1.synchronize()
+        ms = e0.elapsed_time(e1) / K
+        # e2e: this step's token ids from pinned host memory, the next tokens back to the host, every step
+        if world > 1:
+            dist.barrier()
+        KE = max(3, min(K, 20))
+        t0 = time.perf_counter()
+        for i in range(KE):
+            ids.copy_(pin[i % 8], non_blocking=True)
+            run()
+            pnext.copy_(nxt, non_blocking=True)
+            stream.synchronize()
+        e2e_s = (time.perf_counter() - t0) / KE
+    if world > 1:
+        t = torch.tensor([ms, e2e_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_s = float(t[0].item()), float(t[1].item())
+    L.check()
+    status = 0
+    if win is not None:
+        status = win.status()
+        t = torch.tensor([status], device="cuda", dtype=torch.int64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        status = int(t.item())
+        dist.barrier()
+    toks = nxt.cpu().numpy()
+    dec.close()
+    if win is not None:
+        win.close()
+    torch.cuda.empty_cache()
+    if status:
+        raise SystemExit(f"config 4: a wait of the expert-parallel exchange ran out (status {status}); the timing is void")
+    if rank != 0:
+        return None
+    return {"value": C4_BATCH / (ms * 1e-3), "unit": "tok/s", "ms_per_step": ms, "gpu_launches": int(launches) * K, "cuda_graph": captured,
+            "clocks": clocks.summary(), "config": c4_config(world, c["n_layer"]),
+            "e2e": {"value": C4_BATCH / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 4 * T, "d2h_bytes_per_step": 4 * T, "ms_per_step": e2e_s * 1e3,
+                    "steps_in_flight": 1},
+            "next_tokens_in_vocab": bool(((toks >= 0) & (toks < c["vocab"])).all()),
+            "packed_bytes_per_gpu": c["n_layer"] * e_loc * 3 * BYTES_PER_MATRIX}
+
+
 # ---- config 3: expert-parallel decode ---------------------------------------------------------------------------------------
 EP_E, EP_K, EP_B = 512, 10, 64   # BASELINE config 3: 512 routed experts sharded over the ranks, 64 sequences x 1 token, top-10
 
@@ -815,6 +930,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="N = 1: the headline only, without the `workloads` and `ep_base` objects")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--c4-layers", type=int, default=48, help="config 4: decoder layers (48 = the configuration; fewer only for profiling)")
     ap.add_argument("--no-dependent-launch", action="store_true",
                     help="config 1: ordinary launches instead of programmatic dependent launches (for comparison)")
     ap.add_argument("--ep-collectives", default="p2p", choices=["p2p", "a2a", "gather"],
@@ -823,7 +939,7 @@ def main():
     ap.add_argument("--ep-mirror", type=int, default=0,
                     help="config 3, p2p, even rank counts: 1 = ranks r and r + N/2 hold each other's experts too and split their "
                          "joint pairs in the middle (balance to within one pair; twice the expert bytes per GPU)")
-    ap.add_argument("--workload", default=None, choices=["cfg0", "cfg1", "cfg2", "cfg3", "lmhead", "attn", "upload"],
+    ap.add_argument("--workload", default=None, choices=["cfg0", "cfg1", "cfg2", "cfg3", "cfg4", "lmhead", "attn", "upload"],
                     help="one workload alone as the line (profiling): cfg1 one GPU's MoE decode layer; cfg2 the same layer on 512 "
                          "prompt rows (grouped tcgen05 GEMM); cfg3 expert-parallel decode (the default at >1 GPU); cfg0 / lmhead / attn")
     args = ap.parse_args()
@@ -855,6 +971,15 @@ def main():
         if rank == 0:
             line = dict(base, value=r.pop("value"), ms_per_step=r.pop("ms_per_step"), config=ep_config(world), workload_id="cfg3", **r)
             print(json.dumps(line))
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    if workload == "cfg4":
+        r = measure_cfg4(args, min(K, 30), min(W, 3))
+        if rank == 0:
+            print(json.dumps(dict(base, metric="synthetic_moe_decoder_tokens_per_s", value=r.pop("value"), ms_per_step=r.pop("ms_per_step"),
+                                  config=r.pop("config"), workload_id="cfg4", steps=min(K, 30), warmup=min(W, 3), **r)))
         if world > 1:
             dist.destroy_process_group()
         return
@@ -895,6 +1020,13 @@ def main():
         for name in ("cfg0", "lmhead", "attn", "upload"):
             line["workloads"][name] = secondary(name, min(K, 1000), W, peaks, peak_kind, sms, args, sm_mhz=clocks.get("sm_mhz"))
             torch.cuda.empty_cache()
+        try:      # the whole decoder of config 4 on this one GPU (44 GB of experts): reported, with its error if it cannot run
+            r4 = measure_cfg4(args, 10, 2)
+            line["workloads"]["cfg4"] = {k_: r4[k_] for k_ in ("value", "unit", "ms_per_step", "e2e", "gpu_launches", "cuda_graph", "next_tokens_in_vocab")}
+            line["workloads"]["cfg4"]["workload"] = r4["config"]["workload"]
+        except Exception as ex:      # noqa: BLE001
+            line["workloads"]["cfg4"] = {"error": repr(ex)}
+        torch.cuda.empty_cache()
         rr = measure_ep(args, min(K, 400), W)
         line["ep_base"] = {"workload": ep_config(1)["workload"], "value": rr["value"], "unit": "tok/s", "ms_per_step": rr["ms_per_step"],
                            "e2e": rr["e2e"], "parity": rr["parity"], "roofline": rr["roofline"],

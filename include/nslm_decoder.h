@@ -52,6 +52,8 @@ int nsl_decoder_copy_out(NslDecoder* m, int what, int T, float* dst);
 /* Layer l's KV cache (BF16 [max_rows * ctx][n_kv][128] each), to prefill or inspect. */
 uint16_t* nsl_decoder_kcache(NslDecoder* m, int layer);
 uint16_t* nsl_decoder_vcache(NslDecoder* m, int layer);
+/* Copies n BF16 values (device memory) into the start of layer l's K and V caches (a prefilled context for timing). */
+int nsl_decoder_fill_cache(NslDecoder* m, int layer, const uint16_t* k, const uint16_t* v, size_t n);
 /* x = bf16(x + y) over n floats (the residual add of the decoder's stream). */
 void nsl_residual_add(cudaStream_t s, float* x, const float* y, size_t n);
 /* engine/kernels_cuda.h:75  x[t] = row ids[t] of a BF16 table (other table formats are refused). */

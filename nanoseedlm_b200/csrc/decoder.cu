@@ -214,6 +214,12 @@ int nsl_decoder_copy_out(NslDecoder* m, int what, int T, float* dst) {
     return cudaMemcpy(dst, what ? m->lm : m->x, n, cudaMemcpyDeviceToDevice) == cudaSuccess ? 0 : -1;
 }
 uint16_t* nsl_decoder_kcache(NslDecoder* m, int layer) { return layer >= 0 && layer < m->c.n_layer ? m->kc[layer] : NULL; }
+int nsl_decoder_fill_cache(NslDecoder* m, int layer, const uint16_t* k, const uint16_t* v, size_t n) {
+    const size_t cap = (size_t) m->c.max_rows * m->c.ctx * m->c.n_kv * 128;
+    if (layer < 0 || layer >= m->c.n_layer || n > cap) { nsl::set_error("nsl_decoder_fill_cache: layer %d or %zu values out of range", layer, n); return -1; }
+    return cudaMemcpy(m->kc[layer], k, 2 * n, cudaMemcpyDeviceToDevice) == cudaSuccess &&
+           cudaMemcpy(m->vc[layer], v, 2 * n, cudaMemcpyDeviceToDevice) == cudaSuccess ? 0 : -1;
+}
 uint16_t* nsl_decoder_vcache(NslDecoder* m, int layer) { return layer >= 0 && layer < m->c.n_layer ? m->vc[layer] : NULL; }
 
 }   // extern "C"

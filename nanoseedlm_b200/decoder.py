@@ -65,6 +65,11 @@ class Decoder:
             raise RuntimeError("nsl_decoder_copy_out failed")
         return out
 
+    def fill_cache(self, layer, k, v):
+        """k / v: bf16 device tensors copied into the start of the layer's caches."""
+        if self.lib.nsl_decoder_fill_cache(C.c_void_p(self.h), layer, _ptr(k), _ptr(v), k.numel()):
+            raise RuntimeError(L.last_error() or "nsl_decoder_fill_cache failed")
+
     def close(self):
         if self.h:
             self.lib.nsl_decoder_destroy(C.c_void_p(self.h))

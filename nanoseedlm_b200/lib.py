@@ -166,6 +166,7 @@ PROTOTYPES = {
     "nsl_decoder_copy_out": (_i, [_vp, _i, _i, _vp]),
     "nsl_decoder_kcache": (_vp, [_vp, _i]),
     "nsl_decoder_vcache": (_vp, [_vp, _i]),
+    "nsl_decoder_fill_cache": (_i, [_vp, _i, _vp, _vp, _sz]),
     "nsl_residual_add": (None, [_vp, _vp, _vp, _sz]),
     "kc_embed": (None, [_vp, _i, WSlice, _i, _vp, _vp, _i]),
     "kc_gnorm": (None, [_vp, _i, C.c_float, _vp, _vp, _vp, _i]),

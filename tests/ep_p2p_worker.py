@@ -14,6 +14,7 @@ import torch.distributed as dist
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 
 def main():
@@ -76,8 +77,29 @@ def main():
             out = g.step(0, 0)
         stream.synchronize()
     check(torch.equal(out, want), "graphed p2p step differs")
+    # the whole decoder step with its routed experts behind the window: this rank's rows against the same rows through a
+    # decoder that holds every expert locally (same weights on every rank)
+    from nanoseedlm_b200 import decoder
+    import test_gpu_decoder as TD
+    c = dict(TD.CFG, n_exp=8 if 8 % world == 0 else 4 * world)
+    hw = TD.make_weights(oracle, moe, c["n_layer"], c["d"], c["n_head"], c["n_kv"], c["n_exp"], c["ff_exp"], c["ff_shared"], c["vocab"], seed=2)
+    Td, e_loc = 2, c["n_exp"] // world
+    dwin = ep.P2PWindow.create(world, rank, Td, c["d"], c["top_k"])
+    dec_ep = decoder.host_decoder(decoder.make_cfg(max_rows=Td, exp_lo=rank * e_loc, exp_hi=(rank + 1) * e_loc, eps=TD.EPS, theta=TD.THETA, **c), hw, dwin)
+    dec_1 = decoder.host_decoder(decoder.make_cfg(max_rows=Td, eps=TD.EPS, theta=TD.THETA, **c), hw)
+    ids = torch.tensor([3 + rank, 100 + 7 * rank], dtype=torch.int32, device="cuda")
+    n1, n2 = torch.zeros(Td, dtype=torch.int32, device="cuda"), torch.zeros(Td, dtype=torch.int32, device="cuda")
+    for step in range(3):
+        ri = decoder.row_info([step] * Td, [0, c["ctx"]])
+        dec_ep.step(ids, ri, Td, n1)
+        dec_1.step(ids, ri, Td, n2)
+        torch.cuda.synchronize()
+        a, b = dec_ep.hidden(Td).cpu().numpy(), dec_1.hidden(Td).cpu().numpy()
+        check(np.max(np.abs(a - b)) <= 2e-2 * np.max(np.abs(b)) and np.mean(np.abs(a - b) <= 1e-3 * np.max(np.abs(b))) > 0.9,
+              f"decoder step {step}: expert-parallel rows differ from the one-GPU decoder's ({np.max(np.abs(a - b)) / np.max(np.abs(b)):.2e})")
+        ids = n2.clone()
     torch.cuda.synchronize()                                          # this rank's kernels have all finished
-    status = p2p.window.status() or raw.window.status() or (mir.window.status() if mir is not None else 0)
+    status = p2p.window.status() or dwin.status() or raw.window.status() or (mir.window.status() if mir is not None else 0)
     check(status == 0, f"a wait ran out (status {status})")
     check(worst <= 1e-5, f"against the one-GPU layer: {worst}")
     check(worst_oracle <= 1e-3, f"against the oracle: {worst_oracle}")
@@ -86,7 +108,9 @@ def main():
     bad = torch.tensor([len(failures)], device="cuda")
     dist.all_reduce(bad)                                              # every rank has drained and knows the outcome
     dist.barrier()
-    for w in (p2p.window, raw.window) + ((mir.window,) if mir is not None else ()):
+    dec_ep.close()
+    dec_1.close()
+    for w in (p2p.window, raw.window, dwin) + ((mir.window,) if mir is not None else ()):
         w.close()
     dist.barrier()
     if failures:
