@@ -656,7 +656,7 @@ def measure_cfg4(args, K, W):
     c = dict(C4, n_layer=args.c4_layers)
     T = C4_BATCH // world
     e_loc = c["n_exp"] // world
-    cfg = decoder.make_cfg(max_rows=T, exp_lo=rank * e_loc, exp_hi=(rank + 1) * e_loc, **c)
+    cfg = decoder.make_cfg(max_rows=T, exp_lo=rank * e_loc, exp_hi=(rank + 1) * e_loc, dense_bf16=int(not args.c4_dense_seed), **c)
     win = ep.P2PWindow.create(world, rank, T, D, c["top_k"]) if world > 1 else None
     dec = decoder.random_decoder(cfg, seed=11, win=win)
     gen = torch.Generator(device="cuda").manual_seed(100 + rank)
@@ -741,6 +741,9 @@ def measure_cfg4(args, K, W):
         return None
     return {"value": C4_BATCH / (ms * 1e-3), "unit": "tok/s", "ms_per_step": ms, "gpu_launches": int(launches) * K, "cuda_graph": captured,
             "clocks": clocks.summary(), "config": c4_config(world, c["n_layer"]),
+            "dense_matrices": "regenerated from their seeds in every call" if args.c4_dense_seed else
+                              "expanded once at load to BF16 in HBM (27 MB a layer), the values the tensor-core path rounds seed weights to; "
+                              "the routed experts are regenerated from their seeds in every call",
             "e2e": {"value": C4_BATCH / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 4 * T, "d2h_bytes_per_step": 4 * T, "ms_per_step": e2e_s * 1e3,
                     "steps_in_flight": 1},
             "next_tokens_in_vocab": bool(((toks >= 0) & (toks < c["vocab"])).all()),
@@ -930,6 +933,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="N = 1: the headline only, without the `workloads` and `ep_base` objects")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--c4-dense-seed", action="store_true", help="config 4: regenerate the dense matrices from their seeds in every call too")
     ap.add_argument("--c4-layers", type=int, default=48, help="config 4: decoder layers (48 = the configuration; fewer only for profiling)")
     ap.add_argument("--no-dependent-launch", action="store_true",
                     help="config 1: ordinary launches instead of programmatic dependent launches (for comparison)")
@@ -1022,7 +1026,7 @@ def main():
             torch.cuda.empty_cache()
         try:      # the whole decoder of config 4 on this one GPU (44 GB of experts): reported, with its error if it cannot run
             r4 = measure_cfg4(args, 10, 2)
-            line["workloads"]["cfg4"] = {k_: r4[k_] for k_ in ("value", "unit", "ms_per_step", "e2e", "gpu_launches", "cuda_graph", "next_tokens_in_vocab")}
+            line["workloads"]["cfg4"] = {k_: r4[k_] for k_ in ("value", "unit", "ms_per_step", "e2e", "gpu_launches", "cuda_graph", "next_tokens_in_vocab", "dense_matrices")}
             line["workloads"]["cfg4"]["workload"] = r4["config"]["workload"]
         except Exception as ex:      # noqa: BLE001
             line["workloads"]["cfg4"] = {"error": repr(ex)}

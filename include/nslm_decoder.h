@@ -24,6 +24,10 @@ typedef struct {
     int32_t vocab, max_rows, ctx;              /* rows per step at most; positions per sequence slot */
     int32_t exp_lo, exp_hi;                    /* the routed experts this rank holds (0, n_exp on one GPU) */
     float eps, rope_theta;
+    int32_t dense_bf16;                        /* 1: the dense matrices (q, k, v, o, router, shared expert) are expanded ONCE at
+                                                  creation to BF16 in device memory (the values the tensor-core path rounds seed
+                                                  weights to, engine/kernels_moe.cu:405-412) and served from there; 0: regenerated
+                                                  from their seeds in every call, as the routed experts always are */
 } NslDecoderCfg;
 
 typedef struct {                               /* one layer's weights in device memory (the caller owns them) */

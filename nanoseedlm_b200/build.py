@@ -7,7 +7,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libnslm_b200.so")
-SOURCES = ["common.cu", "seed_mv.cu", "moe_misc.cu", "seed_gemm.cu", "moe_host.cu", "ep.cu", "ep_p2p.cu", "mova.cu", "q4_head.cu", "pack.cu", "attn.cu", "xcache.cu", "decoder_ops.cu", "decoder.cu"]
+SOURCES = ["common.cu", "seed_mv.cu", "moe_misc.cu", "seed_gemm.cu", "moe_host.cu", "ep.cu", "ep_p2p.cu", "mova.cu", "q4_head.cu", "pack.cu", "attn.cu", "xcache.cu", "decoder_ops.cu", "decoder.cu", "dense_bf16.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
               "-Xptxas", "-v"]
 

@@ -59,6 +59,8 @@ void nsl_decoder_destroy(NslDecoder* m) {
     delete m;
 }
 
+static bool expand_dense(NslDecoder* m, WSlice& w, int K, int R);
+
 NslDecoder* nsl_decoder_create(const NslDecoderCfg* cfg, const NslDecoderLayer* layers, WSlice embed, const uint16_t* norm_out,
                                WSlice head, const uint32_t* G, const NslEpWindow* win) {
     const NslDecoderCfg& c = *cfg;
@@ -109,11 +111,21 @@ NslDecoder* nsl_decoder_create(const NslDecoderCfg* cfg, const NslDecoderLayer* 
     if (ok) {
         std::vector<float> inv(64), ones(T, 1.0f);
         for (int p = 0; p < 64; ++p) inv[p] = (float) std::pow((double) c.rope_theta, -(double) p / 64.0);
-        std::vector<WSlice> st(2 * (size_t) c.n_layer);
+        std::vector<WSlice> st(2 * (size_t) c.n_layer);      // (the seed form: used when the dense matrices are not expanded)
         for (int l = 0; l < c.n_layer; ++l) { st[2 * l] = layers[l].sg; st[2 * l + 1] = layers[l].su; }
         ok = cudaMemcpy(m->inv, inv.data(), 256, cudaMemcpyHostToDevice) == cudaSuccess &&
              cudaMemcpy(m->ones, ones.data(), 4 * T, cudaMemcpyHostToDevice) == cudaSuccess &&
              cudaMemcpy(m->shared_tab, st.data(), sizeof(WSlice) * st.size(), cudaMemcpyHostToDevice) == cudaSuccess;
+    }
+    if (ok && c.dense_bf16) {
+        const int dd = c.d, HQi = c.n_head * 128, HKi = c.n_kv * 128;
+        for (int l = 0; ok && l < c.n_layer; ++l) {
+            NslDecoderLayer& Ly = m->L[l];
+            ok = expand_dense(m, Ly.wq, dd, HQi) && expand_dense(m, Ly.wk, dd, HKi) && expand_dense(m, Ly.wv, dd, HKi) && expand_dense(m, Ly.wo, HQi, dd) &&
+                 expand_dense(m, Ly.router, dd, c.n_exp + 1) && expand_dense(m, Ly.sg, dd, c.ff_shared) && expand_dense(m, Ly.su, dd, c.ff_shared) &&
+                 expand_dense(m, Ly.sd, c.ff_shared, dd);
+        }
+        ok = ok && cudaDeviceSynchronize() == cudaSuccess;
     }
     if (!ok) {
         nsl::set_error("nsl_decoder_create: out of memory");
@@ -126,8 +138,21 @@ NslDecoder* nsl_decoder_create(const NslDecoderCfg* cfg, const NslDecoderLayer* 
 
 // y (+)= W x for T rows: the mat-vec for up to MV_MAXT rows, the tensor-core GEMM beyond (engine/qwen4_cuda.c: mv()).
 static void dense(NslDecoder* m, cudaStream_t s, const WSlice& w, int K, int R, const float* x, float* y, int T, int add) {
-    if (T <= MV_MAXT) kc_mv(s, MF_SEED4P4, w, K, R, x, K, y, R, T, add, m->G);
-    else kc_mm(s, MF_SEED4P4, w, K, R, x, K, y, R, T, add, m->G);
+    const int fmt = m->c.dense_bf16 ? MF_BF16 : MF_SEED4P4;
+    if (T <= MV_MAXT) kc_mv(s, fmt, w, K, R, x, K, y, R, T, add, m->G);
+    else kc_mm(s, fmt, w, K, R, x, K, y, R, T, add, m->G);
+}
+
+// A dense SEED4P4 matrix expanded once to BF16 [R][K] in device memory; w then points at the expansion.
+static bool expand_dense(NslDecoder* m, WSlice& w, int K, int R) {
+    uint16_t* out = (uint16_t*) dec_alloc(m, 2 * (size_t) R * K);
+    if (!out) return false;
+    nsl_decode_bf16(0, w, K, R, out, m->G);
+    WSlice b;
+    memset(&b, 0, sizeof b);
+    b.p[0] = out;
+    w = b;
+    return true;
 }
 
 int nsl_decoder_step(NslDecoder* m, cudaStream_t s, const int32_t* ids, const RowInfo* ri, int T, int32_t* next) {
@@ -159,14 +184,14 @@ int nsl_decoder_step(NslDecoder* m, cudaStream_t s, const int32_t* ids, const Ro
         cudaStreamWaitEvent(m->s2, m->ev_x, 0);
         {
             nsl::PdlScope off(false);      // the side stream's first kernel follows an event, not a kernel
-            if (T <= MV_MAXT) {
+            if (T <= MV_MAXT && !c.dense_bf16) {
                 kc_mv_gu(m->s2, MF_SEED4P4, m->shared_tab + 2 * l, m->shared_tab + 2 * l + 1, d, fs, m->h, d, m->As, fs, m->zero_sel, T, 1, m->G);
                 kc_mv(m->s2, MF_SEED4P4, L.sd, fs, d, m->As, fs, m->sh, d, T, 0, m->G);
             } else {
-                kc_mm(m->s2, MF_SEED4P4, L.sg, d, fs, m->h, d, m->Gs, fs, T, 0, m->G);
-                kc_mm(m->s2, MF_SEED4P4, L.su, d, fs, m->h, d, m->Us, fs, T, 0, m->G);
+                dense(m, m->s2, L.sg, d, fs, m->h, m->Gs, T, 0);
+                dense(m, m->s2, L.su, d, fs, m->h, m->Us, T, 0);
                 kc_swiglu(m->s2, m->Gs, m->Us, m->As, T * fs);
-                kc_mm(m->s2, MF_SEED4P4, L.sd, fs, d, m->As, fs, m->sh, d, T, 0, m->G);
+                dense(m, m->s2, L.sd, fs, d, m->As, m->sh, T, 0);
             }
         }
         cudaEventRecord(m->ev_sh, m->s2);

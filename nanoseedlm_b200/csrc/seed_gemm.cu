@@ -123,7 +123,7 @@ __device__ __forceinline__ QuadIn load_quad(const WSlice& w, int row, int kb, in
     return q;
 }
 
-template <int NT>
+template <int NT, bool BF16W>
 __global__ void __launch_bounds__(GM_THREADS, 2) seed_gemm_kernel(MmParams a, KConst kc) {
     if (a.ntiles && (int) blockIdx.y >= *a.ntiles) return;
     extern __shared__ uint8_t smem_raw[];
@@ -156,7 +156,7 @@ __global__ void __launch_bounds__(GM_THREADS, 2) seed_gemm_kernel(MmParams a, KC
     const int r0 = (int) blockIdx.x * GM_BM;
     const int NB = a.K / 8, KT = (a.K + GM_BK - 1) / GM_BK;
 
-    load_stream_tab(tab, a.G, tid, GM_THREADS);
+    if (!BF16W) load_stream_tab(tab, a.G, tid, GM_THREADS);
     if (tid < GM_BN) {
         const bool ok = tid < count;
         srow[tid] = !ok ? -1 : a.grouped ? a.perm[start + tid] / a.xdiv : start + tid;
@@ -185,11 +185,25 @@ __global__ void __launch_bounds__(GM_THREADS, 2) seed_gemm_kernel(MmParams a, KC
         const int prow = tid >> 1, half = tid & 1;
         const int grow = r0 + prow;
         const bool vec = (NB & 3) == 0;
-        QuadIn cur = load_quad(w, grow, half * 4, a.R, NB, vec), nxt = cur;
+        QuadIn cur = {{0u, 0u}, {0u, 0u}, 0u, false}, nxt = cur;
+        uint4 bcur[4], bnxt[4];      // BF16 weights: this thread's 32 values of the K step, as stored
+        auto load_bf16 = [&](int kt, uint4* o) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int k = kt * GM_BK + half * 32 + 8 * i;
+                o[i] = grow < a.R && k < a.K ? __ldg((const uint4*) ((const uint16_t*) w.p[0] + (size_t) grow * a.K + k)) : make_uint4(0u, 0u, 0u, 0u);
+            }
+        };
+        if (BF16W) load_bf16(0, bcur);
+        else cur = load_quad(w, grow, half * 4, a.R, NB, vec);
+        nxt = cur;
         bool live = true;
         for (int kt = 0; kt < KT && live; ++kt) {
             const int s = kt % GM_STAGES;
-            if (kt + 1 < KT) nxt = load_quad(w, grow, (kt + 1) * 8 + half * 4, a.R, NB, vec);
+            if (kt + 1 < KT) {
+                if (BF16W) load_bf16(kt + 1, bnxt);
+                else nxt = load_quad(w, grow, (kt + 1) * 8 + half * 4, a.R, NB, vec);
+            }
             if (kt >= GM_STAGES && !mbar_wait(bar_empty + 8 * s, ((kt / GM_STAGES) - 1) & 1, &abort_flag)) {
                 abort_flag = 1;
                 atomicCAS(&g_mm_status, 0, 1);
@@ -197,9 +211,16 @@ __global__ void __launch_bounds__(GM_THREADS, 2) seed_gemm_kernel(MmParams a, KC
                 break;
             }
             uint8_t* stage = smem + (size_t) s * STAGE_BYTES;
-            // weights: two block pairs, expanded side by side
+            if (BF16W) {      // stored weights: the row's four 16-byte chunks of this half, as they are
 #pragma unroll
-            for (int bp = 0; bp < 2; ++bp) {
+                for (int i = 0; i < 4; ++i) {
+                    const int chunk = half * 4 + i;
+                    *(uint4*) (stage + (uint32_t) prow * 128u + (uint32_t) ((chunk ^ (prow & 7)) << 4)) = bcur[i];
+                }
+            }
+            // seed weights: two block pairs, expanded side by side
+#pragma unroll
+            for (int bp = 0; bp < (BF16W ? 0 : 2); ++bp) {
                 float wa[8], wb[8];
                 if (cur.live) {
                     const uint32_t cd = cur.codes >> (8 * bp);
@@ -260,6 +281,10 @@ __global__ void __launch_bounds__(GM_THREADS, 2) seed_gemm_kernel(MmParams a, KC
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the MMA's reads
             mbar_arrive(bar_full + 8 * s);
             cur = nxt;
+            if (BF16W) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) bcur[i] = bnxt[i];
+            }
         }
         // ---- epilogue: TMEM lane = weight row, column = token ----------------------------------------------------------
         if (live && !mbar_wait(bar_done, 0, &abort_flag)) {
@@ -317,31 +342,36 @@ __global__ void __launch_bounds__(GM_THREADS, 2) seed_gemm_kernel(MmParams a, KC
 
 static int g_exact;   // kc_seed_gemm_f32: process-wide, as the reference's switch (engine/kernels_moe.cu:2354)
 
-template <int NT>
+template <int NT, bool BF16W>
 static void launch_gemm_nt(cudaStream_t s, const MmParams& a, dim3 grid) {
     const size_t smem = (size_t) GM_STAGES * (NT + 1) * GM_TILE_BYTES + 1024;
     static bool attr_set[16];
     int dev = 0;
     cudaGetDevice(&dev);
     if (!attr_set[dev & 15]) {
-        cudaFuncSetAttribute(seed_gemm_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+        cudaFuncSetAttribute(seed_gemm_kernel<NT, BF16W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
         attr_set[dev & 15] = true;
     }
-    seed_gemm_kernel<NT><<<grid, GM_THREADS, smem, s>>>(a, kconst());
+    seed_gemm_kernel<NT, BF16W><<<grid, GM_THREADS, smem, s>>>(a, kconst());
     count_launch();
 }
 
 static void launch_gemm(cudaStream_t s, int fmt, const char* who, MmParams a, int tiles_y) {
-    if (fmt != MF_SEED4P4) { set_error("%s: weight format %d is not served by this library (SEED4P4 = %d only)", who, fmt, (int) MF_SEED4P4); return; }
+    if (fmt != MF_SEED4P4 && fmt != MF_BF16) {
+        set_error("%s: weight format %d is not served by this library (SEED4P4 = %d and BF16 = %d only)", who, fmt, (int) MF_SEED4P4, (int) MF_BF16);
+        return;
+    }
     if (a.K <= 0 || a.K % 8 || a.R <= 0) { set_error("%s: K = %d (a multiple of 8), R = %d", who, a.K, a.R); return; }
+    if (fmt == MF_BF16 && ((a.ws == NULL && !aligned16(a.w0.p[0])))) { set_error("%s: BF16 weights must be 16-byte aligned", who); return; }
     if (tiles_y <= 0) return;
     if (!aligned16(a.X) || (a.packed ? a.xs % 8 : a.xs % 4)) {
         set_error("%s: inputs must be 16-byte aligned with a row stride that is a multiple of 16 bytes", who);
         return;
     }
     const dim3 grid((unsigned) ((a.R + GM_BM - 1) / GM_BM), (unsigned) tiles_y);
-    if (g_exact) launch_gemm_nt<3>(s, a, grid);
-    else launch_gemm_nt<1>(s, a, grid);
+    if (fmt == MF_BF16) launch_gemm_nt<1, true>(s, a, grid);      // stored BF16 weights (p[0] = [R][K]): no expansion, one term
+    else if (g_exact) launch_gemm_nt<3, false>(s, a, grid);
+    else launch_gemm_nt<1, false>(s, a, grid);
 }
 
 }   // namespace nsl

@@ -12,7 +12,7 @@ from .moe import DeviceLayer, ExpertStack
 
 class NslDecoderCfg(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("n_layer", "d", "n_head", "n_kv", "n_exp", "top_k", "ff_exp", "ff_shared", "vocab", "max_rows",
-                                         "ctx", "exp_lo", "exp_hi")] + [("eps", C.c_float), ("rope_theta", C.c_float)]
+                                         "ctx", "exp_lo", "exp_hi")] + [("eps", C.c_float), ("rope_theta", C.c_float), ("dense_bf16", C.c_int32)]
 
 
 class NslDecoderLayer(C.Structure):
@@ -86,9 +86,10 @@ def row_info(pos, kv0):
     return out
 
 
-def make_cfg(n_layer, d, n_head, n_kv, n_exp, top_k, ff_exp, ff_shared, vocab, max_rows, ctx, exp_lo=0, exp_hi=None, eps=1e-6, theta=1e6):
+def make_cfg(n_layer, d, n_head, n_kv, n_exp, top_k, ff_exp, ff_shared, vocab, max_rows, ctx, exp_lo=0, exp_hi=None, eps=1e-6, theta=1e6,
+             dense_bf16=0):
     return NslDecoderCfg(n_layer, d, n_head, n_kv, n_exp, top_k, ff_exp, ff_shared, vocab, max_rows, ctx, exp_lo,
-                         n_exp if exp_hi is None else exp_hi, eps, theta)
+                         n_exp if exp_hi is None else exp_hi, eps, theta, dense_bf16)
 
 
 def random_decoder(cfg, seed=0, win=None):

@@ -65,27 +65,37 @@ def make_weights(oracle, moe, n_layer, d, n_head, n_kv, n_exp, ff, ffs, vocab, s
 class HostDecoder:
     """The reference: one step over T rows, each its own sequence slot of `ctx` positions; caches kept between steps."""
 
-    def __init__(self, oracle, hw, d, n_head, n_kv, n_exp, k, slots, ctx):
+    def __init__(self, oracle, hw, d, n_head, n_kv, n_exp, k, slots, ctx, dense_bf16=False):
         self.o, self.hw, self.d, self.n_head, self.n_kv, self.n_exp, self.k = oracle, hw, d, n_head, n_kv, n_exp, k
+        self.dense_bf16, self.wcache = dense_bf16, {}
         self.K = [np.zeros((slots * ctx, n_kv, 128), np.uint16) for _ in hw["layers"]]
         self.V = [np.zeros((slots * ctx, n_kv, 128), np.uint16) for _ in hw["layers"]]
+
+    def dense(self, m, x, T, add=0, y0=None):
+        """A dense projection: the seed mat-vec, or (dense_bf16) the product with the weights rounded to bf16 once."""
+        if not self.dense_bf16:
+            return self.o.mv(m, x, T, add=add, y0=y0)
+        if id(m) not in self.wcache:
+            self.wcache[id(m)] = bfr(self.o.decode_rows_f32(m)).astype(np.float64)
+        acc = bfr((np.asarray(x, np.float64).reshape(T, -1) @ self.wcache[id(m)].T).astype(np.float32))
+        return bfr(np.asarray(y0, np.float32).reshape(T, -1) + acc) if add else acc
 
     def step(self, ids, pos, kv0):
         o, d, T = self.o, self.d, len(ids)
         x = bf_val(self.hw["embed"][ids])
         for l, hl in enumerate(self.hw["layers"]):
             h = gnorm(x, hl["norm_attn"])
-            q = o.mv(hl["wq"], h, T).reshape(T, self.n_head, 128)
-            kk = o.mv(hl["wk"], h, T).reshape(T, self.n_kv, 128)
-            vv = o.mv(hl["wv"], h, T).reshape(T, self.n_kv, 128)
+            q = self.dense(hl["wq"], h, T).reshape(T, self.n_head, 128)
+            kk = self.dense(hl["wk"], h, T).reshape(T, self.n_kv, 128)
+            vv = self.dense(hl["wv"], h, T).reshape(T, self.n_kv, 128)
             for t in range(T):
                 q[t] = bfr(rope(q[t], pos[t]))
                 self.K[l][kv0[t] + pos[t]] = bf_bits(rope(kk[t], pos[t]))
                 self.V[l][kv0[t] + pos[t]] = bf_bits(vv[t])
             att, _ = o.attn_decode(q, self.K[l], self.V[l], pos, kv0, self.n_kv, np.float32(1 / np.sqrt(128.0)))
-            x = o.mv(hl["wo"], att.reshape(T, -1), T, add=1, y0=x)
+            x = self.dense(hl["wo"], att.reshape(T, -1), T, add=1, y0=x)
             h = gnorm(x, hl["norm_ffn"])
-            logits = o.mv(hl["router"], h, T)
+            logits = self.dense(hl["router"], h, T)
             ind, wt = o.route(np.ascontiguousarray(logits[:, :self.n_exp]), self.k)
             ex = hl["experts"]
             D = np.zeros((T * self.k, d), np.float32)
@@ -95,7 +105,11 @@ class HostDecoder:
                     e = int(ind[t, j])
                     a = o.mv_gu(ex.matrix(o, "gate", e), ex.matrix(o, "up", e), h[t])
                     D[t * self.k + j] = o.mv(ex.matrix(o, "down", e), a)[0]
-                sh[t] = o.mv(hl["sd"], o.mv_gu(hl["sg"], hl["su"], h[t]))[0]
+                if self.dense_bf16:
+                    a = o.swiglu(self.dense(hl["sg"], h[t], 1)[0], self.dense(hl["su"], h[t], 1)[0])
+                    sh[t] = self.dense(hl["sd"], a, 1)[0]
+                else:
+                    sh[t] = o.mv(hl["sd"], o.mv_gu(hl["sg"], hl["su"], h[t]))[0]
             br = o.q4_moe_combine(D, wt, sh, np.ascontiguousarray(logits[:, self.n_exp]), T, d, self.k)
             x = bfr(x + br)
         lm, _ = o.q4_mv(*self.hw["head"], gnorm(x, self.hw["norm_out"]))
@@ -105,17 +119,17 @@ class HostDecoder:
 CFG = dict(n_layer=2, d=256, n_head=4, n_kv=2, n_exp=8, top_k=2, ff_exp=64, ff_shared=64, vocab=512, ctx=8)
 
 
-@pytest.mark.parametrize("windowed", [False, True])
-def test_decoder_steps_against_the_host_reference(oracle, windowed):
+@pytest.mark.parametrize("windowed,dense_bf16", [(False, 0), (True, 0), (False, 1)])
+def test_decoder_steps_against_the_host_reference(oracle, windowed, dense_bf16):
     import torch
     from nanoseedlm_b200 import decoder, ep, lib as L, moe
     c = CFG
     T = 3
     hw = make_weights(oracle, moe, c["n_layer"], c["d"], c["n_head"], c["n_kv"], c["n_exp"], c["ff_exp"], c["ff_shared"], c["vocab"])
-    cfg = decoder.make_cfg(max_rows=T, eps=EPS, theta=THETA, **c)
+    cfg = decoder.make_cfg(max_rows=T, eps=EPS, theta=THETA, dense_bf16=dense_bf16, **c)
     win = ep.P2PWindow.create(1, 0, T, c["d"], c["top_k"]) if windowed else None
     dec = decoder.host_decoder(cfg, hw, win)
-    ref = HostDecoder(oracle, hw, c["d"], c["n_head"], c["n_kv"], c["n_exp"], c["top_k"], T, c["ctx"])
+    ref = HostDecoder(oracle, hw, c["d"], c["n_head"], c["n_kv"], c["n_exp"], c["top_k"], T, c["ctx"], dense_bf16=bool(dense_bf16))
     kv0 = [t * c["ctx"] for t in range(T)]
     nxt = torch.zeros(T, dtype=torch.int32, device="cuda")
     ids = np.array([5, 77, 300], np.int32)
@@ -203,6 +217,34 @@ def test_small_kernels_alone(oracle):
     lib.kc_embed(None, 0, w0, d, idd.data_ptr(), out.data_ptr(), 4)
     torch.cuda.synchronize()
     assert np.array_equal(out.cpu().numpy(), bf_val(table[ids]))
+
+
+@pytest.mark.parametrize("R,K,T", [(40, 256, 1), (40, 256, 5), (300, 2048, 8), (40, 128, 12), (300, 512, 40), (136, 256, 130)])
+def test_stored_bf16_weights(oracle, R, K, T):
+    """kc_mv (T <= 8) and kc_mm (more rows) with MF_BF16 weights [R][K]: y = bf16(W . x) with f32 sums, and the residual form."""
+    import torch
+    from nanoseedlm_b200 import kernels, lib as L
+    lib = L.load()
+    rng = np.random.default_rng(R + K + T)
+    W = bfr(rng.standard_normal((R, K)).astype(np.float32) * 0.05)
+    x = bfr(rng.standard_normal((T, K)).astype(np.float32))
+    y0 = bfr(rng.standard_normal((T, R)).astype(np.float32))
+    wd, xd = kernels.dev(bf_bits(W)), kernels.dev(x)
+    w = L.WSlice()
+    w.p[0] = wd.data_ptr()
+    acc = x.astype(np.float64) @ W.astype(np.float64).T
+    mag = np.abs(x).astype(np.float64) @ np.abs(W).astype(np.float64).T
+    fn = lib.kc_mv if T <= 8 else lib.kc_mm
+    for add in (0, 1):
+        yd = kernels.dev(y0.copy())
+        fn(None, 0, w, K, R, xd.data_ptr(), K, yd.data_ptr(), R, T, add, None)
+        torch.cuda.synchronize()
+        L.check()
+        want = bfr(y0 + bfr(acc.astype(np.float32))) if add else bfr(acc.astype(np.float32))
+        got = yd.cpu().numpy()
+        slack = 64 * 1.2e-7 * mag + (np.abs(acc) / 128 if add else 0)
+        assert (np.abs(got.astype(np.float64) - want) <= np.abs(want) / 128.0 + 1e-30 + slack).all()
+    assert lib.nsl_mm_status() == 0
 
 
 def test_decoder_step_of_more_rows_than_a_mat_vec_takes(oracle):
