@@ -8,7 +8,7 @@ roofline at 1 / 2 / 4 / 8 GPUs, next to the CPU seed path timed on the same host
 
 N = 1.  The headline is BASELINE config 1 at M = 8 (the multi-token-prediction verify batch): a step = router top-8 over
 128 experts (in the prologue of the gate+up kernel), the routed experts' gate + up + SwiGLU and down projections
-regenerated from their seeds, one expansion per distinct expert, and the weighted combine.  Steps rotate over enough
+regenerated from their seeds pair by pair, and the weighted combine.  Steps rotate over enough
 independent synthetic layers that every step's packed streams come from HBM, not L2.  The same JSON line carries
 `workloads` (config 0, config 1 at M = 1 and 4, config 2, the LM head, decode attention: time per step and roofline
 each) and `ep_base` = config 3 with all 512 experts on the one GPU, the base of the strong-scaling series that the N > 1
@@ -42,8 +42,8 @@ BLOCKS_PER_MATRIX = D * FF // 8                           # 131,072 blocks of 8 
 ALU_FLOOR = 53 / 64        # clocks per block per SM: 53 logic-pipe operations per block, 64 logic lanes per SM and clock
                            # (profiles/logic_pipe_rates.md)
 METRIC = "seed_decode_moe_gemv_tokens_per_s"
-# DRAM bytes per launch of the gate+up kernel from ncu (profiles/mv_grp_gate_up_config1_M8.md): per distinct expert
-# (gate + up streams) and the rest (activations, tables)
+# DRAM bytes per launch of the gate+up kernel from ncu (profiles/mv_pair_gate_up_config1.md): per distinct expert
+# (gate + up streams: pairs that share an expert find its streams in L2) and the rest (activations, tables)
 NCU_TRAFFIC_PER_DISTINCT = 1.114e6
 NCU_TRAFFIC_FIXED = 0.9e6
 
@@ -414,6 +414,67 @@ def measure_layer(c, M, K, W, sample_clocks=True, with_e2e=True, dependent_launc
     return res
 
 
+def measure_ref_gpu(c, M, K, W, mine_out=None):
+    """The reference's OWN CUDA kernels (engine/kernels_moe.cu + engine/kernels_qwen4.cu compiled unmodified for sm_100a into
+    oracle/_ref/libnslm_ref_gpu.so) on the same layers, inputs and rotation as measure_layer: per step kq4_route_ld, kc_mv_gu,
+    kc_mv_sel and kq4_moe_combine (engine/qwen4_cuda.c:1033-1078), captured as a CUDA graph and timed with CUDA events.  The
+    checker's use of the reference: a reported baseline and a parity check of one step, never the product path."""
+    from oracle import ref_gpu
+    ref = ref_gpu.lib()
+    if ref is None:
+        return {"unavailable": "oracle/_ref/libnslm_ref_gpu.so was not built (needs the reference's sources and nvcc)"}
+    torch, L, layers, NL, stream = c.torch, c.L, c.layers, c.NL, c.stream
+    NB, P = 16, M * TOPK
+    hx, hl, _ = c.inputs(M, NB)
+    dx, dl = torch.from_numpy(hx).cuda(), torch.from_numpy(hl).cuda()
+    cfg = ref_gpu.qwen4_cfg(E, TOPK)
+    cfgp = C.c_void_p(cfg.ctypes.data)
+    from nanoseedlm_b200 import kernels
+    G = kernels.stream_table()
+    ind = torch.zeros(P, dtype=torch.int32, device="cuda")
+    wt = torch.zeros(P, device="cuda")
+    A = torch.zeros(P, FF, device="cuda")
+    Dx = torch.zeros(P, D, device="cuda")
+    sh, sg = torch.zeros(M, D, device="cuda"), torch.zeros(M, device="cuda")      # no shared expert in config 1: a zero term
+    out = torch.zeros(M, D, device="cuda")
+
+    def enqueue(step):
+        lay, b, s = layers[step % NL], step % NB, stream.cuda_stream
+        ref.kq4_route_ld(s, cfgp, dl[b].data_ptr(), E, ind.data_ptr(), wt.data_ptr(), M)
+        ref.kc_mv_gu(s, L.MF_SEED4P4, lay.gate.table.data_ptr(), lay.up.table.data_ptr(), D, FF, dx[b].data_ptr(), D, A.data_ptr(), FF,
+                     ind.data_ptr(), P, TOPK, G.data_ptr())
+        ref.kc_mv_sel(s, L.MF_SEED4P4, lay.down.table.data_ptr(), FF, D, A.data_ptr(), FF, Dx.data_ptr(), D, ind.data_ptr(), P, 1, G.data_ptr())
+        ref.kq4_moe_combine(s, D, TOPK, Dx.data_ptr(), wt.data_ptr(), sh.data_ptr(), sg.data_ptr(), 0, out.data_ptr(), M)
+
+    res = {"kernels": "the reference's engine/kernels_moe.cu + engine/kernels_qwen4.cu, unmodified, nvcc -O3 sm_100a", "launches_per_step": 4}
+    with torch.cuda.stream(stream):
+        enqueue(0)      # step 0 = the step measure_layer hands to the parity checks (layer 0, batch 0)
+        stream.synchronize()
+        if mine_out is not None:
+            r = out.cpu().numpy()
+            res["this_library_vs_reference_max_rel"] = float(np.max(np.abs(mine_out - r)) / np.max(np.abs(r)))
+        for i in range(W):
+            enqueue(i)
+        stream.synchronize()
+        chunk = min(K, 100)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for i in range(chunk):
+                enqueue(W + i)
+        graph.replay()
+        stream.synchronize()
+        reps = max(1, min(K, 400) // chunk)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(reps):
+            graph.replay()
+        e1.record(stream)
+        e1.synchronize()
+    ms = e0.elapsed_time(e1) / (reps * chunk)
+    res.update(ms_per_step=ms, value=M / (ms * 1e-3), unit="tok/s", steps=reps * chunk)
+    return res
+
+
 def alu_roofline(us, blocks, sm_mhz, sms):
     """Clocks per expanded block per SM against the logic pipe's floor."""
     clk = us * 1e-6 * sm_mhz * 1e6 * sms / blocks
@@ -423,12 +484,13 @@ def alu_roofline(us, blocks, sm_mhz, sms):
 
 def layer_roofline(r, M, sm_mhz, sms, peaks, peak_kind):
     """The roofline object of a config-1 / config-2 measurement: HBM fraction of the dominant kernel and, since the kernel
-    is bound by the integer / logic pipe, that pipe's floor (one expansion per DISTINCT expert)."""
+    is bound by the integer / logic pipe, that pipe's floor.  `alu.frac` counts one expansion per DISTINCT expert (the algorithmic minimum);
+    `alu.frac_of_expanded_blocks` counts the blocks the kernel does expand (config 1: every pair)."""
     k = r["kernel"]
     mats = 1 if M > 8 else 2      # config 2 times the gate GEMM, config 1 the gate+up mat-vec
     nbytes = k["distinct_experts_per_launch"] * mats * BYTES_PER_MATRIX + M * D * 4 + M * TOPK * FF * 4
     achieved = nbytes / (k["us_per_launch"] * 1e-6) / 1e9
-    name = "seed_gemm_kernel (kc_mm_grouped_dev, gate projection)" if M > 8 else "mv_grp_kernel<gate+up> with the router in its prologue (nsl_mv_gu_routed)"
+    name = "seed_gemm_kernel (kc_mm_grouped_dev, gate projection)" if M > 8 else "mv_pair_kernel<gate+up> with the router in its prologue (nsl_mv_gu_routed)"
     out = {"bound": "hbm", "kernel": name, "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
            "peak_kind": peak_kind, "us_per_launch": k["us_per_launch"], "algorithmic_bytes_per_launch": nbytes,
            "traffic": (k["distinct_experts_per_launch"] * NCU_TRAFFIC_PER_DISTINCT + NCU_TRAFFIC_FIXED) if M <= 8 else None,
@@ -439,7 +501,9 @@ def layer_roofline(r, M, sm_mhz, sms, peaks, peak_kind):
         out["alu"] = alu_roofline(k["us_per_launch"], blocks, sm_mhz, sms)
         out["alu"]["bytes_time_us"] = nbytes / (peaks["hbm_gbs"] * 1e9) * 1e6
         if M <= 8:
-            out["alu"]["frac_if_every_pair_expanded"] = out["alu"]["frac"] * M * TOPK / k["distinct_experts_per_launch"]
+            out["alu"]["frac_of_expanded_blocks"] = out["alu"]["frac"] * M * TOPK / k["distinct_experts_per_launch"]
+            out["alu"]["note"] = ("frac: one expansion per distinct expert (the algorithmic minimum); frac_of_expanded_blocks: the kernel expands "
+                                  "every (row, expert) pair, since sharing an expansion between pairs measured no faster at <= 64 pairs")
         else:
             tf = 2.0 * M * TOPK * FF * D / (k["us_per_launch"] * 1e-6) / 1e12
             out["tensor"] = {"achieved_tflops": tf, "peak_tflops": peaks["bf16_tflops"], "frac": tf / peaks["bf16_tflops"],
@@ -910,7 +974,7 @@ def measure_ep(args, K, W, quiet_clocks=False):
            "pairs_on_rank0_last_step": pairs, "parity": parity,
            "e2e": {"value": EP_B / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": t_loc * D * 4 + t_loc * EP_E * 4,
                    "d2h_bytes_per_step": t_loc * D * 4, "ms_per_step": e2e_s * 1e3, "steps_in_flight": 1},
-           "roofline": {"bound": "hbm", "kernel": "the step's seed mat-vecs (mv_grp_kernel: gate+up and down over the ranks' pairs)",
+           "roofline": {"bound": "hbm", "kernel": "the step's seed mat-vecs (gate+up and down over the ranks' pairs: mv_grp_kernel beyond 64 pairs a rank, else mv_pair_kernel)",
                         "achieved": gbs, "peak": peaks["hbm_gbs"] * world, "unit": "GB/s", "frac": gbs / (peaks["hbm_gbs"] * world),
                         "peak_kind": peak_kind, "traffic": None, "expected_distinct_experts": distinct,
                         "note": "whole step (mat-vecs + exchange) over the aggregate HBM peak of the ranks; the kernels are bound by "
@@ -1016,6 +1080,10 @@ def main():
         line["workloads"] = wl
     step0 = r["step0"]
     layer0 = c.layers[0]
+    if M <= 8 and not args.no_extra:      # the reference's own CUDA kernels on the same layers and inputs (a baseline, like the CPU's)
+        line["ref_gpu"] = measure_ref_gpu(c, M, min(K, 400), W, mine_out=step0[2])
+        if extra and "ms_per_step" in line["ref_gpu"]:
+            line["ref_gpu"]["m1"] = {k_: v for k_, v in measure_ref_gpu(c, 1, min(K, 400), W).items() if k_ in ("ms_per_step", "value", "unit")}
     if not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline_cfg1(os.cpu_count() or 1, M, layer0 if M <= 8 else None, step0[0], step0[1], step0[2] if M <= 8 else None)
     del c, r

@@ -156,7 +156,7 @@ void kc_heads_deq(cudaStream_t s, int fmt, WSlice W, const uint32_t* G, int H, i
 /* engine/kernels_moe.metal:78-84, engine/kernels_cuda.h:56-72: field order is the ABI. */
 typedef struct {
     int32_t n_head, n_kv, chunk, n_splits;   /* chunk: target keys per split; a row at position pos uses
-                                                min(n_splits, ceil((pos + 1) / chunk)) splits, whatever rows share the call */
+                                                min(n_splits, ceil((pos + 1) / chunk)) splits (see nsl_attn_batch_invariant) */
     float scale;
 } AttnArgs;
 typedef struct { int32_t pos, kv0; int32_t pad[2]; } RowInfo;   /* kv0: the cache row of the sequence slot's position 0 */
@@ -169,28 +169,19 @@ typedef struct { KvSeg a, b; int32_t nv, fmt; } KvView;             /* positions
  * codes, ks / vs [rows][n_kv] f32: a value is bf16(code * scale), engine/kernels_moe.cu:807-824); FP8 / FP4 are refused.
  * Any group size n_head / n_kv up to 16. */
 void kc_attn(cudaStream_t s, AttnArgs a, const float* q, KvView kv, const RowInfo* ri, float* part, const float* g, float* o, int T);
-/* No counterpart in the reference: the form of kc_attn's first pass.  Tensor cores (heads of a KV head as the columns of
- * the products) with the step's keys dealt evenly to the blocks whatever a.n_splits asks (used when a.n_splits >= 3 and
- * T <= 1024; otherwise form 2): 1 (default) one warp per ring of K / V rows, 7 two warps per ring (groups of <= 8; larger
- * groups run form 1), 3 and 4 form 1 with three-slot rings / two blocks an SM, 5 and 6 forms 1 and 3 with the rows
- * brought by the copy engine (cp.async.bulk).  2: tensor cores, one block per (split, KV head, row).  0: scalar, one warp
- * per head (BF16 caches).  The partials' use of `part` is internal to the two kernels in every form and never exceeds
- * the size above.  nsl_attn_status: 0, or 1 once a bounded wait for rows ran out in forms 5 / 6 (that call's outputs are
- * invalid; never expected); synchronises the device. */
-void nsl_attn_set_variant(int v);
-int nsl_attn_status(void);
+/* No counterpart in the reference.  kc_attn's first pass runs on the tensor cores (the heads of a KV head are the columns of
+ * the products).  By default, when a.n_splits >= 3 and T <= 1024, the step's keys are dealt evenly to the blocks whatever
+ * a.n_splits asks: the cuts of a row's keys then depend on all rows of the step, so the same row run alone and run in a
+ * batch can differ in the last bits of the f32 sums (both within the reference's bound).  on = 1 makes every call use one
+ * block per (split, KV head, row), the reference's cuts: a row's output is then bit-identical whatever rows share the call.
+ * The partials' use of `part` is internal to the two kernels in both forms and never exceeds the size above. */
+void nsl_attn_batch_invariant(int on);
 
 /* ---- greedy decoding over the LM head's logits ------------------------------------------------------------------------ */
 /* engine/kernels_cuda.h:177-178  out[i] = arg max of row i of logits [n][V] (ties: the lowest id); prob[i] (optional) =
  * its softmax probability. */
 void kc_argmax(cudaStream_t s, const float* logits, int32_t* out, int V, int n);
 void kc_argmax_p(cudaStream_t s, const float* logits, int32_t* out, float* prob, int V, int n);
-/* No counterpart in the reference: picks the form of the Q4 mat-vec where several fit (results within the same bound;
- * for timing): 1, the default: K split over a block's warps, the inputs' fragments in registers (K = 1024, 2048, 4096),
- * else as 2; 2: every warp walks all of K through a ring of eight-group passes, 8 warps per SM; 0: the same with four-
- * group passes and 16 warps per SM. */
-void nsl_q4_set_variant(int v);
-
 /* ---- expert cache -------------------------------------------------------------------------------------------------- */
 /* engine/kernels_cuda.h:53  LRU admit of the units selected by inds[count] of sparse layer sl. */
 void kc_cache_admit(cudaStream_t s, const CachePool* p, int sl, const int32_t* inds, int count, int flags);

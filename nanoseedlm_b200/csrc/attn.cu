@@ -1,18 +1,9 @@
-// Decode attention over a BF16 or 8-bit KV cache with grouped query heads: split-key partial passes and their reduction
-// with the softplus output gate (engine/kernels_moe.cu:887-952, 2421-2426; engine/kernels_cuda.h:56-72, 130-131).
-// Three forms of the first pass: scalar (below), tensor cores with a block per caller split, tensor cores with the
-// step's keys dealt evenly to the blocks (the default; further down).
-//
-// The scalar form (BF16 caches): one block per (split, KV head, row); one warp per query head of the KV head (any group size up to 16, where the
-// reference fixes 4).  The two halves of a step of 32 keys use two thread layouts, so that neither needs a reduction
-// per key:
-//   scores   lane = key: a lane walks its own key's 128 values against the head's scaled query in shared memory;
-//   values   lane = 4 dims: the 32 weights are broadcast by shuffle and every V row is one 256-byte read.
-// The step's K and V rows are copied into shared memory once for the group (cp.async, the next step's rows in flight
-// while this one is computed); K rows sit 272 bytes apart there so that 32 lanes walking 32 rows touch distinct banks
-// (read straight from global memory the same walk costs 32 L1 wavefronts per load: 326 us against 134 MB per layer).
-// The online softmax rescales once per step.  Partials and the reduction have the reference's layout and rounding
-// points: part[row][head][split] = (m, l, acc[128]); o = bf16(bf16(acc / l) * bf16(softplus(g))).
+// Decode attention over a BF16 or 8-bit KV cache with grouped query heads: split-key partial passes on the tensor cores
+// and their reduction with the softplus output gate (engine/kernels_moe.cu:887-952, 2421-2426; engine/kernels_cuda.h:56-72,
+// 130-131).  Two forms of the first pass: the step's keys dealt evenly to the blocks (the default), and a block per caller
+// split (a row's result then never depends on the rows it shares a call with).
+// Partials and the reduction have the reference's layout and rounding points: part[row][head][split] = (m, l, acc[128]);
+// o = bf16(bf16(acc / l) * bf16(softplus(g))).
 #include <math.h>
 
 #include "common.cuh"
@@ -31,88 +22,9 @@ __device__ __forceinline__ const uint16_t* kv_row(const KvView& kv, int is_v, in
 __device__ __forceinline__ float bf_lo(uint32_t u) { return __uint_as_float(u << 16); }
 __device__ __forceinline__ float bf_hi(uint32_t u) { return __uint_as_float(u & 0xFFFF0000u); }
 
-constexpr int ATT_TILE = 32, ATT_KROW = 272;      // keys per step; bytes of a staged K row (256 + 16: conflict-free row walks)
+constexpr int ATT_KROW = 272;      // bytes of a staged K row (256 + 16: ldmatrix then touches distinct banks)
 
-__device__ __forceinline__ void attn_cp16(void* smem, const void* gmem) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned) __cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
-}
-
-__global__ void __launch_bounds__(32 * ATT_MAX_GROUP) attn_split_kernel(AttnArgs a, const float* __restrict__ q, KvView kv,
-                                                                        const RowInfo* __restrict__ ri, float* __restrict__ part) {
-    __shared__ __align__(16) float qs[ATT_MAX_GROUP][ATT_HD];
-    __shared__ __align__(16) unsigned char kt[2][ATT_TILE * ATT_KROW];      // the step's K rows, shared by the group's warps
-    __shared__ __align__(16) unsigned char vt[2][ATT_TILE * 256];           // and its V rows
-    const int split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int group = a.n_head / a.n_kv, qh = kvh * group + warp;
-    grid_dependents_go();
-    grid_dependency_wait();
-    {
-        const float4 v = *(const float4*) (q + ((size_t) t * a.n_head + qh) * ATT_HD + lane * 4);
-        *(float4*) &qs[warp][lane * 4] = make_float4(v.x * a.scale, v.y * a.scale, v.z * a.scale, v.w * a.scale);
-    }
-    const int pos = ri[t].pos, kv0 = ri[t].kv0;
-    const int nsr = a.chunk > 0 ? min(a.n_splits, (pos + a.chunk) / a.chunk) : 1;   // this row's split count, whatever rows share the call
-    const int chunk = (pos + nsr) / nsr;                          // ceil((pos + 1) / nsr)
-    const int p0 = split * chunk, p1 = min(pos + 1, p0 + chunk);  // splits >= nsr are empty
-    // the block's threads copy a step's 32 K rows and 32 V rows (16 pieces of 16 bytes each) into a stage
-    auto stage_in = [&](int st, int p) {
-        for (int i = threadIdx.x; i < 2 * ATT_TILE * 16; i += blockDim.x) {
-            const int is_v = i >= ATT_TILE * 16, r = (i >> 4) & (ATT_TILE - 1), piece = i & 15;
-            const uint16_t* src = kv_row(kv, is_v, kv0 + min(p + r, p1 - 1), a.n_kv, kvh) + piece * 8;
-            attn_cp16(is_v ? vt[st] + r * 256 + piece * 16 : kt[st] + r * ATT_KROW + piece * 16, src);
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-    };
-    float m = -INFINITY, l = 0.0f;
-    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    if (p0 < p1) stage_in(0, p0);
-    int st = 0;
-    for (int p = p0; p < p1; p += ATT_TILE, st ^= 1) {
-        if (p + ATT_TILE < p1) {
-            stage_in(st ^ 1, p + ATT_TILE);      // the next step's rows fly while this one is computed
-            asm volatile("cp.async.wait_group 1;" ::: "memory");
-        } else {
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-        }
-        __syncthreads();
-        const bool valid = p + lane < p1;
-        const unsigned char* kr = kt[st] + lane * ATT_KROW;
-        float s = 0.0f;
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const uint4 k8 = *(const uint4*) (kr + j * 16);
-            const float4 qa = *(const float4*) &qs[warp][8 * j], qb = *(const float4*) &qs[warp][8 * j + 4];
-            s = fmaf(qa.x, bf_lo(k8.x), s); s = fmaf(qa.y, bf_hi(k8.x), s);
-            s = fmaf(qa.z, bf_lo(k8.y), s); s = fmaf(qa.w, bf_hi(k8.y), s);
-            s = fmaf(qb.x, bf_lo(k8.z), s); s = fmaf(qb.y, bf_hi(k8.z), s);
-            s = fmaf(qb.z, bf_lo(k8.w), s); s = fmaf(qb.w, bf_hi(k8.w), s);
-        }
-        if (!valid) s = -INFINITY;
-        float mx = s;
-        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
-        mx = fmaxf(mx, m);
-        const float cor = expf(m - mx), e = valid ? expf(s - mx) : 0.0f;
-        l = fmaf(l, cor, e);      // per lane: the lanes' sums meet once, after the last step
-        acc.x *= cor; acc.y *= cor; acc.z *= cor; acc.w *= cor;
-        m = mx;
-        const int nk = min(ATT_TILE, p1 - p);
-        const uint2* vr = (const uint2*) vt[st] + lane;
-        for (int kk = 0; kk < nk; ++kk) {
-            const float pk = __shfl_sync(0xFFFFFFFFu, e, kk);
-            const uint2 v4 = vr[kk * 32];
-            acc.x = fmaf(pk, bf_lo(v4.x), acc.x); acc.y = fmaf(pk, bf_hi(v4.x), acc.y);
-            acc.z = fmaf(pk, bf_lo(v4.y), acc.z); acc.w = fmaf(pk, bf_hi(v4.y), acc.w);
-        }
-        __syncthreads();      // the stage may be refilled by the step after next
-    }
-    for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xFFFFFFFFu, l, o);
-    float* pp = part + (((size_t) t * a.n_head + qh) * a.n_splits + split) * (ATT_HD + 2);
-    if (lane == 0) { pp[0] = m; pp[1] = l; }
-    pp[2 + lane * 4 + 0] = acc.x; pp[2 + lane * 4 + 1] = acc.y; pp[2 + lane * 4 + 2] = acc.z; pp[2 + lane * 4 + 3] = acc.w;
-}
-
-// ---- the same pass on the tensor cores -------------------------------------------------------------------------------------
+// ---- the first pass on the tensor cores -----------------------------------------------------------------------------------
 // One warp serves ALL query heads of the KV head: they are the columns of mma.sync.m16n8k16 products (bf16 in, f32
 // accumulate; 8 heads a tile, columns beyond the group are zero; see attn_keys for the two products).  Queries are
 // bf16-valued, so the score products are exact and the softmax scale is applied to the f32 sums; the weights enter the
@@ -148,16 +60,15 @@ __device__ __forceinline__ void attn_cp16s(unsigned smem, const void* gmem) {
 
 // The 16 K rows and 16 V rows of the step at key p into a slot: 32 lanes x 8 pieces of 16 bytes each (rows beyond the range
 // repeat its last row; their scores are masked).  Always one cp.async group, empty when the step lies beyond the range.
-// N of the step's 8 row pairs, from pair i0 on (a ring's warps share a step's copies).
-template <int N = ATT_MT / 2>
-__device__ __forceinline__ void attn_fill_slot(unsigned char* slot, const KvView& kv, int n_kv, int kvh, int kv0, int p, int p1, int lane, int i0 = 0) {
+__device__ __forceinline__ void attn_fill_slot(unsigned char* slot, const KvView& kv, int n_kv, int kvh, int kv0, int p, int p1, int lane) {
+    constexpr int N = ATT_MT / 2;
     if (p < p1) {
         const int rl = lane >> 4, piece = lane & 15;
-        const unsigned sk = (unsigned) __cvta_generic_to_shared(slot) + (2 * i0 + rl) * ATT_KROW + piece * 16, sv = sk + ATT_MT * ATT_KROW;
+        const unsigned sk = (unsigned) __cvta_generic_to_shared(slot) + rl * ATT_KROW + piece * 16, sv = sk + ATT_MT * ATT_KROW;
         const int row0 = kv0 + p;
         if (p + ATT_MT <= p1 && (row0 + ATT_MT <= kv.nv || row0 >= kv.nv)) {      // 16 whole rows of one segment: one address, strides
-            const unsigned char* kb = (const unsigned char*) (kv_row(kv, 0, row0 + 2 * i0 + rl, n_kv, kvh) + piece * 8);
-            const unsigned char* vb = (const unsigned char*) (kv_row(kv, 1, row0 + 2 * i0 + rl, n_kv, kvh) + piece * 8);
+            const unsigned char* kb = (const unsigned char*) (kv_row(kv, 0, row0 + rl, n_kv, kvh) + piece * 8);
+            const unsigned char* vb = (const unsigned char*) (kv_row(kv, 1, row0 + rl, n_kv, kvh) + piece * 8);
             const size_t two_rows = (size_t) n_kv * (2 * ATT_HD * 2);
 #pragma unroll
             for (int i = 0; i < N; ++i) {
@@ -167,7 +78,7 @@ __device__ __forceinline__ void attn_fill_slot(unsigned char* slot, const KvView
         } else {
 #pragma unroll
             for (int i = 0; i < N; ++i) {
-                const int row = kv0 + min(p + 2 * (i0 + i) + rl, p1 - 1);
+                const int row = kv0 + min(p + 2 * i + rl, p1 - 1);
                 attn_cp16s(sk + i * 2 * ATT_KROW, kv_row(kv, 0, row, n_kv, kvh) + piece * 8);
                 attn_cp16s(sv + i * 2 * ATT_VROW, kv_row(kv, 1, row, n_kv, kvh) + piece * 8);
             }
@@ -176,55 +87,7 @@ __device__ __forceinline__ void attn_fill_slot(unsigned char* slot, const KvView
     asm volatile("cp.async.commit_group;" ::: "memory");
 }
 
-// ---- K / V rows by the copy engine (cp.async.bulk, one 256-byte row per lane) ------------------------------------------
-// A warp's slot has an mbarrier: lane 0 announces the step's 8192 bytes, every lane issues one row (lanes 0-15 K, 16-31 V),
-// the copies count their bytes down and the wait ends when all have landed.  No per-16-byte load-store requests: the
-// requests a step keeps in flight no longer go through the SM's load-store path.
-__device__ int g_attn_wait_failed;      // set when a wait for a slot's rows ran out (never expected: the copies always land)
-
-__device__ __forceinline__ unsigned long long attn_now_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned) __cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
-    unsigned ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded: gives up after one second (or 2^24 polls) and reports it.
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = attn_now_ns();
-    for (unsigned i = 1; i < (1u << 24); ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 255u) == 0 && attn_now_ns() - t0 > 1000000000ull) break;
-    }
-    return false;
-}
-__device__ __forceinline__ void bulk_row(unsigned dst, const void* src, unsigned bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "l"(src), "r"(2 * ATT_HD), "r"(bar) : "memory");
-}
-// The step at key p into a slot, if it lies in the range.  All 32 lanes call it.
-__device__ __forceinline__ void attn_fill_slot_bulk(unsigned char* slot, unsigned bar, const KvView& kv, int n_kv, int kvh, int kv0, int p,
-                                                    int p1, int lane) {
-    if (p < p1) {
-        if (lane == 0) mbar_expect_tx(bar, 2 * ATT_MT * 2 * ATT_HD);
-        __syncwarp();
-        const int r = lane & 15, is_v = lane >> 4;
-        const int row = kv0 + min(p + r, p1 - 1);      // rows beyond the range repeat its last row; their scores are masked
-        bulk_row(smem_u32(slot) + is_v * ATT_MT * ATT_KROW + r * ATT_KROW, kv_row(kv, is_v, row, n_kv, kvh), bar);
-    }
-}
 
 // ---- the 8-bit cache (KV_Q8: int8 codes, one f32 scale per row and KV head; engine/kernels_cuda.h:58-59) ------------------
 // A warp's ring holds the raw rows of two steps (16 K rows and 16 V rows of 128 bytes, then their 32 scales); before a step
@@ -241,21 +104,20 @@ __device__ __forceinline__ const KvSeg& kv_seg_of(const KvView& kv, int abs_pos,
     row = first ? abs_pos : abs_pos - kv.nv;
     return first ? kv.a : kv.b;
 }
-// The step at key p, raw: 256 pieces of 16 bytes (8 rounds of 32) and 32 scales.  This warp takes N rounds from round i0 on
-// (and the scales when i0 = 0).  Always one cp.async group.
-template <int N = 8>
-__device__ __forceinline__ void attn_fill_raw(unsigned char* raw, const KvView& kv, int n_kv, int kvh, int kv0, int p, int p1, int lane, int i0 = 0) {
+// The step at key p, raw: 256 pieces of 16 bytes (8 rounds of 32) and 32 scales.
+// Always one cp.async group.
+__device__ __forceinline__ void attn_fill_raw(unsigned char* raw, const KvView& kv, int n_kv, int kvh, int kv0, int p, int p1, int lane) {
     if (p < p1) {
         const unsigned base = smem_u32(raw);
 #pragma unroll
-        for (int i = 0; i < N; ++i) {
-            const int id = (i0 + i) * 32 + lane, is_v = id >> 7, r = (id >> 3) & 15, piece = id & 7;
+        for (int i = 0; i < 8; ++i) {
+            const int id = i * 32 + lane, is_v = id >> 7, r = (id >> 3) & 15, piece = id & 7;
             int row;
             const KvSeg& sg = kv_seg_of(kv, kv0 + min(p + r, p1 - 1), row);
             attn_cp16s(base + is_v * ATT_RAW_V + r * ATT_HD + piece * 16,
                        (const unsigned char*) (is_v ? sg.v : sg.k) + ((size_t) row * n_kv + kvh) * ATT_HD + piece * 16);
         }
-        if (i0 == 0) {
+        {
             const int is_v = lane >> 4, r = lane & 15;
             int row;
             const KvSeg& sg = kv_seg_of(kv, kv0 + min(p + r, p1 - 1), row);
@@ -268,12 +130,11 @@ __device__ __forceinline__ uint32_t q8_pair(uint32_t u, int i, float s) {      /
     const float a = (float) (int) (signed char) ((u >> (8 * i)) & 255u) * s, b = (float) (int) (signed char) ((u >> (8 * i + 8)) & 255u) * s;
     return pack_bf16x2(a, b);
 }
-// Raw rows -> the BF16 slot (rows 272 bytes apart, K then V): N of the 8 rounds from round i0 on.
-template <int N = 8>
-__device__ __forceinline__ void attn_expand_raw(unsigned char* slot, const unsigned char* raw, int lane, int i0 = 0) {
+// Raw rows -> the BF16 slot (rows 272 bytes apart, K then V).
+__device__ __forceinline__ void attn_expand_raw(unsigned char* slot, const unsigned char* raw, int lane) {
 #pragma unroll
-    for (int i = 0; i < N; ++i) {
-        const int id = (i0 + i) * 32 + lane, is_v = id >> 7, r = (id >> 3) & 15, piece = id & 7;
+    for (int i = 0; i < 8; ++i) {
+        const int id = i * 32 + lane, is_v = id >> 7, r = (id >> 3) & 15, piece = id & 7;
         const uint4 u = *(const uint4*) (raw + is_v * ATT_RAW_V + r * ATT_HD + piece * 16);
         const float sc = *(const float*) (raw + ATT_RAW_SCALES + (is_v * ATT_MT + r) * 4);
         uint4 lo, hi;
@@ -308,52 +169,26 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {      // an 8 x
 //                                                          as bf16 pairs, transposed across the warp by movmatrix
 // A lane holds keys r0 and r0 + 8 of heads 2 q4 and 2 q4 + 1 of each tile: the maxima and sums of a head run over the 8
 // lanes of equal q4.  Ends with the block in step (shared memory reusable).
-// SRC: how the rows come.  ATT_SRC_ASYNC: BF16 rows by cp.async; ATT_SRC_BULK: BF16 rows by the copy engine (bars = the
-// warp's NSLOT mbarriers; ring = the slots' phase bits, bit 31 set once a wait ran out, after which the warp computes
-// nothing more); ATT_SRC_Q8: the 8-bit cache (NSLOT = 2: one BF16 slot and two raw slots).
-// PW: warps per ring (block = 4 rings x PW warps).  2: the ring's two warps share a step: each copies half its rows, both
-// compute the scores and the softmax (identical values), each takes 64 of the 128 dims of the value product; they meet at a
-// named barrier of their own.  Twice the warps on the same shared memory, for the latency of a warp's own step.
-enum { ATT_SRC_ASYNC = 0, ATT_SRC_BULK = 1, ATT_SRC_Q8 = 2 };
-template <int PW>
-__device__ __forceinline__ void ring_sync(int ring) {
-    if (PW == 1) {
-        __syncwarp();
-    } else if (ring == 0) {      // literal barrier numbers: the kernel then reserves 5 barriers, not all 16
-        asm volatile("bar.sync 1, %0;" ::"n"(32 * PW) : "memory");
-    } else if (ring == 1) {
-        asm volatile("bar.sync 2, %0;" ::"n"(32 * PW) : "memory");
-    } else if (ring == 2) {
-        asm volatile("bar.sync 3, %0;" ::"n"(32 * PW) : "memory");
-    } else {
-        asm volatile("bar.sync 4, %0;" ::"n"(32 * PW) : "memory");
-    }
-}
-template <int NSLOT, int NT, int SRC, int PW = 1>
+// SRC: how the rows come.  ATT_SRC_ASYNC: BF16 rows by cp.async; ATT_SRC_Q8: the 8-bit cache (one BF16 slot and two raw slots).
+enum { ATT_SRC_ASYNC = 0, ATT_SRC_Q8 = 2 };
+template <int NSLOT, int NT, int SRC>
 __device__ __forceinline__ void attn_keys(const AttnArgs& a, const float* __restrict__ q, const KvView& kv, int t, int kvh, int kv0,
-                                          int p0, int p1, unsigned char* att_smem, float* pp, size_t head_stride, unsigned bars,
-                                          unsigned& ring) {
+                                          int p0, int p1, unsigned char* att_smem, float* pp, size_t head_stride) {
     constexpr int STAGE = NSLOT * ATT_SLOT, STRIDE = ATT_MMA_WARPS * ATT_MT;
-    const int lane = threadIdx.x & 31, ring_id = (threadIdx.x >> 5) / PW, half = (threadIdx.x >> 5) % PW, q4 = lane & 3, r0 = lane >> 2;
+    const int lane = threadIdx.x & 31, ring_id = threadIdx.x >> 5, q4 = lane & 3, r0 = lane >> 2;
     const int group = a.n_head / a.n_kv;
     unsigned char* stage = att_smem + (size_t) ring_id * STAGE;
-    constexpr bool BULK = SRC == ATT_SRC_BULK, Q8 = SRC == ATT_SRC_Q8;
-    constexpr int DT = 8 / PW;      // tiles of 16 dims of the value product a warp takes
+    constexpr bool Q8 = SRC == ATT_SRC_Q8;
+    constexpr int DT = 8;      // tiles of 16 dims of the value product
     static_assert(!Q8 || NSLOT == 2, "the 8-bit cache's ring has two raw slots");
-    static_assert(PW == 1 || (PW == 2 && !BULK), "rings of two warps copy with cp.async");
     unsigned char* raw = stage + ATT_SLOT;      // Q8: the two raw slots behind the BF16 slot
     int p = p0 + ring_id * ATT_MT;
-    if (BULK) {
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the ring held a state (plain stores) before
-        if (ring >> 31) p = p1;
-#pragma unroll
-        for (int i = 0; i < NSLOT - 1; ++i) attn_fill_slot_bulk(stage + i * ATT_SLOT, bars + 8 * i, kv, a.n_kv, kvh, kv0, p + i * STRIDE, p1, lane);
-    } else if (Q8) {
-        attn_fill_raw<8 / PW>(raw, kv, a.n_kv, kvh, kv0, p, p1, lane, half * (8 / PW));
+    if (Q8) {
+        attn_fill_raw(raw, kv, a.n_kv, kvh, kv0, p, p1, lane);
     } else {
 #pragma unroll
         for (int i = 0; i < NSLOT - 1; ++i)
-            attn_fill_slot<8 / PW>(stage + i * ATT_SLOT, kv, a.n_kv, kvh, kv0, p + i * STRIDE, p1, lane, half * (8 / PW));
+            attn_fill_slot(stage + i * ATT_SLOT, kv, a.n_kv, kvh, kv0, p + i * STRIDE, p1, lane);
     }
     // Q^T as the B fragments of the 8 steps over the 128 dims: column r0 of a tile = head 8 nt + r0 (zero beyond the group);
     // the first rows of K and V fly meanwhile
@@ -384,30 +219,21 @@ __device__ __forceinline__ void attn_keys(const AttnArgs& a, const float* __rest
     //   K (A = keys x dims):   tiles (keys 0-7 | 8-15) x (dims +0 | +8) in the order a0 a1 a2 a3 = (k lo, d lo) (k hi, d lo) (k lo, d hi) (k hi, d hi)
     //   V (A = dims x keys, transposed on load): (d lo, k lo) (d hi, k lo) (d lo, k hi) (d hi, k hi)
     const int k_off = ((lane & 7) + ((lane >> 3) & 1) * 8) * ATT_KROW + (lane >> 4) * 16;
-    const int v_off = ATT_MT * ATT_KROW + ((lane & 7) + (lane >> 4) * 8) * ATT_VROW + ((lane >> 3) & 1) * 16 + half * DT * 32;
+    const int v_off = ATT_MT * ATT_KROW + ((lane & 7) + (lane >> 4) * 8) * ATT_VROW + ((lane >> 3) & 1) * 16;
     int cur = 0, nxt = NSLOT - 1;      // the slot in use; the slot the step NSLOT - 1 ahead goes to (its reads ended with the
                                        // previous step's closing ring_sync)
     for (; p < p1; p += STRIDE) {
-        if (BULK) {
-            attn_fill_slot_bulk(stage + nxt * ATT_SLOT, bars + 8 * nxt, kv, a.n_kv, kvh, kv0, p + (NSLOT - 1) * STRIDE, p1, lane);
-            const bool landed = __all_sync(0xFFFFFFFFu, mbar_wait(bars + 8 * cur, (ring >> cur) & 1u));
-            ring ^= 1u << cur;
-            if (!landed) {      // give up: the flag tells the host, the rest of the range is skipped
-                if (lane == 0) atomicExch(&g_attn_wait_failed, 1);
-                ring |= 1u << 31;
-                break;
-            }
-        } else if (Q8) {
-            attn_fill_raw<8 / PW>(raw + nxt * ATT_RAW, kv, a.n_kv, kvh, kv0, p + STRIDE, p1, lane, half * (8 / PW));
+        if (Q8) {
+            attn_fill_raw(raw + nxt * ATT_RAW, kv, a.n_kv, kvh, kv0, p + STRIDE, p1, lane);
             asm volatile("cp.async.wait_group 1;" ::: "memory");
-            ring_sync<PW>(ring_id);
+            __syncwarp();
             // the BF16 slot's reads ended with the previous step's closing ring_sync
-            attn_expand_raw<8 / PW>(stage, raw + cur * ATT_RAW, lane, half * (8 / PW));
+            attn_expand_raw(stage, raw + cur * ATT_RAW, lane);
         } else {
-            attn_fill_slot<8 / PW>(stage + nxt * ATT_SLOT, kv, a.n_kv, kvh, kv0, p + (NSLOT - 1) * STRIDE, p1, lane, half * (8 / PW));
+            attn_fill_slot(stage + nxt * ATT_SLOT, kv, a.n_kv, kvh, kv0, p + (NSLOT - 1) * STRIDE, p1, lane);
             asm volatile("cp.async.wait_group %0;" ::"n"(NSLOT - 1) : "memory");
         }
-        ring_sync<PW>(ring_id);
+        __syncwarp();
         const unsigned char* slot = Q8 ? stage : stage + cur * ATT_SLOT;
         nxt = cur;
         cur = cur + 1 == NSLOT ? 0 : cur + 1;
@@ -465,11 +291,11 @@ __device__ __forceinline__ void attn_keys(const AttnArgs& a, const float* __rest
                 mma_bf16(ot[nt][i], va, pl[nt][0], pl[nt][1]);
             }
         }
-        ring_sync<PW>(ring_id);      // this slot's reads are done before a later step refills it
+        __syncwarp();      // this slot's reads are done before a later step refills it
     }
-    if (!BULK) asm volatile("cp.async.wait_group 0;" ::: "memory");      // only empty groups are left
+    asm volatile("cp.async.wait_group 0;" ::: "memory");      // only empty groups are left
     // the ring's state into the ring: [16 heads][130] = m (natural units; -inf stays -inf), l, acc (each warp its dims)
-    ring_sync<PW>(ring_id);
+    __syncwarp();
     float* mine = (float*) stage;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
@@ -479,19 +305,19 @@ __device__ __forceinline__ void attn_keys(const AttnArgs& a, const float* __rest
             l[nt][1] += __shfl_xor_sync(0xFFFFFFFFu, l[nt][1], off);
         }
         float* ha = mine + (8 * nt + 2 * q4) * 130, *hb = ha + 130;
-        if (r0 == 0 && half == 0) {
+        if (r0 == 0) {
             ha[0] = m[nt][0] * 0.69314718055994531f; ha[1] = l[nt][0];
             hb[0] = m[nt][1] * 0.69314718055994531f; hb[1] = l[nt][1];
         }
 #pragma unroll
         for (int i = 0; i < DT; ++i) {
-            const int d = 2 + 16 * (i + half * DT) + r0;
+            const int d = 2 + 16 * i + r0;
             ha[d] = ot[nt][i][0]; hb[d] = ot[nt][i][1]; ha[d + 8] = ot[nt][i][2]; hb[d + 8] = ot[nt][i][3];
         }
     }
     __syncthreads();
     // merge the rings' states.  A head's four weights exp(m_ring - max) are the same for all 128 dims: thread h computes
-    // them once (and the head's m and l), then a thread handles dim d of every PW-th head.
+    // them once (and the head's m and l), then thread d handles dim d of every head.
     __shared__ float merge_c[ATT_MMA_WARPS][ATT_MAX_GROUP], merge_m[ATT_MAX_GROUP], merge_l[ATT_MAX_GROUP];
     if (threadIdx.x < group) {
         const int h = threadIdx.x;
@@ -508,8 +334,8 @@ __device__ __forceinline__ void attn_keys(const AttnArgs& a, const float* __rest
         merge_l[h] = ll;
     }
     __syncthreads();
-    const int d = threadIdx.x & (ATT_HD - 1);
-    for (int h = threadIdx.x / ATT_HD; h < group; h += PW) {
+    const int d = threadIdx.x;
+    for (int h = 0; h < group; ++h) {
         float acc = 0.0f;
 #pragma unroll
         for (int w = 0; w < ATT_MMA_WARPS; ++w) acc = fmaf(((const float*) (att_smem + (size_t) w * STAGE))[h * 130 + 2 + d], merge_c[w][h], acc);
@@ -533,9 +359,8 @@ __global__ void __launch_bounds__(32 * ATT_MMA_WARPS) attn_split_mma_kernel(Attn
     const int nsr = a.chunk > 0 ? min(a.n_splits, (pos + a.chunk) / a.chunk) : 1;
     const int chunk = (pos + nsr) / nsr;
     const int p0 = split * chunk, p1 = min(pos + 1, p0 + chunk);
-    unsigned ring = 0;
     attn_keys<NSLOT, NT, SRC>(a, q, kv, t, kvh, kv0, p0, p1, att_smem, part + (((size_t) t * a.n_head + kvh * group) * a.n_splits + split) * (ATT_HD + 2),
-                                (size_t) a.n_splits * (ATT_HD + 2), 0u, ring);
+                                (size_t) a.n_splits * (ATT_HD + 2));
 }
 
 // ---- the balanced form ------------------------------------------------------------------------------------------------
@@ -595,23 +420,15 @@ __device__ __forceinline__ AttnPlan attn_plan(const RowInfo* __restrict__ ri, in
     return pl;
 }
 
-template <int NSLOT, int NT, int SRC, int PW>
-__global__ void __launch_bounds__(32 * ATT_MMA_WARPS * PW, NT == 2 && SRC == ATT_SRC_Q8 ? 2 : 3)      // three blocks an SM: <= 168 / 85 registers
+template <int NSLOT, int NT, int SRC>
+__global__ void __launch_bounds__(32 * ATT_MMA_WARPS, NT == 2 && SRC == ATT_SRC_Q8 ? 2 : 3)      // three blocks an SM: <= 168 / 85 registers
 attn_flat_mma_kernel(AttnArgs a, const float* __restrict__ q, KvView kv, const RowInfo* __restrict__ ri, float* __restrict__ part, int T) {
     extern __shared__ __align__(16) unsigned char att_smem[];
     __shared__ int pre[ATT_MAX_ROWS + 1];
-    __shared__ __align__(8) unsigned long long att_bars[ATT_MMA_WARPS][4];      // a warp's slots' mbarriers (BULK)
     const int group = a.n_head / a.n_kv;
-    const unsigned bars = smem_u32(&att_bars[(threadIdx.x >> 5) / PW][0]);
-    unsigned ring = 0;
-    if (SRC == ATT_SRC_BULK) {
-        if ((threadIdx.x & 31) < NSLOT) mbar_init(bars + 8 * (threadIdx.x & 31), 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        __syncwarp();
-    }
     grid_dependents_go();
     grid_dependency_wait();
-    const AttnPlan pl = attn_plan<ATT_MMA_WARPS * PW>(ri, T, a.n_kv, a.n_splits, (int) gridDim.x, pre);
+    const AttnPlan pl = attn_plan<ATT_MMA_WARPS>(ri, T, a.n_kv, a.n_splits, (int) gridDim.x, pre);
     int x = (int) blockIdx.x * pl.per;
     const int xe = min(pl.total, x + pl.per);
     while (x < xe) {
@@ -627,9 +444,9 @@ attn_flat_mma_kernel(AttnArgs a, const float* __restrict__ q, KvView kv, const R
         const int end = min(xe, first + u);
         const int pos = max(ri[t].pos, 0), kv0 = ri[t].kv0;
         const int slot = (int) blockIdx.x - first / pl.per;
-        attn_keys<NSLOT, NT, SRC, PW>(a, q, kv, t, kvh, kv0, (x - first) * ATT_MT, min(pos + 1, (end - first) * ATT_MT), att_smem,
+        attn_keys<NSLOT, NT, SRC>(a, q, kv, t, kvh, kv0, (x - first) * ATT_MT, min(pos + 1, (end - first) * ATT_MT), att_smem,
                                   part + (((size_t) t * a.n_head + kvh * group) * a.n_splits + slot) * (ATT_HD + 2),
-                                  (size_t) a.n_splits * (ATT_HD + 2), bars, ring);
+                                  (size_t) a.n_splits * (ATT_HD + 2));
         x = end;
     }
 }
@@ -686,11 +503,7 @@ __global__ void __launch_bounds__(ATT_HD) attn_reduce_kernel(AttnArgs a, const f
 
 using namespace nsl;
 
-static int g_attn_variant = 1;   // the first pass.  Tensor cores, the step's keys dealt evenly to the blocks: 1 (default): one
-                                 // warp a ring; 7: two warps a ring (groups of <= 8; larger groups run form 1); 3: as 1 with
-                                 // three-slot rings (two blocks an SM); 4: as 1 with two blocks an SM; 5 / 6: as 1 / 3 with
-                                 // the K and V rows brought by the copy engine (cp.async.bulk).  2: tensor cores, one block
-                                 // per caller split.  0: the scalar pass (one warp per query head)
+static int g_attn_invariant = 0;   // 1: the first pass always runs a block per caller split (see nsl_attn_batch_invariant)
 
 template <typename K>
 static void attn_smem_attr(K kernel, int bytes, bool* done) {
@@ -710,19 +523,12 @@ static int attn_sm_count() {
     return n[dev & 15] > 0 ? n[dev & 15] : 148;
 }
 
-template <int NSLOT, int NT, int SRC, int PW = 1>
+template <int NT, int SRC>
 static void launch_attn_flat(cudaStream_t s, int n_blocks, const AttnArgs& a, const float* q, const KvView& kv, const RowInfo* ri, float* part, int T) {
     static bool done[16];
-    constexpr int SMEM = ATT_MMA_WARPS * NSLOT * ATT_SLOT;
-    attn_smem_attr(attn_flat_mma_kernel<NSLOT, NT, SRC, PW>, SMEM, done);
-    launch(attn_flat_mma_kernel<NSLOT, NT, SRC, PW>, dim3((unsigned) n_blocks), 32 * ATT_MMA_WARPS * PW, (size_t) SMEM, s, a, q, kv, ri, part, T);
-}
-
-template <int NSLOT, int SRC>
-static void launch_attn_flat_group(cudaStream_t s, int n_blocks, int group, const AttnArgs& a, const float* q, const KvView& kv, const RowInfo* ri,
-                                   float* part, int T) {
-    if (group <= 8) launch_attn_flat<NSLOT, 1, SRC>(s, n_blocks, a, q, kv, ri, part, T);
-    else launch_attn_flat<NSLOT, 2, SRC>(s, n_blocks, a, q, kv, ri, part, T);
+    constexpr int SMEM = ATT_MMA_WARPS * 2 * ATT_SLOT;
+    attn_smem_attr(attn_flat_mma_kernel<2, NT, SRC>, SMEM, done);
+    launch(attn_flat_mma_kernel<2, NT, SRC>, dim3((unsigned) n_blocks), 32 * ATT_MMA_WARPS, (size_t) SMEM, s, a, q, kv, ri, part, T);
 }
 
 template <int NT, int SRC>
@@ -736,18 +542,10 @@ static void launch_attn_split(cudaStream_t s, const AttnArgs& a, const float* q,
 
 extern "C" {
 
-// Picks the form of kc_attn's first pass (see g_attn_variant).  All forms meet the same bound; for tests and timing.
-void nsl_attn_set_variant(int v) { g_attn_variant = v >= 0 && v <= 7 ? v : 1; }
-
-// 0, or 1 once a bounded wait for a step's K / V rows ran out in the copy-engine forms (the outputs of that call are
-// invalid).  Synchronises the device.
-int nsl_attn_status(void) {
-    int v = 0;
-    const int zero = 0;
-    if (cudaMemcpyFromSymbol(&v, g_attn_wait_failed, sizeof v) != cudaSuccess) return -1;
-    if (v) cudaMemcpyToSymbol(g_attn_wait_failed, &zero, sizeof zero);      // reading clears it, as the other status calls do
-    return v;
-}
+// on = 1: the first pass always runs one block per (caller split, KV head, row), so a row's keys are cut by its own position
+// alone and its output is bit-identical whatever rows share the call.  0 (default): the balanced form where it applies, whose
+// cuts (and with them the order of the f32 sums, within the same bound) depend on all rows of the step.
+void nsl_attn_batch_invariant(int on) { g_attn_invariant = on != 0; }
 
 void kc_attn(cudaStream_t s, AttnArgs a, const float* q, KvView kv, const RowInfo* ri, float* part, const float* g, float* o, int T) {
     if (T < 1) return;
@@ -764,27 +562,19 @@ void kc_attn(cudaStream_t s, AttnArgs a, const float* q, KvView kv, const RowInf
                   a.n_head, a.n_kv, (int) ATT_MAX_GROUP, a.n_splits, a.chunk);
         return;
     }
-    const int variant = q8 && (g_attn_variant == 0 || g_attn_variant == 3 || g_attn_variant == 5 || g_attn_variant == 6) ? 1 : g_attn_variant;      // Q8: forms 1, 2, 4, 7
-    const bool flat = (variant == 1 || variant >= 3) && a.n_splits >= 3 && a.chunk > 0 && T <= ATT_MAX_ROWS;
+    const bool flat = !g_attn_invariant && a.n_splits >= 3 && a.chunk > 0 && T <= ATT_MAX_ROWS;
     int n_blocks = 0;
     if (flat) {
-        const bool three = variant == 3 || variant == 6, bulk = variant == 5 || variant == 6;
-        // three blocks with two-slot rings (70 KB of shared memory) fit an SM, two with three-slot rings
-        n_blocks = (three || variant == 4 ? 2 : 3) * attn_sm_count();
-        if (variant == 7 && group <= 8 && q8) launch_attn_flat<2, 1, ATT_SRC_Q8, 2>(s, n_blocks, a, q, kv, ri, part, T);
-        else if (variant == 7 && group <= 8) launch_attn_flat<2, 1, ATT_SRC_ASYNC, 2>(s, n_blocks, a, q, kv, ri, part, T);
-        else if (q8) launch_attn_flat_group<2, ATT_SRC_Q8>(s, n_blocks, group, a, q, kv, ri, part, T);
-        else if (!three && !bulk || variant == 7) launch_attn_flat_group<2, ATT_SRC_ASYNC>(s, n_blocks, group, a, q, kv, ri, part, T);
-        else if (!three) launch_attn_flat_group<2, ATT_SRC_BULK>(s, n_blocks, group, a, q, kv, ri, part, T);
-        else if (!bulk) launch_attn_flat_group<3, ATT_SRC_ASYNC>(s, n_blocks, group, a, q, kv, ri, part, T);
-        else launch_attn_flat_group<3, ATT_SRC_BULK>(s, n_blocks, group, a, q, kv, ri, part, T);
-    } else if (variant != 0) {
+        n_blocks = 3 * attn_sm_count();      // three blocks with two-slot rings (70 KB of shared memory) fit an SM
+        if (q8 && group <= 8) launch_attn_flat<1, ATT_SRC_Q8>(s, n_blocks, a, q, kv, ri, part, T);
+        else if (q8) launch_attn_flat<2, ATT_SRC_Q8>(s, n_blocks, a, q, kv, ri, part, T);
+        else if (group <= 8) launch_attn_flat<1, ATT_SRC_ASYNC>(s, n_blocks, a, q, kv, ri, part, T);
+        else launch_attn_flat<2, ATT_SRC_ASYNC>(s, n_blocks, a, q, kv, ri, part, T);
+    } else {
         if (q8 && group <= 8) launch_attn_split<1, ATT_SRC_Q8>(s, a, q, kv, ri, part, T);
         else if (q8) launch_attn_split<2, ATT_SRC_Q8>(s, a, q, kv, ri, part, T);
         else if (group <= 8) launch_attn_split<1, ATT_SRC_ASYNC>(s, a, q, kv, ri, part, T);
         else launch_attn_split<2, ATT_SRC_ASYNC>(s, a, q, kv, ri, part, T);
-    } else {
-        launch(attn_split_kernel, dim3((unsigned) a.n_splits, (unsigned) a.n_kv, (unsigned) T), 32 * group, 0, s, a, q, kv, ri, part);
     }
     PdlScope chain(true);      // the reduction's blocks come in while the first pass drains
     launch(attn_reduce_kernel, dim3((unsigned) a.n_head, (unsigned) T), ATT_HD, 0, s, a, (const float*) part, g, o, ri, T, n_blocks);

@@ -42,9 +42,11 @@ __global__ void __launch_bounds__(1024) ep_dispatch_kernel(NslEpWindow w, const 
     }
 }
 
-// Router + bf16 packing + dispatch in one kernel: block t routes local token t (warp 0) while its other warps convert
-// the token's row and store it into every rank's receive area; then the ids and weights follow and the block signals
-// one row to every rank.
+// Router + bf16 packing + dispatch in one kernel.  Block (t, r) serves local token t and destination rank r: warp 0 routes
+// the token (every destination's block repeats the few microseconds of routing rather than wait for one block's picks),
+// the other warps convert the token's row to bf16 and store it into rank r's receive area; then the ids and weights follow
+// and the block signals one row to rank r.  One block per (token, destination) keeps each block's remote stores short: with
+// a block per token the eight destinations' stores ran one after the other.
 template <int PER>
 __global__ void __launch_bounds__(256) ep_route_dispatch_kernel(NslEpWindow w, const float* __restrict__ logits, int ld,
                                                                const float* __restrict__ x, int E, int k, int d,
@@ -53,11 +55,13 @@ __global__ void __launch_bounds__(256) ep_route_dispatch_kernel(NslEpWindow w, c
     __shared__ int32_t s_ind[32];
     __shared__ float s_wt[32];
     grid_dependents_go();
-    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x, r = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    char* slot = recv_slot(w, r);
     if (warp == 0) {
         route_row<PER>(E, k, logits + (size_t) t * ld, lane, s_ind, s_wt);
     } else {
         const float4* xr = (const float4*) (x + (size_t) t * d);
+        uint4* dst = (uint4*) (slot + (size_t) t * d * 2);
         for (int i = threadIdx.x - 32; i < d / 8; i += 224) {
             const float4 a = __ldg(xr + 2 * i), b = __ldg(xr + 2 * i + 1);
             uint4 o;
@@ -65,24 +69,22 @@ __global__ void __launch_bounds__(256) ep_route_dispatch_kernel(NslEpWindow w, c
             o.y = bf16_bits(a.z) | ((uint32_t) bf16_bits(a.w) << 16);
             o.z = bf16_bits(b.x) | ((uint32_t) bf16_bits(b.y) << 16);
             o.w = bf16_bits(b.z) | ((uint32_t) bf16_bits(b.w) << 16);
-            for (int r = 0; r < w.n; ++r) ((uint4*) (recv_slot(w, r) + (size_t) t * d * 2))[i] = o;
+            dst[i] = o;
         }
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < w.n * k; i += 256) {
-        const int r = i / k, j = i - r * k;
-        char* slot = recv_slot(w, r);
-        ((int32_t*) (slot + ind_off))[t * k + j] = s_ind[j];
-        ((float*) (slot + wt_off))[t * k + j] = s_wt[j];
-    }
-    if (ind_out && (int) threadIdx.x < k) {      // the caller's own copy of its tokens' routing
-        ind_out[t * k + threadIdx.x] = s_ind[threadIdx.x];
-        wt_out[t * k + threadIdx.x] = s_wt[threadIdx.x];
+    if ((int) threadIdx.x < k) {
+        ((int32_t*) (slot + ind_off))[t * k + threadIdx.x] = s_ind[threadIdx.x];
+        ((float*) (slot + wt_off))[t * k + threadIdx.x] = s_wt[threadIdx.x];
+        if (ind_out && r == 0) {      // the caller's own copy of its tokens' routing
+            ind_out[t * k + threadIdx.x] = s_ind[threadIdx.x];
+            wt_out[t * k + threadIdx.x] = s_wt[threadIdx.x];
+        }
     }
     __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence_system();
-        for (int r = 0; r < w.n; ++r) red_add_sys(flag_of(w, r, w.dflag_off, w.me), 1u);
+        red_add_sys(flag_of(w, r, w.dflag_off, w.me), 1u);
     }
 }
 
@@ -208,7 +210,7 @@ void nsl_ep_p2p_route_dispatch(cudaStream_t s, NslEpWindow w, int n_exp, int top
                   n_exp, top_k, d);
         return;
     }
-    const unsigned grid = (unsigned) w.t_loc;
+    const dim3 grid((unsigned) w.t_loc, (unsigned) w.n);
     if (n_exp <= 128) ep_route_dispatch_kernel<4><<<grid, 256, 0, s>>>(w, logits, ld, x, n_exp, top_k, d, ind_off, wt_off, ind_out, wt_out);
     else if (n_exp <= 512) ep_route_dispatch_kernel<16><<<grid, 256, 0, s>>>(w, logits, ld, x, n_exp, top_k, d, ind_off, wt_off, ind_out, wt_out);
     else ep_route_dispatch_kernel<32><<<grid, 256, 0, s>>>(w, logits, ld, x, n_exp, top_k, d, ind_off, wt_off, ind_out, wt_out);

@@ -515,9 +515,6 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
     }
 }
 
-static int g_q4_variant = 1;   // 1 (default): K split over the warps where K allows, else the ring with 8 warps; 2: the ring with
-                               // 8 warps x 4 stages of 8 groups; 0: the ring with 16 warps x 4 stages of 4 groups
-
 // Called by kc_mv for fmt == MF_Q4.  Returns false (with the error recorded) when the shape is not served.
 bool launch_q4_mv(cudaStream_t s, const WSlice& w, int K, int R, const float* x, int xs, float* y, int ys, int T, int add) {
     if (K < Q4_GROUP || K % Q4_GROUP || R < 1 || T < 1 || T > MV_MAXT || (w.gs != 0 && w.gs != 6)) {
@@ -538,7 +535,7 @@ bool launch_q4_mv(cudaStream_t s, const WSlice& w, int K, int R, const float* x,
         attr_set[dev & 15] = true;
     }
     const size_t budget = (size_t) max_smem_optin() - 1024;
-    if (g_q4_variant == 1 && aligned16(w.p[0]) && (K == 1024 || K == 2048 || K == 4096)) {      // K split over the block's warps
+    if (aligned16(w.p[0]) && (K == 1024 || K == 2048 || K == 4096)) {      // K split over the block's warps
         const int warps = K / 256, nst = warps == 16 ? 3 : 6;      // stages per warp: what fits beside 16 warps' rings
         const size_t total = smem + (size_t) 2 * warps * 512 + (size_t) warps * nst * Q4Ring<4>::STAGE;
         if (total <= budget) {
@@ -553,13 +550,10 @@ bool launch_q4_mv(cudaStream_t s, const WSlice& w, int K, int R, const float* x,
     if (K % 512 == 0 && aligned16(w.p[0]) && smem + (size_t) 8 * 2 * Q4Ring<8>::STAGE <= budget) {      // streams through shared memory
         // 8 warps with three passes of eight groups in flight each (measured faster than 16 warps with three passes of four:
         // 66.9 against 77.2 us on the 151936 x 2048 head), or 8 warps with one pass in flight when shared memory is short
-        const int variant = smem + (size_t) 16 * 4 * Q4Ring<4>::STAGE <= budget ? (g_q4_variant == 0 ? 0 : 1)
-                          : smem + (size_t) 8 * 4 * Q4Ring<8>::STAGE <= budget ? 1 : 2;
-        const int warps = variant == 0 ? 16 : 8;
-        int blocks = (tiles + warps - 1) / warps;
+        const bool deep = smem + (size_t) 8 * 4 * Q4Ring<8>::STAGE <= budget;
+        int blocks = (tiles + 7) / 8;
         if (blocks > sm_count()) blocks = sm_count();
-        if (variant == 0) launch_q4_ring<4, 16, 4>(s, smem + (size_t) 16 * 4 * Q4Ring<4>::STAGE, blocks, w, K, R, x, xs, y, ys, T, add);
-        else if (variant == 1) launch_q4_ring<4, 8, 8>(s, smem + (size_t) 8 * 4 * Q4Ring<8>::STAGE, blocks, w, K, R, x, xs, y, ys, T, add);
+        if (deep) launch_q4_ring<4, 8, 8>(s, smem + (size_t) 8 * 4 * Q4Ring<8>::STAGE, blocks, w, K, R, x, xs, y, ys, T, add);
         else launch_q4_ring<2, 8, 8>(s, smem + (size_t) 8 * 2 * Q4Ring<8>::STAGE, blocks, w, K, R, x, xs, y, ys, T, add);
         count_launch();
         return true;
@@ -590,8 +584,5 @@ void kc_argmax_p(cudaStream_t s, const float* logits, int32_t* out, float* prob,
 }
 
 void kc_argmax(cudaStream_t s, const float* logits, int32_t* out, int V, int n) { kc_argmax_p(s, logits, out, NULL, V, n); }
-
-// Picks between the two ring shapes of the Q4 mat-vec where both fit (1, the default: 8 warps; 0: 16 warps): for timing.
-void nsl_q4_set_variant(int v) { g_q4_variant = v < 0 || v > 2 ? 1 : v; }
 
 }   // extern "C"

@@ -94,10 +94,8 @@ PROTOTYPES = {
     "kc_router_topk": (None, [_vp, RouterArgs, _vp, _vp, _vp, _vp, _i]),
     "kc_heads_mv": (None, [_vp, HmvArgs, _i, WSlice, _vp, _vp, _vp, _vp, _i]),
     "kc_heads_deq": (None, [_vp, _i, WSlice, _vp, _i, _i, _i, _vp]),
-    "nsl_attn_set_variant": (None, [_i]),
-    "nsl_attn_status": (_i, []),
+    "nsl_attn_batch_invariant": (None, [_i]),
     "kc_attn": (None, [_vp, AttnArgs, _vp, KvView, _vp, _vp, _vp, _vp, _i]),
-    "nsl_q4_set_variant": (None, [_i]),
     "kc_argmax": (None, [_vp, _vp, _vp, _i, _i]),
     "kc_argmax_p": (None, [_vp, _vp, _vp, _vp, _i, _i]),
     "kc_cache_admit": (None, [_vp, C.POINTER(CachePool), _i, _vp, _i, _i]),

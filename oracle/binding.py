@@ -12,9 +12,10 @@ _LIB = None
 _REF = None
 
 
-def build(ref_root="/root/reference"):
-    """Compile liboracle.so (and oracle/_ref when the reference tree is present)."""
-    subprocess.run(["make", "-s", "-C", HERE, f"REF={ref_root}"], check=True)
+def build(ref_root=None):
+    """Compile liboracle.so (and oracle/_ref when the reference tree is present: ref_root, else $NSLM_REFERENCE_ROOT, else a
+    checkout named `reference` beside this repository)."""
+    subprocess.run(["make", "-s", "-C", HERE] + ([f"REF={ref_root}"] if ref_root else []), check=True)
 
 
 def lib():

@@ -13,16 +13,14 @@ pytestmark = pytest.mark.gpu
 
 
 def run_case(nh, nkv, NP, pos, kv0, ns, chunk, gate=True, nv=None, seed=21):
-    for variant in (1, 2, 3, 4, 5, 6, 7, 0):   # tensor cores (balanced blocks; a block per split; three-slot rings; two blocks an
-                                               # SM; rows by the copy engine with two and three slots; two warps a ring), the scalar pass
-        run_variant(variant, nh, nkv, NP, pos, kv0, ns, chunk, gate, nv, seed)
-    for variant in (1, 2, 4, 7):               # the 8-bit cache: balanced blocks, a block per split, two blocks an SM, two warps a ring
-        run_variant(variant, nh, nkv, NP, pos, kv0, ns, chunk, gate, nv, seed, q8=True)
+    for invariant in (0, 1):      # the step's keys dealt evenly to the blocks (default); a block per caller split
+        run_variant(invariant, nh, nkv, NP, pos, kv0, ns, chunk, gate, nv, seed)
+        run_variant(invariant, nh, nkv, NP, pos, kv0, ns, chunk, gate, nv, seed, q8=True)      # the 8-bit cache
 
 
 def run_variant(variant, nh, nkv, NP, pos, kv0, ns, chunk, gate, nv, seed, q8=False):
     from nanoseedlm_b200 import kernels, lib as L
-    L.load().nsl_attn_set_variant(variant)
+    L.load().nsl_attn_batch_invariant(variant)
     rng = np.random.default_rng(seed)
     T = len(pos)
     q = B.bfr((rng.random((T, nh, 128), np.float32) * 2 - 1) * 2)
@@ -38,8 +36,7 @@ def run_variant(variant, nh, nkv, NP, pos, kv0, ns, chunk, gate, nv, seed, q8=Fa
     else:
         o = kernels.kt_attn(a, q, Kc, Vc, pos, kv0, g if gate else None, nv)
     ref, _ = B.attn_decode(q, Kc, Vc, pos, kv0, nkv, scale, g if gate else None)
-    L.load().nsl_attn_set_variant(1)      # back to the default
-    assert L.load().nsl_attn_status() == 0      # no wait for K / V rows ran out
+    L.load().nsl_attn_batch_invariant(0)      # back to the default
     # the reference's bound; an output whose attention value sits on a bf16 rounding boundary can land one unit further
     # after the gate's second rounding: at most one element in a thousand, and never beyond twice the bound
     bound = np.abs(ref) / 128 + 2e-6
@@ -63,8 +60,37 @@ def test_ragged_rows_as_the_reference_host_splits_them():
     rng = np.random.default_rng(3)
     pos = [2999, 0, 15, 16, 1500, 127, 128, 2047, 700, 31, 2998, 5]
     run_case(8, 2, 12 * 3008, pos, [3008 * i for i in range(12)], 32, 128, seed=9)
-    for variant in (1, 3, 5, 6, 7):
-        run_variant(variant, 16, 1, 6000, [5999], [0], 32, 188, True, None, 4)      # one row, one KV head: its units over 30 blocks
+    run_variant(0, 16, 1, 6000, [5999], [0], 32, 188, True, None, 4)      # one row, one KV head: its units over 30 blocks
+
+
+def test_a_row_alone_and_in_a_batch():
+    """With nsl_attn_batch_invariant(1) a row's output is bit-identical whatever rows share the call (its keys are cut by its
+    own position alone, as the reference cuts them: engine/kernels_moe.cu:887-952); the default balanced form cuts a row's
+    keys by the whole step's load, so alone and batched agree only within the kernel's bound."""
+    from nanoseedlm_b200 import kernels, lib as L
+    rng = np.random.default_rng(12)
+    nh, nkv, ns, chunk = 8, 2, 16, 128
+    pos = [1900, 7, 640, 1203, 64, 1999]
+    kv0 = [2000 * i for i in range(len(pos))]
+    NP = 2000 * len(pos)
+    q = B.bfr((rng.random((len(pos), nh, 128), np.float32) * 2 - 1) * 2)
+    g = B.bfr((rng.random((len(pos), nh, 128), np.float32) * 2 - 1) * 3)
+    Kc = B.f2bf((rng.random((NP, nkv, 128), np.float32) * 2 - 1) * 2)
+    Vc = B.f2bf(rng.random((NP, nkv, 128), np.float32) * 2 - 1)
+    a = L.AttnArgs(nh, nkv, chunk, ns, float(1 / np.sqrt(128.0)))
+    ref, _ = B.attn_decode(q, Kc, Vc, pos, kv0, nkv, np.float32(1 / np.sqrt(128.0)), g)
+    try:
+        for on in (1, 0):
+            L.load().nsl_attn_batch_invariant(on)
+            batch = kernels.kt_attn(a, q, Kc, Vc, pos, kv0, g, None)
+            for t in (0, 3, 5):
+                alone = kernels.kt_attn(a, q[t:t + 1], Kc, Vc, pos[t:t + 1], kv0[t:t + 1], g[t:t + 1], None)
+                if on:
+                    assert np.array_equal(alone[0].view(np.uint32), batch[t].view(np.uint32)), t
+                else:
+                    assert (np.abs(alone[0] - batch[t]) <= 2 * (np.abs(ref[t]) / 128 + 2e-6)).all(), t
+    finally:
+        L.load().nsl_attn_batch_invariant(0)
 
 
 def test_one_split_no_gate_and_two_segments():
