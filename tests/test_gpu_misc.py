@@ -42,7 +42,7 @@ def test_bucket_against_host_grouping(oracle, n, rows, k):
     assert np.array_equal(perm, rperm) and tiles == rtiles and nt == len(rtiles)
 
 
-def test_swiglu_combines_and_pack(oracle):
+def test_swiglu_and_combines(oracle):
     from nanoseedlm_b200 import kernels
     n = 5000
     g = oracle.normal(1, n, bf16=True) * 3
@@ -61,6 +61,11 @@ def test_swiglu_combines_and_pack(oracle):
     ref = oracle.moe_combine(Db, wb, shb, xb, T, d, k).reshape(T, d)
     assert np.mean(got.reshape(T, d) == ref) > 0.99   # bf16 points; an f32 sum-order flip may move one ulp
     assert np.max(np.abs(got.reshape(T, d) - ref)) <= np.max(np.abs(ref)) / 64
+
+
+def test_pack_input_bf16_any_length(oracle):
+    """Round to nearest even, every element of any n (the reference's kernel packs whole groups of 8: engine/kernels_moe.cu:2196-2201)."""
+    from nanoseedlm_b200 import kernels
     x = oracle.normal(11, 1003)
     u32 = x.view(np.uint32).astype(np.uint64)
     want = ((u32 + 0x7FFF + ((u32 >> 16) & 1)) >> 16).astype(np.uint16)

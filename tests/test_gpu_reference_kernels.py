@@ -157,7 +157,7 @@ def test_reference_kernels_pass_this_suites_checks(oracle, golden):
             test_gpu_misc.test_route_shapes(oracle, T, E, k)
         for n, rows, k in ((128, 512, 10), (512, 64, 10), (4, 1, 1)):
             test_gpu_misc.test_bucket_against_host_grouping(oracle, n, rows, k)
-        test_gpu_misc.test_swiglu_combines_and_pack(oracle)
+        test_gpu_misc.test_swiglu_and_combines(oracle)
         for K in (256, 512, 4096):      # the reference's own K list (tests/test_mova_kernels.c:161)
             test_gpu_mv.test_mv_dense_tokens_add_and_batch_invariance(oracle, K)
         test_gpu_cache.test_cache_admit_copy_and_identical_results(oracle)
