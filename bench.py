@@ -40,7 +40,8 @@ D, FF, E, TOPK = 2048, 512, 128, 8
 BYTES_PER_MATRIX = D * FF // 8 * 4 + D * FF // 16        # 589,824: seeds + coefficient words + exponent codes
 BLOCKS_PER_MATRIX = D * FF // 8                           # 131,072 blocks of 8 weights
 ALU_FLOOR = 53 / 64        # clocks per block per SM: 53 logic-pipe operations per block, 64 logic lanes per SM and clock
-                           # (profiles/logic_pipe_rates.md)
+                           # (ncu agrees: 113.4 k blocks per SM in 141.3 k active cycles with sm__pipe_alu_cycles_active
+                           # at 70 %; profiles/mv_pair_gate_up_config1.md)
 METRIC = "seed_decode_moe_gemv_tokens_per_s"
 # DRAM bytes per launch of the gate+up kernel from ncu (profiles/mv_pair_gate_up_config1.md): per distinct expert
 # (gate + up streams: pairs that share an expert find its streams in L2) and the rest (activations, tables)
@@ -836,7 +837,9 @@ def measure_ep(args, K, W, quiet_clocks=False):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     lib = L.load()
-    e_loc, t_loc = EP_E // world, EP_B // world
+    share = max(1, args.ep_share) if world == 1 else 1      # one GPU running the share a rank has at `share` GPUs (profiling)
+    n_exp, n_rows = EP_E // share, EP_B // share
+    e_loc, t_loc = n_exp // world, n_rows // world
     NL = max(2, min(args.layers, int(6e9 // (e_loc * 3 * BYTES_PER_MATRIX))))
     mirror = bool(args.ep_mirror) and world % 2 == 0 and args.ep_collectives == "p2p"
 
@@ -848,17 +851,17 @@ def measure_ep(args, K, W, quiet_clocks=False):
     if mirror:              # this rank also holds its partner's experts (own first, then the partner's)
         layers = [moe.DeviceLayer.concat(a, b) for a, b in zip(layers, experts_of((rank + world // 2) % world))]
     be = ep.CudaBackend(layers[0])
-    epl = ep.ExpertParallelMoe(be, D, EP_K, EP_E, t_loc, collectives=args.ep_collectives, mirror=mirror)
+    epl = ep.ExpertParallelMoe(be, D, EP_K, n_exp, t_loc, collectives=args.ep_collectives, mirror=mirror)
     NB = 8
     rng = np.random.default_rng(7)      # the whole batch on every rank; a rank takes its rows
-    gx = bf16r(rng.standard_normal((NB, EP_B, D)).astype(np.float32))
-    gl = rng.standard_normal((NB, EP_B, EP_E)).astype(np.float32)
+    gx = bf16r(rng.standard_normal((NB, n_rows, D)).astype(np.float32))
+    gl = rng.standard_normal((NB, n_rows, n_exp)).astype(np.float32)
     rows = slice(rank * t_loc, (rank + 1) * t_loc)
     hx, hl = np.ascontiguousarray(gx[:, rows]), np.ascontiguousarray(gl[:, rows])
     dx, dl = torch.from_numpy(hx).cuda(), torch.from_numpy(hl).cuda()
     px, pl = torch.from_numpy(hx).pin_memory(), torch.from_numpy(hl).pin_memory()
     pout = torch.zeros(t_loc, D).pin_memory()
-    sx, sl = torch.zeros(t_loc, D, device="cuda"), torch.zeros(t_loc, EP_E, device="cuda")
+    sx, sl = torch.zeros(t_loc, D, device="cuda"), torch.zeros(t_loc, n_exp, device="cuda")
     stream = torch.cuda.Stream()
     torch.cuda.synchronize()
 
@@ -885,7 +888,7 @@ def measure_ep(args, K, W, quiet_clocks=False):
             whole = parts[0]
             for p in parts[1:]:
                 whole = moe.DeviceLayer.concat(whole, p)
-        m1 = moe.Moe(whole, EP_K, EP_B)
+        m1 = moe.Moe(whole, EP_K, n_rows)
         m1.set_grouped_min_tokens(10 ** 6)
         want, _ = m1.forward_host(gx[0], gl[0])
         m1.close()
@@ -967,12 +970,12 @@ def measure_ep(args, K, W, quiet_clocks=False):
     peaks, peak_kind = measured_peaks()
     # the whole step against the packed-bytes roofline: the experts a step touches, in expectation over the routing
     # (E (1 - (1 - k/E)^B) distinct experts of 3 matrices each), read once by whichever rank owns them
-    distinct = EP_E * (1.0 - (1.0 - EP_K / EP_E) ** EP_B)
+    distinct = n_exp * (1.0 - (1.0 - EP_K / n_exp) ** n_rows)
     gbs = distinct * 3 * BYTES_PER_MATRIX / (ms_per_step * 1e-3) / 1e9
-    res = {"value": EP_B / (ms_per_step * 1e-3), "ms_per_step": ms_per_step, "gpu_launches": int(launches), "cuda_graph": captured,
+    res = {"value": n_rows / (ms_per_step * 1e-3), "ms_per_step": ms_per_step, "gpu_launches": int(launches), "cuda_graph": captured,
            "collectives": args.ep_collectives, "mirrored_ranks": mirror, "clocks": clocks.summary(), "l2_policy": l2_policy(NL, e_loc),
            "pairs_on_rank0_last_step": pairs, "parity": parity,
-           "e2e": {"value": EP_B / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": t_loc * D * 4 + t_loc * EP_E * 4,
+           "e2e": {"value": n_rows / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": t_loc * D * 4 + t_loc * n_exp * 4,
                    "d2h_bytes_per_step": t_loc * D * 4, "ms_per_step": e2e_s * 1e3, "steps_in_flight": 1},
            "roofline": {"bound": "hbm", "kernel": "the step's seed mat-vecs (gate+up and down over the ranks' pairs: mv_grp_kernel beyond 64 pairs a rank, else mv_pair_kernel)",
                         "achieved": gbs, "peak": peaks["hbm_gbs"] * world, "unit": "GB/s", "frac": gbs / (peaks["hbm_gbs"] * world),
@@ -1007,7 +1010,10 @@ def main():
     ap.add_argument("--ep-mirror", type=int, default=0,
                     help="config 3, p2p, even rank counts: 1 = ranks r and r + N/2 hold each other's experts too and split their "
                          "joint pairs in the middle (balance to within one pair; twice the expert bytes per GPU)")
-    ap.add_argument("--workload", default=None, choices=["cfg0", "cfg1", "cfg2", "cfg3", "cfg4", "lmhead", "attn", "upload"],
+    ap.add_argument("--ep-share", type=int, default=1,
+                    help="config 3 on ONE GPU, profiling: run the share one rank has at this many GPUs (512 / n experts, 64 / n rows x "
+                         "top-10: the pair count and expert count of a rank's mat-vecs, without the other ranks)")
+    ap.add_argument("--workload", default=None, choices=["cfg0", "cfg1", "cfg2", "cfg3", "cfg4", "lmhead", "attn", "upload", "p3"],
                     help="one workload alone as the line (profiling): cfg1 one GPU's MoE decode layer; cfg2 the same layer on 512 "
                          "prompt rows (grouped tcgen05 GEMM); cfg3 expert-parallel decode (the default at >1 GPU); cfg0 / lmhead / attn")
     args = ap.parse_args()
@@ -1038,6 +1044,10 @@ def main():
         r = measure_ep(args, K, W)
         if rank == 0:
             line = dict(base, value=r.pop("value"), ms_per_step=r.pop("ms_per_step"), config=ep_config(world), workload_id="cfg3", **r)
+            if world == 1 and args.ep_share > 1:
+                line["workload_id"] = f"cfg3_share_of_{args.ep_share}"
+                line["config"] = dict(line["config"], share=f"one rank's share at {args.ep_share} GPUs: {EP_E // args.ep_share} experts, "
+                                                            f"{EP_B // args.ep_share} rows x top-{EP_K}, alone on one GPU (no exchange partner)")
             print(json.dumps(line))
         if world > 1:
             dist.destroy_process_group()
@@ -1052,7 +1062,7 @@ def main():
             dist.destroy_process_group()
         return
 
-    if workload in ("cfg0", "lmhead", "attn", "upload"):      # one secondary workload alone
+    if workload in ("cfg0", "lmhead", "attn", "upload", "p3"):      # one secondary workload alone
         print(json.dumps(dict(base, **secondary(workload, K, W, peaks, peak_kind, sms, args))))
         return
 
@@ -1089,7 +1099,7 @@ def main():
     del c, r
     torch.cuda.empty_cache()
     if extra:
-        for name in ("cfg0", "lmhead", "attn", "upload"):
+        for name in ("cfg0", "lmhead", "attn", "upload", "p3"):
             line["workloads"][name] = secondary(name, min(K, 1000), W, peaks, peak_kind, sms, args, sm_mhz=clocks.get("sm_mhz"))
             torch.cuda.empty_cache()
         try:      # the whole decoder of config 4 on this one GPU (44 GB of experts): reported, with its error if it cannot run
@@ -1107,6 +1117,80 @@ def main():
     print(json.dumps(line))
 
 
+def measure_p3(K, W):
+    """The config-1 / config-2 layer with P = 3 (MF_SEED4) experts: 8 decode rows through kc_mv_gu / kc_mv_sel (the any-shape
+    mat-vec kernel serves this format) and 512 prompt rows through kc_bucket + kc_mm_grouped_dev (the tcgen05 GEMM with the
+    P = 3 tile producer).  4 layers rotated (0.8 GB of packed streams)."""
+    import torch
+    from nanoseedlm_b200 import kernels, lib as L
+    lib = L.load()
+    NL, nb = 4, D * FF // 8
+    gen = torch.Generator(device="cuda").manual_seed(303)
+    keep, tabs = [], []
+    for _ in range(NL):
+        lay = []
+        for _m in range(3):      # gate, up [FF][D]; down [D][FF]: the same block count
+            seeds = torch.randint(1, 65536, (E, nb), generator=gen, device="cuda", dtype=torch.int32).to(torch.int16)
+            nibs = torch.randint(0, 65536, (E, nb), generator=gen, device="cuda", dtype=torch.int32).to(torch.int16)
+            arr = (L.WSlice * E)()
+            for e in range(E):
+                arr[e].p[0], arr[e].p[1], arr[e].eb = seeds[e].data_ptr(), nibs[e].data_ptr(), -22
+            tab = torch.empty(E * C.sizeof(L.WSlice), dtype=torch.uint8, device="cuda")
+            tab.copy_(torch.frombuffer(bytearray(bytes(arr)), dtype=torch.uint8))
+            keep += [seeds, nibs]
+            lay.append(tab)
+        tabs.append(lay)
+    G = kernels.stream_table()
+    stream = torch.cuda.Stream()
+    s = stream.cuda_stream
+    out = {}
+    for M in (8, 512):
+        P = M * TOPK
+        rng = np.random.default_rng(5 + M)
+        x = torch.from_numpy(bf16r(rng.standard_normal((M, D)).astype(np.float32))).cuda()
+        lg = torch.from_numpy(rng.standard_normal((M, E)).astype(np.float32)).cuda()
+        ind, wt = torch.zeros(P, dtype=torch.int32, device="cuda"), torch.zeros(P, device="cuda")
+        A, U, Dx = torch.zeros(P, FF, device="cuda"), torch.zeros(P, FF, device="cuda"), torch.zeros(P, D, device="cuda")
+        perm = torch.zeros(P, dtype=torch.int32, device="cuda")
+        tiles = torch.zeros((P // 128 + E + 1) * 4, dtype=torch.int32, device="cuda")
+        work = torch.zeros(2 * E + 3, dtype=torch.int32, device="cuda")
+        res, sh, sg = torch.zeros(M, D, device="cuda"), torch.zeros(M, D, device="cuda"), torch.zeros(M, device="cuda")
+        mt = P // 128 + E
+
+        def step(i):
+            g, u, d = (t.data_ptr() for t in tabs[i % NL])
+            lib.nsl_route(s, E, TOPK, lg.data_ptr(), E, ind.data_ptr(), wt.data_ptr(), M)
+            if M <= 8:
+                lib.kc_mv_gu(s, L.MF_SEED4, g, u, D, FF, x.data_ptr(), D, A.data_ptr(), FF, ind.data_ptr(), P, TOPK, G.data_ptr())
+                lib.kc_mv_sel(s, L.MF_SEED4, d, FF, D, A.data_ptr(), FF, Dx.data_ptr(), D, ind.data_ptr(), P, 1, G.data_ptr())
+            else:
+                lib.kc_bucket(s, ind.data_ptr(), P, E, perm.data_ptr(), tiles.data_ptr(), work.data_ptr())
+                for tab, dst in ((g, A), (u, U)):
+                    lib.kc_mm_grouped_dev(s, L.MF_SEED4, tab, D, FF, x.data_ptr(), D, dst.data_ptr(), FF, TOPK, perm.data_ptr(), tiles.data_ptr(),
+                                          work.data_ptr(), mt, G.data_ptr())
+                lib.kc_swiglu(s, A.data_ptr(), U.data_ptr(), A.data_ptr(), P * FF)
+                lib.kc_mm_grouped_dev(s, L.MF_SEED4, d, FF, D, A.data_ptr(), FF, Dx.data_ptr(), D, 1, perm.data_ptr(), tiles.data_ptr(),
+                                      work.data_ptr(), mt, G.data_ptr())
+            lib.kq4_moe_combine(s, D, TOPK, Dx.data_ptr(), wt.data_ptr(), sh.data_ptr(), sg.data_ptr(), 1, res.data_ptr(), M)
+
+        n = min(K, 200)
+        with torch.cuda.stream(stream):
+            for i in range(max(W, 3)):
+                step(i)
+            stream.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for i in range(n):
+                step(W + i)
+            e1.record(stream)
+            e1.synchronize()
+        L.check()
+        ms = e0.elapsed_time(e1) / n
+        out[f"m{M}"] = {"ms_per_step": ms, "value": M / (ms * 1e-3), "unit": "tok/s", "finite": bool(torch.isfinite(res).all().item())}
+    out["mm_status"] = int(lib.nsl_mm_status())
+    return out
+
+
 def secondary(name, K, W, peaks, peak_kind, sms, args, sm_mhz=None):
     """cfg0, the LM head or decode attention as a result object with its roofline."""
     if name == "cfg0":
@@ -1121,6 +1205,10 @@ def secondary(name, K, W, peaks, peak_kind, sms, args, sm_mhz=None):
         return out
     if name == "upload":
         return measure_upload(K, W)
+    if name == "p3":
+        r = measure_p3(K, W)
+        return dict(r, workload=f"the config-1 / config-2 layer with P = 3 (MF_SEED4) experts: hidden {D}, {E} experts of intermediate {FF}, top-{TOPK}; "
+                                "8 decode rows (any-shape mat-vec kernel) and 512 prompt rows (tcgen05 GEMM with the P = 3 tile producer)")
     if name == "lmhead":
         r = measure_lmhead(8, min(K, 300), W)
         gbs = r["bytes"] / (r["mv_us"] * 1e-6) / 1e9

@@ -96,9 +96,11 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* v) {
 }
 
 // A thread's share of one K step: 4 consecutive blocks of its row = two block pairs (seed / coefficient words packed
-// two per 32-bit word, even block low) and their 4 exponent codes (one nibble each, block j at bits 4j).
+// two per 32-bit word, even block low) and their 4 exponent codes (one nibble each, block j at bits 4j).  P = 3 (SEED4)
+// has no code stream: a block's code is the low nibble of its nibble word, read where the weights are formed.
 struct QuadIn { uint32_t sw[2], cw[2], codes; bool live; };
 
+template <bool P3>
 __device__ __forceinline__ QuadIn load_quad(const WSlice& w, int row, int kb, int R, int NB, bool vec) {
     QuadIn q = {{0u, 0u}, {0u, 0u}, 0u, false};
     if (row >= R || kb >= NB) return q;
@@ -108,13 +110,13 @@ __device__ __forceinline__ QuadIn load_quad(const WSlice& w, int row, int kb, in
         const uint2 s2 = __ldg((const uint2*) ((const uint16_t*) w.p[0] + g));
         const uint2 c2 = __ldg((const uint2*) ((const uint16_t*) w.p[1] + g));
         q.sw[0] = s2.x; q.sw[1] = s2.y; q.cw[0] = c2.x; q.cw[1] = c2.y;
-        q.codes = __ldg((const uint16_t*) ((const uint8_t*) w.p[3] + (g >> 1)));
+        if (!P3) q.codes = __ldg((const uint16_t*) ((const uint8_t*) w.p[3] + (g >> 1)));
     } else {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             if (kb + j >= NB) break;   // (a missing block keeps seed 0: its weights are forced to zero below)
             const uint32_t sd = __ldg((const uint16_t*) w.p[0] + g + j), cf = __ldg((const uint16_t*) w.p[1] + g + j);
-            const uint32_t cd = (__ldg((const uint8_t*) w.p[3] + ((g + j) >> 1)) >> (((g + j) & 1) * 4)) & 15u;
+            const uint32_t cd = P3 ? 0u : (__ldg((const uint8_t*) w.p[3] + ((g + j) >> 1)) >> (((g + j) & 1) * 4)) & 15u;
             q.sw[j >> 1] |= sd << (16 * (j & 1));
             q.cw[j >> 1] |= cf << (16 * (j & 1));
             q.codes |= cd << (4 * j);
@@ -123,8 +125,10 @@ __device__ __forceinline__ QuadIn load_quad(const WSlice& w, int row, int kb, in
     return q;
 }
 
-template <int NT, bool BF16W>
+// WF: the weights' form.  0: SEED4P4 blocks; 1: stored BF16 values; 2: SEED4 (P = 3) blocks.
+template <int NT, int WF>
 __global__ void __launch_bounds__(GM_THREADS, 2) seed_gemm_kernel(MmParams a, KConst kc) {
+    constexpr bool BF16W = WF == 1, P3 = WF == 2;
     if (a.ntiles && (int) blockIdx.y >= *a.ntiles) return;
     extern __shared__ uint8_t smem_raw[];
     __shared__ StreamTab tab;
@@ -195,14 +199,14 @@ __global__ void __launch_bounds__(GM_THREADS, 2) seed_gemm_kernel(MmParams a, KC
             }
         };
         if (BF16W) load_bf16(0, bcur);
-        else cur = load_quad(w, grow, half * 4, a.R, NB, vec);
+        else cur = load_quad<P3>(w, grow, half * 4, a.R, NB, vec);
         nxt = cur;
         bool live = true;
         for (int kt = 0; kt < KT && live; ++kt) {
             const int s = kt % GM_STAGES;
             if (kt + 1 < KT) {
                 if (BF16W) load_bf16(kt + 1, bnxt);
-                else nxt = load_quad(w, grow, (kt + 1) * 8 + half * 4, a.R, NB, vec);
+                else nxt = load_quad<P3>(w, grow, (kt + 1) * 8 + half * 4, a.R, NB, vec);
             }
             if (kt >= GM_STAGES && !mbar_wait(bar_empty + 8 * s, ((kt / GM_STAGES) - 1) & 1, &abort_flag)) {
                 abort_flag = 1;
@@ -222,13 +226,20 @@ __global__ void __launch_bounds__(GM_THREADS, 2) seed_gemm_kernel(MmParams a, KC
 #pragma unroll
             for (int bp = 0; bp < (BF16W ? 0 : 2); ++bp) {
                 float wa[8], wb[8];
-                if (cur.live) {
+                if (cur.live && P3) {      // two P = 3 blocks, each bit for bit as nsl_decode3_f32 gives it
+                    const uint32_t sa = cur.sw[bp] & 0xFFFFu, sb = cur.sw[bp] >> 16, na = cur.cw[bp] & 0xFFFFu, nb = cur.cw[bp] >> 16;
+                    const uint32_t ga = stream_bits(tab, sa), gb = stream_bits(tab, sb);
+                    block_weights3(sa | (ga << 16), ga, na, exact_scale45(w.eb + (int) (na & 15u) + 1), kc, wa);
+                    block_weights3(sb | (gb << 16), gb, nb, exact_scale45(w.eb + (int) (nb & 15u) + 1), kc, wb);
+                } else if (cur.live) {
                     const uint32_t cd = cur.codes >> (8 * bp);
                     const u64 sc2 = pack2(exact_scale45(w.eb + (int) (cd & 15u)), exact_scale45(w.eb + (int) ((cd >> 4) & 15u)));
                     u64 w2[8];
                     pair_weights(tab, cur.sw[bp], cur.cw[bp], sc2, kc, w2);
 #pragma unroll
                     for (int i = 0; i < 8; ++i) unpack2(w2[i], wa[i], wb[i]);
+                }
+                if (cur.live) {
                     if (!vec) {   // a row whose block count is not a multiple of 4 ends inside a quad: blocks past it are zero
                         const bool has_a = (cur.sw[bp] & 0xFFFFu) != 0u, has_b = (cur.sw[bp] >> 16) != 0u;
 #pragma unroll
@@ -340,25 +351,28 @@ __global__ void __launch_bounds__(GM_THREADS, 2) seed_gemm_kernel(MmParams a, KC
     }
 }
 
+bool launch_bf16_mm_skinny(cudaStream_t s, const WSlice& w, int K, int R, const float* x, int xs, float* y, int ys, int T, int add);
+
 static int g_exact;   // kc_seed_gemm_f32: process-wide, as the reference's switch (engine/kernels_moe.cu:2354)
 
-template <int NT, bool BF16W>
+template <int NT, int WF>
 static void launch_gemm_nt(cudaStream_t s, const MmParams& a, dim3 grid) {
     const size_t smem = (size_t) GM_STAGES * (NT + 1) * GM_TILE_BYTES + 1024;
     static bool attr_set[16];
     int dev = 0;
     cudaGetDevice(&dev);
     if (!attr_set[dev & 15]) {
-        cudaFuncSetAttribute(seed_gemm_kernel<NT, BF16W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+        cudaFuncSetAttribute(seed_gemm_kernel<NT, WF>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
         attr_set[dev & 15] = true;
     }
-    seed_gemm_kernel<NT, BF16W><<<grid, GM_THREADS, smem, s>>>(a, kconst());
+    seed_gemm_kernel<NT, WF><<<grid, GM_THREADS, smem, s>>>(a, kconst());
     count_launch();
 }
 
 static void launch_gemm(cudaStream_t s, int fmt, const char* who, MmParams a, int tiles_y) {
-    if (fmt != MF_SEED4P4 && fmt != MF_BF16) {
-        set_error("%s: weight format %d is not served by this library (SEED4P4 = %d and BF16 = %d only)", who, fmt, (int) MF_SEED4P4, (int) MF_BF16);
+    if (fmt != MF_SEED4P4 && fmt != MF_SEED4 && fmt != MF_BF16) {
+        set_error("%s: weight format %d is not served by this library (SEED4P4 = %d, SEED4 = %d and BF16 = %d only)", who, fmt, (int) MF_SEED4P4,
+                  (int) MF_SEED4, (int) MF_BF16);
         return;
     }
     if (a.K <= 0 || a.K % 8 || a.R <= 0) { set_error("%s: K = %d (a multiple of 8), R = %d", who, a.K, a.R); return; }
@@ -369,9 +383,10 @@ static void launch_gemm(cudaStream_t s, int fmt, const char* who, MmParams a, in
         return;
     }
     const dim3 grid((unsigned) ((a.R + GM_BM - 1) / GM_BM), (unsigned) tiles_y);
-    if (fmt == MF_BF16) launch_gemm_nt<1, true>(s, a, grid);      // stored BF16 weights (p[0] = [R][K]): no expansion, one term
-    else if (g_exact) launch_gemm_nt<3, false>(s, a, grid);
-    else launch_gemm_nt<1, false>(s, a, grid);
+    if (fmt == MF_BF16) launch_gemm_nt<1, 1>(s, a, grid);      // stored BF16 weights (p[0] = [R][K]): no expansion, one term
+    else if (fmt == MF_SEED4) { if (g_exact) launch_gemm_nt<3, 2>(s, a, grid); else launch_gemm_nt<1, 2>(s, a, grid); }      // P = 3
+    else if (g_exact) launch_gemm_nt<3, 0>(s, a, grid);
+    else launch_gemm_nt<1, 0>(s, a, grid);
 }
 
 }   // namespace nsl
@@ -384,6 +399,7 @@ void kc_seed_gemm_f32(int on) { g_exact = on; }
 
 void kc_mm(cudaStream_t s, int fmt, WSlice w, int K, int R, const float* x, int xs, float* y, int ys, int T, int add,
            const uint32_t* G) {
+    if (fmt == MF_BF16 && launch_bf16_mm_skinny(s, w, K, R, x, xs, y, ys, T, add)) return;      // a decode batch (dense_bf16.cu)
     MmParams a = {NULL, w, x, y, NULL, NULL, NULL, G, NULL, K, R, T, xs, ys, 1, add, 0, 0};
     launch_gemm(s, fmt, "kc_mm", a, (T + GM_BN - 1) / GM_BN);
 }

@@ -84,11 +84,12 @@ __device__ __forceinline__ Chunk load_chunk3(const uint4* s, const uint4* c, con
     return k;
 }
 
+template <int PF = 4>      // PF = 3: the SEED4 format has no code stream (a block's code rides in its nibble word)
 __device__ __forceinline__ Chunk load_chunk(const WSlice& w, size_t chunk_index) {
     Chunk k;
     k.s = __ldg((const uint4*) w.p[0] + chunk_index);
     k.c = __ldg((const uint4*) w.p[1] + chunk_index);
-    k.cd = __ldg((const uint32_t*) w.p[3] + chunk_index);
+    k.cd = PF == 4 ? __ldg((const uint32_t*) w.p[3] + chunk_index) : 0u;
     return k;
 }
 
@@ -229,7 +230,9 @@ __device__ __forceinline__ void stage_pair_inputs(const MvParams& a, int xr, int
 // block's warps take its steps round-robin, and the next row's streams are prefetched while the current row is expanded.
 // Optionally the block first ROUTES: with logits given, warp t picks token t's top-k experts (route.cuh) and the pair
 // list is the T * top_k (token, expert) pairs; block 0 also stores ids and weights for the kernels that follow.
-template <int MODE>
+// PF: coefficients per block.  4: SEED4P4; 3: SEED4 (24 states, the nibble word; the products are half as large, which the
+// slice scale makes up).
+template <int MODE, int PF>
 __global__ void __launch_bounds__(MV_THREADS, 2) mv_pair_kernel(MvParams a, KConst kc, int lpr_log2, RouteFuse rf) {
     __shared__ StreamTab tab;
     __shared__ int32_t r_ind[256];   // the fused router's picks
@@ -274,8 +277,8 @@ __global__ void __launch_bounds__(MV_THREADS, 2) mv_pair_kernel(MvParams a, KCon
         int r = st * rpw + ro;
         Chunk ka, kb;
         if (st < s_hi && r < a.R) {
-            ka = load_chunk(wa, (size_t) r * lpr + jc);
-            if (MODE == MODE_GU) kb = load_chunk(wb, (size_t) r * lpr + jc);
+            ka = load_chunk<PF>(wa, (size_t) r * lpr + jc);
+            if (MODE == MODE_GU) kb = load_chunk<PF>(wb, (size_t) r * lpr + jc);
         }
         if (pair != p_first) __syncthreads();   // the previous pair's inputs are no longer read
         if (threadIdx.x < lpr * 4) {
@@ -283,14 +286,14 @@ __global__ void __launch_bounds__(MV_THREADS, 2) mv_pair_kernel(MvParams a, KCon
             stage_pair_inputs(a, a.xrow ? a.xrow[pair] : pair / a.xdiv, j, bp, sx, sm);
         }
         __syncthreads();   // inputs staged (and, for the block's first pair, the stream table loaded)
-        const float sca = slice_scale(wa.eb), scb = slice_scale(wb.eb);
+        const float sca = slice_scale(wa.eb + (4 - PF)), scb = slice_scale(wb.eb + (4 - PF));
         for (; st < s_hi; st += MV_WARPS, r += MV_WARPS * rpw) {
             const bool ok = r < a.R;
             const int rn = r + MV_WARPS * rpw;
             Chunk na, nb;
             if (st + MV_WARPS < s_hi && rn < a.R) {
-                na = load_chunk(wa, (size_t) rn * lpr + jc);
-                if (MODE == MODE_GU) nb = load_chunk(wb, (size_t) rn * lpr + jc);
+                na = load_chunk<PF>(wa, (size_t) rn * lpr + jc);
+                if (MODE == MODE_GU) nb = load_chunk<PF>(wb, (size_t) rn * lpr + jc);
             }
             u64 acc = 0ull, accu = 0ull;
             if (ok) {
@@ -303,17 +306,27 @@ __global__ void __launch_bounds__(MV_THREADS, 2) mv_pair_kernel(MvParams a, KCon
                     for (int cq = 0; cq < 4; ++cq) { const ulonglong2 t = sx[(bp * 4 + cq) * 32 + jc]; x2[2 * cq] = t.x; x2[2 * cq + 1] = t.y; }
 #pragma unroll
                     for (int pq = 0; pq < 2; ++pq) { const ulonglong2 t = sm[(bp * 2 + pq) * 32 + jc]; xm2[2 * pq] = t.x; xm2[2 * pq + 1] = t.y; }
-                    {
+                    if (PF == 4) {
                         u64 v[32], q[4];
                         pair_states(tab, swa[bp], v);
                         pair_coefs(cwa[bp], kc, q);
                         acc = fma2(pair_dot(v, q, x2, xm2), code_scale_pair(ka.cd, bp, kc), acc);
+                    } else {
+                        u64 v[24], q[3];
+                        pair_states3(tab, swa[bp], v);
+                        pair_coefs3(cwa[bp], kc, q);
+                        acc = fma2(pair_dot3(v, q, x2, xm2), code_scale_pair3(cwa[bp], kc), acc);
                     }
-                    if (MODE == MODE_GU) {
+                    if (MODE == MODE_GU && PF == 4) {
                         u64 v[32], q[4];
                         pair_states(tab, swb[bp], v);
                         pair_coefs(cwb[bp], kc, q);
                         accu = fma2(pair_dot(v, q, x2, xm2), code_scale_pair(kb.cd, bp, kc), accu);
+                    } else if (MODE == MODE_GU) {
+                        u64 v[24], q[3];
+                        pair_states3(tab, swb[bp], v);
+                        pair_coefs3(cwb[bp], kc, q);
+                        accu = fma2(pair_dot3(v, q, x2, xm2), code_scale_pair3(cwb[bp], kc), accu);
                     }
                 }
             }
@@ -941,7 +954,7 @@ static int g_grp_min_pairs = GRP_MIN_PAIRS;
 template <int MODE>
 static void launch_grp(cudaStream_t s, const MvParams& a, int lpr_log2, const RouteFuse& rf) {
     if (a.P <= g_grp_min_pairs || rf.logits) {
-        launch(mv_pair_kernel<MODE>, sm_count() * 2, MV_THREADS, 0, s, a, kconst(), lpr_log2, rf);
+        launch(mv_pair_kernel<MODE, 4>, sm_count() * 2, MV_THREADS, 0, s, a, kconst(), lpr_log2, rf);
         return;
     }
     static bool attr_set[16];
@@ -991,12 +1004,21 @@ static void launch_mv(cudaStream_t s, const MvParams& a, int T, const RouteFuse&
     count_launch();
 }
 
-// P = 3 (SEED4): the any-shape kernel serves every form.
+// P = 3 (SEED4): the pair kernel for rows of 64 * 2^j <= 2048 weights -- the routed experts' gathers, and a dense call as T
+// "pairs" on the one slice (token t reads input row t and writes output row t; every token expands the rows itself, so a
+// token's result cannot depend on the others) -- the any-shape kernel for everything else.
 template <int MODE>
 static void launch_mv3(cudaStream_t s, const MvParams& a, int T) {
     if (a.R <= 0 || a.P <= 0 || T <= 0) return;
     if (a.K <= 0 || a.K % 8) { set_error("seed mat-vec: K = %d is not a multiple of 8", a.K); return; }
     if (T > MV_MAXT) { set_error("seed mat-vec: %d tokens, at most %d", T, MV_MAXT); return; }
+    const int ch = a.K / 64;
+    const bool chunked = a.K % 64 == 0 && aligned16(a.x) && a.xs % 4 == 0 && (a.ws != NULL || (aligned16(a.w0.p[0]) && aligned16(a.w0.p[1])));
+    if (chunked && ch > 0 && (ch & (ch - 1)) == 0 && ch <= 32) {
+        launch(mv_pair_kernel<MODE, 3>, sm_count() * 2, MV_THREADS, 0, s, a, kconst(), log2_floor(ch), RouteFuse{});
+        count_launch();
+        return;
+    }
     launch(mv_generic_kernel<MODE, 3>, sm_count() * 2, MV_THREADS, 0, s, a, kconst(), a.sel ? 1 : T);
     count_launch();
 }

@@ -421,18 +421,19 @@ def kt_bucket(inds, n):
 
 
 def kt_mm(w, x, T, add=0, y0=None, s=0, exact=False, packed=False):
-    """Dense prompt GEMM of slice s: x [T][K] -> y [T][R]."""
+    """Dense prompt GEMM of slice s: x [T][K] -> y [T][R] (w: a SeedWeight, or a SeedWeight3 for the P = 3 format)."""
     lib = L.load()
+    fmt = L.MF_SEED4 if isinstance(w, SeedWeight3) else L.MF_SEED4P4
     lib.kc_seed_gemm_f32(int(exact))
     xd = dev(np.asarray(x, np.float32).reshape(T, w.K))
     yd = dev(np.asarray(y0, np.float32).reshape(T, w.R)) if y0 is not None else torch.zeros(T, w.R, device="cuda")
     if packed:
         xp = torch.zeros(T * w.K, dtype=torch.int16, device="cuda")
         lib.kc_pack_input_bf16(_stream(), _ptr(xd), _ptr(xp), T * w.K)
-        lib.kc_mm_packed(_stream(), L.MF_SEED4P4, w.slice(s), w.K, w.R, _ptr(xp), w.K, _ptr(yd), w.R, T, add,
+        lib.kc_mm_packed(_stream(), fmt, w.slice(s), w.K, w.R, _ptr(xp), w.K, _ptr(yd), w.R, T, add,
                          _ptr(stream_table()))
     else:
-        lib.kc_mm(_stream(), L.MF_SEED4P4, w.slice(s), w.K, w.R, _ptr(xd), w.K, _ptr(yd), w.R, T, add,
+        lib.kc_mm(_stream(), fmt, w.slice(s), w.K, w.R, _ptr(xd), w.K, _ptr(yd), w.R, T, add,
                   _ptr(stream_table()))
     _done()
     lib.kc_seed_gemm_f32(0)
@@ -442,6 +443,7 @@ def kt_mm(w, x, T, add=0, y0=None, s=0, exact=False, packed=False):
 def kt_mm_grouped(w, P, xdiv, perm, tiles, x, exact=False, mode="host"):
     """Grouped prompt GEMM over a tile table.  mode: 'host' (kc_mm_grouped), 'dev' (kc_mm_grouped_dev) or 'packed'."""
     lib = L.load()
+    fmt = L.MF_SEED4 if isinstance(w, SeedWeight3) else L.MF_SEED4P4
     lib.kc_seed_gemm_f32(int(exact))
     xd = dev(np.asarray(x, np.float32).reshape(-1, w.K))
     yd = torch.zeros(P, w.R, device="cuda")
@@ -452,17 +454,17 @@ def kt_mm_grouped(w, P, xdiv, perm, tiles, x, exact=False, mode="host"):
     td = dev(tl)
     nt = len(tiles)
     if mode == "host":
-        lib.kc_mm_grouped(_stream(), L.MF_SEED4P4, _ptr(w.table), w.K, w.R, _ptr(xd), w.K, _ptr(yd), w.R, xdiv, _ptr(pd),
+        lib.kc_mm_grouped(_stream(), fmt, _ptr(w.table), w.K, w.R, _ptr(xd), w.K, _ptr(yd), w.R, xdiv, _ptr(pd),
                           _ptr(td), nt, _ptr(stream_table()))
     else:
         ntd = dev(np.array([nt], np.int32))
         if mode == "dev":
-            lib.kc_mm_grouped_dev(_stream(), L.MF_SEED4P4, _ptr(w.table), w.K, w.R, _ptr(xd), w.K, _ptr(yd), w.R, xdiv,
+            lib.kc_mm_grouped_dev(_stream(), fmt, _ptr(w.table), w.K, w.R, _ptr(xd), w.K, _ptr(yd), w.R, xdiv,
                                   _ptr(pd), _ptr(td), _ptr(ntd), nt + 3, _ptr(stream_table()))
         else:
             xp = torch.zeros(xd.numel(), dtype=torch.int16, device="cuda")
             lib.kc_pack_input_bf16(_stream(), _ptr(xd), _ptr(xp), xd.numel())
-            lib.kc_mm_grouped_packed(_stream(), L.MF_SEED4P4, _ptr(w.table), w.K, w.R, _ptr(xp), w.K, _ptr(yd), w.R,
+            lib.kc_mm_grouped_packed(_stream(), fmt, _ptr(w.table), w.K, w.R, _ptr(xp), w.K, _ptr(yd), w.R,
                                      xdiv, _ptr(pd), _ptr(td), _ptr(ntd), nt + 3, _ptr(stream_table()))
     _done()
     lib.kc_seed_gemm_f32(0)

@@ -219,7 +219,8 @@ def test_small_kernels_alone(oracle):
     assert np.array_equal(out.cpu().numpy(), bf_val(table[ids]))
 
 
-@pytest.mark.parametrize("R,K,T", [(40, 256, 1), (40, 256, 5), (300, 2048, 8), (40, 128, 12), (300, 512, 40), (136, 256, 130)])
+@pytest.mark.parametrize("R,K,T", [(40, 256, 1), (40, 256, 5), (300, 2048, 8), (40, 128, 12), (300, 512, 40), (136, 256, 130), (2048, 2048, 32),
+                                   (513, 2048, 32), (24, 256, 9), (40, 512, 64), (16, 256, 17)])
 def test_stored_bf16_weights(oracle, R, K, T):
     """kc_mv (T <= 8) and kc_mm (more rows) with MF_BF16 weights [R][K]: y = bf16(W . x) with f32 sums, and the residual form."""
     import torch
@@ -245,6 +246,13 @@ def test_stored_bf16_weights(oracle, R, K, T):
         slack = 64 * 1.2e-7 * mag + (np.abs(acc) / 128 if add else 0)
         assert (np.abs(got.astype(np.float64) - want) <= np.abs(want) / 128.0 + 1e-30 + slack).all()
     assert lib.nsl_mm_status() == 0
+    if 8 < T <= 64 and K % 256 == 0:      # the decode-batch GEMM: a row's result does not depend on the rows it shares the call with
+        y9 = kernels.dev(np.zeros((9, R), np.float32))
+        lib.kc_mm(None, 0, w, K, R, xd.data_ptr(), K, y9.data_ptr(), R, 9, 0, None)
+        yT = kernels.dev(np.zeros((T, R), np.float32))
+        lib.kc_mm(None, 0, w, K, R, xd.data_ptr(), K, yT.data_ptr(), R, T, 0, None)
+        torch.cuda.synchronize()
+        assert torch.equal(y9[:9], yT[:9])
 
 
 def test_decoder_step_of_more_rows_than_a_mat_vec_takes(oracle):
