@@ -620,7 +620,10 @@ def measure_attn(K, W):
     import torch
     from nanoseedlm_b200 import lib as L
     lib = L.load()
-    NH, NKV, CTX, NSEQ, NS, NL = 16, 2, 4096, 32, 32, 3      # 32 splits: the reference host's choice for 32 rows of 4096 keys
+    NH, NKV, CTX, NSEQ, NL = 16, 2, 4096, 32, 3
+    NS = int(os.environ.get("NSL_ATTN_SPLITS", "32"))      # 32 splits: the reference host's choice for 32 rows of 4096 keys
+    invariant = os.environ.get("NSL_ATTN_INVARIANT", "0") == "1"      # time the form with one block per caller split instead
+    lib.nsl_attn_batch_invariant(int(invariant))
     gen = torch.Generator(device="cuda").manual_seed(5)
     caches = [(torch.randn(NSEQ * CTX, NKV, 128, generator=gen, device="cuda").to(torch.bfloat16),
                torch.randn(NSEQ * CTX, NKV, 128, generator=gen, device="cuda").to(torch.bfloat16)) for _ in range(NL)]
@@ -653,8 +656,10 @@ def measure_attn(K, W):
         e1.record(stream)
         e1.synchronize()
         ms = e0.elapsed_time(e1) / K
+    lib.nsl_attn_batch_invariant(0)
     L.check()
-    return {"ms_per_step": ms, "tokens": NSEQ, "bytes": 2 * NSEQ * CTX * NKV * 128 * 2 + 3 * NSEQ * NH * 128 * 4}
+    return {"ms_per_step": ms, "tokens": NSEQ, "bytes": 2 * NSEQ * CTX * NKV * 128 * 2 + 3 * NSEQ * NH * 128 * 4, "splits": NS,
+            "form": "one block per caller split (batch-invariant)" if invariant else "balanced blocks (default)"}
 
 
 def measure_upload(K, W):
@@ -1218,7 +1223,8 @@ def secondary(name, K, W, peaks, peak_kind, sms, args, sm_mhz=None):
                              "frac": gbs / peaks["hbm_gbs"], "peak_kind": peak_kind, "us_per_launch": r["mv_us"], "bytes_per_launch": r["bytes"]}}
     r = measure_attn(min(K, 500), W)
     gbs = r["bytes"] / (r["ms_per_step"] * 1e-3) / 1e9
-    return {"workload": "decode attention, 16 query / 2 KV heads of 128, BF16 cache of 4096 positions x 32 sequences (134 MB per layer), 32 splits; 3 layers rotated",
+    return {"workload": f"decode attention, 16 query / 2 KV heads of 128, BF16 cache of 4096 positions x 32 sequences (134 MB per layer), {r['splits']} splits, "
+                        f"{r['form']}; 3 layers rotated",
             "ms_per_step": r["ms_per_step"], "value": r["tokens"] / (r["ms_per_step"] * 1e-3), "unit": "tok/s",
             "roofline": {"bound": "hbm", "kernel": "attn_flat_mma_kernel + attn_reduce_kernel (kc_attn)", "achieved": gbs, "peak": peaks["hbm_gbs"],
                          "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"], "peak_kind": peak_kind, "bytes_per_step": r["bytes"]}}

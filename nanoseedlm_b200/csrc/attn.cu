@@ -353,8 +353,8 @@ __global__ void __launch_bounds__(32 * ATT_MMA_WARPS) attn_split_mma_kernel(Attn
     extern __shared__ __align__(16) unsigned char att_smem[];      // the warps' rings, later their states
     const int split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
     const int group = a.n_head / a.n_kv;
-    grid_dependents_go();
-    grid_dependency_wait();
+    grid_dependency_wait();      // the rows' positions and q may come from the previous kernel in the stream
+    grid_dependents_go();        // only now: the reduction reads the rows' positions as soon as it starts
     const int pos = ri[t].pos, kv0 = ri[t].kv0;
     const int nsr = a.chunk > 0 ? min(a.n_splits, (pos + a.chunk) / a.chunk) : 1;
     const int chunk = (pos + nsr) / nsr;
@@ -426,8 +426,8 @@ attn_flat_mma_kernel(AttnArgs a, const float* __restrict__ q, KvView kv, const R
     extern __shared__ __align__(16) unsigned char att_smem[];
     __shared__ int pre[ATT_MAX_ROWS + 1];
     const int group = a.n_head / a.n_kv;
-    grid_dependents_go();
-    grid_dependency_wait();
+    grid_dependency_wait();      // the rows' positions and q may come from the previous kernel in the stream
+    grid_dependents_go();        // only now: the reduction reads the rows' positions as soon as it starts
     const AttnPlan pl = attn_plan<ATT_MMA_WARPS>(ri, T, a.n_kv, a.n_splits, (int) gridDim.x, pre);
     int x = (int) blockIdx.x * pl.per;
     const int xe = min(pl.total, x + pl.per);
@@ -463,13 +463,16 @@ __global__ void __launch_bounds__(ATT_HD) attn_reduce_kernel(AttnArgs a, const f
     __shared__ int pre[ATT_MAX_ROWS + 1];
     const int h = blockIdx.x, t = blockIdx.y, d = threadIdx.x;
     grid_dependents_go();
-    grid_dependency_wait();      // the rows' positions may come from the kernel before kc_attn: nothing is read earlier
+    // This kernel is always launched behind the first pass, whose blocks let their dependents go only AFTER their own wait
+    // for the kernel before kc_attn: by the time a block runs here the rows' positions are final, and the plan can be made
+    // while the first pass is still running.  The partials are read after the wait below.
     int n = a.n_splits;
     if (n_blocks > 0) {
         const AttnPlan pl = attn_plan<ATT_HD / 32>(ri, T, a.n_kv, a.n_splits, n_blocks, pre);
         const int u = pre[t + 1] - pre[t], first = a.n_kv * pre[t] + (h / (a.n_head / a.n_kv)) * u;
         n = (first + u - 1) / pl.per - first / pl.per + 1;
     }
+    grid_dependency_wait();
     const float* pp = part + ((size_t) t * a.n_head + h) * a.n_splits * (ATT_HD + 2);
     __shared__ float pm[ATT_HD], pl[ATT_HD], pc[ATT_HD];      // the partials' (m, l): one load each, side by side; their weights
     float m = -INFINITY, l = 0.0f, acc = 0.0f;
