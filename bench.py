@@ -418,8 +418,9 @@ def measure_layer(c, M, K, W, sample_clocks=True, with_e2e=True, dependent_launc
 def measure_ref_gpu(c, M, K, W, mine_out=None):
     """The reference's OWN CUDA kernels (engine/kernels_moe.cu + engine/kernels_qwen4.cu compiled unmodified for sm_100a into
     oracle/_ref/libnslm_ref_gpu.so) on the same layers, inputs and rotation as measure_layer: per step kq4_route_ld, kc_mv_gu,
-    kc_mv_sel and kq4_moe_combine (engine/qwen4_cuda.c:1033-1078), captured as a CUDA graph and timed with CUDA events.  The
-    checker's use of the reference: a reported baseline and a parity check of one step, never the product path."""
+    kc_mv_sel and kq4_moe_combine (engine/qwen4_cuda.c:1033-1078; for M > 8 prompt rows its kc_bucket + kc_mm_grouped_dev x 3 +
+    kc_swiglu path, :1058-1064), captured as a CUDA graph and timed with CUDA events.  The checker's use of the reference: a
+    reported baseline and a parity check of one step, never the product path."""
     from oracle import ref_gpu
     ref = ref_gpu.lib()
     if ref is None:
@@ -438,16 +439,32 @@ def measure_ref_gpu(c, M, K, W, mine_out=None):
     Dx = torch.zeros(P, D, device="cuda")
     sh, sg = torch.zeros(M, D, device="cuda"), torch.zeros(M, device="cuda")      # no shared expert in config 1: a zero term
     out = torch.zeros(M, D, device="cuda")
+    if M > 8:
+        U = torch.zeros(P, FF, device="cuda")
+        perm = torch.zeros(P, dtype=torch.int32, device="cuda")
+        tiles = torch.zeros((P // 128 + E + 1) * 4, dtype=torch.int32, device="cuda")
+        work = torch.zeros(2 * E + 3, dtype=torch.int32, device="cuda")
+        mt = P // 128 + E
 
     def enqueue(step):
         lay, b, s = layers[step % NL], step % NB, stream.cuda_stream
         ref.kq4_route_ld(s, cfgp, dl[b].data_ptr(), E, ind.data_ptr(), wt.data_ptr(), M)
+        if M > 8:
+            ref.kc_bucket(s, ind.data_ptr(), P, E, perm.data_ptr(), tiles.data_ptr(), work.data_ptr())
+            for tab, dst in ((lay.gate, A), (lay.up, U)):
+                ref.kc_mm_grouped_dev(s, L.MF_SEED4P4, tab.table.data_ptr(), D, FF, dx[b].data_ptr(), D, dst.data_ptr(), FF, TOPK, perm.data_ptr(),
+                                      tiles.data_ptr(), work.data_ptr(), mt, G.data_ptr())
+            ref.kc_swiglu(s, A.data_ptr(), U.data_ptr(), A.data_ptr(), P * FF)
+            ref.kc_mm_grouped_dev(s, L.MF_SEED4P4, lay.down.table.data_ptr(), FF, D, A.data_ptr(), FF, Dx.data_ptr(), D, 1, perm.data_ptr(),
+                                  tiles.data_ptr(), work.data_ptr(), mt, G.data_ptr())
+            ref.kq4_moe_combine(s, D, TOPK, Dx.data_ptr(), wt.data_ptr(), sh.data_ptr(), sg.data_ptr(), 0, out.data_ptr(), M)
+            return
         ref.kc_mv_gu(s, L.MF_SEED4P4, lay.gate.table.data_ptr(), lay.up.table.data_ptr(), D, FF, dx[b].data_ptr(), D, A.data_ptr(), FF,
                      ind.data_ptr(), P, TOPK, G.data_ptr())
         ref.kc_mv_sel(s, L.MF_SEED4P4, lay.down.table.data_ptr(), FF, D, A.data_ptr(), FF, Dx.data_ptr(), D, ind.data_ptr(), P, 1, G.data_ptr())
         ref.kq4_moe_combine(s, D, TOPK, Dx.data_ptr(), wt.data_ptr(), sh.data_ptr(), sg.data_ptr(), 0, out.data_ptr(), M)
 
-    res = {"kernels": "the reference's engine/kernels_moe.cu + engine/kernels_qwen4.cu, unmodified, nvcc -O3 sm_100a", "launches_per_step": 4}
+    res = {"kernels": "the reference's engine/kernels_moe.cu + engine/kernels_qwen4.cu, unmodified, nvcc -O3 sm_100a", "launches_per_step": 4 if M <= 8 else 8}
     with torch.cuda.stream(stream):
         enqueue(0)      # step 0 = the step measure_layer hands to the parity checks (layer 0, batch 0)
         stream.synchronize()
@@ -457,14 +474,14 @@ def measure_ref_gpu(c, M, K, W, mine_out=None):
         for i in range(W):
             enqueue(i)
         stream.synchronize()
-        chunk = min(K, 100)
+        chunk = min(K, 100 if M <= 8 else 10)
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
             for i in range(chunk):
                 enqueue(W + i)
         graph.replay()
         stream.synchronize()
-        reps = max(1, min(K, 400) // chunk)
+        reps = max(1, min(K, 400 if M <= 8 else 40) // chunk)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         for _ in range(reps):
@@ -563,11 +580,12 @@ def measure_cfg0(K, W):
 LM_V, LM_D = 151936, 2048   # the LM head of the reference's Qwen-class model (affine int4, groups of 64)
 
 
-def measure_lmhead(T, K, W):
-    """The dense affine-int4 LM head (kc_mv with MF_Q4) + greedy arg-max, an HBM-bound kernel."""
+def measure_lmhead(T, K, W, lib=None):
+    """The dense affine-int4 LM head (kc_mv with MF_Q4) + greedy arg-max, an HBM-bound kernel.  lib: the library whose kc_mv /
+    kc_argmax are timed (default: this one; the reference's kernels for the `ref_gpu` leg)."""
     import torch
     from nanoseedlm_b200 import lib as L
-    lib = L.load()
+    lib = lib or L.load()
     NM = 4
     gen = torch.Generator(device="cuda").manual_seed(77)
     mats = []
@@ -707,7 +725,8 @@ C4 = dict(n_layer=48, d=D, n_head=16, n_kv=2, n_exp=512, top_k=10, ff_exp=FF, ff
 C4_BATCH = 32
 
 
-def c4_config(world, layers):
+def c4_config(world, layers, batch=C4_BATCH):
+    C4_BATCH = batch      # noqa: N806 (the profiling option's batch, printed as it ran)
     return {"workload": f"BASELINE config 4: random-init synthetic MoE decoder, {layers} layers, hidden {D}, GQA 16 query / 2 KV heads of 128, BF16 KV "
                         f"cache with 4096 prefilled positions, 512 seed-encoded routed experts (top-10) + 1 shared expert per layer, vocab 151936 "
                         f"with an affine int4 LM head, decode at batch {C4_BATCH}, experts sharded over {world} GPU(s)",
@@ -724,7 +743,8 @@ def measure_cfg4(args, K, W):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     c = dict(C4, n_layer=args.c4_layers)
-    T = C4_BATCH // world
+    batch = args.c4_batch if args.c4_batch > 0 and world == 1 else C4_BATCH
+    T = batch // world
     e_loc = c["n_exp"] // world
     cfg = decoder.make_cfg(max_rows=T, exp_lo=rank * e_loc, exp_hi=(rank + 1) * e_loc, dense_bf16=int(not args.c4_dense_seed), **c)
     win = ep.P2PWindow.create(world, rank, T, D, c["top_k"]) if world > 1 else None
@@ -809,12 +829,12 @@ def measure_cfg4(args, K, W):
         raise SystemExit(f"config 4: a wait of the expert-parallel exchange ran out (status {status}); the timing is void")
     if rank != 0:
         return None
-    return {"value": C4_BATCH / (ms * 1e-3), "unit": "tok/s", "ms_per_step": ms, "gpu_launches": int(launches) * K, "cuda_graph": captured,
-            "clocks": clocks.summary(), "config": c4_config(world, c["n_layer"]),
+    return {"value": batch / (ms * 1e-3), "unit": "tok/s", "ms_per_step": ms, "gpu_launches": int(launches) * K, "cuda_graph": captured,
+            "clocks": clocks.summary(), "config": c4_config(world, c["n_layer"], batch),
             "dense_matrices": "regenerated from their seeds in every call" if args.c4_dense_seed else
                               "expanded once at load to BF16 in HBM (27 MB a layer), the values the tensor-core path rounds seed weights to; "
                               "the routed experts are regenerated from their seeds in every call",
-            "e2e": {"value": C4_BATCH / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 4 * T, "d2h_bytes_per_step": 4 * T, "ms_per_step": e2e_s * 1e3,
+            "e2e": {"value": batch / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 4 * T, "d2h_bytes_per_step": 4 * T, "ms_per_step": e2e_s * 1e3,
                     "steps_in_flight": 1},
             "next_tokens_in_vocab": bool(((toks >= 0) & (toks < c["vocab"])).all()),
             "packed_bytes_per_gpu": c["n_layer"] * e_loc * 3 * BYTES_PER_MATRIX}
@@ -1006,6 +1026,8 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="N = 1: the headline only, without the `workloads` and `ep_base` objects")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--c4-dense-seed", action="store_true", help="config 4: regenerate the dense matrices from their seeds in every call too")
+    ap.add_argument("--c4-batch", type=int, default=0, help="config 4: sequences per step (32 = the configuration; fewer only for profiling "
+                                                             "one rank's dense and attention sizes on one GPU)")
     ap.add_argument("--c4-layers", type=int, default=48, help="config 4: decoder layers (48 = the configuration; fewer only for profiling)")
     ap.add_argument("--no-dependent-launch", action="store_true",
                     help="config 1: ordinary launches instead of programmatic dependent launches (for comparison)")
@@ -1098,11 +1120,18 @@ def main():
     if M <= 8 and not args.no_extra:      # the reference's own CUDA kernels on the same layers and inputs (a baseline, like the CPU's)
         line["ref_gpu"] = measure_ref_gpu(c, M, min(K, 400), W, mine_out=step0[2])
         if extra and "ms_per_step" in line["ref_gpu"]:
-            line["ref_gpu"]["m1"] = {k_: v for k_, v in measure_ref_gpu(c, 1, min(K, 400), W).items() if k_ in ("ms_per_step", "value", "unit")}
+            keep = ("ms_per_step", "value", "unit", "launches_per_step")
+            line["ref_gpu"]["m1"] = {k_: v for k_, v in measure_ref_gpu(c, 1, min(K, 400), W).items() if k_ in keep}
+            line["ref_gpu"]["cfg2"] = {k_: v for k_, v in measure_ref_gpu(c, 512, 40, W).items() if k_ in keep}
     if not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline_cfg1(os.cpu_count() or 1, M, layer0 if M <= 8 else None, step0[0], step0[1], step0[2] if M <= 8 else None)
     del c, r
     torch.cuda.empty_cache()
+    if extra and "ms_per_step" in line.get("ref_gpu", {}):      # the reference's kc_mv (MF_Q4) + kc_argmax on the LM head
+        from oracle import ref_gpu
+        rl = measure_lmhead(8, 100, W, lib=ref_gpu.lib())
+        line["ref_gpu"]["lmhead"] = {"ms_per_step": rl["ms_per_step"], "value": rl["tokens"] / (rl["ms_per_step"] * 1e-3), "unit": "tok/s"}
+        torch.cuda.empty_cache()
     if extra:
         for name in ("cfg0", "lmhead", "attn", "upload", "p3"):
             line["workloads"][name] = secondary(name, min(K, 1000), W, peaks, peak_kind, sms, args, sm_mhz=clocks.get("sm_mhz"))

@@ -1025,6 +1025,7 @@ static void launch_mv3(cudaStream_t s, const MvParams& a, int T) {
 
 bool launch_q4_mv(cudaStream_t s, const WSlice& w, int K, int R, const float* x, int xs, float* y, int ys, int T, int add);
 void launch_bf16_mv(cudaStream_t s, const WSlice& w, int K, int R, const float* x, int xs, float* y, int ys, int T, int add);
+bool launch_bf16_mm_skinny(cudaStream_t s, const WSlice& w, int K, int R, const float* x, int xs, float* y, int ys, int T, int add);
 
 static bool seed_fmt(int fmt, const char* who) {      // the mat-vec entry points: P = 4 and P = 3 seeds
     if (fmt == MF_SEED4P4 || fmt == MF_SEED4) return true;
@@ -1041,7 +1042,10 @@ extern "C" {
 void kc_mv(cudaStream_t s, int fmt, WSlice w, int K, int R, const float* x, int xs, float* y, int ys, int T, int add,
            const uint32_t* G) {
     if (fmt == MF_Q4) { launch_q4_mv(s, w, K, R, x, xs, y, ys, T, add); return; }   // the LM head's affine int4 (q4_head.cu)
-    if (fmt == MF_BF16) { launch_bf16_mv(s, w, K, R, x, xs, y, ys, T, add); return; }   // stored BF16 weights (dense_bf16.cu)
+    if (fmt == MF_BF16) {      // stored BF16 weights (dense_bf16.cu): the tensor-core kernel where its shape rules allow, else a warp per row
+        if (!launch_bf16_mm_skinny(s, w, K, R, x, xs, y, ys, T, add)) launch_bf16_mv(s, w, K, R, x, xs, y, ys, T, add);
+        return;
+    }
     if (!seed_fmt(fmt, "kc_mv")) return;
     MvParams a = {NULL, NULL, w, NULL, x, y, G, K, R, T, 1, xs, ys, add, 0, NULL, NULL, 0};
     if (fmt == MF_SEED4) launch_mv3<MODE_ROUND>(s, a, T);

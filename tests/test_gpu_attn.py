@@ -1,9 +1,13 @@
 """Decode attention over a BF16 or 8-bit KV cache (kc_attn) against a double-precision reference.
 
 The first case is the reference's own kernel test (tests/test_mova_kernels.c:660-715): GQA 8/2, three rows at
-positions 300, 299, 37 in sequence slots based at cache rows 0, 310, 600, five splits; bound |o - ref| <= |ref| / 128 + 2e-6
-(met by at least 999 outputs in 1000, twice the bound by all: see run_variant).  Every case also runs on the 8-bit cache
-built from the same values as the reference's test builds it (tests/test_mova_kernels.c:584-604, 688)."""
+positions 300, 299, 37 in sequence slots based at cache rows 0, 310, 600, five splits; bound |o - ref| <= |ref| / 128 + 2e-6,
+met by EVERY output as in the reference's test.  The same strict bound holds for every other case here when there is no
+output gate.  With the gate the attention value is rounded to bf16 twice (before and after the gate, as the reference
+does): where f32 summation noise flips the first rounding the second can land one unit further, which happens to 1-2
+outputs in 10,000 of the larger cases (up to 1.33 x the bound measured); those cases allow one output in a thousand beyond
+the bound and none beyond twice it.  Every case also runs on the 8-bit cache built from the same values as the
+reference's test builds it (tests/test_mova_kernels.c:584-604, 688)."""
 import numpy as np
 import pytest
 
@@ -12,13 +16,15 @@ from oracle import binding as B
 pytestmark = pytest.mark.gpu
 
 
-def run_case(nh, nkv, NP, pos, kv0, ns, chunk, gate=True, nv=None, seed=21):
+def run_case(nh, nkv, NP, pos, kv0, ns, chunk, gate=True, nv=None, seed=21, strict=False):
     for invariant in (0, 1):      # the step's keys dealt evenly to the blocks (default); a block per caller split
-        run_variant(invariant, nh, nkv, NP, pos, kv0, ns, chunk, gate, nv, seed)
-        run_variant(invariant, nh, nkv, NP, pos, kv0, ns, chunk, gate, nv, seed, q8=True)      # the 8-bit cache
+        run_variant(invariant, nh, nkv, NP, pos, kv0, ns, chunk, gate, nv, seed, strict=strict)
+        run_variant(invariant, nh, nkv, NP, pos, kv0, ns, chunk, gate, nv, seed, q8=True, strict=strict)      # the 8-bit cache
+        if gate:                  # the same without the output gate: one rounding, the strict bound
+            run_variant(invariant, nh, nkv, NP, pos, kv0, ns, chunk, False, nv, seed)
 
 
-def run_variant(variant, nh, nkv, NP, pos, kv0, ns, chunk, gate, nv, seed, q8=False):
+def run_variant(variant, nh, nkv, NP, pos, kv0, ns, chunk, gate, nv, seed, q8=False, strict=False):
     from nanoseedlm_b200 import kernels, lib as L
     L.load().nsl_attn_batch_invariant(variant)
     rng = np.random.default_rng(seed)
@@ -37,16 +43,17 @@ def run_variant(variant, nh, nkv, NP, pos, kv0, ns, chunk, gate, nv, seed, q8=Fa
         o = kernels.kt_attn(a, q, Kc, Vc, pos, kv0, g if gate else None, nv)
     ref, _ = B.attn_decode(q, Kc, Vc, pos, kv0, nkv, scale, g if gate else None)
     L.load().nsl_attn_batch_invariant(0)      # back to the default
-    # the reference's bound; an output whose attention value sits on a bf16 rounding boundary can land one unit further
-    # after the gate's second rounding: at most one element in a thousand, and never beyond twice the bound
-    bound = np.abs(ref) / 128 + 2e-6
+    bound = np.abs(ref) / 128 + 2e-6      # the reference's bound
     bad = np.abs(o - ref) > bound
-    assert bad.mean() <= 1e-3, (variant, int(bad.sum()), float(np.max(np.abs(o - ref))))
-    assert (np.abs(o - ref) <= 2 * bound).all(), (variant, float(np.max(np.abs(o - ref) / bound)))
+    if strict or not gate:
+        assert not bad.any(), (variant, q8, int(bad.sum()), float(np.max(np.abs(o - ref) / bound)))
+    else:      # an output whose attention value sits on a bf16 rounding boundary can land one unit further after the gate's second rounding
+        assert bad.mean() <= 1e-3, (variant, int(bad.sum()), float(np.max(np.abs(o - ref))))
+        assert (np.abs(o - ref) <= 2 * bound).all(), (variant, float(np.max(np.abs(o - ref) / bound)))
 
 
 def test_reference_case_gqa_8_over_2():
-    run_case(8, 2, 640, [300, 299, 37], [0, 310, 600], 5, (301 + 4) // 5)
+    run_case(8, 2, 640, [300, 299, 37], [0, 310, 600], 5, (301 + 4) // 5, strict=True)
 
 
 @pytest.mark.parametrize("nh,nkv", [(16, 2), (4, 4), (32, 2), (3, 1)])

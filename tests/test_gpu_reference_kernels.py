@@ -162,4 +162,4 @@ def test_reference_kernels_pass_this_suites_checks(oracle, golden):
             test_gpu_mv.test_mv_dense_tokens_add_and_batch_invariance(oracle, K)
         test_gpu_cache.test_cache_admit_copy_and_identical_results(oracle)
         test_gpu_gemm.test_mm_grouped_tile_table(oracle, False, "dev")
-        test_gpu_attn.run_variant(0, 8, 2, 640, [300, 299, 37], [0, 310, 600], 5, (301 + 4) // 5, True, None, 21)
+        test_gpu_attn.run_variant(0, 8, 2, 640, [300, 299, 37], [0, 310, 600], 5, (301 + 4) // 5, True, None, 21, strict=True)
