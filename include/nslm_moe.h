@@ -32,6 +32,9 @@ void nsl_moe_set_rounding(NslMoe* m, int bf16_points);
 /* Programmatic dependent launch of the decode path's kernels (default on): each kernel's blocks become resident while
  * the previous kernel drains and wait for its completion before they touch its results.  0 = ordinary launches. */
 void nsl_moe_set_dependent_launch(NslMoe* m, int on);
+/* 1 (default): in the host and pinned forms the combine kernel stores the result rows straight into the pinned output buffer
+ * (no device-to-host copy is enqueued).  0: the result goes to device memory and a copy brings it to the host. */
+void nsl_moe_set_direct_output(NslMoe* m, int on);
 /* x [T][d], logits [T][n_exp] and out [T][d] in device memory; launches only. */
 int nsl_moe_forward_dev(NslMoe* m, cudaStream_t s, const float* x, const float* logits, int T, float* out);
 /* The same with host buffers: staged through pinned memory, copied both ways on the layer's stream, synchronised.

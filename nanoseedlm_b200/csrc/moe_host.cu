@@ -24,6 +24,7 @@ struct NslMoe {
     int grouped_min_tokens;       // rows from which the grouped prompt path is taken (MV_MAXT + 1)
     int raw;                      // 1: no bf16 rounding points on the mat-vec path
     int pdl;                      // 1 (default): the decode path's kernels are programmatic dependent launches
+    int direct_out;               // 1 (default): the pinned forms' combine kernel stores the result straight into pinned host memory
 };
 
 static void* dalloc(size_t n) {
@@ -46,8 +47,8 @@ NslMoe* nsl_moe_create(int d, int ff, int n_exp, int top_k, int max_tokens, cons
     m->grouped_min_tokens = MV_MAXT + 1;
     m->pdl = 1;
     const size_t T = (size_t) max_tokens, P = T * top_k;
-    m->x = (float*) dalloc(T * d * 4);
-    m->logits = (float*) dalloc(T * n_exp * 4);
+    m->x = (float*) dalloc(T * d * 4 + T * n_exp * 4);      // inputs in one block (rows, then logits): one copy brings both
+    m->logits = m->x ? m->x + T * d : NULL;
     m->wt = (float*) dalloc(P * 4);
     m->ind = (int32_t*) dalloc(P * 4);
     m->A = (float*) dalloc(P * ff * 4);
@@ -59,8 +60,9 @@ NslMoe* nsl_moe_create(int d, int ff, int n_exp, int top_k, int max_tokens, cons
     m->perm = (int32_t*) dalloc(P * 4);
     m->tiles = (MmTile*) dalloc((P / MMT_BN + n_exp + 1) * sizeof(MmTile));
     m->ntiles = (int32_t*) dalloc((2 * (size_t) n_exp + 3) * 4);
-    cudaHostAlloc((void**) &m->hx, T * d * 4, cudaHostAllocDefault);
-    cudaHostAlloc((void**) &m->hlogits, T * n_exp * 4, cudaHostAllocDefault);
+    cudaHostAlloc((void**) &m->hx, T * d * 4 + T * n_exp * 4, cudaHostAllocDefault);      // the same layout in pinned memory
+    m->hlogits = m->hx ? m->hx + T * d : NULL;
+    m->direct_out = 1;
     cudaHostAlloc((void**) &m->hout, T * d * 4, cudaHostAllocDefault);
     cudaHostAlloc((void**) &m->hind, P * 4, cudaHostAllocDefault);
     cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking);
@@ -77,12 +79,13 @@ void nsl_moe_set_layer(NslMoe* m, const WSlice* wg, const WSlice* wu, const WSli
 void nsl_moe_set_grouped_min_tokens(NslMoe* m, int t) { m->grouped_min_tokens = t; }
 void nsl_moe_set_rounding(NslMoe* m, int bf16_points) { m->raw = !bf16_points; }
 void nsl_moe_set_dependent_launch(NslMoe* m, int on) { m->pdl = on != 0; }
+void nsl_moe_set_direct_output(NslMoe* m, int on) { m->direct_out = on != 0; }
 
 void nsl_moe_destroy(NslMoe* m) {
     if (!m) return;
-    void* dv[] = {m->x, m->logits, m->wt, m->ind, m->A, m->Dx, m->out, m->Gb, m->Ub, m->perm, m->tiles, m->ntiles};
+    void* dv[] = {m->x, m->wt, m->ind, m->A, m->Dx, m->out, m->Gb, m->Ub, m->perm, m->tiles, m->ntiles};
     for (void* p : dv) if (p) cudaFree(p);
-    void* hv[] = {m->hx, m->hlogits, m->hout, m->hind};
+    void* hv[] = {m->hx, m->hout, m->hind};
     for (void* p : hv) if (p) cudaFreeHost(p);
     if (m->stream) cudaStreamDestroy(m->stream);
     free(m);
@@ -121,6 +124,22 @@ int nsl_moe_forward_dev(NslMoe* m, cudaStream_t s, const float* x, const float* 
     return 0;
 }
 
+// The pinned forms' device work: the inputs' copy, the layer, the result to pinned memory.  A full batch's rows and logits
+// are adjacent in both staging blocks and travel as ONE copy; the combine kernel stores its rows straight into the pinned
+// output (posted writes over PCIe: no device-to-host copy to launch and wait for) unless direct output is switched off.
+static int submit_pinned(NslMoe* m, int T) {
+    if (T < 1 || T > m->max_tokens) { nsl::set_error("nsl_moe_forward: %d rows, at most %d", T, m->max_tokens); return -1; }
+    const size_t xb = (size_t) T * m->d * 4, lb = (size_t) T * m->n_exp * 4;
+    if (T == m->max_tokens) cudaMemcpyAsync(m->x, m->hx, xb + lb, cudaMemcpyHostToDevice, m->stream);
+    else {
+        cudaMemcpyAsync(m->x, m->hx, xb, cudaMemcpyHostToDevice, m->stream);
+        cudaMemcpyAsync(m->logits, m->hlogits, lb, cudaMemcpyHostToDevice, m->stream);
+    }
+    if (m->direct_out && xb <= 256 * 1024) return nsl_moe_forward_dev(m, m->stream, m->x, m->logits, T, m->hout);      // decode-sized results
+    if (nsl_moe_forward_dev(m, m->stream, m->x, m->logits, T, m->out)) return -1;
+    return cudaMemcpyAsync(m->hout, m->out, xb, cudaMemcpyDeviceToHost, m->stream) == cudaSuccess ? 0 : -1;
+}
+
 // Host form: x and logits in HOST memory, out to host memory.  Copies go through the layer's pinned staging buffers on
 // its own stream; returns after the result is on the host (-1 on an argument or CUDA error).
 int nsl_moe_forward_host(NslMoe* m, const float* x, const float* logits, int T, float* out, int32_t* ind_out) {
@@ -128,10 +147,7 @@ int nsl_moe_forward_host(NslMoe* m, const float* x, const float* logits, int T, 
     const size_t xb = (size_t) T * m->d * 4, lb = (size_t) T * m->n_exp * 4;
     memcpy(m->hx, x, xb);
     memcpy(m->hlogits, logits, lb);
-    cudaMemcpyAsync(m->x, m->hx, xb, cudaMemcpyHostToDevice, m->stream);
-    cudaMemcpyAsync(m->logits, m->hlogits, lb, cudaMemcpyHostToDevice, m->stream);
-    if (nsl_moe_forward_dev(m, m->stream, m->x, m->logits, T, m->out)) return -1;
-    cudaMemcpyAsync(m->hout, m->out, xb, cudaMemcpyDeviceToHost, m->stream);
+    if (submit_pinned(m, T)) return -1;
     if (ind_out) cudaMemcpyAsync(m->hind, m->ind, (size_t) T * m->top_k * 4, cudaMemcpyDeviceToHost, m->stream);
     if (cudaStreamSynchronize(m->stream) != cudaSuccess || cudaGetLastError() != cudaSuccess) {
         nsl::set_error("nsl_moe_forward_host: CUDA error");
@@ -153,14 +169,7 @@ cudaStream_t nsl_moe_stream(NslMoe* m) { return m->stream; }
 // The same with inputs already in the pinned buffers and the result left there: H2D, the layer, D2H, one sync.
 // nsl_moe_submit_pinned enqueues without waiting and nsl_moe_wait waits, so that a caller with two handles keeps two
 // steps in flight (one's copies and launch latency under the other's kernels).
-int nsl_moe_submit_pinned(NslMoe* m, int T) {
-    if (T < 1 || T > m->max_tokens) { nsl::set_error("nsl_moe_forward: %d rows, at most %d", T, m->max_tokens); return -1; }
-    const size_t xb = (size_t) T * m->d * 4, lb = (size_t) T * m->n_exp * 4;
-    cudaMemcpyAsync(m->x, m->hx, xb, cudaMemcpyHostToDevice, m->stream);
-    cudaMemcpyAsync(m->logits, m->hlogits, lb, cudaMemcpyHostToDevice, m->stream);
-    if (nsl_moe_forward_dev(m, m->stream, m->x, m->logits, T, m->out)) return -1;
-    return cudaMemcpyAsync(m->hout, m->out, xb, cudaMemcpyDeviceToHost, m->stream) == cudaSuccess ? 0 : -1;
-}
+int nsl_moe_submit_pinned(NslMoe* m, int T) { return submit_pinned(m, T); }
 
 int nsl_moe_wait(NslMoe* m) { return cudaStreamSynchronize(m->stream) == cudaSuccess ? 0 : -1; }
 

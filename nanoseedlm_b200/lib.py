@@ -133,6 +133,7 @@ PROTOTYPES = {
     "nsl_moe_stream": (_vp, [_vp]),
     "nsl_moe_set_rounding": (None, [_vp, _i]),
     "nsl_moe_set_dependent_launch": (None, [_vp, _i]),
+    "nsl_moe_set_direct_output": (None, [_vp, _i]),
     # include/nslm_pack.h
     "nsl_blk4_bytes": (_sz, [_i, _i, _i]),
     "nsl_blk4_split": (_i, [_vp, _sz, _i, _i, _i, _vp, _vp, _vp, _vp]),

@@ -172,6 +172,10 @@ class Moe:
         L.check()
         return out, ind
 
+    def set_direct_output(self, on):
+        """Whether the pinned forms' combine kernel stores straight into the pinned output (default) or a copy brings it."""
+        self.lib.nsl_moe_set_direct_output(self.h, int(on))
+
     def forward_pinned(self, T):
         """Inputs already in self.hx / self.hlogits; the result lands in self.hout."""
         if self.lib.nsl_moe_forward_pinned(self.h, T):
