@@ -399,10 +399,8 @@ __device__ __forceinline__ void pair_weights(const StreamTab& tab, uint32_t sw, 
                              fma2(q[1], pack2(-1.4693679385278594e-39f, -1.4693679385278594e-39f),
                                   mul2(q[0], pack2(-7.346839692639297e-40f, -7.346839692639297e-40f)))));
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
-        const u64 t = fma2(q[3], v[4 * c + 3], fma2(q[2], v[4 * c + 2], fma2(q[1], v[4 * c + 1], mul2(q[0], v[4 * c]))));
-        w2[c] = mul2(add2(t, kq), sc2);
-    }
+    for (int c = 0; c < 8; ++c)      // the centring term first: every partial sum stays an exact integer multiple of 2^-45 below 2^24
+        w2[c] = mul2(fma2(q[3], v[4 * c + 3], fma2(q[2], v[4 * c + 2], fma2(q[1], v[4 * c + 1], fma2(q[0], v[4 * c], kq)))), sc2);
 }
 // Two f32 -> one word of two bf16 (round to nearest even), low half = a.
 __device__ __forceinline__ uint32_t bf16x2_bits(float a, float b) {

@@ -60,7 +60,8 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-// Bounded wait: false after GM_WAIT_LIMIT polls (the caller records the code and stops).
+// Bounded wait: false after GM_WAIT_LIMIT polls (the caller records the code and stops).  Polling on purpose: the suspended
+// form (mbarrier.try_wait) saved the polls' instructions but cost 3 us per 174 us launch in wake-up latency.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     for (uint32_t i = 0; i < GM_WAIT_LIMIT; ++i) {
         if (mbar_test(bar, parity)) return true;
@@ -126,7 +127,9 @@ __device__ __forceinline__ QuadIn load_quad(const WSlice& w, int row, int kb, in
 }
 
 // WF: the weights' form.  0: SEED4P4 blocks; 1: stored BF16 values; 2: SEED4 (P = 3) blocks.
-template <int NT, int WF>
+// VEC: rows are whole quads of blocks (K a multiple of 32), so a thread's four blocks are one aligned load per stream and no
+// row ends inside a quad.
+template <int NT, int WF, bool VEC>
 __global__ void __launch_bounds__(GM_THREADS, 2) seed_gemm_kernel(MmParams a, KConst kc) {
     constexpr bool BF16W = WF == 1, P3 = WF == 2;
     if (a.ntiles && (int) blockIdx.y >= *a.ntiles) return;
@@ -188,7 +191,7 @@ __global__ void __launch_bounds__(GM_THREADS, 2) seed_gemm_kernel(MmParams a, KC
         // ---- producers: weight tile (thread = row, half of the 8 blocks) and input tile (thread = token, half of 64 k) --
         const int prow = tid >> 1, half = tid & 1;
         const int grow = r0 + prow;
-        const bool vec = (NB & 3) == 0;
+        constexpr bool vec = VEC;
         QuadIn cur = {{0u, 0u}, {0u, 0u}, 0u, false}, nxt = cur;
         uint4 bcur[4], bnxt[4];      // BF16 weights: this thread's 32 values of the K step, as stored
         auto load_bf16 = [&](int kt, uint4* o) {
@@ -355,18 +358,23 @@ bool launch_bf16_mm_skinny(cudaStream_t s, const WSlice& w, int K, int R, const 
 
 static int g_exact;   // kc_seed_gemm_f32: process-wide, as the reference's switch (engine/kernels_moe.cu:2354)
 
-template <int NT, int WF>
-static void launch_gemm_nt(cudaStream_t s, const MmParams& a, dim3 grid) {
+template <int NT, int WF, bool VEC>
+static void launch_gemm_v(cudaStream_t s, const MmParams& a, dim3 grid) {
     const size_t smem = (size_t) GM_STAGES * (NT + 1) * GM_TILE_BYTES + 1024;
     static bool attr_set[16];
     int dev = 0;
     cudaGetDevice(&dev);
     if (!attr_set[dev & 15]) {
-        cudaFuncSetAttribute(seed_gemm_kernel<NT, WF>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+        cudaFuncSetAttribute(seed_gemm_kernel<NT, WF, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
         attr_set[dev & 15] = true;
     }
-    seed_gemm_kernel<NT, WF><<<grid, GM_THREADS, smem, s>>>(a, kconst());
+    seed_gemm_kernel<NT, WF, VEC><<<grid, GM_THREADS, smem, s>>>(a, kconst());
     count_launch();
+}
+template <int NT, int WF>
+static void launch_gemm_nt(cudaStream_t s, const MmParams& a, dim3 grid) {
+    if (WF == 1 || a.K % 32 == 0) launch_gemm_v<NT, WF, true>(s, a, grid);      // stored BF16 weights have no quads
+    else launch_gemm_v<NT, WF, false>(s, a, grid);
 }
 
 static void launch_gemm(cudaStream_t s, int fmt, const char* who, MmParams a, int tiles_y) {
