@@ -41,7 +41,7 @@ BYTES_PER_MATRIX = D * FF // 8 * 4 + D * FF // 16        # 589,824: seeds + coef
 BLOCKS_PER_MATRIX = D * FF // 8                           # 131,072 blocks of 8 weights
 ALU_FLOOR = 53 / 64        # clocks per block per SM: 53 logic-pipe operations per block, 64 logic lanes per SM and clock
                            # (ncu agrees: 113.4 k blocks per SM in 141.3 k active cycles with sm__pipe_alu_cycles_active
-                           # at 70 %; profiles/mv_pair_gate_up_config1.md)
+                           # at 70 %; profiles/logic_pipe_rates.md)
 METRIC = "seed_decode_moe_gemv_tokens_per_s"
 # DRAM bytes per launch of the gate+up kernel from ncu (profiles/mv_pair_gate_up_config1.md): per distinct expert
 # (gate + up streams: pairs that share an expert find its streams in L2) and the rest (activations, tables)
