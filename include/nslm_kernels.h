@@ -234,11 +234,13 @@ void nsl_decode3_bf16(cudaStream_t s, WSlice w, int K, int R, uint16_t* out, con
 void nsl_mv_gu_routed(cudaStream_t s, const WSlice* wg, const WSlice* wu, int K, int R, const float* x, int xs, float* a, int ys,
                       int n_exp, int top_k, const float* logits, int ld, int T, int32_t* ind, float* wt, int raw,
                       const uint32_t* G);
-/* Programmatic dependent launch for the calling thread's next launches of the mat-vec kernels (kc_mv*, nsl_mv*),
- * kq4_moe_combine and nsl_ep_combine: while on, such a kernel may become resident before the previous kernel in its
- * stream has finished and waits on the device for its completion before it touches memory a neighbour writes.  Turn it
- * A kernel launched this way reads and writes nothing a neighbour touches before that wait, so it is safe after any
- * kernel; after a copy or another kind of node it is an ordinary launch. */
+/* Programmatic dependent launch for the calling thread's next launches of: the seed mat-vecs (kc_mv, kc_mv_sel, kc_mv_gu,
+ * nsl_mv*), the MF_Q4 and MF_BF16 forms of kc_mv / kc_mm's decode-batch kernel, kq4_moe_combine, nsl_ep_combine and the
+ * peer-memory exchange kernels, kc_attn (whose reduction is always a dependent launch of its first pass), kc_gnorm,
+ * kc_rope_kv and nsl_residual_add.  While on, such a kernel may become resident before the previous kernel in its stream
+ * has finished; it waits on the device for that kernel's completion before it reads or writes anything a neighbour
+ * touches, so it is safe after any kernel; after a copy or another kind of node it is an ordinary launch.  Thread-local;
+ * turn it off again (0) before launching anything else on the stream. */
 void nsl_dependent_launch(int on);
 
 #ifdef __cplusplus
