@@ -946,7 +946,8 @@ def measure_ep(args, K, W, quiet_clocks=False):
         launches = (lib.nsl_launch_count() - launches0) * K
         captured = not args.no_graph
         if captured:
-            gs = ep.GraphedSteps(epl, layers, [(dx[b], dl[b]) for b in range(NB)])
+            combos = sorted({(i % NB, i % NL) for i in range(2 * W + K + 1)}) if args.ep_collectives == "p2p" else ()
+            gs = ep.GraphedSteps(epl, layers, [(dx[b], dl[b]) for b in range(NB)], whole=combos)      # one graph per step
             run_step = lambda i: gs.step(i % NB, i % NL)
         else:
             run_step = one

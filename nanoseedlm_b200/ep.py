@@ -199,9 +199,13 @@ class GraphedSteps:
     the two all-to-alls issued between them as ordinary NCCL calls.  One first graph per input batch
     and one second graph per resident layer are captured up front; a step then costs three graph launches and two
     collective calls on the host instead of a dozen kernel launches.  (Capturing the collectives themselves into a graph
-    did not complete on this system, so they stay outside.)"""
+    did not complete on this system, so they stay outside.)
 
-    def __init__(self, ep, layers, inputs):
+    whole (peer-memory exchange only): the (input batch, layer) pairs whose step is captured as ONE graph, as an engine that
+    replays a graph per decode forward would hold it: no second graph launch, and the dispatch kernel's dependents come in
+    while it drains."""
+
+    def __init__(self, ep, layers, inputs, whole=()):
         self.ep, be = ep, ep.be
         stream = torch.cuda.current_stream()
 
@@ -231,9 +235,19 @@ class GraphedSteps:
         self.first = [capture(lambda x=x, l=l: first(x, l)) for x, l in inputs]
         self.second = [capture(lambda layer=layer: second(layer)) for layer in layers]
         self.third = None if gather or self.p2p else capture(lambda: be.reduce(ep))
+        self.whole = {}
+        if self.p2p:
+            for i, j in whole:
+                if (i, j) not in self.whole:
+                    x, l = inputs[i]
+                    self.whole[(i, j)] = capture(lambda x=x, l=l, layer=layers[j]: (first(x, l), second(layer)))
 
     def step(self, i_input, i_layer):
         ep = self.ep
+        g = self.whole.get((i_input, i_layer))
+        if g is not None:
+            g.replay()
+            return ep.out
         self.first[i_input].replay()
         if self.p2p:      # the exchanges are inside the graphs: two launches make a step
             self.second[i_layer].replay()

@@ -77,6 +77,13 @@ def main():
             out = g.step(0, 0)
         stream.synchronize()
     check(torch.equal(out, want), "graphed p2p step differs")
+    dist.barrier()
+    with torch.cuda.stream(stream):      # the whole step as one graph
+        g1 = ep.GraphedSteps(p2p, [mine], [(dx, dl)], whole=[(0, 0)])
+        for _ in range(3):
+            out = g1.step(0, 0)
+        stream.synchronize()
+    check(torch.equal(out, want), "p2p step captured as one graph differs")
     # the whole decoder step with its routed experts behind the window: this rank's rows against the same rows through a
     # decoder that holds every expert locally (same weights on every rank)
     from nanoseedlm_b200 import decoder

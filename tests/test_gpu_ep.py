@@ -80,7 +80,8 @@ def test_p2p_exchange_single_rank_and_graphs(oracle):
         assert np.max(np.abs(out - refs[i])) <= 1e-6 * np.max(np.abs(refs[i]))
     stream = torch.cuda.Stream()
     with torch.cuda.stream(stream):
-        g = ep.GraphedSteps(epl, [layer], list(zip(dx, dl)))
+        g = ep.GraphedSteps(epl, [layer], list(zip(dx, dl)), whole=[(1, 0), (2, 0)])      # inputs 1 and 2: the whole step as one graph
+        assert set(g.whole) == {(1, 0), (2, 0)}
         for i in (2, 1, 0, 1):
             out = g.step(i, 0)
             stream.synchronize()
