@@ -48,6 +48,10 @@ int nsl_moe_forward_pinned(NslMoe* m, int T);
 /* The same in two halves: submit enqueues the copies and the layer on the handle's stream and returns; wait blocks until
  * the result is in the pinned output buffer.  Two handles used alternately keep two steps in flight. */
 int nsl_moe_submit_pinned(NslMoe* m, int T);
+/* nsl_moe_submit_pinned from the caller's own pinned memory: block = max_tokens rows of d floats followed by max_tokens rows
+ * of n_exp logits (a full batch), copied to the device as it lies (one copy, no staging copy on the host); the result lands in
+ * nsl_moe_host_out as usual.  Pair with nsl_moe_wait. */
+int nsl_moe_submit_block(NslMoe* m, const float* block);
 int nsl_moe_wait(NslMoe* m);
 /* Routing of the last forward (device memory) and the layer's stream. */
 const int32_t* nsl_moe_dev_ind(NslMoe* m);

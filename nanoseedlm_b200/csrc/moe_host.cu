@@ -126,10 +126,11 @@ int nsl_moe_forward_dev(NslMoe* m, cudaStream_t s, const float* x, const float* 
 // The pinned forms' device work: the inputs' copy, the layer, the result to pinned memory.  A full batch's rows and logits
 // are adjacent in both staging blocks and travel as ONE copy; the combine kernel stores its rows straight into the pinned
 // output (posted writes over PCIe: no device-to-host copy to launch and wait for) unless direct output is switched off.
-static int submit_pinned(NslMoe* m, int T) {
+static int submit_pinned(NslMoe* m, int T, const float* block = NULL) {
     if (T < 1 || T > m->max_tokens) { nsl::set_error("nsl_moe_forward: %d rows, at most %d", T, m->max_tokens); return -1; }
     const size_t xb = (size_t) T * m->d * 4, lb = (size_t) T * m->n_exp * 4;
-    if (T == m->max_tokens) cudaMemcpyAsync(m->x, m->hx, xb + lb, cudaMemcpyHostToDevice, m->stream);
+    if (block) cudaMemcpyAsync(m->x, block, xb + lb, cudaMemcpyHostToDevice, m->stream);      // the caller's own pinned block (T == max_tokens)
+    else if (T == m->max_tokens) cudaMemcpyAsync(m->x, m->hx, xb + lb, cudaMemcpyHostToDevice, m->stream);
     else {
         cudaMemcpyAsync(m->x, m->hx, xb, cudaMemcpyHostToDevice, m->stream);
         cudaMemcpyAsync(m->logits, m->hlogits, lb, cudaMemcpyHostToDevice, m->stream);
@@ -169,6 +170,13 @@ cudaStream_t nsl_moe_stream(NslMoe* m) { return m->stream; }
 // nsl_moe_submit_pinned enqueues without waiting and nsl_moe_wait waits, so that a caller with two handles keeps two
 // steps in flight (one's copies and launch latency under the other's kernels).
 int nsl_moe_submit_pinned(NslMoe* m, int T) { return submit_pinned(m, T); }
+
+// The same from the caller's own pinned memory: block = max_tokens rows of d floats followed by max_tokens rows of n_exp logits
+// (a full batch), copied as it lies; the result lands in the layer's pinned output (nsl_moe_host_out).
+int nsl_moe_submit_block(NslMoe* m, const float* block) {
+    if (!block) { nsl::set_error("nsl_moe_submit_block: no input block"); return -1; }
+    return submit_pinned(m, m->max_tokens, block);
+}
 
 int nsl_moe_wait(NslMoe* m) { return cudaStreamSynchronize(m->stream) == cudaSuccess ? 0 : -1; }
 

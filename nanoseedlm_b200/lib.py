@@ -127,6 +127,7 @@ PROTOTYPES = {
     "nsl_moe_host_out": (_vp, [_vp]),
     "nsl_moe_forward_pinned": (_i, [_vp, _i]),
     "nsl_moe_submit_pinned": (_i, [_vp, _i]),
+    "nsl_moe_submit_block": (_i, [_vp, _vp]),
     "nsl_moe_wait": (_i, [_vp]),
     "nsl_moe_dev_ind": (_vp, [_vp]),
     "nsl_moe_dev_wt": (_vp, [_vp]),

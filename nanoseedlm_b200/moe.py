@@ -172,6 +172,13 @@ class Moe:
         L.check()
         return out, ind
 
+    def forward_block(self, block):
+        """One full batch from the caller's own pinned block (a pinned torch tensor or an address: max_tokens rows of d floats, then
+        max_tokens rows of logits); the result lands in self.hout."""
+        ptr = block.data_ptr() if hasattr(block, "data_ptr") else int(block)
+        if self.lib.nsl_moe_submit_block(self.h, C.c_void_p(ptr)) or self.lib.nsl_moe_wait(self.h):
+            raise RuntimeError(L.last_error() or "nsl_moe_submit_block failed")
+
     def set_direct_output(self, on):
         """Whether the pinned forms' combine kernel stores straight into the pinned output (default) or a copy brings it."""
         self.lib.nsl_moe_set_direct_output(self.h, int(on))

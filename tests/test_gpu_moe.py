@@ -116,6 +116,34 @@ def test_pinned_forward_in_two_halves_with_two_handles(oracle):
         m.close()
 
 
+def test_full_batch_from_the_callers_pinned_block_and_both_result_paths(oracle):
+    """nsl_moe_submit_block (rows then logits in the caller's pinned memory, one copy) and the pinned forms with the result
+    stored by the combine kernel or brought by a copy: all bit-equal to forward_host."""
+    import torch
+    from nanoseedlm_b200 import moe
+    d, ff, E, k, T = 256, 64, 16, 4, 8
+    layer = moe.DeviceLayer.from_host(moe.HostLayer(oracle, d, ff, E, seed=93))
+    m = moe.Moe(layer, k, T)
+    x = oracle.normal(60, T * d, bf16=True).reshape(T, d)
+    lg = oracle.normal(61, T * E).reshape(T, E)
+    want = m.forward_host(x, lg)[0].copy()
+    block = torch.cat([torch.from_numpy(x).reshape(-1), torch.from_numpy(lg).reshape(-1)]).pin_memory()
+    for direct in (1, 0):
+        m.set_direct_output(direct)
+        m.hout[:] = 0
+        m.forward_block(block)
+        assert np.array_equal(m.hout[:T], want)
+        m.hout[:] = 0
+        m.hx[:T], m.hlogits[:T] = x, lg
+        m.forward_pinned(T)
+        assert np.array_equal(m.hout[:T], want)
+        m.hout[:] = 0
+        m.hx[:5], m.hlogits[:5] = x[:5], lg[:5]      # fewer rows than the layer holds: two copies
+        m.forward_pinned(5)
+        assert np.array_equal(m.hout[:5], want[:5])
+    m.close()
+
+
 def test_dependent_launches_change_nothing(oracle):
     """The decode path with programmatic dependent launches (the default) and with ordinary launches: the same bits,
     directly and replayed from a CUDA graph of several steps."""
