@@ -10,10 +10,11 @@
  * Conventions (engine/kernels_cuda.h:1-7; engine/qwen4_cuda.c:1219-1234): the first argument is the stream; calls
  * are asynchronous launches that return void and allocate nothing; the caller owns every buffer; errors surface at the
  * caller's cudaStreamSynchronize + cudaGetLastError.  Activations are f32 arrays of bf16-rounded values; xs / ys are
- * row strides in floats.  The SEED4P4 weight format (MF_SEED4P4) is implemented everywhere; the mat-vec entry points
- * (kc_mv, kc_mv_sel, kc_mv_gu) also serve MF_SEED4 (P = 3: p[0] seeds, p[1] nibble words -- exponent code in bits 0-3,
- * coefficient p in bits 4p+4..4p+7 --, eb the exponent bias, G the 24- or 32-bit stream table) and the dense kc_mv
- * MF_Q4: a call with another format launches nothing and records an error that nsl_last_error() returns. */
+ * row strides in floats.  The SEED4P4 weight format (MF_SEED4P4) is implemented everywhere; the mat-vec and GEMM entry
+ * points (kc_mv, kc_mv_sel, kc_mv_gu, kc_mm*) also serve MF_SEED4 (P = 3: p[0] seeds, p[1] nibble words -- exponent code
+ * in bits 0-3, coefficient p in bits 4p+4..4p+7 --, eb the exponent bias, G the 24- or 32-bit stream table), the dense
+ * kc_mv MF_Q4, and the dense kc_mv / kc_mm stored BF16 values (MF_BF16: p[0] = [R][K]): a call with another format
+ * launches nothing and records an error that nsl_last_error() returns. */
 #pragma once
 #include <stddef.h>
 #include <stdint.h>

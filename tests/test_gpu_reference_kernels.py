@@ -163,3 +163,53 @@ def test_reference_kernels_pass_this_suites_checks(oracle, golden):
         test_gpu_cache.test_cache_admit_copy_and_identical_results(oracle)
         test_gpu_gemm.test_mm_grouped_tile_table(oracle, False, "dev")
         test_gpu_attn.run_variant(0, 8, 2, 640, [300, 299, 37], [0, 310, 600], 5, (301 + 4) // 5, True, None, 21, strict=True)
+
+
+@contextlib.contextmanager
+def stream_table_24_bits():
+    """The table the reference's hosts pass with MF_SEED4 tensors: lfsr_stream24 = the low 24 bits of the 32-bit table
+    (nslm/lfsr.h:40-49; engine/qwen4_cuda.c:265)."""
+    import torch
+    from nanoseedlm_b200 import kernels
+    g32 = kernels.stream_table()
+    d = torch.cuda.current_device()
+    kernels._table[d] = kernels.dev(g32.cpu().numpy().view(np.uint32) & np.uint32(0xFFFFFF))
+    try:
+        yield
+    finally:
+        kernels._table[d] = g32
+
+
+def test_p3_format_against_the_reference_kernels_with_the_24_bit_table(oracle):
+    """MF_SEED4 (P = 3): this library with the 24-bit table == this library with the 32-bit table, bit for bit (it reads no
+    stream bit beyond 23 for this format), and within the bf16 bound of the reference's own P = 3 kernels, for the dense
+    mat-vec (1 and 5 tokens), the gather and gate + up at the tuned kernel's shapes, and the grouped GEMM."""
+    from nanoseedlm_b200 import kernels
+    from oracle import binding as B
+    R, K, S = 96, 512, 4
+    mats = [B.Matrix3(R, K, 500 + s, eb=-20 - s % 2) for s in range(S)]
+    mu = [B.Matrix3(R, K, 600 + s, eb=-21 + s % 2) for s in range(S)]
+    w, wu = kernels.SeedWeight3(mats), kernels.SeedWeight3(mu)
+    rng = np.random.default_rng(17)
+    x = B.bfr(rng.standard_normal((6, K)).astype(np.float32))
+    sel = rng.integers(0, S, 12)
+    perm, tiles = [], []
+    for s in range(S):
+        st = len(perm)
+        perm += [p for p in range(12) if sel[p] == s]
+        if len(perm) > st:
+            tiles.append((s, st, len(perm) - st))
+
+    def run():
+        return [kernels.kt_mv3(w, x[:1], 1), kernels.kt_mv3(w, x[:5], 5), kernels.kt_mv3_sel(w, sel, 2, x), kernels.kt_mv3_gu(w, wu, sel, 2, x),
+                kernels.kt_mm_grouped(w, 12, 2, perm, tiles, x, mode="dev")]
+
+    wide = run()
+    with stream_table_24_bits():
+        narrow = run()
+        with reference_kernels():
+            ref = run()
+    for a, b in zip(wide, narrow):
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+    for i, (a, r) in enumerate(zip(narrow, ref)):
+        close(a, r, f"P = 3 case {i}", units=2 if i == 3 else 1)
