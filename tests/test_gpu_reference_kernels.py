@@ -165,6 +165,39 @@ def test_reference_kernels_pass_this_suites_checks(oracle, golden):
         test_gpu_attn.run_variant(0, 8, 2, 640, [300, 299, 37], [0, 310, 600], 5, (301 + 4) // 5, True, None, 21, strict=True)
 
 
+def test_reference_kernels_pass_the_checks_either_side_of_the_path(oracle):
+    """The same for the kernels around the seed products, at the sizes the reference's kernels serve: its router holds
+    n <= 128 experts and top_k <= 16 (engine/kernels_moe.cu:742-772), its per-head mat-vec T <= 8 rows
+    (engine/kernels_moe.cu:2437-2440), its GEMM K a multiple of 32 (engine/kernels_cuda.h:118)."""
+    import test_gpu_decoder
+    import test_gpu_gemm
+    import test_gpu_mova
+    import test_gpu_mv
+    import test_gpu_q4
+    from nanoseedlm_b200 import kernels, lib as L
+    with reference_kernels():
+        for d, n, k, T in ((512, 20, 4, 5), (2048, 128, 8, 8), (2048, 100, 8, 3)):
+            test_gpu_mova.test_router(kernels, L, d, n, k, T)
+        for n, k in ((100, 8), (64, 4), (1, 1)):
+            test_gpu_mova.test_router_topk_ties_to_lowest_id(kernels, L, n, k)
+        for O, I, T, gate in ((96, 128, 3, 0), (128, 192, 5, 1), (6144, 128, 2, 1), (33, 2048, 4, 0)):
+            test_gpu_mova.test_heads_mv(kernels, O, I, T, gate)
+        for O, I in ((96, 128), (128, 192)):
+            test_gpu_mova.test_heads_deq_bit_exact(kernels, O, I)
+        for R, K in ((24, 256), (24, 4096), (37, 2048), (1000, 64), (16, 8192)):
+            test_gpu_q4.test_q4_dense_tokens_add_and_batch_invariance(R, K)
+        for V, n in ((151936, 3), (1000, 5), (7, 2)):
+            test_gpu_q4.test_argmax_ties_to_the_lowest_id_and_probability(V, n)
+        for R, K in ((24, 256), (24, 512), (512, 2048), (24, 136)):
+            test_gpu_mv.test_mv_gather(oracle, R, K)
+        for R, K in ((24, 256), (512, 2048), (24, 72)):
+            test_gpu_mv.test_mv_gate_up_swiglu(oracle, R, K)
+        for exact in (False, True):
+            for R, K, T in ((40, 128, 45), (128, 64, 16), (300, 512, 130)):
+                test_gpu_gemm.test_mm_dense_residual(oracle, exact, R, K, T)
+        test_gpu_decoder.test_small_kernels_alone(oracle)
+
+
 @contextlib.contextmanager
 def stream_table_24_bits():
     """The table the reference's hosts pass with MF_SEED4 tensors: lfsr_stream24 = the low 24 bits of the 32-bit table
