@@ -28,13 +28,26 @@ __device__ __forceinline__ void mma_bf16_16x8x16(float* c, const uint32_t* a, ui
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// One code word -> four bf16 pairs {q_i - 8, q_(i+4) - 8}, i = 0..3.
+// One code word -> four bf16 pairs {q_i - 8, q_(i+4) - 8}, i = 0..3.  (w >> 4i) & mask | bias is ONE three-input logic
+// operation when mask and bias are register (or constant-bank) operands; written with immediates the compiler emits an
+// AND and an OR (the instruction takes one immediate), which doubled the logic-pipe work of the whole kernel.  The two
+// words therefore live in constant memory, where the compiler cannot see their values.
+static __constant__ uint32_t q4_nib_mask = 0x000F000Fu, q4_nib_bias = 0x43004300u;
 __device__ __forceinline__ void unpack8(uint32_t w, uint32_t* r) {
+    const uint32_t mask = q4_nib_mask, bias = q4_nib_bias;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const uint32_t v = ((w >> (4 * i)) & 0x000F000Fu) | 0x43004300u;      // {128 + q_i, 128 + q_(i+4)}
+        uint32_t v;      // {128 + q_i, 128 + q_(i+4)}
+        asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(v) : "r"(w >> (4 * i)), "r"(mask), "r"(bias));
         asm("sub.bf16x2 %0, %1, %2;" : "=r"(r[i]) : "r"(v), "r"(0x43084308u));   // - 136
     }
+}
+
+// The first product of a group: the accumulator starts from zero (no registers to clear).
+__device__ __forceinline__ void mma_bf16_16x8x16_first(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
+                 : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.0f));
 }
 
 __device__ __forceinline__ float bf16_to_f32(uint16_t h) { return __uint_as_float((uint32_t) h << 16); }
@@ -308,41 +321,60 @@ __global__ void __launch_bounds__(32 * WARPS, 1) q4_mv_ring_kernel(const uint32_
 // so its 32 fragment registers and 8 input sums are loaded once and stay in registers; per tile a warp streams
 // 16 rows x 128 bytes of codes (+ 8 scales, 8 biases per row) through its cp.async ring, runs 16 MMAs, and the warps'
 // partial sums meet in shared memory (8 KB per tile), where they are added in warp order.  K = 256 x WARPS.
-template <int WARPS, int NST>
-__global__ void __launch_bounds__(32 * WARPS, 1) q4_mv_ksplit_kernel(const uint32_t* __restrict__ codes, const uint16_t* __restrict__ S,
+// BPS blocks share an SM (16 warps in all): a block's barrier per tile then overlaps another block's work.  Shared
+// memory: the partial sums, then the staged inputs, whose place the rings take once every warp holds its fragments.
+template <int WARPS, int NST, int BPS>
+__global__ void __launch_bounds__(32 * WARPS, BPS) q4_mv_ksplit_kernel(const uint32_t* __restrict__ codes, const uint16_t* __restrict__ S,
                                                                      const uint16_t* __restrict__ B, int K, int R,
                                                                      const float* __restrict__ x, int xs, float* __restrict__ y,
                                                                      int ys, int T, int add) {
     constexpr int ROW = Q4Ring<4>::ROW, STAGE = Q4Ring<4>::STAGE;
+    constexpr int G = 4 * WARPS, KB = 128 * WARPS;      // groups and bytes of codes per row (K = 256 x WARPS)
     extern __shared__ __align__(16) uint32_t q4_smem[];
-    const int G = K / Q4_GROUP;      // = 4 * WARPS
-    uint32_t* xb = q4_smem;
-    float* xsum = (float*) (q4_smem + (size_t) G * 256);
-    float* part = xsum + G * 8;                                                  // [2][WARPS][32][4]
-    unsigned char* ring = (unsigned char*) (part + 2 * WARPS * 128) + (size_t) (threadIdx.x >> 5) * NST * STAGE;
+    float* part = (float*) q4_smem;                                              // [2][WARPS][32][4]
+    uint32_t* xb = q4_smem + 2 * WARPS * 128;
+    float* xsum = (float*) (xb + (size_t) G * 256);
+    // the rings take the place of the staged inputs once those sit in the warps' registers
+    unsigned char* ring = (unsigned char*) xb + (size_t) (threadIdx.x >> 5) * NST * STAGE;
     grid_dependents_go();
     grid_dependency_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, q = lane & 3, rr = lane >> 2;
     const int tiles = (R + 15) / 16;
     const int my_tiles = (int) blockIdx.x < tiles ? (tiles - (int) blockIdx.x + (int) gridDim.x - 1) / (int) gridDim.x : 0;
 
-    auto issue = [&](int idx) {      // tile number idx of this block: this warp's 128-byte slice of its 16 rows
-        if (idx < my_tiles) {
-            const int tile = blockIdx.x + idx * gridDim.x;
-            unsigned char* st = ring + (size_t) (idx % NST) * STAGE;
+    // the copies of the next tile to fetch: running source pointers (a tile further = gridDim.x x 16 rows) and stage
+    int nidx = 0, nstage = 0, ntile = blockIdx.x;
+    const unsigned char* csrc = (const unsigned char*) codes + ((size_t) blockIdx.x * 16 + (lane >> 3)) * KB + warp * 128 + (lane & 7) * 16;
+    const uint16_t* ssrc = (lane >> 4 ? B : S) + ((size_t) blockIdx.x * 16 + (lane & 15)) * G + warp * 4;
+    const size_t cstep = (size_t) gridDim.x * 16 * KB, sstep = (size_t) gridDim.x * 16 * G;
+    const unsigned cdst = (unsigned) __cvta_generic_to_shared(ring) + (lane >> 3) * ROW + (lane & 7) * 16;
+    const unsigned sdst = (unsigned) __cvta_generic_to_shared(ring) + (lane & 15) * ROW + 128 + (lane >> 4) * 8;
+    auto issue = [&]() {      // this warp's 128-byte slice of the 16 rows of its block's next tile
+        if (nidx < my_tiles) {
+            const unsigned so = (unsigned) nstage * STAGE;
+            if (ntile * 16 + 16 <= R) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int lr = 4 * i + (lane >> 3), piece = lane & 7, row = min(tile * 16 + lr, R - 1);
-                cp_async16(st + lr * ROW + piece * 16, (const unsigned char*) (codes + (size_t) row * (K / 8) + warp * 32) + piece * 16);
+                for (int i = 0; i < 4; ++i)
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(cdst + so + i * 4 * ROW), "l"(csrc + (size_t) i * 4 * KB) : "memory");
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(sdst + so), "l"(ssrc) : "memory");
+            } else {      // the last, partial tile: rows beyond R - 1 read row R - 1 (their results are not stored)
+                unsigned char* st = ring + so;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int lr = 4 * i + (lane >> 3), piece = lane & 7, row = min(ntile * 16 + lr, R - 1);
+                    cp_async16(st + lr * ROW + piece * 16, (const unsigned char*) codes + (size_t) row * KB + warp * 128 + piece * 16);
+                }
+                const int lr = lane & 15, row = min(ntile * 16 + lr, R - 1);
+                cp_async8(st + lr * ROW + 128 + (lane >> 4) * 8, (lane >> 4 ? B : S) + (size_t) row * G + warp * 4);
             }
-            const int lr = lane & 15, row = min(tile * 16 + lr, R - 1);
-            cp_async8(st + lr * ROW + 128 + (lane >> 4) * 8, (lane >> 4 ? B : S) + (size_t) row * G + warp * 4);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
+        ++nidx;
+        ntile += gridDim.x;
+        csrc += cstep;
+        ssrc += sstep;
+        nstage = nstage + 1 == NST ? 0 : nstage + 1;
     };
-#pragma unroll
-    for (int i = 0; i < NST - 1; ++i) issue(i);
-
     const bool vec = (xs & 3) == 0 && aligned16_dev(x);
     for (int i = threadIdx.x; i < G * 32; i += 32 * WARPS) {
         const int g = i >> 5, sq = (i >> 3) & 3, n = i & 7;
@@ -389,12 +421,17 @@ __global__ void __launch_bounds__(32 * WARPS, 1) q4_mv_ksplit_kernel(const uint3
         xg[j][0] = xsum[g * 8 + 2 * q];
         xg[j][1] = xsum[g * 8 + 2 * q + 1];
     }
+    __syncthreads();      // every warp has its inputs: their place is the rings' now
+#pragma unroll
+    for (int i = 0; i < NST - 1; ++i) issue();
 
+    int stage = 0;
     for (int idx = 0; idx < my_tiles; ++idx) {
         asm volatile("cp.async.wait_group %0;" ::"n"(NST - 2) : "memory");
         __syncwarp();
         const int tile = blockIdx.x + idx * gridDim.x;
-        const unsigned char* st = ring + (size_t) (idx % NST) * STAGE;
+        const unsigned char* st = ring + (size_t) stage * STAGE;
+        stage = stage + 1 == NST ? 0 : stage + 1;
         const unsigned char* row0 = st + rr * ROW, *row1 = st + (rr + 8) * ROW;
         const uint4 t0 = *(const uint4*) (row0 + 128), t2 = *(const uint4*) (row1 + 128);      // {4 scales, 4 biases}
         const uint32_t sa0[2] = {t0.x, t0.y}, ba0[2] = {t0.z, t0.w}, sa1[2] = {t2.x, t2.y}, ba1[2] = {t2.z, t2.w};
@@ -406,23 +443,23 @@ __global__ void __launch_bounds__(32 * WARPS, 1) q4_mv_ksplit_kernel(const uint3
             uint32_t a0[8], a1[8];
             unpack8(w0.x, a0); unpack8(w0.y, a0 + 4);
             unpack8(w1.x, a1); unpack8(w1.y, a1 + 4);
-            float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            float c[4];
             const uint32_t f0[4] = {a0[0], a1[0], a0[4], a1[4]}, f1[4] = {a0[1], a1[1], a0[5], a1[5]};
             const uint32_t f2[4] = {a0[2], a1[2], a0[6], a1[6]}, f3[4] = {a0[3], a1[3], a0[7], a1[7]};
-            mma_bf16_16x8x16(c, f0, breg[j][0], breg[j][1]);
+            mma_bf16_16x8x16_first(c, f0, breg[j][0], breg[j][1]);
             mma_bf16_16x8x16(c, f1, breg[j][2], breg[j][3]);
             mma_bf16_16x8x16(c, f2, breg[j][4], breg[j][5]);
             mma_bf16_16x8x16(c, f3, breg[j][6], breg[j][7]);
             const float s0 = bf16_to_f32((uint16_t) (sa0[j >> 1] >> sh)), s1 = bf16_to_f32((uint16_t) (sa1[j >> 1] >> sh));
             const float e0 = fmaf(8.0f, s0, bf16_to_f32((uint16_t) (ba0[j >> 1] >> sh)));
             const float e1 = fmaf(8.0f, s1, bf16_to_f32((uint16_t) (ba1[j >> 1] >> sh)));
-            out[0] += fmaf(s0, c[0], e0 * xg[j][0]);
-            out[1] += fmaf(s0, c[1], e0 * xg[j][1]);
-            out[2] += fmaf(s1, c[2], e1 * xg[j][0]);
-            out[3] += fmaf(s1, c[3], e1 * xg[j][1]);
+            out[0] = fmaf(s0, c[0], fmaf(e0, xg[j][0], out[0]));
+            out[1] = fmaf(s0, c[1], fmaf(e0, xg[j][1], out[1]));
+            out[2] = fmaf(s1, c[2], fmaf(e1, xg[j][0], out[2]));
+            out[3] = fmaf(s1, c[3], fmaf(e1, xg[j][1], out[3]));
         }
         __syncwarp();
-        issue(idx + NST - 1);
+        issue();
         float* pb = part + (size_t) (idx & 1) * WARPS * 128;
         *(float4*) (pb + (warp * 32 + lane) * 4) = make_float4(out[0], out[1], out[2], out[3]);
         __syncthreads();      // the block's partial sums of this tile are in; the other buffer is free for the next tile
@@ -442,17 +479,17 @@ __global__ void __launch_bounds__(32 * WARPS, 1) q4_mv_ksplit_kernel(const uint3
     asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
 
-template <int WARPS, int NST>
+template <int WARPS, int NST, int BPS>
 static void launch_q4_ksplit(cudaStream_t s, size_t total, int blocks, const WSlice& w, int K, int R, const float* x, int xs, float* y,
                              int ys, int T, int add) {
     static bool attr_set[16];
     int dev = 0;
     cudaGetDevice(&dev);
     if (!attr_set[dev & 15]) {
-        cudaFuncSetAttribute(q4_mv_ksplit_kernel<WARPS, NST>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin() - 1024);
+        cudaFuncSetAttribute(q4_mv_ksplit_kernel<WARPS, NST, BPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem_optin() - 1024);
         attr_set[dev & 15] = true;
     }
-    launch(q4_mv_ksplit_kernel<WARPS, NST>, (unsigned) blocks, 32 * WARPS, total, s, (const uint32_t*) w.p[0], (const uint16_t*) w.p[1],
+    launch(q4_mv_ksplit_kernel<WARPS, NST, BPS>, (unsigned) blocks, 32 * WARPS, total, s, (const uint32_t*) w.p[0], (const uint16_t*) w.p[1],
            (const uint16_t*) w.p[2], K, R, x, xs, y, ys, T, add);
 }
 
@@ -536,16 +573,18 @@ bool launch_q4_mv(cudaStream_t s, const WSlice& w, int K, int R, const float* x,
     }
     const size_t budget = (size_t) max_smem_optin() - 1024;
     if (aligned16(w.p[0]) && (K == 1024 || K == 2048 || K == 4096)) {      // K split over the block's warps
-        const int warps = K / 256, nst = warps == 16 ? 3 : 6;      // stages per warp: what fits beside 16 warps' rings
-        const size_t total = smem + (size_t) 2 * warps * 512 + (size_t) warps * nst * Q4Ring<4>::STAGE;
-        if (total <= budget) {
-            const int blocks = tiles < sm_count() ? tiles : sm_count();
-            if (warps == 4) launch_q4_ksplit<4, 6>(s, total, blocks, w, K, R, x, xs, y, ys, T, add);
-            else if (warps == 8) launch_q4_ksplit<8, 6>(s, total, blocks, w, K, R, x, xs, y, ys, T, add);
-            else launch_q4_ksplit<16, 3>(s, total, blocks, w, K, R, x, xs, y, ys, T, add);
-            count_launch();
-            return true;
-        }
+        // 16 warps an SM in blocks of K / 256 warps, four stages per warp in the place of the staged inputs: with two
+        // blocks an SM one block's barrier per tile overlaps the other's work (151936 x 2048: 51.9 us with one block of
+        // 8 warps and 6 stages, 49.2 us with two blocks of 4 stages)
+        const int warps = K / 256, bps = 16 / warps;
+        const size_t rings = (size_t) warps * 4 * Q4Ring<4>::STAGE;
+        const size_t total = (size_t) 2 * warps * 512 + (rings > smem ? rings : smem);
+        const int blocks = tiles < bps * sm_count() ? tiles : bps * sm_count();
+        if (warps == 4) launch_q4_ksplit<4, 4, 4>(s, total, blocks, w, K, R, x, xs, y, ys, T, add);
+        else if (warps == 8) launch_q4_ksplit<8, 4, 2>(s, total, blocks, w, K, R, x, xs, y, ys, T, add);
+        else launch_q4_ksplit<16, 4, 1>(s, total, blocks, w, K, R, x, xs, y, ys, T, add);
+        count_launch();
+        return true;
     }
     if (K % 512 == 0 && aligned16(w.p[0]) && smem + (size_t) 8 * 2 * Q4Ring<8>::STAGE <= budget) {      // streams through shared memory
         // 8 warps with three passes of eight groups in flight each (measured faster than 16 warps with three passes of four:

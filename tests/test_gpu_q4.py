@@ -23,7 +23,7 @@ def bf16v(a):
     return (B.f2bf(np.asarray(a, np.float32)).astype(np.uint32) << 16).view(np.float32)
 
 
-@pytest.mark.parametrize("R,K", [(24, 256), (24, 512), (24, 4096), (37, 2048), (1000, 64), (16, 8192)])
+@pytest.mark.parametrize("R,K", [(24, 256), (24, 512), (24, 4096), (37, 2048), (1000, 64), (16, 8192), (40, 1024), (5000, 1024), (5000, 2048), (2400, 4096)])
 def test_q4_dense_tokens_add_and_batch_invariance(R, K):
     from nanoseedlm_b200 import kernels
     codes, scales, biases = q4_weights(R, K, R + K)
