@@ -341,6 +341,7 @@ def measure_layer(c, M, K, W, sample_clocks=True, with_e2e=True, dependent_launc
     perm = torch.zeros(P, dtype=torch.int32, device="cuda")
     tiles = torch.zeros((P // 128 + E + 1) * 4, dtype=torch.int32, device="cuda")
     work = torch.zeros(2 * E + 3, dtype=torch.int32, device="cuda")
+    xp = torch.zeros(M * D, dtype=torch.int16, device="cuda")
     with torch.cuda.stream(stream):
         evs = []
         KR = min(K, 400)
@@ -349,11 +350,12 @@ def measure_layer(c, M, K, W, sample_clocks=True, with_e2e=True, dependent_launc
             if M > 8:
                 lib.nsl_route(stream.cuda_stream, E, TOPK, dl[b].data_ptr(), E, ind.data_ptr(), wt.data_ptr(), M)
                 lib.kc_bucket(stream.cuda_stream, ind.data_ptr(), P, E, perm.data_ptr(), tiles.data_ptr(), work.data_ptr())
+                lib.kc_pack_input_bf16(stream.cuda_stream, dx[b].data_ptr(), xp.data_ptr(), M * D)
             a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a0.record(stream)
-            if M > 8:
-                lib.kc_mm_grouped_dev(stream.cuda_stream, L.MF_SEED4P4, lay.gate.table.data_ptr(), D, FF, dx[b].data_ptr(), D,
-                                      A.data_ptr(), FF, TOPK, perm.data_ptr(), tiles.data_ptr(), work.data_ptr(), P // 128 + E, G.data_ptr())
+            if M > 8:      # as the layer launches it: the rows packed to bf16 beforehand
+                lib.kc_mm_grouped_packed(stream.cuda_stream, L.MF_SEED4P4, lay.gate.table.data_ptr(), D, FF, xp.data_ptr(), D,
+                                         A.data_ptr(), FF, TOPK, perm.data_ptr(), tiles.data_ptr(), work.data_ptr(), P // 128 + E, G.data_ptr())
             else:
                 lib.nsl_mv_gu_routed(stream.cuda_stream, lay.gate.table.data_ptr(), lay.up.table.data_ptr(), D, FF, dx[b].data_ptr(), D,
                                      A.data_ptr(), FF, E, TOPK, dl[b].data_ptr(), E, M, ind.data_ptr(), wt.data_ptr(), 0, G.data_ptr())

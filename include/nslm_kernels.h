@@ -200,6 +200,9 @@ void kc_cache_copy(cudaStream_t s, const CachePool* p, int blocks);
  * the array, which keeps the last call's offsets: calls that overlap on the GPU (two streams) race. */
 void nsl_bucket_noalloc(cudaStream_t s, const int32_t* inds, int count, int n, int32_t* perm, MmTile* tiles,
                         int32_t* ntiles_out);
+/* kc_swiglu with the results stored as packed bf16 (they are bf16 values): the input form of kc_mm_grouped_packed for
+ * the down projection.  n even. */
+void nsl_swiglu_packed(cudaStream_t s, const float* g, const float* u, uint16_t* a, int n);
 /* The router with its two sizes passed directly. */
 void nsl_route(cudaStream_t s, int n_exp, int top_k, const float* logits, int ld, int32_t* ind, float* wt, int T);
 /* Mat-vec with the f32 accumulator stored unrounded (the CPU seed path's result convention,

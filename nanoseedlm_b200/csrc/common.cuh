@@ -21,6 +21,7 @@ inline bool aligned16(const void* p) { return ((uintptr_t) p & 15u) == 0; }
 // launch() calls grid_dependency_wait() before it reads or writes anything a neighbouring kernel touches; without the
 // scope the launch is an ordinary one and the wait returns at once.
 extern thread_local bool tl_pdl;
+extern thread_local bool tl_mm_overlap;   // seed_gemm.cu: the next GEMM launch is independent of its predecessor in the stream
 struct PdlScope {
     bool prev;
     explicit PdlScope(bool on) : prev(tl_pdl) { tl_pdl = on; }

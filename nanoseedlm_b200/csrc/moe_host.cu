@@ -16,6 +16,7 @@ struct NslMoe {
     const WSlice *wg, *wu, *wd;   // device tables [n_exp]
     const uint32_t* G;            // device stream table
     float *x, *logits, *wt, *A, *Dx, *Gb, *out;
+    uint16_t *xp, *Ap;            // prompt path: the rows and the SwiGLU results as packed bf16 (the GEMMs' input form)
     int32_t *ind, *perm, *ntiles;
     MmTile* tiles;
     float *hx, *hlogits, *hout;   // pinned staging for the host-buffer entry point
@@ -56,6 +57,8 @@ NslMoe* nsl_moe_create(int d, int ff, int n_exp, int top_k, int max_tokens, cons
     m->out = (float*) dalloc(T * d * 4);
     const bool big = max_tokens > MV_MAXT;
     m->Gb = big ? (float*) dalloc(P * ff * 4) : NULL;
+    m->xp = big ? (uint16_t*) dalloc(T * d * 2) : NULL;
+    m->Ap = big ? (uint16_t*) dalloc(P * ff * 2) : NULL;
     m->perm = (int32_t*) dalloc(P * 4);
     m->tiles = (MmTile*) dalloc((P / MMT_BN + n_exp + 1) * sizeof(MmTile));
     m->ntiles = (int32_t*) dalloc((2 * (size_t) n_exp + 3) * 4);
@@ -66,7 +69,7 @@ NslMoe* nsl_moe_create(int d, int ff, int n_exp, int top_k, int max_tokens, cons
     cudaHostAlloc((void**) &m->hind, P * 4, cudaHostAllocDefault);
     cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking);
     if (!m->x || !m->logits || !m->wt || !m->ind || !m->A || !m->Dx || !m->out || !m->perm || !m->tiles || !m->ntiles ||
-        !m->hx || !m->hlogits || !m->hout || !m->hind || !m->stream || (big && !m->Gb)) {
+        !m->hx || !m->hlogits || !m->hout || !m->hind || !m->stream || (big && (!m->Gb || !m->xp || !m->Ap))) {
         nsl::set_error("nsl_moe_create: out of memory");
         nsl_moe_destroy(m);      // frees whatever was obtained
         return NULL;
@@ -82,7 +85,7 @@ void nsl_moe_set_direct_output(NslMoe* m, int on) { m->direct_out = on != 0; }
 
 void nsl_moe_destroy(NslMoe* m) {
     if (!m) return;
-    void* dv[] = {m->x, m->wt, m->ind, m->A, m->Dx, m->out, m->Gb, m->perm, m->tiles, m->ntiles};
+    void* dv[] = {m->x, m->wt, m->ind, m->A, m->Dx, m->out, m->Gb, m->xp, m->Ap, m->perm, m->tiles, m->ntiles};
     for (void* p : dv) if (p) cudaFree(p);
     void* hv[] = {m->hx, m->hout, m->hind};
     for (void* p : hv) if (p) cudaFreeHost(p);
@@ -99,10 +102,17 @@ int nsl_moe_forward_dev(NslMoe* m, cudaStream_t s, const float* x, const float* 
         const int mt = P / MMT_BN + m->n_exp;
         nsl_route(s, m->n_exp, k, logits, m->n_exp, m->ind, m->wt, T);
         kc_bucket(s, m->ind, P, m->n_exp, m->perm, m->tiles, m->ntiles);
-        kc_mm_grouped_dev(s, MF_SEED4P4, m->wg, d, ff, x, d, m->Gb, ff, k, m->perm, m->tiles, m->ntiles, mt, m->G);
-        kc_mm_grouped_dev(s, MF_SEED4P4, m->wu, d, ff, x, d, m->A, ff, k, m->perm, m->tiles, m->ntiles, mt, m->G);
-        kc_swiglu(s, m->Gb, m->A, m->A, P * ff);      // in place over the up projection (SwiGLU in the up GEMM's epilogue measured 27 us slower a layer)
-        kc_mm_grouped_dev(s, MF_SEED4P4, m->wd, ff, d, m->A, ff, m->Dx, d, 1, m->perm, m->tiles, m->ntiles, mt, m->G);
+        // The rows are packed to bf16 once (every row tile of every expert reads them), the up projection is launched as
+        // a dependent of the gate projection it does not depend on (its blocks fill the gate grid's last wave), and the
+        // SwiGLU results (bf16 values) go to the down projection packed.  (SwiGLU in the up GEMM's epilogue measured
+        // 27 us slower a layer.)
+        kc_pack_input_bf16(s, x, m->xp, (size_t) T * d);
+        kc_mm_grouped_packed(s, MF_SEED4P4, m->wg, d, ff, m->xp, d, m->Gb, ff, k, m->perm, m->tiles, m->ntiles, mt, m->G);
+        nsl::tl_mm_overlap = true;
+        kc_mm_grouped_packed(s, MF_SEED4P4, m->wu, d, ff, m->xp, d, m->A, ff, k, m->perm, m->tiles, m->ntiles, mt, m->G);
+        nsl::tl_mm_overlap = false;
+        nsl_swiglu_packed(s, m->Gb, m->A, m->Ap, P * ff);
+        kc_mm_grouped_packed(s, MF_SEED4P4, m->wd, ff, d, m->Ap, ff, m->Dx, d, 1, m->perm, m->tiles, m->ntiles, mt, m->G);
         kq4_moe_combine(s, d, k, m->Dx, m->wt, NULL, NULL, 0, out, T);
         return 0;
     }

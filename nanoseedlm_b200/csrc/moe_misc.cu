@@ -31,6 +31,15 @@ __global__ void swiglu_kernel(const float* __restrict__ g, const float* __restri
         a[i] = bf16_round(silu_bf16(g[i]) * u[i]);
 }
 
+// The same values as bf16 bits (they are bf16 values already): the packed input of the down projection's GEMM.
+__global__ void swiglu_packed_kernel(const float* __restrict__ g, const float* __restrict__ u, uint16_t* __restrict__ a, int n) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n / 2; i += gridDim.x * blockDim.x) {
+        const float2 gv = ((const float2*) g)[i], uv = ((const float2*) u)[i];
+        const uint32_t lo = __float_as_uint(bf16_round(silu_bf16(gv.x) * uv.x)) >> 16, hi = __float_as_uint(bf16_round(silu_bf16(gv.y) * uv.y)) & 0xFFFF0000u;
+        ((uint32_t*) a)[i] = lo | hi;
+    }
+}
+
 // out[t][i] = sigmoid(sg[t*sgld]) sh[t][i] + sum_j wt[t][j] D[t*k+j][i], plain f32, j ascending; sh == NULL: no shared
 // expert term.
 __global__ void q4_combine_kernel(int d, int k, const float* __restrict__ D, const float* __restrict__ wt,
@@ -371,6 +380,14 @@ void kc_swiglu(cudaStream_t s, const float* g, const float* u, float* a, int n) 
     if (n <= 0) return;
     const int blocks = (n + 255) / 256;
     swiglu_kernel<<<blocks < sm_count() * 16 ? blocks : sm_count() * 16, 256, 0, s>>>(g, u, a, n);
+    count_launch();
+}
+
+// kc_swiglu with the result as packed bf16 (n even): what kc_mm_grouped_packed reads.
+void nsl_swiglu_packed(cudaStream_t s, const float* g, const float* u, uint16_t* a, int n) {
+    if (n <= 0) return;
+    const int blocks = (n / 2 + 255) / 256;
+    swiglu_packed_kernel<<<blocks < sm_count() * 16 ? blocks : sm_count() * 16, 256, 0, s>>>(g, u, a, n);
     count_launch();
 }
 

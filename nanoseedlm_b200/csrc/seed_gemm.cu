@@ -132,6 +132,9 @@ __device__ __forceinline__ QuadIn load_quad(const WSlice& w, int row, int kb, in
 template <int NT, int WF, bool VEC>
 __global__ void __launch_bounds__(GM_THREADS, 2) seed_gemm_kernel(MmParams a, KConst kc) {
     constexpr bool BF16W = WF == 1, P3 = WF == 2;
+    // A launch that follows this one and does not depend on it (the up projection after the gate projection) may be made
+    // a programmatic dependent launch: its blocks then fill the SMs this grid's last wave leaves idle.
+    grid_dependents_go();
     if (a.ntiles && (int) blockIdx.y >= *a.ntiles) return;
     extern __shared__ uint8_t smem_raw[];
     __shared__ StreamTab tab;
@@ -204,6 +207,21 @@ __global__ void __launch_bounds__(GM_THREADS, 2) seed_gemm_kernel(MmParams a, KC
         if (BF16W) load_bf16(0, bcur);
         else cur = load_quad<P3>(w, grow, half * 4, a.R, NB, vec);
         nxt = cur;
+        // packed inputs: this thread's 16-byte chunks of the K step's n_eff x 64 tile (chunk ci = tid + 256 i), requested one
+        // K step ahead so that they land during the expansion
+        uint4 xq[4];
+        auto load_x = [&](int kt) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int ci = tid + i * GM_PRODUCERS;
+                xq[i] = make_uint4(0u, 0u, 0u, 0u);
+                if (ci < n_eff * 8) {
+                    const int src = srow[ci >> 3], k = kt * GM_BK + 8 * (ci & 7);
+                    if (src >= 0 && k < a.K) xq[i] = __ldg((const uint4*) ((const uint16_t*) a.X + (size_t) src * a.xs + k));
+                }
+            }
+        };
+        if (a.packed) load_x(0);
         bool live = true;
         for (int kt = 0; kt < KT && live; ++kt) {
             const int s = kt % GM_STAGES;
@@ -224,6 +242,15 @@ __global__ void __launch_bounds__(GM_THREADS, 2) seed_gemm_kernel(MmParams a, KC
                     const int chunk = half * 4 + i;
                     *(uint4*) (stage + (uint32_t) prow * 128u + (uint32_t) ((chunk ^ (prow & 7)) << 4)) = bcur[i];
                 }
+            }
+            if (a.packed) {      // this K step's inputs (requested a step ago), then the next step's request
+                uint8_t* bt = stage + (size_t) NT * GM_TILE_BYTES;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int ci = tid + i * GM_PRODUCERS, n = ci >> 3, chunk = ci & 7;
+                    if (ci < n_eff * 8) *(uint4*) (bt + (uint32_t) n * 128u + (uint32_t) ((chunk ^ (n & 7)) << 4)) = xq[i];
+                }
+                if (kt + 1 < KT) load_x(kt + 1);
             }
             // seed weights: two block pairs, expanded side by side
 #pragma unroll
@@ -274,20 +301,17 @@ __global__ void __launch_bounds__(GM_THREADS, 2) seed_gemm_kernel(MmParams a, KC
                     }
                 }
             }
-            // inputs: the n_eff x 64 tile as 16-byte chunks (8 values) dealt round-robin to the producer threads
-            {
+            // f32 inputs: the n_eff x 64 tile as 16-byte chunks (8 values) dealt round-robin to the producer threads
+            if (!a.packed) {
                 uint8_t* bt = stage + (size_t) NT * GM_TILE_BYTES;
                 for (int ci = tid; ci < n_eff * 8; ci += GM_PRODUCERS) {
                     const int n = ci >> 3, chunk = ci & 7, src = srow[n], k = kt * GM_BK + 8 * chunk;
                     uint4 o = make_uint4(0u, 0u, 0u, 0u);
                     if (src >= 0 && k < a.K) {
-                        if (a.packed) o = __ldg((const uint4*) ((const uint16_t*) a.X + (size_t) src * a.xs + k));
-                        else {
-                            const float4* xp = (const float4*) ((const float*) a.X + (size_t) src * a.xs + k);
-                            const float4 x0 = __ldg(xp), x1 = __ldg(xp + 1);
-                            o = make_uint4(bf16x2_bits(x0.x, x0.y), bf16x2_bits(x0.z, x0.w), bf16x2_bits(x1.x, x1.y),
-                                           bf16x2_bits(x1.z, x1.w));
-                        }
+                        const float4* xp = (const float4*) ((const float*) a.X + (size_t) src * a.xs + k);
+                        const float4 x0 = __ldg(xp), x1 = __ldg(xp + 1);
+                        o = make_uint4(bf16x2_bits(x0.x, x0.y), bf16x2_bits(x0.z, x0.w), bf16x2_bits(x1.x, x1.y),
+                                       bf16x2_bits(x1.z, x1.w));
                     }
                     *(uint4*) (bt + (uint32_t) n * 128u + (uint32_t) ((chunk ^ (n & 7)) << 4)) = o;
                 }
@@ -356,6 +380,8 @@ __global__ void __launch_bounds__(GM_THREADS, 2) seed_gemm_kernel(MmParams a, KC
 
 bool launch_bf16_mm_skinny(cudaStream_t s, const WSlice& w, int K, int R, const float* x, int xs, float* y, int ys, int T, int add);
 
+thread_local bool tl_mm_overlap = false;
+
 static int g_exact;   // kc_seed_gemm_f32: process-wide, as the reference's switch (engine/kernels_moe.cu:2354)
 
 template <int NT, int WF, bool VEC>
@@ -368,7 +394,9 @@ static void launch_gemm_v(cudaStream_t s, const MmParams& a, dim3 grid) {
         cudaFuncSetAttribute(seed_gemm_kernel<NT, WF, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
         attr_set[dev & 15] = true;
     }
-    seed_gemm_kernel<NT, WF, VEC><<<grid, GM_THREADS, smem, s>>>(a, kconst());
+    // tl_mm_overlap: the caller says this launch reads nothing its predecessor in the stream writes
+    PdlScope pdl(tl_mm_overlap);
+    launch(seed_gemm_kernel<NT, WF, VEC>, grid, GM_THREADS, smem, s, a, kconst());
     count_launch();
 }
 template <int NT, int WF>

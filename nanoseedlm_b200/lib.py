@@ -102,6 +102,7 @@ PROTOTYPES = {
     "kc_cache_copy": (None, [_vp, C.POINTER(CachePool), _i]),
     "nsl_bucket_noalloc": (None, [_vp, _vp, _i, _i, _vp, _vp, _vp]),
     "nsl_route": (None, [_vp, _i, _i, _vp, _i, _vp, _vp, _i]),
+    "nsl_swiglu_packed": (None, [_vp, _vp, _vp, _vp, _i]),
     "nsl_mv_raw": (None, [_vp, _vp, _i, _i, _vp, _i, _vp, _i, _vp, _i, _i, _vp]),
     "nsl_mv_gu_raw": (None, [_vp, _vp, _vp, _i, _i, _vp, _i, _vp, _i, _vp, _i, _i, _vp]),
     "nsl_decode_f32": (None, [_vp, WSlice, _i, _i, _vp, _vp]),

@@ -63,6 +63,19 @@ def test_swiglu_and_combines(oracle):
     assert np.max(np.abs(got.reshape(T, d) - ref)) <= np.max(np.abs(ref)) / 64
 
 
+def test_swiglu_packed_is_swiglu_as_bf16_bits(oracle):
+    import torch
+    from nanoseedlm_b200 import kernels, lib as L
+    n = 6002
+    g, u = oracle.normal(11, n, bf16=True) * 3, oracle.normal(12, n, bf16=True)
+    gd, ud = kernels.dev(g), kernels.dev(u)
+    out = torch.zeros(n, dtype=torch.int16, device="cuda")
+    L.load().nsl_swiglu_packed(None, gd.data_ptr(), ud.data_ptr(), out.data_ptr(), n)
+    torch.cuda.synchronize()
+    want = (oracle.swiglu(g, u).view(np.uint32) >> 16).astype(np.uint16)
+    assert np.array_equal(out.cpu().numpy().view(np.uint16), want)
+
+
 def test_pack_input_bf16_any_length(oracle):
     """Round to nearest even, every element of any n (the reference's kernel packs whole groups of 8: engine/kernels_moe.cu:2196-2201)."""
     from nanoseedlm_b200 import kernels
