@@ -175,7 +175,7 @@ __global__ void __launch_bounds__(GM_THREADS, 2) seed_gemm_kernel(MmParams a, KC
     if (tid == 0) {
         abort_flag = 0;
         for (int s = 0; s < GM_STAGES; ++s) {
-            mbar_init(bar_full + 8 * s, GM_PRODUCERS);
+            mbar_init(bar_full + 8 * s, GM_PRODUCERS / 32);      // one arrival per producer warp
             mbar_init(bar_empty + 8 * s, 1);
         }
         mbar_init(bar_done, 1);
@@ -210,12 +210,13 @@ __global__ void __launch_bounds__(GM_THREADS, 2) seed_gemm_kernel(MmParams a, KC
         // packed inputs: this thread's 16-byte chunks of the K step's n_eff x 64 tile (chunk ci = tid + 256 i), requested one
         // K step ahead so that they land during the expansion
         uint4 xq[4];
+        const int nx = (n_eff * 8 + GM_PRODUCERS - 1) / GM_PRODUCERS;      // chunks per thread: 1 for tiles of up to 32 pairs
         auto load_x = [&](int kt) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int ci = tid + i * GM_PRODUCERS;
-                xq[i] = make_uint4(0u, 0u, 0u, 0u);
-                if (ci < n_eff * 8) {
+                if (i < nx) xq[i] = make_uint4(0u, 0u, 0u, 0u);
+                if (i < nx && ci < n_eff * 8) {
                     const int src = srow[ci >> 3], k = kt * GM_BK + 8 * (ci & 7);
                     if (src >= 0 && k < a.K) xq[i] = __ldg((const uint4*) ((const uint16_t*) a.X + (size_t) src * a.xs + k));
                 }
@@ -248,7 +249,7 @@ __global__ void __launch_bounds__(GM_THREADS, 2) seed_gemm_kernel(MmParams a, KC
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const int ci = tid + i * GM_PRODUCERS, n = ci >> 3, chunk = ci & 7;
-                    if (ci < n_eff * 8) *(uint4*) (bt + (uint32_t) n * 128u + (uint32_t) ((chunk ^ (n & 7)) << 4)) = xq[i];
+                    if (i < nx && ci < n_eff * 8) *(uint4*) (bt + (uint32_t) n * 128u + (uint32_t) ((chunk ^ (n & 7)) << 4)) = xq[i];
                 }
                 if (kt + 1 < KT) load_x(kt + 1);
             }
@@ -317,7 +318,8 @@ __global__ void __launch_bounds__(GM_THREADS, 2) seed_gemm_kernel(MmParams a, KC
                 }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the MMA's reads
-            mbar_arrive(bar_full + 8 * s);
+            __syncwarp();                                                  // the warp's 32 lanes have written and fenced:
+            if (lane == 0) mbar_arrive(bar_full + 8 * s);                  // one arrival for all of them (not 32 on one word)
             cur = nxt;
             if (BF16W) {
 #pragma unroll
