@@ -227,7 +227,24 @@ __global__ void __launch_bounds__(GM_THREADS, 2) seed_gemm_kernel(MmParams a, KC
                 }
             }
         };
-        if (a.packed) load_x(0);
+        // f32 inputs: the thread's first two chunks (tiles of up to 64 pairs whole) travel the same way as raw values, two
+        // float4 a chunk in the same registers (xq[2 c], xq[2 c + 1]); further chunks are loaded and converted in place
+        auto load_xf = [&](int kt) {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const int ci = tid + c * GM_PRODUCERS;
+                xq[2 * c] = xq[2 * c + 1] = make_uint4(0u, 0u, 0u, 0u);
+                if (c < nx && ci < n_eff * 8) {
+                    const int src = srow[ci >> 3], k = kt * GM_BK + 8 * (ci & 7);
+                    if (src >= 0 && k < a.K) {
+                        const uint4* xp = (const uint4*) ((const float*) a.X + (size_t) src * a.xs + k);
+                        xq[2 * c] = __ldg(xp);
+                        xq[2 * c + 1] = __ldg(xp + 1);
+                    }
+                }
+            }
+        };
+        if (a.packed) load_x(0); else load_xf(0);
         bool live = true;
         for (int kt = 0; kt < KT && live; ++kt) {
             const int s = kt % GM_STAGES;
@@ -257,6 +274,19 @@ __global__ void __launch_bounds__(GM_THREADS, 2) seed_gemm_kernel(MmParams a, KC
                     if (i < nx && ci < n_eff * 8) *(uint4*) (bt + (uint32_t) n * 128u + (uint32_t) ((chunk ^ (n & 7)) << 4)) = xq[i];
                 }
                 if (kt + 1 < KT) load_x(kt + 1);
+            } else {
+                uint8_t* bt = stage + (size_t) NT * GM_TILE_BYTES;
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const int ci = tid + c * GM_PRODUCERS, n = ci >> 3, chunk = ci & 7;
+                    if (c < nx && ci < n_eff * 8) {
+                        const uint4 lo = xq[2 * c], hi = xq[2 * c + 1];
+                        *(uint4*) (bt + (uint32_t) n * 128u + (uint32_t) ((chunk ^ (n & 7)) << 4)) =
+                            make_uint4(bf16x2_bits(__uint_as_float(lo.x), __uint_as_float(lo.y)), bf16x2_bits(__uint_as_float(lo.z), __uint_as_float(lo.w)),
+                                       bf16x2_bits(__uint_as_float(hi.x), __uint_as_float(hi.y)), bf16x2_bits(__uint_as_float(hi.z), __uint_as_float(hi.w)));
+                    }
+                }
+                if (kt + 1 < KT) load_xf(kt + 1);
             }
             // seed weights: two block pairs, expanded side by side
 #pragma unroll
@@ -310,7 +340,7 @@ __global__ void __launch_bounds__(GM_THREADS, 2) seed_gemm_kernel(MmParams a, KC
             // f32 inputs: the n_eff x 64 tile as 16-byte chunks (8 values) dealt round-robin to the producer threads
             if (!a.packed) {
                 uint8_t* bt = stage + (size_t) NT * GM_TILE_BYTES;
-                for (int ci = tid; ci < n_eff * 8; ci += GM_PRODUCERS) {
+                for (int ci = tid + 2 * GM_PRODUCERS; ci < n_eff * 8; ci += GM_PRODUCERS) {      // chunks beyond the two that were requested ahead
                     const int n = ci >> 3, chunk = ci & 7, src = srow[n], k = kt * GM_BK + 8 * chunk;
                     uint4 o = make_uint4(0u, 0u, 0u, 0u);
                     if (src >= 0 && k < a.K) {
