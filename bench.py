@@ -281,6 +281,9 @@ class Cfg1:
         return hx, hl, distinct
 
 
+ONE_LAUNCH = False     # --one-launch: the decode step as the one fused launch (nsl_mv_step) instead of three dependent launches
+
+
 def measure_layer(c, M, K, W, sample_clocks=True, with_e2e=True, dependent_launch=True):
     """Config 1 (M <= 8) or config 2 (M = 512) on one GPU: tokens/s of whole steps (CUDA graph of `chunk` steps replayed),
     the dominant kernel timed launch by launch, and the end-to-end forms."""
@@ -291,6 +294,7 @@ def measure_layer(c, M, K, W, sample_clocks=True, with_e2e=True, dependent_launc
     dout = torch.zeros(M, D, device="cuda")
     m = c.moe.Moe(layers[0], TOPK, M)
     m.set_dependent_launch(dependent_launch)
+    m.set_one_launch(ONE_LAUNCH)
     res = {"tokens": M}
 
     def enqueue(step, s):
@@ -409,6 +413,7 @@ def measure_layer(c, M, K, W, sample_clocks=True, with_e2e=True, dependent_launc
         # layer L), so it is reported beside the headline, not as it.
         m2 = c.moe.Moe(layers[0], TOPK, M)
         m2.set_dependent_launch(dependent_launch)
+        m2.set_one_launch(ONE_LAUNCH)
         ms, checksum = (m, m2), 0.0
 
         def submit(i):
@@ -1064,6 +1069,7 @@ def main():
     ap.add_argument("--c4-batch", type=int, default=0, help="config 4: sequences per step (32 = the configuration; fewer only for profiling "
                                                              "one rank's dense and attention sizes on one GPU)")
     ap.add_argument("--c4-layers", type=int, default=48, help="config 4: decoder layers (48 = the configuration; fewer only for profiling)")
+    ap.add_argument("--one-launch", action="store_true", help="config 1: the decode step as one fused launch instead of three dependent launches")
     ap.add_argument("--no-dependent-launch", action="store_true",
                     help="config 1: ordinary launches instead of programmatic dependent launches (for comparison)")
     ap.add_argument("--ep-collectives", default="p2p", choices=["p2p", "a2a", "gather"],
@@ -1079,6 +1085,8 @@ def main():
                     help="one workload alone as the line (profiling): cfg1 one GPU's MoE decode layer; cfg2 the same layer on 512 "
                          "prompt rows (grouped tcgen05 GEMM); cfg3 expert-parallel decode (the default at >1 GPU); cfg0 / lmhead / attn")
     args = ap.parse_args()
+    global ONE_LAUNCH
+    ONE_LAUNCH = args.one_launch
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     if args.impl == "reference":

@@ -200,6 +200,17 @@ void kc_cache_copy(cudaStream_t s, const CachePool* p, int blocks);
  * the array, which keeps the last call's offsets: calls that overlap on the GPU (two streams) race. */
 void nsl_bucket_noalloc(cudaStream_t s, const int32_t* inds, int count, int n, int32_t* perm, MmTile* tiles,
                         int32_t* ntiles_out);
+/* The whole decode step of an expert layer -- router, gate + up + SwiGLU, down projection, weighted combine (the four
+ * launches of engine/qwen4_cuda.c:1033-1078) -- as ONE launch whose blocks pass from phase to phase and wait on counters
+ * for what other blocks produce (every wait bounded).  Results are bit for bit those of nsl_mv_gu_routed + kc_mv_sel +
+ * kq4_moe_combine.  Measured slower than those three as dependent launches (config 1, 8 rows: 126.3 against 114.2 us a
+ * step): the dependent launches already hide ramp and prologue, and a block here waits for its neighbours at each phase
+ * change.  Returns 1 = launched; 0 = a size is outside what it serves (T <= MV_MAXT rows, d and ff = 64 * 2^j <=
+ * 2048, aligned rows) and nothing was launched.  sync: 4 * (2 + T + T * top_k) bytes of device memory, zero before the
+ * first call; every call leaves its counters zero; sync[0] = 1 after a launch in which a wait ran out (output not valid). */
+int nsl_mv_step(cudaStream_t s, const WSlice* wg, const WSlice* wu, const WSlice* wd, int d, int ff, const float* x, int xs,
+                int n_exp, int top_k, const float* logits, int ld, int T, int32_t* ind, float* wt, float* A, float* D,
+                float* out, int raw, unsigned* sync, const uint32_t* G);
 /* kc_swiglu with the results stored as packed bf16 (they are bf16 values): the input form of kc_mm_grouped_packed for
  * the down projection.  n even. */
 void nsl_swiglu_packed(cudaStream_t s, const float* g, const float* u, uint16_t* a, int n);

@@ -26,6 +26,8 @@ struct NslMoe {
     int raw;                      // 1: no bf16 rounding points on the mat-vec path
     int pdl;                      // 1 (default): the decode path's kernels are programmatic dependent launches
     int direct_out;               // 1 (default): the pinned forms' combine kernel stores the result straight into pinned host memory
+    int one_launch;               // 1: a decode step whose sizes the fused kernel serves is ONE launch (nsl_mv_step); default 0: it measured slower
+    unsigned* step_sync;          // its counters and status word (zero between launches)
 };
 
 static void* dalloc(size_t n) {
@@ -65,11 +67,14 @@ NslMoe* nsl_moe_create(int d, int ff, int n_exp, int top_k, int max_tokens, cons
     cudaHostAlloc((void**) &m->hx, T * d * 4 + T * n_exp * 4, cudaHostAllocDefault);      // the same layout in pinned memory
     m->hlogits = m->hx ? m->hx + T * d : NULL;
     m->direct_out = 1;
+    m->one_launch = 0;
+    m->step_sync = (unsigned*) dalloc(4 * ((size_t) MV_MAXT * top_k + MV_MAXT + 2));
+    if (m->step_sync) cudaMemset(m->step_sync, 0, 4 * ((size_t) MV_MAXT * top_k + MV_MAXT + 2));
     cudaHostAlloc((void**) &m->hout, T * d * 4, cudaHostAllocDefault);
     cudaHostAlloc((void**) &m->hind, P * 4, cudaHostAllocDefault);
     cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking);
     if (!m->x || !m->logits || !m->wt || !m->ind || !m->A || !m->Dx || !m->out || !m->perm || !m->tiles || !m->ntiles ||
-        !m->hx || !m->hlogits || !m->hout || !m->hind || !m->stream || (big && (!m->Gb || !m->xp || !m->Ap))) {
+        !m->hx || !m->hlogits || !m->hout || !m->hind || !m->stream || (big && (!m->Gb || !m->xp || !m->Ap)) || !m->step_sync) {
         nsl::set_error("nsl_moe_create: out of memory");
         nsl_moe_destroy(m);      // frees whatever was obtained
         return NULL;
@@ -82,10 +87,20 @@ void nsl_moe_set_grouped_min_tokens(NslMoe* m, int t) { m->grouped_min_tokens = 
 void nsl_moe_set_rounding(NslMoe* m, int bf16_points) { m->raw = !bf16_points; }
 void nsl_moe_set_dependent_launch(NslMoe* m, int on) { m->pdl = on != 0; }
 void nsl_moe_set_direct_output(NslMoe* m, int on) { m->direct_out = on != 0; }
+void nsl_moe_set_one_launch(NslMoe* m, int on) { m->one_launch = on != 0; }
+
+// 0, or 1 when a wait inside a one-launch decode step ran out since the last call (the step's output is then not valid).
+// Reads device memory: call it after the layer's work has been waited for.
+int nsl_moe_step_status(NslMoe* m) {
+    int v = 0;
+    if (cudaMemcpy(&v, m->step_sync, 4, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (v) cudaMemset(m->step_sync, 0, 4);
+    return v;
+}
 
 void nsl_moe_destroy(NslMoe* m) {
     if (!m) return;
-    void* dv[] = {m->x, m->wt, m->ind, m->A, m->Dx, m->out, m->Gb, m->xp, m->Ap, m->perm, m->tiles, m->ntiles};
+    void* dv[] = {m->x, m->wt, m->ind, m->A, m->Dx, m->out, m->Gb, m->xp, m->Ap, m->perm, m->tiles, m->ntiles, m->step_sync};
     for (void* p : dv) if (p) cudaFree(p);
     void* hv[] = {m->hx, m->hout, m->hind};
     for (void* p : hv) if (p) cudaFreeHost(p);
@@ -121,6 +136,11 @@ int nsl_moe_forward_dev(NslMoe* m, cudaStream_t s, const float* x, const float* 
     // before touching anything a neighbour writes)
     nsl::PdlScope pdl(m->pdl);
     const bool fused = T <= MV_MAXT && d % 64 == 0 && d <= 2048 && (d & (d - 1)) == 0;
+    // on request, one launch for the whole step where the fused kernel serves the sizes (measured slower than the three
+    // dependent launches: 126.3 against 114.2 us at 8 rows, 70.1 / 65.5 at 4, 26.7 / 26.2 at 1)
+    if (fused && m->one_launch &&
+        nsl_mv_step(s, m->wg, m->wu, m->wd, d, ff, x, d, m->n_exp, k, logits, m->n_exp, T, m->ind, m->wt, m->A, m->Dx, out, m->raw, m->step_sync, m->G))
+        return 0;
     if (fused) nsl_mv_gu_routed(s, m->wg, m->wu, d, ff, x, d, m->A, ff, m->n_exp, k, logits, m->n_exp, T, m->ind, m->wt, m->raw, m->G);
     else {
         nsl_route(s, m->n_exp, k, logits, m->n_exp, m->ind, m->wt, T);

@@ -341,6 +341,241 @@ __global__ void __launch_bounds__(MV_THREADS, 2) mv_pair_kernel(MvParams a, KCon
 }
 
 
+// ---- the whole decode step of an expert layer in one launch -----------------------------------------------------------------
+// Router, gate + up + SwiGLU, down projection and weighted combine as three phases of one grid of two blocks an SM, instead
+// of three dependent launches: a launch boundary costs the step its predecessor's tail (the last blocks' row steps with
+// the other SMs idle), the successor's ramp and the prologue (stream table, router) again, ~4 us each on a step of
+// 26 .. 114 us.  Here a block that has finished its share of a phase starts on the next one at once; what it needs from
+// other blocks it waits for on counters in device memory:
+//   ready[p]  row steps of pair p's gate + up rows stored           (the down projection of pair p reads all of them)
+//   done[t]   row steps of token t's down projections stored        (the combine of token t reads all top_k of them)
+// Each phase is the pair kernel's: the pair-major sequence of row steps cut into contiguous equal shares, so block b
+// works on the same pairs in phases 1 and 2 and waits for its neighbours b - 1 and b + 1 at most; blocks are dispatched
+// in index order and no block waits for a higher-numbered block other than b + 1 before it has finished phase 2, so the
+// grid makes progress even when not all of it is resident.  Every wait is bounded: when one runs out the block records
+// status 1, every other wait ends on seeing it, and the launch returns with its counters cleared (the last block to
+// finish clears them for the next launch; fin counts finished blocks and wraps to zero by itself).
+// Arithmetic and rounding points are those of the three kernels it replaces, operation for operation.
+// Measured (config 1, CUDA graph replay, us per step at 8 / 4 / 1 rows): 126.3 / 70.1 / 26.7 against 114.2 / 65.5 / 26.2
+// for the three dependent launches, so the host layer does not use it by default.  Under ncu the one launch lasts what
+// the three last back to back (130.5 against 129.2 us; the same 75.0 M instructions and 217 k active cycles an SM); what
+// the dependent launches hide between steps -- the next kernel's blocks resident with table, router and first streams
+// ready when the wait ends -- this form cannot, and its barrier stalls are 0.78 per issued instruction against 0.10:
+// at each phase change a block waits for the slowest of the ~6 blocks that share its pairs.
+struct StepSync {
+    unsigned* ready;      // [T * top_k]
+    unsigned* done;       // [T]
+    unsigned* fin;
+    int* status;
+};
+struct StepParams {
+    const WSlice *wg, *wu, *wd;
+    const float* x;       // [T][d]
+    const float* logits;  // [T][ld]
+    float* A;             // [T * top_k][ff]
+    float* D;             // [T * top_k][d]
+    float* out;           // [T][d]
+    int32_t* ind_out;
+    float* wt_out;
+    const uint32_t* G;
+    int xs, ld, n_exp, top_k, T, d, ff, raw;
+    StepSync sy;
+};
+constexpr unsigned STEP_WAIT_LIMIT = 1u << 19;      // polls of ~0.1 us
+
+__device__ __forceinline__ unsigned ld_acquire(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// false: the limit ran out, or another block has reported that its wait did
+__device__ __forceinline__ bool step_wait(const unsigned* counter, unsigned target, int* status) {
+    for (unsigned i = 0; i < STEP_WAIT_LIMIT; ++i) {
+        if (ld_acquire(counter) >= target) return true;
+        if ((i & 63u) == 63u && *(volatile int*) status) return false;
+        __nanosleep(i < 16 ? 32 : 128);
+    }
+    atomicCAS(status, 0, 1);
+    return false;
+}
+
+// A pair's inputs from memory that other blocks of this grid have written: the loads bypass the non-coherent path.
+__device__ __forceinline__ void stage_pair_inputs_cg(const float* xrow, int j, int bp, ulonglong2* sx, ulonglong2* sm) {
+    float x[16], xm[8];
+    const float4* xp = (const float4*) (xrow + (size_t) j * 64 + bp * 16);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float4 t = __ldcg(xp + i);
+        x[4 * i] = t.x * NSL_XSCALE; x[4 * i + 1] = t.y * NSL_XSCALE; x[4 * i + 2] = t.z * NSL_XSCALE; x[4 * i + 3] = t.w * NSL_XSCALE;
+    }
+    block_offsets(x, xm);
+    block_offsets(x + 8, xm + 4);
+#pragma unroll
+    for (int cq = 0; cq < 4; ++cq) {
+        ulonglong2 t;
+        t.x = pack2(x[2 * cq], x[8 + 2 * cq]);
+        t.y = pack2(x[2 * cq + 1], x[8 + 2 * cq + 1]);
+        sx[(bp * 4 + cq) * 32 + j] = t;
+    }
+#pragma unroll
+    for (int pq = 0; pq < 2; ++pq) {
+        ulonglong2 t;
+        t.x = pack2(xm[2 * pq], xm[4 + 2 * pq]);
+        t.y = pack2(xm[2 * pq + 1], xm[4 + 2 * pq + 1]);
+        sm[(bp * 2 + pq) * 32 + j] = t;
+    }
+}
+
+struct StepShared {
+    StreamTab tab;
+    int32_t r_ind[256];
+    float r_wt[256];
+    __align__(16) ulonglong2 sx[4 * 4 * 32];
+    __align__(16) ulonglong2 sm[4 * 2 * 32];
+    int abort;
+};
+
+// One phase: MODE_GU (x -> A, signals ready[pair]) or MODE_ROUND (A -> D, waits for ready[pair], signals done[token]).
+template <int MODE>
+__device__ __forceinline__ void step_phase(const StepParams& p, const KConst& kc, StepShared& sh, int P, int lpr_log2, unsigned rs_gu) {
+    const int K = MODE == MODE_GU ? p.d : p.ff, R = MODE == MODE_GU ? p.ff : p.d;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int lpr = 1 << lpr_log2, rpw = 32 >> lpr_log2;
+    const int jc = lane & (lpr - 1), ro = lane >> lpr_log2;
+    const int rs = (R + rpw - 1) / rpw;
+    const long long total = (long long) P * rs;
+    const long long begin = (long long) blockIdx.x * total / gridDim.x, end = (long long) (blockIdx.x + 1) * total / gridDim.x;
+    if (begin >= end) return;
+    const int p_first = (int) (begin / rs), p_last = (int) ((end - 1) / rs);
+    MvParams a = {};
+    a.y = MODE == MODE_GU ? p.A : p.D;
+    a.ys = R;
+    a.R = R;
+    a.raw = p.raw;
+    for (int pair = p_first; pair <= p_last; ++pair) {
+        const int s_lo = pair == p_first ? (int) (begin - (long long) pair * rs) : 0;
+        const int s_hi = pair == p_last ? (int) (end - (long long) pair * rs) : rs;
+        const int slice = sh.r_ind[pair];
+        const WSlice wa = MODE == MODE_GU ? p.wg[slice] : p.wd[slice];
+        WSlice wb = wa;
+        if (MODE == MODE_GU) wb = p.wu[slice];
+        int st = s_lo + warp;
+        int r = st * rpw + ro;
+        Chunk ka, kb;
+        if (st < s_hi && r < R) {      // the streams do not depend on other blocks: requested before any wait
+            ka = load_chunk<4>(wa, (size_t) r * lpr + jc);
+            if (MODE == MODE_GU) kb = load_chunk<4>(wb, (size_t) r * lpr + jc);
+        }
+        if (MODE == MODE_ROUND && threadIdx.x == 0 && !step_wait(p.sy.ready + pair, rs_gu, p.sy.status)) sh.abort = 1;
+        __syncthreads();   // the previous pair's inputs are no longer read; the wait's outcome is known
+        if (sh.abort) return;
+        if (threadIdx.x < lpr * 4) {
+            const int j = threadIdx.x & (lpr - 1), bp = threadIdx.x >> lpr_log2;
+            if (MODE == MODE_GU) {
+                MvParams ax = {};
+                ax.x = p.x;
+                ax.xs = p.xs;
+                stage_pair_inputs(ax, pair / p.top_k, j, bp, sh.sx, sh.sm);
+            } else stage_pair_inputs_cg(p.A + (size_t) pair * p.ff, j, bp, sh.sx, sh.sm);
+        }
+        __syncthreads();
+        const float sca = slice_scale(wa.eb), scb = slice_scale(wb.eb);
+        for (; st < s_hi; st += MV_WARPS, r += MV_WARPS * rpw) {
+            const bool ok = r < R;
+            const int rn = r + MV_WARPS * rpw;
+            Chunk na, nb;
+            if (st + MV_WARPS < s_hi && rn < R) {
+                na = load_chunk<4>(wa, (size_t) rn * lpr + jc);
+                if (MODE == MODE_GU) nb = load_chunk<4>(wb, (size_t) rn * lpr + jc);
+            }
+            u64 acc = 0ull, accu = 0ull;
+            if (ok) {
+                const uint32_t swa[4] = {ka.s.x, ka.s.y, ka.s.z, ka.s.w}, cwa[4] = {ka.c.x, ka.c.y, ka.c.z, ka.c.w};
+                const uint32_t swb[4] = {kb.s.x, kb.s.y, kb.s.z, kb.s.w}, cwb[4] = {kb.c.x, kb.c.y, kb.c.z, kb.c.w};
+#pragma unroll
+                for (int bp = 0; bp < 4; ++bp) {
+                    u64 x2[8], xm2[4];
+#pragma unroll
+                    for (int cq = 0; cq < 4; ++cq) { const ulonglong2 t = sh.sx[(bp * 4 + cq) * 32 + jc]; x2[2 * cq] = t.x; x2[2 * cq + 1] = t.y; }
+#pragma unroll
+                    for (int pq = 0; pq < 2; ++pq) { const ulonglong2 t = sh.sm[(bp * 2 + pq) * 32 + jc]; xm2[2 * pq] = t.x; xm2[2 * pq + 1] = t.y; }
+                    {
+                        u64 v[32], q[4];
+                        pair_states(sh.tab, swa[bp], v);
+                        pair_coefs(cwa[bp], kc, q);
+                        acc = fma2(pair_dot(v, q, x2, xm2), code_scale_pair(ka.cd, bp, kc), acc);
+                    }
+                    if (MODE == MODE_GU) {
+                        u64 v[32], q[4];
+                        pair_states(sh.tab, swb[bp], v);
+                        pair_coefs(cwb[bp], kc, q);
+                        accu = fma2(pair_dot(v, q, x2, xm2), code_scale_pair(kb.cd, bp, kc), accu);
+                    }
+                }
+            }
+            const float s = group_sum(pair_total(acc), lpr) * sca;
+            float su = 0.0f;
+            if (MODE == MODE_GU) su = group_sum(pair_total(accu), lpr) * scb;
+            if (ok && jc == 0) store_out<MODE>(a, pair, r, s, su);
+            ka = na;
+            if (MODE == MODE_GU) kb = nb;
+        }
+        // this block's row steps of the pair are stored: publish their number
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) atomicAdd(MODE == MODE_GU ? p.sy.ready + pair : p.sy.done + pair / p.top_k, (unsigned) (s_hi - s_lo));
+    }
+}
+
+__global__ void __launch_bounds__(MV_THREADS, 2) mv_step_kernel(StepParams p, KConst kc, int lg_d, int lg_ff) {
+    __shared__ StepShared sh;
+    load_stream_tab(sh.tab, p.G, threadIdx.x, MV_THREADS);
+    if (threadIdx.x == 0) sh.abort = 0;
+    grid_dependents_go();
+    grid_dependency_wait();   // everything below may read what the previous kernel in the stream wrote
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int P = p.T * p.top_k;
+    if (warp < p.T) {         // the router: one warp per token, every block the same picks; block 0 stores them
+        const float* l = p.logits + (size_t) warp * p.ld;
+        if (p.n_exp <= 128) route_row<4>(p.n_exp, p.top_k, l, lane, sh.r_ind + warp * p.top_k, sh.r_wt + warp * p.top_k);
+        else if (p.n_exp <= 512) route_row<16>(p.n_exp, p.top_k, l, lane, sh.r_ind + warp * p.top_k, sh.r_wt + warp * p.top_k);
+        else route_row<32>(p.n_exp, p.top_k, l, lane, sh.r_ind + warp * p.top_k, sh.r_wt + warp * p.top_k);
+    }
+    __syncthreads();
+    if (blockIdx.x == 0 && (int) threadIdx.x < P) {
+        p.ind_out[threadIdx.x] = sh.r_ind[threadIdx.x];
+        p.wt_out[threadIdx.x] = sh.r_wt[threadIdx.x];
+    }
+    const unsigned rs_gu = (unsigned) ((p.ff + (32 >> lg_d) - 1) / (32 >> lg_d));      // row steps of a pair's gate + up rows
+    step_phase<MODE_GU>(p, kc, sh, P, lg_d, rs_gu);
+    if (!sh.abort) step_phase<MODE_ROUND>(p, kc, sh, P, lg_ff, rs_gu);
+    // combine: out[t][i] = sum_j wt[t][j] D[t * k + j][i], plain f32, j ascending (q4_combine_kernel's sum); item = (token, 256 columns)
+    if (!sh.abort) {
+        const int cpr = (p.d + MV_THREADS - 1) / MV_THREADS, rpw_d = 32 >> lg_ff;
+        const unsigned rs_down = (unsigned) ((p.d + rpw_d - 1) / rpw_d) * (unsigned) p.top_k;
+        for (int item = blockIdx.x; item < p.T * cpr; item += gridDim.x) {
+            const int t = item / cpr, i = (item - t * cpr) * MV_THREADS + (int) threadIdx.x;
+            if (threadIdx.x == 0 && !step_wait(p.sy.done + t, rs_down, p.sy.status)) sh.abort = 1;
+            __syncthreads();
+            if (sh.abort) break;
+            if (i < p.d) {
+                float acc = 0.0f;
+                for (int j = 0; j < p.top_k; ++j) acc += sh.r_wt[t * p.top_k + j] * __ldcg(p.D + ((size_t) t * p.top_k + j) * p.d + i);
+                p.out[(size_t) t * p.d + i] = acc;
+            }
+        }
+    }
+    // the last block to finish clears the counters for the next launch
+    __syncthreads();
+    if (threadIdx.x == 0) sh.abort = atomicInc(p.sy.fin, gridDim.x - 1) == gridDim.x - 1 ? 2 : 0;
+    __syncthreads();
+    if (sh.abort == 2) {
+        for (int i = threadIdx.x; i < P; i += MV_THREADS) p.sy.ready[i] = 0u;
+        for (int i = threadIdx.x; i < p.T; i += MV_THREADS) p.sy.done[i] = 0u;
+    }
+}
+
+
 // ---- pairs grouped by expert: one expansion per distinct slice ---------------------------------------------------------
 // Rows of 1, 2, 4, .. 32 chunks (K = 64 .. 2048).  Every block builds the same plan in its prologue: the pair list is
 // sorted by slice in shared memory, runs of pairs that use the same slice are cut into UNITS of at most GRP_NT pairs, and
@@ -1023,6 +1258,17 @@ static void launch_mv3(cudaStream_t s, const MvParams& a, int T) {
     count_launch();
 }
 
+// The decode step in one launch; false (nothing launched) when a size is outside what the pair kernel serves.
+static bool launch_mv_step(cudaStream_t s, const StepParams& p) {
+    const int cd = p.d / 64, cf = p.ff / 64;
+    if (p.T < 1 || p.T > MV_MAXT || p.top_k < 1 || p.top_k > 32 || p.T * p.top_k > 256 || p.n_exp < p.top_k || p.n_exp > 32 * ROUTE_PER_LANE) return false;
+    if (p.d % 64 || p.ff % 64 || cd < 1 || cf < 1 || (cd & (cd - 1)) || (cf & (cf - 1)) || cd > 32 || cf > 32) return false;
+    if (!aligned16(p.x) || p.xs % 4 || !aligned16(p.A) || !aligned16(p.D)) return false;
+    launch(mv_step_kernel, sm_count() * 2, MV_THREADS, 0, s, p, kconst(), log2_floor(cd), log2_floor(cf));
+    count_launch();
+    return true;
+}
+
 bool launch_q4_mv(cudaStream_t s, const WSlice& w, int K, int R, const float* x, int xs, float* y, int ys, int T, int add);
 void launch_bf16_mv(cudaStream_t s, const WSlice& w, int K, int R, const float* x, int xs, float* y, int ys, int T, int add);
 bool launch_bf16_mm_skinny(cudaStream_t s, const WSlice& w, int K, int R, const float* x, int xs, float* y, int ys, int T, int add);
@@ -1094,6 +1340,20 @@ void nsl_mv_gu_routed(cudaStream_t s, const WSlice* wg, const WSlice* wu, int K,
     MvParams a = {wg, wu, WSlice{}, NULL, x, out, G, K, R, T * top_k, top_k, xs, ys, 0, raw, NULL, NULL, 0};
     const RouteFuse rf = {logits, ld, n_exp, top_k, T, ind, wt};
     launch_mv<MODE_GU>(s, a, 1, rf);
+}
+
+// The whole decode step of an expert layer (router, gate + up + SwiGLU, down, combine) as one launch: 1 = launched, 0 = a
+// size is outside what it serves (nothing launched: the caller issues the three launches).  sync: 4 * (2 + T + T * top_k)
+// bytes of device memory, zero before the first call; every call leaves its counters zero.  sync[0] is the status word:
+// 1 after a launch in which a bounded wait ran out (its output is not valid), for the caller to read and clear.
+// A and D are the caller's work buffers [T * top_k][ff] and [T * top_k][d].
+int nsl_mv_step(cudaStream_t s, const WSlice* wg, const WSlice* wu, const WSlice* wd, int d, int ff, const float* x, int xs, int n_exp,
+                int top_k, const float* logits, int ld, int T, int32_t* ind, float* wt, float* A, float* D, float* out, int raw,
+                unsigned* sync, const uint32_t* G) {
+    if (!sync || T < 1 || top_k < 1) return 0;
+    StepParams p = {wg, wu, wd, x, logits, A, D, out, ind, wt, G, xs, ld, n_exp, top_k, T, d, ff, raw,
+                    {sync + 2 + T, sync + 2, sync + 1, (int*) sync}};
+    return launch_mv_step(s, p) ? 1 : 0;
 }
 
 // Expert-parallel forms: a compacted pair list whose length lives on the device.  Pair p uses slice sel[p] and input

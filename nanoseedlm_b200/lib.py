@@ -103,6 +103,7 @@ PROTOTYPES = {
     "nsl_bucket_noalloc": (None, [_vp, _vp, _i, _i, _vp, _vp, _vp]),
     "nsl_route": (None, [_vp, _i, _i, _vp, _i, _vp, _vp, _i]),
     "nsl_swiglu_packed": (None, [_vp, _vp, _vp, _vp, _i]),
+    "nsl_mv_step": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp, _i, _i, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp]),
     "nsl_mv_raw": (None, [_vp, _vp, _i, _i, _vp, _i, _vp, _i, _vp, _i, _i, _vp]),
     "nsl_mv_gu_raw": (None, [_vp, _vp, _vp, _i, _i, _vp, _i, _vp, _i, _vp, _i, _i, _vp]),
     "nsl_decode_f32": (None, [_vp, WSlice, _i, _i, _vp, _vp]),
@@ -136,6 +137,8 @@ PROTOTYPES = {
     "nsl_moe_set_rounding": (None, [_vp, _i]),
     "nsl_moe_set_dependent_launch": (None, [_vp, _i]),
     "nsl_moe_set_direct_output": (None, [_vp, _i]),
+    "nsl_moe_set_one_launch": (None, [_vp, _i]),
+    "nsl_moe_step_status": (_i, [_vp]),
     # include/nslm_pack.h
     "nsl_blk4_bytes": (_sz, [_i, _i, _i]),
     "nsl_blk4_split": (_i, [_vp, _sz, _i, _i, _i, _vp, _vp, _vp, _vp]),

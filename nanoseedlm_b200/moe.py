@@ -183,6 +183,14 @@ class Moe:
         """Whether the pinned forms' combine kernel stores straight into the pinned output (default) or a copy brings it."""
         self.lib.nsl_moe_set_direct_output(self.h, int(on))
 
+    def set_one_launch(self, on):
+        """Whether a decode step is one launch or (default) three dependent launches."""
+        self.lib.nsl_moe_set_one_launch(self.h, int(on))
+
+    def step_status(self):
+        """0, or 1 when a wait inside a one-launch step ran out since the last call."""
+        return int(self.lib.nsl_moe_step_status(self.h))
+
     def forward_pinned(self, T):
         """Inputs already in self.hx / self.hlogits; the result lands in self.hout."""
         if self.lib.nsl_moe_forward_pinned(self.h, T):

@@ -181,3 +181,95 @@ def test_dependent_launches_change_nothing(oracle):
     for o, w in zip(outs, plain):
         assert np.array_equal(o.cpu().numpy(), w)
     m.close()
+
+
+@pytest.mark.parametrize("d,ff,E,k", [(512, 128, 24, 8), (2048, 512, 40, 8), (256, 64, 16, 4)])
+def test_the_decode_step_as_one_launch_gives_the_three_launches_bits(oracle, d, ff, E, k):
+    """nsl_mv_step (router, gate + up + SwiGLU, down, combine as phases of one grid that wait on counters) against the three
+    dependent launches: the same bits for every row count in turn (the counters are left clean whatever T was), with and
+    without the bf16 rounding points, directly and replayed from a CUDA graph; no wait runs out."""
+    import torch
+    from nanoseedlm_b200 import moe
+    h = moe.HostLayer(oracle, d, ff, E, seed=d + 3)
+    layer = moe.DeviceLayer.from_host(h)
+    m = moe.Moe(layer, k, 8)
+    cases = []
+    for T in (8, 1, 5, 8, 2, 1, 7):
+        x = oracle.normal(90 + T, T * d, bf16=True).reshape(T, d)
+        l = oracle.normal(95 + T, T * E).reshape(T, E)
+        cases.append((x, l))
+    for rounding in (True, False):
+        m.set_rounding(rounding)
+        m.set_one_launch(False)
+        want = [(o.copy(), i.copy()) for o, i in (m.forward_host(x, l) for x, l in cases)]
+        m.set_one_launch(True)
+        for rep in range(3):
+            for (x, l), (wo, wi) in zip(cases, want):
+                o, i = m.forward_host(x, l)
+                assert np.array_equal(i, wi)
+                assert np.array_equal(o.view(np.uint32), wo.view(np.uint32))
+        assert m.step_status() == 0
+    m.set_rounding(True)
+    x, l = cases[0]
+    dx, dl, out = torch.from_numpy(x).cuda(), torch.from_numpy(l).cuda(), torch.zeros(8, d, device="cuda")
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        m.forward_dev(dx, dl, out, stream=stream.cuda_stream)
+        stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            for _ in range(4):
+                m.forward_dev(dx, dl, out, stream=stream.cuda_stream)
+        out.zero_()
+        g.replay()
+        stream.synchronize()
+    m.set_one_launch(False)
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), m.forward_host(x, l)[0].view(np.uint32))
+    assert m.step_status() == 0
+    m.close()
+
+
+def test_one_launch_step_called_directly_its_status_word_and_refusals(oracle):
+    """nsl_mv_step through its own entry point: the caller's sync block stays zero but for the status word; a status word
+    that is already set (as after a wait that ran out) is left for the caller and does not wedge the next call; sizes it
+    does not serve are refused with 0 and nothing launched."""
+    import torch
+    from nanoseedlm_b200 import kernels, lib as L, moe
+    lib = L.load()
+    d, ff, E, k, T = 512, 128, 24, 8, 6
+    h = moe.HostLayer(oracle, d, ff, E, seed=31)
+    layer = moe.DeviceLayer.from_host(h)
+    m = moe.Moe(layer, k, 8)
+    x = oracle.normal(7, T * d, bf16=True).reshape(T, d)
+    logits = oracle.normal(8, T * E).reshape(T, E)
+    want, wind = m.forward_host(x, logits)
+    dx, dl = torch.from_numpy(x).cuda(), torch.from_numpy(logits).cuda()
+    P = T * k
+    A, D, out = torch.zeros(P, ff, device="cuda"), torch.zeros(P, d, device="cuda"), torch.zeros(T, d, device="cuda")
+    ind, wt = torch.zeros(P, dtype=torch.int32, device="cuda"), torch.zeros(P, device="cuda")
+    sync = torch.zeros(2 + T + P, dtype=torch.int32, device="cuda")
+    G = kernels.stream_table()
+
+    def call(dd=d, TT=T):
+        return lib.nsl_mv_step(None, layer.gate.table.data_ptr(), layer.up.table.data_ptr(), layer.down.table.data_ptr(), dd, ff, dx.data_ptr(), d, E, k,
+                               dl.data_ptr(), E, TT, ind.data_ptr(), wt.data_ptr(), A.data_ptr(), D.data_ptr(), out.data_ptr(), 0, sync.data_ptr(),
+                               G.data_ptr())
+
+    for _ in range(3):
+        assert call() == 1
+        torch.cuda.synchronize()
+        assert not sync.cpu().numpy().any()
+        assert np.array_equal(out.cpu().numpy().view(np.uint32), want.view(np.uint32))
+        assert np.array_equal(ind.cpu().numpy().reshape(T, k), wind)
+    sync[0] = 1                      # the word a timed-out wait leaves behind
+    assert call() == 1
+    torch.cuda.synchronize()
+    after = sync.cpu().numpy()
+    assert after[0] == 1 and not after[1:].any()
+    sync[0] = 0
+    out.zero_()
+    assert call() == 1
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), want.view(np.uint32))
+    assert call(dd=d + 8) == 0 and call(TT=9) == 0      # not 64 * 2^j; more rows than a decode step has
+    m.close()
