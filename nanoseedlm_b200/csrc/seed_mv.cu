@@ -307,10 +307,9 @@ __global__ void __launch_bounds__(MV_THREADS, 2) mv_pair_kernel(MvParams a, KCon
 #pragma unroll
                     for (int pq = 0; pq < 2; ++pq) { const ulonglong2 t = sm[(bp * 2 + pq) * 32 + jc]; xm2[2 * pq] = t.x; xm2[2 * pq + 1] = t.y; }
                     if (PF == 4) {
-                        u64 v[32], q[4];
-                        pair_states(tab, swa[bp], v);
+                        u64 q[4];
                         pair_coefs(cwa[bp], kc, q);
-                        acc = fma2(pair_dot(v, q, x2, xm2), code_scale_pair(ka.cd, bp, kc), acc);
+                        acc = fma2(pair_expand_dot(tab, swa[bp], q, x2, xm2), code_scale_pair(ka.cd, bp, kc), acc);
                     } else {
                         u64 v[24], q[3];
                         pair_states3(tab, swa[bp], v);
@@ -318,10 +317,9 @@ __global__ void __launch_bounds__(MV_THREADS, 2) mv_pair_kernel(MvParams a, KCon
                         acc = fma2(pair_dot3(v, q, x2, xm2), code_scale_pair3(cwa[bp], kc), acc);
                     }
                     if (MODE == MODE_GU && PF == 4) {
-                        u64 v[32], q[4];
-                        pair_states(tab, swb[bp], v);
+                        u64 q[4];
                         pair_coefs(cwb[bp], kc, q);
-                        accu = fma2(pair_dot(v, q, x2, xm2), code_scale_pair(kb.cd, bp, kc), accu);
+                        accu = fma2(pair_expand_dot(tab, swb[bp], q, x2, xm2), code_scale_pair(kb.cd, bp, kc), accu);
                     } else if (MODE == MODE_GU) {
                         u64 v[24], q[3];
                         pair_states3(tab, swb[bp], v);
@@ -500,16 +498,14 @@ __device__ __forceinline__ void step_phase(const StepParams& p, const KConst& kc
 #pragma unroll
                     for (int pq = 0; pq < 2; ++pq) { const ulonglong2 t = sh.sm[(bp * 2 + pq) * 32 + jc]; xm2[2 * pq] = t.x; xm2[2 * pq + 1] = t.y; }
                     {
-                        u64 v[32], q[4];
-                        pair_states(sh.tab, swa[bp], v);
+                        u64 q[4];
                         pair_coefs(cwa[bp], kc, q);
-                        acc = fma2(pair_dot(v, q, x2, xm2), code_scale_pair(ka.cd, bp, kc), acc);
+                        acc = fma2(pair_expand_dot(sh.tab, swa[bp], q, x2, xm2), code_scale_pair(ka.cd, bp, kc), acc);
                     }
                     if (MODE == MODE_GU) {
-                        u64 v[32], q[4];
-                        pair_states(sh.tab, swb[bp], v);
+                        u64 q[4];
                         pair_coefs(cwb[bp], kc, q);
-                        accu = fma2(pair_dot(v, q, x2, xm2), code_scale_pair(kb.cd, bp, kc), accu);
+                        accu = fma2(pair_expand_dot(sh.tab, swb[bp], q, x2, xm2), code_scale_pair(kb.cd, bp, kc), accu);
                     }
                 }
             }
@@ -717,11 +713,11 @@ __device__ __noinline__ void unit_rows(UnitArgs ua, Chunk ka, Chunk kb) {
         u64 acc[NT], accu[NT];
 #pragma unroll
         for (int t = 0; t < NT; ++t) acc[t] = accu[t] = 0ull;
-        if (NT == 1 && MODE == MODE_GU) {      // one pair: its inputs are read once per block pair for both matrices
+        if (NT == 1) {      // one pair: the pair kernel's loop (its inputs are read once per block pair for both matrices)
             Chunk na, nb;
             if (more) {   // the next step's streams fly during this step's expansion
                 na = load_chunk3(ua.sa, ua.ca, ua.da, (size_t) rn * lpr + jc);
-                nb = load_chunk3(ua.sb, ua.cb, ua.db, (size_t) rn * lpr + jc);
+                if (MODE == MODE_GU) nb = load_chunk3(ua.sb, ua.cb, ua.db, (size_t) rn * lpr + jc);
             }
             if (ok) {
                 const uint32_t swa[4] = {ka.s.x, ka.s.y, ka.s.z, ka.s.w}, cwa[4] = {ka.c.x, ka.c.y, ka.c.z, ka.c.w};
@@ -733,21 +729,19 @@ __device__ __noinline__ void unit_rows(UnitArgs ua, Chunk ka, Chunk kb) {
                     for (int cq = 0; cq < 4; ++cq) { const ulonglong2 u = sh.sx[0][(bp * 4 + cq) * 32 + jc]; x2[2 * cq] = u.x; x2[2 * cq + 1] = u.y; }
                     offsets_from_sum(sh.ss[0][bp * 32 + jc], xm2);
                     {
-                        u64 v[32], q[4];
-                        pair_states(sh.tab, swa[bp], v);
+                        u64 q[4];
                         pair_coefs(cwa[bp], kc, q);
-                        acc[0] = fma2(pair_dot(v, q, x2, xm2), code_scale_pair(ka.cd, bp, kc), acc[0]);
+                        acc[0] = fma2(pair_expand_dot(sh.tab, swa[bp], q, x2, xm2), code_scale_pair(ka.cd, bp, kc), acc[0]);
                     }
-                    {
-                        u64 v[32], q[4];
-                        pair_states(sh.tab, swb[bp], v);
+                    if (MODE == MODE_GU) {
+                        u64 q[4];
                         pair_coefs(cwb[bp], kc, q);
-                        accu[0] = fma2(pair_dot(v, q, x2, xm2), code_scale_pair(kb.cd, bp, kc), accu[0]);
+                        accu[0] = fma2(pair_expand_dot(sh.tab, swb[bp], q, x2, xm2), code_scale_pair(kb.cd, bp, kc), accu[0]);
                     }
                 }
             }
             ka = na;
-            kb = nb;
+            if (MODE == MODE_GU) kb = nb;
         } else {
             // several pairs (or one matrix): a matrix's streams for the next step are requested as soon as this step has
             // used them up, into the registers they leave free, so no second set of stream registers is held
