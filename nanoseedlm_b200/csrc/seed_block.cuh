@@ -409,8 +409,10 @@ __device__ __forceinline__ u64 code_scale_pair3(uint32_t nw, const KConst& k) {
 // Exact form for two adjacent blocks at once (the GEMM's weight tiles): w2[c] = {weight c of the even block, of the odd
 // block}, bit for bit as block_weights gives them.  sc2 = {exact_scale45 of the even block, of the odd block}.
 __device__ __forceinline__ void pair_weights(const StreamTab& tab, uint32_t sw, uint32_t cw, u64 sc2, const KConst& k, u64* w2) {
-    u64 v[32], q[4];
-    pair_states(tab, sw, v);
+    u64 q[4];
+    const uint32_t g0 = lut_word(tab.lo, __byte_perm(sw, 0, 0x4440)) ^ lut_word(tab.hi, __byte_perm(sw, 0, 0x4441));
+    const uint32_t g1 = lut_word(tab.lo, __byte_perm(sw, 0, 0x4442)) ^ lut_word(tab.hi, __byte_perm(sw, 0, 0x4443));
+    const uint32_t a0 = __byte_perm(sw, g0, 0x5410), a1 = __byte_perm(sw, g1, 0x5432);
     const uint32_t c1 = cw >> 16;
     q[0] = add2(and_xor_pair<0x000Fu>(cw, c1, k.cxor_x[0]), pack2(k.coff_x[0], k.coff_x[0]));
     q[1] = add2(and_xor_pair<0x00F0u>(cw, c1, k.cxor_x[1]), pack2(k.coff_x[1], k.coff_x[1]));
@@ -420,9 +422,18 @@ __device__ __forceinline__ void pair_weights(const StreamTab& tab, uint32_t sw, 
                         fma2(q[2], pack2(-2.938735877055719e-39f, -2.938735877055719e-39f),
                              fma2(q[1], pack2(-1.4693679385278594e-39f, -1.4693679385278594e-39f),
                                   mul2(q[0], pack2(-7.346839692639297e-40f, -7.346839692639297e-40f)))));
-#pragma unroll
-    for (int c = 0; c < 8; ++c)      // the centring term first: every partial sum stays an exact integer multiple of 2^-45 below 2^24
-        w2[c] = mul2(fma2(q[3], v[4 * c + 3], fma2(q[2], v[4 * c + 2], fma2(q[1], v[4 * c + 1], fma2(q[0], v[4 * c], kq)))), sc2);
+    // weight by weight (its shifts and ANDs, then its multiply-adds: the two pipes alternate in program order); the centring
+    // term first: every partial sum stays an exact integer multiple of 2^-45 below 2^24
+#define NSL_WX(C)                                                                                               \
+    {                                                                                                           \
+        const uint32_t y0 = weight_word<C>(a0, g0), y1 = weight_word<C>(a1, g1);                                \
+        w2[C] = mul2(fma2(q[3], pack2(state_value<3>(y0), state_value<3>(y1)),                                  \
+                          fma2(q[2], pack2(state_value<2>(y0), state_value<2>(y1)),                             \
+                               fma2(q[1], pack2(state_value<1>(y0), state_value<1>(y1)),                        \
+                                    fma2(q[0], pack2(state_value<0>(y0), state_value<0>(y1)), kq)))), sc2);     \
+    }
+    NSL_WX(0) NSL_WX(1) NSL_WX(2) NSL_WX(3) NSL_WX(4) NSL_WX(5) NSL_WX(6) NSL_WX(7)
+#undef NSL_WX
 }
 // Two f32 -> one word of two bf16 (round to nearest even), low half = a.
 __device__ __forceinline__ uint32_t bf16x2_bits(float a, float b) {
