@@ -1195,8 +1195,8 @@ def main():
 
 
 def measure_p3(K, W):
-    """The config-1 / config-2 layer with P = 3 (MF_SEED4) experts: 8 decode rows through kc_mv_gu / kc_mv_sel (the any-shape
-    mat-vec kernel serves this format) and 512 prompt rows through kc_bucket + kc_mm_grouped_dev (the tcgen05 GEMM with the
+    """The config-1 / config-2 layer with P = 3 (MF_SEED4) experts: 8 decode rows through kc_mv_gu / kc_mv_sel (the pair
+    kernel's P = 3 form) and 512 prompt rows through kc_bucket + kc_mm_grouped_dev (the tcgen05 GEMM with the
     P = 3 tile producer).  4 layers rotated (0.8 GB of packed streams)."""
     import torch
     from nanoseedlm_b200 import kernels, lib as L
@@ -1285,7 +1285,7 @@ def secondary(name, K, W, peaks, peak_kind, sms, args, sm_mhz=None):
     if name == "p3":
         r = measure_p3(K, W)
         return dict(r, workload=f"the config-1 / config-2 layer with P = 3 (MF_SEED4) experts: hidden {D}, {E} experts of intermediate {FF}, top-{TOPK}; "
-                                "8 decode rows (any-shape mat-vec kernel) and 512 prompt rows (tcgen05 GEMM with the P = 3 tile producer)")
+                                "8 decode rows (the pair kernel's P = 3 form) and 512 prompt rows (tcgen05 GEMM with the P = 3 tile producer)")
     if name == "lmhead":
         r = measure_lmhead(8, min(K, 300), W)
         gbs = r["bytes"] / (r["mv_us"] * 1e-6) / 1e9

@@ -263,17 +263,20 @@ __device__ __forceinline__ float states_dot3(const float* v, const float* q, con
 }
 // The eight weights bit for bit: q"_p = q_p 2^(99-p), products in units of 2^-46, sc46 = fl(R32 2^e) * 2^46.
 __device__ __forceinline__ void block_weights3(uint32_t a, uint32_t g, uint32_t nib, float sc46, const KConst& k, float* w) {
-    float v[24], q[3];
-    block_states3(a, g, v);
+    float q[3];
     q[0] = coef_raw<1>(nib, k.cxor_x[1]) + k.coff_x[1];
     q[1] = coef_raw<2>(nib, k.cxor_x[2]) + k.coff_x[2];
     q[2] = coef_raw<3>(nib, k.cxor_x[3]) + k.coff_x[3];
     const float kq = __fmaf_rn(q[2], -2.938735877055719e-39f, __fmaf_rn(q[1], -1.4693679385278594e-39f, __fmul_rn(q[0], -7.346839692639297e-40f)));
-#pragma unroll
-    for (int c = 0; c < 8; ++c) {
-        const float t = __fmaf_rn(q[2], v[3 * c + 2], __fmaf_rn(q[1], v[3 * c + 1], __fmul_rn(q[0], v[3 * c])));
-        w[c] = __fmul_rn(__fadd_rn(t, kq), sc46);
+    // weight by weight: its shift and three ANDs, then its arithmetic, so that the two pipes alternate in program order
+#define NSL_WX3(C)                                                                                                                        \
+    {                                                                                                                                     \
+        const uint32_t y = weight_word3<C>(a, g);                                                                                         \
+        const float t = __fmaf_rn(q[2], state_value<2>(y), __fmaf_rn(q[1], state_value<1>(y), __fmul_rn(q[0], state_value<0>(y))));      \
+        w[C] = __fmul_rn(__fadd_rn(t, kq), sc46);                                                                                         \
     }
+    NSL_WX3(0) NSL_WX3(1) NSL_WX3(2) NSL_WX3(3) NSL_WX3(4) NSL_WX3(5) NSL_WX3(6) NSL_WX3(7)
+#undef NSL_WX3
 }
 
 // ---- two adjacent blocks as f32x2 pairs {even block, odd block} ----------------------------------------------------
@@ -400,6 +403,23 @@ __device__ __forceinline__ u64 pair_dot3(const u64* v, const u64* q, const u64* 
         d1 = fma2(x2[c], v[3 * c + 1], d1);
         d2 = fma2(x2[c], v[3 * c + 2], d2);
     }
+    return fma2(q[2], d2, fma2(q[1], d1, mul2(q[0], d0)));
+}
+// pair_states3 + pair_dot3 weight by weight (see pair_expand_dot): the same bits.
+__device__ __forceinline__ u64 pair_expand_dot3(const StreamTab& tab, uint32_t sw, const u64* q, const u64* x2, const u64* xm2) {
+    const uint32_t g0 = lut_word(tab.lo, __byte_perm(sw, 0, 0x4440)) ^ lut_word(tab.hi, __byte_perm(sw, 0, 0x4441));
+    const uint32_t g1 = lut_word(tab.lo, __byte_perm(sw, 0, 0x4442)) ^ lut_word(tab.hi, __byte_perm(sw, 0, 0x4443));
+    const uint32_t a0 = __byte_perm(sw, g0, 0x5410), a1 = __byte_perm(sw, g1, 0x5432);
+    u64 d0 = xm2[0], d1 = xm2[1], d2 = xm2[2];
+#define NSL_W23(C)                                                                   \
+    {                                                                                \
+        const uint32_t y0 = weight_word3<C>(a0, g0), y1 = weight_word3<C>(a1, g1);   \
+        d0 = fma2(x2[C], pack2(state_value<0>(y0), state_value<0>(y1)), d0);         \
+        d1 = fma2(x2[C], pack2(state_value<1>(y0), state_value<1>(y1)), d1);         \
+        d2 = fma2(x2[C], pack2(state_value<2>(y0), state_value<2>(y1)), d2);         \
+    }
+    NSL_W23(0) NSL_W23(1) NSL_W23(2) NSL_W23(3) NSL_W23(4) NSL_W23(5) NSL_W23(6) NSL_W23(7)
+#undef NSL_W23
     return fma2(q[2], d2, fma2(q[1], d1, mul2(q[0], d0)));
 }
 __device__ __forceinline__ u64 code_scale_pair3(uint32_t nw, const KConst& k) {

@@ -311,20 +311,18 @@ __global__ void __launch_bounds__(MV_THREADS, 2) mv_pair_kernel(MvParams a, KCon
                         pair_coefs(cwa[bp], kc, q);
                         acc = fma2(pair_expand_dot(tab, swa[bp], q, x2, xm2), code_scale_pair(ka.cd, bp, kc), acc);
                     } else {
-                        u64 v[24], q[3];
-                        pair_states3(tab, swa[bp], v);
+                        u64 q[3];
                         pair_coefs3(cwa[bp], kc, q);
-                        acc = fma2(pair_dot3(v, q, x2, xm2), code_scale_pair3(cwa[bp], kc), acc);
+                        acc = fma2(pair_expand_dot3(tab, swa[bp], q, x2, xm2), code_scale_pair3(cwa[bp], kc), acc);
                     }
                     if (MODE == MODE_GU && PF == 4) {
                         u64 q[4];
                         pair_coefs(cwb[bp], kc, q);
                         accu = fma2(pair_expand_dot(tab, swb[bp], q, x2, xm2), code_scale_pair(kb.cd, bp, kc), accu);
                     } else if (MODE == MODE_GU) {
-                        u64 v[24], q[3];
-                        pair_states3(tab, swb[bp], v);
+                        u64 q[3];
                         pair_coefs3(cwb[bp], kc, q);
-                        accu = fma2(pair_dot3(v, q, x2, xm2), code_scale_pair3(cwb[bp], kc), accu);
+                        accu = fma2(pair_expand_dot3(tab, swb[bp], q, x2, xm2), code_scale_pair3(cwb[bp], kc), accu);
                     }
                 }
             }
