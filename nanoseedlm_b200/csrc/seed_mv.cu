@@ -93,21 +93,6 @@ __device__ __forceinline__ Chunk load_chunk(const WSlice& w, size_t chunk_index)
     return k;
 }
 
-// One chunk (four block pairs) against one token's 64 inputs held in registers as pairs:
-// x2[bp][c] = {x[16 bp + c], x[16 bp + 8 + c]}, xm2[bp][p] likewise.  acc2 = {sum over even blocks, sum over odd blocks}.
-__device__ __forceinline__ u64 chunk_dot(const StreamTab& tab, const KConst& kc, const Chunk& k, const u64* x2, const u64* xm2,
-                                         u64 acc2) {
-    const uint32_t sw[4] = {k.s.x, k.s.y, k.s.z, k.s.w}, cw[4] = {k.c.x, k.c.y, k.c.z, k.c.w};
-#pragma unroll
-    for (int bp = 0; bp < 4; ++bp) {
-        u64 v[32], q[4];
-        pair_states(tab, sw[bp], v);
-        pair_coefs(cw[bp], kc, q);
-        const u64 e2 = code_scale_pair(k.cd, bp, kc);
-        acc2 = fma2(pair_dot(v, q, x2 + 8 * bp, xm2 + 4 * bp), e2, acc2);
-    }
-    return acc2;
-}
 __device__ __forceinline__ float pair_total(u64 acc2) {
     float lo, hi;
     unpack2(acc2, lo, hi);
