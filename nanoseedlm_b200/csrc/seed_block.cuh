@@ -375,37 +375,14 @@ __device__ __forceinline__ u64 pair_expand_dot(const StreamTab& tab, uint32_t sw
 // The same for two adjacent P = 3 blocks (see block_states3 / block_coefs3 / states_dot3): 24 state-value pairs, the three
 // coefficient pairs of the two nibble words packed in nw, and {2^(code - 15) of the even block, of the odd block} from the
 // words' low nibbles.
-__device__ __forceinline__ void pair_states3(const StreamTab& tab, uint32_t sw, u64* v) {
-    const uint32_t g0 = lut_word(tab.lo, __byte_perm(sw, 0, 0x4440)) ^ lut_word(tab.hi, __byte_perm(sw, 0, 0x4441));
-    const uint32_t g1 = lut_word(tab.lo, __byte_perm(sw, 0, 0x4442)) ^ lut_word(tab.hi, __byte_perm(sw, 0, 0x4443));
-    const uint32_t a0 = __byte_perm(sw, g0, 0x5410), a1 = __byte_perm(sw, g1, 0x5432);
-#define NSL_V23(C)                                                                   \
-    {                                                                                \
-        const uint32_t y0 = weight_word3<C>(a0, g0), y1 = weight_word3<C>(a1, g1);   \
-        v[3 * C + 0] = pack2(state_value<0>(y0), state_value<0>(y1));                \
-        v[3 * C + 1] = pack2(state_value<1>(y0), state_value<1>(y1));                \
-        v[3 * C + 2] = pack2(state_value<2>(y0), state_value<2>(y1));                \
-    }
-    NSL_V23(0) NSL_V23(1) NSL_V23(2) NSL_V23(3) NSL_V23(4) NSL_V23(5) NSL_V23(6) NSL_V23(7)
-#undef NSL_V23
-}
 __device__ __forceinline__ void pair_coefs3(uint32_t nw, const KConst& k, u64* q) {
     const uint32_t n1 = nw >> 16;
     q[0] = add2(and_xor_pair<0x00F0u>(nw, n1, k.cxor[1]), pack2(k.coff[1], k.coff[1]));
     q[1] = add2(and_xor_pair<0x0F00u>(nw, n1, k.cxor[2]), pack2(k.coff[2], k.coff[2]));
     q[2] = add2(and_xor_pair<0xF000u>(nw, n1, k.cxor[3]), pack2(k.coff[3], k.coff[3]));
 }
-__device__ __forceinline__ u64 pair_dot3(const u64* v, const u64* q, const u64* x2, const u64* xm2) {
-    u64 d0 = xm2[0], d1 = xm2[1], d2 = xm2[2];
-#pragma unroll
-    for (int c = 0; c < 8; ++c) {
-        d0 = fma2(x2[c], v[3 * c + 0], d0);
-        d1 = fma2(x2[c], v[3 * c + 1], d1);
-        d2 = fma2(x2[c], v[3 * c + 2], d2);
-    }
-    return fma2(q[2], d2, fma2(q[1], d1, mul2(q[0], d0)));
-}
-// pair_states3 + pair_dot3 weight by weight (see pair_expand_dot): the same bits.
+// The P = 3 form of pair_expand_dot: 24 state-value pairs, weight by weight; d_p = xm_p + sum_c x_c v_cp (c ascending),
+// result = (q0 d0 + q1 d1) + q2 d2.
 __device__ __forceinline__ u64 pair_expand_dot3(const StreamTab& tab, uint32_t sw, const u64* q, const u64* x2, const u64* xm2) {
     const uint32_t g0 = lut_word(tab.lo, __byte_perm(sw, 0, 0x4440)) ^ lut_word(tab.hi, __byte_perm(sw, 0, 0x4441));
     const uint32_t g1 = lut_word(tab.lo, __byte_perm(sw, 0, 0x4442)) ^ lut_word(tab.hi, __byte_perm(sw, 0, 0x4443));
